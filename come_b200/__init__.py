@@ -1,0 +1,15 @@
+"""come_b200 -- B200 (sm_100a) kernels for the Co-Me accelerated-inference hot path.
+
+Host side in Python/PyTorch (device memory, streams), compute in ``libcome_b200.so`` behind a C ABI
+(``include/come_b200.h``).  The modules mirror the operator surface of the reference project:
+
+* :mod:`come_b200.co_me_cuext`          -- ``co_me_token_merge_cuda`` / ``co_me_token_split_cuda``
+* :mod:`come_b200.flash_attn_fwd_cuda`  -- ``varlen_fwd`` / ``varlen_fwd_w_perkey_bias``
+* :mod:`come_b200.flash_attn`           -- ``flash_attn_varlen_qkvpacked_func[_w_perkey_bias]``
+* :mod:`come_b200.cuda_extension`       -- stands in for the reference's ``src.cuda_extension`` package
+* :mod:`come_b200.token_merger`         -- ``JaggedTokens``, ``func_token_merge[_2d]``, ``func_token_split``,
+  ``MergePlan``, ``select_windows`` and the 2-D merger class
+"""
+from . import _lib  # noqa: F401
+
+__version__ = "0.1.0"

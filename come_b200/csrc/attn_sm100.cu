@@ -1,0 +1,573 @@
+// Variable-length biased attention forward on Blackwell tensor cores (sm_100a): tcgen05.mma with TMEM
+// accumulators, TMA-fed 128-byte-swizzled Q/K/V tiles, warp-specialised roles.
+//
+// One CTA owns up to two 128-row query tiles of one (segment, head) and walks the segment's keys 128 at a time.
+//   warps 0-3 / 4-7 : softmax group of query tile 0 / 1.  Thread r owns score row r (TMEM lane r): it reads the
+//                     128 scores of a step from TMEM, applies scale + per-key bias (log2 domain), keeps the
+//                     running max / sum, writes the probabilities back to TMEM as 16-bit pairs and rescales the
+//                     output accumulator only when the running max grew by more than 2^8.
+//   warp 8          : producer.  Stages the bias slice of every key tile in shared memory (-inf past the segment
+//                     end, which is what masks the ragged tail) and issues the TMA loads of Q, K and V.
+//   warp 9          : one thread issues every tcgen05.mma: S = Q K^T (both operands in shared memory) and
+//                     O += P V (P read from TMEM, V from shared memory, N-major).
+// TMEM columns: S0 [0,128) S1 [128,256) O0 [256,320) O1 [320,384) P0 [384,448) P1 [448,512).
+//
+// Every wait on an mbarrier is bounded: after ~2^29 clock ticks the waiter raises the CTA's abort flag and the
+// library's device status word, every role falls through to the common exit, TMEM is released and the kernel
+// returns instead of hanging.
+#include "attn_sm100.cuh"
+
+#include <cuda.h>
+
+#include <type_traits>
+
+namespace come {
+
+namespace {
+
+constexpr int kBlockM = 128;
+constexpr int kBlockN = 128;
+constexpr int kHeadDim = 64;
+constexpr int kStages = 6;       // K/V ring slots, 16 KiB each
+constexpr int kBiasStages = 4;
+constexpr int kThreads = 320;
+constexpr int kTileBytes = kBlockN * kHeadDim * 2;  // 16384
+constexpr uint32_t kTmemCols = 512;
+constexpr long long kWaitTicks = 1ll << 29;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+constexpr float kRescaleThreshold = 8.0f;  // log2 units
+
+struct SharedStorage {
+    alignas(1024) uint8_t q[2][kTileBytes];
+    alignas(1024) uint8_t kv[kStages][kTileBytes];
+    alignas(16) float bias[kBiasStages][kBlockN];
+    alignas(8) uint64_t q_full[2];
+    uint64_t kv_full[kStages];
+    uint64_t kv_empty[kStages];
+    uint64_t bias_full[kBiasStages];
+    uint64_t bias_empty[kBiasStages];
+    uint64_t s_full[2];
+    uint64_t s_empty[2];
+    uint64_t p_full[2];
+    uint64_t o_done[2];
+    uint32_t tmem_base;
+    volatile uint32_t abort_flag;
+};
+
+// ---- PTX wrappers ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false (and raises the abort flag + the device status word) when it gives up.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, SharedStorage &sh, unsigned int *status,
+                                          uint32_t code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (true) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (sh.abort_flag != 0) return false;
+        if (clock64() - t0 > kWaitTicks) {
+            sh.abort_flag = 1;
+            atomicOr(status, code);
+            return false;
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *map, int c0, int c1, int c2, uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(smem_u32(bar))
+        : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ void tc_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// D[tmem] (+)= A[smem] * B[smem]
+__device__ __forceinline__ void tc_mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem]
+__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// 32 lanes x 32 consecutive 32-bit columns: thread i of the warp receives lane (base lane + i).
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+          "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+          "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+template <bool kBF16> __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    if constexpr (kBF16) {
+        __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+        return *reinterpret_cast<uint32_t *>(&v);
+    } else {
+        __half2 v = __floats2half2_rn(lo, hi);
+        return *reinterpret_cast<uint32_t *>(&v);
+    }
+}
+
+// Shared-memory matrix descriptor of a tile whose rows are 128 bytes wide and 128-byte swizzled (what a TMA
+// load with a 64-element 16-bit inner box produces): 8-row groups are 1024 bytes apart.  The same encoding
+// serves a K-major operand (rows = M/N index, advance 32 bytes per 16-element K step) and an MN-major operand
+// (rows = K index, advance 2048 bytes per 16-row K step).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFF) >> 4);  // start address
+    d |= (uint64_t)1 << 16;                   // leading byte offset (unused for a single swizzle atom)
+    d |= (uint64_t)(1024 >> 4) << 32;         // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;                   // descriptor version of sm_100
+    d |= (uint64_t)2 << 61;                   // 128-byte swizzle
+    return d;
+}
+
+// Instruction descriptor of tcgen05.mma.kind::f16: float32 accumulate, 16-bit A/B of the given format.
+__host__ __device__ constexpr uint32_t make_idesc(bool bf16, int M, int N, bool b_mn_major) {
+    return (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) | ((b_mn_major ? 1u : 0u) << 16) |
+           ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
+enum : uint32_t {
+    kErrQFull = 1u << 0, kErrKvFull = 1u << 1, kErrKvEmpty = 1u << 2, kErrBiasFull = 1u << 3, kErrBiasEmpty = 1u << 4,
+    kErrSFull = 1u << 5, kErrSEmpty = 1u << 6, kErrPFull = 1u << 7, kErrODone = 1u << 8,
+};
+
+template <bool kBF16>
+__global__ void __launch_bounds__(kThreads, 1)
+attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                      const __grid_constant__ CUtensorMap map_v, const void *__restrict__ bias_ptr,
+                      const int *__restrict__ cu, float scale_log2, void *__restrict__ out_ptr, int64_t o_rs,
+                      float *__restrict__ lse, int64_t total, unsigned int *__restrict__ status) {
+    using T = typename std::conditional<kBF16, __nv_bfloat16, __half>::type;
+    extern __shared__ uint8_t smem_raw[];
+    SharedStorage &sh = *reinterpret_cast<SharedStorage *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+
+    const int seg = blockIdx.y, head = blockIdx.z;
+    const int s0 = cu[seg], s1 = cu[seg + 1];
+    const int seg_len = s1 - s0;
+    const int q_off = blockIdx.x * (2 * kBlockM);
+    if (q_off >= seg_len) return;  // uniform for the CTA, nothing allocated yet
+    const int q_row0 = s0 + q_off;
+    const int n_mt = (q_off + kBlockM < seg_len) ? 2 : 1;  // query tiles with at least one valid row
+    const int n_kv = (seg_len + kBlockN - 1) / kBlockN;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        // an earlier CTA that gave up leaves the status word raised: later CTAs then skip their work
+        sh.abort_flag = (*(volatile unsigned int *)status != 0) ? 1u : 0u;
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&sh.q_full[i], 1);
+            mbar_init(&sh.s_full[i], 1);
+            mbar_init(&sh.s_empty[i], kBlockM);
+            mbar_init(&sh.p_full[i], kBlockM);
+            mbar_init(&sh.o_done[i], 1);
+        }
+        for (int i = 0; i < kStages; ++i) {
+            mbar_init(&sh.kv_full[i], 1);
+            mbar_init(&sh.kv_empty[i], 1);
+        }
+        for (int i = 0; i < kBiasStages; ++i) {
+            mbar_init(&sh.bias_full[i], 1);
+            mbar_init(&sh.bias_empty[i], 4 * n_mt);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 9) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh.tmem_base)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = sh.tmem_base;
+    const bool dead = sh.abort_flag != 0;  // read after the barrier: uniform for the CTA
+
+    if (dead) {
+        // fall through to the common exit
+    } else if (warp == 8) {
+        // ===== producer =====================================================================================
+        const T *bias = reinterpret_cast<const T *>(bias_ptr);
+        bool ok = true;
+        if (lane == 0) {
+            for (int t = 0; t < n_mt; ++t) {
+                mbar_arrive_expect_tx(&sh.q_full[t], kTileBytes);
+                tma_load_3d(sh.q[t], &map_q, 0, head, q_row0 + t * kBlockM, &sh.q_full[t]);
+            }
+        }
+        int it = 0;  // ring position, advanced once per K or V tile in the order K0 K1 V0 K2 V1 ... V(n-1)
+        for (int step = 0; step <= n_kv && ok; ++step) {
+            if (step < n_kv) {
+                const int bs = step % kBiasStages;
+                ok = mbar_wait(&sh.bias_empty[bs], ((step / kBiasStages) & 1) ^ 1, sh, status, kErrBiasEmpty);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                const int key0 = s0 + step * kBlockN + lane * 4;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int key = key0 + i;
+                    float b = -INFINITY;
+                    if (key < s1) b = bias ? Elem<T>::to_f32(bias[key]) * kLog2e : 0.0f;
+                    sh.bias[bs][lane * 4 + i] = b;
+                }
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(&sh.bias_full[bs]);
+                    const int stage = it % kStages;
+                    ok = mbar_wait(&sh.kv_empty[stage], ((it / kStages) & 1) ^ 1, sh, status, kErrKvEmpty);
+                    if (ok) {
+                        mbar_arrive_expect_tx(&sh.kv_full[stage], kTileBytes);
+                        tma_load_3d(sh.kv[stage], &map_k, 0, head, s0 + step * kBlockN, &sh.kv_full[stage]);
+                    }
+                }
+                ok = __all_sync(0xffffffffu, ok);
+                ++it;
+            }
+            if (step >= 1 && ok) {
+                if (lane == 0) {
+                    const int stage = it % kStages;
+                    ok = mbar_wait(&sh.kv_empty[stage], ((it / kStages) & 1) ^ 1, sh, status, kErrKvEmpty);
+                    if (ok) {
+                        mbar_arrive_expect_tx(&sh.kv_full[stage], kTileBytes);
+                        tma_load_3d(sh.kv[stage], &map_v, 0, head, s0 + (step - 1) * kBlockN, &sh.kv_full[stage]);
+                    }
+                }
+                ok = __all_sync(0xffffffffu, ok);
+                ++it;
+            }
+        }
+    } else if (warp == 9) {
+        // ===== MMA issuer ===================================================================================
+        if (lane == 0) {
+            constexpr uint32_t idesc_qk = make_idesc(kBF16, kBlockM, kBlockN, false);
+            constexpr uint32_t idesc_pv = make_idesc(kBF16, kBlockM, kHeadDim, true);
+            bool ok = true;
+            for (int t = 0; t < n_mt && ok; ++t) ok = mbar_wait(&sh.q_full[t], 0, sh, status, kErrQFull);
+            const uint64_t q_desc[2] = {make_smem_desc(smem_u32(sh.q[0])), make_smem_desc(smem_u32(sh.q[1]))};
+            int it = 0;
+            for (int step = 0; step <= n_kv && ok; ++step) {
+                if (step < n_kv) {
+                    const int stage = it % kStages;
+                    ok = mbar_wait(&sh.kv_full[stage], (it / kStages) & 1, sh, status, kErrKvFull);
+                    if (!ok) break;
+                    const uint64_t k_desc = make_smem_desc(smem_u32(sh.kv[stage]));
+                    for (int t = 0; t < n_mt; ++t) {
+                        if (step > 0) {
+                            ok = mbar_wait(&sh.s_empty[t], (step - 1) & 1, sh, status, kErrSEmpty);
+                            if (!ok) break;
+                        }
+                        tc_fence_after();
+                        const uint32_t s_tmem = tmem + t * kBlockN;
+#pragma unroll
+                        for (int kk = 0; kk < kHeadDim / 16; ++kk)
+                            tc_mma_ss(s_tmem, q_desc[t] + kk * 2, k_desc + kk * 2, idesc_qk, kk > 0);
+                        tc_commit(&sh.s_full[t]);
+                    }
+                    if (!ok) break;
+                    tc_commit(&sh.kv_empty[stage]);
+                    ++it;
+                }
+                if (step >= 1) {
+                    const int j = step - 1;
+                    const int stage = it % kStages;
+                    ok = mbar_wait(&sh.kv_full[stage], (it / kStages) & 1, sh, status, kErrKvFull);
+                    if (!ok) break;
+                    const uint64_t v_desc = make_smem_desc(smem_u32(sh.kv[stage]));
+                    for (int t = 0; t < n_mt; ++t) {
+                        ok = mbar_wait(&sh.p_full[t], j & 1, sh, status, kErrPFull);
+                        if (!ok) break;
+                        tc_fence_after();
+                        const uint32_t o_tmem = tmem + 256 + t * kHeadDim;
+                        const uint32_t p_tmem = tmem + 384 + t * 64;
+#pragma unroll
+                        for (int kk = 0; kk < kBlockN / 16; ++kk)
+                            tc_mma_ts(o_tmem, p_tmem + kk * 8, v_desc + kk * (2048 >> 4), idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+                        tc_commit(&sh.o_done[t]);
+                    }
+                    if (!ok) break;
+                    tc_commit(&sh.kv_empty[stage]);
+                    ++it;
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp < 4 * n_mt) {
+        // ===== softmax group of query tile t ================================================================
+        const int t = warp >> 2;
+        const int r = threadIdx.x & 127;                          // row inside the tile == TMEM lane
+        const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
+        const uint32_t s_tmem = tmem + lane_addr + t * kBlockN;
+        const uint32_t o_tmem = tmem + lane_addr + 256 + t * kHeadDim;
+        const uint32_t p_tmem = tmem + lane_addr + 384 + t * 64;
+        const int row = q_row0 + t * kBlockM + r;
+        float m_ref = -INFINITY, l = 0.0f;
+        bool ok = true;
+
+        for (int j = 0; j < n_kv; ++j) {
+            ok = mbar_wait(&sh.s_full[t], j & 1, sh, status, kErrSFull);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            uint32_t s[4][32];
+            tmem_ld32(s_tmem + 0, s[0]);
+            tmem_ld32(s_tmem + 32, s[1]);
+            tmem_ld32(s_tmem + 64, s[2]);
+            tmem_ld32(s_tmem + 96, s[3]);
+            tc_wait_ld();
+            tc_fence_before();
+            mbar_arrive(&sh.s_empty[t]);  // scores are in registers: the next S = Q K^T may overwrite TMEM
+
+            const int bs = j % kBiasStages;
+            ok = mbar_wait(&sh.bias_full[bs], (j / kBiasStages) & 1, sh, status, kErrBiasFull);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            float m_tile = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+#pragma unroll
+                for (int i = 0; i < 32; i += 4) {
+                    const float4 b = *reinterpret_cast<const float4 *>(&sh.bias[bs][c * 32 + i]);
+                    float x0 = fmaf(__uint_as_float(s[c][i + 0]), scale_log2, b.x);
+                    float x1 = fmaf(__uint_as_float(s[c][i + 1]), scale_log2, b.y);
+                    float x2 = fmaf(__uint_as_float(s[c][i + 2]), scale_log2, b.z);
+                    float x3 = fmaf(__uint_as_float(s[c][i + 3]), scale_log2, b.w);
+                    s[c][i + 0] = __float_as_uint(x0);
+                    s[c][i + 1] = __float_as_uint(x1);
+                    s[c][i + 2] = __float_as_uint(x2);
+                    s[c][i + 3] = __float_as_uint(x3);
+                    m_tile = fmaxf(m_tile, fmaxf(fmaxf(x0, x1), fmaxf(x2, x3)));
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sh.bias_empty[bs]);
+
+            bool need = false;
+            if (j == 0) {
+                m_ref = m_tile;
+            } else {
+                need = m_tile > m_ref + kRescaleThreshold;
+                // PV of the previous step must be complete: O is then stable and the P buffer is free again
+                ok = mbar_wait(&sh.o_done[t], (j - 1) & 1, sh, status, kErrODone);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tc_fence_after();
+                if (__any_sync(0xffffffffu, need)) {
+                    float alpha = 1.0f;
+                    if (need) {
+                        alpha = fast_exp2(m_ref - m_tile);
+                        m_ref = m_tile;
+                        l *= alpha;
+                    }
+                    uint32_t o[2][32];
+                    tmem_ld32(o_tmem + 0, o[0]);
+                    tmem_ld32(o_tmem + 32, o[1]);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int c = 0; c < 2; ++c)
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) o[c][i] = __float_as_uint(__uint_as_float(o[c][i]) * alpha);
+                    tmem_st32(o_tmem + 0, o[0]);
+                    tmem_st32(o_tmem + 32, o[1]);
+                }
+            }
+
+            float sum = 0.0f;
+#pragma unroll
+            for (int c = 0; c < 4; c += 2) {
+                uint32_t p[32];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    const float p0 = fast_exp2(__uint_as_float(s[c][i]) - m_ref);
+                    const float p1 = fast_exp2(__uint_as_float(s[c][i + 1]) - m_ref);
+                    const float p2 = fast_exp2(__uint_as_float(s[c + 1][i]) - m_ref);
+                    const float p3 = fast_exp2(__uint_as_float(s[c + 1][i + 1]) - m_ref);
+                    sum += (p0 + p1) + (p2 + p3);
+                    p[i / 2] = pack2<kBF16>(p0, p1);
+                    p[16 + i / 2] = pack2<kBF16>(p2, p3);
+                }
+                tmem_st32(p_tmem + c * 16, p);  // 64 keys -> 32 columns of 16-bit pairs
+            }
+            l += sum;
+            tc_wait_st();
+            tc_fence_before();
+            mbar_arrive(&sh.p_full[t]);
+        }
+
+        if (ok) {
+            ok = mbar_wait(&sh.o_done[t], (n_kv - 1) & 1, sh, status, kErrODone);
+            ok = __all_sync(0xffffffffu, ok);
+        }
+        if (ok) {
+            tc_fence_after();
+            uint32_t o[2][32];
+            tmem_ld32(o_tmem + 0, o[0]);
+            tmem_ld32(o_tmem + 32, o[1]);
+            tc_wait_ld();
+            if (row < s1) {
+                const float inv = 1.0f / l;
+                uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<T *>(out_ptr) + (int64_t)row * o_rs + (int64_t)head * kHeadDim);
+#pragma unroll
+                for (int c = 0; c < 2; ++c)
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        uint4 v;
+                        v.x = pack2<kBF16>(__uint_as_float(o[c][i + 0]) * inv, __uint_as_float(o[c][i + 1]) * inv);
+                        v.y = pack2<kBF16>(__uint_as_float(o[c][i + 2]) * inv, __uint_as_float(o[c][i + 3]) * inv);
+                        v.z = pack2<kBF16>(__uint_as_float(o[c][i + 4]) * inv, __uint_as_float(o[c][i + 5]) * inv);
+                        v.w = pack2<kBF16>(__uint_as_float(o[c][i + 6]) * inv, __uint_as_float(o[c][i + 7]) * inv);
+                        dst[(c * 32 + i) / 8] = v;
+                    }
+                if (lse) lse[(int64_t)head * total + row] = (m_ref + log2f(l)) * kLn2;
+            }
+        }
+    }
+
+    // ===== common exit ==========================================================================================
+    tc_fence_before();
+    __syncthreads();
+    if (sh.abort_flag != 0) {
+        // give loads that may still be in flight time to land before the shared memory is released
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    }
+    if (warp == 9) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+    }
+}
+
+// ---- host side --------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// [total, H, 64] view with arbitrary row stride; box = 128 rows x 1 head x 64 elements, 128-byte swizzle.
+int make_map(CUtensorMap *map, const void *base, int dtype, int64_t total, int H, int64_t row_stride) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) {
+        set_error("cuTensorMapEncodeTiled is not available from the CUDA driver");
+        return COME_ERR_CUDA;
+    }
+    cuuint64_t dims[3] = {(cuuint64_t)kHeadDim, (cuuint64_t)H, (cuuint64_t)total};
+    cuuint64_t strides[2] = {(cuuint64_t)kHeadDim * 2, (cuuint64_t)row_stride * 2};
+    cuuint32_t box[3] = {(cuuint32_t)kHeadDim, 1, (cuuint32_t)kBlockN};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(map, dtype == COME_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+                    const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_error("cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+        return COME_ERR_CUDA;
+    }
+    return COME_OK;
+}
+
+}  // namespace
+
+bool attn_sm100_supported(const AttnArgs &a) {
+    if (a.D != kHeadDim) return false;
+    if (a.dtype != COME_BF16 && a.dtype != COME_F16) return false;
+    auto al16 = [](const void *p) { return ((uintptr_t)p & 15) == 0; };
+    if (!al16(a.q) || !al16(a.k) || !al16(a.v) || !al16(a.out)) return false;
+    if (a.q_rs % 8 || a.k_rs % 8 || a.v_rs % 8 || a.o_rs % 8) return false;
+    return true;
+}
+
+int attn_sm100_launch(const AttnArgs &a, cudaStream_t stream) {
+    unsigned int *status = status_word_dev();
+    if (!status) return COME_ERR_CUDA;
+    CUtensorMap mq, mk, mv;
+    int rc;
+    if ((rc = make_map(&mq, a.q, a.dtype, a.total, a.H, a.q_rs)) != COME_OK) return rc;
+    if ((rc = make_map(&mk, a.k, a.dtype, a.total, a.H, a.k_rs)) != COME_OK) return rc;
+    if ((rc = make_map(&mv, a.v, a.dtype, a.total, a.H, a.v_rs)) != COME_OK) return rc;
+    const size_t smem = sizeof(SharedStorage) + 1024;
+    dim3 grid((a.max_seqlen + 2 * kBlockM - 1) / (2 * kBlockM), a.nseg, a.H);
+    const float scale_log2 = a.scale * kLog2e;
+    if (a.dtype == COME_BF16) {
+        COME_CUDA(cudaFuncSetAttribute(attn_fwd_sm100_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        attn_fwd_sm100_kernel<true><<<grid, kThreads, smem, stream>>>(mq, mk, mv, a.bias, a.cu, scale_log2, a.out, a.o_rs, a.lse,
+                                                                     a.total, status);
+    } else {
+        COME_CUDA(cudaFuncSetAttribute(attn_fwd_sm100_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        attn_fwd_sm100_kernel<false><<<grid, kThreads, smem, stream>>>(mq, mk, mv, a.bias, a.cu, scale_log2, a.out, a.o_rs, a.lse,
+                                                                      a.total, status);
+    }
+    return check_launch("come_attn_varlen_fwd (tcgen05 kernel)");
+}
+
+}  // namespace come

@@ -1,0 +1,25 @@
+// Interface between the attention dispatcher and the tcgen05 tensor-core kernel.
+#pragma once
+#include "come_internal.cuh"
+
+namespace come {
+
+struct AttnArgs {
+    const void *q, *k, *v, *bias;
+    const int32_t *cu;
+    void *out;
+    float *lse;
+    int dtype;
+    int64_t total;
+    int H, D;
+    int64_t q_rs, k_rs, v_rs, o_rs;  // row strides in elements
+    int nseg, max_seqlen;
+    float scale;
+};
+
+// True when the tensor-core kernel can take the problem (head_dim 64, TMA-compatible addresses and strides).
+bool attn_sm100_supported(const AttnArgs &a);
+// Enqueues the tensor-core kernel; returns a COME_* code.
+int attn_sm100_launch(const AttnArgs &a, cudaStream_t stream);
+
+}  // namespace come

@@ -1,0 +1,468 @@
+// Token merge / unmerge for sm_100a: index plan, packed-row gather with window means, row gather back.
+//
+// All three data kernels are HBM-bandwidth bound.  They move 16-byte vectors, keep a full window's loads
+// in flight per thread before the first add, and run as persistent grid-stride loops sized to the SM count.
+#include "come_internal.cuh"
+
+#include <mutex>
+
+namespace come {
+
+// ---- common host state -------------------------------------------------------------------------------------
+static thread_local char t_error[512] = "";
+
+void set_error(const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(t_error, sizeof(t_error), fmt, ap);
+    va_end(ap);
+}
+
+static __device__ unsigned int g_status_word = 0;
+
+unsigned int *status_word_dev() {
+    unsigned int *p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress((void **)&p, g_status_word);
+    if (e != cudaSuccess) {
+        set_error("cudaGetSymbolAddress(status word) failed: %s", cudaGetErrorString(e));
+        return nullptr;
+    }
+    return p;
+}
+
+int sm_count() {
+    static int cached[64];
+    static std::mutex mu;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    std::lock_guard<std::mutex> lock(mu);
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+int make_layout(const come_layout_t *in, FrameLayout *out) {
+    COME_REQUIRE(in != nullptr, "layout is NULL");
+    COME_REQUIRE(in->start_index >= 0, "start_index must be >= 0, got %d", in->start_index);
+    FrameLayout L{};
+    L.start = in->start_index;
+    if (in->grid_h == 0) {
+        COME_REQUIRE(in->group_w > 0, "group_size must be > 0, got %d", in->group_w);
+        COME_REQUIRE(in->n_groups >= 0, "n_groups must be >= 0, got %d", in->n_groups);
+        L.H = 0;
+        L.W = 0;
+        L.gh = 1;
+        L.gw = in->group_w;
+        L.G = in->group_w;
+        L.M = in->n_groups;
+        L.Wm = in->n_groups;
+        L.prefix = in->start_index;
+        L.N = (int)((int64_t)L.start + (int64_t)L.M * L.G);
+        COME_REQUIRE((int64_t)L.start + (int64_t)L.M * L.G < (1ll << 31), "frame too long");
+    } else {
+        COME_REQUIRE(in->grid_h > 0 && in->grid_w > 0, "grid must be positive, got (%d, %d)", in->grid_h, in->grid_w);
+        COME_REQUIRE(in->group_h > 0 && in->group_w > 0, "group_h and group_w must be > 0, got (%d, %d)",
+                     in->group_h, in->group_w);
+        COME_REQUIRE((int64_t)in->grid_h * in->grid_w + in->start_index < (1ll << 31), "frame too long");
+        L.H = in->grid_h;
+        L.W = in->grid_w;
+        L.gh = in->group_h;
+        L.gw = in->group_w;
+        L.G = in->group_h * in->group_w;
+        L.Wm = L.W / L.gw;
+        L.Hc = (L.H / L.gh) * L.gh;
+        L.Wc = L.Wm * L.gw;
+        L.edge_cols = L.W - L.Wc;
+        L.M = (L.H / L.gh) * L.Wm;
+        L.N = L.start + L.H * L.W;
+        L.prefix = L.N - L.M * L.G;
+    }
+    *out = L;
+    return COME_OK;
+}
+
+// ---- index plan ------------------------------------------------------------------------------------------------
+// Pass 1: one warp per frame counts the merged windows of its row and records the packed frame length.
+__global__ void plan_count_kernel(const uint8_t *__restrict__ mask, int frames, int M, int G, int prefix,
+                                  int *__restrict__ frame_len) {
+    int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    int lane = threadIdx.x & 31;
+    if (warp >= frames) return;
+    const uint8_t *row = mask + (size_t)warp * M;
+    int k = 0;
+    for (int m = lane; m < M; m += 32) k += row[m] != 0;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) k += __shfl_xor_sync(0xffffffffu, k, o);
+    if (lane == 0) frame_len[warp] = prefix + (M - k) * G + k;
+}
+
+// Pass 2: one CTA per frame.  Sums the lengths of the preceding frames (its packed base row), scans its own
+// row of the mask, and writes group_prefix, offsets, rev_id and weight.
+constexpr int kPlanThreads = 256;
+
+__global__ void __launch_bounds__(kPlanThreads)
+plan_write_kernel(const uint8_t *__restrict__ mask, const int *__restrict__ frame_len, int frames, FrameLayout L,
+                  int *__restrict__ group_prefix, int *__restrict__ offsets, int64_t *__restrict__ rev,
+                  float *__restrict__ weight, int *__restrict__ seg_max) {
+    __shared__ int s_warp[kPlanThreads / 32];
+    __shared__ int s_base, s_carry;
+    const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+
+    // packed base row of this frame = sum of the lengths of frames [0, b)
+    int part = 0, mx = 0;
+    const int upto = (b == 0) ? frames : b;  // CTA 0 also produces the grand total and the longest frame
+    for (int i = tid; i < upto; i += kPlanThreads) {
+        int len = frame_len[i];
+        part += len;
+        mx = max(mx, len);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        part += __shfl_xor_sync(0xffffffffu, part, o);
+        mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    }
+    __shared__ int s_max[kPlanThreads / 32];
+    if (lane == 0) {
+        s_warp[wid] = part;
+        s_max[wid] = mx;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        int tot = 0, m2 = 0;
+        for (int w = 0; w < kPlanThreads / 32; ++w) {
+            tot += s_warp[w];
+            m2 = max(m2, s_max[w]);
+        }
+        if (b == 0) {
+            offsets[frames] = tot;
+            offsets[0] = 0;
+            if (seg_max) *seg_max = m2;
+            s_base = 0;
+        } else {
+            offsets[b] = tot;
+            s_base = tot;
+        }
+        s_carry = 0;
+    }
+    __syncthreads();
+    const int base = s_base;
+    const int64_t tok0 = (int64_t)b * L.N;
+
+    // never-merged prefix rows
+    for (int s = tid; s < L.prefix; s += kPlanThreads) {
+        rev[tok0 + L.src_token(s)] = base + s;
+        weight[base + s] = 1.0f;
+    }
+
+    // exclusive scan of (mask ? 1 : G) over the M groups, tile by tile
+    const uint8_t *row = mask + (size_t)b * L.M;
+    for (int t0 = 0; t0 < L.M; t0 += kPlanThreads) {
+        const int m = t0 + tid;
+        const bool valid = m < L.M;
+        const bool merged = valid && row[m] != 0;
+        const int len = valid ? (merged ? 1 : L.G) : 0;
+        int incl = len;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            int n = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += n;
+        }
+        __syncthreads();  // s_warp / s_carry of the previous tile fully consumed
+        if (lane == 31) s_warp[wid] = incl;
+        __syncthreads();
+        int warp_off = 0;
+        for (int w = 0; w < wid; ++w) warp_off += s_warp[w];
+        const int excl = s_carry + warp_off + incl - len;
+        if (valid) {
+            group_prefix[(size_t)b * L.M + m] = excl;
+            const int dst = base + L.prefix + excl;
+            const int r0 = L.prefix + m * L.G;
+            if (merged) {
+                weight[dst] = (float)L.G;
+                for (int g = 0; g < L.G; ++g) rev[tok0 + L.src_token(r0 + g)] = dst;
+            } else {
+                for (int g = 0; g < L.G; ++g) {
+                    weight[dst + g] = 1.0f;
+                    rev[tok0 + L.src_token(r0 + g)] = dst + g;
+                }
+            }
+        }
+        __syncthreads();
+        if (tid == kPlanThreads - 1) s_carry = excl + len;  // total of this tile carried to the next
+    }
+}
+
+// ---- merge data movement ----------------------------------------------------------------------------------------
+// One work unit = one window (G source rows) or one chunk of up to G prefix rows.  A CTA walks units with a
+// grid stride; inside a unit a thread owns 16-byte column vectors.  VEC = elements per vector (1 = scalar path
+// for rows that are not 16-byte multiples).
+constexpr int kMergeThreads = 256;
+constexpr int kMaxInFlight = 12;  // rows whose loads are issued before the first add / store
+
+template <typename T, int VEC> struct VecIO;
+template <> struct VecIO<float, 4> {
+    using V = float4;
+    static __device__ __forceinline__ void unpack(const V &v, float (&f)[4]) { f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w; }
+    static __device__ __forceinline__ V pack(const float (&f)[4]) { return make_float4(f[0], f[1], f[2], f[3]); }
+};
+template <typename T> struct VecIO<T, 8> {  // __half / __nv_bfloat16
+    using V = uint4;
+    static __device__ __forceinline__ void unpack(const V &v, float (&f)[8]) {
+        const T *e = reinterpret_cast<const T *>(&v);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] = Elem<T>::to_f32(e[i]);
+    }
+    static __device__ __forceinline__ V pack(const float (&f)[8]) {
+        V v;
+        T *e = reinterpret_cast<T *>(&v);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) e[i] = Elem<T>::from_f32(f[i]);
+        return v;
+    }
+};
+template <typename T> struct VecIO<T, 1> {
+    using V = T;
+    static __device__ __forceinline__ void unpack(const V &v, float (&f)[1]) { f[0] = Elem<T>::to_f32(v); }
+    static __device__ __forceinline__ V pack(const float (&f)[1]) { return Elem<T>::from_f32(f[0]); }
+};
+
+template <typename V> __device__ __forceinline__ V ld_stream(const V *p) { return __ldcs(p); }
+template <> __device__ __forceinline__ __half ld_stream<__half>(const __half *p) { return *p; }
+template <> __device__ __forceinline__ __nv_bfloat16 ld_stream<__nv_bfloat16>(const __nv_bfloat16 *p) { return *p; }
+template <typename V> __device__ __forceinline__ void st_stream(V *p, const V &v) { __stcs(p, v); }
+template <> __device__ __forceinline__ void st_stream<__half>(__half *p, const __half &v) { *p = v; }
+template <> __device__ __forceinline__ void st_stream<__nv_bfloat16>(__nv_bfloat16 *p, const __nv_bfloat16 &v) { *p = v; }
+
+template <typename T, int VEC>
+__global__ void __launch_bounds__(kMergeThreads)
+merge_kernel(const T *__restrict__ tokens, const uint8_t *__restrict__ mask, const int *__restrict__ group_prefix,
+             const int *__restrict__ offsets, FrameLayout L, int frames, int64_t C, T *__restrict__ out) {
+    using IO = VecIO<T, VEC>;
+    using V = typename IO::V;
+    extern __shared__ int s_src[];  // source token of every row of the current unit (G entries)
+    const int G = L.G;
+    const int prefix_units = (L.prefix + G - 1) / G;
+    const int units_per_frame = prefix_units + L.M;
+    const int64_t n_units = (int64_t)frames * units_per_frame;
+    const int64_t Cv = C / VEC;
+    const float fG = (float)G;
+
+    for (int64_t u = blockIdx.x; u < n_units; u += gridDim.x) {
+        const int b = (int)(u / units_per_frame);
+        const int unit = (int)(u - (int64_t)b * units_per_frame);
+        const int base = offsets[b];
+        int r0, rows, dst;
+        bool merged = false;
+        if (unit < prefix_units) {
+            r0 = unit * G;
+            rows = min(G, L.prefix - r0);
+            dst = base + r0;
+        } else {
+            const int m = unit - prefix_units;
+            r0 = L.prefix + m * G;
+            rows = G;
+            dst = base + L.prefix + group_prefix[(size_t)b * L.M + m];
+            merged = mask[(size_t)b * L.M + m] != 0;
+        }
+        __syncthreads();  // previous unit's s_src no longer read
+        for (int g = threadIdx.x; g < rows; g += kMergeThreads) s_src[g] = L.src_token(r0 + g);
+        __syncthreads();
+        const V *src_base = reinterpret_cast<const V *>(tokens) + (int64_t)b * L.N * Cv;
+        V *dst_base = reinterpret_cast<V *>(out) + (int64_t)dst * Cv;
+
+        for (int64_t v = threadIdx.x; v < Cv; v += kMergeThreads) {
+            if (merged) {
+                float acc[VEC];
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) acc[i] = 0.0f;
+                for (int g0 = 0; g0 < rows; g0 += kMaxInFlight) {
+                    V buf[kMaxInFlight];
+#pragma unroll
+                    for (int i = 0; i < kMaxInFlight; ++i)
+                        if (g0 + i < rows) buf[i] = ld_stream(src_base + (int64_t)s_src[g0 + i] * Cv + v);
+#pragma unroll
+                    for (int i = 0; i < kMaxInFlight; ++i)
+                        if (g0 + i < rows) {
+                            float f[VEC];
+                            IO::unpack(buf[i], f);
+#pragma unroll
+                            for (int j = 0; j < VEC; ++j) acc[j] = __fadd_rn(acc[j], f[j]);
+                        }
+                }
+#pragma unroll
+                for (int j = 0; j < VEC; ++j) acc[j] = __fdiv_rn(acc[j], fG);
+                st_stream(dst_base + v, IO::pack(acc));
+            } else {
+                for (int g0 = 0; g0 < rows; g0 += kMaxInFlight) {
+                    V buf[kMaxInFlight];
+#pragma unroll
+                    for (int i = 0; i < kMaxInFlight; ++i)
+                        if (g0 + i < rows) buf[i] = ld_stream(src_base + (int64_t)s_src[g0 + i] * Cv + v);
+#pragma unroll
+                    for (int i = 0; i < kMaxInFlight; ++i)
+                        if (g0 + i < rows) st_stream(dst_base + (int64_t)(g0 + i) * Cv + v, buf[i]);
+                }
+            }
+        }
+    }
+}
+
+// ---- unmerge ------------------------------------------------------------------------------------------------------
+constexpr int kUnmergeThreads = 256;
+constexpr int kUnmergeBatch = 4;
+
+template <typename V>
+__global__ void __launch_bounds__(kUnmergeThreads)
+unmerge_kernel(const V *__restrict__ merged, const int64_t *__restrict__ rev, int64_t total, int64_t Cv,
+               V *__restrict__ out) {
+    const int64_t n = total * Cv;
+    const int64_t stride = (int64_t)gridDim.x * kUnmergeThreads;
+    for (int64_t i0 = (int64_t)blockIdx.x * kUnmergeThreads + threadIdx.x; i0 < n; i0 += stride * kUnmergeBatch) {
+        V buf[kUnmergeBatch];
+#pragma unroll
+        for (int k = 0; k < kUnmergeBatch; ++k) {
+            const int64_t i = i0 + k * stride;
+            if (i < n) {
+                const int64_t row = i / Cv, v = i - row * Cv;
+                buf[k] = merged[__ldg(rev + row) * Cv + v];  // merged rows are re-read up to G times: keep in L2
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < kUnmergeBatch; ++k) {
+            const int64_t i = i0 + k * stride;
+            if (i < n) st_stream(out + i, buf[k]);
+        }
+    }
+}
+
+}  // namespace come
+
+// =====================================================================================================================
+// C ABI
+// =====================================================================================================================
+using namespace come;
+
+extern "C" int come_version(void) { return COME_B200_VERSION; }
+extern "C" const char *come_last_error(void) { return t_error; }
+
+extern "C" int come_layout_info(const come_layout_t *layout, int64_t *n_groups, int64_t *tokens_per_frame,
+                                int64_t *prefix_len) {
+    FrameLayout L;
+    int rc = make_layout(layout, &L);
+    if (rc != COME_OK) return rc;
+    if (n_groups) *n_groups = L.M;
+    if (tokens_per_frame) *tokens_per_frame = L.N;
+    if (prefix_len) *prefix_len = L.prefix;
+    return COME_OK;
+}
+
+extern "C" size_t come_merge_plan_workspace_bytes(int64_t frames) {
+    return (size_t)(frames > 0 ? frames : 1) * sizeof(int);
+}
+
+extern "C" int come_merge_plan(const uint8_t *mask_dev, int64_t frames, const come_layout_t *layout,
+                               int32_t *group_prefix_dev, int32_t *offsets_dev, int64_t *rev_id_dev,
+                               float *weight_dev, int32_t *seg_max_dev, void *workspace_dev, size_t workspace_bytes,
+                               void *stream) {
+    FrameLayout L;
+    int rc = make_layout(layout, &L);
+    if (rc != COME_OK) return rc;
+    COME_REQUIRE(frames >= 0, "frames must be >= 0");
+    COME_REQUIRE(offsets_dev && rev_id_dev && weight_dev, "plan outputs must not be NULL");
+    COME_REQUIRE(L.M == 0 || (mask_dev && group_prefix_dev), "mask / group_prefix must not be NULL");
+    COME_REQUIRE(frames * (int64_t)L.N < (1ll << 31), "frames * tokens_per_frame must fit int32 row indices");
+    COME_REQUIRE(workspace_dev && workspace_bytes >= come_merge_plan_workspace_bytes(frames),
+                 "workspace too small: need %zu bytes", come_merge_plan_workspace_bytes(frames));
+    cudaStream_t st = (cudaStream_t)stream;
+    if (frames == 0) {
+        COME_CUDA(cudaMemsetAsync(offsets_dev, 0, sizeof(int32_t), st));
+        if (seg_max_dev) COME_CUDA(cudaMemsetAsync(seg_max_dev, 0, sizeof(int32_t), st));
+        return COME_OK;
+    }
+    int *frame_len = (int *)workspace_dev;
+    const int warps_per_block = 8;
+    plan_count_kernel<<<(unsigned)((frames + warps_per_block - 1) / warps_per_block), warps_per_block * 32, 0, st>>>(
+        mask_dev, (int)frames, L.M, L.G, L.prefix, frame_len);
+    plan_write_kernel<<<(unsigned)frames, kPlanThreads, 0, st>>>(mask_dev, frame_len, (int)frames, L, group_prefix_dev,
+                                                                  offsets_dev, rev_id_dev, weight_dev, seg_max_dev);
+    return check_launch("come_merge_plan");
+}
+
+template <typename T>
+static int launch_merge(const void *tokens, int64_t frames, int64_t C, const FrameLayout &L, const uint8_t *mask,
+                        const int32_t *gp, const int32_t *off, void *out, cudaStream_t st) {
+    constexpr int VEC = 16 / sizeof(T);
+    const int prefix_units = (L.prefix + L.G - 1) / L.G;
+    const int64_t n_units = frames * (int64_t)(prefix_units + L.M);
+    if (n_units == 0 || C == 0) return COME_OK;
+    const int64_t max_blocks = (int64_t)sm_count() * 8;  // 8 resident CTAs of 256 threads per SM
+    const unsigned grid = (unsigned)(n_units < max_blocks ? n_units : max_blocks);
+    const size_t smem = (size_t)L.G * sizeof(int);
+    const bool vec_ok = (C % VEC == 0) && ((uintptr_t)tokens % 16 == 0) && ((uintptr_t)out % 16 == 0);
+    if (vec_ok)
+        merge_kernel<T, VEC><<<grid, kMergeThreads, smem, st>>>((const T *)tokens, mask, gp, off, L, (int)frames, C, (T *)out);
+    else
+        merge_kernel<T, 1><<<grid, kMergeThreads, smem, st>>>((const T *)tokens, mask, gp, off, L, (int)frames, C, (T *)out);
+    return check_launch("come_merge");
+}
+
+extern "C" int come_merge(const void *tokens_dev, int dtype, int64_t frames, int64_t channels,
+                          const come_layout_t *layout, const uint8_t *mask_dev, const int32_t *group_prefix_dev,
+                          const int32_t *offsets_dev, void *out_dev, void *stream) {
+    FrameLayout L;
+    int rc = make_layout(layout, &L);
+    if (rc != COME_OK) return rc;
+    COME_REQUIRE(frames >= 0 && channels >= 0, "frames and channels must be >= 0");
+    COME_REQUIRE(dtype == COME_F32 || dtype == COME_F16 || dtype == COME_BF16, "unknown dtype %d", dtype);
+    COME_REQUIRE((size_t)L.G * sizeof(int) <= 48 * 1024, "group_size %d too large", L.G);
+    if (frames == 0 || channels == 0) return COME_OK;
+    COME_REQUIRE(tokens_dev && out_dev && offsets_dev, "tokens / out / offsets must not be NULL");
+    COME_REQUIRE(L.M == 0 || (mask_dev && group_prefix_dev), "mask / group_prefix must not be NULL");
+    cudaStream_t st = (cudaStream_t)stream;
+    switch (dtype) {
+        case COME_F32: return launch_merge<float>(tokens_dev, frames, channels, L, mask_dev, group_prefix_dev, offsets_dev, out_dev, st);
+        case COME_F16: return launch_merge<__half>(tokens_dev, frames, channels, L, mask_dev, group_prefix_dev, offsets_dev, out_dev, st);
+        default: return launch_merge<__nv_bfloat16>(tokens_dev, frames, channels, L, mask_dev, group_prefix_dev, offsets_dev, out_dev, st);
+    }
+}
+
+template <typename V>
+static int launch_unmerge(const void *merged, const int64_t *rev, int64_t total, int64_t Cv, void *out, cudaStream_t st) {
+    const int64_t n = total * Cv;
+    const int64_t per_block = (int64_t)kUnmergeThreads * kUnmergeBatch;
+    int64_t blocks = (n + per_block - 1) / per_block;
+    const int64_t max_blocks = (int64_t)sm_count() * 8;
+    if (blocks > max_blocks) blocks = max_blocks;
+    unmerge_kernel<V><<<(unsigned)blocks, kUnmergeThreads, 0, st>>>((const V *)merged, rev, total, Cv, (V *)out);
+    return check_launch("come_unmerge");
+}
+
+extern "C" int come_unmerge(const void *merged_dev, const int64_t *rev_id_dev, int64_t total, int64_t channels,
+                            int dtype, void *out_dev, void *stream) {
+    COME_REQUIRE(total >= 0 && channels >= 0, "total and channels must be >= 0");
+    COME_REQUIRE(dtype == COME_F32 || dtype == COME_F16 || dtype == COME_BF16, "unknown dtype %d", dtype);
+    if (total == 0 || channels == 0) return COME_OK;
+    COME_REQUIRE(merged_dev && rev_id_dev && out_dev, "merged / rev_id / out must not be NULL");
+    cudaStream_t st = (cudaStream_t)stream;
+    const size_t row_bytes = (size_t)channels * dtype_size(dtype);
+    const bool aligned = ((uintptr_t)merged_dev % 16 == 0) && ((uintptr_t)out_dev % 16 == 0);
+    if (row_bytes % 16 == 0 && aligned) return launch_unmerge<uint4>(merged_dev, rev_id_dev, total, row_bytes / 16, out_dev, st);
+    if (row_bytes % 4 == 0 && ((uintptr_t)merged_dev % 4 == 0) && ((uintptr_t)out_dev % 4 == 0))
+        return launch_unmerge<uint32_t>(merged_dev, rev_id_dev, total, row_bytes / 4, out_dev, st);
+    return launch_unmerge<uint16_t>(merged_dev, rev_id_dev, total, row_bytes / 2, out_dev, st);
+}
+
+extern "C" int come_device_status(uint32_t *value, int clear) {
+    COME_REQUIRE(value != nullptr, "value is NULL");
+    unsigned int v = 0;
+    unsigned int *word = come::status_word_dev();
+    if (!word) return COME_ERR_CUDA;
+    COME_CUDA(cudaDeviceSynchronize());
+    COME_CUDA(cudaMemcpy(&v, word, sizeof(v), cudaMemcpyDeviceToHost));
+    *value = v;
+    if (clear && v != 0) COME_CUDA(cudaMemset(word, 0, sizeof(v)));
+    return COME_OK;
+}

@@ -1,0 +1,158 @@
+"""Stand-in for the reference's compiled ``flash_attn_fwd_cuda`` module
+(``src/cuda_extension/flash_attn/flash_api.cpp:538-607``): ``varlen_fwd`` and ``varlen_fwd_w_perkey_bias``
+with the reference's positional signature and return value ``[out, softmax_lse, p, rng_state]``.
+
+Only what the Co-Me inference path uses is implemented (self-attention over packed segments, no dropout,
+non-causal, no window, no softcap, no ALiBi, no paged KV); every other request raises instead of being
+ignored.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+from ._torch_util import dtype_code, ptr, stream_ptr
+
+__all__ = ["varlen_fwd", "varlen_fwd_w_perkey_bias"]
+
+BACKEND_AUTO, BACKEND_CUDA_CORE, BACKEND_TCGEN05 = 0, 1, 2
+_backend = BACKEND_AUTO
+
+
+def set_backend(backend: int) -> int:
+    """Select the attention kernel (0 automatic, 1 CUDA-core kernel, 2 require tcgen05); returns the old value."""
+    global _backend
+    old, _backend = _backend, int(backend)
+    return old
+
+
+def _unsupported(what: str):
+    raise NotImplementedError(f"come_b200 attention: {what} is not supported (forward-only Co-Me inference build)")
+
+
+def _impl(q, k, v, out_, cu_seqlens_q, cu_seqlens_k, seqused_k, leftpad_k, block_table, alibi_slopes, perkey_bias,
+          max_seqlen_q, max_seqlen_k, p_dropout, softmax_scale, zero_tensors, is_causal, window_size_left,
+          window_size_right, softcap, return_softmax, gen_):
+    if q.dtype not in (torch.float16, torch.bfloat16):
+        raise RuntimeError("FlashAttention only support fp16 and bf16 data type")
+    if k.dtype != q.dtype:
+        raise RuntimeError("query and key must have the same dtype")
+    if v.dtype != q.dtype:
+        raise RuntimeError("query and value must have the same dtype")
+    if cu_seqlens_q.dtype != torch.int32:
+        raise RuntimeError("cu_seqlens_q must have dtype int32")
+    if cu_seqlens_k.dtype != torch.int32:
+        raise RuntimeError("cu_seqlens_k must have dtype int32")
+    for name, t in (("q", q), ("k", k), ("v", v), ("cu_seqlens_q", cu_seqlens_q), ("cu_seqlens_k", cu_seqlens_k)):
+        if not t.is_cuda:
+            raise RuntimeError(f"{name} must be on CUDA")
+    for t in (q, k, v):
+        if t.stride(-1) != 1:
+            raise RuntimeError("Input tensor must have contiguous last dimension")
+    if not cu_seqlens_q.is_contiguous() or not cu_seqlens_k.is_contiguous():
+        raise RuntimeError("cu_seqlens must be contiguous")
+    if block_table is not None:
+        _unsupported("paged KV (block_table)")
+    if seqused_k is not None:
+        _unsupported("seqused_k")
+    if leftpad_k is not None:
+        _unsupported("leftpad_k")
+    if alibi_slopes is not None:
+        _unsupported("alibi_slopes")
+    if p_dropout != 0.0:
+        _unsupported("dropout")
+    if return_softmax:
+        raise RuntimeError("return_softmax is only supported when p_dropout > 0.0")
+    if is_causal and max_seqlen_q != 1:
+        _unsupported("causal masking")
+    if (window_size_left >= 0 and window_size_left < max_seqlen_k) or (window_size_right >= 0 and window_size_right < max_seqlen_k):
+        _unsupported("sliding-window attention")
+    if softcap > 0.0:
+        _unsupported("softcap")
+
+    total_q, num_heads, head_size = q.shape
+    batch_size = cu_seqlens_q.numel() - 1
+    if batch_size <= 0:
+        raise RuntimeError("batch size must be positive")
+    if head_size > 256:
+        raise RuntimeError("FlashAttention forward only supports head dimension at most 256")
+    if head_size % 8 != 0:
+        raise RuntimeError("query, key, value, and out_ must have a head_size that is a multiple of 8")
+    if tuple(k.shape) != (k.shape[0], num_heads, head_size) or tuple(v.shape) != tuple(k.shape):
+        if k.shape[1] != num_heads:
+            _unsupported("grouped-query attention (num_heads_k != num_heads)")
+        raise RuntimeError("k / v must have shape (total_k, num_heads, head_size)")
+    total_k = k.shape[0]
+    if cu_seqlens_k.numel() != batch_size + 1:
+        raise RuntimeError("cu_seqlens_k must have shape (batch_size + 1)")
+    same_cu = cu_seqlens_q.data_ptr() == cu_seqlens_k.data_ptr() or (
+        total_q == total_k and max_seqlen_q == max_seqlen_k and torch.equal(cu_seqlens_q, cu_seqlens_k))
+    if not same_cu:
+        _unsupported("cross attention (cu_seqlens_q != cu_seqlens_k)")
+
+    if out_ is not None:
+        out = out_
+        if out.dtype != q.dtype:
+            raise RuntimeError("Output must have the same dtype as inputs")
+        if not out.is_cuda:
+            raise RuntimeError("out must be on CUDA")
+        if out.stride(-1) != 1 or out.stride(1) != head_size:
+            raise RuntimeError("Output tensor must have contiguous last dimension")
+        if tuple(out.shape) != (total_q, num_heads, head_size):
+            raise RuntimeError("out must have shape (total_q, num_heads, head_size)")
+    else:
+        out = torch.empty((total_q, num_heads, head_size), dtype=q.dtype, device=q.device)
+    softmax_lse = torch.empty((num_heads, total_q), dtype=torch.float32, device=q.device)
+    p = torch.empty((0,), dtype=q.dtype, device=q.device)
+    rng_state = torch.empty((2,), dtype=torch.int64, device=q.device)
+
+    bias = None
+    if perkey_bias is not None:
+        if perkey_bias.dtype != q.dtype:
+            raise RuntimeError(f"perkey_bias dtype must match QKV dtype ({q.dtype}), got {perkey_bias.dtype}")
+        if not perkey_bias.is_cuda:
+            raise RuntimeError("perkey_bias must be on CUDA")
+        if not perkey_bias.is_contiguous():
+            raise RuntimeError("perkey_bias must be contiguous")
+        if tuple(perkey_bias.shape) != (total_k,):
+            raise RuntimeError(f"perkey_bias must have shape (total_k,), got {tuple(perkey_bias.shape)}")
+        bias = perkey_bias
+
+    if zero_tensors:
+        out.zero_()
+        softmax_lse.fill_(float("-inf"))
+    if max_seqlen_k <= 0 or total_q == 0:
+        out.zero_()
+        softmax_lse.fill_(float("inf"))
+        return [out, softmax_lse, p, rng_state]
+
+    def head_packed(t):
+        # heads must be adjacent (stride head_size); a strided view over a packed qkv buffer qualifies
+        return t if t.stride(1) == head_size else t.contiguous()
+
+    q, k, v = head_packed(q), head_packed(k), head_packed(v)
+    with torch.cuda.device(q.device):
+        _lib.check(_lib.lib().come_attn_varlen_fwd(
+            ptr(q), ptr(k), ptr(v), dtype_code(q.dtype), total_q, num_heads, head_size, q.stride(0), k.stride(0),
+            v.stride(0), ptr(bias), ptr(cu_seqlens_q), batch_size, int(max_seqlen_q), float(softmax_scale), ptr(out),
+            out.stride(0), ptr(softmax_lse), _backend, stream_ptr(q.device)))
+    return [out, softmax_lse, p, rng_state]
+
+
+def varlen_fwd(q, k, v, out_, cu_seqlens_q, cu_seqlens_k, seqused_k, leftpad_k, block_table, alibi_slopes,
+               max_seqlen_q, max_seqlen_k, p_dropout, softmax_scale, zero_tensors, is_causal, window_size_left,
+               window_size_right, softcap, return_softmax, gen_):
+    """Forward pass (variable length); see ``flash_api.cpp:538-567``."""
+    return _impl(q, k, v, out_, cu_seqlens_q, cu_seqlens_k, seqused_k, leftpad_k, block_table, alibi_slopes, None,
+                 max_seqlen_q, max_seqlen_k, p_dropout, softmax_scale, zero_tensors, is_causal, window_size_left,
+                 window_size_right, softcap, return_softmax, gen_)
+
+
+def varlen_fwd_w_perkey_bias(q, k, v, out_, cu_seqlens_q, cu_seqlens_k, seqused_k, leftpad_k, block_table,
+                             alibi_slopes, perkey_bias, max_seqlen_q, max_seqlen_k, p_dropout, softmax_scale,
+                             zero_tensors, is_causal, window_size_left, window_size_right, softcap, return_softmax,
+                             gen_):
+    """Forward pass (variable length) with a per-key additive bias; see ``flash_api.cpp:570-599``."""
+    return _impl(q, k, v, out_, cu_seqlens_q, cu_seqlens_k, seqused_k, leftpad_k, block_table, alibi_slopes,
+                 perkey_bias, max_seqlen_q, max_seqlen_k, p_dropout, softmax_scale, zero_tensors, is_causal,
+                 window_size_left, window_size_right, softcap, return_softmax, gen_)

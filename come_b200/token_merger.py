@@ -1,0 +1,330 @@
+"""Host-side mirror of the reference's token-merger operator interface, on top of ``libcome_b200.so``.
+
+* :class:`JaggedTokens` -- the packed variable-length container (``src/interface/token_merger.py:11-100``).
+* :func:`func_token_merge`, :func:`func_token_split` -- ``src/accelerate/token_merger/co_me.py:152-254``.
+* :func:`func_token_merge_2d` -- ``src/accelerate/token_merger/co_me_2d.py:174-211``; here the 2-D window gather
+  runs inside the merge kernel (no permuted copy of the tokens) and grids that the windows do not tile exactly
+  (37x37 with 3x3 windows) are accepted: uncovered patches are emitted right after the special tokens.
+* :class:`MergePlan` -- everything of a merge that depends on the mask only, computed once per ``build_ctx``
+  (one device->host read for the packed length) and reused by every merge / split / attention call.
+* :func:`select_windows` -- the tensor code of ``build_ctx`` (``co_me_2d.py:268-298``, ``co_me.py:54-73``).
+* :class:`CoMe2DTokenMerger` -- ``ITokenMerger`` implementation with the reference's method names.
+
+Argument validation raises ``ValueError`` with the reference's messages before anything is launched.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import Any, Callable, Optional, Tuple
+
+import torch
+
+from . import _lib, co_me_cuext
+from ._torch_util import dtype_code, ptr, require_cuda, stream_ptr
+
+__all__ = [
+    "JaggedTokens", "MergePlan", "func_token_merge", "func_token_split", "func_token_merge_2d", "select_windows",
+    "CoMe2DTokenMerger",
+]
+
+
+# ---------------------------------------------------------------------------------------------------------
+# JaggedTokens
+# ---------------------------------------------------------------------------------------------------------
+@dataclass
+class JaggedTokens:
+    """Packed variable-length tokens: ``tokens [1, P, C]``, ``weight [P]`` (tokens represented by each row),
+    ``offset [M+1]`` int64 segment boundaries."""
+    tokens: torch.Tensor
+    weight: torch.Tensor
+    offset: torch.Tensor
+
+    def apply(self, func: Callable[[torch.Tensor], torch.Tensor]) -> "JaggedTokens":
+        return JaggedTokens(tokens=func(self.tokens), weight=self.weight, offset=self.offset)
+
+    def add_suffix(self, suffix: torch.Tensor) -> "JaggedTokens":
+        """Append ``T`` dense tokens (weight 1) to each of the ``M`` segments; ``suffix`` is ``(M, T, C)``."""
+        M = self.offset.shape[0] - 1
+        if suffix.shape[0] != M:
+            raise ValueError(f"suffix batch dim ({suffix.shape[0]}) must match segment count ({M})")
+        T, Cc = suffix.shape[1], suffix.shape[2]
+        P_old = self.tokens.shape[1]
+        dev = self.offset.device
+        seg_len = self.offset[1:] - self.offset[:-1]
+        seg_id = torch.repeat_interleave(torch.arange(M, device=dev), seg_len, output_size=P_old)
+        new_pos = torch.arange(P_old, device=dev) + seg_id * T
+        new_offset = self.offset + torch.arange(M + 1, device=dev, dtype=self.offset.dtype) * T
+        new_tokens = torch.empty(1, P_old + M * T, Cc, device=self.tokens.device, dtype=self.tokens.dtype)
+        new_weight = torch.ones(P_old + M * T, device=self.weight.device, dtype=self.weight.dtype)
+        new_tokens[0, new_pos] = self.tokens[0]
+        new_weight[new_pos] = self.weight
+        tail = (new_offset[1:, None] - T + torch.arange(T, device=dev)[None, :]).reshape(-1)
+        new_tokens[0, tail] = suffix.reshape(-1, Cc)
+        return JaggedTokens(tokens=new_tokens, weight=new_weight, offset=new_offset)
+
+    def split_suffix(self, count: int) -> Tuple["JaggedTokens", torch.Tensor]:
+        """Remove the last ``count`` tokens of every segment (inverse of :meth:`add_suffix`)."""
+        M = self.offset.shape[0] - 1
+        T, Cc = count, self.tokens.shape[2]
+        P_old = self.tokens.shape[1]
+        P_new = P_old - M * T
+        if P_new < 0:
+            raise ValueError(f"Cannot strip {T} tokens from each of {M} segments (total tokens = {P_old})")
+        dev = self.offset.device
+        orig_offset = self.offset - torch.arange(M + 1, device=dev, dtype=self.offset.dtype) * T
+        seg_len = orig_offset[1:] - orig_offset[:-1]
+        if (seg_len < 0).any():
+            raise ValueError(f"count={T} exceeds the length of at least one segment")
+        tail = (self.offset[1:, None] - T + torch.arange(T, device=dev)[None, :]).reshape(-1)
+        suffix = self.tokens[0, tail].reshape(M, T, Cc)
+        seg_id = torch.repeat_interleave(torch.arange(M, device=dev), seg_len, output_size=P_new)
+        keep = torch.arange(P_new, device=dev) + seg_id * T
+        return JaggedTokens(tokens=self.tokens[0, keep].unsqueeze(0), weight=self.weight[keep],
+                            offset=orig_offset), suffix
+
+
+# ---------------------------------------------------------------------------------------------------------
+# validation (messages follow the reference so its tests read the same)
+# ---------------------------------------------------------------------------------------------------------
+def _validate_token_merge_args(tokens, start_index, group_size, merge_mask) -> None:
+    if start_index < 0:
+        raise ValueError(f"start_index must be >= 0, got {start_index}")
+    if group_size <= 0:
+        raise ValueError(f"group_size must be > 0, got {group_size}")
+    if merge_mask.dtype != torch.bool:
+        raise ValueError(f"merge_mask must be of dtype torch.bool, got {merge_mask.dtype}")
+    B, N, _C = tokens.shape
+    _Bm, M = merge_mask.shape
+    if _Bm != B:
+        raise ValueError(f"merge_mask batch ({_Bm}) must match tokens batch ({B})")
+    if N != start_index + M * group_size:
+        raise ValueError(
+            f"Expected N = start_index + M * group_size = {start_index} + {M} * {group_size} = "
+            f"{start_index + M * group_size}, got N = {N}")
+
+
+def _validate_token_merge_2d_args(tokens, start_index, group_h, group_w, H, W, merge_mask, ragged) -> None:
+    if start_index < 0:
+        raise ValueError(f"start_index must be >= 0, got {start_index}")
+    if group_h <= 0 or group_w <= 0:
+        raise ValueError(f"group_h and group_w must be > 0, got ({group_h}, {group_w})")
+    if not ragged:
+        if H % group_h != 0:
+            raise ValueError(f"H ({H}) must be divisible by group_h ({group_h})")
+        if W % group_w != 0:
+            raise ValueError(f"W ({W}) must be divisible by group_w ({group_w})")
+    if merge_mask.dtype != torch.bool:
+        raise ValueError(f"merge_mask must be of dtype torch.bool, got {merge_mask.dtype}")
+    B, N, _C = tokens.shape
+    _Bm, M = merge_mask.shape
+    M_expected = (H // group_h) * (W // group_w)
+    if _Bm != B:
+        raise ValueError(f"merge_mask batch ({_Bm}) must match tokens batch ({B})")
+    if N != start_index + H * W:
+        raise ValueError(f"Expected N = start_index + H * W = {start_index} + {H * W} = {start_index + H * W}, got N = {N}")
+    if M != M_expected:
+        raise ValueError(f"Expected M = (H // group_h) * (W // group_w) = {M_expected}, got M = {M}")
+
+
+# ---------------------------------------------------------------------------------------------------------
+# MergePlan
+# ---------------------------------------------------------------------------------------------------------
+class MergePlan:
+    """Index plan of a merge mask: packed offsets, ``rev_id``, ``weight``, per-key attention bias and the
+    longest segment, built by one pair of small kernels and ONE device->host read.
+
+    The reference recomputes all of this inside every ``merge`` call (114 times per forward in its direct
+    mode); with a plan, ``merge`` and ``split`` are pure data movement and attention needs no
+    ``max_seqlen`` read-back.
+    """
+
+    def __init__(self, merge_mask: torch.Tensor, layout: _lib.Layout):
+        require_cuda(merge_mask, "merge_mask")
+        if merge_mask.dtype != torch.bool or merge_mask.dim() != 2:
+            raise ValueError(f"merge_mask must be a [frames, M] tensor of dtype torch.bool, got {merge_mask.dtype}")
+        n_groups, n_tok, prefix = C.c_int64(), C.c_int64(), C.c_int64()
+        _lib.check(_lib.lib().come_layout_info(C.byref(layout), C.byref(n_groups), C.byref(n_tok), C.byref(prefix)))
+        if merge_mask.shape[1] != n_groups.value:
+            raise ValueError(f"Expected M = {n_groups.value}, got M = {merge_mask.shape[1]}")
+        self.layout = layout
+        self.frames = int(merge_mask.shape[0])
+        self.tokens_per_frame = int(n_tok.value)
+        self.prefix_len = int(prefix.value)
+        self.mask = merge_mask.contiguous()
+        self._mask_u8 = self.mask.view(torch.uint8)
+        self.group_prefix, self.offsets_i32, self.rev_id, weight_full, seg_max = co_me_cuext.merge_plan_raw(
+            self._mask_u8, layout, self.tokens_per_frame)
+        if self.frames > 0:
+            host = torch.stack([self.offsets_i32[-1], seg_max[0]]).tolist()  # the single synchronising read
+            self.total, self.max_seqlen = int(host[0]), int(host[1])
+        else:
+            self.total, self.max_seqlen = 0, 0
+        self.weight = weight_full[: self.total]
+        self.offset = self.offsets_i32.long()
+        self._bias = {}
+
+    # -- derived, cached ---------------------------------------------------------------------------------
+    def perkey_bias(self, dtype: torch.dtype) -> torch.Tensor:
+        """``log(weight)`` in the run dtype (``src/accelerate/vggt/module/bias_attention.py:120``)."""
+        if dtype not in self._bias:
+            self._bias[dtype] = self.weight.log().to(dtype)
+        return self._bias[dtype]
+
+    def cu_seqlens(self, frames_per_segment: int = 1) -> torch.Tensor:
+        """int32 segment boundaries; ``frames_per_segment = S`` concatenates the frames of a scene into one
+        segment (global attention, ``src/accelerate/vggt/fused.py:136,149``)."""
+        return self.offsets_i32 if frames_per_segment == 1 else self.offsets_i32[::frames_per_segment].contiguous()
+
+    # -- data movement -----------------------------------------------------------------------------------
+    def merge(self, tokens: torch.Tensor) -> torch.Tensor:
+        """``tokens [frames, N, C]`` -> packed ``[P, C]``."""
+        require_cuda(tokens, "tokens")
+        if tokens.dim() != 3 or tokens.shape[0] != self.frames or tokens.shape[1] != self.tokens_per_frame:
+            raise ValueError(f"Expected tokens [{self.frames}, {self.tokens_per_frame}, C], got {tuple(tokens.shape)}")
+        tokens = tokens.contiguous()
+        out = torch.empty((self.total, tokens.shape[2]), dtype=tokens.dtype, device=tokens.device)
+        with torch.cuda.device(tokens.device):
+            _lib.check(_lib.lib().come_merge(ptr(tokens), dtype_code(tokens.dtype, "tokens"), self.frames,
+                                             tokens.shape[2], C.byref(self.layout), ptr(self._mask_u8),
+                                             ptr(self.group_prefix), ptr(self.offsets_i32), ptr(out),
+                                             stream_ptr(tokens.device)))
+        return out
+
+    def split(self, merged: torch.Tensor) -> torch.Tensor:
+        """packed ``[P, C]`` -> ``[frames * N, C]``."""
+        return co_me_cuext.co_me_token_split_cuda(merged, self.rev_id, merged.shape[-1])
+
+    def jagged(self, tokens: torch.Tensor) -> JaggedTokens:
+        return JaggedTokens(tokens=self.merge(tokens).unsqueeze(0), weight=self.weight, offset=self.offset)
+
+
+# ---------------------------------------------------------------------------------------------------------
+# functional API
+# ---------------------------------------------------------------------------------------------------------
+def func_token_merge(tokens: torch.Tensor, start_index: int, group_size: int, merge_mask: torch.Tensor):
+    """Merge token groups according to ``merge_mask``.
+
+    Args:
+        tokens:      ``[B, N, C]`` CUDA tensor.
+        start_index: number of leading special tokens excluded from merging.
+        group_size:  ``G`` tokens per merge group.
+        merge_mask:  ``[B, M]`` bool; ``True`` merges the group into its mean, ``False`` keeps ``G`` tokens.
+
+    Returns:
+        ``(JaggedTokens, rev_id)``; ``rev_id[B*N]`` maps every original token to its packed row.
+    """
+    _validate_token_merge_args(tokens, start_index, group_size, merge_mask)
+    out_flat, offsets, rev_id, weight = co_me_cuext.co_me_token_merge_cuda(tokens.contiguous(), start_index, group_size,
+                                                                         merge_mask.contiguous())
+    return JaggedTokens(tokens=out_flat.unsqueeze(0), weight=weight, offset=offsets.long()), rev_id
+
+
+def func_token_split(tokens: JaggedTokens, rev_id: torch.Tensor, bsnc_shape: Tuple[int, int, int, int]) -> torch.Tensor:
+    """Inverse of :func:`func_token_merge`: gather the packed rows back to ``[B*S, N, C]``."""
+    B, S, N, Cc = bsnc_shape
+    flat = tokens.tokens.squeeze(0)
+    restored = co_me_cuext.co_me_token_split_cuda(flat.contiguous(), rev_id.contiguous(), Cc)
+    return restored.reshape(B * S, N, Cc)
+
+
+def func_token_merge_2d(tokens: torch.Tensor, start_index: int, group_h: int, group_w: int, H: int, W: int,
+                        merge_mask: torch.Tensor, allow_ragged: bool = False):
+    """Merge ``group_h x group_w`` windows of a row-major ``H x W`` patch grid (window order = raster order).
+
+    Same results as the reference's rearrange-then-1-D path, produced by one gather kernel.  With
+    ``allow_ragged`` the grid need not be a multiple of the window: windows tile the top-left part and the
+    uncovered patches follow the special tokens, never merged.
+    """
+    _validate_token_merge_2d_args(tokens, start_index, group_h, group_w, H, W, merge_mask, allow_ragged)
+    plan = MergePlan(merge_mask, _lib.Layout.two_d(start_index, H, W, group_h, group_w))
+    return plan.jagged(tokens), plan.rev_id
+
+
+def select_windows(confidence: torch.Tensor, B: int, S: int, H: int, W: int, group_h: int, group_w: int,
+                   threshold: float, mode: str = "pairwise-rank", scope: str = "batch") -> torch.Tensor:
+    """Per-patch confidence ``[B, S*H*W]`` -> bool merge mask ``[B*S, M]``.
+
+    ``mode``: ``"pairwise-rank"`` (``mean < quantile(mean, threshold)``) or ``"abs_mse"`` (``mean < threshold``);
+    ``scope``: ``"batch"`` ranks all windows of a batch element together (2-D merger class), ``"frame"`` ranks
+    per frame (1-D merger class).  The z-normalised ``"mse"`` mode of the reference is not provided.
+    """
+    require_cuda(confidence, "confidence")
+    if mode == "mse":
+        raise NotImplementedError("the z-normalised 'mse' confidence mode is not provided by come_b200")
+    if mode not in ("pairwise-rank", "abs_mse"):
+        raise ValueError(f"unknown confidence mode {mode!r}")
+    if scope not in ("batch", "frame"):
+        raise ValueError(f"unknown scope {scope!r}")
+    if mode == "pairwise-rank" and not (0.0 <= threshold <= 1.0):
+        raise ValueError(f"Ranking mode requires threshold in [0, 1], got {threshold}")
+    if confidence.numel() != B * S * H * W:
+        raise ValueError(f"Expected {B * S * H * W} confidences, got {confidence.numel()}")
+    conf = confidence.contiguous()
+    M = (H // group_h) * (W // group_w)
+    mask = torch.empty((B * S, M), dtype=torch.bool, device=conf.device)
+    with torch.cuda.device(conf.device):
+        _lib.check(_lib.lib().come_select_windows(
+            ptr(conf), dtype_code(conf.dtype, "confidence"), B, S, H, W, group_h, group_w, float(threshold),
+            _lib.COME_SELECT_RANK if mode == "pairwise-rank" else _lib.COME_SELECT_ABS,
+            _lib.COME_SCOPE_BATCH if scope == "batch" else _lib.COME_SCOPE_FRAME, ptr(mask), stream_ptr(conf.device)))
+    return mask
+
+
+# ---------------------------------------------------------------------------------------------------------
+# ITokenMerger-style class
+# ---------------------------------------------------------------------------------------------------------
+class CoMe2DTokenMerger:
+    """2-D Co-Me merger with the reference's ``ITokenMerger`` method names
+    (``src/interface/token_merger.py:102-116``, ``src/accelerate/token_merger/co_me_2d.py:214-352``).
+
+    ``predictor(feature_bshwc_bf16, BPHWC=(B, S, H, W, C)) -> confidence [B, S*H*W, 1]`` is any callable (the
+    reference loads a distilled ``GlobalAttentionConfidence``; a seeded MLP head serves the synthetic
+    benchmark configurations).  ``build_ctx`` returns ``(mask, (B, S, C, H, W), plan)``: the first two entries
+    are the reference's context, the third is the cached :class:`MergePlan`.
+    """
+
+    def __init__(self, start_idx: int, group_h: int, group_w: int, threshold: float, predictor: Callable[..., torch.Tensor],
+                 conf_mode: str = "pairwise-rank", allow_ragged: bool = True):
+        self.start_idx = start_idx
+        self.group_h = group_h
+        self.group_w = group_w
+        self.threshold = threshold
+        self.predictor = predictor
+        self.conf_mode = conf_mode
+        self.allow_ragged = allow_ragged
+
+    def build_ctx(self, feature: torch.Tensor) -> Any:
+        B, S, Cc, H, W = feature.shape
+        if not self.allow_ragged:
+            if H % self.group_h != 0:
+                raise ValueError(f"H ({H}) must be divisible by group_h ({self.group_h})")
+            if W % self.group_w != 0:
+                raise ValueError(f"W ({W}) must be divisible by group_w ({self.group_w})")
+        confidence = self.predictor(feature.permute(0, 1, 3, 4, 2).bfloat16(), BPHWC=(B, S, H, W, Cc)).squeeze(-1)
+        mask = select_windows(confidence, B, S, H, W, self.group_h, self.group_w, self.threshold, self.conf_mode, "batch")
+        plan = MergePlan(mask, _lib.Layout.two_d(self.start_idx, H, W, self.group_h, self.group_w))
+        return (mask, (B, S, Cc, H, W), plan)
+
+    def _plan_for(self, ctx, start_index: Optional[int]) -> MergePlan:
+        mask, (B, S, Cc, H, W), plan = ctx
+        if start_index is None or start_index == self.start_idx:
+            return plan
+        return MergePlan(mask, _lib.Layout.two_d(start_index, H, W, self.group_h, self.group_w))
+
+    def merge(self, ctx, tokens: torch.Tensor, stub: Any = None, *, start_index: Optional[int] = None):
+        plan = self._plan_for(ctx, start_index)
+        return plan.jagged(tokens.flatten(0, 1)), (plan.rev_id, tokens.shape)
+
+    def split(self, ctx, stub: Any, tokens: JaggedTokens) -> torch.Tensor:
+        rev_id, shape_bsnc = stub
+        B, S, N, Cc = shape_bsnc
+        return func_token_split(tokens, rev_id, shape_bsnc).view(B, S, N, Cc)
+
+    def build_infer_mask(self, ctx) -> torch.Tensor:
+        mask, (B, S, _, H, W), _plan = ctx
+        Mh, Mw = H // self.group_h, W // self.group_w
+        m = mask.reshape(B * S, Mh, 1, Mw, 1).expand(-1, -1, self.group_h, -1, self.group_w)
+        full = torch.zeros((B * S, H, W), dtype=torch.bool, device=mask.device)
+        full[:, : Mh * self.group_h, : Mw * self.group_w] = m.reshape(B * S, Mh * self.group_h, Mw * self.group_w)
+        return full.reshape(B, S, H, W)

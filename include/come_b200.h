@@ -1,0 +1,150 @@
+/*
+ * come_b200 -- C ABI of the B200 (sm_100a) kernels for the Co-Me accelerated-inference hot path:
+ * confidence-guided window selection, token merge into a packed variable-length sequence, biased
+ * variable-length attention, and unmerge.
+ *
+ * Conventions
+ *   - every pointer named *_dev is DEVICE memory on the current CUDA device; nothing here allocates or
+ *     frees device memory, the caller owns every buffer (outputs and workspaces included);
+ *   - `stream` is a cudaStream_t passed as void*; all work is enqueued on it and nothing synchronises;
+ *   - functions return COME_OK (0) or a negative COME_ERR_* code and never throw; a human-readable
+ *     message for the last failure on the calling thread is available from come_last_error();
+ *   - dtype is COME_F32 / COME_F16 / COME_BF16.
+ *
+ * Each entry point names the interface of the reference project (paths relative to its root) it replaces.
+ */
+#ifndef COME_B200_H
+#define COME_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define COME_B200_VERSION 100
+
+enum { COME_F32 = 0, COME_F16 = 1, COME_BF16 = 2 };
+
+enum {
+    COME_OK = 0,
+    COME_ERR_ARG = -1,         /* invalid argument (shape, alignment, null pointer) */
+    COME_ERR_CUDA = -2,        /* a CUDA runtime / driver call failed */
+    COME_ERR_UNSUPPORTED = -3, /* valid request that this build deliberately does not implement */
+    COME_ERR_DEVICE = -4       /* a kernel raised the device status word (bounded wait ran out) */
+};
+
+/* selection modes / scopes of come_select_windows */
+enum { COME_SELECT_RANK = 0, COME_SELECT_ABS = 1 };
+enum { COME_SCOPE_BATCH = 0, COME_SCOPE_FRAME = 1 };
+
+/*
+ * Token order of one frame.  grid_h == 0 selects the 1-D operator: `n_groups` groups of `group_w`
+ * consecutive tokens behind `start_index` special tokens (N = start_index + n_groups * group_w).
+ * grid_h > 0 selects the 2-D operator on a row-major grid_h x grid_w patch grid behind the special tokens
+ * (N = start_index + grid_h * grid_w): group_h x group_w windows tile the top-left
+ * floor(grid_h/group_h)*group_h x floor(grid_w/group_w)*group_w region in raster order; patches outside
+ * that region are never merged and are emitted, in row-major order, directly after the special tokens.
+ */
+typedef struct come_layout {
+    int32_t start_index;
+    int32_t grid_h, grid_w;
+    int32_t group_h, group_w;
+    int32_t n_groups; /* 1-D only; ignored (derived) for the 2-D operator */
+} come_layout_t;
+
+int come_version(void);
+const char *come_last_error(void);
+
+/* Number of groups (windows) per frame, tokens per frame and never-merged prefix length of a layout. */
+int come_layout_info(const come_layout_t *layout, int64_t *n_groups, int64_t *tokens_per_frame,
+                     int64_t *prefix_len);
+
+/*
+ * Window selection: per-patch confidence -> boolean merge mask.
+ * Replaces the tensor code of _CoMe_2D_Base.build_ctx (src/accelerate/token_merger/co_me_2d.py:268-298)
+ * and CoMe_TokenMerger.build_ctx (src/accelerate/token_merger/co_me.py:54-73).
+ *   conf_dev   [batch, frames_per_batch * grid_h * grid_w], dtype
+ *   mask_dev   [batch * frames_per_batch, M] uint8 (0/1), M = floor(grid_h/group_h) * floor(grid_w/group_w)
+ *   mode       COME_SELECT_RANK: mask = mean < quantile(mean, threshold) (linear interpolation, float32);
+ *              COME_SELECT_ABS : mask = mean < threshold
+ *   scope      COME_SCOPE_BATCH: one quantile per batch element over all its frames (2-D merger class);
+ *              COME_SCOPE_FRAME: one quantile per frame (1-D merger class, standalone op chain)
+ * At most 32768 windows per quantile group.
+ */
+int come_select_windows(const void *conf_dev, int dtype, int64_t batch, int64_t frames_per_batch, int grid_h,
+                        int grid_w, int group_h, int group_w, float threshold, int mode, int scope,
+                        uint8_t *mask_dev, void *stream);
+
+/*
+ * Merge index plan: everything of a merge that depends on the mask only.
+ * Replaces block_prefix_scan_kernel + at::cumsum (src/cuda_extension/co_me/src/kernel_token_merge.cu:12-46,
+ * 284-286) and the rev_id / weight writes of the scatter kernels (:92-107,146-161,186-190); fallback
+ * src/accelerate/token_merger/co_me.py:177-222.
+ *   mask_dev          [frames, M] uint8
+ *   group_prefix_dev  [frames, M] int32   exclusive scan of (mask ? 1 : G) inside a frame
+ *   offsets_dev       [frames + 1] int32  packed start row of every frame; offsets[frames] = P
+ *   rev_id_dev        [frames * N] int64  packed row of every input token, in the input token order
+ *   weight_dev        [>= P] float32      tokens represented by every packed row (G or 1); a buffer of
+ *                                         frames * N floats always suffices
+ *   seg_max_dev       [1] int32           longest packed frame (max_seqlen of frame attention); may be NULL
+ *   workspace_dev     come_merge_plan_workspace_bytes(frames) bytes of scratch
+ */
+size_t come_merge_plan_workspace_bytes(int64_t frames);
+int come_merge_plan(const uint8_t *mask_dev, int64_t frames, const come_layout_t *layout,
+                    int32_t *group_prefix_dev, int32_t *offsets_dev, int64_t *rev_id_dev, float *weight_dev,
+                    int32_t *seg_max_dev, void *workspace_dev, size_t workspace_bytes, void *stream);
+
+/*
+ * Merge data movement: packed rows from the token grid.
+ * Replaces token_merge_scatter_kernel{_vec4,} + token_merge_special_kernel
+ * (src/cuda_extension/co_me/src/kernel_token_merge.cu:50-191) and, for a 2-D layout, the gather pass of
+ * func_token_merge_2d (src/accelerate/token_merger/co_me_2d.py:193-211).
+ *   tokens_dev [frames, N, channels] contiguous; out_dev [P, channels]; same dtype.
+ * A merged window is the float32 left-to-right sum of its G rows divided by G, rounded once to dtype.
+ */
+int come_merge(const void *tokens_dev, int dtype, int64_t frames, int64_t channels, const come_layout_t *layout,
+               const uint8_t *mask_dev, const int32_t *group_prefix_dev, const int32_t *offsets_dev,
+               void *out_dev, void *stream);
+
+/*
+ * Unmerge: out[i, :] = merged[rev_id[i], :].
+ * Replaces token_split_gather_kernel{_vec4,} (src/cuda_extension/co_me/src/kernel_token_merge.cu:195-233,
+ * host :354-398); fallback index_select (src/accelerate/token_merger/co_me.py:241-254).
+ */
+int come_unmerge(const void *merged_dev, const int64_t *rev_id_dev, int64_t total, int64_t channels, int dtype,
+                 void *out_dev, void *stream);
+
+/*
+ * Variable-length attention forward with an optional additive per-key bias:
+ *   out[s:e, h] = softmax(q[s:e, h] k[s:e, h]^T * softmax_scale + bias[s:e][None, :]) v[s:e, h]
+ * for every packed segment [cu_seqlens[i], cu_seqlens[i+1]) and head h; non-causal, no dropout.
+ * Replaces varlen_fwd / varlen_fwd_w_perkey_bias (src/cuda_extension/flash_attn/flash_api.cpp:291-599,
+ * kernel src/cuda_extension/flash_attn/src/flash_fwd_kernel.h:30-55,80-545).
+ *   q/k/v_dev     element (row, head, d) at ptr[row * row_stride + head * head_dim + d] (strides in elements);
+ *                 dtype COME_F16 or COME_BF16
+ *   bias_dev      [total] in dtype, or NULL
+ *   out_dev       [total, num_heads, head_dim] with row stride out_row_stride (elements)
+ *   lse_dev       [num_heads, total] float32 log-sum-exp of the biased scaled scores; may be NULL
+ *   max_seqlen    upper bound of the segment lengths (sizes the grid only)
+ * head_dim 64 runs on the tcgen05 tensor-core kernel; other head dims (multiples of 8 up to 256) run on a
+ * plain CUDA-core kernel.  `backend`: 0 = automatic, 1 = force the CUDA-core kernel, 2 = require tcgen05.
+ */
+int come_attn_varlen_fwd(const void *q_dev, const void *k_dev, const void *v_dev, int dtype, int64_t total,
+                         int num_heads, int head_dim, int64_t q_row_stride, int64_t k_row_stride,
+                         int64_t v_row_stride, const void *bias_dev, const int32_t *cu_seqlens_dev,
+                         int num_segments, int max_seqlen, float softmax_scale, void *out_dev,
+                         int64_t out_row_stride, float *lse_dev, int backend, void *stream);
+
+/*
+ * Device status word: kernels that wait on hardware barriers give up after a bounded number of polls and
+ * record a non-zero code here instead of hanging.  Reads it back (synchronises the device) and optionally
+ * clears it.  Returns COME_OK with *value == 0 when no kernel reported a problem.
+ */
+int come_device_status(uint32_t *value, int clear);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* COME_B200_H */

@@ -1,0 +1,329 @@
+"""CPU oracle for the Co-Me hot path (merge plan, merge, unmerge, window selection, biased attention).
+
+TEST INFRASTRUCTURE ONLY.  This module is a plain numpy restatement of the reference algorithm and is
+imported by the test-suite, by the smoke check and by the CPU-baseline leg of the benchmark — never by the
+product package, which must fail loudly when its CUDA library is missing.
+
+Every function cites the reference file (paths relative to the reference project root) it restates.
+Pinned against the reference: the committed fixtures under ``tests/golden`` were produced by importing the
+reference's own PyTorch implementation on CPU (``tests/golden/make_golden.py``) and against the literal
+known-answer cases of the reference's test-suite (``tests/golden/reference_cases.py``).
+"""
+from __future__ import annotations
+
+import numpy as np
+
+__all__ = [
+    "merge_plan",
+    "token_merge",
+    "token_split",
+    "block_perm_2d",
+    "token_merge_2d",
+    "ragged_layout_2d",
+    "token_merge_2d_ragged",
+    "window_means",
+    "quantile_linear",
+    "select_windows",
+    "attention_bias",
+    "perkey_bias_from_weight",
+    "max_seqlen",
+]
+
+
+# --------------------------------------------------------------------------------------------------------
+# merge index plan
+# --------------------------------------------------------------------------------------------------------
+def merge_plan(mask: np.ndarray, group_size: int, start_index: int):
+    """Index plan of one merge.
+
+    Restates ``src/accelerate/token_merger/co_me.py:177-183,199-201`` (and the device twin
+    ``src/cuda_extension/co_me/src/kernel_token_merge.cu:12-46,284-286``):
+    a merged group emits one row, a kept group emits ``G`` rows, every frame starts with ``start_index``
+    untouched rows.
+
+    Returns ``(group_prefix[B,M] int64, offsets[B+1] int64, P)``.
+    """
+    mask = np.asarray(mask, dtype=bool)
+    B, M = mask.shape
+    G = int(group_size)
+    group_len = np.where(mask, 1, G).astype(np.int64)
+    group_prefix = np.cumsum(group_len, axis=1) - group_len
+    k_b = mask.sum(axis=1, dtype=np.int64)
+    L_b = start_index + (M - k_b) * G + k_b
+    offsets = np.zeros(B + 1, dtype=np.int64)
+    offsets[1:] = np.cumsum(L_b)
+    return group_prefix, offsets, int(offsets[-1])
+
+
+def _mean_rows_sequential(rows: np.ndarray) -> np.ndarray:
+    """Mean over axis -2 accumulated g = 0, 1, ... in the array's own precision, then a true division.
+
+    This is the rounding the reference's CPU path produces for ``img.mean(dim=2)``
+    (``co_me.py:192-193``): a left-to-right sum in the element type followed by ``/ G``.
+    float16 / bfloat16 inputs must be passed as float32 by the caller and rounded afterwards.
+    """
+    G = rows.shape[-2]
+    acc = np.zeros(rows.shape[:-2] + rows.shape[-1:], dtype=rows.dtype)
+    for g in range(G):
+        acc = acc + rows[..., g, :]
+    return acc / rows.dtype.type(G)
+
+
+# --------------------------------------------------------------------------------------------------------
+# 1-D merge / split
+# --------------------------------------------------------------------------------------------------------
+def token_merge(tokens: np.ndarray, start_index: int, group_size: int, mask: np.ndarray):
+    """``func_token_merge`` (``src/accelerate/token_merger/co_me.py:152-222``).
+
+    tokens ``[B, N, C]`` with ``N = start_index + M * G``; mask ``[B, M]`` bool.
+    Returns ``(out[P,C], offsets[B+1] int64, rev_id[B*N] int64, weight[P] float32)``.
+    """
+    tokens = np.asarray(tokens)
+    mask = np.asarray(mask, dtype=bool)
+    B, N, C = tokens.shape
+    _, M = mask.shape
+    G = int(group_size)
+    S = int(start_index)
+    if N != S + M * G:
+        raise ValueError(f"Expected N = start_index + M * group_size = {S + M * G}, got N = {N}")
+    group_prefix, offsets, P = merge_plan(mask, G, S)
+
+    out = np.empty((P, C), dtype=tokens.dtype)
+    rev = np.empty((B, N), dtype=np.int64)
+    weight = np.empty((P,), dtype=np.float32)
+    base = offsets[:-1]
+
+    special_pos = base[:, None] + np.arange(S, dtype=np.int64)[None, :]
+    out[special_pos.reshape(-1)] = tokens[:, :S, :].reshape(-1, C)
+    rev[:, :S] = special_pos
+    weight[special_pos.reshape(-1)] = 1.0
+
+    img = tokens[:, S:, :].reshape(B, M, G, C)
+    merged = _mean_rows_sequential(img)
+    group_base = base[:, None] + S + group_prefix  # [B, M]
+    unmerged_pos = group_base[..., None] + np.arange(G, dtype=np.int64)
+
+    merged_pos = group_base[mask]
+    out[merged_pos] = merged[mask]
+    weight[merged_pos] = float(G)
+
+    keep = ~mask
+    keep_pos = unmerged_pos[keep].reshape(-1)
+    out[keep_pos] = img[keep].reshape(-1, C)
+    weight[keep_pos] = 1.0
+
+    rev[:, S:] = np.where(mask[..., None], group_base[..., None], unmerged_pos).reshape(B, M * G)
+    return out, offsets, rev.reshape(-1), weight
+
+
+def token_split(merged: np.ndarray, rev_id: np.ndarray) -> np.ndarray:
+    """``func_token_split`` (``src/accelerate/token_merger/co_me.py:241-254``): ``out[i] = merged[rev_id[i]]``."""
+    return np.asarray(merged)[np.asarray(rev_id, dtype=np.int64)]
+
+
+# --------------------------------------------------------------------------------------------------------
+# 2-D merge
+# --------------------------------------------------------------------------------------------------------
+def block_perm_2d(H: int, W: int, gh: int, gw: int) -> np.ndarray:
+    """Row-major patch index of every (window, in-window) slot, windows in raster order.
+
+    Restates ``_build_2d_block_perm`` (``src/accelerate/token_merger/co_me_2d.py:26-35``).
+    """
+    idx = np.arange(H * W, dtype=np.int64).reshape(H // gh, gh, W // gw, gw)
+    return idx.transpose(0, 2, 1, 3).reshape(-1)
+
+
+def token_merge_2d(tokens, start_index, gh, gw, H, W, mask):
+    """``func_token_merge_2d`` / ``naive_func_token_merge_2d``
+    (``src/accelerate/token_merger/co_me_2d.py:77-211``): permute the patch grid into window order, run the
+    1-D merge with ``G = gh * gw``, and report ``rev_id`` in the original row-major token order.
+    """
+    tokens = np.asarray(tokens)
+    B, N, C = tokens.shape
+    if H % gh or W % gw:
+        raise ValueError("H and W must be divisible by the window size")
+    if N != start_index + H * W:
+        raise ValueError(f"Expected N = start_index + H * W = {start_index + H * W}, got N = {N}")
+    perm = np.concatenate([np.arange(start_index, dtype=np.int64), block_perm_2d(H, W, gh, gw) + start_index])
+    out, offsets, rev_perm, weight = token_merge(tokens[:, perm, :], start_index, gh * gw, mask)
+    inv = np.empty(N, dtype=np.int64)
+    inv[perm] = np.arange(N, dtype=np.int64)
+    rev = rev_perm.reshape(B, N)[:, inv]
+    return out, offsets, rev.reshape(-1), weight
+
+
+def ragged_layout_2d(start_index: int, H: int, W: int, gh: int, gw: int):
+    """Token order used when the patch grid is not a multiple of the window (e.g. 37x37 with 3x3 windows).
+
+    The reference itself rejects such grids (``co_me_2d.py:255-258``); the extension keeps the reference's
+    1-D semantics by moving the patches that no window covers (right columns and bottom rows, in row-major
+    order) directly behind the special tokens, so that they become part of the never-merged prefix
+    (``start_index' = start_index + #edge``), exactly as ``func_token_merge_2d`` permutes a divisible grid
+    (``co_me_2d.py:193-211``).
+
+    Returns ``(perm[N], prefix_len, M)`` with ``perm`` mapping merge order -> original token index.
+    """
+    Hc, Wc = (H // gh) * gh, (W // gw) * gw
+    yy, xx = np.meshgrid(np.arange(H), np.arange(W), indexing="ij")
+    covered = (yy < Hc) & (xx < Wc)
+    edge = (yy * W + xx)[~covered].reshape(-1).astype(np.int64)  # row-major order
+    idx = (np.arange(Hc, dtype=np.int64)[:, None] * W + np.arange(Wc, dtype=np.int64)[None, :])
+    win = idx.reshape(Hc // gh, gh, Wc // gw, gw).transpose(0, 2, 1, 3).reshape(-1)
+    perm = np.concatenate([np.arange(start_index, dtype=np.int64), edge + start_index, win + start_index])
+    return perm, start_index + edge.size, (Hc // gh) * (Wc // gw)
+
+
+def token_merge_2d_ragged(tokens, start_index, gh, gw, H, W, mask):
+    """2-D merge over the top-left ``floor(H/gh)*gh x floor(W/gw)*gw`` region; see :func:`ragged_layout_2d`."""
+    tokens = np.asarray(tokens)
+    B, N, C = tokens.shape
+    if N != start_index + H * W:
+        raise ValueError(f"Expected N = start_index + H * W = {start_index + H * W}, got N = {N}")
+    perm, prefix, M = ragged_layout_2d(start_index, H, W, gh, gw)
+    if np.asarray(mask).shape != (B, M):
+        raise ValueError(f"Expected M = {M}")
+    out, offsets, rev_perm, weight = token_merge(tokens[:, perm, :], prefix, gh * gw, mask)
+    inv = np.empty(N, dtype=np.int64)
+    inv[perm] = np.arange(N, dtype=np.int64)
+    rev = rev_perm.reshape(B, N)[:, inv]
+    return out, offsets, rev.reshape(-1), weight
+
+
+# --------------------------------------------------------------------------------------------------------
+# window selection
+# --------------------------------------------------------------------------------------------------------
+def _round_like(x32: np.ndarray, kind: str) -> np.ndarray:
+    """Round float32 values to the storage precision ``kind`` and return them as float32."""
+    if kind == "f32":
+        return x32.astype(np.float32)
+    if kind == "f16":
+        return x32.astype(np.float16).astype(np.float32)
+    if kind == "bf16":
+        u = x32.astype(np.float32).view(np.uint32).astype(np.uint64)
+        nan = np.isnan(x32)
+        r = ((u + 0x7FFF + ((u >> 16) & 1)) >> 16) << 16  # round to nearest even
+        out = (r & 0xFFFFFFFF).astype(np.uint32).view(np.float32)
+        return np.where(nan, np.float32(np.nan), out)
+    raise ValueError(kind)
+
+
+def window_means(conf: np.ndarray, H: int, W: int, gh: int, gw: int, kind: str = "f32") -> np.ndarray:
+    """Per-window mean confidence ``[F, M]`` from per-patch confidence ``[F, H*W]``.
+
+    Restates ``conf_blocks.mean(dim=-1)`` (``src/accelerate/token_merger/co_me_2d.py:270-272,291``).  Windows
+    tile the top-left ``floor(H/gh)*gh x floor(W/gw)*gw`` region in raster order.  The sum runs over the window
+    row by row (``g = 0 .. gh*gw-1``) in float32 and is divided by ``gh*gw``; the result is rounded to the
+    confidence storage precision ``kind`` ("f32", "f16", "bf16") like a tensor of that dtype would be.
+    """
+    conf = np.asarray(conf, dtype=np.float32)
+    F = conf.shape[0]
+    Hm, Wm = H // gh, W // gw
+    grid = conf.reshape(F, H, W)[:, : Hm * gh, : Wm * gw]
+    blocks = grid.reshape(F, Hm, gh, Wm, gw).transpose(0, 1, 3, 2, 4).reshape(F, Hm * Wm, gh * gw)
+    acc = np.zeros((F, Hm * Wm), dtype=np.float32)
+    for g in range(gh * gw):
+        acc = acc + blocks[:, :, g]
+    return _round_like(acc / np.float32(gh * gw), kind)
+
+
+def quantile_linear(values: np.ndarray, q: float) -> np.float32:
+    """``torch.quantile(values.float(), q)`` with the default linear interpolation, restated.
+
+    PyTorch 2.x (``aten/src/ATen/native/Sorting.cpp`` ``quantile_compute`` + ``cpu/LerpKernel.cpp``): sort
+    ascending, ``rank = q * (n - 1)`` in float32, ``lo = floor(rank)``, ``hi = ceil(rank)``, ``w = rank - lo``
+    and a fused-multiply-add lerp: ``fma(w, b - a, a)`` for ``w < 0.5`` and ``fma(w - 1, b - a, b)`` otherwise
+    (one rounding; the product of two float32 is exact in float64, which stands in for the fused operation).
+    Checked against ``torch.quantile`` itself in the CPU tests.
+    """
+    v = np.sort(np.asarray(values, dtype=np.float32).reshape(-1))
+    n = v.size
+    rank = np.float32(q) * np.float32(n - 1)
+    lo = np.floor(rank)
+    hi = np.ceil(rank)
+    w = np.float32(rank - lo)
+    a, b = v[int(lo)], v[int(hi)]
+    d = np.float32(b - a)
+    if w < np.float32(0.5):
+        return np.float32(np.float64(w) * np.float64(d) + np.float64(a))
+    return np.float32(np.float64(np.float32(w - np.float32(1.0))) * np.float64(d) + np.float64(b))
+
+
+def select_windows(conf, B, S, H, W, gh, gw, threshold, mode="pairwise-rank", scope="batch", kind="f32"):
+    """Merge mask ``[B*S, M]`` from per-patch confidence ``[B, S*H*W]``.
+
+    Restates the tensor code of ``_CoMe_2D_Base.build_ctx`` (``src/accelerate/token_merger/co_me_2d.py:268-298``)
+    and of ``CoMe_TokenMerger.build_ctx`` (``src/accelerate/token_merger/co_me.py:54-73``):
+
+    * ``pairwise-rank``: ``mask = mean < quantile(mean.float(), threshold)``; the quantile is taken over all
+      ``S*M`` windows of a batch element (``scope="batch"``, the 2-D class) or over the ``M`` windows of a frame
+      (``scope="frame"``, the 1-D class and the standalone op-chain configuration);
+    * ``abs_mse``: ``mask = mean < threshold``;
+    * ``mse``: confidences are z-normalised per batch element (unbiased std, ``+1e-3``) before the window mean.
+    """
+    conf = np.asarray(conf, dtype=np.float32).reshape(B, S * H * W)
+    if mode == "mse":
+        mu = conf.mean(axis=-1, keepdims=True, dtype=np.float32)
+        sd = conf.std(axis=-1, keepdims=True, ddof=1, dtype=np.float32)
+        conf = _round_like((conf - mu) / (sd + np.float32(1e-3)), kind)
+    means = window_means(conf.reshape(B * S, H * W), H, W, gh, gw, kind)  # [B*S, M]
+    M = means.shape[1]
+    if mode in ("abs_mse", "mse"):
+        return means < np.float32(threshold)
+    if mode != "pairwise-rank":
+        raise ValueError(mode)
+    if not (0.0 <= threshold <= 1.0):
+        raise ValueError(f"Ranking mode requires threshold in [0, 1], got {threshold}")
+    if scope == "batch":
+        grouped = means.reshape(B, S * M)
+    elif scope == "frame":
+        grouped = means.reshape(B * S, M)
+    else:
+        raise ValueError(scope)
+    thr = np.array([quantile_linear(row, threshold) for row in grouped], dtype=np.float32)
+    return (grouped < thr[:, None]).reshape(B * S, M)
+
+
+# --------------------------------------------------------------------------------------------------------
+# biased variable-length attention
+# --------------------------------------------------------------------------------------------------------
+def perkey_bias_from_weight(weight: np.ndarray, kind: str = "bf16") -> np.ndarray:
+    """``log(weight)`` rounded to the run dtype (``src/accelerate/vggt/module/bias_attention.py:120``)."""
+    return _round_like(np.log(np.asarray(weight, dtype=np.float32)), kind)
+
+
+def max_seqlen(cu_seqlens: np.ndarray) -> int:
+    """``infer_flash_attn_varlen_max_seqlen`` (``src/cuda_extension/flash_attn/__init__.py:21-33``)."""
+    cu = np.asarray(cu_seqlens, dtype=np.int64)
+    return int((cu[1:] - cu[:-1]).max()) if cu.size > 1 else 0
+
+
+def attention_bias(q, k, v, bias, cu_seqlens, scale):
+    """fp32 biased softmax attention per segment and head.
+
+    Restates the reference's test oracle ``_reference_attention_with_bias``
+    (``test/auto_test/test_flex_attention_bias.py:26-36``):
+    ``softmax(q @ k.T * scale + bias[None, :]) @ v`` for every packed segment ``[cu[i], cu[i+1])`` and head,
+    which is what the device kernel computes (``src/cuda_extension/flash_attn/src/flash_fwd_kernel.h:30-55``).
+
+    q, k, v ``[P, H, D]`` float32; bias ``[P]`` float32 or ``None``; returns ``(out[P,H,D], lse[H,P])`` float32.
+    """
+    q = np.asarray(q, dtype=np.float32)
+    k = np.asarray(k, dtype=np.float32)
+    v = np.asarray(v, dtype=np.float32)
+    P, Hh, D = q.shape
+    cu = np.asarray(cu_seqlens, dtype=np.int64)
+    out = np.zeros((P, Hh, D), dtype=np.float32)
+    lse = np.full((Hh, P), np.inf, dtype=np.float32)
+    for i in range(cu.size - 1):
+        s, e = int(cu[i]), int(cu[i + 1])
+        if e <= s:
+            continue
+        b = np.zeros(e - s, np.float32) if bias is None else np.asarray(bias[s:e], dtype=np.float32)
+        for h in range(Hh):
+            logits = (q[s:e, h, :] @ k[s:e, h, :].T) * np.float32(scale) + b[None, :]
+            m = logits.max(axis=-1, keepdims=True)
+            p = np.exp(logits - m)
+            l = p.sum(axis=-1, keepdims=True)
+            out[s:e, h, :] = (p / l) @ v[s:e, h, :]
+            lse[h, s:e] = (m + np.log(l))[:, 0]
+    return out, lse

@@ -1,0 +1,127 @@
+"""Seeded input generators shared by ``make_golden.py`` (which runs the reference on them) and by the tests
+(which feed the same inputs to the oracle and to the CUDA library and compare with the stored outputs).
+
+All randomness comes from ``numpy.random.default_rng`` so that no reference checkout is needed to rebuild an
+input.  Values meant for a 16-bit dtype are rounded here and carried as float32.
+"""
+from __future__ import annotations
+
+import numpy as np
+
+
+def round_bf16(x: np.ndarray) -> np.ndarray:
+    u = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    r = ((u + 0x7FFF + ((u >> 16) & 1)) >> 16) << 16
+    return (r & 0xFFFFFFFF).astype(np.uint32).view(np.float32)
+
+
+def round_kind(x: np.ndarray, kind: str) -> np.ndarray:
+    if kind == "f32":
+        return np.ascontiguousarray(x, dtype=np.float32)
+    if kind == "bf16":
+        return round_bf16(x)
+    if kind == "f16":
+        return x.astype(np.float16).astype(np.float32)
+    raise ValueError(kind)
+
+
+def summarize_rows(a: np.ndarray, stride: int = 251) -> dict:
+    """Compact fingerprint of a float matrix: exact per-row float64 sums, and every ``stride``-th row in full
+    (small matrices are kept whole)."""
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    if a.size <= 1 << 15:
+        return {"full": a}
+    return {"rowsum": a.astype(np.float64).sum(axis=1), "sample": a[::stride].copy(),
+            "stride": np.asarray(stride)}
+
+
+def check_rows(a: np.ndarray, store, prefix: str, rtol: float = 0.0, atol: float = 0.0) -> None:
+    """Assert that ``a`` matches the fingerprint written by :func:`summarize_rows` (bit for bit by default;
+    the row sums get the element tolerance times the row length)."""
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    if prefix + "full" in store:
+        np.testing.assert_allclose(a, store[prefix + "full"], rtol=rtol, atol=atol)
+        return
+    n = a.shape[1]
+    np.testing.assert_allclose(a.astype(np.float64).sum(axis=1), store[prefix + "rowsum"], rtol=rtol,
+                               atol=n * (atol + rtol * float(np.abs(a).max())))
+    np.testing.assert_allclose(a[:: int(store[prefix + "stride"])], store[prefix + "sample"], rtol=rtol, atol=atol)
+
+
+# ---- merge ------------------------------------------------------------------------------------------------
+def merge1d_inputs(i: int, cfg, kind: str = "f32"):
+    B, M, G, S, C = cfg
+    rng = np.random.default_rng(4200 + i)
+    tokens = round_kind(rng.standard_normal((B, S + M * G, C), dtype=np.float32), kind)
+    ratio = rng.uniform(0.1, 0.9)
+    mask = rng.random((B, M)) < ratio
+    return tokens, mask
+
+
+def merge2d_inputs(i: int, cfg):
+    B, H, W, gh, gw, S, C = cfg
+    rng = np.random.default_rng(4300 + i)
+    tokens = rng.standard_normal((B, S + H * W, C), dtype=np.float32)
+    mask = rng.random((B, (H // gh) * (W // gw))) < 0.5
+    return tokens, mask
+
+
+# ---- selection ---------------------------------------------------------------------------------------------
+SELECT_CASES = {
+    # name: batch, frames, grid, window, threshold, mode, merger class ("2d": quantile over the whole batch
+    # element, "1d": per frame over consecutive groups), confidence dtype
+    "rank2d_bf16": dict(B=1, S=8, H=36, W=36, gh=3, gw=3, thr=0.5, mode="pairwise-rank", cls="2d", kind="bf16"),
+    "rank2d_b2_f32": dict(B=2, S=4, H=12, W=12, gh=3, gw=3, thr=0.3, mode="pairwise-rank", cls="2d", kind="f32"),
+    "rank2d_2x3_bf16": dict(B=2, S=3, H=8, W=12, gh=2, gw=3, thr=0.75, mode="pairwise-rank", cls="2d", kind="bf16"),
+    "rank2d_thr0": dict(B=1, S=2, H=6, W=6, gh=3, gw=3, thr=0.0, mode="pairwise-rank", cls="2d", kind="bf16"),
+    "rank2d_thr1": dict(B=1, S=2, H=6, W=6, gh=3, gw=3, thr=1.0, mode="pairwise-rank", cls="2d", kind="bf16"),
+    "rank2d_100f_bf16": dict(B=1, S=100, H=36, W=36, gh=3, gw=3, thr=0.5, mode="pairwise-rank", cls="2d", kind="bf16"),
+    "abs2d_bf16": dict(B=2, S=2, H=9, W=9, gh=3, gw=3, thr=0.45, mode="abs_mse", cls="2d", kind="bf16"),
+    "rank1d_bf16": dict(B=2, S=3, H=6, W=18, gh=1, gw=9, thr=0.5, mode="pairwise-rank", cls="1d", kind="bf16"),
+    "rank1d_f16": dict(B=1, S=4, H=4, W=16, gh=1, gw=4, thr=0.25, mode="pairwise-rank", cls="1d", kind="f16"),
+}
+
+
+def select_inputs(name: str) -> np.ndarray:
+    spec = SELECT_CASES[name]
+    rng = np.random.default_rng(abs(hash_name(name)))
+    conf = rng.random((spec["B"], spec["S"] * spec["H"] * spec["W"]), dtype=np.float32)
+    return round_kind(conf, spec["kind"])
+
+
+def hash_name(name: str) -> int:
+    h = 2166136261
+    for ch in name.encode():
+        h = ((h ^ ch) * 16777619) & 0xFFFFFFFF
+    return h
+
+
+# ---- attention ---------------------------------------------------------------------------------------------
+EXTRA_ATTENTION_CASES = [  # (seq_lens, H, D, dtype) beyond the reference's own list
+    ([798, 300], 1, 64, "bf16"),   # one post-merge frame length of the headline configuration + a short one
+    ([1, 7, 129], 2, 64, "bf16"),  # degenerate and just-over-a-tile segments
+    ([257], 3, 64, "f16"),
+]
+
+
+def attention_inputs(i: int, case):
+    seq_lens, H, D, kind = case
+    P = int(sum(seq_lens))
+    rng = np.random.default_rng(4400 + i)
+    qkv = round_kind(rng.standard_normal((P, 3, H, D), dtype=np.float32), kind)
+    weight = np.maximum(rng.random(P, dtype=np.float32), np.float32(1e-3))
+    if i % 2 == 1:  # merge-count style weights {1, 9}
+        weight = np.where(rng.random(P) < 0.25, np.float32(9.0), np.float32(1.0))
+    bias = round_kind(np.log(weight.astype(np.float32)), kind)
+    cu = np.zeros(len(seq_lens) + 1, np.int32)
+    cu[1:] = np.cumsum(seq_lens)
+    return qkv, bias, cu
+
+
+# ---- headline standalone configuration -----------------------------------------------------------------------
+def cfg1_inputs(frames: int = 8, channels: int = 1024):
+    """8 frames x (5 special + 37x37 patch) tokens ~N(0,1), per-patch confidence ~U(0,1), seed 0."""
+    rng = np.random.default_rng(0)
+    tokens = rng.standard_normal((frames, 5 + 37 * 37, channels), dtype=np.float32)
+    conf = rng.random((frames, 37 * 37), dtype=np.float32)
+    return tokens, conf

@@ -1,0 +1,209 @@
+"""Generate the golden fixtures in this directory by running the REFERENCE implementation on CPU.
+
+Usage (only where a checkout of the reference is available)::
+
+    python tests/golden/make_golden.py --reference /path/to/CoMe
+
+The reference's PyTorch fallback path (``CUDAExtension.disable()``) is imported unmodified; four modules that
+are not installed here (``hydra``, ``omegaconf``, ``pypose`` and the compiled ``src.cuda_extension``) are
+replaced by empty stubs.  Inputs are drawn from ``numpy.random.default_rng(seed)`` so that the tests can
+regenerate them without the reference; outputs are stored in ``*.npz`` files (integer outputs in full, large
+float outputs as per-row float64 sums plus a strided sample of complete rows).
+
+The tests never import the reference; they only read the ``*.npz`` files written here.
+"""
+from __future__ import annotations
+
+import argparse
+import os
+import sys
+import types
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, HERE)
+sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+
+from reference_cases import RANDOM_CONFIGS_1D, RANDOM_CONFIGS_2D, ATTENTION_CASES  # noqa: E402
+from golden_inputs import (  # noqa: E402
+    merge1d_inputs, merge2d_inputs, select_inputs, SELECT_CASES, attention_inputs, EXTRA_ATTENTION_CASES,
+    cfg1_inputs, summarize_rows,
+)
+
+
+def import_reference(root: str):
+    def stub(name, **attrs):
+        m = types.ModuleType(name)
+        m.__dict__.update(attrs)
+        sys.modules[name] = m
+        return m
+
+    stub("hydra")
+    sys.modules["hydra"].utils = stub("hydra.utils", instantiate=lambda *a, **k: None)
+    stub("omegaconf", DictConfig=dict, OmegaConf=object)
+    stub("pypose")
+    sys.path.insert(0, root)
+    import src  # noqa: F401  (the reference's real top-level package)
+
+    ce = types.ModuleType("src.cuda_extension")
+    ce.__path__ = []
+    ce.co_me_cuext = types.ModuleType("co_me_cuext")
+    ce.flash_attn_varlen_qkvpacked_func = None
+    ce.flash_attn_varlen_qkvpacked_func_w_perkey_bias = None
+    ce.infer_flash_attn_varlen_max_seqlen = None
+    sys.modules["src.cuda_extension"] = ce
+    fa = types.ModuleType("src.cuda_extension.flash_attn")
+    fa.infer_flash_attn_varlen_max_seqlen = None
+    sys.modules["src.cuda_extension.flash_attn"] = fa
+
+    from src.accelerate.token_merger import co_me, co_me_2d
+    from src.utility.feature import CUDAExtension
+    import test.auto_test.test_flex_attention_bias as attn_test
+
+    return co_me, co_me_2d, CUDAExtension, attn_test
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--reference", default="/root/reference")
+    args = ap.parse_args()
+    import torch
+
+    co_me, co_me_2d, CUDAExtension, attn_test = import_reference(args.reference)
+    import oracle.come_oracle as orc
+
+    def t(x):
+        return torch.from_numpy(np.ascontiguousarray(x))
+
+    def close(ours, ref, kind="f32"):
+        """Features: the reference's vectorised CPU reduction may differ from the left-to-right sum by one
+        rounding (observed <= 1.2e-7 relative); indices and counts are compared exactly elsewhere."""
+        tol = 1e-6 if kind == "f32" else 8e-3
+        return np.allclose(ours, ref, rtol=tol, atol=tol)
+
+    # ---- 1-D merge / split -----------------------------------------------------------------------------
+    store = {}
+    for i, cfg in enumerate(RANDOM_CONFIGS_1D):
+        for kind in ("f32", "bf16"):
+            tokens, mask = merge1d_inputs(i, cfg, kind)
+            B, M, G, S, C = cfg
+            tt = t(tokens).bfloat16() if kind == "bf16" else t(tokens)
+            with CUDAExtension.disable():
+                jag, rev = co_me.func_token_merge(tt, S, G, t(mask))
+                restored = co_me.func_token_split(jag, rev, (1, B, S + M * G, C))
+            out = jag.tokens[0].float().numpy()
+            # the oracle must agree bit for bit with the reference before anything is written
+            o_out, o_off, o_rev, o_w = orc.token_merge(tokens, S, G, mask)
+            if kind == "bf16":
+                o_out = orc._round_like(o_out, "bf16")
+            assert close(o_out, out, kind), ("merge tokens", cfg, kind)
+            assert np.array_equal(o_off, jag.offset.numpy()) and np.array_equal(o_rev, rev.numpy())
+            assert np.array_equal(o_w, jag.weight.numpy())
+            assert close(orc.token_split(o_out, o_rev), restored.float().numpy().reshape(-1, C), kind)
+            key = f"c{i}_{kind}"
+            store[key + "_offset"] = jag.offset.numpy()
+            store[key + "_rev"] = rev.numpy().astype(np.int32)
+            store[key + "_weight"] = jag.weight.numpy().astype(np.uint8)
+            store.update({f"{key}_out_{k}": v for k, v in summarize_rows(out).items()})
+            store.update({f"{key}_res_{k}": v for k, v in summarize_rows(restored.float().numpy().reshape(-1, C)).items()})
+    np.savez_compressed(os.path.join(HERE, "merge_1d.npz"), **store)
+
+    # ---- 2-D merge ---------------------------------------------------------------------------------------
+    store = {}
+    for i, cfg in enumerate(RANDOM_CONFIGS_2D):
+        tokens, mask = merge2d_inputs(i, cfg)
+        B, H, W, gh, gw, S, C = cfg
+        with CUDAExtension.disable():
+            jn, rn = co_me_2d.naive_func_token_merge_2d(t(tokens), S, gh, gw, H, W, t(mask))
+            jc, rc = co_me_2d.func_token_merge_2d(t(tokens), S, gh, gw, H, W, t(mask))
+        assert torch.allclose(jn.tokens, jc.tokens, rtol=1e-6, atol=1e-6) and torch.equal(rn, rc) and torch.equal(jn.offset, jc.offset)
+        o_out, o_off, o_rev, o_w = orc.token_merge_2d(tokens, S, gh, gw, H, W, mask)
+        assert close(o_out, jn.tokens[0].numpy()) and np.array_equal(o_rev, rn.numpy())
+        assert np.array_equal(o_off, jn.offset.numpy()) and np.array_equal(o_w, jn.weight.numpy())
+        key = f"c{i}"
+        store[key + "_offset"] = jn.offset.numpy()
+        store[key + "_rev"] = rn.numpy().astype(np.int32)
+        store[key + "_weight"] = jn.weight.numpy().astype(np.uint8)
+        store.update({f"{key}_out_{k}": v for k, v in summarize_rows(jn.tokens[0].numpy()).items()})
+    np.savez_compressed(os.path.join(HERE, "merge_2d.npz"), **store)
+
+    # ---- window selection: the reference's own build_ctx tensor code behind a stand-in predictor -------
+    store = {}
+    for name, spec in SELECT_CASES.items():
+        conf = select_inputs(name)  # float32 array holding values exactly representable in spec["kind"]
+        B, S, H, W = spec["B"], spec["S"], spec["H"], spec["W"]
+        dt = {"f32": torch.float32, "bf16": torch.bfloat16, "f16": torch.float16}[spec["kind"]]
+        conf_t = t(conf).to(dt).reshape(B, S * H * W, 1)
+        if spec["cls"] == "2d":
+            merger = object.__new__(co_me_2d.CoMe_2D_TokenMerger)
+            merger.group_h, merger.group_w = spec["gh"], spec["gw"]
+            merger.conf_mode = co_me_2d.CoMe_2D_TokenMerger.ConfidenceMode(spec["mode"])
+        else:
+            merger = object.__new__(co_me.CoMe_TokenMerger)
+            merger.group_size = spec["gh"] * spec["gw"]
+            merger.conf_mode = co_me.CoMe_TokenMerger.ConfidenceMode(spec["mode"])
+        merger.start_idx = 5
+        merger.threshold = spec["thr"]
+        merger.predictor = lambda feature, BPHWC, _c=conf_t: _c
+        feature = torch.zeros(B, S, 4, H, W)
+        mask, _shape = merger.build_ctx(feature)
+        mask = mask.numpy()
+        scope = "batch" if spec["cls"] == "2d" else "frame"
+        o_mask = orc.select_windows(conf, B, S, H, W, spec["gh"], spec["gw"], spec["thr"], spec["mode"], scope,
+                                    spec["kind"])
+        assert np.array_equal(o_mask, mask), ("select", name, int((o_mask != mask).sum()))
+        store[name + "_mask"] = np.packbits(mask.reshape(-1))
+        store[name + "_shape"] = np.asarray(mask.shape)
+    np.savez_compressed(os.path.join(HERE, "select.npz"), **store)
+
+    # ---- biased attention: the reference test-suite's fp32 oracle ----------------------------------------
+    store = {}
+    for i, case in enumerate(list(ATTENTION_CASES) + list(EXTRA_ATTENTION_CASES)):
+        seq_lens, Hh, D, kind = case
+        qkv, bias, cu = attention_inputs(i, case)
+        scale = 1.0 / (D ** 0.5)
+        out = np.zeros((qkv.shape[0], Hh, D), np.float32)
+        q, k, v = (t(qkv[:, j]) for j in range(3))
+        for s in range(len(seq_lens)):
+            a, b = int(cu[s]), int(cu[s + 1])
+            for h in range(Hh):
+                out[a:b, h] = attn_test._reference_attention_with_bias(
+                    q[a:b, h], k[a:b, h], v[a:b, h], t(bias)[a:b], scale).numpy()
+        o_out, _ = orc.attention_bias(qkv[:, 0], qkv[:, 1], qkv[:, 2], bias, cu, scale)
+        assert np.allclose(o_out, out, atol=2e-6, rtol=1e-5), ("attention", case, np.abs(o_out - out).max())
+        store[f"a{i}_out"] = out.astype(np.float32)
+    np.savez_compressed(os.path.join(HERE, "attention.npz"), **store)
+
+    # ---- standalone op chain of the headline configuration (8 x 1374 tokens, 37x37 grid, 3x3 windows) ----
+    tokens, conf = cfg1_inputs()
+    B, N, C = tokens.shape
+    mask = orc.select_windows(conf, 8, 1, 37, 37, 3, 3, 0.5, "pairwise-rank", "frame", "f32")
+    # reference selection arithmetic on the same window means (torch.quantile + strict <)
+    means = t(orc.window_means(conf, 37, 37, 3, 3))
+    ref_mask = (means < torch.quantile(means.float(), 0.5, dim=-1, keepdim=True)).numpy()
+    assert np.array_equal(mask, ref_mask)
+    perm, prefix, M = orc.ragged_layout_2d(5, 37, 37, 3, 3)
+    with CUDAExtension.disable():
+        jag, rev_perm = co_me.func_token_merge(t(tokens[:, perm, :]), prefix, 9, t(mask))
+    inv = np.empty(N, np.int64)
+    inv[perm] = np.arange(N)
+    rev = rev_perm.numpy().reshape(B, N)[:, inv].reshape(-1)
+    o_out, o_off, o_rev, o_w = orc.token_merge_2d_ragged(tokens, 5, 3, 3, 37, 37, mask)
+    assert close(o_out, jag.tokens[0].numpy()) and np.array_equal(o_rev, rev)
+    assert np.array_equal(o_off, jag.offset.numpy()) and np.array_equal(o_w, jag.weight.numpy())
+    with CUDAExtension.disable():
+        restored = co_me.func_token_split(jag, t(rev), (1, B, N, C)).numpy().reshape(-1, C)
+    store = dict(mask=np.packbits(mask.reshape(-1)), offset=jag.offset.numpy(), rev=rev.astype(np.int32),
+                 weight=jag.weight.numpy().astype(np.uint8))
+    store.update({f"out_{k}": v for k, v in summarize_rows(jag.tokens[0].numpy(), 97).items()})
+    store.update({f"res_{k}": v for k, v in summarize_rows(restored, 211).items()})
+    np.savez_compressed(os.path.join(HERE, "cfg1_chain.npz"), **store)
+    print("fixtures written to", HERE)
+    for f in sorted(os.listdir(HERE)):
+        if f.endswith(".npz"):
+            print(f"  {f}: {os.path.getsize(os.path.join(HERE, f)) / 1024:.0f} KiB")
+
+
+if __name__ == "__main__":
+    main()

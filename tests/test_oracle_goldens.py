@@ -1,0 +1,148 @@
+"""The CPU oracle against the reference: literal known-answer cases of the reference's tests and fixtures
+written by running the reference itself (tests/golden/make_golden.py).  No GPU needed."""
+import os
+
+import numpy as np
+import pytest
+
+import golden_inputs as gi
+import reference_cases as rc
+from oracle import clib, come_oracle as orc
+
+FEATURE_TOL = dict(rtol=1e-6, atol=1e-6)  # the reference's vectorised CPU sum may round once differently
+
+
+def _load(golden_dir, name):
+    return np.load(os.path.join(golden_dir, name))
+
+
+@pytest.mark.parametrize("idx", range(len(rc.CASES_1D)))
+@pytest.mark.parametrize("impl", ["numpy", "c"])
+def test_reference_literals_1d(idx, impl):
+    c = rc.as_arrays(rc.CASES_1D[idx])
+    merge = orc.token_merge if impl == "numpy" else clib.token_merge
+    split = orc.token_split if impl == "numpy" else clib.token_split
+    out, off, rev, w = merge(c["tokens"], c["start_index"], c["group_size"], c["mask"])
+    np.testing.assert_array_equal(out, c["out"])
+    np.testing.assert_array_equal(off, c["offset"])
+    np.testing.assert_array_equal(rev, c["rev"])
+    np.testing.assert_array_equal(w, c["weight"])
+    B, N, C = c["tokens"].shape
+    np.testing.assert_array_equal(split(out, rev).reshape(B, N, C), c["restored"])
+
+
+@pytest.mark.parametrize("idx", range(len(rc.CASES_2D)))
+@pytest.mark.parametrize("impl", ["numpy", "numpy-ragged", "c"])
+def test_reference_literals_2d(idx, impl):
+    c = rc.as_arrays(rc.CASES_2D[idx])
+    fn = {"numpy": orc.token_merge_2d, "numpy-ragged": orc.token_merge_2d_ragged, "c": clib.token_merge_2d}[impl]
+    out, off, rev, w = fn(c["tokens"], c["start_index"], c["gh"], c["gw"], c["H"], c["W"], c["mask"])
+    np.testing.assert_array_equal(out, c["out"])
+    np.testing.assert_array_equal(off, c["offset"])
+    np.testing.assert_array_equal(rev, c["rev"])
+    np.testing.assert_array_equal(w, c["weight"])
+    B, N, C = c["tokens"].shape
+    np.testing.assert_array_equal(orc.token_split(out, rev).reshape(B, N, C), c["restored"])
+
+
+@pytest.mark.parametrize("idx", range(len(rc.RANDOM_CONFIGS_1D)))
+@pytest.mark.parametrize("kind", ["f32", "bf16"])
+def test_merge_1d_fixture(golden_dir, idx, kind):
+    z = _load(golden_dir, "merge_1d.npz")
+    cfg = rc.RANDOM_CONFIGS_1D[idx]
+    tokens, mask = gi.merge1d_inputs(idx, cfg, kind)
+    B, M, G, S, C = cfg
+    key = f"c{idx}_{kind}_"
+    tol = FEATURE_TOL if kind == "f32" else dict(rtol=8e-3, atol=8e-3)
+    for name, impl in (("numpy", orc.token_merge), ("c", lambda *a: clib.token_merge(*a, kind=kind))):
+        out, off, rev, w = impl(tokens, S, G, mask)
+        if name == "numpy" and kind != "f32":
+            out = orc._round_like(out, kind)
+        np.testing.assert_array_equal(off, z[key + "offset"])
+        np.testing.assert_array_equal(rev, z[key + "rev"].astype(np.int64))
+        np.testing.assert_array_equal(w, z[key + "weight"].astype(np.float32))
+        gi.check_rows(out, z, key + "out_", **tol)
+        gi.check_rows(orc.token_split(out, rev), z, key + "res_", **tol)
+        if name == "numpy":
+            first = out
+        else:
+            np.testing.assert_array_equal(out, first)  # the two oracles agree bit for bit
+
+
+@pytest.mark.parametrize("idx", range(len(rc.RANDOM_CONFIGS_2D)))
+def test_merge_2d_fixture(golden_dir, idx):
+    z = _load(golden_dir, "merge_2d.npz")
+    cfg = rc.RANDOM_CONFIGS_2D[idx]
+    tokens, mask = gi.merge2d_inputs(idx, cfg)
+    B, H, W, gh, gw, S, C = cfg
+    key = f"c{idx}_"
+    a = orc.token_merge_2d(tokens, S, gh, gw, H, W, mask)
+    b = clib.token_merge_2d(tokens, S, gh, gw, H, W, mask)
+    c = orc.token_merge_2d_ragged(tokens, S, gh, gw, H, W, mask)
+    for out, off, rev, w in (a, b, c):
+        np.testing.assert_array_equal(off, z[key + "offset"])
+        np.testing.assert_array_equal(rev, z[key + "rev"].astype(np.int64))
+        np.testing.assert_array_equal(w, z[key + "weight"].astype(np.float32))
+        gi.check_rows(out, z, key + "out_", **FEATURE_TOL)
+        np.testing.assert_array_equal(out, a[0])
+
+
+@pytest.mark.parametrize("name", sorted(gi.SELECT_CASES))
+def test_select_fixture(golden_dir, name):
+    z = _load(golden_dir, "select.npz")
+    spec = gi.SELECT_CASES[name]
+    conf = gi.select_inputs(name)
+    shape = tuple(z[name + "_shape"])
+    want = np.unpackbits(z[name + "_mask"])[: shape[0] * shape[1]].reshape(shape).astype(bool)
+    scope = "batch" if spec["cls"] == "2d" else "frame"
+    args = (conf, spec["B"], spec["S"], spec["H"], spec["W"], spec["gh"], spec["gw"], spec["thr"], spec["mode"], scope,
+            spec["kind"])
+    np.testing.assert_array_equal(orc.select_windows(*args), want)
+    np.testing.assert_array_equal(clib.select_windows(*args), want)
+
+
+def test_quantile_matches_torch():
+    torch = pytest.importorskip("torch")
+    rng = np.random.default_rng(7)
+    for n in (1, 2, 3, 7, 144, 145, 1152, 14400):
+        for q in (0.0, 0.1, 0.25, 0.5, 0.75, 0.9, 1.0, 0.333):
+            v = rng.random(n, dtype=np.float32)
+            want = torch.quantile(torch.from_numpy(v), q).item()
+            assert float(orc.quantile_linear(v, q)) == want, (n, q)
+
+
+@pytest.mark.parametrize("idx", range(len(rc.ATTENTION_CASES) + len(gi.EXTRA_ATTENTION_CASES)))
+def test_attention_fixture(golden_dir, idx):
+    z = _load(golden_dir, "attention.npz")
+    case = (list(rc.ATTENTION_CASES) + list(gi.EXTRA_ATTENTION_CASES))[idx]
+    seq_lens, H, D, kind = case
+    qkv, bias, cu = gi.attention_inputs(idx, case)
+    scale = 1.0 / (D ** 0.5)
+    want = z[f"a{idx}_out"]
+    out, lse = orc.attention_bias(qkv[:, 0], qkv[:, 1], qkv[:, 2], bias, cu, scale)
+    np.testing.assert_allclose(out, want, rtol=1e-5, atol=2e-6)
+    out_c, lse_c = clib.attention_bias(qkv, bias, cu, scale)
+    np.testing.assert_allclose(out_c, want, rtol=1e-4, atol=5e-6)
+    np.testing.assert_allclose(lse_c, lse, rtol=1e-5, atol=1e-5)
+
+
+def test_cfg1_chain_fixture(golden_dir):
+    """Standalone op chain of the headline configuration: 8 x (5 + 37x37) tokens, 3x3 windows, 50 % per frame."""
+    z = _load(golden_dir, "cfg1_chain.npz")
+    tokens, conf = gi.cfg1_inputs()
+    mask = orc.select_windows(conf, 8, 1, 37, 37, 3, 3, 0.5, "pairwise-rank", "frame", "f32")
+    want_mask = np.unpackbits(z["mask"])[: 8 * 144].reshape(8, 144).astype(bool)
+    np.testing.assert_array_equal(mask, want_mask)
+    assert (mask.sum(axis=1) == 72).all()
+    np.testing.assert_array_equal(clib.select_windows(conf, 8, 1, 37, 37, 3, 3, 0.5, "pairwise-rank", "frame"), want_mask)
+    out, off, rev, w = clib.token_merge_2d(tokens, 5, 3, 3, 37, 37, mask)
+    assert out.shape == (8 * 798, 1024)
+    np.testing.assert_array_equal(off, z["offset"])
+    np.testing.assert_array_equal(rev, z["rev"].astype(np.int64))
+    np.testing.assert_array_equal(w, z["weight"].astype(np.float32))
+    gi.check_rows(out, z, "out_", **FEATURE_TOL)
+    gi.check_rows(clib.token_split(out, rev), z, "res_", **FEATURE_TOL)
+    # numpy twin on a channel slice (keeps the CPU suite fast)
+    o2 = orc.token_merge_2d_ragged(tokens[:, :, :64], 5, 3, 3, 37, 37, mask)
+    np.testing.assert_array_equal(o2[0], out[:, :64])
+    np.testing.assert_array_equal(o2[2], rev)
