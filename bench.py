@@ -1,0 +1,395 @@
+#!/usr/bin/env python3
+"""Benchmark of the Co-Me hot path on B200: ms/scene of the merge -> biased attention -> unmerge chain at the
+VGGT-1B shapes (8 frames of 518x518: 1374 tokens x 1024 channels per frame, 16 heads x 64, 24 frame + 24 global
+attention layers, 3x3 windows at a 50 % merge ratio), plus merge/unmerge GB/s and biased-attention TFLOP/s.
+
+    python bench.py --gpus N --steps K --warmup W            # this library (one scene per rank and step)
+    python bench.py --impl reference ...                     # the CPU restatement of the reference path (rank 0)
+
+Prints ONE JSON line (rank 0).  Inputs are synthetic (seeded); see DESIGN.md for what each field means.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+FRAMES, GRID, WIN, START, CH, HEADS, HDIM = 8, 37, 3, 5, 1024, 16, 64
+N_TOK = START + GRID * GRID  # 1374
+N_WIN = (GRID // WIN) ** 2   # 144
+LAYERS = ["frame", "global"] * 24
+METRIC = "come_vggt_hot_path_ms_per_scene_8f"
+UNIT = "ms/scene"
+
+
+def workload_name(frames=FRAMES):
+    return (f"VGGT-1B-shape Co-Me op chain, {frames} frames x 518x518 (1374 tok x 1024 ch), 48 attention layers "
+            f"(24 frame + 24 global) each = merge + biased varlen attention (16 heads x 64) + unmerge, 3x3 windows at "
+            f"50 % per frame; projections/MLP GEMMs excluded")
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return dict(hbm_gbs=float(p["hbm_gbs"]), tflops=float(p["bf16_tflops"]),
+                    tflops_sustained=float(p.get("bf16_tflops_sustained", p["bf16_tflops"])), source="measured")
+    return dict(hbm_gbs=6650.0, tflops=1590.0, tflops_sustained=1400.0, source="fallback")
+
+
+# ---- clocks sampler --------------------------------------------------------------------------------------
+class ClockSampler:
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.idx = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.idx)], stdout=subprocess.PIPE, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons, power = [], [], set(), []
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+                power.append(float(f[3]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ---- CPU restatement of the reference path (oracle) ---------------------------------------------------------
+def cpu_chain_sample(frames=FRAMES, attn_rows=1024):
+    """One bounded sample of the scene chain on the host cores with the C oracle (all OpenMP threads).
+
+    Times a full merge and a full unmerge (float32, the dtype of the reference's CPU path), and attention on a
+    slice: frame layers on 1 head x 1 frame x all rows, the global layer on 1 head x `attn_rows` query rows against
+    all keys.  The slices are scaled to all heads / frames / rows and summed over the 48 layers."""
+    from oracle import clib
+    rng = np.random.default_rng(0)
+    tokens = rng.standard_normal((frames, N_TOK, CH), dtype=np.float32)
+    conf = rng.random((1, frames * GRID * GRID), dtype=np.float32)
+    t0 = time.perf_counter()
+    mask = clib.select_windows(conf, 1, frames, GRID, GRID, WIN, WIN, 0.5, "pairwise-rank", "frame")
+    t_sel = time.perf_counter() - t0
+    t0 = time.perf_counter()
+    out, off, rev, w = clib.token_merge_2d(tokens, START, WIN, WIN, GRID, GRID, mask)
+    t_merge = time.perf_counter() - t0
+    t0 = time.perf_counter()
+    clib.token_split(out, rev)
+    t_unmerge = time.perf_counter() - t0
+    P = out.shape[0]
+    L0 = int(off[1] - off[0])
+    bias = np.log(w)
+    qkv1 = rng.standard_normal((P, 3, 1, HDIM), dtype=np.float32)
+    t0 = time.perf_counter()
+    clib.attention_bias(qkv1[:L0], bias[:L0], np.array([0, L0], np.int32), HDIM ** -0.5)
+    t_frame = (time.perf_counter() - t0) * HEADS * frames
+    t0 = time.perf_counter()
+    clib.attention_bias(qkv1, bias, np.array([0, P], np.int32), HDIM ** -0.5, 0, attn_rows)
+    t_global = (time.perf_counter() - t0) * HEADS * (P / attn_rows)
+    per_scene = t_sel + 24 * (t_merge + t_frame + t_unmerge) + 24 * (t_merge + t_global + t_unmerge)
+    detail = dict(select_ms=t_sel * 1e3, merge_ms=t_merge * 1e3, unmerge_ms=t_unmerge * 1e3,
+                  attn_frame_layer_ms=t_frame * 1e3, attn_global_layer_ms=t_global * 1e3)
+    sample = (f"1 scene-sample: full select+merge+unmerge (fp32, {frames}x{N_TOK}x{CH}); attention on 1 head: one frame "
+              f"segment (all rows) and the global segment ({attn_rows} of {P} query rows), scaled to {HEADS} heads / "
+              f"{frames} frames / all rows and x24 layers each")
+    return per_scene * 1e3, clib.num_threads(), sample, detail
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    vals = []
+    detail = {}
+    for i in range(args.warmup + args.steps):
+        v, cores, sample, detail = cpu_chain_sample(attn_rows=256)
+        if i >= args.warmup:
+            vals.append(v)
+    val = statistics.median(vals)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": val, "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic (seeded)", "config": {"workload": workload_name()},
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample, "detail": detail},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# ---- GPU arm ---------------------------------------------------------------------------------------------------
+def run_gpu(args):
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    from come_b200 import _lib
+    from come_b200.chain import CoMeOpChain
+    from come_b200.flash_attn import flash_attn_varlen_qkvpacked_func_w_perkey_bias as attn_fn
+
+    pk = peaks()
+    chain = CoMeOpChain(FRAMES, START, GRID, GRID, WIN, WIN, 0.5, HEADS, HDIM, LAYERS, scope="frame")
+    g = torch.Generator(device="cpu").manual_seed(1234 + rank)
+    x_host = torch.randn((FRAMES, N_TOK, CH), generator=g).bfloat16().pin_memory()
+    conf_host = torch.rand((1, FRAMES * GRID * GRID), generator=g).bfloat16().pin_memory()
+    qkv_host = torch.randn((FRAMES * N_TOK, 3, HEADS, HDIM), generator=g).bfloat16().pin_memory()
+    out_host = torch.empty((FRAMES, N_TOK, CH), dtype=torch.bfloat16).pin_memory()
+    x, conf, qkv_buf = x_host.to(dev), conf_host.to(dev), qkv_host.to(dev)
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)  # > 126 MB L2
+
+    ev = lambda: torch.cuda.Event(enable_timing=True)  # noqa: E731
+
+    def step_resident(timers=None):
+        """One scene with inputs resident in HBM.  With `timers`, every kernel family is bracketed by events."""
+        plan = chain.build_plan(conf)
+        qkv = qkv_buf[: plan.total]
+        bias = plan.perkey_bias(torch.bfloat16)
+        out = None
+        for kind in LAYERS:
+            cu, ml = (plan.cu_seqlens(FRAMES), plan.total) if kind == "global" else (plan.cu_seqlens(1), plan.max_seqlen)
+            if timers is not None:
+                e = [ev() for _ in range(4)]
+                e[0].record()
+            merged = plan.merge(x)
+            if timers is not None:
+                e[1].record()
+            a = attn_fn(qkv, cu, ml, perkey_bias=bias, softmax_scale=chain.scale)
+            if timers is not None:
+                e[2].record()
+            out = plan.split(a.reshape(plan.total, CH))
+            if timers is not None:
+                e[3].record()
+                timers.append((kind, e))
+            del merged
+        return plan, out
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step_resident()
+    barrier()
+    if _lib.device_status(clear=False) != 0:
+        raise RuntimeError("attention kernel raised the device status word during warm-up")
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    # ---- timed region 1: resident inputs, per-step device time ---------------------------------------------------
+    step_ev, timers = [], []
+    barrier()
+    plan = None
+    for _ in range(args.steps):
+        flush.fill_(1)  # L2 flush between timed iterations (outside the per-step events)
+        s, e = ev(), ev()
+        s.record()
+        plan, _ = step_resident(timers)
+        e.record()
+        step_ev.append((s, e))
+    barrier()
+    step_ms = [s.elapsed_time(e) for s, e in step_ev]
+    total_ms = sum(step_ms)
+    # ---- timed region 2: end to end through the public API with host buffers --------------------------------------
+    h2d = x_host.numel() * 2 + conf_host.numel() * 2 + qkv_host.numel() * 2
+    d2h = out_host.numel() * 2
+    for _ in range(2):
+        chain.forward_scene(x_host.to(dev, non_blocking=True), conf_host.to(dev, non_blocking=True), lambda P: qkv_buf[:P])
+    barrier()
+    s, e = ev(), ev()
+    s.record()
+    for _ in range(args.steps):
+        xd = x_host.to(dev, non_blocking=True)
+        cd = conf_host.to(dev, non_blocking=True)
+        qd = qkv_host.to(dev, non_blocking=True)
+        res = chain.forward_scene(xd, cd, lambda P, qd=qd: qd[:P])
+        out_host.copy_(res.reshape(FRAMES, N_TOK, CH), non_blocking=True)
+    e.record()
+    barrier()
+    e2e_ms = s.elapsed_time(e)
+    clocks = sampler.stop() if rank == 0 else None
+    if _lib.device_status(clear=False) != 0:
+        raise RuntimeError("attention kernel raised the device status word during the timed region")
+
+    t = torch.tensor([total_ms, e2e_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms, e2e_ms = t.tolist()
+    scenes = args.steps * world
+    value = total_ms / scenes
+    e2e_value = e2e_ms / scenes
+
+    if rank == 0:
+        P = plan.total
+        seg = (plan.offset[1:] - plan.offset[:-1]).tolist()
+        flops_frame = sum(4.0 * L * L * HDIM * HEADS for L in seg)
+        flops_global = 4.0 * P * P * HDIM * HEADS
+        t_attn = {"frame": 0.0, "global": 0.0}
+        t_merge = t_unmerge = 0.0
+        for kind, e4 in timers:
+            t_merge += e4[0].elapsed_time(e4[1])
+            t_attn[kind] += e4[1].elapsed_time(e4[2])
+            t_unmerge += e4[2].elapsed_time(e4[3])
+        n_layers = len(timers)
+        n_f = sum(1 for k, _ in timers if k == "frame")
+        n_g = n_layers - n_f
+        attn_flops = n_f * flops_frame + n_g * flops_global
+        attn_ms = t_attn["frame"] + t_attn["global"]
+        achieved = attn_flops / (attn_ms * 1e-3) / 1e12
+        merge_bytes = FRAMES * N_TOK * CH * 2 + P * CH * 2 + FRAMES * N_WIN + (FRAMES + 1) * 4
+        unmerge_bytes = P * CH * 2 + FRAMES * N_TOK * 8 + FRAMES * N_TOK * CH * 2
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": total_ms / args.steps, "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic (seeded)",
+            "config": {"workload": workload_name(), "merged_tokens": P, "l2": "flushed between timed steps (256 MB write)",
+                       "parallelism": f"one independent scene per GPU x {world}"},
+            "roofline": {"kernel": "attn_fwd_sm100_kernel (48 launches/scene: 24 frame + 24 global)", "bound": "tensor",
+                         "achieved": achieved, "peak": pk["tflops"], "unit": "TFLOP/s", "frac": achieved / pk["tflops"],
+                         "peak_source": pk["source"] + " burst cuBLAS bf16", "traffic": None,
+                         "frame_tflops": n_f * flops_frame / (t_attn["frame"] * 1e-3) / 1e12,
+                         "global_tflops": n_g * flops_global / (t_attn["global"] * 1e-3) / 1e12,
+                         "avg_launch_ms": attn_ms / n_layers},
+            "roofline_merge": {"bound": "hbm", "achieved": merge_bytes * n_layers / (t_merge * 1e-3) / 1e9, "peak": pk["hbm_gbs"],
+                               "unit": "GB/s", "note": "bf16, 35.6 MB per launch: partly L2-resident inside the chain"},
+            "roofline_unmerge": {"bound": "hbm", "achieved": unmerge_bytes * n_layers / (t_unmerge * 1e-3) / 1e9,
+                                 "peak": pk["hbm_gbs"], "unit": "GB/s"},
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "gpu_launches": chain.launches_per_scene * args.steps,
+            "clocks": clocks,
+        }
+        if world == 1 and not args.no_micro:
+            line["kernels"] = micro(torch, dev, pk)
+        if world == 1 and not args.no_cpu:
+            v, cores, sample, detail = cpu_chain_sample()
+            line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample,
+                                    "detail": detail}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def micro(torch, dev, pk):
+    """Kernel-level numbers on inputs larger than L2: 100-frame fp32 merge / unmerge (GB/s) and the 64-segment
+    ragged biased-attention sweep (TFLOP/s)."""
+    from come_b200 import _lib
+    from come_b200.flash_attn import flash_attn_varlen_qkvpacked_func_w_perkey_bias as attn_fn
+    from come_b200.token_merger import MergePlan
+    res = {}
+    ev = lambda: torch.cuda.Event(enable_timing=True)  # noqa: E731
+
+    def timeit(fn, iters, warm=3):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        s, e = ev(), ev()
+        s.record()
+        for _ in range(iters):
+            fn()
+        e.record()
+        torch.cuda.synchronize()
+        return s.elapsed_time(e) / iters
+
+    frames = 100
+    g = torch.Generator(device=dev).manual_seed(0)
+    x = torch.randn((frames, N_TOK, CH), device=dev, generator=g)
+    mask = torch.rand((frames, N_WIN), device=dev, generator=g) < 0.5
+    plan = MergePlan(mask, _lib.Layout.two_d(START, GRID, GRID, WIN, WIN))
+    P = plan.total
+    merged = plan.merge(x)
+    mb = frames * N_TOK * CH * 4 + P * CH * 4 + frames * N_WIN + (frames + 1) * 4
+    ub = P * CH * 4 + frames * N_TOK * 8 + frames * N_TOK * CH * 4
+    tm = timeit(lambda: plan.merge(x), 20)
+    tu = timeit(lambda: plan.split(merged), 20)
+    tp = timeit(lambda: MergePlan(mask, plan.layout), 10)
+    res["merge_fp32_100f"] = {"GB/s": mb / tm / 1e6, "ms": tm, "bytes": mb, "frac_of_hbm_peak": mb / tm / 1e6 / pk["hbm_gbs"]}
+    res["unmerge_fp32_100f"] = {"GB/s": ub / tu / 1e6, "ms": tu, "bytes": ub, "frac_of_hbm_peak": ub / tu / 1e6 / pk["hbm_gbs"]}
+    res["plan_100f"] = {"ms": tp, "note": "select excluded; 2 kernels + one host read"}
+    del x, merged
+
+    rng = np.random.default_rng(0)
+    lens = [1374 - 8 * int(k) for k in rng.integers(0, 73, size=64)]
+    Pt = sum(lens)
+    cu = torch.tensor(np.concatenate([[0], np.cumsum(lens)]), dtype=torch.int32, device=dev)
+    qkv = torch.randn((Pt, 3, HEADS, HDIM), device=dev, generator=g).bfloat16()
+    cnt = torch.where(torch.rand(Pt, device=dev, generator=g) < 0.1, 9.0, 1.0)
+    bias = cnt.log().bfloat16()
+    flops = sum(4.0 * L * L * HDIM * HEADS for L in lens)
+    ta = timeit(lambda: attn_fn(qkv, cu, max(lens), perkey_bias=bias, softmax_scale=HDIM ** -0.5), 10)
+    res["attn_bias_sweep_64seg"] = {"TFLOP/s": flops / ta / 1e9, "ms": ta, "gflop": flops / 1e9,
+                                    "frac_of_bf16_peak": flops / ta / 1e9 / pk["tflops"]}
+    if _lib.device_status(clear=False) != 0:
+        raise RuntimeError("attention kernel raised the device status word in the kernel sweep")
+    return res
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="come_b200", choices=["come_b200", "reference"])
+    ap.add_argument("--no-micro", action="store_true", help="skip the kernel-level sweep")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        args.warmup = max(args.warmup, 3)
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

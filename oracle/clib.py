@@ -80,8 +80,9 @@ def select_windows(conf, B, S, H, W, gh, gw, threshold, mode="pairwise-rank", sc
     return mask.astype(bool)
 
 
-def attention_bias(qkv, bias, cu_seqlens, scale):
-    """qkv [P, 3, H, D] float32 packed; returns (out [P,H,D], lse [H,P])."""
+def attention_bias(qkv, bias, cu_seqlens, scale, q_lo=0, q_hi=-1):
+    """qkv [P, 3, H, D] float32 packed; returns (out [P,H,D], lse [H,P]).  ``q_lo/q_hi`` restrict the query rows
+    of every segment (bounded benchmark samples); rows outside stay uninitialised."""
     qkv = np.ascontiguousarray(qkv, np.float32)
     P, _, Hh, D = qkv.shape
     cu = np.ascontiguousarray(cu_seqlens, np.int32)
@@ -92,5 +93,5 @@ def attention_bias(qkv, bias, cu_seqlens, scale):
     hd = Hh * D * 4
     lib().orc_attention(C.c_void_p(base), C.c_void_p(base + hd), C.c_void_p(base + 2 * hd), C.c_int64(3 * Hh * D),
                         _p(b), _p(cu), C.c_int64(cu.size - 1), C.c_int64(P), C.c_int64(Hh), C.c_int64(D),
-                        C.c_float(scale), _p(out), _p(lse))
+                        C.c_float(scale), _p(out), _p(lse), C.c_int64(q_lo), C.c_int64(q_hi))
     return out, lse

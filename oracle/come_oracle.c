@@ -156,21 +156,21 @@ int orc_select(const float *conf, int64_t B, int64_t S, int64_t H, int64_t W, in
 
 /* ---- biased attention: test/auto_test/test_flex_attention_bias.py:26-36 ----------------------------------
  * out = softmax(q k^T * scale + bias[None, :]) v per packed segment and head, float32 throughout.
- * q, k, v: element (row, h, d) at ptr[row * row_stride + h * D + d]; out [P, H, D]; lse [H, P]; bias may be NULL. */
+ * q, k, v: element (row, h, d) at ptr[row * row_stride + h * D + d]; out [P, H, D]; lse [H, P]; bias may be NULL.
+ * Only query rows [q_lo, q_hi) of every segment are computed (q_hi < 0: to the segment end); the benchmark's
+ * bounded CPU sample uses that, the tests always pass the whole range. */
 void orc_attention(const float *q, const float *k, const float *v, int64_t row_stride, const float *bias,
                    const int32_t *cu, int64_t nseg, int64_t P, int64_t Hh, int64_t D, float scale, float *out,
-                   float *lse) {
-    int64_t maxlen = 0;
+                   float *lse, int64_t q_lo, int64_t q_hi) {
     for (int64_t s = 0; s < nseg; ++s)
-        if (cu[s + 1] - cu[s] > maxlen) maxlen = cu[s + 1] - cu[s];
+        for (int64_t h = 0; h < Hh; ++h) {
+            const int64_t a = cu[s], e = cu[s + 1];
+            const int64_t i_lo = a + q_lo, i_hi = (q_hi >= 0 && a + q_hi < e) ? a + q_hi : e;
 #pragma omp parallel
-    {
-        float *logit = (float *)malloc((size_t)(maxlen > 0 ? maxlen : 1) * sizeof(float));
-#pragma omp for collapse(2) schedule(dynamic, 1)
-        for (int64_t s = 0; s < nseg; ++s)
-            for (int64_t h = 0; h < Hh; ++h) {
-                int64_t a = cu[s], e = cu[s + 1];
-                for (int64_t i = a; i < e; ++i) {
+            {
+                float *logit = (float *)malloc((size_t)(e > a ? e - a : 1) * sizeof(float));
+#pragma omp for schedule(dynamic, 8)
+                for (int64_t i = i_lo; i < i_hi; ++i) {
                     const float *qi = q + i * row_stride + h * D;
                     float mx = -INFINITY;
                     for (int64_t j = a; j < e; ++j) {
@@ -193,9 +193,9 @@ void orc_attention(const float *q, const float *k, const float *v, int64_t row_s
                     for (int64_t d = 0; d < D; ++d) o[d] /= l;
                     lse[h * P + i] = mx + logf(l);
                 }
+                free(logit);
             }
-        free(logit);
-    }
+        }
 }
 
 int orc_num_threads(void) {

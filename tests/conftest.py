@@ -7,8 +7,9 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 GOLDEN = os.path.join(ROOT, "tests", "golden")
-if GOLDEN not in sys.path:
-    sys.path.insert(0, GOLDEN)
+for extra in (GOLDEN, os.path.join(ROOT, "tests")):
+    if extra not in sys.path:
+        sys.path.insert(0, extra)
 
 
 def pytest_configure(config):

@@ -1,0 +1,210 @@
+"""Biased variable-length attention parity on the GPU, through the C ABI.
+
+Mirrors test/auto_test/test_flex_attention_bias.py:206-331 of the reference (segment-length sets, head shapes,
+fp16 + bf16, zero-bias == plain kernel, bias has an effect) with the reference's tolerance (1e-2 abs/rel), plus
+the 2e-2 absolute bar against the fp32 oracle on the post-merge lengths of the benchmark configurations.
+Every case runs on both device kernels where both apply: the tcgen05 tensor-core kernel (head_dim 64) and the
+CUDA-core kernel (any head_dim).
+"""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import golden_inputs as gi
+import reference_cases as rc
+from gpu_util import TORCH_DTYPE, to_dev, to_np
+from oracle import clib
+
+pytestmark = pytest.mark.gpu
+
+ALL_CASES = list(rc.ATTENTION_CASES) + list(gi.EXTRA_ATTENTION_CASES)
+
+
+@pytest.fixture
+def backend():
+    from come_b200 import flash_attn_fwd_cuda as fa
+
+    def setter(b):
+        fa.set_backend(b)
+
+    yield setter
+    fa.set_backend(fa.BACKEND_AUTO)
+
+
+def _check_status():
+    from come_b200 import _lib
+    assert _lib.device_status(clear=True) == 0, "a tensor-core kernel wait ran out (device status word raised)"
+
+
+def _backends_for(D):
+    return ["cuda-core", "tcgen05"] if D == 64 else ["cuda-core"]
+
+
+@pytest.mark.parametrize("idx", range(len(ALL_CASES)))
+@pytest.mark.parametrize("which", ["cuda-core", "tcgen05"])
+def test_bias_matches_reference_oracle(golden_dir, backend, idx, which):
+    from come_b200 import flash_attn as api, flash_attn_fwd_cuda as fa
+    seq_lens, H, D, kind = ALL_CASES[idx]
+    if which not in _backends_for(D):
+        pytest.skip("tensor-core kernel serves head_dim 64 only")
+    backend(fa.BACKEND_TCGEN05 if which == "tcgen05" else fa.BACKEND_CUDA_CORE)
+    z = np.load(os.path.join(golden_dir, "attention.npz"))
+    qkv, bias, cu = gi.attention_inputs(idx, ALL_CASES[idx])
+    want = z[f"a{idx}_out"]
+    out = api.flash_attn_varlen_qkvpacked_func_w_perkey_bias(
+        to_dev(qkv, kind), torch.from_numpy(cu).cuda(), max(seq_lens), perkey_bias=to_dev(bias, kind),
+        softmax_scale=1.0 / (D ** 0.5))
+    assert isinstance(out, torch.Tensor) and tuple(out.shape) == (sum(seq_lens), H, D)
+    assert out.dtype == TORCH_DTYPE[kind]
+    np.testing.assert_allclose(to_np(out), want, atol=rc.ATTENTION_ATOL, rtol=rc.ATTENTION_RTOL)
+    _check_status()
+
+
+@pytest.mark.parametrize("which", ["cuda-core", "tcgen05"])
+@pytest.mark.parametrize("kind", ["f16", "bf16"])
+def test_zero_bias_matches_plain_and_lse(backend, which, kind):
+    from come_b200 import flash_attn as api, flash_attn_fwd_cuda as fa
+    backend(fa.BACKEND_TCGEN05 if which == "tcgen05" else fa.BACKEND_CUDA_CORE)
+    seq_lens, H, D = [64, 64, 200], 4, 64
+    P = sum(seq_lens)
+    rng = np.random.default_rng(21)
+    qkv = gi.round_kind(rng.standard_normal((P, 3, H, D), dtype=np.float32), kind)
+    cu = torch.tensor([0, 64, 128, 328], dtype=torch.int32, device="cuda")
+    scale = 1.0 / (D ** 0.5)
+    q_dev = to_dev(qkv, kind)
+    plain, lse, _ = api.flash_attn_varlen_qkvpacked_func(q_dev, cu, 200, softmax_scale=scale, return_attn_probs=True)
+    biased = api.flash_attn_varlen_qkvpacked_func_w_perkey_bias(q_dev, cu, 200, perkey_bias=torch.zeros(P, device="cuda", dtype=q_dev.dtype), softmax_scale=scale)
+    torch.testing.assert_close(plain, biased, atol=1e-4, rtol=1e-4)
+    want, want_lse = clib.attention_bias(qkv, None, cu.cpu().numpy(), scale)
+    np.testing.assert_allclose(to_np(plain), want, atol=1e-2, rtol=1e-2)
+    assert tuple(lse.shape) == (H, P) and lse.dtype == torch.float32
+    np.testing.assert_allclose(to_np(lse), want_lse, atol=2e-3, rtol=1e-3)
+    _check_status()
+
+
+@pytest.mark.parametrize("which", ["cuda-core", "tcgen05"])
+def test_bias_has_effect(backend, which):
+    from come_b200 import flash_attn as api, flash_attn_fwd_cuda as fa
+    backend(fa.BACKEND_TCGEN05 if which == "tcgen05" else fa.BACKEND_CUDA_CORE)
+    P, H, D = 128, 2, 64
+    g = torch.Generator(device="cpu").manual_seed(42)
+    qkv = torch.randn(P, 3, H, D, generator=g).half().cuda()
+    cu = torch.tensor([0, 128], device="cuda", dtype=torch.int32)
+    b0 = torch.zeros(P, device="cuda", dtype=torch.float16)
+    b1 = torch.randn(P, generator=g).half().cuda()
+    o0 = api.flash_attn_varlen_qkvpacked_func_w_perkey_bias(qkv, cu, 128, perkey_bias=b0, softmax_scale=D ** -0.5)
+    o1 = api.flash_attn_varlen_qkvpacked_func_w_perkey_bias(qkv, cu, 128, perkey_bias=b1, softmax_scale=D ** -0.5)
+    assert not torch.allclose(o0, o1, atol=1e-4)
+    _check_status()
+
+
+def _merge_like_inputs(rng, lengths, H, D, kind):
+    """Segments laid out like merged frames: 78 never-merged tokens, then windows; merged windows count 9."""
+    P = int(sum(lengths))
+    qkv = gi.round_kind(rng.standard_normal((P, 3, H, D), dtype=np.float32), kind)
+    count = np.ones(P, np.float32)
+    pos = 0
+    for L in lengths:
+        k = (1374 - L) // 8
+        merged = np.zeros(144, bool)
+        merged[rng.permutation(144)[:k]] = True
+        row = pos + 78
+        for m in range(144):
+            if merged[m]:
+                count[row] = 9.0
+                row += 1
+            else:
+                row += 9
+        assert row == pos + L
+        pos += L
+    cu = np.zeros(len(lengths) + 1, np.int32)
+    cu[1:] = np.cumsum(lengths)
+    return qkv, count, cu
+
+
+@pytest.mark.parametrize("which", ["cuda-core", "tcgen05"])
+def test_post_merge_lengths_bf16_vs_fp32_oracle(backend, which):
+    """Ragged post-merge frame lengths 1374 - 8k (kernel-sweep configuration, reduced to 6 segments x 4 heads so
+    that the CPU oracle finishes in seconds); bias = log(count) with counts in {1, 9}; bar 2e-2 absolute."""
+    from come_b200 import flash_attn as api, flash_attn_fwd_cuda as fa
+    backend(fa.BACKEND_TCGEN05 if which == "tcgen05" else fa.BACKEND_CUDA_CORE)
+    rng = np.random.default_rng(0)
+    lengths = [1374 - 8 * int(k) for k in rng.integers(0, 73, size=6)]
+    H, D = 4, 64
+    qkv, count, cu = _merge_like_inputs(rng, lengths, H, D, "bf16")
+    bias32 = np.log(count)
+    bias = to_dev(bias32, "bf16")
+    out = api.flash_attn_varlen_qkvpacked_func_w_perkey_bias(to_dev(qkv, "bf16"), torch.from_numpy(cu).cuda(), max(lengths),
+                                                             perkey_bias=bias, softmax_scale=D ** -0.5)
+    want, _ = clib.attention_bias(qkv, bias32, cu, D ** -0.5)  # fp32 log(count), as the oracle is specified
+    assert np.abs(to_np(out) - want).max() <= 2e-2
+    _check_status()
+
+
+def test_global_segment_and_strided_views(backend):
+    """One long segment (all frames of a scene concatenated) and q/k/v given as strided views of one buffer."""
+    from come_b200 import flash_attn_fwd_cuda as fa
+    backend(fa.BACKEND_TCGEN05)
+    rng = np.random.default_rng(3)
+    P, H, D = 3 * 798 + 17, 2, 64
+    qkv = gi.round_kind(rng.standard_normal((P, 3, H, D), dtype=np.float32), "bf16")
+    count = np.where(rng.random(P) < 0.1, 9.0, 1.0).astype(np.float32)
+    bias = gi.round_kind(np.log(count), "bf16")
+    cu = np.array([0, P], np.int32)
+    t = to_dev(qkv, "bf16")
+    res = fa.varlen_fwd_w_perkey_bias(t[:, 0], t[:, 1], t[:, 2], None, torch.from_numpy(cu).cuda(), torch.from_numpy(cu).cuda(),
+                                      None, None, None, None, to_dev(bias, "bf16"), P, P, 0.0, D ** -0.5, False, False, -1, -1,
+                                      0.0, False, None)
+    out, lse, p, rng_state = res
+    want, want_lse = clib.attention_bias(qkv, bias, cu, D ** -0.5)
+    assert np.abs(to_np(out) - want).max() <= 2e-2
+    np.testing.assert_allclose(to_np(lse), want_lse, atol=2e-3, rtol=1e-3)
+    assert p.numel() == 0 and tuple(rng_state.shape) == (2,) and rng_state.dtype == torch.int64
+    _check_status()
+
+
+def test_large_magnitude_scores_rescale_path(backend):
+    """Scores that grow along the keys force the running-max rescale of the output accumulator."""
+    from come_b200 import flash_attn as api, flash_attn_fwd_cuda as fa
+    backend(fa.BACKEND_TCGEN05)
+    rng = np.random.default_rng(4)
+    P, H, D = 700, 2, 64
+    qkv = rng.standard_normal((P, 3, H, D), dtype=np.float32)
+    qkv[:, 1] *= np.linspace(0.2, 6.0, P, dtype=np.float32)[:, None, None]  # later keys score much higher / lower
+    qkv = gi.round_kind(qkv, "bf16")
+    cu = np.array([0, 300, 700], np.int32)
+    out = api.flash_attn_varlen_qkvpacked_func(to_dev(qkv, "bf16"), torch.from_numpy(cu).cuda(), 400, softmax_scale=D ** -0.5)
+    want, _ = clib.attention_bias(qkv, None, cu, D ** -0.5)
+    assert np.abs(to_np(out) - want).max() <= 2e-2
+    _check_status()
+
+
+def test_rejects_what_it_does_not_implement():
+    from come_b200 import flash_attn as api
+    qkv = torch.zeros((16, 3, 2, 64), dtype=torch.float16, device="cuda")
+    cu = torch.tensor([0, 16], dtype=torch.int32, device="cuda")
+    with pytest.raises(NotImplementedError):
+        api.flash_attn_varlen_qkvpacked_func(qkv, cu, 16, dropout_p=0.1)
+    with pytest.raises(NotImplementedError):
+        api.flash_attn_varlen_qkvpacked_func(qkv, cu, 16, causal=True)
+    with pytest.raises(NotImplementedError):
+        api.flash_attn_varlen_qkvpacked_func(qkv, cu, 16, window_size=(4, 4))
+    with pytest.raises(NotImplementedError):
+        api.flash_attn_varlen_qkvpacked_func(qkv, cu, 16, softcap=1.0)
+    with pytest.raises(RuntimeError, match="fp16 and bf16"):
+        api.flash_attn_varlen_qkvpacked_func(qkv.float(), cu, 16)
+    with pytest.raises(RuntimeError, match="perkey_bias dtype"):
+        api.flash_attn_varlen_qkvpacked_func_w_perkey_bias(qkv, cu, 16, perkey_bias=torch.zeros(16, device="cuda"))
+    with pytest.raises(RuntimeError, match="int32"):
+        api.flash_attn_varlen_qkvpacked_func(qkv, cu.long(), 16)
+    x = torch.zeros((16, 3, 2, 64), dtype=torch.float16, device="cuda", requires_grad=True)
+    with pytest.raises(RuntimeError, match="backward is not supported"):
+        api.flash_attn_varlen_qkvpacked_func(x, cu, 16).sum().backward()
+
+
+def test_infer_max_seqlen():
+    from come_b200.flash_attn import infer_flash_attn_varlen_max_seqlen
+    cu = torch.tensor([0, 5, 12, 14], dtype=torch.int32, device="cuda")
+    assert infer_flash_attn_varlen_max_seqlen(cu) == 7
