@@ -375,8 +375,68 @@ def micro(torch, dev, pk):
     return res
 
 
+def run_only(args):
+    """One kernel family on one size, a few launches: the command the ncu captures under profiles/ were made with."""
+    import torch
+    from come_b200 import _lib
+    from come_b200.flash_attn import flash_attn_varlen_qkvpacked_func_w_perkey_bias as attn_fn
+    from come_b200.token_merger import MergePlan
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    g = torch.Generator(device=dev).manual_seed(0)
+    ev = lambda: torch.cuda.Event(enable_timing=True)  # noqa: E731
+    out = {"only": args.only}
+    if args.only in ("merge", "unmerge"):
+        dt = {"f32": torch.float32, "bf16": torch.bfloat16}[args.dtype]
+        x = torch.randn((args.frames, N_TOK, CH), device=dev, generator=g).to(dt)
+        mask = torch.rand((args.frames, N_WIN), device=dev, generator=g) < 0.5
+        plan = MergePlan(mask, _lib.Layout.two_d(START, GRID, GRID, WIN, WIN))
+        merged = plan.merge(x)
+        es = x.element_size()
+        if args.only == "merge":
+            fn, nbytes = (lambda: plan.merge(x)), args.frames * N_TOK * CH * es + plan.total * CH * es + args.frames * N_WIN + (args.frames + 1) * 4
+        else:
+            fn, nbytes = (lambda: plan.split(merged)), plan.total * CH * es + args.frames * N_TOK * 8 + args.frames * N_TOK * CH * es
+        out.update(frames=args.frames, dtype=args.dtype, bytes=nbytes)
+    else:
+        if args.segments == 1:
+            lens = [args.tokens]
+        else:
+            rng = np.random.default_rng(0)
+            lens = [1374 - 8 * int(k) for k in rng.integers(0, 73, size=args.segments)]
+        Pt = sum(lens)
+        cu = torch.tensor(np.concatenate([[0], np.cumsum(lens)]), dtype=torch.int32, device=dev)
+        qkv = torch.randn((Pt, 3, HEADS, HDIM), device=dev, generator=g).bfloat16()
+        bias = torch.where(torch.rand(Pt, device=dev, generator=g) < 0.1, 9.0, 1.0).log().bfloat16()
+        fn = lambda: attn_fn(qkv, cu, max(lens), perkey_bias=bias, softmax_scale=HDIM ** -0.5)  # noqa: E731
+        out.update(segments=len(lens), tokens=Pt, flops=sum(4.0 * L * L * HDIM * HEADS for L in lens))
+    for _ in range(2):
+        fn()
+    torch.cuda.synchronize()
+    s, e = ev(), ev()
+    s.record()
+    for _ in range(args.iters):
+        fn()
+    e.record()
+    torch.cuda.synchronize()
+    ms = s.elapsed_time(e) / args.iters
+    out["ms"] = ms
+    if "bytes" in out:
+        out["GB/s"] = out["bytes"] / ms / 1e6
+    else:
+        out["TFLOP/s"] = out["flops"] / ms / 1e9
+    assert _lib.device_status(clear=False) == 0
+    print(json.dumps(out))
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--only", choices=["attn", "merge", "unmerge"], help="run one kernel family on one size and exit")
+    ap.add_argument("--frames", type=int, default=100, help="--only merge/unmerge: frames")
+    ap.add_argument("--dtype", default="f32", choices=["f32", "bf16"], help="--only merge/unmerge: element type")
+    ap.add_argument("--tokens", type=int, default=6384, help="--only attn with --segments 1: segment length")
+    ap.add_argument("--segments", type=int, default=1, help="--only attn: 1 = one segment, else ragged 1374-8k sweep")
+    ap.add_argument("--iters", type=int, default=3, help="--only: timed launches")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
@@ -384,7 +444,9 @@ def main():
     ap.add_argument("--no-micro", action="store_true", help="skip the kernel-level sweep")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.only:
+        run_only(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         args.warmup = max(args.warmup, 3)

@@ -200,7 +200,7 @@ plan_write_kernel(const uint8_t *__restrict__ mask, const int *__restrict__ fram
 // grid stride; inside a unit a thread owns 16-byte column vectors.  VEC = elements per vector (1 = scalar path
 // for rows that are not 16-byte multiples).
 constexpr int kMergeThreads = 256;
-constexpr int kMaxInFlight = 12;  // rows whose loads are issued before the first add / store
+constexpr int kMaxInFlight = 9;   // rows whose loads are issued before the first add / store
 
 template <typename T, int VEC> struct VecIO;
 template <> struct VecIO<float, 4> {
@@ -237,7 +237,7 @@ template <> __device__ __forceinline__ void st_stream<__half>(__half *p, const _
 template <> __device__ __forceinline__ void st_stream<__nv_bfloat16>(__nv_bfloat16 *p, const __nv_bfloat16 &v) { *p = v; }
 
 template <typename T, int VEC>
-__global__ void __launch_bounds__(kMergeThreads)
+__global__ void __launch_bounds__(kMergeThreads, 2)
 merge_kernel(const T *__restrict__ tokens, const uint8_t *__restrict__ mask, const int *__restrict__ group_prefix,
              const int *__restrict__ offsets, FrameLayout L, int frames, int64_t C, T *__restrict__ out) {
     using IO = VecIO<T, VEC>;
@@ -371,8 +371,9 @@ extern "C" int come_merge_plan(const uint8_t *mask_dev, int64_t frames, const co
     int rc = make_layout(layout, &L);
     if (rc != COME_OK) return rc;
     COME_REQUIRE(frames >= 0, "frames must be >= 0");
-    COME_REQUIRE(offsets_dev && rev_id_dev && weight_dev, "plan outputs must not be NULL");
-    COME_REQUIRE(L.M == 0 || (mask_dev && group_prefix_dev), "mask / group_prefix must not be NULL");
+    COME_REQUIRE(offsets_dev, "offsets must not be NULL");
+    COME_REQUIRE(frames == 0 || (int64_t)L.N == 0 || (rev_id_dev && weight_dev), "rev_id / weight must not be NULL");
+    COME_REQUIRE(frames == 0 || L.M == 0 || (mask_dev && group_prefix_dev), "mask / group_prefix must not be NULL");
     COME_REQUIRE(frames * (int64_t)L.N < (1ll << 31), "frames * tokens_per_frame must fit int32 row indices");
     COME_REQUIRE(workspace_dev && workspace_bytes >= come_merge_plan_workspace_bytes(frames),
                  "workspace too small: need %zu bytes", come_merge_plan_workspace_bytes(frames));
