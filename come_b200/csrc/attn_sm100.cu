@@ -2,14 +2,17 @@
 // accumulators, TMA-fed 128-byte-swizzled Q/K/V tiles, warp-specialised roles.
 //
 // One CTA owns up to two 128-row query tiles of one (segment, head) and walks the segment's keys 128 at a time.
-//   warps 0-3 / 4-7 : softmax group of query tile 0 / 1.  Thread r owns score row r (TMEM lane r): it reads the
-//                     128 scores of a step from TMEM, applies scale + per-key bias (log2 domain), keeps the
-//                     running max / sum, writes the probabilities back to TMEM as 16-bit pairs and rescales the
-//                     output accumulator only when the running max grew by more than 2^8.
-//   warp 8          : producer.  Stages the bias slice of every key tile in shared memory (-inf past the segment
-//                     end, which is what masks the ragged tail) and issues the TMA loads of Q, K and V.
-//   warp 9          : one thread issues every tcgen05.mma: S = Q K^T (both operands in shared memory) and
-//                     O += P V (P read from TMEM, V from shared memory, N-major).
+//   warps 0-3 / 4-7 : softmax group of query tile 0 / 1.  Thread r owns score row r (TMEM lane r).  Per key tile it
+//                     reads the scores 64 columns at a time, tracks the row max with 3-input max, computes
+//                     p = exp2(s * scale*log2e - m) with one FFMA + one MUFU per score, writes p back to TMEM as
+//                     16-bit pairs (the A operand of P V) and rescales the accumulator only when the running max
+//                     grew by more than 2^8 (exact: the final normalisation uses the same reference max).
+//   warp 8          : producer.  Issues the TMA loads of Q, K and V and stages, per key tile, a "bias slab": a
+//                     128-byte-swizzled tile whose first two columns hold bias/scale split into a high and a low
+//                     16-bit part (a large negative number past the segment end, which masks the ragged tail).
+//   warp 9          : one thread issues every tcgen05.mma.  S = Q K^T takes four K=16 steps over the head
+//                     dimension plus one K=16 step [1 1 0 ...] x [bias_hi bias_lo 0 ...]^T that adds the per-key
+//                     bias inside the tensor core; O += P V reads P from TMEM and V (N-major) from shared memory.
 // TMEM columns: S0 [0,128) S1 [128,256) O0 [256,320) O1 [320,384) P0 [384,448) P1 [448,512).
 //
 // Every wait on an mbarrier is bounded: after ~2^29 clock ticks the waiter raises the CTA's abort flag and the
@@ -29,7 +32,7 @@ constexpr int kBlockM = 128;
 constexpr int kBlockN = 128;
 constexpr int kHeadDim = 64;
 constexpr int kStages = 6;       // K/V ring slots, 16 KiB each
-constexpr int kBiasStages = 4;
+constexpr int kSlabStages = 3;   // bias slab ring slots, 16 KiB each (only two 16-byte chunks per row are used)
 constexpr int kThreads = 320;
 constexpr int kTileBytes = kBlockN * kHeadDim * 2;  // 16384
 constexpr uint32_t kTmemCols = 512;
@@ -37,16 +40,19 @@ constexpr long long kWaitTicks = 1ll << 29;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
+constexpr float kMasked = -3.0e38f;        // "minus infinity" of a masked key, still finite in bfloat16
 
 struct SharedStorage {
     alignas(1024) uint8_t q[2][kTileBytes];
     alignas(1024) uint8_t kv[kStages][kTileBytes];
-    alignas(16) float bias[kBiasStages][kBlockN];
+    alignas(1024) uint8_t q_slab[kTileBytes];             // columns 0,1 = 1.0, rest 0: the A side of the bias step
+    alignas(1024) uint8_t k_slab[kSlabStages][kTileBytes];  // columns 0,1 = bias/scale (hi, lo): the B side
     alignas(8) uint64_t q_full[2];
+    uint64_t q_slab_full;
     uint64_t kv_full[kStages];
     uint64_t kv_empty[kStages];
-    uint64_t bias_full[kBiasStages];
-    uint64_t bias_empty[kBiasStages];
+    uint64_t slab_full[kSlabStages];
+    uint64_t slab_empty[kSlabStages];
     uint64_t s_full[2];
     uint64_t s_empty[2];
     uint64_t p_full[2];
@@ -152,6 +158,24 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
         : "memory");
 }
 
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+// Makes generic-proxy shared-memory writes of this thread visible to the async proxy (tcgen05.mma operands).
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
+}
+// Row r of a slab (128-byte rows, 128-byte swizzle): logical 16-byte chunk c lives at physical chunk c ^ (r % 8).
+// Writes columns 0..7 = {v01 (two 16-bit values), 0 ...} and columns 8..15 = 0; the other chunks are never read.
+__device__ __forceinline__ void slab_write_row(uint32_t slab_addr, int r, uint32_t v01) {
+    const uint32_t row = slab_addr + (uint32_t)r * 128u;
+    st_shared_v4(row + (uint32_t)((0 ^ (r & 7)) << 4), v01, 0u, 0u, 0u);
+    st_shared_v4(row + (uint32_t)((1 ^ (r & 7)) << 4), 0u, 0u, 0u, 0u);
+}
+
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -189,7 +213,7 @@ __host__ __device__ constexpr uint32_t make_idesc(bool bf16, int M, int N, bool 
 }
 
 enum : uint32_t {
-    kErrQFull = 1u << 0, kErrKvFull = 1u << 1, kErrKvEmpty = 1u << 2, kErrBiasFull = 1u << 3, kErrBiasEmpty = 1u << 4,
+    kErrQFull = 1u << 0, kErrKvFull = 1u << 1, kErrKvEmpty = 1u << 2, kErrSlabFull = 1u << 3, kErrSlabEmpty = 1u << 4,
     kErrSFull = 1u << 5, kErrSEmpty = 1u << 6, kErrPFull = 1u << 7, kErrODone = 1u << 8,
 };
 
@@ -197,7 +221,7 @@ template <bool kBF16>
 __global__ void __launch_bounds__(kThreads, 1)
 attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                       const __grid_constant__ CUtensorMap map_v, const void *__restrict__ bias_ptr,
-                      const int *__restrict__ cu, float scale_log2, void *__restrict__ out_ptr, int64_t o_rs,
+                      const int *__restrict__ cu, float scale_log2, float inv_scale, void *__restrict__ out_ptr, int64_t o_rs,
                       float *__restrict__ lse, int64_t total, unsigned int *__restrict__ status) {
     using T = typename std::conditional<kBF16, __nv_bfloat16, __half>::type;
     extern __shared__ uint8_t smem_raw[];
@@ -211,6 +235,10 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     const int q_row0 = s0 + q_off;
     const int n_mt = (q_off + kBlockM < seg_len) ? 2 : 1;  // query tiles with at least one valid row
     const int n_kv = (seg_len + kBlockN - 1) / kBlockN;
+    const bool has_bias = bias_ptr != nullptr;
+    const bool ragged_tail = (seg_len % kBlockN) != 0;
+    // a key tile needs the bias step when there is a bias, or when it is the partial last tile (masking)
+    auto uses_slab = [&](int j) { return has_bias || (ragged_tail && j == n_kv - 1); };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -228,10 +256,11 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             mbar_init(&sh.kv_full[i], 1);
             mbar_init(&sh.kv_empty[i], 1);
         }
-        for (int i = 0; i < kBiasStages; ++i) {
-            mbar_init(&sh.bias_full[i], 1);
-            mbar_init(&sh.bias_empty[i], 4 * n_mt);
+        for (int i = 0; i < kSlabStages; ++i) {
+            mbar_init(&sh.slab_full[i], 1);
+            mbar_init(&sh.slab_empty[i], 1);
         }
+        mbar_init(&sh.q_slab_full, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 9) {
@@ -256,24 +285,44 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 tma_load_3d(sh.q[t], &map_q, 0, head, q_row0 + t * kBlockM, &sh.q_full[t]);
             }
         }
-        int it = 0;  // ring position, advanced once per K or V tile in the order K0 K1 V0 K2 V1 ... V(n-1)
+        {   // the constant A side of the bias step: columns 0 and 1 are 1.0.  Both slabs are bfloat16 whatever the
+            // q/k/v dtype (the bias step is an MMA instruction of its own): bias/scale and the mask value need its range.
+            const uint32_t ones = pack2<true>(1.0f, 1.0f);
+            const uint32_t qs = smem_u32(sh.q_slab);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) slab_write_row(qs, lane * 4 + i, ones);
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sh.q_slab_full);
+        }
+        int it = 0;       // K/V ring position, advanced once per K or V tile in the order K0 K1 V0 K2 V1 ... V(n-1)
+        int slab_it = 0;  // bias slab ring position, advanced once per key tile that uses the bias step
         for (int step = 0; step <= n_kv && ok; ++step) {
             if (step < n_kv) {
-                const int bs = step % kBiasStages;
-                ok = mbar_wait(&sh.bias_empty[bs], ((step / kBiasStages) & 1) ^ 1, sh, status, kErrBiasEmpty);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-                const int key0 = s0 + step * kBlockN + lane * 4;
+                if (uses_slab(step)) {
+                    const int bs = slab_it % kSlabStages;
+                    ok = mbar_wait(&sh.slab_empty[bs], ((slab_it / kSlabStages) & 1) ^ 1, sh, status, kErrSlabEmpty);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
+                    const uint32_t ks = smem_u32(sh.k_slab[bs]);
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const int key = key0 + i;
-                    float b = -INFINITY;
-                    if (key < s1) b = bias ? Elem<T>::to_f32(bias[key]) * kLog2e : 0.0f;
-                    sh.bias[bs][lane * 4 + i] = b;
+                    for (int i = 0; i < 4; ++i) {
+                        const int r = lane * 4 + i;
+                        const int key = s0 + step * kBlockN + r;
+                        float hi = kMasked, lo = 0.0f;
+                        if (key < s1) {
+                            const float b = has_bias ? Elem<T>::to_f32(bias[key]) * inv_scale : 0.0f;
+                            hi = __bfloat162float(__float2bfloat16_rn(b));
+                            lo = b - hi;
+                        }
+                        slab_write_row(ks, r, pack2<true>(hi, lo));
+                    }
+                    fence_proxy_async();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&sh.slab_full[bs]);
+                    ++slab_it;
                 }
-                __syncwarp();
                 if (lane == 0) {
-                    mbar_arrive(&sh.bias_full[bs]);
                     const int stage = it % kStages;
                     ok = mbar_wait(&sh.kv_empty[stage], ((it / kStages) & 1) ^ 1, sh, status, kErrKvEmpty);
                     if (ok) {
@@ -301,17 +350,27 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         // ===== MMA issuer ===================================================================================
         if (lane == 0) {
             constexpr uint32_t idesc_qk = make_idesc(kBF16, kBlockM, kBlockN, false);
+            constexpr uint32_t idesc_slab = make_idesc(true, kBlockM, kBlockN, false);
             constexpr uint32_t idesc_pv = make_idesc(kBF16, kBlockM, kHeadDim, true);
             bool ok = true;
             for (int t = 0; t < n_mt && ok; ++t) ok = mbar_wait(&sh.q_full[t], 0, sh, status, kErrQFull);
+            if (ok) ok = mbar_wait(&sh.q_slab_full, 0, sh, status, kErrQFull);
             const uint64_t q_desc[2] = {make_smem_desc(smem_u32(sh.q[0])), make_smem_desc(smem_u32(sh.q[1]))};
-            int it = 0;
+            const uint64_t q_slab_desc = make_smem_desc(smem_u32(sh.q_slab));
+            int it = 0, slab_it = 0;
             for (int step = 0; step <= n_kv && ok; ++step) {
                 if (step < n_kv) {
                     const int stage = it % kStages;
                     ok = mbar_wait(&sh.kv_full[stage], (it / kStages) & 1, sh, status, kErrKvFull);
                     if (!ok) break;
                     const uint64_t k_desc = make_smem_desc(smem_u32(sh.kv[stage]));
+                    const bool slab = uses_slab(step);
+                    const int bs = slab_it % kSlabStages;
+                    if (slab) {
+                        ok = mbar_wait(&sh.slab_full[bs], (slab_it / kSlabStages) & 1, sh, status, kErrSlabFull);
+                        if (!ok) break;
+                    }
+                    const uint64_t k_slab_desc = make_smem_desc(smem_u32(sh.k_slab[bs]));
                     for (int t = 0; t < n_mt; ++t) {
                         if (step > 0) {
                             ok = mbar_wait(&sh.s_empty[t], (step - 1) & 1, sh, status, kErrSEmpty);
@@ -322,10 +381,15 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
 #pragma unroll
                         for (int kk = 0; kk < kHeadDim / 16; ++kk)
                             tc_mma_ss(s_tmem, q_desc[t] + kk * 2, k_desc + kk * 2, idesc_qk, kk > 0);
+                        if (slab) tc_mma_ss(s_tmem, q_slab_desc, k_slab_desc, idesc_slab, 1u);
                         tc_commit(&sh.s_full[t]);
                     }
                     if (!ok) break;
                     tc_commit(&sh.kv_empty[stage]);
+                    if (slab) {
+                        tc_commit(&sh.slab_empty[bs]);
+                        ++slab_it;
+                    }
                     ++it;
                 }
                 if (step >= 1) {
@@ -361,94 +425,96 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         const uint32_t o_tmem = tmem + lane_addr + 256 + t * kHeadDim;
         const uint32_t p_tmem = tmem + lane_addr + 384 + t * 64;
         const int row = q_row0 + t * kBlockM + r;
-        float m_ref = -INFINITY, l = 0.0f;
+        float m_ref = -INFINITY, l = 0.0f;  // reference max (log2 units, scale applied) and running sum
         bool ok = true;
 
-        for (int j = 0; j < n_kv; ++j) {
+        for (int j = 0; j < n_kv && ok; ++j) {
             ok = mbar_wait(&sh.s_full[t], j & 1, sh, status, kErrSFull);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
-            uint32_t s[4][32];
-            tmem_ld32(s_tmem + 0, s[0]);
-            tmem_ld32(s_tmem + 32, s[1]);
-            tmem_ld32(s_tmem + 64, s[2]);
-            tmem_ld32(s_tmem + 96, s[3]);
-            tc_wait_ld();
-            tc_fence_before();
-            mbar_arrive(&sh.s_empty[t]);  // scores are in registers: the next S = Q K^T may overwrite TMEM
-
-            const int bs = j % kBiasStages;
-            ok = mbar_wait(&sh.bias_full[bs], (j / kBiasStages) & 1, sh, status, kErrBiasFull);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            float m_tile = -INFINITY;
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-#pragma unroll
-                for (int i = 0; i < 32; i += 4) {
-                    const float4 b = *reinterpret_cast<const float4 *>(&sh.bias[bs][c * 32 + i]);
-                    float x0 = fmaf(__uint_as_float(s[c][i + 0]), scale_log2, b.x);
-                    float x1 = fmaf(__uint_as_float(s[c][i + 1]), scale_log2, b.y);
-                    float x2 = fmaf(__uint_as_float(s[c][i + 2]), scale_log2, b.z);
-                    float x3 = fmaf(__uint_as_float(s[c][i + 3]), scale_log2, b.w);
-                    s[c][i + 0] = __float_as_uint(x0);
-                    s[c][i + 1] = __float_as_uint(x1);
-                    s[c][i + 2] = __float_as_uint(x2);
-                    s[c][i + 3] = __float_as_uint(x3);
-                    m_tile = fmaxf(m_tile, fmaxf(fmaxf(x0, x1), fmaxf(x2, x3)));
+            for (int h = 0; h < 2; ++h) {
+                uint32_t a[64];
+                tmem_ld32(s_tmem + h * 64, *reinterpret_cast<uint32_t(*)[32]>(&a[0]));
+                tmem_ld32(s_tmem + h * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&a[32]));
+                tc_wait_ld();
+                if (h == 1) {
+                    tc_fence_before();
+                    mbar_arrive(&sh.s_empty[t]);  // all 128 scores are in registers: S may be overwritten
                 }
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&sh.bias_empty[bs]);
-
-            bool need = false;
-            if (j == 0) {
-                m_ref = m_tile;
-            } else {
-                need = m_tile > m_ref + kRescaleThreshold;
-                // PV of the previous step must be complete: O is then stable and the P buffer is free again
-                ok = mbar_wait(&sh.o_done[t], (j - 1) & 1, sh, status, kErrODone);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-                tc_fence_after();
+                // row max of this half: four independent 3-input chains
+                float mx[4];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    mx[c] = __uint_as_float(a[16 * c]);
+#pragma unroll
+                    for (int i = 1; i < 15; i += 2)
+                        mx[c] = max3(mx[c], __uint_as_float(a[16 * c + i]), __uint_as_float(a[16 * c + i + 1]));
+                    mx[c] = fmaxf(mx[c], __uint_as_float(a[16 * c + 15]));
+                }
+                const float t_max = fmaxf(max3(mx[0], mx[1], mx[2]), mx[3]) * scale_log2;
+                const bool need = t_max > m_ref + kRescaleThreshold;  // always true on the first half (m_ref = -inf)
+                if (h == 0 && j > 0) {
+                    // P V of the previous key tile must be complete: O is stable and the P buffer is free again
+                    ok = mbar_wait(&sh.o_done[t], (j - 1) & 1, sh, status, kErrODone);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
+                    tc_fence_after();
+                }
                 if (__any_sync(0xffffffffu, need)) {
                     float alpha = 1.0f;
                     if (need) {
-                        alpha = fast_exp2(m_ref - m_tile);
-                        m_ref = m_tile;
+                        alpha = (m_ref == -INFINITY) ? 0.0f : fast_exp2(m_ref - t_max);
+                        m_ref = t_max;
                         l *= alpha;
                     }
-                    uint32_t o[2][32];
-                    tmem_ld32(o_tmem + 0, o[0]);
-                    tmem_ld32(o_tmem + 32, o[1]);
-                    tc_wait_ld();
+                    if (j > 0) {  // rescale what earlier key tiles accumulated
+                        uint32_t o[2][32];
+                        tmem_ld32(o_tmem + 0, o[0]);
+                        tmem_ld32(o_tmem + 32, o[1]);
+                        tc_wait_ld();
 #pragma unroll
-                    for (int c = 0; c < 2; ++c)
+                        for (int c = 0; c < 2; ++c)
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) o[c][i] = __float_as_uint(__uint_as_float(o[c][i]) * alpha);
-                    tmem_st32(o_tmem + 0, o[0]);
-                    tmem_st32(o_tmem + 32, o[1]);
+                            for (int i = 0; i < 32; ++i) o[c][i] = __float_as_uint(__uint_as_float(o[c][i]) * alpha);
+                        tmem_st32(o_tmem + 0, o[0]);
+                        tmem_st32(o_tmem + 32, o[1]);
+                    }
+                    if (h == 1) {  // and the first half of this tile's probabilities, already staged in TMEM
+                        uint32_t q0[32];
+                        tc_wait_st();
+                        tmem_ld32(p_tmem, q0);
+                        tc_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            float lo, hi;
+                            if constexpr (kBF16) {
+                                const float2 f = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162 *>(&q0[i]));
+                                lo = f.x; hi = f.y;
+                            } else {
+                                const float2 f = __half22float2(*reinterpret_cast<__half2 *>(&q0[i]));
+                                lo = f.x; hi = f.y;
+                            }
+                            q0[i] = pack2<kBF16>(lo * alpha, hi * alpha);
+                        }
+                        tmem_st32(p_tmem, q0);
+                    }
                 }
-            }
-
-            float sum = 0.0f;
+                const float neg_m = -m_ref;
+                float sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                uint32_t pk[32];
 #pragma unroll
-            for (int c = 0; c < 4; c += 2) {
-                uint32_t p[32];
-#pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    const float p0 = fast_exp2(__uint_as_float(s[c][i]) - m_ref);
-                    const float p1 = fast_exp2(__uint_as_float(s[c][i + 1]) - m_ref);
-                    const float p2 = fast_exp2(__uint_as_float(s[c + 1][i]) - m_ref);
-                    const float p3 = fast_exp2(__uint_as_float(s[c + 1][i + 1]) - m_ref);
-                    sum += (p0 + p1) + (p2 + p3);
-                    p[i / 2] = pack2<kBF16>(p0, p1);
-                    p[16 + i / 2] = pack2<kBF16>(p2, p3);
+                for (int i = 0; i < 64; i += 2) {
+                    const float p0 = fast_exp2(fmaf(__uint_as_float(a[i]), scale_log2, neg_m));
+                    const float p1 = fast_exp2(fmaf(__uint_as_float(a[i + 1]), scale_log2, neg_m));
+                    sum[(i >> 1) & 3] += p0 + p1;
+                    pk[i >> 1] = pack2<kBF16>(p0, p1);
                 }
-                tmem_st32(p_tmem + c * 16, p);  // 64 keys -> 32 columns of 16-bit pairs
+                l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
+                tmem_st32(p_tmem + h * 32, pk);  // 64 keys -> 32 columns of 16-bit pairs
             }
-            l += sum;
+            if (!ok) break;
             tc_wait_st();
             tc_fence_before();
             mbar_arrive(&sh.p_full[t]);
@@ -544,6 +610,8 @@ bool attn_sm100_supported(const AttnArgs &a) {
     auto al16 = [](const void *p) { return ((uintptr_t)p & 15) == 0; };
     if (!al16(a.q) || !al16(a.k) || !al16(a.v) || !al16(a.out)) return false;
     if (a.q_rs % 8 || a.k_rs % 8 || a.v_rs % 8 || a.o_rs % 8) return false;
+    // the row max is taken on raw scores and the bias is divided by the scale: both need a positive finite scale
+    if (!(a.scale > 0.0f) || !(a.scale < 3.0e38f)) return false;
     return true;
 }
 
@@ -558,13 +626,14 @@ int attn_sm100_launch(const AttnArgs &a, cudaStream_t stream) {
     const size_t smem = sizeof(SharedStorage) + 1024;
     dim3 grid((a.max_seqlen + 2 * kBlockM - 1) / (2 * kBlockM), a.nseg, a.H);
     const float scale_log2 = a.scale * kLog2e;
+    const float inv_scale = 1.0f / a.scale;
     if (a.dtype == COME_BF16) {
         COME_CUDA(cudaFuncSetAttribute(attn_fwd_sm100_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        attn_fwd_sm100_kernel<true><<<grid, kThreads, smem, stream>>>(mq, mk, mv, a.bias, a.cu, scale_log2, a.out, a.o_rs, a.lse,
+        attn_fwd_sm100_kernel<true><<<grid, kThreads, smem, stream>>>(mq, mk, mv, a.bias, a.cu, scale_log2, inv_scale, a.out, a.o_rs, a.lse,
                                                                      a.total, status);
     } else {
         COME_CUDA(cudaFuncSetAttribute(attn_fwd_sm100_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        attn_fwd_sm100_kernel<false><<<grid, kThreads, smem, stream>>>(mq, mk, mv, a.bias, a.cu, scale_log2, a.out, a.o_rs, a.lse,
+        attn_fwd_sm100_kernel<false><<<grid, kThreads, smem, stream>>>(mq, mk, mv, a.bias, a.cu, scale_log2, inv_scale, a.out, a.o_rs, a.lse,
                                                                       a.total, status);
     }
     return check_launch("come_attn_varlen_fwd (tcgen05 kernel)");
