@@ -41,7 +41,7 @@ def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) 
         obj = os.path.join(BUILD, os.path.basename(src)[:-3] + ".o")
         if not force and _newer(obj, [src] + hdrs):
             return obj, ""
-        cmd = [nvcc, *NVCC_FLAGS, "-c", src, "-o", obj]
+        cmd = [nvcc, *NVCC_FLAGS, *os.environ.get("COME_EXTRA_NVCC_FLAGS", "").split(), "-c", src, "-o", obj]
         if ptxas_info:
             cmd[1:1] = ["-Xptxas", "-v"]
         r = subprocess.run(cmd, capture_output=True, text=True)

@@ -3,16 +3,19 @@
 //
 // One CTA owns up to two 128-row query tiles of one (segment, head) and walks the segment's keys 128 at a time.
 //   warps 0-3 / 4-7 : softmax group of query tile 0 / 1.  Thread r owns score row r (TMEM lane r).  Per key tile it
-//                     reads the scores 64 columns at a time, tracks the row max with 3-input max, computes
+//                     reads the scores 32 columns at a time (the next TMEM load in flight behind the current
+//                     quarter's arithmetic), tracks the row max with 3-input max, computes
 //                     p = exp2(s * scale*log2e - m) with one FFMA + one MUFU per score, writes p back to TMEM as
 //                     16-bit pairs (the A operand of P V) and rescales the accumulator only when the running max
 //                     grew by more than 2^8 (exact: the final normalisation uses the same reference max).
 //   warp 8          : producer.  Issues the TMA loads of Q, K and V and stages, per key tile, a "bias slab": a
 //                     128-byte-swizzled tile whose first two columns hold bias/scale split into a high and a low
 //                     16-bit part (a large negative number past the segment end, which masks the ragged tail).
-//   warp 9          : one thread issues every tcgen05.mma.  S = Q K^T takes four K=16 steps over the head
-//                     dimension plus one K=16 step [1 1 0 ...] x [bias_hi bias_lo 0 ...]^T that adds the per-key
-//                     bias inside the tensor core; O += P V reads P from TMEM and V (N-major) from shared memory.
+//   warps 9, 10     : MMA issuer of query tile 0 / 1 (one elected lane issues).  S = Q K^T takes four K=16 steps
+//                     over the head dimension plus one K=16 step [1 1 0 ...] x [bias_hi bias_lo 0 ...]^T that adds
+//                     the per-key bias inside the tensor core; O += P V reads P from TMEM and V (N-major) from
+//                     shared memory.  S(j+1) is issued as soon as the softmax group holds S(j) in registers, P V as
+//                     soon as P(j) is staged, so a softmax group never waits for its own tile's scores.
 // TMEM columns: S0 [0,128) S1 [128,256) O0 [256,320) O1 [320,384) P0 [384,448) P1 [448,512).
 //
 // Every wait on an mbarrier is bounded: after ~2^29 clock ticks the waiter raises the CTA's abort flag and the
@@ -33,7 +36,7 @@ constexpr int kBlockN = 128;
 constexpr int kHeadDim = 64;
 constexpr int kStages = 6;       // K/V ring slots, 16 KiB each
 constexpr int kSlabStages = 3;   // bias slab ring slots, 16 KiB each (only two 16-byte chunks per row are used)
-constexpr int kThreads = 320;
+constexpr int kThreads = 384;   // 8 softmax warps, producer, two MMA issuers (one per query tile), one spare
 constexpr int kTileBytes = kBlockN * kHeadDim * 2;  // 16384
 constexpr uint32_t kTmemCols = 512;
 constexpr long long kWaitTicks = 1ll << 29;
@@ -54,9 +57,9 @@ struct SharedStorage {
     uint64_t slab_full[kSlabStages];
     uint64_t slab_empty[kSlabStages];
     uint64_t s_full[2];
-    uint64_t s_empty[2];
     uint64_t p_full[2];
     uint64_t o_done[2];
+    uint64_t s_empty[2];
     uint32_t tmem_base;
     volatile uint32_t abort_flag;
 };
@@ -84,13 +87,44 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// Optional cycle accounting of the barrier waits of CTA (0,0,0) (build with -DCOME_ATTN_PROFILE; development aid):
+// slot = bit index of the wait's error code (+16 for the second softmax group); slot 15 / 31 = softmax loop total.
+#ifdef COME_ATTN_PROFILE
+__device__ unsigned long long g_attn_timers[32];
+__device__ long long g_attn_trace[4][16][4];  // [role: wg0, wg1, mma t0, mma t1][step][event]
+#define PROF_TRACE(role, step, ev)                                                                      \
+    do {                                                                                                \
+        if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (threadIdx.x & 31) == 0 && (step) < 16) \
+            g_attn_trace[role][step][ev] = clock64();                                                   \
+    } while (0)
+__device__ __forceinline__ void prof_add(int slot, long long t0) {
+    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (threadIdx.x & 31) == 0 && (threadIdx.x < 32 || threadIdx.x >= 128))
+        atomicAdd(&g_attn_timers[slot + ((threadIdx.x >= 128 && threadIdx.x < 256) ? 16 : 0)], (unsigned long long)(clock64() - t0));
+}
+#else
+#define PROF_TRACE(role, step, ev) do {} while (0)
+#endif
+
 // Bounded wait.  Returns false (and raises the abort flag + the device status word) when it gives up.
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, SharedStorage &sh, unsigned int *status,
                                           uint32_t code) {
+#ifdef COME_ATTN_PROFILE
+    const long long t0 = clock64();
+    if (mbar_try_wait(bar, parity)) {
+        prof_add(__ffs((int)code) - 1, t0);
+        return true;
+    }
+#else
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
+#endif
     while (true) {
-        if (mbar_try_wait(bar, parity)) return true;
+        if (mbar_try_wait(bar, parity)) {
+#ifdef COME_ATTN_PROFILE
+            prof_add(__ffs((int)code) - 1, t0);
+#endif
+            return true;
+        }
         if (sh.abort_flag != 0) return false;
         if (clock64() - t0 > kWaitTicks) {
             sh.abort_flag = 1;
@@ -112,23 +146,28 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
+// The three wrappers below are called by ALL lanes of an issuer warp in warp-uniform control flow; one elected lane
+// executes the instruction.  Keeping the surrounding address arithmetic uniform is what lets the issue loop keep
+// up with the tensor core (a divergent single-thread loop measured ~70 clocks per instruction, this form ~30-60).
 __device__ __forceinline__ void tc_commit(uint64_t *bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+    asm volatile(
+        "{\n\t.reg .pred e;\n\telect.sync _|e, 0xffffffff;\n\t"
+        "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}"
+        ::"r"(smem_u32(bar)) : "memory");
 }
-
 // D[tmem] (+)= A[smem] * B[smem]
 __device__ __forceinline__ void tc_mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        "{\n\t.reg .pred p, e;\n\telect.sync _|e, 0xffffffff;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
 // D[tmem] (+)= A[tmem] * B[smem]
 __device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        "{\n\t.reg .pred p, e;\n\telect.sync _|e, 0xffffffff;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
         ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
@@ -155,6 +194,24 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
           "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
           "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
           "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
         : "memory");
 }
 
@@ -248,17 +305,17 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         for (int i = 0; i < 2; ++i) {
             mbar_init(&sh.q_full[i], 1);
             mbar_init(&sh.s_full[i], 1);
-            mbar_init(&sh.s_empty[i], kBlockM);
             mbar_init(&sh.p_full[i], kBlockM);
             mbar_init(&sh.o_done[i], 1);
+            mbar_init(&sh.s_empty[i], kBlockM);
         }
         for (int i = 0; i < kStages; ++i) {
             mbar_init(&sh.kv_full[i], 1);
-            mbar_init(&sh.kv_empty[i], 1);
+            mbar_init(&sh.kv_empty[i], n_mt);  // released by the issuer of every active query tile
         }
         for (int i = 0; i < kSlabStages; ++i) {
             mbar_init(&sh.slab_full[i], 1);
-            mbar_init(&sh.slab_empty[i], 1);
+            mbar_init(&sh.slab_empty[i], n_mt);
         }
         mbar_init(&sh.q_slab_full, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -295,124 +352,114 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             __syncwarp();
             if (lane == 0) mbar_arrive(&sh.q_slab_full);
         }
-        int it = 0;       // K/V ring position, advanced once per K or V tile in the order K0 K1 V0 K2 V1 ... V(n-1)
+        int it = 0;       // K/V ring position, advanced once per K or V tile in the order K0 V0 K1 V1 ...
         int slab_it = 0;  // bias slab ring position, advanced once per key tile that uses the bias step
-        for (int step = 0; step <= n_kv && ok; ++step) {
-            if (step < n_kv) {
-                if (uses_slab(step)) {
-                    const int bs = slab_it % kSlabStages;
-                    ok = mbar_wait(&sh.slab_empty[bs], ((slab_it / kSlabStages) & 1) ^ 1, sh, status, kErrSlabEmpty);
-                    ok = __all_sync(0xffffffffu, ok);
-                    if (!ok) break;
-                    const uint32_t ks = smem_u32(sh.k_slab[bs]);
+        for (int j = 0; j < n_kv && ok; ++j) {
+            if (uses_slab(j)) {
+                const int bs = slab_it % kSlabStages;
+                ok = mbar_wait(&sh.slab_empty[bs], ((slab_it / kSlabStages) & 1) ^ 1, sh, status, kErrSlabEmpty);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                const uint32_t ks = smem_u32(sh.k_slab[bs]);
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const int r = lane * 4 + i;
-                        const int key = s0 + step * kBlockN + r;
-                        float hi = kMasked, lo = 0.0f;
-                        if (key < s1) {
-                            const float b = has_bias ? Elem<T>::to_f32(bias[key]) * inv_scale : 0.0f;
-                            hi = __bfloat162float(__float2bfloat16_rn(b));
-                            lo = b - hi;
-                        }
-                        slab_write_row(ks, r, pack2<true>(hi, lo));
+                for (int i = 0; i < 4; ++i) {
+                    const int r = lane * 4 + i;
+                    const int key = s0 + j * kBlockN + r;
+                    float hi = kMasked, lo = 0.0f;
+                    if (key < s1) {
+                        const float b = has_bias ? Elem<T>::to_f32(bias[key]) * inv_scale : 0.0f;
+                        hi = __bfloat162float(__float2bfloat16_rn(b));
+                        lo = b - hi;
                     }
-                    fence_proxy_async();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&sh.slab_full[bs]);
-                    ++slab_it;
+                    slab_write_row(ks, r, pack2<true>(hi, lo));
                 }
-                if (lane == 0) {
-                    const int stage = it % kStages;
-                    ok = mbar_wait(&sh.kv_empty[stage], ((it / kStages) & 1) ^ 1, sh, status, kErrKvEmpty);
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sh.slab_full[bs]);
+                ++slab_it;
+            }
+            if (lane == 0) {
+#pragma unroll
+                for (int kv = 0; kv < 2 && ok; ++kv) {  // K tile, then V tile of the same keys
+                    const int stage = (it + kv) % kStages;
+                    ok = mbar_wait(&sh.kv_empty[stage], (((it + kv) / kStages) & 1) ^ 1, sh, status, kErrKvEmpty);
                     if (ok) {
                         mbar_arrive_expect_tx(&sh.kv_full[stage], kTileBytes);
-                        tma_load_3d(sh.kv[stage], &map_k, 0, head, s0 + step * kBlockN, &sh.kv_full[stage]);
+                        tma_load_3d(sh.kv[stage], kv == 0 ? &map_k : &map_v, 0, head, s0 + j * kBlockN, &sh.kv_full[stage]);
                     }
                 }
-                ok = __all_sync(0xffffffffu, ok);
-                ++it;
             }
-            if (step >= 1 && ok) {
-                if (lane == 0) {
-                    const int stage = it % kStages;
-                    ok = mbar_wait(&sh.kv_empty[stage], ((it / kStages) & 1) ^ 1, sh, status, kErrKvEmpty);
-                    if (ok) {
-                        mbar_arrive_expect_tx(&sh.kv_full[stage], kTileBytes);
-                        tma_load_3d(sh.kv[stage], &map_v, 0, head, s0 + (step - 1) * kBlockN, &sh.kv_full[stage]);
-                    }
-                }
-                ok = __all_sync(0xffffffffu, ok);
-                ++it;
-            }
+            ok = __all_sync(0xffffffffu, ok);
+            it += 2;
         }
-    } else if (warp == 9) {
-        // ===== MMA issuer ===================================================================================
-        if (lane == 0) {
+    } else if (warp == 9 || warp == 10) {
+        // ===== MMA issuer of query tile t (all lanes run the loop, one elected lane issues) ================
+        const int t = warp - 9;
+        if (t < n_mt) {
             constexpr uint32_t idesc_qk = make_idesc(kBF16, kBlockM, kBlockN, false);
             constexpr uint32_t idesc_slab = make_idesc(true, kBlockM, kBlockN, false);
             constexpr uint32_t idesc_pv = make_idesc(kBF16, kBlockM, kHeadDim, true);
-            bool ok = true;
-            for (int t = 0; t < n_mt && ok; ++t) ok = mbar_wait(&sh.q_full[t], 0, sh, status, kErrQFull);
-            if (ok) ok = mbar_wait(&sh.q_slab_full, 0, sh, status, kErrQFull);
-            const uint64_t q_desc[2] = {make_smem_desc(smem_u32(sh.q[0])), make_smem_desc(smem_u32(sh.q[1]))};
+            const uint64_t q_desc = make_smem_desc(smem_u32(sh.q[t]));
             const uint64_t q_slab_desc = make_smem_desc(smem_u32(sh.q_slab));
-            int it = 0, slab_it = 0;
-            for (int step = 0; step <= n_kv && ok; ++step) {
-                if (step < n_kv) {
-                    const int stage = it % kStages;
-                    ok = mbar_wait(&sh.kv_full[stage], (it / kStages) & 1, sh, status, kErrKvFull);
-                    if (!ok) break;
-                    const uint64_t k_desc = make_smem_desc(smem_u32(sh.kv[stage]));
-                    const bool slab = uses_slab(step);
-                    const int bs = slab_it % kSlabStages;
-                    if (slab) {
-                        ok = mbar_wait(&sh.slab_full[bs], (slab_it / kSlabStages) & 1, sh, status, kErrSlabFull);
-                        if (!ok) break;
-                    }
-                    const uint64_t k_slab_desc = make_smem_desc(smem_u32(sh.k_slab[bs]));
-                    for (int t = 0; t < n_mt; ++t) {
-                        if (step > 0) {
-                            ok = mbar_wait(&sh.s_empty[t], (step - 1) & 1, sh, status, kErrSEmpty);
-                            if (!ok) break;
-                        }
-                        tc_fence_after();
-                        const uint32_t s_tmem = tmem + t * kBlockN;
-#pragma unroll
-                        for (int kk = 0; kk < kHeadDim / 16; ++kk)
-                            tc_mma_ss(s_tmem, q_desc[t] + kk * 2, k_desc + kk * 2, idesc_qk, kk > 0);
-                        if (slab) tc_mma_ss(s_tmem, q_slab_desc, k_slab_desc, idesc_slab, 1u);
-                        tc_commit(&sh.s_full[t]);
-                    }
-                    if (!ok) break;
-                    tc_commit(&sh.kv_empty[stage]);
-                    if (slab) {
-                        tc_commit(&sh.slab_empty[bs]);
-                        ++slab_it;
-                    }
-                    ++it;
+            const uint64_t kv_desc0 = make_smem_desc(smem_u32(sh.kv[0]));       // slot i: + i * (kTileBytes >> 4)
+            const uint64_t k_slab_desc0 = make_smem_desc(smem_u32(sh.k_slab[0]));
+            const uint32_t s_tmem = tmem + t * kBlockN;
+            const uint32_t o_tmem = tmem + 256 + t * kHeadDim;
+            const uint32_t p_tmem = tmem + 384 + t * 64;
+            bool ok = mbar_wait(&sh.q_full[t], 0, sh, status, kErrQFull);
+            if (ok) ok = mbar_wait(&sh.q_slab_full, 0, sh, status, kErrQFull);
+            ok = __all_sync(0xffffffffu, ok);
+            int slab_it = 0;
+            // S(0), then per key tile j: S(j+1) = Q K_(j+1)^T as soon as the softmax group has read S(j) into registers,
+            // and O += P(j) V_j as soon as P(j) is staged.  Ring slot of K_j is 2j, of V_j is 2j+1.  The other query
+            // tile's issuer runs the same loop independently.
+            auto issue_s = [&](int jj) -> bool {  // jj = key tile whose scores are produced
+                const int k_it = 2 * jj, k_slot = k_it % kStages;
+                const bool slab = uses_slab(jj);
+                const int bs = slab_it % kSlabStages;
+                bool good = mbar_wait(&sh.kv_full[k_slot], (k_it / kStages) & 1, sh, status, kErrKvFull);
+                if (good && slab) good = mbar_wait(&sh.slab_full[bs], (slab_it / kSlabStages) & 1, sh, status, kErrSlabFull);
+                if (good && jj > 0) good = mbar_wait(&sh.s_empty[t], (jj - 1) & 1, sh, status, kErrSEmpty);
+                good = __all_sync(0xffffffffu, good);
+                if (!good) return false;
+                tc_fence_after();
+                const uint64_t k_desc = kv_desc0 + (uint64_t)(k_slot * (kTileBytes >> 4));
+                tc_mma_ss(s_tmem, q_desc + 0, k_desc + 0, idesc_qk, 0u);
+                tc_mma_ss(s_tmem, q_desc + 2, k_desc + 2, idesc_qk, 1u);
+                tc_mma_ss(s_tmem, q_desc + 4, k_desc + 4, idesc_qk, 1u);
+                tc_mma_ss(s_tmem, q_desc + 6, k_desc + 6, idesc_qk, 1u);
+                if (slab) tc_mma_ss(s_tmem, q_slab_desc, k_slab_desc0 + (uint64_t)(bs * (kTileBytes >> 4)), idesc_slab, 1u);
+                tc_commit(&sh.s_full[t]);
+                tc_commit(&sh.kv_empty[k_slot]);
+                if (slab) {
+                    tc_commit(&sh.slab_empty[bs]);
+                    ++slab_it;
                 }
-                if (step >= 1) {
-                    const int j = step - 1;
-                    const int stage = it % kStages;
-                    ok = mbar_wait(&sh.kv_full[stage], (it / kStages) & 1, sh, status, kErrKvFull);
+                return true;
+            };
+            if (ok) ok = issue_s(0);
+            for (int j = 0; j < n_kv && ok; ++j) {
+                if (j + 1 < n_kv) {
+                    ok = issue_s(j + 1);
                     if (!ok) break;
-                    const uint64_t v_desc = make_smem_desc(smem_u32(sh.kv[stage]));
-                    for (int t = 0; t < n_mt; ++t) {
-                        ok = mbar_wait(&sh.p_full[t], j & 1, sh, status, kErrPFull);
-                        if (!ok) break;
-                        tc_fence_after();
-                        const uint32_t o_tmem = tmem + 256 + t * kHeadDim;
-                        const uint32_t p_tmem = tmem + 384 + t * 64;
-#pragma unroll
-                        for (int kk = 0; kk < kBlockN / 16; ++kk)
-                            tc_mma_ts(o_tmem, p_tmem + kk * 8, v_desc + kk * (2048 >> 4), idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
-                        tc_commit(&sh.o_done[t]);
-                    }
-                    if (!ok) break;
-                    tc_commit(&sh.kv_empty[stage]);
-                    ++it;
                 }
+                const int v_it = 2 * j + 1, v_slot = v_it % kStages;
+                ok = mbar_wait(&sh.kv_full[v_slot], (v_it / kStages) & 1, sh, status, kErrKvFull);
+                if (ok) ok = mbar_wait(&sh.p_full[t], j & 1, sh, status, kErrPFull);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tc_fence_after();
+                const uint64_t v_desc = kv_desc0 + (uint64_t)(v_slot * (kTileBytes >> 4));
+                tc_mma_ts(o_tmem, p_tmem + 0, v_desc + 0 * 128, idesc_pv, j > 0 ? 1u : 0u);
+                tc_mma_ts(o_tmem, p_tmem + 8, v_desc + 1 * 128, idesc_pv, 1u);
+                tc_mma_ts(o_tmem, p_tmem + 16, v_desc + 2 * 128, idesc_pv, 1u);
+                tc_mma_ts(o_tmem, p_tmem + 24, v_desc + 3 * 128, idesc_pv, 1u);
+                tc_mma_ts(o_tmem, p_tmem + 32, v_desc + 4 * 128, idesc_pv, 1u);
+                tc_mma_ts(o_tmem, p_tmem + 40, v_desc + 5 * 128, idesc_pv, 1u);
+                tc_mma_ts(o_tmem, p_tmem + 48, v_desc + 6 * 128, idesc_pv, 1u);
+                tc_mma_ts(o_tmem, p_tmem + 56, v_desc + 7 * 128, idesc_pv, 1u);
+                tc_commit(&sh.o_done[t]);
+                tc_commit(&sh.kv_empty[v_slot]);
             }
         }
         __syncwarp();
@@ -427,41 +474,36 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         const int row = q_row0 + t * kBlockM + r;
         float m_ref = -INFINITY, l = 0.0f;  // reference max (log2 units, scale applied) and running sum
         bool ok = true;
+#ifdef COME_ATTN_PROFILE
+        const long long prof_loop_t0 = clock64();
+#endif
 
         for (int j = 0; j < n_kv && ok; ++j) {
+            if ((warp & 3) == 0) PROF_TRACE(t, j, 0);
             ok = mbar_wait(&sh.s_full[t], j & 1, sh, status, kErrSFull);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
+            if ((warp & 3) == 0) PROF_TRACE(t, j, 1);
+            // The 128 scores of the row are processed 32 columns at a time; the TMEM load of the next quarter is in
+            // flight while the current one is turned into probabilities.
+            uint32_t buf[2][32];
+            tmem_ld32(s_tmem, buf[0]);
+            tc_wait_ld();
+            bool o_ready = (j == 0);  // P V of the previous key tile complete: O stable, P buffer free
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                uint32_t a[64];
-                tmem_ld32(s_tmem + h * 64, *reinterpret_cast<uint32_t(*)[32]>(&a[0]));
-                tmem_ld32(s_tmem + h * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&a[32]));
-                tc_wait_ld();
-                if (h == 1) {
-                    tc_fence_before();
-                    mbar_arrive(&sh.s_empty[t]);  // all 128 scores are in registers: S may be overwritten
-                }
-                // row max of this half: four independent 3-input chains
-                float mx[4];
+            for (int q = 0; q < 4; ++q) {
+                uint32_t(&a)[32] = buf[q & 1];
+                if (q < 3) tmem_ld32(s_tmem + 32 * (q + 1), buf[(q + 1) & 1]);
+                // row max of this quarter: two independent 3-input chains
+                float m0 = __uint_as_float(a[0]), m1 = __uint_as_float(a[15]);
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    mx[c] = __uint_as_float(a[16 * c]);
-#pragma unroll
-                    for (int i = 1; i < 15; i += 2)
-                        mx[c] = max3(mx[c], __uint_as_float(a[16 * c + i]), __uint_as_float(a[16 * c + i + 1]));
-                    mx[c] = fmaxf(mx[c], __uint_as_float(a[16 * c + 15]));
+                for (int i = 1; i < 15; i += 2) {
+                    m0 = max3(m0, __uint_as_float(a[i]), __uint_as_float(a[i + 1]));
+                    m1 = max3(m1, __uint_as_float(a[15 + i]), __uint_as_float(a[15 + i + 1]));
                 }
-                const float t_max = fmaxf(max3(mx[0], mx[1], mx[2]), mx[3]) * scale_log2;
-                const bool need = t_max > m_ref + kRescaleThreshold;  // always true on the first half (m_ref = -inf)
-                if (h == 0 && j > 0) {
-                    // P V of the previous key tile must be complete: O is stable and the P buffer is free again
-                    ok = mbar_wait(&sh.o_done[t], (j - 1) & 1, sh, status, kErrODone);
-                    ok = __all_sync(0xffffffffu, ok);
-                    if (!ok) break;
-                    tc_fence_after();
-                }
+                const float t_max = max3(m0, m1, fmaxf(__uint_as_float(a[29]), fmaxf(__uint_as_float(a[30]), __uint_as_float(a[31])))) * scale_log2;
+                const bool need = t_max > m_ref + kRescaleThreshold;  // always true on the very first quarter (m_ref = -inf)
                 if (__any_sync(0xffffffffu, need)) {
                     float alpha = 1.0f;
                     if (need) {
@@ -470,7 +512,15 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                         l *= alpha;
                     }
                     if (j > 0) {  // rescale what earlier key tiles accumulated
+                        if (!o_ready) {
+                            ok = mbar_wait(&sh.o_done[t], (j - 1) & 1, sh, status, kErrODone);
+                            ok = __all_sync(0xffffffffu, ok);
+                            if (!ok) break;
+                            tc_fence_after();
+                            o_ready = true;
+                        }
                         uint32_t o[2][32];
+                        tc_wait_ld();  // (also completes the prefetch; the rare path may serialise)
                         tmem_ld32(o_tmem + 0, o[0]);
                         tmem_ld32(o_tmem + 32, o[1]);
                         tc_wait_ld();
@@ -481,45 +531,67 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                         tmem_st32(o_tmem + 0, o[0]);
                         tmem_st32(o_tmem + 32, o[1]);
                     }
-                    if (h == 1) {  // and the first half of this tile's probabilities, already staged in TMEM
-                        uint32_t q0[32];
+#pragma unroll
+                    for (int qq = 0; qq < q; ++qq) {  // and this tile's probabilities already staged in TMEM
+                        uint32_t st[16];
                         tc_wait_st();
-                        tmem_ld32(p_tmem, q0);
+                        tmem_ld16(p_tmem + 16 * qq, st);
                         tc_wait_ld();
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) {
+                        for (int i = 0; i < 16; ++i) {
                             float lo, hi;
                             if constexpr (kBF16) {
-                                const float2 f = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162 *>(&q0[i]));
+                                const float2 f = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162 *>(&st[i]));
                                 lo = f.x; hi = f.y;
                             } else {
-                                const float2 f = __half22float2(*reinterpret_cast<__half2 *>(&q0[i]));
+                                const float2 f = __half22float2(*reinterpret_cast<__half2 *>(&st[i]));
                                 lo = f.x; hi = f.y;
                             }
-                            q0[i] = pack2<kBF16>(lo * alpha, hi * alpha);
+                            st[i] = pack2<kBF16>(lo * alpha, hi * alpha);
                         }
-                        tmem_st32(p_tmem, q0);
+                        tmem_st16(p_tmem + 16 * qq, st);
                     }
                 }
                 const float neg_m = -m_ref;
-                float sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                uint32_t pk[32];
+                float sum0 = 0.0f, sum1 = 0.0f;
+                uint32_t pk[16];
 #pragma unroll
-                for (int i = 0; i < 64; i += 2) {
+                for (int i = 0; i < 32; i += 4) {
                     const float p0 = fast_exp2(fmaf(__uint_as_float(a[i]), scale_log2, neg_m));
                     const float p1 = fast_exp2(fmaf(__uint_as_float(a[i + 1]), scale_log2, neg_m));
-                    sum[(i >> 1) & 3] += p0 + p1;
+                    const float p2 = fast_exp2(fmaf(__uint_as_float(a[i + 2]), scale_log2, neg_m));
+                    const float p3 = fast_exp2(fmaf(__uint_as_float(a[i + 3]), scale_log2, neg_m));
+                    sum0 += p0 + p1;
+                    sum1 += p2 + p3;
                     pk[i >> 1] = pack2<kBF16>(p0, p1);
+                    pk[(i >> 1) + 1] = pack2<kBF16>(p2, p3);
                 }
-                l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
-                tmem_st32(p_tmem + h * 32, pk);  // 64 keys -> 32 columns of 16-bit pairs
+                l += sum0 + sum1;
+                if (!o_ready) {
+                    ok = mbar_wait(&sh.o_done[t], (j - 1) & 1, sh, status, kErrODone);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
+                    tc_fence_after();
+                    o_ready = true;
+                }
+                tmem_st16(p_tmem + 16 * q, pk);  // 32 keys -> 16 columns of 16-bit pairs
+                if (q < 3) tc_wait_ld();         // the next quarter has landed
+                if (q == 2) {
+                    tc_fence_before();
+                    mbar_arrive(&sh.s_empty[t]);  // all 128 scores are in registers: S may be overwritten
+                }
             }
             if (!ok) break;
+            if ((warp & 3) == 0) PROF_TRACE(t, j, 2);
             tc_wait_st();
             tc_fence_before();
             mbar_arrive(&sh.p_full[t]);
+            if ((warp & 3) == 0) PROF_TRACE(t, j, 3);
         }
 
+#ifdef COME_ATTN_PROFILE
+        prof_add(15, prof_loop_t0);
+#endif
         if (ok) {
             ok = mbar_wait(&sh.o_done[t], (n_kv - 1) & 1, sh, status, kErrODone);
             ok = __all_sync(0xffffffffu, ok);
@@ -603,6 +675,19 @@ int make_map(CUtensorMap *map, const void *base, int dtype, int64_t total, int H
 }
 
 }  // namespace
+
+#ifdef COME_ATTN_PROFILE
+extern "C" int come_debug_attn_timers(unsigned long long *host32, int clear) {
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(host32, g_attn_timers, sizeof(unsigned long long) * 32);
+    cudaMemcpyFromSymbol(host32 + 32, g_attn_trace, sizeof(g_attn_trace));
+    if (clear) {
+        unsigned long long z[32] = {0};
+        cudaMemcpyToSymbol(g_attn_timers, z, sizeof(z));
+    }
+    return 0;
+}
+#endif
 
 bool attn_sm100_supported(const AttnArgs &a) {
     if (a.D != kHeadDim) return false;
