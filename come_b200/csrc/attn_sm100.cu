@@ -298,6 +298,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     auto uses_slab = [&](int j) { return has_bias || (ragged_tail && j == n_kv - 1); };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (warp == 0) PROF_TRACE(2, 0, 0);  // kernel entry
 
     if (threadIdx.x == 0) {
         // an earlier CTA that gave up leaves the status word raised: later CTAs then skip their work
@@ -328,6 +329,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = sh.tmem_base;
+    if (warp == 0) PROF_TRACE(2, 0, 1);  // set-up done
     const bool dead = sh.abort_flag != 0;  // read after the barrier: uniform for the CTA
 
     if (dead) {
@@ -592,6 +594,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
 #ifdef COME_ATTN_PROFILE
         prof_add(15, prof_loop_t0);
 #endif
+        if (warp == 0) PROF_TRACE(2, 0, 2);  // key loop done
         if (ok) {
             ok = mbar_wait(&sh.o_done[t], (n_kv - 1) & 1, sh, status, kErrODone);
             ok = __all_sync(0xffffffffu, ok);
@@ -622,8 +625,10 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     }
 
     // ===== common exit ==========================================================================================
+    if (warp == 0) PROF_TRACE(2, 0, 3);  // output stored
     tc_fence_before();
     __syncthreads();
+    if (warp == 0) PROF_TRACE(2, 1, 0);  // all roles done
     if (sh.abort_flag != 0) {
         // give loads that may still be in flight time to land before the shared memory is released
         for (int i = 0; i < 64; ++i) __nanosleep(1000);
