@@ -392,6 +392,49 @@ extern "C" int come_merge_plan(const uint8_t *mask_dev, int64_t frames, const co
     return check_launch("come_merge_plan");
 }
 
+// ---- allocation-free plan --------------------------------------------------------------------------------------
+// Scratch of come_merge_plan_static: one packed frame length per frame.  A __device__ array is part of the
+// loaded module, so every GPU that loads the library carries these 16 KiB until the process exits.
+static __device__ __align__(256) int g_plan_scratch[COME_MERGE_PLAN_STATIC_MAX_FRAMES];
+
+// Device address of g_plan_scratch on the current device.  In host code the array's name is only a handle; the
+// address a kernel can use has to be asked for, once per device, with that device current.
+static int *plan_scratch_dev() {
+    static int *cached[64];
+    static std::mutex mu;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= 64) {
+        set_error("cudaGetDevice failed or device index out of range: %s", cudaGetErrorString(e));
+        return nullptr;
+    }
+    std::lock_guard<std::mutex> lock(mu);
+    if (!cached[dev]) {
+        int *p = nullptr;
+        e = cudaGetSymbolAddress((void **)&p, g_plan_scratch);
+        if (e != cudaSuccess || p == nullptr) {
+            set_error("cudaGetSymbolAddress(plan scratch) failed: %s", cudaGetErrorString(e));
+            return nullptr;
+        }
+        cached[dev] = p;
+    }
+    return cached[dev];
+}
+
+extern "C" int come_merge_plan_static(const uint8_t *mask_dev, int64_t frames, const come_layout_t *layout,
+                                      int32_t *group_prefix_dev, int32_t *offsets_dev, int64_t *rev_id_dev,
+                                      float *weight_dev, int32_t *seg_max_dev, void *stream) {
+    COME_REQUIRE(frames <= COME_MERGE_PLAN_STATIC_MAX_FRAMES,
+                 "come_merge_plan_static handles at most %d frames per call, got %lld; use come_merge_plan with a "
+                 "caller-provided workspace for more",
+                 COME_MERGE_PLAN_STATIC_MAX_FRAMES, (long long)frames);
+    int *scratch = plan_scratch_dev();
+    if (!scratch) return COME_ERR_CUDA;
+    // Every entry of the scratch that pass 2 reads is written by pass 1 of the same call: nothing to clear.
+    return come_merge_plan(mask_dev, frames, layout, group_prefix_dev, offsets_dev, rev_id_dev, weight_dev, seg_max_dev,
+                           scratch, sizeof(int) * COME_MERGE_PLAN_STATIC_MAX_FRAMES, stream);
+}
+
 template <typename T>
 static int launch_merge(const void *tokens, int64_t frames, int64_t C, const FrameLayout &L, const uint8_t *mask,
                         const int32_t *gp, const int32_t *off, void *out, cudaStream_t st) {

@@ -97,6 +97,28 @@ int come_merge_plan(const uint8_t *mask_dev, int64_t frames, const come_layout_t
                     int32_t *seg_max_dev, void *workspace_dev, size_t workspace_bytes, void *stream);
 
 /*
+ * Same plan, for callers that must not allocate device memory and have no workspace to hand over.
+ * No counterpart in the reference (its extension allocates freely through the PyTorch allocator).
+ *
+ * Who needs it: an inference-engine plugin whose enqueue hook runs after the engine has frozen its memory plan,
+ * a real-time loop that forbids allocation once it is running, or a host that only owns the tensors it was given.
+ * Such a caller still passes every input and output buffer; only the scratch (one int per frame) comes from a
+ * fixed array inside the library, so every GPU that loads the library holds COME_MERGE_PLAN_STATIC_MAX_FRAMES ints
+ * (16 KiB) for the life of the process.  The function calls no cudaMalloc / cudaFree or other allocating routine.
+ *
+ *   - frames above COME_MERGE_PLAN_STATIC_MAX_FRAMES are refused with COME_ERR_ARG and a message;
+ *   - the first call on a device looks up the array's device address (cudaGetSymbolAddress, once per device, with
+ *     that device current); make that first call before starting any stream capture;
+ *   - all calls on a device share the one array, which keeps the previous call's contents (each call overwrites
+ *     the part it reads, nothing relies on zeros); two calls whose kernels overlap on the GPU -- different streams
+ *     without an ordering between them -- race on it and produce garbage.  Order them, or use come_merge_plan.
+ */
+#define COME_MERGE_PLAN_STATIC_MAX_FRAMES 4096
+int come_merge_plan_static(const uint8_t *mask_dev, int64_t frames, const come_layout_t *layout,
+                           int32_t *group_prefix_dev, int32_t *offsets_dev, int64_t *rev_id_dev, float *weight_dev,
+                           int32_t *seg_max_dev, void *stream);
+
+/*
  * Merge data movement: packed rows from the token grid.
  * Replaces token_merge_scatter_kernel{_vec4,} + token_merge_special_kernel
  * (src/cuda_extension/co_me/src/kernel_token_merge.cu:50-191) and, for a 2-D layout, the gather pass of
