@@ -3,8 +3,8 @@
 //
 // One CTA owns up to two 128-row query tiles of one (segment, head) and walks the segment's keys 128 at a time.
 //   warps 0-3 / 4-7 : softmax group of query tile 0 / 1.  Thread r owns score row r (TMEM lane r).  Per key tile it
-//                     reads the scores 32 columns at a time (the next TMEM load in flight behind the current
-//                     quarter's arithmetic), tracks the row max with 3-input max, computes
+//                     pulls the 128 scores into registers (S is free for the next Q K^T at once), then works 32
+//                     columns at a time: row max with 3-input max,
 //                     p = exp2(s * scale*log2e - m) with one FFMA + one MUFU per score, writes p back to TMEM as
 //                     16-bit pairs (the A operand of P V) and rescales the accumulator only when the running max
 //                     grew by more than 2^8 (exact: the final normalisation uses the same reference max).
@@ -91,7 +91,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
 // slot = bit index of the wait's error code (+16 for the second softmax group); slot 15 / 31 = softmax loop total.
 #ifdef COME_ATTN_PROFILE
 __device__ unsigned long long g_attn_timers[32];
-__device__ long long g_attn_trace[4][16][4];  // [role: wg0, wg1, mma t0, mma t1][step][event]
+__device__ long long g_attn_trace[4][16][8];  // [role: wg0, wg1, mma t0, mma t1][step][event]
 #define PROF_TRACE(role, step, ev)                                                                      \
     do {                                                                                                \
         if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (threadIdx.x & 31) == 0 && (step) < 16) \
@@ -329,6 +329,9 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = sh.tmem_base;
+    // Register budget: the producer / issuer warpgroup needs few registers and hands its share to the two softmax
+    // warpgroups, which keep a whole 128-score row live (8 x 32 x 224 + 4 x 32 x 56 = 64512 <= 65536).
+    // (each role branch below starts with its setmaxnreg; the whole of warpgroup 2 = warps 8-11 must release.)
     if (warp == 0) PROF_TRACE(2, 0, 1);  // set-up done
     const bool dead = sh.abort_flag != 0;  // read after the barrier: uniform for the CTA
 
@@ -336,6 +339,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         // fall through to the common exit
     } else if (warp == 8) {
         // ===== producer =====================================================================================
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
         const T *bias = reinterpret_cast<const T *>(bias_ptr);
         bool ok = true;
         if (lane == 0) {
@@ -396,6 +400,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         }
     } else if (warp == 9 || warp == 10) {
         // ===== MMA issuer of query tile t (all lanes run the loop, one elected lane issues) ================
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
         const int t = warp - 9;
         if (t < n_mt) {
             constexpr uint32_t idesc_qk = make_idesc(kBF16, kBlockM, kBlockN, false);
@@ -465,8 +470,11 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             }
         }
         __syncwarp();
+    } else if (warp == 11) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");  // spare warp of the producer / issuer warpgroup
     } else if (warp < 4 * n_mt) {
         // ===== softmax group of query tile t ================================================================
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
         const int t = warp >> 2;
         const int r = threadIdx.x & 127;                          // row inside the tile == TMEM lane
         const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
@@ -487,16 +495,21 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             if (!ok) break;
             tc_fence_after();
             if ((warp & 3) == 0) PROF_TRACE(t, j, 1);
-            // The 128 scores of the row are processed 32 columns at a time; the TMEM load of the next quarter is in
-            // flight while the current one is turned into probabilities.
-            uint32_t buf[2][32];
-            tmem_ld32(s_tmem, buf[0]);
+            // The whole 128-score row is pulled into registers at once, which frees S for the next Q K^T right away;
+            // the row is then turned into probabilities 32 columns at a time.
+            uint32_t srow[4][32];
+            tmem_ld32(s_tmem + 0, srow[0]);
+            tmem_ld32(s_tmem + 32, srow[1]);
+            tmem_ld32(s_tmem + 64, srow[2]);
+            tmem_ld32(s_tmem + 96, srow[3]);
             tc_wait_ld();
+            if ((warp & 3) == 0) PROF_TRACE(t, j, 4);
+            tc_fence_before();
+            mbar_arrive(&sh.s_empty[t]);
             bool o_ready = (j == 0);  // P V of the previous key tile complete: O stable, P buffer free
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
-                uint32_t(&a)[32] = buf[q & 1];
-                if (q < 3) tmem_ld32(s_tmem + 32 * (q + 1), buf[(q + 1) & 1]);
+                uint32_t(&a)[32] = srow[q];
                 // row max of this quarter: two independent 3-input chains
                 float m0 = __uint_as_float(a[0]), m1 = __uint_as_float(a[15]);
 #pragma unroll
@@ -522,7 +535,6 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                             o_ready = true;
                         }
                         uint32_t o[2][32];
-                        tc_wait_ld();  // (also completes the prefetch; the rare path may serialise)
                         tmem_ld32(o_tmem + 0, o[0]);
                         tmem_ld32(o_tmem + 32, o[1]);
                         tc_wait_ld();
@@ -577,11 +589,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     o_ready = true;
                 }
                 tmem_st16(p_tmem + 16 * q, pk);  // 32 keys -> 16 columns of 16-bit pairs
-                if (q < 3) tc_wait_ld();         // the next quarter has landed
-                if (q == 2) {
-                    tc_fence_before();
-                    mbar_arrive(&sh.s_empty[t]);  // all 128 scores are in registers: S may be overwritten
-                }
+                if ((warp & 3) == 0 && q < 3) PROF_TRACE(t, j, 5 + q);
             }
             if (!ok) break;
             if ((warp & 3) == 0) PROF_TRACE(t, j, 2);
