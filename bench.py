@@ -321,6 +321,88 @@ def run_gpu(args):
         dist.destroy_process_group()
 
 
+def run_frames100(args):
+    """ONE scene of 100 frames (137,400 tokens before merging) sharded by frame over the ranks.  Frame layers are
+    local; a global layer all-gathers the merged K/V rows over NCCL and attends the local query rows to all keys
+    (strong scaling: the scene is fixed, more GPUs shorten it)."""
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    from come_b200 import _lib
+    from come_b200.chain import ShardedOpChain
+    frames = 100
+    pk = peaks()
+    chain = ShardedOpChain(frames, None, START, GRID, GRID, WIN, WIN, 0.5, HEADS, HDIM, LAYERS)
+    g = torch.Generator(device="cpu").manual_seed(4321)
+    conf = torch.rand((1, frames * GRID * GRID), generator=g).bfloat16().to(dev)  # replicated
+    gp, lp = chain.build_plans(conf)
+    n_local = chain.f_hi - chain.f_lo
+    gl = torch.Generator(device=dev).manual_seed(100 + rank)
+    x = torch.randn((n_local, N_TOK, CH), device=dev, generator=gl).bfloat16()
+    q = torch.randn((lp.total, HEADS, HDIM), device=dev, generator=gl).bfloat16()
+    kv = torch.randn((lp.total, 2, HEADS, HDIM), device=dev, generator=gl).bfloat16()
+    ev = lambda: torch.cuda.Event(enable_timing=True)  # noqa: E731
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def step():
+        chain.build_plans(conf)
+        out = None
+        for kind in LAYERS:
+            out = chain.layer(gp, lp, x, q, kv, kind)
+        return out
+
+    for _ in range(min(args.warmup, 3)):
+        step()
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    s, e = ev(), ev()
+    s.record()
+    for _ in range(args.steps):
+        step()
+    e.record()
+    barrier()
+    ms = torch.tensor([s.elapsed_time(e)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    clocks = sampler.stop() if rank == 0 else None
+    assert _lib.device_status(clear=False) == 0
+    if rank == 0:
+        per_scene = ms.item() / args.steps
+        P = gp.total
+        seg = (gp.offset[1:] - gp.offset[:-1]).tolist()
+        flops = 24 * (sum(4.0 * L * L * HDIM * HEADS for L in seg) + 4.0 * P * P * HDIM * HEADS)
+        kv_bytes = P * 2 * HEADS * HDIM * 2
+        line = {
+            "metric": "come_vggt_hot_path_ms_per_scene_100f", "value": per_scene, "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_scene, "higher_is_better": False,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic (seeded)",
+            "config": {"workload": workload_name(frames), "merged_tokens": P, "frames_per_s": frames / per_scene * 1e3,
+                       "parallelism": f"frames sharded over {world} GPU(s); frame layers local, global layers all-gather "
+                                      f"{kv_bytes / 1e6:.0f} MB of merged K/V per layer over NCCL",
+                       "l2": "inputs larger than L2 (merged K/V of one layer alone is > 126 MB)"},
+            "attention_tflops_aggregate": flops / (per_scene * 1e-3) / 1e12,
+            "attention_frac_of_bf16_peak_per_gpu": flops / (per_scene * 1e-3) / 1e12 / world / pk["tflops"],
+            "gpu_launches": (3 + 2 * 3 + 3 * len(LAYERS)) * args.steps, "clocks": clocks,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def micro(torch, dev, pk):
     """Kernel-level numbers on inputs larger than L2: 100-frame fp32 merge / unmerge (GB/s) and the 64-segment
     ragged biased-attention sweep (TFLOP/s)."""
@@ -441,6 +523,9 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="come_b200", choices=["come_b200", "reference"])
+    ap.add_argument("--workload", default="scenes8", choices=["scenes8", "frames100"],
+                    help="scenes8: one independent 8-frame scene per GPU (default); frames100: ONE 100-frame scene whose "
+                         "frames are sharded over the GPUs, global attention over all-gathered K/V")
     ap.add_argument("--no-micro", action="store_true", help="skip the kernel-level sweep")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     args = ap.parse_args()
@@ -448,6 +533,9 @@ def main():
         run_only(args)
     elif args.impl == "reference":
         run_reference(args)
+    elif args.workload == "frames100":
+        args.warmup = max(args.warmup, 3)
+        run_frames100(args)
     else:
         args.warmup = max(args.warmup, 3)
         run_gpu(args)

@@ -18,7 +18,7 @@ COME_SCOPE_BATCH, COME_SCOPE_FRAME = 0, 1
 EXPORTS = (
     "come_version", "come_last_error", "come_layout_info", "come_select_windows",
     "come_merge_plan_workspace_bytes", "come_merge_plan", "come_merge_plan_static", "come_merge", "come_unmerge",
-    "come_attn_varlen_fwd", "come_device_status",
+    "come_attn_varlen_fwd", "come_attn_varlen_fwd_rows", "come_device_status",
 )
 
 
@@ -62,6 +62,8 @@ def lib() -> C.CDLL:
     l.come_unmerge.argtypes = [vp, vp, i64, i64, i32, vp, vp]
     l.come_attn_varlen_fwd.argtypes = [vp, vp, vp, i32, i64, i32, i32, i64, i64, i64, vp, vp, i32, i32, f32, vp, i64,
                                        vp, i32, vp]
+    l.come_attn_varlen_fwd_rows.argtypes = [vp, vp, vp, i32, i64, i64, i64, i32, i32, i64, i64, i64, vp, vp, i32, i32, f32, vp,
+                                            i64, vp, i32, vp]
     l.come_device_status.argtypes = [C.POINTER(C.c_uint32), i32]
     for name in EXPORTS:
         fn = getattr(l, name)

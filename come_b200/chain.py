@@ -15,7 +15,7 @@ from . import _lib
 from .flash_attn import flash_attn_varlen_qkvpacked_func_w_perkey_bias
 from .token_merger import MergePlan, select_windows
 
-__all__ = ["CoMeOpChain"]
+__all__ = ["CoMeOpChain", "ShardedOpChain"]
 
 
 class CoMeOpChain:
@@ -69,3 +69,64 @@ class CoMeOpChain:
         for kind in self.layer_kinds:
             out = self.layer(plan, x, qkv, kind)
         return out
+
+
+class ShardedOpChain:
+    """The operator chain of ONE scene sharded over the ranks of a process group by frame.
+
+    Every rank owns a contiguous range of frames: its selection, merge, frame attention and unmerge are local.  A
+    global layer all-gathers the merged key / value rows (``[P_local, 2, heads, head_dim]`` per rank, nothing else)
+    and attends the local query rows to all of them with the row-range attention kernel.  The confidence of all
+    frames is replicated (a few hundred KB), so every rank derives the same global packed offsets without a collective.
+    """
+
+    def __init__(self, frames_total: int, group=None, start_index: int = 5, grid_h: int = 37, grid_w: int = 37,
+                 group_h: int = 3, group_w: int = 3, threshold: float = 0.5, num_heads: int = 16, head_dim: int = 64,
+                 layer_kinds: Optional[Sequence[str]] = None):
+        import torch.distributed as dist
+
+        from .dist import shard_range
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.frames_total = frames_total
+        self.f_lo, self.f_hi = shard_range(frames_total, self.world, self.rank)
+        self.layout = _lib.Layout.two_d(start_index, grid_h, grid_w, group_h, group_w)
+        self.grid = (grid_h, grid_w, group_h, group_w)
+        self.threshold = threshold
+        self.num_heads, self.head_dim = num_heads, head_dim
+        self.scale = head_dim ** -0.5
+        self.layer_kinds = list(layer_kinds) if layer_kinds is not None else ["frame", "global"] * 24
+
+    def build_plans(self, confidence_all: torch.Tensor):
+        """``confidence_all [1, frames_total * H * W]`` (replicated) -> ``(global_plan, local_plan)``."""
+        from .dist import rows_per_rank
+        H, W, gh, gw = self.grid
+        mask_all = select_windows(confidence_all, 1, self.frames_total, H, W, gh, gw, self.threshold, "pairwise-rank", "frame")
+        global_plan = MergePlan(mask_all, self.layout)
+        local_plan = MergePlan(mask_all[self.f_lo:self.f_hi].contiguous(), self.layout)
+        offsets = global_plan.offset.tolist()
+        self.rows = rows_per_rank(offsets, self.world)
+        self.row_begin = int(offsets[self.f_lo])
+        assert self.rows[self.rank] == local_plan.total
+        self.cu_global = torch.tensor([0, global_plan.total], dtype=torch.int32, device=mask_all.device)
+        return global_plan, local_plan
+
+    def layer(self, global_plan: MergePlan, local_plan: MergePlan, x_local: torch.Tensor, q_local: torch.Tensor,
+              kv_local: torch.Tensor, kind: str) -> torch.Tensor:
+        """``x_local [frames_local, N, C]``; ``q_local [P_local, heads, head_dim]`` and ``kv_local [P_local, 2, heads,
+        head_dim]`` stand in for the projections of the merged local tokens."""
+        from .dist import gather_rows
+        from .flash_attn_fwd_cuda import varlen_fwd_rows
+        merged = local_plan.merge(x_local)
+        dtype = q_local.dtype
+        if kind == "frame":
+            out, _ = varlen_fwd_rows(q_local, kv_local[:, 0], kv_local[:, 1], local_plan.cu_seqlens(1), local_plan.max_seqlen,
+                                     local_plan.perkey_bias(dtype), self.scale, 0)
+        else:
+            kv_all = gather_rows(kv_local, self.rows, self.group) if self.world > 1 else kv_local
+            out, _ = varlen_fwd_rows(q_local, kv_all[:, 0], kv_all[:, 1], self.cu_global, global_plan.total,
+                                     global_plan.perkey_bias(dtype), self.scale, self.row_begin)
+        del merged
+        y = out.reshape(local_plan.total, self.num_heads * self.head_dim)
+        return local_plan.split(y).reshape(self.f_hi - self.f_lo, local_plan.tokens_per_frame, -1)

@@ -14,15 +14,15 @@ template <typename T>
 __global__ void __launch_bounds__(kGenericWarps * 32)
 attn_generic_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *__restrict__ v, int64_t q_rs,
                     int64_t k_rs, int64_t v_rs, const T *__restrict__ bias, const int *__restrict__ cu, int H, int D,
-                    float scale, T *__restrict__ out, int64_t o_rs, float *__restrict__ lse, int64_t total) {
+                    float scale, T *__restrict__ out, int64_t o_rs, float *__restrict__ lse, int q_begin, int q_end) {
     __shared__ float s_q[kGenericWarps][kGenericMaxD];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int seg = blockIdx.y, h = blockIdx.z;
     const int s0 = cu[seg], s1 = cu[seg + 1];
-    const int row = s0 + blockIdx.x * kGenericWarps + warp;
-    if (row >= s1) return;  // whole warp leaves together
+    const int row = max(s0, q_begin) + blockIdx.x * kGenericWarps + warp;  // global row; q / out / lse hold rows [q_begin, q_end)
+    if (row >= min(s1, q_end)) return;  // whole warp leaves together
 
-    const T *qrow = q + (int64_t)row * q_rs + (int64_t)h * D;
+    const T *qrow = q + (int64_t)(row - q_begin) * q_rs + (int64_t)h * D;
     for (int d = lane; d < D; d += 32) s_q[warp][d] = Elem<T>::to_f32(qrow[d]);
     __syncwarp();
 
@@ -65,22 +65,23 @@ attn_generic_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *_
         m = m_new;
     }
     const float inv = 1.0f / l;
-    T *orow = out + (int64_t)row * o_rs + (int64_t)h * D;
+    T *orow = out + (int64_t)(row - q_begin) * o_rs + (int64_t)h * D;
 #pragma unroll
     for (int i = 0; i < kGenericMaxD / 32; ++i) {
         const int d = lane + 32 * i;
         if (d < D) orow[d] = Elem<T>::from_f32(acc[i] * inv);
     }
-    if (lse && lane == 0) lse[(int64_t)h * total + row] = m + logf(l);
+    if (lse && lane == 0) lse[(int64_t)h * (q_end - q_begin) + (row - q_begin)] = m + logf(l);
 }
 
 template <typename T>
 static int launch_generic(const void *q, const void *k, const void *v, int64_t q_rs, int64_t k_rs, int64_t v_rs,
                           const void *bias, const int *cu, int nseg, int max_seqlen, int H, int D, float scale, void *out,
-                          int64_t o_rs, float *lse, int64_t total, cudaStream_t st) {
-    dim3 grid((max_seqlen + kGenericWarps - 1) / kGenericWarps, nseg, H);
+                          int64_t o_rs, float *lse, int64_t q_begin, int64_t q_end, cudaStream_t st) {
+    const int64_t span = max_seqlen < q_end - q_begin ? max_seqlen : q_end - q_begin;
+    dim3 grid((unsigned)((span + kGenericWarps - 1) / kGenericWarps), nseg, H);
     attn_generic_kernel<T><<<grid, kGenericWarps * 32, 0, st>>>((const T *)q, (const T *)k, (const T *)v, q_rs, k_rs, v_rs,
-                                                                (const T *)bias, cu, H, D, scale, (T *)out, o_rs, lse, total);
+                                                                (const T *)bias, cu, H, D, scale, (T *)out, o_rs, lse, (int)q_begin, (int)q_end);
     return check_launch("come_attn_varlen_fwd (CUDA-core kernel)");
 }
 
@@ -88,14 +89,16 @@ static int launch_generic(const void *q, const void *k, const void *v, int64_t q
 
 using namespace come;
 
-extern "C" int come_attn_varlen_fwd(const void *q_dev, const void *k_dev, const void *v_dev, int dtype, int64_t total,
-                                    int num_heads, int head_dim, int64_t q_row_stride, int64_t k_row_stride,
-                                    int64_t v_row_stride, const void *bias_dev, const int32_t *cu_seqlens_dev,
-                                    int num_segments, int max_seqlen, float softmax_scale, void *out_dev,
-                                    int64_t out_row_stride, float *lse_dev, int backend, void *stream) {
+static int attn_dispatch(const void *q_dev, const void *k_dev, const void *v_dev, int dtype, int64_t total,
+                         int64_t q_begin, int64_t q_rows, int num_heads, int head_dim, int64_t q_row_stride,
+                         int64_t k_row_stride, int64_t v_row_stride, const void *bias_dev, const int32_t *cu_seqlens_dev,
+                         int num_segments, int max_seqlen, float softmax_scale, void *out_dev, int64_t out_row_stride,
+                         float *lse_dev, int backend, void *stream) {
     COME_REQUIRE(dtype == COME_F16 || dtype == COME_BF16, "FlashAttention only support fp16 and bf16 data type");
     COME_REQUIRE(num_segments > 0, "batch size must be positive");
     COME_REQUIRE(total >= 0 && num_heads > 0, "total must be >= 0 and num_heads > 0");
+    COME_REQUIRE(q_begin >= 0 && q_rows >= 0 && q_begin + q_rows <= total, "query rows [%lld, %lld) must lie inside [0, %lld)",
+                 (long long)q_begin, (long long)(q_begin + q_rows), (long long)total);
     COME_REQUIRE(head_dim > 0 && head_dim <= 256, "FlashAttention forward only supports head dimension at most 256");
     COME_REQUIRE(head_dim % 8 == 0, "query, key, value, and out_ must have a head_size that is a multiple of 8");
     COME_REQUIRE(max_seqlen >= 0, "max_seqlen must be >= 0");
@@ -104,27 +107,48 @@ extern "C" int come_attn_varlen_fwd(const void *q_dev, const void *k_dev, const 
     COME_REQUIRE(q_row_stride >= hd && k_row_stride >= hd && v_row_stride >= hd && out_row_stride >= hd,
                  "row strides must cover num_heads * head_dim elements");
     COME_REQUIRE(total < (1ll << 31), "total tokens must fit int32");
-    if (total == 0 || max_seqlen == 0) return COME_OK;
+    if (total == 0 || max_seqlen == 0 || q_rows == 0) return COME_OK;
     COME_REQUIRE(q_dev && k_dev && v_dev && out_dev && cu_seqlens_dev, "q / k / v / out / cu_seqlens must not be NULL");
     cudaStream_t st = (cudaStream_t)stream;
 
     AttnArgs a;
     a.q = q_dev; a.k = k_dev; a.v = v_dev; a.bias = bias_dev; a.cu = cu_seqlens_dev; a.out = out_dev; a.lse = lse_dev;
-    a.dtype = dtype; a.total = total; a.H = num_heads; a.D = head_dim;
+    a.dtype = dtype; a.total = total; a.q_begin = q_begin; a.q_end = q_begin + q_rows; a.H = num_heads; a.D = head_dim;
     a.q_rs = q_row_stride; a.k_rs = k_row_stride; a.v_rs = v_row_stride; a.o_rs = out_row_stride;
     a.nseg = num_segments; a.max_seqlen = max_seqlen; a.scale = softmax_scale;
 
     const bool tc_ok = attn_sm100_supported(a);
     if (backend == 2 && !tc_ok) {
-        set_error("tcgen05 attention needs head_dim 64, 16-byte aligned q/k/v and strides that are multiples of 8 elements");
+        set_error("tcgen05 attention needs head_dim 64, a positive scale, 16-byte aligned q/k/v/out and strides that are multiples of 8 elements");
         return COME_ERR_UNSUPPORTED;
     }
     if (tc_ok && backend != 1) return attn_sm100_launch(a, st);
     if (dtype == COME_F16)
         return launch_generic<__half>(q_dev, k_dev, v_dev, q_row_stride, k_row_stride, v_row_stride, bias_dev, cu_seqlens_dev,
                                       num_segments, max_seqlen, num_heads, head_dim, softmax_scale, out_dev, out_row_stride,
-                                      lse_dev, total, st);
+                                      lse_dev, a.q_begin, a.q_end, st);
     return launch_generic<__nv_bfloat16>(q_dev, k_dev, v_dev, q_row_stride, k_row_stride, v_row_stride, bias_dev,
                                          cu_seqlens_dev, num_segments, max_seqlen, num_heads, head_dim, softmax_scale,
-                                         out_dev, out_row_stride, lse_dev, total, st);
+                                         out_dev, out_row_stride, lse_dev, a.q_begin, a.q_end, st);
+}
+
+extern "C" int come_attn_varlen_fwd(const void *q_dev, const void *k_dev, const void *v_dev, int dtype, int64_t total,
+                                    int num_heads, int head_dim, int64_t q_row_stride, int64_t k_row_stride,
+                                    int64_t v_row_stride, const void *bias_dev, const int32_t *cu_seqlens_dev,
+                                    int num_segments, int max_seqlen, float softmax_scale, void *out_dev,
+                                    int64_t out_row_stride, float *lse_dev, int backend, void *stream) {
+    return attn_dispatch(q_dev, k_dev, v_dev, dtype, total, 0, total, num_heads, head_dim, q_row_stride, k_row_stride,
+                         v_row_stride, bias_dev, cu_seqlens_dev, num_segments, max_seqlen, softmax_scale, out_dev,
+                         out_row_stride, lse_dev, backend, stream);
+}
+
+extern "C" int come_attn_varlen_fwd_rows(const void *q_dev, const void *k_dev, const void *v_dev, int dtype, int64_t total,
+                                         int64_t q_row_begin, int64_t q_rows, int num_heads, int head_dim,
+                                         int64_t q_row_stride, int64_t k_row_stride, int64_t v_row_stride,
+                                         const void *bias_dev, const int32_t *cu_seqlens_dev, int num_segments,
+                                         int max_seqlen, float softmax_scale, void *out_dev, int64_t out_row_stride,
+                                         float *lse_dev, int backend, void *stream) {
+    return attn_dispatch(q_dev, k_dev, v_dev, dtype, total, q_row_begin, q_rows, num_heads, head_dim, q_row_stride,
+                         k_row_stride, v_row_stride, bias_dev, cu_seqlens_dev, num_segments, max_seqlen, softmax_scale,
+                         out_dev, out_row_stride, lse_dev, backend, stream);
 }

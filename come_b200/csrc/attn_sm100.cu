@@ -279,7 +279,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                       const __grid_constant__ CUtensorMap map_v, const void *__restrict__ bias_ptr,
                       const int *__restrict__ cu, float scale_log2, float inv_scale, void *__restrict__ out_ptr, int64_t o_rs,
-                      float *__restrict__ lse, int64_t total, unsigned int *__restrict__ status) {
+                      float *__restrict__ lse, int q_begin, int q_end, unsigned int *__restrict__ status) {
     using T = typename std::conditional<kBF16, __nv_bfloat16, __half>::type;
     extern __shared__ uint8_t smem_raw[];
     SharedStorage &sh = *reinterpret_cast<SharedStorage *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -287,10 +287,12 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     const int seg = blockIdx.y, head = blockIdx.z;
     const int s0 = cu[seg], s1 = cu[seg + 1];
     const int seg_len = s1 - s0;
-    const int q_off = blockIdx.x * (2 * kBlockM);
-    if (q_off >= seg_len) return;  // uniform for the CTA, nothing allocated yet
-    const int q_row0 = s0 + q_off;
-    const int n_mt = (q_off + kBlockM < seg_len) ? 2 : 1;  // query tiles with at least one valid row
+    // Query rows of this launch: global rows [q_begin, q_end) (the whole packed sequence for plain self-attention; a
+    // slice when the query rows are sharded).  q / out / lse are indexed by (global row - q_begin); k / v by global row.
+    const int q_lo = max(s0, q_begin), q_hi = min(s1, q_end);
+    const int q_row0 = q_lo + blockIdx.x * (2 * kBlockM);
+    if (q_row0 >= q_hi) return;  // uniform for the CTA, nothing allocated yet
+    const int n_mt = (q_row0 + kBlockM < q_hi) ? 2 : 1;  // query tiles with at least one valid row
     const int n_kv = (seg_len + kBlockN - 1) / kBlockN;
     const bool has_bias = bias_ptr != nullptr;
     const bool ragged_tail = (seg_len % kBlockN) != 0;
@@ -345,7 +347,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         if (lane == 0) {
             for (int t = 0; t < n_mt; ++t) {
                 mbar_arrive_expect_tx(&sh.q_full[t], kTileBytes);
-                tma_load_3d(sh.q[t], &map_q, 0, head, q_row0 + t * kBlockM, &sh.q_full[t]);
+                tma_load_3d(sh.q[t], &map_q, 0, head, q_row0 - q_begin + t * kBlockM, &sh.q_full[t]);
             }
         }
         {   // the constant A side of the bias step: columns 0 and 1 are 1.0.  Both slabs are bfloat16 whatever the
@@ -613,9 +615,9 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             tmem_ld32(o_tmem + 0, o[0]);
             tmem_ld32(o_tmem + 32, o[1]);
             tc_wait_ld();
-            if (row < s1) {
+            if (row < q_hi) {
                 const float inv = 1.0f / l;
-                uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<T *>(out_ptr) + (int64_t)row * o_rs + (int64_t)head * kHeadDim);
+                uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<T *>(out_ptr) + (int64_t)(row - q_begin) * o_rs + (int64_t)head * kHeadDim);
 #pragma unroll
                 for (int c = 0; c < 2; ++c)
 #pragma unroll
@@ -627,7 +629,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                         v.w = pack2<kBF16>(__uint_as_float(o[c][i + 6]) * inv, __uint_as_float(o[c][i + 7]) * inv);
                         dst[(c * 32 + i) / 8] = v;
                     }
-                if (lse) lse[(int64_t)head * total + row] = (m_ref + log2f(l)) * kLn2;
+                if (lse) lse[(int64_t)head * (q_end - q_begin) + (row - q_begin)] = (m_ref + log2f(l)) * kLn2;
             }
         }
     }
@@ -718,21 +720,23 @@ int attn_sm100_launch(const AttnArgs &a, cudaStream_t stream) {
     if (!status) return COME_ERR_CUDA;
     CUtensorMap mq, mk, mv;
     int rc;
-    if ((rc = make_map(&mq, a.q, a.dtype, a.total, a.H, a.q_rs)) != COME_OK) return rc;
+    if ((rc = make_map(&mq, a.q, a.dtype, a.q_end - a.q_begin, a.H, a.q_rs)) != COME_OK) return rc;
     if ((rc = make_map(&mk, a.k, a.dtype, a.total, a.H, a.k_rs)) != COME_OK) return rc;
     if ((rc = make_map(&mv, a.v, a.dtype, a.total, a.H, a.v_rs)) != COME_OK) return rc;
     const size_t smem = sizeof(SharedStorage) + 1024;
-    dim3 grid((a.max_seqlen + 2 * kBlockM - 1) / (2 * kBlockM), a.nseg, a.H);
+    const int64_t q_rows = a.q_end - a.q_begin;
+    const int64_t span = a.max_seqlen < q_rows ? a.max_seqlen : q_rows;  // most query rows any segment can own here
+    dim3 grid((unsigned)((span + 2 * kBlockM - 1) / (2 * kBlockM)), a.nseg, a.H);
     const float scale_log2 = a.scale * kLog2e;
     const float inv_scale = 1.0f / a.scale;
     if (a.dtype == COME_BF16) {
         COME_CUDA(cudaFuncSetAttribute(attn_fwd_sm100_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         attn_fwd_sm100_kernel<true><<<grid, kThreads, smem, stream>>>(mq, mk, mv, a.bias, a.cu, scale_log2, inv_scale, a.out, a.o_rs, a.lse,
-                                                                     a.total, status);
+                                                                     (int)a.q_begin, (int)a.q_end, status);
     } else {
         COME_CUDA(cudaFuncSetAttribute(attn_fwd_sm100_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         attn_fwd_sm100_kernel<false><<<grid, kThreads, smem, stream>>>(mq, mk, mv, a.bias, a.cu, scale_log2, inv_scale, a.out, a.o_rs, a.lse,
-                                                                      a.total, status);
+                                                                      (int)a.q_begin, (int)a.q_end, status);
     }
     return check_launch("come_attn_varlen_fwd (tcgen05 kernel)");
 }

@@ -10,7 +10,8 @@ struct AttnArgs {
     void *out;
     float *lse;
     int dtype;
-    int64_t total;
+    int64_t total;            // rows of k / v (all packed tokens)
+    int64_t q_begin, q_end;   // global rows that q / out / lse cover: [q_begin, q_end)
     int H, D;
     int64_t q_rs, k_rs, v_rs, o_rs;  // row strides in elements
     int nseg, max_seqlen;

@@ -13,7 +13,7 @@ import torch
 from . import _lib
 from ._torch_util import dtype_code, ptr, stream_ptr
 
-__all__ = ["varlen_fwd", "varlen_fwd_w_perkey_bias"]
+__all__ = ["varlen_fwd", "varlen_fwd_w_perkey_bias", "varlen_fwd_rows"]
 
 BACKEND_AUTO, BACKEND_CUDA_CORE, BACKEND_TCGEN05 = 0, 1, 2
 _backend = BACKEND_AUTO
@@ -156,3 +156,41 @@ def varlen_fwd_w_perkey_bias(q, k, v, out_, cu_seqlens_q, cu_seqlens_k, seqused_
     return _impl(q, k, v, out_, cu_seqlens_q, cu_seqlens_k, seqused_k, leftpad_k, block_table, alibi_slopes,
                  perkey_bias, max_seqlen_q, max_seqlen_k, p_dropout, softmax_scale, zero_tensors, is_causal,
                  window_size_left, window_size_right, softcap, return_softmax, gen_)
+
+
+def varlen_fwd_rows(q_rows, k, v, cu_seqlens, max_seqlen, perkey_bias, softmax_scale, row_begin, out_=None):
+    """Attention of a slice of the query rows against all keys / values (no counterpart in the reference: the
+    per-GPU piece of global attention sharded by query rows).
+
+    ``q_rows`` ``[rows, H, D]`` holds the global packed rows ``[row_begin, row_begin + rows)``; ``k`` / ``v``
+    ``[total, H, D]``, ``perkey_bias`` ``[total]`` or ``None`` and ``cu_seqlens`` describe all packed tokens.
+    Returns ``[out [rows, H, D], softmax_lse [H, rows]]``.
+    """
+    if q_rows.dtype not in (torch.float16, torch.bfloat16):
+        raise RuntimeError("FlashAttention only support fp16 and bf16 data type")
+    if k.dtype != q_rows.dtype or v.dtype != q_rows.dtype:
+        raise RuntimeError("query, key and value must have the same dtype")
+    if cu_seqlens.dtype != torch.int32 or not cu_seqlens.is_contiguous():
+        raise RuntimeError("cu_seqlens must be a contiguous int32 tensor")
+    rows, num_heads, head_size = q_rows.shape
+    total = k.shape[0]
+    if tuple(k.shape) != (total, num_heads, head_size) or tuple(v.shape) != (total, num_heads, head_size):
+        raise RuntimeError("k / v must have shape (total, num_heads, head_size)")
+    if row_begin < 0 or row_begin + rows > total:
+        raise RuntimeError(f"query rows [{row_begin}, {row_begin + rows}) must lie inside [0, {total})")
+    for t in (q_rows, k, v):
+        if not t.is_cuda:
+            raise RuntimeError("q / k / v must be on CUDA")
+        if t.stride(-1) != 1 or t.stride(1) != head_size:
+            raise RuntimeError("q / k / v must have adjacent heads and a contiguous last dimension")
+    if perkey_bias is not None and (perkey_bias.dtype != q_rows.dtype or tuple(perkey_bias.shape) != (total,)
+                                    or not perkey_bias.is_contiguous()):
+        raise RuntimeError("perkey_bias must be a contiguous (total,) tensor of the q/k/v dtype")
+    out = out_ if out_ is not None else torch.empty((rows, num_heads, head_size), dtype=q_rows.dtype, device=q_rows.device)
+    lse = torch.empty((num_heads, rows), dtype=torch.float32, device=q_rows.device)
+    with torch.cuda.device(q_rows.device):
+        _lib.check(_lib.lib().come_attn_varlen_fwd_rows(
+            ptr(q_rows), ptr(k), ptr(v), dtype_code(q_rows.dtype), total, int(row_begin), rows, num_heads, head_size,
+            q_rows.stride(0), k.stride(0), v.stride(0), ptr(perkey_bias), ptr(cu_seqlens), cu_seqlens.numel() - 1,
+            int(max_seqlen), float(softmax_scale), ptr(out), out.stride(0), ptr(lse), _backend, stream_ptr(q_rows.device)))
+    return [out, lse]

@@ -160,6 +160,19 @@ int come_attn_varlen_fwd(const void *q_dev, const void *k_dev, const void *v_dev
                          int64_t out_row_stride, float *lse_dev, int backend, void *stream);
 
 /*
+ * The same attention for a slice of the query rows: q / out / lse hold only the global rows
+ * [q_row_begin, q_row_begin + q_rows) (lse is [num_heads, q_rows]), k / v / bias / cu_seqlens still describe all
+ * `total` packed tokens.  This is the per-GPU piece of global attention sharded by query rows: every GPU attends
+ * its own rows to the all-gathered keys and values.  No counterpart in the reference (single GPU only); with
+ * q_row_begin = 0 and q_rows = total it is come_attn_varlen_fwd.
+ */
+int come_attn_varlen_fwd_rows(const void *q_dev, const void *k_dev, const void *v_dev, int dtype, int64_t total,
+                              int64_t q_row_begin, int64_t q_rows, int num_heads, int head_dim, int64_t q_row_stride,
+                              int64_t k_row_stride, int64_t v_row_stride, const void *bias_dev,
+                              const int32_t *cu_seqlens_dev, int num_segments, int max_seqlen, float softmax_scale,
+                              void *out_dev, int64_t out_row_stride, float *lse_dev, int backend, void *stream);
+
+/*
  * Device status word: kernels that wait on hardware barriers give up after a bounded number of polls and
  * record a non-zero code here instead of hanging.  Reads it back (synchronises the device) and optionally
  * clears it.  Returns COME_OK with *value == 0 when no kernel reported a problem.

@@ -208,3 +208,29 @@ def test_infer_max_seqlen():
     from come_b200.flash_attn import infer_flash_attn_varlen_max_seqlen
     cu = torch.tensor([0, 5, 12, 14], dtype=torch.int32, device="cuda")
     assert infer_flash_attn_varlen_max_seqlen(cu) == 7
+
+
+@pytest.mark.parametrize("which", ["cuda-core", "tcgen05"])
+@pytest.mark.parametrize("seq_lens,cuts", [([3000], [0, 1111, 1999, 3000]), ([700, 300, 900], [0, 650, 1000, 1900])])
+def test_query_row_slices_match_full_attention(backend, which, seq_lens, cuts):
+    """Global attention sharded by query rows: attending every slice of the rows to all keys / values must give the
+    same rows as one full launch (the per-GPU piece of the multi-GPU path, exercised here on one GPU)."""
+    from come_b200 import flash_attn_fwd_cuda as fa
+    backend(fa.BACKEND_TCGEN05 if which == "tcgen05" else fa.BACKEND_CUDA_CORE)
+    H, D = 2, 64
+    P = sum(seq_lens)
+    rng = np.random.default_rng(31)
+    qkv = to_dev(gi.round_kind(rng.standard_normal((P, 3, H, D), dtype=np.float32), "bf16"), "bf16")
+    bias = to_dev(gi.round_kind(np.log(np.where(rng.random(P) < 0.2, 9.0, 1.0)).astype(np.float32), "bf16"), "bf16")
+    cu = torch.tensor(np.concatenate([[0], np.cumsum(seq_lens)]), dtype=torch.int32, device="cuda")
+    full, full_lse = fa.varlen_fwd_rows(qkv[:, 0], qkv[:, 1], qkv[:, 2], cu, max(seq_lens), bias, D ** -0.5, 0)
+    ref = fa.varlen_fwd_w_perkey_bias(qkv[:, 0], qkv[:, 1], qkv[:, 2], None, cu, cu, None, None, None, None, bias, max(seq_lens),
+                                      max(seq_lens), 0.0, D ** -0.5, False, False, -1, -1, 0.0, False, None)
+    assert torch.equal(full, ref[0]) and torch.equal(full_lse, ref[1])
+    for a, b in zip(cuts[:-1], cuts[1:]):
+        q_slice = qkv[a:b, 0].contiguous()  # a rank only holds its own query rows
+        out, lse = fa.varlen_fwd_rows(q_slice, qkv[:, 1], qkv[:, 2], cu, max(seq_lens), bias, D ** -0.5, a)
+        assert tuple(out.shape) == (b - a, H, D) and tuple(lse.shape) == (H, b - a)
+        torch.testing.assert_close(out, full[a:b], atol=0, rtol=0)
+        torch.testing.assert_close(lse, full_lse[:, a:b], atol=0, rtol=0)
+    _check_status()

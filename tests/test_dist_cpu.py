@@ -1,0 +1,66 @@
+"""Host-side logic of the multi-GPU path on CPU: frame sharding and the uneven row all-gather over a 2-rank gloo
+group (the attention itself needs a GPU and is covered by the row-range test there)."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+
+def test_shard_range_is_contiguous_and_balanced():
+    from come_b200.dist import rows_per_rank, shard_range
+    for n, world in ((100, 8), (8, 8), (5, 8), (256, 3), (1, 1)):
+        ranges = [shard_range(n, world, r) for r in range(world)]
+        assert ranges[0][0] == 0 and ranges[-1][1] == n
+        assert all(ranges[i][1] == ranges[i + 1][0] for i in range(world - 1))
+        sizes = [hi - lo for lo, hi in ranges]
+        assert max(sizes) - min(sizes) <= 1
+    offsets = [0, 10, 25, 31, 40, 58]  # 5 frames
+    assert rows_per_rank(offsets, 2) == [31, 27]
+    assert rows_per_rank(offsets, 5) == [10, 15, 6, 9, 18]
+    with pytest.raises(ValueError):
+        shard_range(4, 2, 2)
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, rows, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from come_b200.dist import gather_rows
+        local = torch.arange(rows[rank] * 6, dtype=torch.float32).reshape(rows[rank], 2, 3) + 1000 * rank
+        got = gather_rows(local, rows)
+        want = torch.cat([torch.arange(rows[r] * 6, dtype=torch.float32).reshape(rows[r], 2, 3) + 1000 * r for r in range(world)])
+        ok = torch.equal(got, want)
+        # an inconsistent row table is reported on the host before any collective is started
+        try:
+            gather_rows(local, list(rows) + [1])
+            ok = False
+        except ValueError:
+            pass
+        q.put((rank, ok))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("rows", [[5, 3], [4, 4], [0, 7]])
+def test_gather_rows_uneven_gloo(rows):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, rows, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    results = dict(q.get(timeout=10) for _ in range(2))
+    assert results == {0: True, 1: True}
