@@ -4,7 +4,8 @@
 // One CTA owns up to two 128-row query tiles of one (segment, head) and walks the segment's keys 128 at a time.
 //   warps 0-3 / 4-7 : softmax group of query tile 0 / 1.  Thread r owns score row r (TMEM lane r).  Per key tile it
 //                     pulls the 128 scores into registers (S is free for the next Q K^T at once), then works 32
-//                     columns at a time: row max with 3-input max,
+//                     columns at a time: row max with 3-input max, packed float32x2 arithmetic, a third of the
+//                     exponentials on the FMA pipe (cubic polynomial) instead of the special-function unit,
 //                     p = exp2(s * scale*log2e - m) with one FFMA + one MUFU per score, writes p back to TMEM as
 //                     16-bit pairs (the A operand of P V) and rescales the accumulator only when the running max
 //                     grew by more than 2^8 (exact: the final normalisation uses the same reference max).
@@ -237,6 +238,52 @@ __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
+}
+
+// ---- packed float32x2 arithmetic (one instruction for two lanes: halves the issue slots of the softmax) ----------
+typedef unsigned long long f32x2_t;
+__device__ __forceinline__ f32x2_t pack_f32x2(float lo, float hi) {
+    f32x2_t d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "f"(lo), "f"(hi));
+    return d;
+}
+__device__ __forceinline__ void unpack_f32x2(f32x2_t v, float &lo, float &hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ f32x2_t fma_f32x2(f32x2_t a, f32x2_t b, f32x2_t c) {
+    f32x2_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ f32x2_t add_f32x2(f32x2_t a, f32x2_t b) {
+    f32x2_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+// 2^x for two values on the FMA / integer pipes instead of the special-function unit (which is the bottleneck of
+// the head_dim-64 kernel): round-to-nearest range reduction x = n + f, f in [-0.5, 0.5], cubic fit of 2^f (relative
+// error 1.0e-4, far below the 16-bit rounding of the probabilities), n added to the exponent field as an integer.
+// Inputs below -125 are clamped (the result is then ~2^-125, i.e. zero for all purposes).
+__device__ __forceinline__ void exp2_poly_x2(float x0, float x1, float &r0, float &r1) {
+    const f32x2_t magic = pack_f32x2(12582912.0f, 12582912.0f);  // 1.5 * 2^23: adding it rounds to an integer
+    const f32x2_t neg_magic = pack_f32x2(-12582912.0f, -12582912.0f);
+    const f32x2_t minus_one = pack_f32x2(-1.0f, -1.0f);
+    const f32x2_t c3 = pack_f32x2(0.05583828315138817f, 0.05583828315138817f);
+    const f32x2_t c2 = pack_f32x2(0.2426394820213318f, 0.2426394820213318f);
+    const f32x2_t c1 = pack_f32x2(0.6931367516517639f, 0.6931367516517639f);
+    const f32x2_t c0 = pack_f32x2(0.9999245405197144f, 0.9999245405197144f);
+    const f32x2_t x = pack_f32x2(fmaxf(x0, -125.0f), fmaxf(x1, -125.0f));
+    const f32x2_t t = add_f32x2(x, magic);        // low mantissa bits of t hold n = round(x)
+    const f32x2_t n = add_f32x2(t, neg_magic);
+    const f32x2_t f = fma_f32x2(n, minus_one, x);
+    f32x2_t p = fma_f32x2(c3, f, c2);
+    p = fma_f32x2(p, f, c1);
+    p = fma_f32x2(p, f, c0);
+    float p0, p1, t0, t1;
+    unpack_f32x2(p, p0, p1);
+    unpack_f32x2(t, t0, t1);
+    r0 = __int_as_float(__float_as_int(p0) + (__float_as_int(t0) << 23));
+    r1 = __int_as_float(__float_as_int(p1) + (__float_as_int(t1) << 23));
 }
 
 template <bool kBF16> __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
@@ -568,21 +615,30 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                         tmem_st16(p_tmem + 16 * qq, st);
                     }
                 }
-                const float neg_m = -m_ref;
-                float sum0 = 0.0f, sum1 = 0.0f;
+                // p = 2^(s * scale*log2e - m_ref), two scores per instruction; every third pair takes the polynomial
+                // route so that the special-function unit and the FMA pipe share the exponentials.
+                const f32x2_t scale2 = pack_f32x2(scale_log2, scale_log2), neg_m2 = pack_f32x2(-m_ref, -m_ref);
+                f32x2_t sum2 = pack_f32x2(0.0f, 0.0f);
                 uint32_t pk[16];
 #pragma unroll
-                for (int i = 0; i < 32; i += 4) {
-                    const float p0 = fast_exp2(fmaf(__uint_as_float(a[i]), scale_log2, neg_m));
-                    const float p1 = fast_exp2(fmaf(__uint_as_float(a[i + 1]), scale_log2, neg_m));
-                    const float p2 = fast_exp2(fmaf(__uint_as_float(a[i + 2]), scale_log2, neg_m));
-                    const float p3 = fast_exp2(fmaf(__uint_as_float(a[i + 3]), scale_log2, neg_m));
-                    sum0 += p0 + p1;
-                    sum1 += p2 + p3;
-                    pk[i >> 1] = pack2<kBF16>(p0, p1);
-                    pk[(i >> 1) + 1] = pack2<kBF16>(p2, p3);
+                for (int pair = 0; pair < 16; ++pair) {
+                    const f32x2_t x2 = fma_f32x2(pack_f32x2(__uint_as_float(a[2 * pair]), __uint_as_float(a[2 * pair + 1])), scale2, neg_m2);
+                    float x0, x1, p0, p1;
+                    unpack_f32x2(x2, x0, x1);
+                    if (pair % 3 == 2) {
+                        exp2_poly_x2(x0, x1, p0, p1);
+                    } else {
+                        p0 = fast_exp2(x0);
+                        p1 = fast_exp2(x1);
+                    }
+                    sum2 = add_f32x2(sum2, pack_f32x2(p0, p1));
+                    pk[pair] = pack2<kBF16>(p0, p1);
                 }
-                l += sum0 + sum1;
+                {
+                    float s_lo, s_hi;
+                    unpack_f32x2(sum2, s_lo, s_hi);
+                    l += s_lo + s_hi;
+                }
                 if (!o_ready) {
                     ok = mbar_wait(&sh.o_done[t], (j - 1) & 1, sh, status, kErrODone);
                     ok = __all_sync(0xffffffffu, ok);
