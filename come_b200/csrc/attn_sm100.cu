@@ -771,6 +771,17 @@ bool attn_sm100_supported(const AttnArgs &a) {
     return true;
 }
 
+// The shared-memory opt-in of a kernel is set once per device and dtype (not again on every launch, so that
+// launches stay cheap and legal inside a stream capture).  Returns whether it was already done and marks it done.
+static bool attr_done(int which) {
+    static bool done[64][2];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
+    const bool was = done[dev][which];
+    done[dev][which] = true;
+    return was;
+}
+
 int attn_sm100_launch(const AttnArgs &a, cudaStream_t stream) {
     unsigned int *status = status_word_dev();
     if (!status) return COME_ERR_CUDA;
@@ -786,11 +797,11 @@ int attn_sm100_launch(const AttnArgs &a, cudaStream_t stream) {
     const float scale_log2 = a.scale * kLog2e;
     const float inv_scale = 1.0f / a.scale;
     if (a.dtype == COME_BF16) {
-        COME_CUDA(cudaFuncSetAttribute(attn_fwd_sm100_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        if (!attr_done(0)) COME_CUDA(cudaFuncSetAttribute(attn_fwd_sm100_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         attn_fwd_sm100_kernel<true><<<grid, kThreads, smem, stream>>>(mq, mk, mv, a.bias, a.cu, scale_log2, inv_scale, a.out, a.o_rs, a.lse,
                                                                      (int)a.q_begin, (int)a.q_end, status);
     } else {
-        COME_CUDA(cudaFuncSetAttribute(attn_fwd_sm100_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        if (!attr_done(1)) COME_CUDA(cudaFuncSetAttribute(attn_fwd_sm100_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         attn_fwd_sm100_kernel<false><<<grid, kThreads, smem, stream>>>(mq, mk, mv, a.bias, a.cu, scale_log2, inv_scale, a.out, a.o_rs, a.lse,
                                                                       (int)a.q_begin, (int)a.q_end, status);
     }

@@ -21,13 +21,24 @@ void set_error(const char *fmt, ...) {
 static __device__ unsigned int g_status_word = 0;
 
 unsigned int *status_word_dev() {
-    unsigned int *p = nullptr;
-    cudaError_t e = cudaGetSymbolAddress((void **)&p, g_status_word);
-    if (e != cudaSuccess) {
-        set_error("cudaGetSymbolAddress(status word) failed: %s", cudaGetErrorString(e));
+    static unsigned int *cached[64];  // looked up once per device (keeps later calls legal inside a stream capture)
+    static std::mutex mu;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+        set_error("cudaGetDevice failed or device index out of range");
         return nullptr;
     }
-    return p;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!cached[dev]) {
+        unsigned int *p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress((void **)&p, g_status_word);
+        if (e != cudaSuccess) {
+            set_error("cudaGetSymbolAddress(status word) failed: %s", cudaGetErrorString(e));
+            return nullptr;
+        }
+        cached[dev] = p;
+    }
+    return cached[dev];
 }
 
 int sm_count() {

@@ -1,0 +1,130 @@
+"""A whole scene of the Co-Me operator chain as ONE CUDA graph, with no device->host read anywhere.
+
+The reference reads the packed length back to the host inside every merge (``kernel_token_merge.cu:265``) and the
+longest segment inside every attention call (``flash_attn/__init__.py:33``), because its output shapes depend on
+them.  Here every buffer is allocated once for the worst case (nothing merged: ``frames * N`` packed rows) and every
+kernel is launched for the worst case too: kernels read the real sizes (``offsets``, ``cu_seqlens``) from device
+memory and the surplus CTAs exit at once.  The launch sequence therefore does not depend on the mask, is captured
+once, and is replayed for every scene: selection -> plan -> per layer (merge, biased attention, unmerge).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import List, Optional, Sequence
+
+import torch
+
+from . import _lib
+from ._torch_util import dtype_code, ptr, stream_ptr
+
+__all__ = ["StaticScene"]
+
+
+class StaticScene:
+    """Fixed-shape scene runner: ``run(x, confidence, qkv)`` copies the inputs into its static buffers, replays the
+    captured graph and returns the static output ``[frames, N, C]`` (valid until the next ``run``)."""
+
+    def __init__(self, frames: int, channels: int = 1024, start_index: int = 5, grid_h: int = 37, grid_w: int = 37,
+                 group_h: int = 3, group_w: int = 3, threshold: float = 0.5, num_heads: int = 16, head_dim: int = 64,
+                 layer_kinds: Optional[Sequence[str]] = None, scope: str = "frame", dtype: torch.dtype = torch.bfloat16,
+                 device: Optional[torch.device] = None):
+        if num_heads * head_dim != channels:
+            raise ValueError("channels must equal num_heads * head_dim (the attention output is unmerged as tokens)")
+        self.dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.frames, self.C, self.H, self.D = frames, channels, num_heads, head_dim
+        self.grid = (grid_h, grid_w, group_h, group_w)
+        self.threshold, self.scope, self.dtype = float(threshold), scope, dtype
+        self.scale = head_dim ** -0.5
+        self.layer_kinds: List[str] = list(layer_kinds) if layer_kinds is not None else ["frame", "global"] * 24
+        self.layout = _lib.Layout.two_d(start_index, grid_h, grid_w, group_h, group_w)
+        n_groups, n_tok, prefix = C.c_int64(), C.c_int64(), C.c_int64()
+        _lib.check(_lib.lib().come_layout_info(C.byref(self.layout), C.byref(n_groups), C.byref(n_tok), C.byref(prefix)))
+        self.M, self.N = int(n_groups.value), int(n_tok.value)
+        rows = frames * self.N  # worst case: nothing merged
+        self.rows_max = rows
+        d, dt = self.dev, dtype
+        e = torch.empty
+        # inputs
+        self.x = e((frames, self.N, channels), dtype=dt, device=d)
+        self.conf = e((1, frames * grid_h * grid_w), dtype=dt, device=d)
+        self.qkv = e((rows, 3, num_heads, head_dim), dtype=dt, device=d)
+        # plan
+        self.mask = e((frames, self.M), dtype=torch.uint8, device=d)
+        self.group_prefix = e((frames, self.M), dtype=torch.int32, device=d)
+        self.offsets = e((frames + 1,), dtype=torch.int32, device=d)
+        self.rev = e((rows,), dtype=torch.int64, device=d)
+        self.weight = torch.ones((rows,), dtype=torch.float32, device=d)
+        self.seg_max = e((1,), dtype=torch.int32, device=d)
+        self.bias = e((rows,), dtype=dt, device=d)
+        self.cu_global = torch.zeros((2,), dtype=torch.int32, device=d)
+        self.ws_bytes = int(_lib.lib().come_merge_plan_workspace_bytes(frames))
+        self.ws = e((self.ws_bytes,), dtype=torch.uint8, device=d)
+        # per-layer scratch and output
+        self.merged = e((rows, channels), dtype=dt, device=d)
+        self.attn = e((rows, num_heads, head_dim), dtype=dt, device=d)
+        self.lse = e((num_heads, rows), dtype=torch.float32, device=d)
+        self.out = e((frames, self.N, channels), dtype=dt, device=d)
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.launches_per_scene = 3 + 3 * len(self.layer_kinds)
+
+    # -- the launch sequence (same for every mask) -----------------------------------------------------------
+    def _enqueue(self) -> None:
+        lib, st, code = _lib.lib(), stream_ptr(self.dev), dtype_code(self.dtype)
+        H_, W_, gh, gw = self.grid
+        _lib.check(lib.come_select_windows(ptr(self.conf), code, 1, self.frames, H_, W_, gh, gw, self.threshold,
+                                           _lib.COME_SELECT_RANK,
+                                           _lib.COME_SCOPE_FRAME if self.scope == "frame" else _lib.COME_SCOPE_BATCH,
+                                           ptr(self.mask), st))
+        _lib.check(lib.come_merge_plan(ptr(self.mask), self.frames, C.byref(self.layout), ptr(self.group_prefix),
+                                       ptr(self.offsets), ptr(self.rev), ptr(self.weight), ptr(self.seg_max), ptr(self.ws),
+                                       self.ws_bytes, st))
+        # per-key bias log(count) in the run dtype; rows past the packed length hold stale counts and are never read
+        torch.log(self.weight, out=self._bias32)
+        self.bias.copy_(self._bias32)
+        self.cu_global[1:].copy_(self.offsets[-1:])
+        q, k, v = self.qkv[:, 0], self.qkv[:, 1], self.qkv[:, 2]
+        for kind in self.layer_kinds:
+            _lib.check(lib.come_merge(ptr(self.x), code, self.frames, self.C, C.byref(self.layout), ptr(self.mask),
+                                      ptr(self.group_prefix), ptr(self.offsets), ptr(self.merged), st))
+            if kind == "global":
+                cu, nseg, max_len = self.cu_global, 1, self.rows_max
+            else:
+                cu, nseg, max_len = self.offsets, self.frames, self.N
+            _lib.check(lib.come_attn_varlen_fwd(ptr(q), ptr(k), ptr(v), code, self.rows_max, self.H, self.D, q.stride(0),
+                                                k.stride(0), v.stride(0), ptr(self.bias), ptr(cu), nseg, max_len,
+                                                self.scale, ptr(self.attn), self.attn.stride(0), ptr(self.lse), 0, st))
+            _lib.check(lib.come_unmerge(ptr(self.attn), ptr(self.rev), self.rows_max, self.C, code, ptr(self.out), st))
+
+    def capture(self) -> "StaticScene":
+        """Run the sequence once eagerly (first-use set-up of the library happens outside the capture), then capture it."""
+        self._bias32 = torch.empty((self.rows_max,), dtype=torch.float32, device=self.dev)
+        with torch.cuda.device(self.dev):
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                self._enqueue()
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph):
+                self._enqueue()
+        return self
+
+    def run(self, x: Optional[torch.Tensor] = None, confidence: Optional[torch.Tensor] = None,
+            qkv: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Inputs may live on the host (pinned) or the device; ``None`` keeps what the static buffers hold.
+        ``qkv`` may have fewer rows than the worst case (only the first ``P`` packed rows are read)."""
+        if self.graph is None:
+            self.capture()
+        if x is not None:
+            self.x.copy_(x, non_blocking=True)
+        if confidence is not None:
+            self.conf.copy_(confidence.reshape(self.conf.shape), non_blocking=True)
+        if qkv is not None:
+            self.qkv[: qkv.shape[0]].copy_(qkv, non_blocking=True)
+        self.graph.replay()
+        return self.out
+
+    def packed_rows(self) -> int:
+        """Packed length of the last scene (reads one int back: for reporting, not needed to run)."""
+        return int(self.offsets[-1].item())
