@@ -228,7 +228,24 @@ def run_gpu(args):
     if rank == 0:
         sampler.start()
         time.sleep(0.3)
-    # ---- timed region 1: resident inputs, per-step device time ---------------------------------------------------
+    # ---- timed region 0 (-> `value`): the captured scene graph, inputs resident, per-step device time ----------------
+    from come_b200.static_scene import StaticScene
+    scene = StaticScene(FRAMES, CH, START, GRID, GRID, WIN, WIN, 0.5, HEADS, HDIM, LAYERS, "frame", torch.bfloat16, dev).capture()
+    for _ in range(3):
+        scene.run(x_host, conf_host, qkv_host)
+    barrier()
+    graph_ev = []
+    for _ in range(args.steps):
+        flush.fill_(1)  # L2 flush between timed iterations (outside the per-step events)
+        s, e = ev(), ev()
+        s.record()
+        scene.run()
+        e.record()
+        graph_ev.append((s, e))
+    barrier()
+    graph_ms = sum(s.elapsed_time(e) for s, e in graph_ev)
+    # ---- timed region 1 (-> `roofline`): the same scene launched kernel by kernel, each kernel family bracketed by
+    # CUDA events on the launching stream (the graph cannot be bracketed from inside) -------------------------------
     step_ev, timers = [], []
     barrier()
     plan = None
@@ -246,16 +263,13 @@ def run_gpu(args):
     h2d = x_host.numel() * 2 + conf_host.numel() * 2 + qkv_host.numel() * 2
     d2h = out_host.numel() * 2
     for _ in range(2):
-        chain.forward_scene(x_host.to(dev, non_blocking=True), conf_host.to(dev, non_blocking=True), lambda P: qkv_buf[:P])
+        out_host.copy_(scene.run(x_host, conf_host, qkv_host), non_blocking=True)
     barrier()
     s, e = ev(), ev()
     s.record()
     for _ in range(args.steps):
-        xd = x_host.to(dev, non_blocking=True)
-        cd = conf_host.to(dev, non_blocking=True)
-        qd = qkv_host.to(dev, non_blocking=True)
-        res = chain.forward_scene(xd, cd, lambda P, qd=qd: qd[:P])
-        out_host.copy_(res.reshape(FRAMES, N_TOK, CH), non_blocking=True)
+        res = scene.run(x_host, conf_host, qkv_host)  # pinned host -> device copies, then the graph
+        out_host.copy_(res, non_blocking=True)         # device -> pinned host
     e.record()
     barrier()
     e2e_ms = s.elapsed_time(e)
@@ -263,12 +277,13 @@ def run_gpu(args):
     if _lib.device_status(clear=False) != 0:
         raise RuntimeError("attention kernel raised the device status word during the timed region")
 
-    t = torch.tensor([total_ms, e2e_ms], dtype=torch.float64, device=dev)
+    t = torch.tensor([total_ms, e2e_ms, graph_ms], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    total_ms, e2e_ms = t.tolist()
+    total_ms, e2e_ms, graph_ms = t.tolist()
     scenes = args.steps * world
-    value = total_ms / scenes
+    value = graph_ms / scenes
+    eager_value = total_ms / scenes
     e2e_value = e2e_ms / scenes
 
     if rank == 0:
@@ -292,9 +307,11 @@ def run_gpu(args):
         unmerge_bytes = P * CH * 2 + FRAMES * N_TOK * 8 + FRAMES * N_TOK * CH * 2
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": total_ms / args.steps, "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
+            "ms_per_step": graph_ms / args.steps, "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic (seeded)",
             "config": {"workload": workload_name(), "merged_tokens": P, "l2": "flushed between timed steps (256 MB write)",
+                       "launch": "one CUDA graph per scene (StaticScene): worst-case grids, no device-to-host read",
+                       "eager_ms_per_scene": eager_value,
                        "parallelism": f"one independent scene per GPU x {world}"},
             "roofline": {"kernel": "attn_fwd_sm100_kernel (48 launches/scene: 24 frame + 24 global)", "bound": "tensor",
                          "achieved": achieved, "peak": pk["tflops"], "unit": "TFLOP/s", "frac": achieved / pk["tflops"],
@@ -307,7 +324,7 @@ def run_gpu(args):
             "roofline_unmerge": {"bound": "hbm", "achieved": unmerge_bytes * n_layers / (t_unmerge * 1e-3) / 1e9,
                                  "peak": pk["hbm_gbs"], "unit": "GB/s"},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-            "gpu_launches": chain.launches_per_scene * args.steps,
+            "gpu_launches": scene.launches_per_scene * args.steps,
             "clocks": clocks,
         }
         if world == 1 and not args.no_micro:
