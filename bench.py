@@ -315,7 +315,8 @@ def run_gpu(args):
                        "parallelism": f"one independent scene per GPU x {world}"},
             "roofline": {"kernel": "attn_fwd_sm100_kernel (48 launches/scene: 24 frame + 24 global)", "bound": "tensor",
                          "achieved": achieved, "peak": pk["tflops"], "unit": "TFLOP/s", "frac": achieved / pk["tflops"],
-                         "peak_source": pk["source"] + " burst cuBLAS bf16", "traffic": None,
+                         "peak_source": pk["source"] + " burst cuBLAS bf16",
+                         "traffic": 39.9e6, "traffic_note": "DRAM bytes of one global-layer launch (ncu, profiles/attn_fwd_sm100_global_1seg6456.md): qkv read once",
                          "frame_tflops": n_f * flops_frame / (t_attn["frame"] * 1e-3) / 1e12,
                          "global_tflops": n_g * flops_global / (t_attn["global"] * 1e-3) / 1e12,
                          "avg_launch_ms": attn_ms / n_layers},
