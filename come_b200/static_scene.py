@@ -125,6 +125,69 @@ class StaticScene:
         self.graph.replay()
         return self.out
 
+    # -- pipelined host <-> device traffic -------------------------------------------------------------------
+    def _pipe_init(self) -> None:
+        d = self.dev
+        self._copy_stream = torch.cuda.Stream(device=d)
+        self._stage = [(torch.empty_like(self.x), torch.empty_like(self.conf), torch.empty_like(self.qkv)) for _ in range(2)]
+        self._out_stage = [torch.empty_like(self.out) for _ in range(2)]
+        self._staged = [torch.cuda.Event() for _ in range(2)]    # inputs of slot i are on the device
+        self._consumed = [torch.cuda.Event() for _ in range(2)]  # slot i has been copied into the static inputs
+        self._done = [torch.cuda.Event() for _ in range(2)]      # output of slot i is in its staging buffer
+        self._drained = [torch.cuda.Event() for _ in range(2)]   # output staging buffer i has left for the host
+        self._put = self._get = 0
+
+    def stage(self, x_host: torch.Tensor, conf_host: torch.Tensor, qkv_host: torch.Tensor) -> None:
+        """Start copying the NEXT scene's (pinned) host inputs to the device on a side stream; returns at once.  At
+        most two scenes may be staged ahead of :meth:`run_staged`."""
+        if not hasattr(self, "_copy_stream"):
+            self._pipe_init()
+        i = self._put % 2
+        with torch.cuda.stream(self._copy_stream):
+            if self._put >= 2:
+                self._copy_stream.wait_event(self._consumed[i])
+            sx, sc, sq = self._stage[i]
+            sx.copy_(x_host, non_blocking=True)
+            sc.copy_(conf_host.reshape(sc.shape), non_blocking=True)
+            sq[: qkv_host.shape[0]].copy_(qkv_host, non_blocking=True)
+            self._staged[i].record(self._copy_stream)
+        self._put += 1
+
+    def run_staged(self, out_host: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Run the oldest staged scene on the current stream; with ``out_host`` (pinned) the result is sent to the
+        host on the side stream while the next scene computes.  Returns the device staging buffer of the result."""
+        if self.graph is None:
+            self.capture()
+        if self._get >= self._put:
+            raise RuntimeError("run_staged() without a staged scene")
+        i = self._get % 2
+        cur = torch.cuda.current_stream(self.dev)
+        cur.wait_event(self._staged[i])
+        sx, sc, sq = self._stage[i]
+        self.x.copy_(sx, non_blocking=True)
+        self.conf.copy_(sc, non_blocking=True)
+        self.qkv.copy_(sq, non_blocking=True)
+        self._consumed[i].record(cur)
+        self.graph.replay()
+        if self._get >= 2:
+            cur.wait_event(self._drained[i])
+        self._out_stage[i].copy_(self.out, non_blocking=True)
+        self._done[i].record(cur)
+        if out_host is not None:
+            with torch.cuda.stream(self._copy_stream):
+                self._copy_stream.wait_event(self._done[i])
+                out_host.copy_(self._out_stage[i], non_blocking=True)
+                self._drained[i].record(self._copy_stream)
+        else:
+            self._drained[i].record(cur)
+        self._get += 1
+        return self._out_stage[i]
+
+    def drain(self) -> None:
+        """Wait for every outstanding copy of the pipeline."""
+        if hasattr(self, "_copy_stream"):
+            self._copy_stream.synchronize()
+
     def packed_rows(self) -> int:
         """Packed length of the last scene (reads one int back: for reporting, not needed to run)."""
         return int(self.offsets[-1].item())

@@ -53,3 +53,26 @@ def test_eager_chain_layer_matches_oracle():
     want, _ = clib.attention_bias(qkv.float().cpu().numpy(), bias, np.array([0, P], np.int32), D ** -0.5)
     want_tokens = want.reshape(P, C)[rev].reshape(frames, 1374, C)
     assert np.abs(y.float().cpu().numpy() - want_tokens).max() <= 2e-2
+
+
+def test_static_scene_pipeline_matches_plain_run():
+    """Staging the next scene's host inputs and draining the previous result on a side stream must not change results."""
+    from come_b200.static_scene import StaticScene
+    frames, C, H, D = 2, 128, 2, 64
+    kinds = ["frame", "global"]
+    scene = StaticScene(frames, channels=C, num_heads=H, head_dim=D, layer_kinds=kinds).capture()
+    g = torch.Generator(device="cpu").manual_seed(11)
+    scenes = [(torch.randn((frames, 1374, C), generator=g).bfloat16().pin_memory(),
+               torch.rand((1, frames * 1369), generator=g).bfloat16().pin_memory(),
+               torch.randn((frames * 1374, 3, H, D), generator=g).bfloat16().pin_memory()) for _ in range(5)]
+    want = [scene.run(*sc).clone().cpu() for sc in scenes]
+    outs = [torch.empty((frames, 1374, C), dtype=torch.bfloat16).pin_memory() for _ in scenes]
+    scene.stage(*scenes[0])
+    for k in range(len(scenes)):
+        if k + 1 < len(scenes):
+            scene.stage(*scenes[k + 1])
+        scene.run_staged(outs[k])
+    scene.drain()
+    torch.cuda.synchronize()
+    for got, ref in zip(outs, want):
+        torch.testing.assert_close(got, ref, atol=0, rtol=0)
