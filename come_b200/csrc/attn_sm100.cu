@@ -296,6 +296,45 @@ template <bool kBF16> __device__ __forceinline__ uint32_t pack2(float lo, float 
     }
 }
 
+// Rare path of the softmax: a row's running max grew by more than the threshold, so everything accumulated against
+// the old reference max is scaled by alpha = 2^(old - new): the output accumulator (if earlier key tiles exist) and
+// the quarters of this tile's probabilities already staged in TMEM.  Kept out of line: inlined four times into the
+// unrolled quarter loop it doubles the hot loop's code size for a path taken a handful of times per row.
+template <bool kBF16>
+__device__ __noinline__ void rescale_staged(uint32_t o_tmem, uint32_t p_tmem, float alpha, bool scale_o, int staged_quarters) {
+    if (scale_o) {
+        uint32_t o[2][32];
+        tmem_ld32(o_tmem + 0, o[0]);
+        tmem_ld32(o_tmem + 32, o[1]);
+        tc_wait_ld();
+#pragma unroll
+        for (int c = 0; c < 2; ++c)
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[c][i] = __float_as_uint(__uint_as_float(o[c][i]) * alpha);
+        tmem_st32(o_tmem + 0, o[0]);
+        tmem_st32(o_tmem + 32, o[1]);
+    }
+    for (int qq = 0; qq < staged_quarters; ++qq) {
+        uint32_t st[16];
+        tc_wait_st();
+        tmem_ld16(p_tmem + 16 * qq, st);
+        tc_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            float lo, hi;
+            if constexpr (kBF16) {
+                const float2 f = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162 *>(&st[i]));
+                lo = f.x; hi = f.y;
+            } else {
+                const float2 f = __half22float2(*reinterpret_cast<__half2 *>(&st[i]));
+                lo = f.x; hi = f.y;
+            }
+            st[i] = pack2<kBF16>(lo * alpha, hi * alpha);
+        }
+        tmem_st16(p_tmem + 16 * qq, st);
+    }
+}
+
 // Shared-memory matrix descriptor of a tile whose rows are 128 bytes wide and 128-byte swizzled (what a TMA
 // load with a 64-element 16-bit inner box produces): 8-row groups are 1024 bytes apart.  The same encoding
 // serves a K-major operand (rows = M/N index, advance 32 bytes per 16-element K step) and an MN-major operand
@@ -583,37 +622,8 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                             tc_fence_after();
                             o_ready = true;
                         }
-                        uint32_t o[2][32];
-                        tmem_ld32(o_tmem + 0, o[0]);
-                        tmem_ld32(o_tmem + 32, o[1]);
-                        tc_wait_ld();
-#pragma unroll
-                        for (int c = 0; c < 2; ++c)
-#pragma unroll
-                            for (int i = 0; i < 32; ++i) o[c][i] = __float_as_uint(__uint_as_float(o[c][i]) * alpha);
-                        tmem_st32(o_tmem + 0, o[0]);
-                        tmem_st32(o_tmem + 32, o[1]);
                     }
-#pragma unroll
-                    for (int qq = 0; qq < q; ++qq) {  // and this tile's probabilities already staged in TMEM
-                        uint32_t st[16];
-                        tc_wait_st();
-                        tmem_ld16(p_tmem + 16 * qq, st);
-                        tc_wait_ld();
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) {
-                            float lo, hi;
-                            if constexpr (kBF16) {
-                                const float2 f = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162 *>(&st[i]));
-                                lo = f.x; hi = f.y;
-                            } else {
-                                const float2 f = __half22float2(*reinterpret_cast<__half2 *>(&st[i]));
-                                lo = f.x; hi = f.y;
-                            }
-                            st[i] = pack2<kBF16>(lo * alpha, hi * alpha);
-                        }
-                        tmem_st16(p_tmem + 16 * qq, st);
-                    }
+                    rescale_staged<kBF16>(o_tmem, p_tmem, alpha, j > 0, q);
                 }
                 // p = 2^(s * scale*log2e - m_ref), two scores per instruction; every third pair takes the polynomial
                 // route so that the special-function unit and the FMA pipe share the exponentials.
