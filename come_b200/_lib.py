@@ -16,7 +16,7 @@ COME_SELECT_RANK, COME_SELECT_ABS = 0, 1
 COME_SCOPE_BATCH, COME_SCOPE_FRAME = 0, 1
 
 EXPORTS = (
-    "come_version", "come_last_error", "come_layout_info", "come_select_windows",
+    "come_version", "come_last_error", "come_layout_info", "come_select_windows", "come_select_windows_ratios",
     "come_merge_plan_workspace_bytes", "come_merge_plan", "come_merge_plan_static", "come_merge", "come_unmerge",
     "come_attn_varlen_fwd", "come_attn_varlen_fwd_rows", "come_device_status",
 )
@@ -54,6 +54,7 @@ def lib() -> C.CDLL:
     l.come_last_error.restype = C.c_char_p
     l.come_layout_info.argtypes = [C.POINTER(Layout), C.POINTER(i64), C.POINTER(i64), C.POINTER(i64)]
     l.come_select_windows.argtypes = [vp, i32, i64, i64, i32, i32, i32, i32, f32, i32, i32, vp, vp]
+    l.come_select_windows_ratios.argtypes = [vp, i32, i64, i64, i32, i32, i32, i32, vp, i32, vp, vp]
     l.come_merge_plan_workspace_bytes.argtypes = [i64]
     l.come_merge_plan_workspace_bytes.restype = C.c_size_t
     l.come_merge_plan.argtypes = [vp, i64, C.POINTER(Layout), vp, vp, vp, vp, vp, vp, C.c_size_t, vp]

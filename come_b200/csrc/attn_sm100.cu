@@ -44,6 +44,12 @@ constexpr long long kWaitTicks = 1ll << 29;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
+// Which of the 16 score pairs of a 32-column quarter take the polynomial exp2 (bit i = pair i); the rest use the
+// special-function unit.  5 of 16 balanced the two pipes best in measurements.
+#ifndef COME_POLY_MASK
+#define COME_POLY_MASK 0x4924u
+#endif
+constexpr uint32_t kPolyPairs = COME_POLY_MASK;
 constexpr float kMasked = -3.0e38f;        // "minus infinity" of a masked key, still finite in bfloat16
 
 struct SharedStorage {
@@ -635,7 +641,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     const f32x2_t x2 = fma_f32x2(pack_f32x2(__uint_as_float(a[2 * pair]), __uint_as_float(a[2 * pair + 1])), scale2, neg_m2);
                     float x0, x1, p0, p1;
                     unpack_f32x2(x2, x0, x1);
-                    if (pair % 3 == 2) {
+                    if ((kPolyPairs >> pair) & 1u) {
                         exp2_poly_x2(x0, x1, p0, p1);
                     } else {
                         p0 = fast_exp2(x0);

@@ -28,8 +28,9 @@ __device__ __forceinline__ float window_mean(const T *__restrict__ conf, int64_t
 
 template <typename T>
 __global__ void __launch_bounds__(kSelectThreads)
-select_rank_kernel(const T *__restrict__ conf, int frames_per_group, int H, int W, int gh, int gw, float q,
-                   uint8_t *__restrict__ mask) {
+select_rank_kernel(const T *__restrict__ conf, int frames_per_group, int H, int W, int gh, int gw, float q_all,
+                   const float *__restrict__ q_per_group, uint8_t *__restrict__ mask) {
+    const float q = q_per_group ? fminf(fmaxf(q_per_group[blockIdx.x], 0.0f), 1.0f) : q_all;
     extern __shared__ float s_val[];  // n_pow2 floats
     __shared__ float s_thr;
     const int Wm = W / gw, M = (H / gh) * Wm;
@@ -87,8 +88,8 @@ __global__ void select_abs_kernel(const T *__restrict__ conf, int64_t n_windows,
 }
 
 template <typename T>
-static int launch_select(const void *conf, int64_t batch, int64_t S, int H, int W, int gh, int gw, float thr, int mode,
-                         int scope, uint8_t *mask, cudaStream_t st) {
+static int launch_select(const void *conf, int64_t batch, int64_t S, int H, int W, int gh, int gw, float thr,
+                         const float *thr_per_group, int mode, int scope, uint8_t *mask, cudaStream_t st) {
     const int M = (H / gh) * (W / gw);
     if (mode == COME_SELECT_ABS) {
         const int64_t n = batch * S * M;
@@ -108,7 +109,7 @@ static int launch_select(const void *conf, int64_t batch, int64_t S, int H, int 
         COME_CUDA(cudaFuncSetAttribute(select_rank_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        kSelectMaxWindows * (int)sizeof(float)));
     select_rank_kernel<T><<<(unsigned)groups, kSelectThreads, smem, st>>>((const T *)conf, frames_per_group, H, W, gh, gw,
-                                                                          thr, mask);
+                                                                          thr, thr_per_group, mask);
     return check_launch("come_select_windows");
 }
 
@@ -116,23 +117,39 @@ static int launch_select(const void *conf, int64_t batch, int64_t S, int H, int 
 
 using namespace come;
 
-extern "C" int come_select_windows(const void *conf_dev, int dtype, int64_t batch, int64_t frames_per_batch,
-                                   int grid_h, int grid_w, int group_h, int group_w, float threshold, int mode,
-                                   int scope, uint8_t *mask_dev, void *stream) {
+static int select_impl(const void *conf_dev, int dtype, int64_t batch, int64_t frames_per_batch, int grid_h, int grid_w,
+                       int group_h, int group_w, float threshold, const float *thr_per_group, int mode, int scope,
+                       uint8_t *mask_dev, void *stream) {
     COME_REQUIRE(batch >= 0 && frames_per_batch >= 0, "batch and frames_per_batch must be >= 0");
     COME_REQUIRE(grid_h > 0 && grid_w > 0 && group_h > 0 && group_w > 0, "grid and window sizes must be positive");
     COME_REQUIRE(group_h <= grid_h && group_w <= grid_w, "window larger than the grid");
     COME_REQUIRE(dtype == COME_F32 || dtype == COME_F16 || dtype == COME_BF16, "unknown dtype %d", dtype);
     COME_REQUIRE(mode == COME_SELECT_RANK || mode == COME_SELECT_ABS, "unknown selection mode %d", mode);
     COME_REQUIRE(scope == COME_SCOPE_BATCH || scope == COME_SCOPE_FRAME, "unknown selection scope %d", scope);
-    if (mode == COME_SELECT_RANK)
+    COME_REQUIRE(thr_per_group == nullptr || mode == COME_SELECT_RANK, "per-group thresholds need the ranking mode");
+    if (mode == COME_SELECT_RANK && !thr_per_group)
         COME_REQUIRE(threshold >= 0.0f && threshold <= 1.0f, "Ranking mode requires threshold in [0, 1], got %g", threshold);
     if (batch == 0 || frames_per_batch == 0) return COME_OK;
     COME_REQUIRE(conf_dev && mask_dev, "conf / mask must not be NULL");
     cudaStream_t st = (cudaStream_t)stream;
     switch (dtype) {
-        case COME_F32: return launch_select<float>(conf_dev, batch, frames_per_batch, grid_h, grid_w, group_h, group_w, threshold, mode, scope, mask_dev, st);
-        case COME_F16: return launch_select<__half>(conf_dev, batch, frames_per_batch, grid_h, grid_w, group_h, group_w, threshold, mode, scope, mask_dev, st);
-        default: return launch_select<__nv_bfloat16>(conf_dev, batch, frames_per_batch, grid_h, grid_w, group_h, group_w, threshold, mode, scope, mask_dev, st);
+        case COME_F32: return launch_select<float>(conf_dev, batch, frames_per_batch, grid_h, grid_w, group_h, group_w, threshold, thr_per_group, mode, scope, mask_dev, st);
+        case COME_F16: return launch_select<__half>(conf_dev, batch, frames_per_batch, grid_h, grid_w, group_h, group_w, threshold, thr_per_group, mode, scope, mask_dev, st);
+        default: return launch_select<__nv_bfloat16>(conf_dev, batch, frames_per_batch, grid_h, grid_w, group_h, group_w, threshold, thr_per_group, mode, scope, mask_dev, st);
     }
+}
+
+extern "C" int come_select_windows(const void *conf_dev, int dtype, int64_t batch, int64_t frames_per_batch,
+                                   int grid_h, int grid_w, int group_h, int group_w, float threshold, int mode,
+                                   int scope, uint8_t *mask_dev, void *stream) {
+    return select_impl(conf_dev, dtype, batch, frames_per_batch, grid_h, grid_w, group_h, group_w, threshold, nullptr, mode,
+                       scope, mask_dev, stream);
+}
+
+extern "C" int come_select_windows_ratios(const void *conf_dev, int dtype, int64_t batch, int64_t frames_per_batch,
+                                          int grid_h, int grid_w, int group_h, int group_w, const float *ratios_dev,
+                                          int scope, uint8_t *mask_dev, void *stream) {
+    COME_REQUIRE(ratios_dev != nullptr, "ratios must not be NULL");
+    return select_impl(conf_dev, dtype, batch, frames_per_batch, grid_h, grid_w, group_h, group_w, 0.5f, ratios_dev,
+                       COME_SELECT_RANK, scope, mask_dev, stream);
 }

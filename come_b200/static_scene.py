@@ -27,11 +27,22 @@ class StaticScene:
     def __init__(self, frames: int, channels: int = 1024, start_index: int = 5, grid_h: int = 37, grid_w: int = 37,
                  group_h: int = 3, group_w: int = 3, threshold: float = 0.5, num_heads: int = 16, head_dim: int = 64,
                  layer_kinds: Optional[Sequence[str]] = None, scope: str = "frame", dtype: torch.dtype = torch.bfloat16,
-                 device: Optional[torch.device] = None):
+                 device: Optional[torch.device] = None, frames_per_scene: Optional[int] = None,
+                 per_frame_ratios: bool = False):
+        """``frames`` frames form ``frames / frames_per_scene`` independent scenes (default: one scene): frame layers
+        attend inside a frame, global layers inside a scene.  With ``per_frame_ratios`` the merge ratio of every frame
+        is read from the static buffer ``ratios [frames]`` (float32) instead of the single ``threshold``."""
         if num_heads * head_dim != channels:
             raise ValueError("channels must equal num_heads * head_dim (the attention output is unmerged as tokens)")
         self.dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         self.frames, self.C, self.H, self.D = frames, channels, num_heads, head_dim
+        self.fps = frames if frames_per_scene is None else int(frames_per_scene)
+        if self.fps <= 0 or frames % self.fps != 0:
+            raise ValueError("frames must be a multiple of frames_per_scene")
+        self.scenes = frames // self.fps
+        if per_frame_ratios and scope != "frame":
+            raise ValueError("per-frame ratios need scope='frame'")
+        self.per_frame_ratios = per_frame_ratios
         self.grid = (grid_h, grid_w, group_h, group_w)
         self.threshold, self.scope, self.dtype = float(threshold), scope, dtype
         self.scale = head_dim ** -0.5
@@ -46,7 +57,7 @@ class StaticScene:
         e = torch.empty
         # inputs
         self.x = e((frames, self.N, channels), dtype=dt, device=d)
-        self.conf = e((1, frames * grid_h * grid_w), dtype=dt, device=d)
+        self.conf = e((self.scenes, self.fps * grid_h * grid_w), dtype=dt, device=d)
         self.qkv = e((rows, 3, num_heads, head_dim), dtype=dt, device=d)
         # plan
         self.mask = e((frames, self.M), dtype=torch.uint8, device=d)
@@ -56,7 +67,8 @@ class StaticScene:
         self.weight = torch.ones((rows,), dtype=torch.float32, device=d)
         self.seg_max = e((1,), dtype=torch.int32, device=d)
         self.bias = e((rows,), dtype=dt, device=d)
-        self.cu_global = torch.zeros((2,), dtype=torch.int32, device=d)
+        self.cu_global = torch.zeros((self.scenes + 1,), dtype=torch.int32, device=d)
+        self.ratios = torch.full((frames,), float(threshold), dtype=torch.float32, device=d)
         self.ws_bytes = int(_lib.lib().come_merge_plan_workspace_bytes(frames))
         self.ws = e((self.ws_bytes,), dtype=torch.uint8, device=d)
         # per-layer scratch and output
@@ -71,23 +83,27 @@ class StaticScene:
     def _enqueue(self) -> None:
         lib, st, code = _lib.lib(), stream_ptr(self.dev), dtype_code(self.dtype)
         H_, W_, gh, gw = self.grid
-        _lib.check(lib.come_select_windows(ptr(self.conf), code, 1, self.frames, H_, W_, gh, gw, self.threshold,
-                                           _lib.COME_SELECT_RANK,
-                                           _lib.COME_SCOPE_FRAME if self.scope == "frame" else _lib.COME_SCOPE_BATCH,
-                                           ptr(self.mask), st))
+        if self.per_frame_ratios:
+            _lib.check(lib.come_select_windows_ratios(ptr(self.conf), code, self.scenes, self.fps, H_, W_, gh, gw,
+                                                      ptr(self.ratios), _lib.COME_SCOPE_FRAME, ptr(self.mask), st))
+        else:
+            _lib.check(lib.come_select_windows(ptr(self.conf), code, self.scenes, self.fps, H_, W_, gh, gw, self.threshold,
+                                               _lib.COME_SELECT_RANK,
+                                               _lib.COME_SCOPE_FRAME if self.scope == "frame" else _lib.COME_SCOPE_BATCH,
+                                               ptr(self.mask), st))
         _lib.check(lib.come_merge_plan(ptr(self.mask), self.frames, C.byref(self.layout), ptr(self.group_prefix),
                                        ptr(self.offsets), ptr(self.rev), ptr(self.weight), ptr(self.seg_max), ptr(self.ws),
                                        self.ws_bytes, st))
         # per-key bias log(count) in the run dtype; rows past the packed length hold stale counts and are never read
         torch.log(self.weight, out=self._bias32)
         self.bias.copy_(self._bias32)
-        self.cu_global[1:].copy_(self.offsets[-1:])
+        self.cu_global.copy_(self.offsets[:: self.fps])  # scene boundaries = every frames_per_scene-th frame offset
         q, k, v = self.qkv[:, 0], self.qkv[:, 1], self.qkv[:, 2]
         for kind in self.layer_kinds:
             _lib.check(lib.come_merge(ptr(self.x), code, self.frames, self.C, C.byref(self.layout), ptr(self.mask),
                                       ptr(self.group_prefix), ptr(self.offsets), ptr(self.merged), st))
             if kind == "global":
-                cu, nseg, max_len = self.cu_global, 1, self.rows_max
+                cu, nseg, max_len = self.cu_global, self.scenes, self.fps * self.N
             else:
                 cu, nseg, max_len = self.offsets, self.frames, self.N
             _lib.check(lib.come_attn_varlen_fwd(ptr(q), ptr(k), ptr(v), code, self.rows_max, self.H, self.D, q.stride(0),

@@ -242,7 +242,7 @@ def func_token_merge_2d(tokens: torch.Tensor, start_index: int, group_h: int, gr
 
 
 def select_windows(confidence: torch.Tensor, B: int, S: int, H: int, W: int, group_h: int, group_w: int,
-                   threshold: float, mode: str = "pairwise-rank", scope: str = "batch") -> torch.Tensor:
+                   threshold, mode: str = "pairwise-rank", scope: str = "batch") -> torch.Tensor:
     """Per-patch confidence ``[B, S*H*W]`` -> bool merge mask ``[B*S, M]``.
 
     ``mode``: ``"pairwise-rank"`` (``mean < quantile(mean, threshold)``) or ``"abs_mse"`` (``mean < threshold``);
@@ -256,13 +256,27 @@ def select_windows(confidence: torch.Tensor, B: int, S: int, H: int, W: int, gro
         raise ValueError(f"unknown confidence mode {mode!r}")
     if scope not in ("batch", "frame"):
         raise ValueError(f"unknown scope {scope!r}")
-    if mode == "pairwise-rank" and not (0.0 <= threshold <= 1.0):
+    ratios = threshold if isinstance(threshold, torch.Tensor) else None  # one quantile level per batch element / frame
+    if ratios is not None:
+        if mode != "pairwise-rank":
+            raise ValueError("per-group thresholds need the ranking mode")
+        groups = B if scope == "batch" else B * S
+        if ratios.numel() != groups or ratios.dtype != torch.float32 or not ratios.is_cuda:
+            raise ValueError(f"Expected {groups} float32 CUDA ratios, got {tuple(ratios.shape)} {ratios.dtype}")
+    elif mode == "pairwise-rank" and not (0.0 <= threshold <= 1.0):
         raise ValueError(f"Ranking mode requires threshold in [0, 1], got {threshold}")
     if confidence.numel() != B * S * H * W:
         raise ValueError(f"Expected {B * S * H * W} confidences, got {confidence.numel()}")
     conf = confidence.contiguous()
     M = (H // group_h) * (W // group_w)
     mask = torch.empty((B * S, M), dtype=torch.bool, device=conf.device)
+    if ratios is not None:
+        ratios = ratios.contiguous()
+        with torch.cuda.device(conf.device):
+            _lib.check(_lib.lib().come_select_windows_ratios(
+                ptr(conf), dtype_code(conf.dtype, "confidence"), B, S, H, W, group_h, group_w, ptr(ratios),
+                _lib.COME_SCOPE_BATCH if scope == "batch" else _lib.COME_SCOPE_FRAME, ptr(mask), stream_ptr(conf.device)))
+        return mask
     with torch.cuda.device(conf.device):
         _lib.check(_lib.lib().come_select_windows(
             ptr(conf), dtype_code(conf.dtype, "confidence"), B, S, H, W, group_h, group_w, float(threshold),

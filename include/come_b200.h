@@ -78,6 +78,17 @@ int come_select_windows(const void *conf_dev, int dtype, int64_t batch, int64_t 
                         uint8_t *mask_dev, void *stream);
 
 /*
+ * Ranking selection with one quantile level per quantile group instead of one for all: ratios_dev holds one float in
+ * [0, 1] (values outside are clamped) per batch element (COME_SCOPE_BATCH) or per frame (COME_SCOPE_FRAME).  Same
+ * arithmetic as come_select_windows otherwise.  The reference configures a single threshold
+ * (src/accelerate/token_merger/co_me_2d.py:291-295); a per-frame merge ratio is what the ragged batch-throughput
+ * configuration of the benchmark draws.
+ */
+int come_select_windows_ratios(const void *conf_dev, int dtype, int64_t batch, int64_t frames_per_batch, int grid_h,
+                               int grid_w, int group_h, int group_w, const float *ratios_dev, int scope,
+                               uint8_t *mask_dev, void *stream);
+
+/*
  * Merge index plan: everything of a merge that depends on the mask only.
  * Replaces block_prefix_scan_kernel + at::cumsum (src/cuda_extension/co_me/src/kernel_token_merge.cu:12-46,
  * 284-286) and the rev_id / weight writes of the scatter kernels (:92-107,146-161,186-190); fallback

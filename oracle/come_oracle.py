@@ -271,7 +271,8 @@ def select_windows(conf, B, S, H, W, gh, gw, threshold, mode="pairwise-rank", sc
         return means < np.float32(threshold)
     if mode != "pairwise-rank":
         raise ValueError(mode)
-    if not (0.0 <= threshold <= 1.0):
+    per_group = np.ndim(threshold) > 0  # one quantile level per group (per-frame merge ratios of the ragged batch)
+    if not per_group and not (0.0 <= threshold <= 1.0):
         raise ValueError(f"Ranking mode requires threshold in [0, 1], got {threshold}")
     if scope == "batch":
         grouped = means.reshape(B, S * M)
@@ -279,7 +280,8 @@ def select_windows(conf, B, S, H, W, gh, gw, threshold, mode="pairwise-rank", sc
         grouped = means.reshape(B * S, M)
     else:
         raise ValueError(scope)
-    thr = np.array([quantile_linear(row, threshold) for row in grouped], dtype=np.float32)
+    levels = np.clip(np.asarray(threshold, np.float32), 0.0, 1.0) if per_group else np.full(len(grouped), threshold)
+    thr = np.array([quantile_linear(row, q) for row, q in zip(grouped, levels)], dtype=np.float32)
     return (grouped < thr[:, None]).reshape(B * S, M)
 
 

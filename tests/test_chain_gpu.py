@@ -76,3 +76,37 @@ def test_static_scene_pipeline_matches_plain_run():
     torch.cuda.synchronize()
     for got, ref in zip(outs, want):
         torch.testing.assert_close(got, ref, atol=0, rtol=0)
+
+
+def test_batch_of_ragged_scenes_matches_oracle_plan_and_per_scene_runs():
+    """Several independent scenes of 4 frames in one static batch, merge ratio drawn per frame from U(0.25, 0.75)
+    (the batch-throughput configuration, reduced): the mask must equal the oracle's per-frame quantile selection, and
+    every scene's output must equal what a one-scene runner computes for it alone."""
+    from come_b200.static_scene import StaticScene
+    from oracle import come_oracle as orc
+    scenes, fps, C, H, D = 3, 4, 128, 2, 64
+    frames = scenes * fps
+    kinds = ["frame", "global"]
+    batch = StaticScene(frames, channels=C, num_heads=H, head_dim=D, layer_kinds=kinds, frames_per_scene=fps,
+                        per_frame_ratios=True).capture()
+    single = StaticScene(fps, channels=C, num_heads=H, head_dim=D, layer_kinds=kinds, per_frame_ratios=True).capture()
+    g = torch.Generator(device="cpu").manual_seed(23)
+    x = torch.randn((frames, 1374, C), generator=g).bfloat16()
+    conf = torch.rand((scenes, fps * 1369), generator=g).bfloat16()
+    ratios = (torch.rand(frames, generator=g) * 0.5 + 0.25).float()
+    # every scene gets its own packed qkv rows: scene s of the batch starts at the batch's packed offset of its first frame
+    qkv_full = torch.randn((frames * 1374, 3, H, D), generator=g).bfloat16()
+    batch.ratios.copy_(ratios)
+    got = batch.run(x, conf, qkv_full).clone()
+    want_mask = orc.select_windows(conf.float().numpy(), scenes, fps, 37, 37, 3, 3, ratios.numpy(), "pairwise-rank", "frame", "bf16")
+    np.testing.assert_array_equal(batch.mask.cpu().numpy().astype(bool), want_mask)
+    lengths = 1374 - 8 * want_mask.sum(axis=1)
+    assert lengths.min() < lengths.max()  # ragged
+    offsets = batch.offsets.cpu().numpy()
+    np.testing.assert_array_equal(np.diff(offsets), lengths)
+    for s_ in range(scenes):
+        f0 = s_ * fps
+        single.ratios.copy_(ratios[f0:f0 + fps])
+        r0, r1 = int(offsets[f0]), int(offsets[f0 + fps])
+        out = single.run(x[f0:f0 + fps], conf[s_:s_ + 1], qkv_full[r0:r1])
+        torch.testing.assert_close(got[f0:f0 + fps], out, atol=0, rtol=0)
