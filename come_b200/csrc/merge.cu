@@ -250,24 +250,35 @@ template <> __device__ __forceinline__ void st_stream<__nv_bfloat16>(__nv_bfloat
 template <typename T, int VEC>
 __global__ void __launch_bounds__(kMergeThreads, 2)
 merge_kernel(const T *__restrict__ tokens, const uint8_t *__restrict__ mask, const int *__restrict__ group_prefix,
-             const int *__restrict__ offsets, FrameLayout L, int frames, int64_t C, T *__restrict__ out) {
+             const int *__restrict__ offsets, FrameLayout L, int frames, int64_t C, int groups, T *__restrict__ out) {
     using IO = VecIO<T, VEC>;
     using V = typename IO::V;
-    extern __shared__ int s_src[];  // source token of every row of the current unit (G entries)
+    extern __shared__ int s_src_all[];  // source token of every row of the current unit, per thread group (groups x G)
     const int G = L.G;
+    // Rows narrower than the CTA (e.g. 1024 x 16-bit = 128 vectors): the host splits the CTA into `groups` thread
+    // groups of `tpg` threads (whole warps), each moving its own unit, so that no thread idles.
+    const int tpg = kMergeThreads / groups;
+    const int grp = threadIdx.x / tpg, tig = threadIdx.x - grp * tpg;
+    int *s_src = s_src_all + grp * G;
     const int prefix_units = (L.prefix + G - 1) / G;
     const int units_per_frame = prefix_units + L.M;
-    const int64_t n_units = (int64_t)frames * units_per_frame;
+    const int n_units = frames * units_per_frame;  // fits: the host checks frames * tokens_per_frame < 2^31
     const int64_t Cv = C / VEC;
     const float fG = (float)G;
 
-    for (int64_t u = blockIdx.x; u < n_units; u += gridDim.x) {
-        const int b = (int)(u / units_per_frame);
-        const int unit = (int)(u - (int64_t)b * units_per_frame);
+    for (int u0 = blockIdx.x * groups; u0 < n_units; u0 += gridDim.x * groups) {
+        const int u = u0 + grp;
+        const bool active = u < n_units;  // the last round may leave some groups without a unit
+        const int b = active ? u / units_per_frame : 0;
+        const int unit = active ? u - b * units_per_frame : 0;
         const int base = offsets[b];
         int r0, rows, dst;
         bool merged = false;
-        if (unit < prefix_units) {
+        if (!active) {
+            r0 = 0;
+            rows = 0;
+            dst = 0;
+        } else if (unit < prefix_units) {
             r0 = unit * G;
             rows = min(G, L.prefix - r0);
             dst = base + r0;
@@ -279,12 +290,12 @@ merge_kernel(const T *__restrict__ tokens, const uint8_t *__restrict__ mask, con
             merged = mask[(size_t)b * L.M + m] != 0;
         }
         __syncthreads();  // previous unit's s_src no longer read
-        for (int g = threadIdx.x; g < rows; g += kMergeThreads) s_src[g] = L.src_token(r0 + g);
+        for (int g = tig; g < rows; g += tpg) s_src[g] = L.src_token(r0 + g);
         __syncthreads();
         const V *src_base = reinterpret_cast<const V *>(tokens) + (int64_t)b * L.N * Cv;
         V *dst_base = reinterpret_cast<V *>(out) + (int64_t)dst * Cv;
 
-        for (int64_t v = threadIdx.x; v < Cv; v += kMergeThreads) {
+        for (int64_t v = tig; v < Cv && active; v += tpg) {
             if (merged) {
                 float acc[VEC];
 #pragma unroll
@@ -345,6 +356,36 @@ unmerge_kernel(const V *__restrict__ merged, const int64_t *__restrict__ rev, in
         for (int k = 0; k < kUnmergeBatch; ++k) {
             const int64_t i = i0 + k * stride;
             if (i < n) st_stream(out + i, buf[k]);
+        }
+    }
+}
+
+// Row-shaped variant for rows of at most 256 vectors that divide 256 (C = 1024 fp32, C = 1024 or 2048 16-bit, ...):
+// a CTA moves kRowBatch groups of adjacent output rows per round, one vector per thread and group, with 32-bit index
+// arithmetic only (the generic kernel spends a 64-bit division per vector), the row index fetched once per row.
+constexpr int kRowBatch = 4;
+
+template <typename V>
+__global__ void __launch_bounds__(kUnmergeThreads)
+unmerge_rows_kernel(const V *__restrict__ merged, const int64_t *__restrict__ rev, int total, int Cv, V *__restrict__ out) {
+    const int rows_per_group = kUnmergeThreads / Cv;
+    const int sub = threadIdx.x / Cv, v = threadIdx.x - sub * Cv;
+    const int rows_per_round = rows_per_group * kRowBatch;
+    for (int row0 = blockIdx.x * rows_per_round; row0 < total; row0 += gridDim.x * rows_per_round) {
+        int64_t src[kRowBatch];
+#pragma unroll
+        for (int k = 0; k < kRowBatch; ++k) {
+            const int row = row0 + k * rows_per_group + sub;
+            if (row < total) src[k] = __ldg(rev + row);
+        }
+        V buf[kRowBatch];
+#pragma unroll
+        for (int k = 0; k < kRowBatch; ++k)
+            if (row0 + k * rows_per_group + sub < total) buf[k] = merged[src[k] * Cv + v];
+#pragma unroll
+        for (int k = 0; k < kRowBatch; ++k) {
+            const int row = row0 + k * rows_per_group + sub;
+            if (row < total) st_stream(out + (int64_t)row * Cv + v, buf[k]);
         }
     }
 }
@@ -454,13 +495,18 @@ static int launch_merge(const void *tokens, int64_t frames, int64_t C, const Fra
     const int64_t n_units = frames * (int64_t)(prefix_units + L.M);
     if (n_units == 0 || C == 0) return COME_OK;
     const int64_t max_blocks = (int64_t)sm_count() * 8;  // 8 resident CTAs of 256 threads per SM
-    const unsigned grid = (unsigned)(n_units < max_blocks ? n_units : max_blocks);
-    const size_t smem = (size_t)L.G * sizeof(int);
     const bool vec_ok = (C % VEC == 0) && ((uintptr_t)tokens % 16 == 0) && ((uintptr_t)out % 16 == 0);
+    const int64_t cv = vec_ok ? C / VEC : C;  // vectors per row as the launched kernel sees them
+    int groups = 1;
+    if (cv >= 32 && cv < kMergeThreads && kMergeThreads % cv == 0) groups = (int)(kMergeThreads / cv);
+    while (groups > 1 && (size_t)L.G * sizeof(int) * groups > 48 * 1024) groups >>= 1;
+    const size_t smem = (size_t)L.G * sizeof(int) * (size_t)groups;
+    const int64_t n_ctas = (n_units + groups - 1) / groups;
+    const unsigned grid = (unsigned)(n_ctas < max_blocks ? n_ctas : max_blocks);
     if (vec_ok)
-        merge_kernel<T, VEC><<<grid, kMergeThreads, smem, st>>>((const T *)tokens, mask, gp, off, L, (int)frames, C, (T *)out);
+        merge_kernel<T, VEC><<<grid, kMergeThreads, smem, st>>>((const T *)tokens, mask, gp, off, L, (int)frames, C, groups, (T *)out);
     else
-        merge_kernel<T, 1><<<grid, kMergeThreads, smem, st>>>((const T *)tokens, mask, gp, off, L, (int)frames, C, (T *)out);
+        merge_kernel<T, 1><<<grid, kMergeThreads, smem, st>>>((const T *)tokens, mask, gp, off, L, (int)frames, C, groups, (T *)out);
     return check_launch("come_merge");
 }
 
@@ -473,6 +519,7 @@ extern "C" int come_merge(const void *tokens_dev, int dtype, int64_t frames, int
     COME_REQUIRE(frames >= 0 && channels >= 0, "frames and channels must be >= 0");
     COME_REQUIRE(dtype == COME_F32 || dtype == COME_F16 || dtype == COME_BF16, "unknown dtype %d", dtype);
     COME_REQUIRE((size_t)L.G * sizeof(int) <= 48 * 1024, "group_size %d too large", L.G);
+    COME_REQUIRE(frames * (int64_t)L.N < (1ll << 31), "frames * tokens_per_frame must fit int32 row indices");
     if (frames == 0 || channels == 0) return COME_OK;
     COME_REQUIRE(tokens_dev && out_dev && offsets_dev, "tokens / out / offsets must not be NULL");
     COME_REQUIRE(L.M == 0 || (mask_dev && group_prefix_dev), "mask / group_prefix must not be NULL");
@@ -486,6 +533,14 @@ extern "C" int come_merge(const void *tokens_dev, int dtype, int64_t frames, int
 
 template <typename V>
 static int launch_unmerge(const void *merged, const int64_t *rev, int64_t total, int64_t Cv, void *out, cudaStream_t st) {
+    if (Cv <= kUnmergeThreads && kUnmergeThreads % Cv == 0 && total < (1ll << 31)) {
+        const int rows_per_round = (kUnmergeThreads / (int)Cv) * kRowBatch;
+        int64_t blocks = (total + rows_per_round - 1) / rows_per_round;
+        const int64_t max_blocks = (int64_t)sm_count() * 8;
+        if (blocks > max_blocks) blocks = max_blocks;
+        unmerge_rows_kernel<V><<<(unsigned)blocks, kUnmergeThreads, 0, st>>>((const V *)merged, rev, (int)total, (int)Cv, (V *)out);
+        return check_launch("come_unmerge");
+    }
     const int64_t n = total * Cv;
     const int64_t per_block = (int64_t)kUnmergeThreads * kUnmergeBatch;
     int64_t blocks = (n + per_block - 1) / per_block;
