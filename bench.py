@@ -583,6 +583,19 @@ def run_only(args):
         else:
             fn, nbytes = (lambda: plan.split(merged)), plan.total * CH * es + args.frames * N_TOK * 8 + args.frames * N_TOK * CH * es
         out.update(frames=args.frames, dtype=args.dtype, bytes=nbytes)
+    elif args.only == "prepare":
+        # q/k LayerNorm + 2-D rotary embedding + log(count) bias on the packed rows of `frames` half-merged frames
+        from come_b200.qkv import RotaryPositionEmbedding2D, prepare_packed_self_attention_qkv
+        mask = torch.rand((args.frames, N_WIN), device=dev, generator=g) < 0.5
+        plan = MergePlan(mask, _lib.Layout.two_d(START, GRID, GRID, WIN, WIN))
+        Pt = plan.total
+        qkv = torch.randn((Pt, 3, HEADS, HDIM), device=dev, generator=g).bfloat16()
+        ln_q = torch.nn.LayerNorm(HDIM).to(dev).bfloat16()
+        ln_k = torch.nn.LayerNorm(HDIM).to(dev).bfloat16()
+        rope, pos = RotaryPositionEmbedding2D(100.0), plan.positions()
+        fn = lambda: prepare_packed_self_attention_qkv(qkv, ln_q, ln_k, rope, pos, torch.bfloat16, weight=plan.weight)  # noqa: E731
+        # q and k read and written once, positions, counts in, bias out
+        out.update(frames=args.frames, tokens=Pt, bytes=Pt * (4 * HEADS * HDIM * 2 + 16 + 4 + 2))
     else:
         if args.segments == 1:
             lens = [args.tokens]
@@ -616,7 +629,7 @@ def run_only(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--only", choices=["attn", "merge", "unmerge"], help="run one kernel family on one size and exit")
+    ap.add_argument("--only", choices=["attn", "merge", "unmerge", "prepare"], help="run one kernel family on one size and exit")
     ap.add_argument("--frames", type=int, default=100, help="--only merge/unmerge: frames")
     ap.add_argument("--dtype", default="f32", choices=["f32", "bf16"], help="--only merge/unmerge: element type")
     ap.add_argument("--tokens", type=int, default=6384, help="--only attn with --segments 1: segment length")

@@ -7,6 +7,8 @@ Host side in Python/PyTorch (device memory, streams), compute in ``libcome_b200.
 * :mod:`come_b200.flash_attn_fwd_cuda`  -- ``varlen_fwd`` / ``varlen_fwd_w_perkey_bias``
 * :mod:`come_b200.flash_attn`           -- ``flash_attn_varlen_qkvpacked_func[_w_perkey_bias]``
 * :mod:`come_b200.cuda_extension`       -- stands in for the reference's ``src.cuda_extension`` package
+* :mod:`come_b200.qkv`                  -- ``prepare_packed_self_attention_qkv`` (q/k LayerNorm + 2-D RoPE + bias in
+  one kernel), ``RotaryPositionEmbedding2D``
 * :mod:`come_b200.token_merger`         -- ``JaggedTokens``, ``func_token_merge[_2d]``, ``func_token_split``,
   ``MergePlan``, ``select_windows`` and the 2-D merger class
 """

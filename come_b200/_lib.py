@@ -18,7 +18,8 @@ COME_SCOPE_BATCH, COME_SCOPE_FRAME = 0, 1
 EXPORTS = (
     "come_version", "come_last_error", "come_layout_info", "come_select_windows", "come_select_windows_ratios",
     "come_merge_plan_workspace_bytes", "come_merge_plan", "come_merge_plan_static", "come_merge", "come_unmerge",
-    "come_attn_varlen_fwd", "come_attn_varlen_fwd_rows", "come_device_status",
+    "come_attn_varlen_fwd", "come_attn_varlen_fwd_rows", "come_qkv_prepare", "come_packed_positions",
+    "come_device_status",
 )
 
 
@@ -65,6 +66,8 @@ def lib() -> C.CDLL:
                                        vp, i32, vp]
     l.come_attn_varlen_fwd_rows.argtypes = [vp, vp, vp, i32, i64, i64, i64, i32, i32, i64, i64, i64, vp, vp, i32, i32, f32, vp,
                                             i64, vp, i32, vp]
+    l.come_qkv_prepare.argtypes = [vp, i32, i64, i32, i32, vp, vp, vp, vp, f32, vp, vp, vp, i64, vp, vp, vp]
+    l.come_packed_positions.argtypes = [vp, vp, i64, C.POINTER(Layout), vp, vp]
     l.come_device_status.argtypes = [C.POINTER(C.c_uint32), i32]
     for name in EXPORTS:
         fn = getattr(l, name)

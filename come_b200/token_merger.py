@@ -163,6 +163,7 @@ class MergePlan:
         self.weight = weight_full[: self.total]
         self.offset = self.offsets_i32.long()
         self._bias = {}
+        self._positions = None
 
     # -- derived, cached ---------------------------------------------------------------------------------
     def perkey_bias(self, dtype: torch.dtype) -> torch.Tensor:
@@ -175,6 +176,19 @@ class MergePlan:
         """int32 segment boundaries; ``frames_per_segment = S`` concatenates the frames of a scene into one
         segment (global attention, ``src/accelerate/vggt/fused.py:136,149``)."""
         return self.offsets_i32 if frames_per_segment == 1 else self.offsets_i32[::frames_per_segment].contiguous()
+
+    def positions(self) -> torch.Tensor:
+        """``[P, 2]`` int64 (y, x) positions of the packed rows, computed from the plan alone
+        (``come_packed_positions``): what the reference obtains by merging the bfloat16 position tensor and
+        truncating it (``src/accelerate/vggt/fused.py:113-129``).  2-D layouts only."""
+        if self._positions is None:
+            pos = torch.empty(self.total, 2, dtype=torch.int64, device=self.mask.device)
+            with torch.cuda.device(self.mask.device):
+                _lib.check(_lib.lib().come_packed_positions(ptr(self._mask_u8), ptr(self.rev_id), self.frames,
+                                                            C.byref(self.layout), ptr(pos),
+                                                            stream_ptr(self.mask.device)))
+            self._positions = pos
+        return self._positions
 
     # -- data movement -----------------------------------------------------------------------------------
     def merge(self, tokens: torch.Tensor) -> torch.Tensor:

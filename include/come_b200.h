@@ -184,6 +184,39 @@ int come_attn_varlen_fwd_rows(const void *q_dev, const void *k_dev, const void *
                               void *out_dev, int64_t out_row_stride, float *lse_dev, int backend, void *stream);
 
 /*
+ * Pre-attention preparation of the packed qkv tensor [total, 3, num_heads, head_dim], in place, one pass:
+ *   q, k <- LayerNorm over head_dim (affine gamma / beta; skipped when the four pointers are NULL)
+ *   q, k <- 2-D rotary position embedding with integer positions pos[total, 2] = (y, x): the first head_dim/2
+ *           features rotate with y, the rest with x (skipped when pos_dev is NULL)
+ *   bias_out[i] = log(weight[i]) in dtype (skipped when both are NULL)
+ * v is not touched.  Replaces prepare_packed_self_attention_qkv, inference branch
+ * (src/accelerate/common/qkv.py:29-39: q_norm, k_norm, rope applied through four full-tensor copies), the rotary
+ * module it calls (src/thirdparty/vggt/layers/rope.py:116-187) and the bias expression of the attention module
+ * (src/accelerate/vggt/module/bias_attention.py:120).  Arithmetic follows the reference's roundings: statistics and
+ * the affine map in float32, the normalised value rounded to dtype, then t*cos, rot(t)*sin and their sum each
+ * rounded to dtype.
+ *   cos/sin_table_dev  [table_rows, head_dim/2] in dtype: row p = cos / sin of the dtype-rounded angles
+ *                      p * base^(-2i/(head_dim/2)), i = 0..head_dim/4-1, repeated twice
+ *                      (rope.py:87-114; the caller caches them like the reference does)
+ *   gamma / beta       [head_dim] in dtype
+ * A position outside [0, table_rows) is clamped and raises bit 16 of the device status word.
+ * dtype COME_F16 or COME_BF16; head_dim 32/64/128/256 with 2*num_heads*head_dim/8 <= 512 threads (a multiple of 32).
+ */
+int come_qkv_prepare(void *qkv_dev, int dtype, int64_t total, int num_heads, int head_dim, const void *q_gamma_dev,
+                     const void *q_beta_dev, const void *k_gamma_dev, const void *k_beta_dev, float eps,
+                     const int64_t *pos_dev, const void *cos_table_dev, const void *sin_table_dev, int64_t table_rows,
+                     const float *weight_dev, void *bias_out_dev, void *stream);
+
+/*
+ * Integer (y, x) positions of the packed rows, pos_out[P, 2] int64, computed from the merge plan alone: special
+ * tokens (0, 0), patch (y, x) -> (y + 1, x + 1), a merged window -> the truncated bfloat16 mean of its patches'
+ * positions (its centre).  Replaces merging the [B, S, N, 2] bfloat16 position tensor through the token merger and
+ * truncating it (src/accelerate/vggt/fused.py:113-129).  2-D layouts only.
+ */
+int come_packed_positions(const uint8_t *mask_dev, const int64_t *rev_id_dev, int64_t frames,
+                          const come_layout_t *layout, int64_t *pos_out_dev, void *stream);
+
+/*
  * Device status word: kernels that wait on hardware barriers give up after a bounded number of polls and
  * record a non-zero code here instead of hanging.  Reads it back (synchronises the device) and optionally
  * clears it.  Returns COME_OK with *value == 0 when no kernel reported a problem.

@@ -27,6 +27,11 @@ __all__ = [
     "attention_bias",
     "perkey_bias_from_weight",
     "max_seqlen",
+    "rope_tables",
+    "layer_norm_heads",
+    "rope_2d",
+    "qkv_prepare",
+    "packed_positions",
 ]
 
 
@@ -329,3 +334,117 @@ def attention_bias(q, k, v, bias, cu_seqlens, scale):
             out[s:e, h, :] = (p / l) @ v[s:e, h, :]
             lse[h, s:e] = (m + np.log(l))[:, 0]
     return out, lse
+
+
+# --------------------------------------------------------------------------------------------------------
+# pre-attention preparation of the packed qkv tensor: q/k LayerNorm over the head dimension, 2-D rotary
+# position embedding, per-key bias
+# --------------------------------------------------------------------------------------------------------
+def rope_tables(feature_dim: int, max_position: int, base_frequency: float = 100.0, kind: str = "bf16"):
+    """cos / sin tables ``[max_position, feature_dim]`` of the 1-D rotary embedding, in the run dtype.
+
+    ``RotaryPositionEmbedding2D._compute_frequency_components``
+    (``src/thirdparty/vggt/layers/rope.py:87-114``): ``inv_freq = 1 / base ** (arange(0, dim, 2) / dim)`` in
+    float32, ``angles = position * inv_freq`` in float32, ROUNDED TO THE RUN DTYPE, duplicated along the last
+    axis, then cos / sin evaluated and rounded to the run dtype again.
+    """
+    exponents = np.arange(0, feature_dim, 2, dtype=np.float32) / np.float32(feature_dim)
+    inv_freq = (np.float32(1.0) / np.power(np.float32(base_frequency), exponents, dtype=np.float32)).astype(np.float32)
+    positions = np.arange(max_position, dtype=np.float32)
+    angles = _round_like((positions[:, None] * inv_freq[None, :]).astype(np.float32), kind)
+    angles = np.concatenate([angles, angles], axis=-1)
+    return _round_like(np.cos(angles, dtype=np.float32), kind), _round_like(np.sin(angles, dtype=np.float32), kind)
+
+
+def _sum_lanes_of_8(x: np.ndarray) -> np.ndarray:
+    """Float32 sum over the last axis (a power of two >= 8) in a fixed order: left-to-right inside each run of
+    8 consecutive elements, then a pairwise tree over the runs.  The order is part of the oracle's definition
+    so that the CUDA kernel (8 elements per lane, butterfly over lanes) can be compared bit for bit."""
+    D = x.shape[-1]
+    r = x.reshape(x.shape[:-1] + (D // 8, 8)).astype(np.float32)
+    acc = r[..., 0].copy()
+    for i in range(1, 8):
+        acc = (acc + r[..., i]).astype(np.float32)
+    while acc.shape[-1] > 1:
+        acc = (acc[..., 0::2] + acc[..., 1::2]).astype(np.float32)
+    return acc[..., 0]
+
+
+def layer_norm_heads(x: np.ndarray, gamma: np.ndarray, beta: np.ndarray, eps: float, kind: str = "bf16"):
+    """``nn.LayerNorm(head_dim)`` applied to ``x[..., D]`` held in the run dtype (``q_norm`` / ``k_norm`` of
+    the attention module, called at ``src/accelerate/common/qkv.py:30-31``).
+
+    Statistics and the affine map are evaluated in float32 (as PyTorch does for 16-bit inputs), every
+    operation rounded separately: ``mean = sum / D``, ``var = sum((x - mean)^2) / D``,
+    ``rstd = 1 / sqrt(var + eps)``, ``y = gamma * (rstd * (x - mean)) + beta``, then rounded to the run dtype.
+    """
+    x = x.astype(np.float32)
+    D = x.shape[-1]
+    fD = np.float32(D)
+    mean = (_sum_lanes_of_8(x) / fD).astype(np.float32)
+    d = (x - mean[..., None]).astype(np.float32)
+    var = (_sum_lanes_of_8((d * d).astype(np.float32)) / fD).astype(np.float32)
+    rstd = (np.float32(1.0) / np.sqrt((var + np.float32(eps)).astype(np.float32))).astype(np.float32)
+    y = (rstd[..., None] * d).astype(np.float32)
+    y = (gamma.astype(np.float32) * y).astype(np.float32)
+    y = (y + beta.astype(np.float32)).astype(np.float32)
+    return _round_like(y, kind)
+
+
+def rope_2d(x: np.ndarray, pos: np.ndarray, cos_t: np.ndarray, sin_t: np.ndarray, kind: str = "bf16"):
+    """2-D rotary embedding of ``x[P, H, D]`` with integer positions ``pos[P, 2]`` (y, x).
+
+    ``RotaryPositionEmbedding2D.forward`` / ``_apply_1d_rope`` / ``_rotate_features``
+    (``src/thirdparty/vggt/layers/rope.py:116-187``): the first ``D/2`` features rotate with the y position,
+    the second ``D/2`` with the x position; inside a half, ``out = t * cos + rot(t) * sin`` with
+    ``rot(t) = cat(-t[D/4:], t[:D/4])``.  All three operations happen in the run dtype, i.e. each result is
+    rounded to it.
+    """
+    x = x.astype(np.float32)
+    P, H, D = x.shape
+    half, quarter = D // 2, D // 4
+    out = np.empty_like(x)
+    for axis in range(2):
+        t = x[:, :, axis * half:(axis + 1) * half]
+        rot = np.concatenate([-t[..., quarter:], t[..., :quarter]], axis=-1)
+        c = cos_t[pos[:, axis]][:, None, :]
+        s = sin_t[pos[:, axis]][:, None, :]
+        a = _round_like((t * c).astype(np.float32), kind)
+        b = _round_like((rot * s).astype(np.float32), kind)
+        out[:, :, axis * half:(axis + 1) * half] = _round_like((a + b).astype(np.float32), kind)
+    return out
+
+
+def qkv_prepare(qkv, q_gamma, q_beta, k_gamma, k_beta, eps, pos, cos_t, sin_t, kind="bf16"):
+    """``prepare_packed_self_attention_qkv`` without gradients (``src/accelerate/common/qkv.py:29-39``):
+    q and k of the packed ``[P, 3, H, D]`` tensor are layer-normalised over ``D`` (skipped when ``gamma`` is
+    None, the ``nn.Identity`` case), then rotated (skipped when ``pos`` is None); v is untouched."""
+    out = np.array(qkv, dtype=np.float32, copy=True)
+    for j, (g, b) in enumerate(((q_gamma, q_beta), (k_gamma, k_beta))):
+        y = out[:, j]
+        if g is not None:
+            y = layer_norm_heads(y, g, b, eps, kind)
+        if pos is not None:
+            y = rope_2d(y, pos, cos_t, sin_t, kind)
+        out[:, j] = y
+    return out
+
+
+def packed_positions(mask: np.ndarray, start_index: int, H: int, W: int, gh: int, gw: int) -> np.ndarray:
+    """Integer (y, x) position of every packed row after the merge, ``[P, 2]`` int64.
+
+    ``src/accelerate/vggt/fused.py:113-129``: special tokens sit at (0, 0), patch (y, x) at (y + 1, x + 1);
+    the position tensor is merged like the features in bfloat16 and truncated with ``.long()``.  The mean of
+    a ``gh x gw`` window of integer coordinates is ``first + (g - 1) / 2`` per axis; this function evaluates
+    exactly what the reference evaluates (float32 sum, division by the window size, bfloat16 rounding,
+    truncation) on the ragged layout.
+    """
+    mask = np.asarray(mask, dtype=bool)
+    B = mask.shape[0]
+    ys, xs = np.meshgrid(np.arange(H), np.arange(W), indexing="ij")
+    p = np.zeros((start_index + H * W, 2), np.float32)
+    p[start_index:, 0] = ys.reshape(-1) + 1
+    p[start_index:, 1] = xs.reshape(-1) + 1
+    pos = np.broadcast_to(p, (B,) + p.shape)
+    merged, _off, _rev, _w = token_merge_2d_ragged(_round_like(pos, "bf16"), start_index, gh, gw, H, W, mask)
+    return np.trunc(_round_like(merged, "bf16")).astype(np.int64)

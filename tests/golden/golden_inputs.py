@@ -125,3 +125,41 @@ def cfg1_inputs(frames: int = 8, channels: int = 1024):
     tokens = rng.standard_normal((frames, 5 + 37 * 37, channels), dtype=np.float32)
     conf = rng.random((frames, 37 * 37), dtype=np.float32)
     return tokens, conf
+
+
+# ---- pre-attention preparation (q/k LayerNorm + 2-D rotary embedding) -------------------------------------------
+PREPARE_CASES = [  # (P, H, D, dtype, use_norm, use_rope)
+    (150, 16, 64, "bf16", True, True),   # the attention shape of the headline configuration
+    (129, 4, 32, "f16", True, True),
+    (64, 2, 128, "bf16", True, True),
+    (100, 16, 64, "bf16", False, True),  # nn.Identity norms
+    (100, 16, 64, "f16", True, False),   # no rotary embedding
+]
+PREPARE_EPS = 1e-5          # nn.LayerNorm default, as the attention module builds q_norm / k_norm
+PREPARE_MAX_POSITION = 38   # 37 x 37 patch grid + 1
+
+
+def prepare_inputs(i: int, case):
+    """qkv [P,3,H,D], (q_gamma, q_beta, k_gamma, k_beta) [D] and positions [P,2]; floats exactly representable in
+    the case's dtype."""
+    P, H, D, kind, _norm, _rope = case
+    rng = np.random.default_rng(7700 + i)
+    qkv = round_kind(rng.standard_normal((P, 3, H, D), dtype=np.float32) * np.float32(1.5) + np.float32(0.3), kind)
+    params = [round_kind(np.float32(1.0) + np.float32(0.2) * rng.standard_normal(D, dtype=np.float32), kind),
+              round_kind(np.float32(0.1) * rng.standard_normal(D, dtype=np.float32), kind),
+              round_kind(np.float32(1.0) + np.float32(0.2) * rng.standard_normal(D, dtype=np.float32), kind),
+              round_kind(np.float32(0.1) * rng.standard_normal(D, dtype=np.float32), kind)]
+    pos = rng.integers(0, PREPARE_MAX_POSITION, size=(P, 2)).astype(np.int64)
+    return qkv, params, pos
+
+
+POSITION_CASES = [  # (frames, H, W, gh, gw, start_index): grids the reference's 2-D merger accepts (H % gh == 0)
+    (3, 36, 36, 3, 3, 5),
+    (2, 8, 12, 2, 3, 1),
+]
+
+
+def position_mask(i: int, case) -> np.ndarray:
+    frames, H, W, gh, gw, _s = case
+    rng = np.random.default_rng(7900 + i)
+    return rng.random((frames, (H // gh) * (W // gw))) < 0.5

@@ -28,7 +28,8 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
 from reference_cases import RANDOM_CONFIGS_1D, RANDOM_CONFIGS_2D, ATTENTION_CASES  # noqa: E402
 from golden_inputs import (  # noqa: E402
     merge1d_inputs, merge2d_inputs, select_inputs, SELECT_CASES, attention_inputs, EXTRA_ATTENTION_CASES,
-    cfg1_inputs, summarize_rows,
+    cfg1_inputs, summarize_rows, PREPARE_CASES, PREPARE_EPS, PREPARE_MAX_POSITION, prepare_inputs, POSITION_CASES,
+    position_mask,
 )
 
 
@@ -62,6 +63,15 @@ def import_reference(root: str):
     import test.auto_test.test_flex_attention_bias as attn_test
 
     return co_me, co_me_2d, CUDAExtension, attn_test
+
+
+def import_file(root: str, rel: str, name: str):
+    """A single reference source file as a module (its package __init__ pulls in unrelated model code)."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location(name, os.path.join(root, rel))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
 
 
 def main():
@@ -174,6 +184,62 @@ def main():
         assert np.allclose(o_out, out, atol=2e-6, rtol=1e-5), ("attention", case, np.abs(o_out - out).max())
         store[f"a{i}_out"] = out.astype(np.float32)
     np.savez_compressed(os.path.join(HERE, "attention.npz"), **store)
+
+    # ---- pre-attention preparation: the reference's prepare_packed_self_attention_qkv + rotary module ------
+    ref_qkv = import_file(args.reference, "src/accelerate/common/qkv.py", "ref_common_qkv")
+    ref_rope = import_file(args.reference, "src/thirdparty/vggt/layers/rope.py", "ref_vggt_rope")
+    store = {}
+    for i, case in enumerate(PREPARE_CASES):
+        P, Hh, D, kind, use_norm, use_rope = case
+        dt = {"bf16": torch.bfloat16, "f16": torch.float16}[kind]
+        qkv, params, pos = prepare_inputs(i, case)
+        norms = []
+        for j in range(2):
+            if use_norm:
+                n = torch.nn.LayerNorm(D, eps=PREPARE_EPS).to(dt)
+                with torch.no_grad():
+                    n.weight.copy_(t(params[2 * j]))
+                    n.bias.copy_(t(params[2 * j + 1]))
+            else:
+                n = torch.nn.Identity()
+            norms.append(n)
+        rope = ref_rope.RotaryPositionEmbedding2D(frequency=100.0) if use_rope else None
+        with torch.no_grad():
+            ref = ref_qkv.prepare_packed_self_attention_qkv(t(qkv).to(dt), norms[0], norms[1], rope,
+                                                            t(pos)[None] if use_rope else None, dt)
+        ref = ref.float().numpy()
+        cos_t, sin_t = orc.rope_tables(D // 2, PREPARE_MAX_POSITION, 100.0, kind)
+        if use_rope:  # the tables themselves must agree bit for bit
+            rc, rs = rope._compute_frequency_components(D // 2, PREPARE_MAX_POSITION, torch.device("cpu"), dt)
+            assert np.array_equal(rc.float().numpy(), cos_t) and np.array_equal(rs.float().numpy(), sin_t), case
+        ours = orc.qkv_prepare(qkv, *(params if use_norm else [None] * 4), PREPARE_EPS, pos if use_rope else None,
+                               cos_t, sin_t, kind)
+        # LayerNorm statistics are summed in another order by the reference's CPU kernel: a normalised value
+        # that lands next to a rounding boundary may differ by one unit in the last place of the run dtype, and
+        # the rotation mixes two such values: bound = 2 ulp at the head vector's largest magnitude
+        ulp = 2.0 * np.abs(ref).max(axis=-1, keepdims=True) * (2.0 ** -7 if kind == "bf16" else 2.0 ** -10)
+        assert np.all(np.abs(ours - ref) <= ulp), ("prepare", case, np.abs(ours - ref).max())
+        assert np.mean(ours != ref) < (1e-3 if use_norm else 1e-12), ("prepare", case, np.mean(ours != ref))
+        assert np.array_equal(ours[:, 2], ref[:, 2])
+        store[f"p{i}_qk"] = ref[:, :2].astype(np.float16 if kind == "f16" else np.float32).view(
+            np.uint16 if kind == "f16" else np.uint32)
+        if kind == "bf16":
+            store[f"p{i}_qk"] = (store[f"p{i}_qk"] >> 16).astype(np.uint16)  # bfloat16 bit patterns
+    # packed positions: the position tensor merged in bfloat16 by the reference's 2-D merger, truncated
+    for i, case in enumerate(POSITION_CASES):
+        frames, H, W, gh, gw, start = case
+        mask = position_mask(i, case)
+        ys, xs = np.meshgrid(np.arange(H), np.arange(W), indexing="ij")
+        p = np.zeros((start + H * W, 2), np.float32)
+        p[start:, 0] = ys.reshape(-1) + 1
+        p[start:, 1] = xs.reshape(-1) + 1
+        pos = t(np.broadcast_to(p, (frames,) + p.shape).copy()).to(torch.bfloat16)
+        with CUDAExtension.disable():
+            jag, _rev = co_me_2d.func_token_merge_2d(pos, start, gh, gw, H, W, t(mask))
+        ref_pos = jag.tokens[0].long().numpy()
+        assert np.array_equal(orc.packed_positions(mask, start, H, W, gh, gw), ref_pos), ("positions", case)
+        store[f"pos{i}"] = ref_pos.astype(np.int16)
+    np.savez_compressed(os.path.join(HERE, "prepare.npz"), **store)
 
     # ---- standalone op chain of the headline configuration (8 x 1374 tokens, 37x37 grid, 3x3 windows) ----
     tokens, conf = cfg1_inputs()

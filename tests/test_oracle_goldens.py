@@ -146,3 +146,62 @@ def test_cfg1_chain_fixture(golden_dir):
     o2 = orc.token_merge_2d_ragged(tokens[:, :, :64], 5, 3, 3, 37, 37, mask)
     np.testing.assert_array_equal(o2[0], out[:, :64])
     np.testing.assert_array_equal(o2[2], rev)
+
+
+def _prepare_fixture(z, i, kind):
+    """q, k of the fixture (stored as 16-bit patterns of the run dtype) as float32."""
+    raw = z[f"p{i}_qk"]
+    if kind == "f16":
+        return raw.view(np.float16).astype(np.float32)
+    return (raw.astype(np.uint32) << 16).view(np.float32)
+
+
+def prepare_tolerance(ref, kind):
+    """Bound used for LayerNorm + rotation against the reference: the reference's CPU LayerNorm sums its
+    statistics in another order, so a normalised value next to a rounding boundary may move by one unit in the
+    last place of the run dtype, and the rotation mixes two such values: 2 ulp at the head vector's largest
+    magnitude (bfloat16 ulp 2^-7 relative, float16 2^-10)."""
+    return 2.0 * np.abs(ref).max(axis=-1, keepdims=True) * (2.0 ** -7 if kind == "bf16" else 2.0 ** -10)
+
+
+@pytest.mark.parametrize("idx", range(len(gi.PREPARE_CASES)))
+def test_prepare_fixture(golden_dir, idx):
+    z = _load(golden_dir, "prepare.npz")
+    case = gi.PREPARE_CASES[idx]
+    P, H, D, kind, use_norm, use_rope = case
+    qkv, params, pos = gi.prepare_inputs(idx, case)
+    cos_t, sin_t = orc.rope_tables(D // 2, gi.PREPARE_MAX_POSITION, 100.0, kind)
+    out = orc.qkv_prepare(qkv, *(params if use_norm else [None] * 4), gi.PREPARE_EPS, pos if use_rope else None,
+                          cos_t, sin_t, kind)
+    ref = _prepare_fixture(z, idx, kind)
+    assert np.all(np.abs(out[:, :2] - ref) <= prepare_tolerance(ref, kind))
+    mismatched = np.mean(out[:, :2] != ref)
+    assert mismatched < (1e-3 if use_norm else 1e-12), mismatched  # rotation alone is bit-exact
+    np.testing.assert_array_equal(out[:, 2], qkv[:, 2])
+
+
+@pytest.mark.parametrize("idx", range(len(gi.POSITION_CASES)))
+def test_positions_fixture(golden_dir, idx):
+    z = _load(golden_dir, "prepare.npz")
+    case = gi.POSITION_CASES[idx]
+    frames, H, W, gh, gw, start = case
+    got = orc.packed_positions(gi.position_mask(idx, case), start, H, W, gh, gw)
+    np.testing.assert_array_equal(got, z[f"pos{idx}"].astype(np.int64))
+
+
+def test_positions_are_window_centres():
+    """Specials at (0, 0), kept patches at (y + 1, x + 1), a merged 3x3 window at its centre; ragged 37x37 grid."""
+    rng = np.random.default_rng(3)
+    mask = rng.random((2, 144)) < 0.5
+    pos = orc.packed_positions(mask, 5, 37, 37, 3, 3)
+    _out, off, rev, w = orc.token_merge_2d_ragged(np.zeros((2, 1374, 1), np.float32), 5, 3, 3, 37, 37, mask)
+    assert pos.shape == (off[-1], 2)
+    rev = rev.reshape(2, 1374)
+    for b in range(2):
+        assert (pos[rev[b, :5]] == 0).all()
+        for y, x in ((0, 0), (36, 36), (10, 36), (36, 3), (17, 20)):
+            row = rev[b, 5 + y * 37 + x]
+            if y < 36 and x < 36 and mask[b, (y // 3) * 12 + x // 3]:
+                assert tuple(pos[row]) == (3 * (y // 3) + 2, 3 * (x // 3) + 2) and w[row] == 9
+            else:
+                assert tuple(pos[row]) == (y + 1, x + 1) and w[row] == 1

@@ -1,0 +1,120 @@
+"""Pre-attention preparation on the GPU (come_qkv_prepare, come_packed_positions) against the oracle, bit for bit,
+and against fixtures written by the reference's prepare_packed_self_attention_qkv + rotary module on CPU."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import golden_inputs as gi
+from gpu_util import TORCH_DTYPE, to_dev, to_np
+from oracle import come_oracle as orc
+from test_oracle_goldens import _prepare_fixture, prepare_tolerance
+
+pytestmark = pytest.mark.gpu
+
+
+def _norm(D, gamma, beta, kind):
+    n = torch.nn.LayerNorm(D, eps=gi.PREPARE_EPS).cuda().to(TORCH_DTYPE[kind])
+    with torch.no_grad():
+        n.weight.copy_(to_dev(gamma, kind))
+        n.bias.copy_(to_dev(beta, kind))
+    return n
+
+
+def _run(qkv, params, pos, kind, use_norm, use_rope, weight=None, max_position=gi.PREPARE_MAX_POSITION):
+    from come_b200.qkv import RotaryPositionEmbedding2D, prepare_packed_self_attention_qkv
+    D = qkv.shape[-1]
+    qn = _norm(D, params[0], params[1], kind) if use_norm else torch.nn.Identity()
+    kn = _norm(D, params[2], params[3], kind) if use_norm else torch.nn.Identity()
+    rope = RotaryPositionEmbedding2D(100.0, max_position=max_position) if use_rope else None
+    t = to_dev(qkv, kind)
+    p = torch.from_numpy(pos).cuda()[None] if use_rope else None
+    w = None if weight is None else torch.from_numpy(weight).cuda()
+    res = prepare_packed_self_attention_qkv(t, qn, kn, rope, p, TORCH_DTYPE[kind], weight=w)
+    if weight is None:
+        assert res is t  # in place, like the reference's inference branch
+        return to_np(t), None
+    assert res[0] is t
+    return to_np(t), to_np(res[1])
+
+
+@pytest.mark.parametrize("idx", range(len(gi.PREPARE_CASES)))
+def test_prepare_fixture_and_oracle(golden_dir, idx):
+    z = np.load(os.path.join(golden_dir, "prepare.npz"))
+    case = gi.PREPARE_CASES[idx]
+    P, H, D, kind, use_norm, use_rope = case
+    qkv, params, pos = gi.prepare_inputs(idx, case)
+    got, _ = _run(qkv, params, pos, kind, use_norm, use_rope)
+    cos_t, sin_t = orc.rope_tables(D // 2, gi.PREPARE_MAX_POSITION, 100.0, kind)
+    want = orc.qkv_prepare(qkv, *(params if use_norm else [None] * 4), gi.PREPARE_EPS, pos if use_rope else None,
+                           cos_t, sin_t, kind)
+    np.testing.assert_array_equal(got, want)  # same order of float32 operations and roundings: bit-exact
+    ref = _prepare_fixture(z, idx, kind)
+    assert np.all(np.abs(got[:, :2] - ref) <= prepare_tolerance(ref, kind))
+    assert np.mean(got[:, :2] != ref) < (1e-3 if use_norm else 1e-12)
+
+
+@pytest.mark.parametrize("P,H,D,kind", [(6384, 16, 64, "bf16"), (1, 16, 64, "bf16"), (5, 8, 128, "f16"),
+                                        (1031, 12, 64, "f16"), (77, 16, 32, "bf16")])
+def test_prepare_oracle_sizes(P, H, D, kind):
+    rng = np.random.default_rng(P + H)
+    qkv = gi.round_kind(rng.standard_normal((P, 3, H, D), dtype=np.float32) * 2 - 0.5, kind)
+    params = [gi.round_kind(1 + 0.3 * rng.standard_normal(D, dtype=np.float32), kind),
+              gi.round_kind(0.2 * rng.standard_normal(D, dtype=np.float32), kind),
+              gi.round_kind(1 + 0.3 * rng.standard_normal(D, dtype=np.float32), kind),
+              gi.round_kind(0.2 * rng.standard_normal(D, dtype=np.float32), kind)]
+    pos = rng.integers(0, 38, size=(P, 2)).astype(np.int64)
+    weight = np.where(rng.random(P) < 0.3, np.float32(9), np.float32(1)).astype(np.float32)
+    got, bias = _run(qkv, params, pos, kind, True, True, weight=weight)
+    cos_t, sin_t = orc.rope_tables(D // 2, 38, 100.0, kind)
+    want = orc.qkv_prepare(qkv, *params, gi.PREPARE_EPS, pos, cos_t, sin_t, kind)
+    np.testing.assert_array_equal(got, want)
+    np.testing.assert_array_equal(bias, orc.perkey_bias_from_weight(weight, kind))
+
+
+def test_prepare_empty_and_errors():
+    from come_b200 import _lib
+    from come_b200.qkv import RotaryPositionEmbedding2D, prepare_packed_self_attention_qkv
+    empty = torch.empty(0, 3, 16, 64, device="cuda", dtype=torch.bfloat16)
+    ln = torch.nn.LayerNorm(64).cuda().bfloat16()
+    assert prepare_packed_self_attention_qkv(empty, ln, ln, None, None, torch.bfloat16) is empty
+    with pytest.raises(RuntimeError):  # run dtype mismatch
+        prepare_packed_self_attention_qkv(torch.zeros(4, 3, 16, 64, device="cuda"), ln, ln, None, None, torch.bfloat16)
+    with pytest.raises(NotImplementedError):  # float32 is not an attention dtype
+        prepare_packed_self_attention_qkv(torch.zeros(4, 3, 16, 64, device="cuda"), torch.nn.Identity(),
+                                          torch.nn.Identity(), None, None, torch.float32)
+    with pytest.raises(NotImplementedError):  # head_dim outside the supported set
+        prepare_packed_self_attention_qkv(torch.zeros(4, 3, 16, 48, device="cuda", dtype=torch.bfloat16),
+                                          torch.nn.Identity(), torch.nn.Identity(), None, None, torch.bfloat16)
+    with pytest.raises(RuntimeError):  # not contiguous
+        prepare_packed_self_attention_qkv(torch.zeros(4, 6, 16, 64, device="cuda", dtype=torch.bfloat16)[:, ::2],
+                                          ln, ln, None, None, torch.bfloat16)
+    # a position beyond the rotary table is clamped and reported through the device status word
+    _lib.device_status(clear=True)
+    t = torch.zeros(4, 3, 16, 64, device="cuda", dtype=torch.bfloat16)
+    pos = torch.tensor([[0, 1], [2, 99], [3, 3], [1, 1]], device="cuda")
+    prepare_packed_self_attention_qkv(t, ln, ln, RotaryPositionEmbedding2D(100.0, max_position=16), pos, torch.bfloat16)
+    assert _lib.device_status(clear=True) == 1 << 16
+    assert _lib.device_status(clear=True) == 0
+
+
+@pytest.mark.parametrize("idx", range(len(gi.POSITION_CASES)))
+def test_positions_fixture(golden_dir, idx):
+    from come_b200 import _lib
+    from come_b200.token_merger import MergePlan
+    z = np.load(os.path.join(golden_dir, "prepare.npz"))
+    case = gi.POSITION_CASES[idx]
+    frames, H, W, gh, gw, start = case
+    mask = gi.position_mask(idx, case)
+    plan = MergePlan(torch.from_numpy(mask).cuda(), _lib.Layout.two_d(start, H, W, gh, gw))
+    np.testing.assert_array_equal(to_np(plan.positions()), z[f"pos{idx}"].astype(np.int64))
+
+
+def test_positions_ragged_grid():
+    from come_b200 import _lib
+    from come_b200.token_merger import MergePlan
+    rng = np.random.default_rng(11)
+    mask = rng.random((8, 144)) < 0.5
+    plan = MergePlan(torch.from_numpy(mask).cuda(), _lib.Layout.two_d(5, 37, 37, 3, 3))
+    np.testing.assert_array_equal(to_np(plan.positions()), orc.packed_positions(mask, 5, 37, 37, 3, 3))
