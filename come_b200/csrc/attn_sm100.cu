@@ -246,26 +246,6 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
-// ---- packed float32x2 arithmetic (one instruction for two lanes: halves the issue slots of the softmax) ----------
-typedef unsigned long long f32x2_t;
-__device__ __forceinline__ f32x2_t pack_f32x2(float lo, float hi) {
-    f32x2_t d;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "f"(lo), "f"(hi));
-    return d;
-}
-__device__ __forceinline__ void unpack_f32x2(f32x2_t v, float &lo, float &hi) {
-    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
-}
-__device__ __forceinline__ f32x2_t fma_f32x2(f32x2_t a, f32x2_t b, f32x2_t c) {
-    f32x2_t d;
-    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
-    return d;
-}
-__device__ __forceinline__ f32x2_t add_f32x2(f32x2_t a, f32x2_t b) {
-    f32x2_t d;
-    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-    return d;
-}
 // 2^x for two values on the FMA / integer pipes instead of the special-function unit (which is the bottleneck of
 // the head_dim-64 kernel): round-to-nearest range reduction x = n + f, f in [-0.5, 0.5], cubic fit of 2^f (relative
 // error 1.0e-4, far below the 16-bit rounding of the probabilities), n added to the exponent field as an integer.

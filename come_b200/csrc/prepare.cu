@@ -44,8 +44,9 @@ template <typename T> struct Vec8 {
 };
 
 // Sum over the `lanes` consecutive lanes that hold one head vector: butterfly, identical in every lane.
-__device__ __forceinline__ float group_sum(float v, int lanes) {
-    for (int m = 1; m < lanes; m <<= 1) v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, m));
+template <int LANES> __device__ __forceinline__ float group_sum(float v) {
+#pragma unroll
+    for (int m = 1; m < LANES; m <<= 1) v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, m));
     return v;
 }
 
@@ -53,59 +54,67 @@ __device__ __forceinline__ float group_sum(float v, int lanes) {
 // of q or of k for every row the CTA visits, so its gamma / beta stay in registers.
 //
 // Rounding sequence (identical to evaluating the reference's tensor expressions in the run dtype):
-//   LayerNorm in float32, one rounding per operation, result rounded to T;
+//   LayerNorm in float32: sums of x and of (x - mean)^2 in a fixed order (the squares accumulated with fused
+//   multiply-adds), y = fma(gamma, rstd * (x - mean), beta), result rounded to T;
 //   rotation: a = T(t * cos), b = T(rot(t) * sin), out = T(a + b).  Products of two 16-bit floats are exact in float32,
 //   so the packed 16-bit multiply (one rounding) equals "multiply in float32, round to T"; likewise the packed add.
-template <typename T>
+template <typename T, int D>
 __global__ void __launch_bounds__(512, 2)
-qkv_prepare_kernel(T *__restrict__ qkv, int64_t total, int H, int D, const T *__restrict__ q_gamma,
+qkv_prepare_kernel(T *__restrict__ qkv, int total, int H, const T *__restrict__ q_gamma,
                    const T *__restrict__ q_beta, const T *__restrict__ k_gamma, const T *__restrict__ k_beta, float eps,
                    const int64_t *__restrict__ pos, const T *__restrict__ cos_t, const T *__restrict__ sin_t,
                    int table_rows, const float *__restrict__ weight, T *__restrict__ bias_out,
                    unsigned int *__restrict__ status) {
     using P2 = Pair<T>;
-    const int lanes = D >> 3;             // lanes per head vector (power of two, 4..32)
+    constexpr int lanes = D >> 3;         // lanes per head vector (power of two, 4..32)
     const int hv = threadIdx.x / lanes;   // 0 .. 2H-1
     const int lane = threadIdx.x - hv * lanes;
     const int which = hv / H;             // 0 = q, 1 = k
     const int head = hv - which * H;
     const int feat = lane * 8;            // first feature of this lane inside the head
-    const int half = D >> 1;
+    constexpr int half = D >> 1;
     const int axis = feat >= half ? 1 : 0;   // y for the first half of the features, x for the second
     const int f_in_half = feat - axis * half;
-    const int partner = lanes >> 2;          // lane distance of the rotation partner (D/4 features)
+    constexpr int partner = lanes >> 2;      // lane distance of the rotation partner (D/4 features)
     // second quarter of a half: rot = +t[f - D/4]; first quarter: rot = -t[f + D/4] (sign bits of both 16-bit halves)
     const uint32_t rot_sign = f_in_half >= (D >> 2) ? 0u : 0x80008000u;
-    const int64_t row_elems = 3ll * H * D;
-    const int64_t col = (int64_t)which * H * D + (int64_t)head * D + feat;
-    const float inv_D = 1.0f / (float)D;  // D is a power of two: multiplying by 1/D rounds like dividing by D
+    // 32-bit indexing in elements is safe: the host checks total * 3 * H * D < 2^31
+    const int row_elems = 3 * H * D;
+    const int col = which * H * D + head * D + feat;
+    constexpr float inv_D = 1.0f / (float)D;  // D is a power of two: multiplying by 1/D rounds like dividing by D
 
     const T *gamma = which ? k_gamma : q_gamma;
     const T *beta = which ? k_beta : q_beta;
-    Vec8<T> g, b;
-    g.zero();
-    b.zero();
+    f32x2_t g2[4], b2[4];  // this thread's 8 gamma / beta values as float32 pairs
+#pragma unroll
+    for (int j = 0; j < 4; ++j) g2[j] = b2[j] = 0ull;
     if (gamma) {
+        Vec8<T> g, b;
         g.load(gamma + feat);
         b.load(beta + feat);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 gg = P2::to_f32(g.pair(j)), bb = P2::to_f32(b.pair(j));
+            g2[j] = pack_f32x2(gg.x, gg.y);
+            b2[j] = pack_f32x2(bb.x, bb.y);
+        }
     }
 
-    for (int64_t r0 = (int64_t)blockIdx.x * kPrepRowsInFlight; r0 < total; r0 += (int64_t)gridDim.x * kPrepRowsInFlight) {
+    for (int r0 = blockIdx.x * kPrepRowsInFlight; r0 < total; r0 += gridDim.x * kPrepRowsInFlight) {
         Vec8<T> x[kPrepRowsInFlight];
         int p[kPrepRowsInFlight];
 #pragma unroll
         for (int i = 0; i < kPrepRowsInFlight; ++i) {
-            const int64_t r = r0 + i;
+            const int r = r0 + i;
             p[i] = 0;
             if (r < total) {
                 x[i].load(qkv + r * row_elems + col);
                 if (pos) {
                     const int64_t pp = __ldg(pos + 2 * r + axis);
-                    if (pp < 0 || pp >= table_rows) {
+                    p[i] = (int)pp;
+                    if ((uint64_t)pp >= (uint64_t)table_rows) {  // negative or past the table
                         if (hv == 0 && f_in_half == 0) atomicOr(status, kErrPositionRange);
                         p[i] = pp < 0 ? 0 : table_rows - 1;
-                    } else {
-                        p[i] = (int)pp;
                     }
                 }
             } else {
@@ -114,39 +123,43 @@ qkv_prepare_kernel(T *__restrict__ qkv, int64_t total, int H, int D, const T *__
         }
 #pragma unroll
         for (int i = 0; i < kPrepRowsInFlight; ++i) {
-            const int64_t r = r0 + i;
+            const int r = r0 + i;
             const bool live = r < total;  // the whole CTA agrees: the shuffles below stay convergent
             Vec8<T> y = x[i];
             if (gamma) {
-                float f[8];
+                // float32 pairs (f0,f1) (f2,f3) (f4,f5) (f6,f7): the even and the odd features are summed as two
+                // left-to-right chains by packed adds, then added together
+                f32x2_t v[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    const float2 v = P2::to_f32(x[i].pair(j));
-                    f[2 * j] = v.x;
-                    f[2 * j + 1] = v.y;
+                    const float2 t = P2::to_f32(x[i].pair(j));
+                    v[j] = pack_f32x2(t.x, t.y);
                 }
-                float sum = f[0];
+                f32x2_t acc = add_f32x2(add_f32x2(add_f32x2(v[0], v[1]), v[2]), v[3]);
+                float even, odd;
+                unpack_f32x2(acc, even, odd);
+                const float mean = __fmul_rn(group_sum<lanes>(__fadd_rn(even, odd)), inv_D);
+                const f32x2_t neg_mean = pack_f32x2(-mean, -mean);
 #pragma unroll
-                for (int j = 1; j < 8; ++j) sum = __fadd_rn(sum, f[j]);
-                const float mean = __fmul_rn(group_sum(sum, lanes), inv_D);
+                for (int j = 0; j < 4; ++j) v[j] = add_f32x2(v[j], neg_mean);
+                acc = mul_f32x2(v[0], v[0]);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) f[j] = __fsub_rn(f[j], mean);
-                float sq = __fmul_rn(f[0], f[0]);
-#pragma unroll
-                for (int j = 1; j < 8; ++j) sq = __fadd_rn(sq, __fmul_rn(f[j], f[j]));
-                const float var = __fmul_rn(group_sum(sq, lanes), inv_D);
+                for (int j = 1; j < 4; ++j) acc = fma_f32x2(v[j], v[j], acc);
+                unpack_f32x2(acc, even, odd);
+                const float var = __fmul_rn(group_sum<lanes>(__fadd_rn(even, odd)), inv_D);
                 const float rstd = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(var, eps)));
+                const f32x2_t rstd2 = pack_f32x2(rstd, rstd);
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    const float2 gg = P2::to_f32(g.pair(j)), bb = P2::to_f32(b.pair(j));
-                    y.set(j, P2::from_f32(__fadd_rn(__fmul_rn(gg.x, __fmul_rn(rstd, f[2 * j])), bb.x),
-                                          __fadd_rn(__fmul_rn(gg.y, __fmul_rn(rstd, f[2 * j + 1])), bb.y)));
+                    float lo, hi;
+                    unpack_f32x2(fma_f32x2(g2[j], mul_f32x2(rstd2, v[j]), b2[j]), lo, hi);
+                    y.set(j, P2::from_f32(lo, hi));
                 }
             }
             if (pos) {
                 Vec8<T> c, s, o;
-                c.load_ro(cos_t + (int64_t)p[i] * half + f_in_half);
-                s.load_ro(sin_t + (int64_t)p[i] * half + f_in_half);
+                c.load_ro(cos_t + p[i] * half + f_in_half);
+                s.load_ro(sin_t + p[i] * half + f_in_half);
 #pragma unroll
                 for (int j = 0; j < 4; ++j) o.w[j] = __shfl_xor_sync(0xffffffffu, y.w[j], partner) ^ rot_sign;
 #pragma unroll
@@ -202,20 +215,40 @@ __global__ void packed_positions_kernel(const uint8_t *__restrict__ mask, const 
     }
 }
 
+template <typename T, int D>
+static int launch_prepare_d(void *qkv, int64_t total, int H, const void *qg, const void *qb, const void *kg,
+                            const void *kb, float eps, const int64_t *pos, const void *cos_t, const void *sin_t,
+                            int table_rows, const float *weight, void *bias_out, cudaStream_t st) {
+    unsigned int *status = status_word_dev();
+    if (!status) return COME_ERR_CUDA;
+    const int threads = 2 * H * (D / 8);
+    int resident = 0;  // CTAs of this size that fit one SM: the grid is exactly one resident wave
+    COME_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, qkv_prepare_kernel<T, D>, threads, 0));
+    if (resident < 1) resident = 1;
+    const int64_t iters = (total + kPrepRowsInFlight - 1) / kPrepRowsInFlight;
+    const int64_t wave = (int64_t)sm_count() * resident;
+    const unsigned grid = (unsigned)(iters < wave ? iters : wave);
+    qkv_prepare_kernel<T, D><<<grid, threads, 0, st>>>((T *)qkv, (int)total, H, (const T *)qg, (const T *)qb,
+                                                      (const T *)kg, (const T *)kb, eps, pos, (const T *)cos_t,
+                                                      (const T *)sin_t, table_rows, weight, (T *)bias_out, status);
+    return check_launch("come_qkv_prepare");
+}
+
 template <typename T>
 static int launch_prepare(void *qkv, int64_t total, int H, int D, const void *qg, const void *qb, const void *kg,
                           const void *kb, float eps, const int64_t *pos, const void *cos_t, const void *sin_t,
                           int table_rows, const float *weight, void *bias_out, cudaStream_t st) {
-    unsigned int *status = status_word_dev();
-    if (!status) return COME_ERR_CUDA;
-    const int threads = 2 * H * (D / 8);
-    const int64_t iters = (total + kPrepRowsInFlight - 1) / kPrepRowsInFlight;
-    const int64_t resident = (int64_t)sm_count() * (2048 / threads > 0 ? 2048 / threads : 1);
-    const unsigned grid = (unsigned)(iters < resident ? iters : resident);
-    qkv_prepare_kernel<T><<<grid, threads, 0, st>>>((T *)qkv, total, H, D, (const T *)qg, (const T *)qb, (const T *)kg,
-                                                   (const T *)kb, eps, pos, (const T *)cos_t, (const T *)sin_t,
-                                                   table_rows, weight, (T *)bias_out, status);
-    return check_launch("come_qkv_prepare");
+#define COME_PREP_CASE(DD) \
+    case DD: return launch_prepare_d<T, DD>(qkv, total, H, qg, qb, kg, kb, eps, pos, cos_t, sin_t, table_rows, weight, bias_out, st)
+    switch (D) {
+        COME_PREP_CASE(32);
+        COME_PREP_CASE(64);
+        COME_PREP_CASE(128);
+        COME_PREP_CASE(256);
+    }
+#undef COME_PREP_CASE
+    set_error("come_qkv_prepare: unsupported head_dim %d", D);
+    return COME_ERR_UNSUPPORTED;
 }
 
 }  // namespace come
@@ -250,6 +283,8 @@ extern "C" int come_qkv_prepare(void *qkv_dev, int dtype, int64_t total, int num
                      "cos / sin tables must be 16-byte aligned");
     }
     if (total == 0) return COME_OK;
+    COME_REQUIRE(total * 3 * (int64_t)num_heads * head_dim < (1ll << 31),
+                 "come_qkv_prepare indexes with 32 bits: total * 3 * num_heads * head_dim must be < 2^31");
     COME_REQUIRE(qkv_dev != nullptr, "qkv must not be NULL");
     COME_REQUIRE((uintptr_t)qkv_dev % 16 == 0, "qkv must be 16-byte aligned");
     COME_REQUIRE(!q_gamma_dev || ((uintptr_t)q_gamma_dev % 16 == 0 && (uintptr_t)q_beta_dev % 16 == 0 &&

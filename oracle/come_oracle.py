@@ -357,14 +357,37 @@ def rope_tables(feature_dim: int, max_position: int, base_frequency: float = 100
 
 
 def _sum_lanes_of_8(x: np.ndarray) -> np.ndarray:
-    """Float32 sum over the last axis (a power of two >= 8) in a fixed order: left-to-right inside each run of
-    8 consecutive elements, then a pairwise tree over the runs.  The order is part of the oracle's definition
-    so that the CUDA kernel (8 elements per lane, butterfly over lanes) can be compared bit for bit."""
+    """Float32 sum over the last axis (a power of two >= 8) in a fixed order: inside each run of 8 consecutive
+    elements the even-indexed and the odd-indexed elements are summed left to right as two chains and the two
+    chains added; then a pairwise tree over the runs.  The order is part of the oracle's definition so that the
+    CUDA kernel (8 elements per lane summed with packed two-lane adds, butterfly over lanes) can be compared bit
+    for bit; any other order moves a result by at most one rounding."""
     D = x.shape[-1]
-    r = x.reshape(x.shape[:-1] + (D // 8, 8)).astype(np.float32)
-    acc = r[..., 0].copy()
-    for i in range(1, 8):
-        acc = (acc + r[..., i]).astype(np.float32)
+    r = x.reshape(x.shape[:-1] + (D // 8, 4, 2)).astype(np.float32)
+    acc = r[..., 0, :].copy()
+    for i in range(1, 4):
+        acc = (acc + r[..., i, :]).astype(np.float32)
+    acc = (acc[..., 0] + acc[..., 1]).astype(np.float32)
+    while acc.shape[-1] > 1:
+        acc = (acc[..., 0::2] + acc[..., 1::2]).astype(np.float32)
+    return acc[..., 0]
+
+
+def _fma32(a: np.ndarray, b: np.ndarray, c: np.ndarray) -> np.ndarray:
+    """Fused multiply-add of float32 values: the product of two float32 is exact in float64, so only the final
+    float64 -> float32 conversion can round twice (odds ~2^-29 per operation, and then by one float32 ulp)."""
+    return (a.astype(np.float64) * b.astype(np.float64) + c.astype(np.float64)).astype(np.float32)
+
+
+def _sumsq_lanes_of_8(d: np.ndarray) -> np.ndarray:
+    """Sum of squares in the order of :func:`_sum_lanes_of_8`, each chain accumulated with fused multiply-adds:
+    ``acc = d0 * d0`` (rounded), then ``acc = fma(d_i, d_i, acc)``."""
+    D = d.shape[-1]
+    r = d.reshape(d.shape[:-1] + (D // 8, 4, 2)).astype(np.float32)
+    acc = (r[..., 0, :] * r[..., 0, :]).astype(np.float32)
+    for i in range(1, 4):
+        acc = _fma32(r[..., i, :], r[..., i, :], acc)
+    acc = (acc[..., 0] + acc[..., 1]).astype(np.float32)
     while acc.shape[-1] > 1:
         acc = (acc[..., 0::2] + acc[..., 1::2]).astype(np.float32)
     return acc[..., 0]
@@ -374,20 +397,21 @@ def layer_norm_heads(x: np.ndarray, gamma: np.ndarray, beta: np.ndarray, eps: fl
     """``nn.LayerNorm(head_dim)`` applied to ``x[..., D]`` held in the run dtype (``q_norm`` / ``k_norm`` of
     the attention module, called at ``src/accelerate/common/qkv.py:30-31``).
 
-    Statistics and the affine map are evaluated in float32 (as PyTorch does for 16-bit inputs), every
-    operation rounded separately: ``mean = sum / D``, ``var = sum((x - mean)^2) / D``,
-    ``rstd = 1 / sqrt(var + eps)``, ``y = gamma * (rstd * (x - mean)) + beta``, then rounded to the run dtype.
+    Statistics and the affine map are evaluated in float32 (as PyTorch does for 16-bit inputs):
+    ``mean = sum(x) / D``, ``var = sum((x - mean)^2) / D`` (two passes), ``rstd = 1 / sqrt(var + eps)``,
+    ``y = fma(gamma, rstd * (x - mean), beta)``, then rounded to the run dtype.  PyTorch's own kernels order the
+    sums differently (and differently on CPU and GPU), which moves a result by at most one unit in the last place
+    of the run dtype; the order chosen here is the CUDA kernel's, so that the two compare bit for bit.
     """
     x = x.astype(np.float32)
     D = x.shape[-1]
-    fD = np.float32(D)
-    mean = (_sum_lanes_of_8(x) / fD).astype(np.float32)
+    inv_d = np.float32(1.0) / np.float32(D)  # exact: D is a power of two
+    mean = (_sum_lanes_of_8(x) * inv_d).astype(np.float32)
     d = (x - mean[..., None]).astype(np.float32)
-    var = (_sum_lanes_of_8((d * d).astype(np.float32)) / fD).astype(np.float32)
+    var = (_sumsq_lanes_of_8(d) * inv_d).astype(np.float32)
     rstd = (np.float32(1.0) / np.sqrt((var + np.float32(eps)).astype(np.float32))).astype(np.float32)
     y = (rstd[..., None] * d).astype(np.float32)
-    y = (gamma.astype(np.float32) * y).astype(np.float32)
-    y = (y + beta.astype(np.float32)).astype(np.float32)
+    y = _fma32(np.broadcast_to(gamma.astype(np.float32), y.shape), y, np.broadcast_to(beta.astype(np.float32), y.shape))
     return _round_like(y, kind)
 
 
