@@ -339,7 +339,7 @@ constexpr int kUnmergeBatch = 4;
 template <typename V>
 __global__ void __launch_bounds__(kUnmergeThreads)
 unmerge_kernel(const V *__restrict__ merged, const int64_t *__restrict__ rev, int64_t total, int64_t Cv,
-               V *__restrict__ out) {
+               V *__restrict__ out, int64_t out_stride) {
     const int64_t n = total * Cv;
     const int64_t stride = (int64_t)gridDim.x * kUnmergeThreads;
     for (int64_t i0 = (int64_t)blockIdx.x * kUnmergeThreads + threadIdx.x; i0 < n; i0 += stride * kUnmergeBatch) {
@@ -355,7 +355,10 @@ unmerge_kernel(const V *__restrict__ merged, const int64_t *__restrict__ rev, in
 #pragma unroll
         for (int k = 0; k < kUnmergeBatch; ++k) {
             const int64_t i = i0 + k * stride;
-            if (i < n) st_stream(out + i, buf[k]);
+            if (i < n) {
+                const int64_t row = i / Cv, v = i - row * Cv;
+                st_stream(out + row * out_stride + v, buf[k]);
+            }
         }
     }
 }
@@ -367,7 +370,8 @@ constexpr int kRowBatch = 4;
 
 template <typename V>
 __global__ void __launch_bounds__(kUnmergeThreads)
-unmerge_rows_kernel(const V *__restrict__ merged, const int64_t *__restrict__ rev, int total, int Cv, V *__restrict__ out) {
+unmerge_rows_kernel(const V *__restrict__ merged, const int64_t *__restrict__ rev, int total, int Cv, V *__restrict__ out,
+                    int64_t out_stride) {
     const int rows_per_group = kUnmergeThreads / Cv;
     const int sub = threadIdx.x / Cv, v = threadIdx.x - sub * Cv;
     const int rows_per_round = rows_per_group * kRowBatch;
@@ -385,7 +389,7 @@ unmerge_rows_kernel(const V *__restrict__ merged, const int64_t *__restrict__ re
 #pragma unroll
         for (int k = 0; k < kRowBatch; ++k) {
             const int row = row0 + k * rows_per_group + sub;
-            if (row < total) st_stream(out + (int64_t)row * Cv + v, buf[k]);
+            if (row < total) st_stream(out + (int64_t)row * out_stride + v, buf[k]);
         }
     }
 }
@@ -532,13 +536,14 @@ extern "C" int come_merge(const void *tokens_dev, int dtype, int64_t frames, int
 }
 
 template <typename V>
-static int launch_unmerge(const void *merged, const int64_t *rev, int64_t total, int64_t Cv, void *out, cudaStream_t st) {
+static int launch_unmerge(const void *merged, const int64_t *rev, int64_t total, int64_t Cv, void *out, int64_t out_stride,
+                          cudaStream_t st) {
     if (Cv <= kUnmergeThreads && kUnmergeThreads % Cv == 0 && total < (1ll << 31)) {
         const int rows_per_round = (kUnmergeThreads / (int)Cv) * kRowBatch;
         int64_t blocks = (total + rows_per_round - 1) / rows_per_round;
         const int64_t max_blocks = (int64_t)sm_count() * 8;
         if (blocks > max_blocks) blocks = max_blocks;
-        unmerge_rows_kernel<V><<<(unsigned)blocks, kUnmergeThreads, 0, st>>>((const V *)merged, rev, (int)total, (int)Cv, (V *)out);
+        unmerge_rows_kernel<V><<<(unsigned)blocks, kUnmergeThreads, 0, st>>>((const V *)merged, rev, (int)total, (int)Cv, (V *)out, out_stride);
         return check_launch("come_unmerge");
     }
     const int64_t n = total * Cv;
@@ -546,23 +551,32 @@ static int launch_unmerge(const void *merged, const int64_t *rev, int64_t total,
     int64_t blocks = (n + per_block - 1) / per_block;
     const int64_t max_blocks = (int64_t)sm_count() * 8;
     if (blocks > max_blocks) blocks = max_blocks;
-    unmerge_kernel<V><<<(unsigned)blocks, kUnmergeThreads, 0, st>>>((const V *)merged, rev, total, Cv, (V *)out);
+    unmerge_kernel<V><<<(unsigned)blocks, kUnmergeThreads, 0, st>>>((const V *)merged, rev, total, Cv, (V *)out, out_stride);
     return check_launch("come_unmerge");
+}
+
+extern "C" int come_unmerge_strided(const void *merged_dev, const int64_t *rev_id_dev, int64_t total, int64_t channels,
+                                    int dtype, void *out_dev, int64_t out_row_stride, void *stream) {
+    COME_REQUIRE(total >= 0 && channels >= 0, "total and channels must be >= 0");
+    COME_REQUIRE(dtype == COME_F32 || dtype == COME_F16 || dtype == COME_BF16, "unknown dtype %d", dtype);
+    COME_REQUIRE(out_row_stride >= channels, "out_row_stride (%lld) must be >= channels (%lld)", (long long)out_row_stride,
+                 (long long)channels);
+    if (total == 0 || channels == 0) return COME_OK;
+    COME_REQUIRE(merged_dev && rev_id_dev && out_dev, "merged / rev_id / out must not be NULL");
+    cudaStream_t st = (cudaStream_t)stream;
+    const size_t es = dtype_size(dtype);
+    const size_t row_bytes = (size_t)channels * es, stride_bytes = (size_t)out_row_stride * es;
+    const uintptr_t m = (uintptr_t)merged_dev, o = (uintptr_t)out_dev;
+    if (row_bytes % 16 == 0 && stride_bytes % 16 == 0 && m % 16 == 0 && o % 16 == 0)
+        return launch_unmerge<uint4>(merged_dev, rev_id_dev, total, row_bytes / 16, out_dev, stride_bytes / 16, st);
+    if (row_bytes % 4 == 0 && stride_bytes % 4 == 0 && m % 4 == 0 && o % 4 == 0)
+        return launch_unmerge<uint32_t>(merged_dev, rev_id_dev, total, row_bytes / 4, out_dev, stride_bytes / 4, st);
+    return launch_unmerge<uint16_t>(merged_dev, rev_id_dev, total, row_bytes / 2, out_dev, stride_bytes / 2, st);
 }
 
 extern "C" int come_unmerge(const void *merged_dev, const int64_t *rev_id_dev, int64_t total, int64_t channels,
                             int dtype, void *out_dev, void *stream) {
-    COME_REQUIRE(total >= 0 && channels >= 0, "total and channels must be >= 0");
-    COME_REQUIRE(dtype == COME_F32 || dtype == COME_F16 || dtype == COME_BF16, "unknown dtype %d", dtype);
-    if (total == 0 || channels == 0) return COME_OK;
-    COME_REQUIRE(merged_dev && rev_id_dev && out_dev, "merged / rev_id / out must not be NULL");
-    cudaStream_t st = (cudaStream_t)stream;
-    const size_t row_bytes = (size_t)channels * dtype_size(dtype);
-    const bool aligned = ((uintptr_t)merged_dev % 16 == 0) && ((uintptr_t)out_dev % 16 == 0);
-    if (row_bytes % 16 == 0 && aligned) return launch_unmerge<uint4>(merged_dev, rev_id_dev, total, row_bytes / 16, out_dev, st);
-    if (row_bytes % 4 == 0 && ((uintptr_t)merged_dev % 4 == 0) && ((uintptr_t)out_dev % 4 == 0))
-        return launch_unmerge<uint32_t>(merged_dev, rev_id_dev, total, row_bytes / 4, out_dev, st);
-    return launch_unmerge<uint16_t>(merged_dev, rev_id_dev, total, row_bytes / 2, out_dev, st);
+    return come_unmerge_strided(merged_dev, rev_id_dev, total, channels, dtype, out_dev, channels, stream);
 }
 
 extern "C" int come_device_status(uint32_t *value, int clear) {

@@ -5,6 +5,8 @@
 //
 // Bandwidth-bound: q and k are read and written once (v is never touched), 16 bytes per lane, several rows in
 // flight per CTA.  The arithmetic follows the reference's sequence of roundings exactly (see the oracle).
+#include <type_traits>
+
 #include "come_internal.cuh"
 
 namespace come {
@@ -58,8 +60,11 @@ template <int LANES> __device__ __forceinline__ float group_sum(float v) {
 //   multiply-adds), y = fma(gamma, rstd * (x - mean), beta), result rounded to T;
 //   rotation: a = T(t * cos), b = T(rot(t) * sin), out = T(a + b).  Products of two 16-bit floats are exact in float32,
 //   so the packed 16-bit multiply (one rounding) equals "multiply in float32, round to T"; likewise the packed add.
-template <typename T, int D>
-__global__ void __launch_bounds__(512, 2)
+// Largest CTA the kernel is compiled for (64 registers per thread: four 256-thread CTAs per SM).
+template <int D> constexpr int prep_max_threads() { return 512; }
+
+template <typename T, int D, bool NORM, bool ROPE>
+__global__ void __launch_bounds__(prep_max_threads<D>(), 2)
 qkv_prepare_kernel(T *__restrict__ qkv, int total, int H, const T *__restrict__ q_gamma,
                    const T *__restrict__ q_beta, const T *__restrict__ k_gamma, const T *__restrict__ k_beta, float eps,
                    const int64_t *__restrict__ pos, const T *__restrict__ cos_t, const T *__restrict__ sin_t,
@@ -88,7 +93,7 @@ qkv_prepare_kernel(T *__restrict__ qkv, int total, int H, const T *__restrict__ 
     f32x2_t g2[4], b2[4];  // this thread's 8 gamma / beta values as float32 pairs
 #pragma unroll
     for (int j = 0; j < 4; ++j) g2[j] = b2[j] = 0ull;
-    if (gamma) {
+    if constexpr (NORM) {
         Vec8<T> g, b;
         g.load(gamma + feat);
         b.load(beta + feat);
@@ -100,16 +105,17 @@ qkv_prepare_kernel(T *__restrict__ qkv, int total, int H, const T *__restrict__ 
         }
     }
 
-    for (int r0 = blockIdx.x * kPrepRowsInFlight; r0 < total; r0 += gridDim.x * kPrepRowsInFlight) {
-        Vec8<T> x[kPrepRowsInFlight];
-        int p[kPrepRowsInFlight];
+    // Loads of one batch of kPrepRowsInFlight rows.  FULL batches (every row inside the tensor) carry no per-row
+    // bounds checks; only the last batch of the tensor can be partial.
+    auto load_batch = [&](auto full_tag, int r0, Vec8<T>(&x)[kPrepRowsInFlight], int(&p)[kPrepRowsInFlight]) {
+        constexpr bool FULL = decltype(full_tag)::value;
 #pragma unroll
         for (int i = 0; i < kPrepRowsInFlight; ++i) {
             const int r = r0 + i;
             p[i] = 0;
-            if (r < total) {
+            if (FULL || r < total) {
                 x[i].load(qkv + r * row_elems + col);
-                if (pos) {
+                if constexpr (ROPE) {
                     const int64_t pp = __ldg(pos + 2 * r + axis);
                     p[i] = (int)pp;
                     if ((uint64_t)pp >= (uint64_t)table_rows) {  // negative or past the table
@@ -121,12 +127,16 @@ qkv_prepare_kernel(T *__restrict__ qkv, int total, int H, const T *__restrict__ 
                 x[i].zero();
             }
         }
+    };
+    // Arithmetic and stores of one loaded batch.
+    auto finish_batch = [&](auto full_tag, int r0, const Vec8<T>(&x)[kPrepRowsInFlight], const int(&p)[kPrepRowsInFlight]) {
+        constexpr bool FULL = decltype(full_tag)::value;
 #pragma unroll
         for (int i = 0; i < kPrepRowsInFlight; ++i) {
             const int r = r0 + i;
-            const bool live = r < total;  // the whole CTA agrees: the shuffles below stay convergent
+            const bool live = FULL || r < total;  // the whole CTA agrees: the shuffles below stay convergent
             Vec8<T> y = x[i];
-            if (gamma) {
+            if constexpr (NORM) {
                 // float32 pairs (f0,f1) (f2,f3) (f4,f5) (f6,f7): the even and the odd features are summed as two
                 // left-to-right chains by packed adds, then added together
                 f32x2_t v[4];
@@ -144,7 +154,7 @@ qkv_prepare_kernel(T *__restrict__ qkv, int total, int H, const T *__restrict__ 
                 for (int j = 0; j < 4; ++j) v[j] = add_f32x2(v[j], neg_mean);
                 acc = mul_f32x2(v[0], v[0]);
 #pragma unroll
-                for (int j = 1; j < 4; ++j) acc = fma_f32x2(v[j], v[j], acc);
+                for (int j = 1; j < 4; ++j) acc = fma_f32x2(v[j], v[j], acc);  // explicit: never a separate mul + add
                 unpack_f32x2(acc, even, odd);
                 const float var = __fmul_rn(group_sum<lanes>(__fadd_rn(even, odd)), inv_D);
                 const float rstd = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(var, eps)));
@@ -156,7 +166,7 @@ qkv_prepare_kernel(T *__restrict__ qkv, int total, int H, const T *__restrict__ 
                     y.set(j, P2::from_f32(lo, hi));
                 }
             }
-            if (pos) {
+            if constexpr (ROPE) {
                 Vec8<T> c, s, o;
                 c.load_ro(cos_t + p[i] * half + f_in_half);
                 s.load_ro(sin_t + p[i] * half + f_in_half);
@@ -171,6 +181,21 @@ qkv_prepare_kernel(T *__restrict__ qkv, int total, int H, const T *__restrict__ 
                 if (bias_out && threadIdx.x == 0) bias_out[r] = Elem<T>::from_f32(logf(weight[r]));
             }
         }
+    };
+
+    // (Issuing the next batch's loads before the current batch's arithmetic was measured slower: the extra registers
+    // cost a quarter of the resident warps.)
+    const int full_end = total - total % kPrepRowsInFlight;  // rows covered by full batches
+    Vec8<T> x[kPrepRowsInFlight];
+    int p[kPrepRowsInFlight];
+    int r0 = blockIdx.x * kPrepRowsInFlight;
+    for (; r0 < full_end; r0 += gridDim.x * kPrepRowsInFlight) {
+        load_batch(std::true_type{}, r0, x, p);
+        finish_batch(std::true_type{}, r0, x, p);
+    }
+    if (r0 < total) {  // at most one CTA reaches the partial batch
+        load_batch(std::false_type{}, r0, x, p);
+        finish_batch(std::false_type{}, r0, x, p);
     }
 }
 
@@ -215,23 +240,40 @@ __global__ void packed_positions_kernel(const uint8_t *__restrict__ mask, const 
     }
 }
 
-template <typename T, int D>
-static int launch_prepare_d(void *qkv, int64_t total, int H, const void *qg, const void *qb, const void *kg,
+template <typename T, int D, bool NORM, bool ROPE>
+static int launch_prepare_k(void *qkv, int64_t total, int H, const void *qg, const void *qb, const void *kg,
                             const void *kb, float eps, const int64_t *pos, const void *cos_t, const void *sin_t,
                             int table_rows, const float *weight, void *bias_out, cudaStream_t st) {
     unsigned int *status = status_word_dev();
     if (!status) return COME_ERR_CUDA;
     const int threads = 2 * H * (D / 8);
+    if (threads > prep_max_threads<D>() || threads % 32 != 0) {
+        set_error("come_qkv_prepare: head_dim %d needs 2*num_heads*head_dim/8 = %d threads per row: must be a multiple of "
+                  "32 and <= %d", D, threads, prep_max_threads<D>());
+        return COME_ERR_UNSUPPORTED;
+    }
     int resident = 0;  // CTAs of this size that fit one SM: the grid is exactly one resident wave
-    COME_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, qkv_prepare_kernel<T, D>, threads, 0));
+    COME_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, qkv_prepare_kernel<T, D, NORM, ROPE>, threads, 0));
     if (resident < 1) resident = 1;
     const int64_t iters = (total + kPrepRowsInFlight - 1) / kPrepRowsInFlight;
     const int64_t wave = (int64_t)sm_count() * resident;
     const unsigned grid = (unsigned)(iters < wave ? iters : wave);
-    qkv_prepare_kernel<T, D><<<grid, threads, 0, st>>>((T *)qkv, (int)total, H, (const T *)qg, (const T *)qb,
+    qkv_prepare_kernel<T, D, NORM, ROPE><<<grid, threads, 0, st>>>((T *)qkv, (int)total, H, (const T *)qg, (const T *)qb,
                                                       (const T *)kg, (const T *)kb, eps, pos, (const T *)cos_t,
                                                       (const T *)sin_t, table_rows, weight, (T *)bias_out, status);
     return check_launch("come_qkv_prepare");
+}
+
+template <typename T, int D>
+static int launch_prepare_d(void *qkv, int64_t total, int H, const void *qg, const void *qb, const void *kg,
+                            const void *kb, float eps, const int64_t *pos, const void *cos_t, const void *sin_t,
+                            int table_rows, const float *weight, void *bias_out, cudaStream_t st) {
+#define COME_PREP_ARGS qkv, total, H, qg, qb, kg, kb, eps, pos, cos_t, sin_t, table_rows, weight, bias_out, st
+    if (qg && pos) return launch_prepare_k<T, D, true, true>(COME_PREP_ARGS);
+    if (qg) return launch_prepare_k<T, D, true, false>(COME_PREP_ARGS);
+    if (pos) return launch_prepare_k<T, D, false, true>(COME_PREP_ARGS);
+    return launch_prepare_k<T, D, false, false>(COME_PREP_ARGS);  // only the bias is left to do
+#undef COME_PREP_ARGS
 }
 
 template <typename T>
@@ -266,10 +308,8 @@ extern "C" int come_qkv_prepare(void *qkv_dev, int dtype, int64_t total, int num
     }
     COME_REQUIRE(dtype == COME_F16 || dtype == COME_BF16, "unknown dtype %d", dtype);
     COME_REQUIRE(total >= 0 && num_heads > 0 && head_dim > 0, "total must be >= 0, num_heads and head_dim > 0");
-    if (!(head_dim == 32 || head_dim == 64 || head_dim == 128 || head_dim == 256) ||
-        2 * num_heads * (head_dim / 8) > 512 || (2 * num_heads * (head_dim / 8)) % 32 != 0) {
-        set_error("come_qkv_prepare supports head_dim 32/64/128/256 with 2*num_heads*head_dim/8 a multiple of 32 and "
-                  "<= 512 (got %d heads of %d)", num_heads, head_dim);
+    if (!(head_dim == 32 || head_dim == 64 || head_dim == 128 || head_dim == 256)) {
+        set_error("come_qkv_prepare supports head_dim 32/64/128/256, got %d", head_dim);
         return COME_ERR_UNSUPPORTED;
     }
     COME_REQUIRE((q_gamma_dev == nullptr) == (q_beta_dev == nullptr) && (k_gamma_dev == nullptr) == (k_beta_dev == nullptr) &&

@@ -209,6 +209,31 @@ class MergePlan:
         """packed ``[P, C]`` -> ``[frames * N, C]``."""
         return co_me_cuext.co_me_token_split_cuda(merged, self.rev_id, merged.shape[-1])
 
+    def split_concat(self, *merged: torch.Tensor) -> torch.Tensor:
+        """Unmerge several packed ``[P, C_k]`` tensors side by side into one ``[frames * N, sum(C_k)]`` tensor:
+        the ``torch.cat((split(frame_tokens), split(global_tokens)), dim=-1)`` of a retained layer
+        (``src/accelerate/vggt/fused.py:157-167``) without materialising the separate splits."""
+        if not merged:
+            raise ValueError("split_concat needs at least one tensor")
+        first = merged[0]
+        for m in merged:
+            require_cuda(m, "merged")
+            if m.dim() != 2 or m.shape[0] != self.total or m.dtype != first.dtype or m.device != first.device:
+                raise ValueError(f"Expected [{self.total}, C] tensors of one dtype on one device, got {tuple(m.shape)} {m.dtype}")
+        width = sum(int(m.shape[1]) for m in merged)
+        rows = self.frames * self.tokens_per_frame
+        out = torch.empty((rows, width), dtype=first.dtype, device=first.device)
+        code = dtype_code(first.dtype, "merged")
+        col = 0
+        with torch.cuda.device(first.device):
+            for m in merged:
+                m = m.contiguous()
+                dst = out.data_ptr() + col * out.element_size()
+                _lib.check(_lib.lib().come_unmerge_strided(ptr(m), ptr(self.rev_id), rows, m.shape[1], code, dst, width,
+                                                           stream_ptr(first.device)))
+                col += int(m.shape[1])
+        return out
+
     def jagged(self, tokens: torch.Tensor) -> JaggedTokens:
         return JaggedTokens(tokens=self.merge(tokens).unsqueeze(0), weight=self.weight, offset=self.offset)
 

@@ -150,6 +150,16 @@ int come_unmerge(const void *merged_dev, const int64_t *rev_id_dev, int64_t tota
                  void *out_dev, void *stream);
 
 /*
+ * Unmerge into a wider destination: out[i * out_row_stride + c] = merged[rev_id[i], c] for c < channels
+ * (out_row_stride in elements, >= channels).  Two calls with out_dev and out_dev + channels write the
+ * [frame-block | global-block] concatenation [B, S, N, 2C] of a retained layer in place, which the reference
+ * builds from two split() results and a torch.cat (src/accelerate/vggt/fused.py:157-167): one full read and
+ * write of the restored tokens less.  With out_row_stride == channels it is come_unmerge.
+ */
+int come_unmerge_strided(const void *merged_dev, const int64_t *rev_id_dev, int64_t total, int64_t channels, int dtype,
+                         void *out_dev, int64_t out_row_stride, void *stream);
+
+/*
  * Variable-length attention forward with an optional additive per-key bias:
  *   out[s:e, h] = softmax(q[s:e, h] k[s:e, h]^T * softmax_scale + bias[s:e][None, :]) v[s:e, h]
  * for every packed segment [cu_seqlens[i], cu_seqlens[i+1]) and head h; non-causal, no dropout.
@@ -200,7 +210,8 @@ int come_attn_varlen_fwd_rows(const void *q_dev, const void *k_dev, const void *
  *                      (rope.py:87-114; the caller caches them like the reference does)
  *   gamma / beta       [head_dim] in dtype
  * A position outside [0, table_rows) is clamped and raises bit 16 of the device status word.
- * dtype COME_F16 or COME_BF16; head_dim 32/64/128/256 with 2*num_heads*head_dim/8 <= 512 threads (a multiple of 32).
+ * dtype COME_F16 or COME_BF16; head_dim 32/64/128/256; one CTA of 2*num_heads*head_dim/8 threads handles a row:
+ * that count must be a multiple of 32 and <= 512.
  */
 int come_qkv_prepare(void *qkv_dev, int dtype, int64_t total, int num_heads, int head_dim, const void *q_gamma_dev,
                      const void *q_beta_dev, const void *k_gamma_dev, const void *k_beta_dev, float eps,

@@ -282,3 +282,23 @@ def test_extension_errors_are_runtime_errors():
         co_me_cuext.co_me_token_merge_cuda(torch.randn(1, 7, 4).cuda(), 0, 2, torch.ones(1, 3, dtype=torch.bool).cuda())
     with pytest.raises(RuntimeError, match="C mismatch"):
         co_me_cuext.co_me_token_split_cuda(torch.randn(3, 4).cuda(), torch.zeros(3, dtype=torch.int64).cuda(), 5)
+
+
+@pytest.mark.parametrize("kind,widths", [("f32", (1024, 1024)), ("bf16", (1024, 1024)), ("f32", (6, 10)), ("f16", (3, 5, 8))])
+def test_split_concat(kind, widths):
+    """Unmerging several packed tensors side by side equals concatenating the oracle's separate unmerges
+    (the [frame | global] concatenation of a retained layer)."""
+    import torch
+    from come_b200 import _lib
+    from come_b200.token_merger import MergePlan
+    from gpu_util import to_dev, to_np
+    import golden_inputs as gi
+    from oracle import come_oracle as orc
+    rng = np.random.default_rng(sum(widths))
+    mask = rng.random((3, 144)) < 0.5
+    plan = MergePlan(torch.from_numpy(mask).cuda(), _lib.Layout.two_d(5, 37, 37, 3, 3))
+    _o, _off, rev, _w = orc.token_merge_2d_ragged(np.zeros((3, 1374, 1), np.float32), 5, 3, 3, 37, 37, mask)
+    parts = [gi.round_kind(rng.standard_normal((plan.total, c), dtype=np.float32), kind) for c in widths]
+    got = to_np(plan.split_concat(*[to_dev(p, kind) for p in parts]))
+    want = np.concatenate([orc.token_split(p, rev) for p in parts], axis=1)
+    np.testing.assert_array_equal(got, want)

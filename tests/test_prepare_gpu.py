@@ -118,3 +118,53 @@ def test_positions_ragged_grid():
     mask = rng.random((8, 144)) < 0.5
     plan = MergePlan(torch.from_numpy(mask).cuda(), _lib.Layout.two_d(5, 37, 37, 3, 3))
     np.testing.assert_array_equal(to_np(plan.positions()), orc.packed_positions(mask, 5, 37, 37, 3, 3))
+
+
+class _Attention(torch.nn.Module):
+    """Stand-in for the model's attention block: the attributes the reference's wrapper reads."""
+
+    def __init__(self, dim, heads):
+        super().__init__()
+        self.num_heads, self.head_dim = heads, dim // heads
+        self.scale = self.head_dim ** -0.5
+        self.qkv = torch.nn.Linear(dim, 3 * dim)
+        self.q_norm = torch.nn.LayerNorm(self.head_dim)
+        self.k_norm = torch.nn.LayerNorm(self.head_dim)
+        self.attn_drop = torch.nn.Dropout(0.0)
+        self.proj = torch.nn.Linear(dim, dim)
+        self.proj_drop = torch.nn.Dropout(0.0)
+        self.rope = type("Rope", (), {"base_frequency": 100.0})()
+
+
+def test_jagged_attention_module():
+    """JaggedAttention_w_Bias = qkv GEMM -> prepare kernel -> biased attention kernel -> proj GEMM; checked against the
+    oracle's prepare + attention applied to the same GEMM output (bfloat16, 2e-2 absolute on the attention output)."""
+    from come_b200.bias_attention import JaggedAttention_w_Bias
+    from come_b200.token_merger import JaggedTokens
+    torch.manual_seed(3)
+    dim, heads = 128, 2
+    mod = JaggedAttention_w_Bias(_Attention(dim, heads).cuda(), "bf16").eval()
+    seq = [130, 57, 300]
+    P = sum(seq)
+    rng = np.random.default_rng(8)
+    tokens = torch.from_numpy(rng.standard_normal((1, P, dim), dtype=np.float32)).cuda().bfloat16()
+    weight = torch.from_numpy(np.where(rng.random(P) < 0.3, 9.0, 1.0).astype(np.float32)).cuda()
+    offset = torch.tensor(np.concatenate([[0], np.cumsum(seq)]), dtype=torch.int64, device="cuda")
+    pos = torch.from_numpy(rng.integers(0, 38, size=(1, P, 2))).cuda()
+    with torch.no_grad():
+        out = mod(JaggedTokens(tokens=tokens, weight=weight, offset=offset), pos=pos)
+        qkv = mod.attn.qkv(tokens[0]).reshape(P, 3, heads, dim // heads)
+    assert out.tokens.shape == (1, P, dim) and out.weight is weight and out.offset is offset
+    a = mod.attn
+    cos_t, sin_t = orc.rope_tables(dim // heads // 2, 256, 100.0, "bf16")
+    prepared = orc.qkv_prepare(to_np(qkv), to_np(a.q_norm.weight), to_np(a.q_norm.bias), to_np(a.k_norm.weight),
+                               to_np(a.k_norm.bias), a.q_norm.eps, to_np(pos)[0], cos_t, sin_t, "bf16")
+    bias = orc.perkey_bias_from_weight(to_np(weight), "bf16")
+    want, _lse = orc.attention_bias(prepared[:, 0], prepared[:, 1], prepared[:, 2], bias, to_np(offset).astype(np.int32),
+                                    a.scale)
+    with torch.no_grad():
+        want_out = a.proj(torch.from_numpy(want.reshape(P, dim)).cuda().bfloat16())
+    err = (out.tokens[0].float() - want_out.float()).abs().max().item()
+    assert err <= 2e-2, err
+    with pytest.raises(ValueError):
+        JaggedAttention_w_Bias(_Attention(dim, heads), "fp32")
