@@ -581,41 +581,40 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             tc_fence_before();
             mbar_arrive(&sh.s_empty[t]);
             bool o_ready = (j == 0);  // P V of the previous key tile complete: O stable, P buffer free
+            // Row max over all 128 scores first: eight independent 3-input chains (16 scores each) keep the ALU pipe fed,
+            // and the rare rescale is decided once per key tile, so the exponentials below are one straight-line block.
+            float mx[8];
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                uint32_t(&a)[32] = srow[q];
-                // row max of this quarter: two independent 3-input chains
-                float m0 = __uint_as_float(a[0]), m1 = __uint_as_float(a[15]);
+            for (int c = 0; c < 8; ++c) {
+                const uint32_t *e = &srow[c >> 1][(c & 1) * 16];
+                float m = max3(__uint_as_float(e[0]), __uint_as_float(e[1]), __uint_as_float(e[2]));
 #pragma unroll
-                for (int i = 1; i < 15; i += 2) {
-                    m0 = max3(m0, __uint_as_float(a[i]), __uint_as_float(a[i + 1]));
-                    m1 = max3(m1, __uint_as_float(a[15 + i]), __uint_as_float(a[15 + i + 1]));
+                for (int i = 3; i < 15; i += 2) m = max3(m, __uint_as_float(e[i]), __uint_as_float(e[i + 1]));
+                mx[c] = fmaxf(m, __uint_as_float(e[15]));
+            }
+            const float t_max = max3(max3(mx[0], mx[1], mx[2]), max3(mx[3], mx[4], mx[5]), fmaxf(mx[6], mx[7])) * scale_log2;
+            const bool need = t_max > m_ref + kRescaleThreshold;  // always true on the first key tile (m_ref = -inf)
+            if (__any_sync(0xffffffffu, need)) {
+                float alpha = 1.0f;
+                if (need) {
+                    alpha = (m_ref == -INFINITY) ? 0.0f : fast_exp2(m_ref - t_max);
+                    m_ref = t_max;
+                    l *= alpha;
                 }
-                const float t_max = max3(m0, m1, fmaxf(__uint_as_float(a[29]), fmaxf(__uint_as_float(a[30]), __uint_as_float(a[31])))) * scale_log2;
-                const bool need = t_max > m_ref + kRescaleThreshold;  // always true on the very first quarter (m_ref = -inf)
-                if (__any_sync(0xffffffffu, need)) {
-                    float alpha = 1.0f;
-                    if (need) {
-                        alpha = (m_ref == -INFINITY) ? 0.0f : fast_exp2(m_ref - t_max);
-                        m_ref = t_max;
-                        l *= alpha;
-                    }
-                    if (j > 0) {  // rescale what earlier key tiles accumulated
-                        if (!o_ready) {
-                            ok = mbar_wait(&sh.o_done[t], (j - 1) & 1, sh, status, kErrODone);
-                            ok = __all_sync(0xffffffffu, ok);
-                            if (!ok) break;
-                            tc_fence_after();
-                            o_ready = true;
-                        }
-                    }
-                    rescale_staged<kBF16>(o_tmem, p_tmem, alpha, j > 0, q);
+                if (j > 0) {  // rescale what earlier key tiles accumulated
+                    ok = mbar_wait(&sh.o_done[t], (j - 1) & 1, sh, status, kErrODone);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
+                    tc_fence_after();
+                    o_ready = true;
+                    rescale_staged<kBF16>(o_tmem, p_tmem, alpha, true, 0);
                 }
-                // p = 2^(s * scale*log2e - m_ref), two scores per instruction; every third pair takes the polynomial
-                // route so that the special-function unit and the FMA pipe share the exponentials.
-                const f32x2_t scale2 = pack_f32x2(scale_log2, scale_log2), neg_m2 = pack_f32x2(-m_ref, -m_ref);
-                f32x2_t sum2 = pack_f32x2(0.0f, 0.0f);
-                uint32_t pk[16];
+            }
+            // p = 2^(s * scale*log2e - m_ref), two scores per instruction; a share of the pairs takes the polynomial
+            // route so that the special-function unit and the FMA pipe split the exponentials.
+            const f32x2_t scale2 = pack_f32x2(scale_log2, scale_log2), neg_m2 = pack_f32x2(-m_ref, -m_ref);
+            f32x2_t sum2 = pack_f32x2(0.0f, 0.0f);
+            auto quarter = [&](const uint32_t(&a)[32], uint32_t(&pk)[16]) {
 #pragma unroll
                 for (int pair = 0; pair < 16; ++pair) {
                     const f32x2_t x2 = fma_f32x2(pack_f32x2(__uint_as_float(a[2 * pair]), __uint_as_float(a[2 * pair + 1])), scale2, neg_m2);
@@ -630,20 +629,30 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     sum2 = add_f32x2(sum2, pack_f32x2(p0, p1));
                     pk[pair] = pack2<kBF16>(p0, p1);
                 }
-                {
-                    float s_lo, s_hi;
-                    unpack_f32x2(sum2, s_lo, s_hi);
-                    l += s_lo + s_hi;
-                }
-                if (!o_ready) {
+            };
+            {
+                uint32_t pk[16];
+                quarter(srow[0], pk);
+                if (!o_ready) {  // the P buffer is free once P V of the previous key tile has completed
                     ok = mbar_wait(&sh.o_done[t], (j - 1) & 1, sh, status, kErrODone);
                     ok = __all_sync(0xffffffffu, ok);
                     if (!ok) break;
                     tc_fence_after();
-                    o_ready = true;
                 }
-                tmem_st16(p_tmem + 16 * q, pk);  // 32 keys -> 16 columns of 16-bit pairs
+                tmem_st16(p_tmem, pk);  // 32 keys -> 16 columns of 16-bit pairs
+                if ((warp & 3) == 0) PROF_TRACE(t, j, 5);
+            }
+#pragma unroll
+            for (int q = 1; q < 4; ++q) {
+                uint32_t pk[16];
+                quarter(srow[q], pk);
+                tmem_st16(p_tmem + 16 * q, pk);
                 if ((warp & 3) == 0 && q < 3) PROF_TRACE(t, j, 5 + q);
+            }
+            {
+                float s_lo, s_hi;
+                unpack_f32x2(sum2, s_lo, s_hi);
+                l += s_lo + s_hi;
             }
             if (!ok) break;
             if ((warp & 3) == 0) PROF_TRACE(t, j, 2);

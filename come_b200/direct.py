@@ -1,0 +1,51 @@
+"""Per-layer ("direct") acceleration of an attention block, mirroring the forward the reference patches into every
+VGGT attention module (``src/accelerate/vggt/direct.py:71-124``): merge the dense tokens, run the jagged attention
+with the ``log(count)`` key bias on the merged tokens, split back to the dense layout.
+
+Differences from the reference's closure, none of them visible in the result:
+
+* the index plan (offsets, ``rev_id``, counts, longest segment, packed positions) comes from a
+  :class:`~come_b200.token_merger.MergePlan` built once per scene, not from a fresh merge of the features and a second
+  merge of the positions in every layer;
+* frame and global segmentation are two views of the plan's offsets (``cu_seqlens(1)`` / ``cu_seqlens(S)``), and the
+  longest segment is known without a device-to-host read.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .bias_attention import JaggedAttention_w_Bias
+from .token_merger import JaggedTokens, MergePlan
+
+__all__ = ["DirectAttention"]
+
+
+class DirectAttention(torch.nn.Module):
+    """Drop-in for ``block.attn.forward(x, pos)`` of a frame (``is_global=False``) or global attention block.
+
+    ``x`` is ``[B*S, N, C]`` (frame blocks) or ``[B, S*N, C]`` (global blocks) exactly as the aggregator passes it;
+    the result has the same shape and dtype.  ``plan`` is the merge plan of the current scene(s) with
+    ``frames = B*S``; ``frames_per_scene = S``.
+    """
+
+    def __init__(self, original_attn: torch.nn.Module, *, is_global: bool, run_dtype: str = "bf16"):
+        super().__init__()
+        self.is_global = is_global
+        self.attn_op = JaggedAttention_w_Bias(original_attn, run_dtype=run_dtype)
+
+    def forward(self, x: torch.Tensor, plan: MergePlan, frames_per_scene: int, use_pos: bool = True) -> torch.Tensor:
+        input_shape, input_dtype = x.shape, x.dtype
+        C = x.shape[-1]
+        dense = x.reshape(plan.frames, plan.tokens_per_frame, C).to(self.attn_op.run_dtype)
+        merged = plan.merge(dense)
+        if self.is_global:
+            offset = plan.offset[::frames_per_scene]
+            max_seqlen = plan.total if plan.frames == frames_per_scene else None  # several scenes: read it back
+        else:
+            offset, max_seqlen = plan.offset, plan.max_seqlen
+        jag = JaggedTokens(tokens=merged.unsqueeze(0), weight=plan.weight, offset=offset)
+        pos: Optional[torch.Tensor] = plan.positions() if use_pos else None
+        out = self.attn_op(jag, pos=pos, max_seqlen=max_seqlen)
+        return plan.split(out.tokens.squeeze(0)).view(*input_shape).to(input_dtype)

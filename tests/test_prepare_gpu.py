@@ -168,3 +168,47 @@ def test_jagged_attention_module():
     assert err <= 2e-2, err
     with pytest.raises(ValueError):
         JaggedAttention_w_Bias(_Attention(dim, heads), "fp32")
+
+
+@pytest.mark.parametrize("is_global", [False, True])
+def test_direct_attention_block(is_global):
+    """The per-layer replacement of block.attn.forward: merge -> jagged biased attention -> split, against the oracle
+    chain (merge, prepare, attention, split) around the same two GEMMs."""
+    from come_b200 import _lib
+    from come_b200.direct import DirectAttention
+    from come_b200.token_merger import MergePlan
+    torch.manual_seed(5)
+    dim, heads, S, Hg, Wg = 128, 2, 3, 7, 8  # 3 frames of 5 + 7x8 tokens, 3x3 windows tile the top-left 6x6
+    rng = np.random.default_rng(21)
+    mask = rng.random((S, 4)) < 0.5
+    plan = MergePlan(torch.from_numpy(mask).cuda(), _lib.Layout.two_d(5, Hg, Wg, 3, 3))
+    N = 5 + Hg * Wg
+    mod = DirectAttention(_Attention(dim, heads).cuda(), is_global=is_global).eval()
+    x32 = rng.standard_normal((S, N, dim), dtype=np.float32)
+    x = torch.from_numpy(x32).cuda()
+    x_in = x.reshape(1, S * N, dim) if is_global else x
+    with torch.no_grad():
+        y = mod(x_in, plan, frames_per_scene=S)
+    assert y.shape == x_in.shape and y.dtype == x.dtype
+    # oracle chain
+    a = mod.attn_op.attn
+    xb = gi.round_kind(x32, "bf16")
+    merged, off, rev, w = orc.token_merge_2d_ragged(xb, 5, 3, 3, Hg, Wg, mask)
+    merged = gi.round_kind(merged, "bf16")
+    P = merged.shape[0]
+    with torch.no_grad():
+        qkv = a.qkv(torch.from_numpy(merged).cuda().bfloat16()).reshape(P, 3, heads, dim // heads)
+    cos_t, sin_t = orc.rope_tables(dim // heads // 2, 256, 100.0, "bf16")
+    pos = orc.packed_positions(mask, 5, Hg, Wg, 3, 3)
+    prepared = orc.qkv_prepare(to_np(qkv), to_np(a.q_norm.weight), to_np(a.q_norm.bias), to_np(a.k_norm.weight),
+                               to_np(a.k_norm.bias), a.q_norm.eps, pos, cos_t, sin_t, "bf16")
+    cu = off.astype(np.int32)
+    if is_global:
+        cu = cu[::S]
+    att, _ = orc.attention_bias(prepared[:, 0], prepared[:, 1], prepared[:, 2], orc.perkey_bias_from_weight(w, "bf16"), cu,
+                                a.scale)
+    with torch.no_grad():
+        proj = a.proj(torch.from_numpy(att.reshape(P, dim)).cuda().bfloat16())
+    want = orc.token_split(to_np(proj), rev).reshape(x_in.shape)
+    err = np.abs(to_np(y) - want).max()
+    assert err <= 2e-2, err
