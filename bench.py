@@ -583,6 +583,42 @@ def run_only(args):
         else:
             fn, nbytes = (lambda: plan.split(merged)), plan.total * CH * es + args.frames * N_TOK * 8 + args.frames * N_TOK * CH * es
         out.update(frames=args.frames, dtype=args.dtype, bytes=nbytes)
+    elif args.only == "direct":
+        # The complete replacement of block.attn.forward in the reference's per-layer mode, 48 layers of one scene:
+        # merge -> qkv GEMM -> q/k LayerNorm + RoPE + bias -> biased attention -> proj GEMM -> unmerge (GEMMs = cuBLAS).
+        from come_b200.direct import DirectAttention
+
+        class Attn(torch.nn.Module):
+            def __init__(self):
+                super().__init__()
+                self.num_heads, self.head_dim, self.scale = HEADS, HDIM, HDIM ** -0.5
+                self.qkv, self.proj = torch.nn.Linear(CH, 3 * CH), torch.nn.Linear(CH, CH)
+                self.q_norm, self.k_norm = torch.nn.LayerNorm(HDIM), torch.nn.LayerNorm(HDIM)
+                self.rope = type("Rope", (), {"base_frequency": 100.0})()
+
+        torch.manual_seed(0)
+        frames = args.frames if args.frames != 100 else 8
+        mask = torch.rand((frames, N_WIN), device=dev, generator=g) < 0.5
+        plan = MergePlan(mask, _lib.Layout.two_d(START, GRID, GRID, WIN, WIN))
+        layers = [DirectAttention(Attn().to(dev), is_global=bool(i % 2)).eval() for i in range(48)]
+        x = torch.randn((frames, N_TOK, CH), device=dev, generator=g).bfloat16()
+
+        def scene():
+            y = x
+            with torch.no_grad():
+                for layer in layers:
+                    y = layer(y.reshape(1, frames * N_TOK, CH) if layer.is_global else y.reshape(frames, N_TOK, CH), plan, frames)
+            return y
+
+        scene()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            scene()
+        fn = graph.replay
+        gemm_flops = 48 * 2.0 * plan.total * CH * 4 * CH
+        out.update(frames=frames, tokens=plan.total, layers=48, launch="CUDA graph of 48 layers",
+                   flops=gemm_flops + sum(4.0 * L * L * HDIM * HEADS for L in ([plan.total] * 24 + [plan.total / frames] * 24 * frames)))
     elif args.only == "prepare":
         # q/k LayerNorm + 2-D rotary embedding + log(count) bias on the packed rows of `frames` half-merged frames
         from come_b200.qkv import RotaryPositionEmbedding2D, prepare_packed_self_attention_qkv
@@ -629,7 +665,7 @@ def run_only(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--only", choices=["attn", "merge", "unmerge", "prepare"], help="run one kernel family on one size and exit")
+    ap.add_argument("--only", choices=["attn", "merge", "unmerge", "prepare", "direct"], help="run one kernel family on one size and exit")
     ap.add_argument("--frames", type=int, default=100, help="--only merge/unmerge: frames")
     ap.add_argument("--dtype", default="f32", choices=["f32", "bf16"], help="--only merge/unmerge: element type")
     ap.add_argument("--tokens", type=int, default=6384, help="--only attn with --segments 1: segment length")

@@ -165,19 +165,25 @@ def test_global_segment_and_strided_views(backend):
     _check_status()
 
 
-def test_large_magnitude_scores_rescale_path(backend):
-    """Scores that grow along the keys force the running-max rescale of the output accumulator."""
+@pytest.mark.parametrize("kind", ["bf16", "f16"])
+@pytest.mark.parametrize("gain", [6.0, 40.0])
+def test_large_magnitude_scores_rescale_path(backend, kind, gain):
+    """Scores that grow along the keys: the reference max taken from the first key tile becomes too small, the kernel
+    has to redo a tile with its true row max and rescale the output accumulator (float16 probabilities overflow first;
+    gain 40 overflows float32 exponentials as well)."""
     from come_b200 import flash_attn as api, flash_attn_fwd_cuda as fa
     backend(fa.BACKEND_TCGEN05)
     rng = np.random.default_rng(4)
     P, H, D = 700, 2, 64
     qkv = rng.standard_normal((P, 3, H, D), dtype=np.float32)
-    qkv[:, 1] *= np.linspace(0.2, 6.0, P, dtype=np.float32)[:, None, None]  # later keys score much higher / lower
-    qkv = gi.round_kind(qkv, "bf16")
+    qkv[:, 1] *= np.linspace(0.2, gain, P, dtype=np.float32)[:, None, None]  # later keys score much higher / lower
+    qkv = gi.round_kind(qkv, kind)
     cu = np.array([0, 300, 700], np.int32)
-    out = api.flash_attn_varlen_qkvpacked_func(to_dev(qkv, "bf16"), torch.from_numpy(cu).cuda(), 400, softmax_scale=D ** -0.5)
+    out = api.flash_attn_varlen_qkvpacked_func(to_dev(qkv, kind), torch.from_numpy(cu).cuda(), 400, softmax_scale=D ** -0.5)
     want, _ = clib.attention_bias(qkv, None, cu, D ** -0.5)
-    assert np.abs(to_np(out) - want).max() <= 2e-2
+    got = to_np(out)
+    assert np.isfinite(got).all()
+    assert np.abs(got - want).max() <= 2e-2
     _check_status()
 
 
