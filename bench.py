@@ -647,6 +647,26 @@ def run_only(args):
     for _ in range(2):
         fn()
     torch.cuda.synchronize()
+    if args.graph and args.only != "direct":
+        # device time without the host's per-call cost: `iters` launches captured into one graph, replayed once
+        eager, graph = fn, torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(args.iters):
+                eager()
+        graph.replay()
+        torch.cuda.synchronize()
+        s, e = ev(), ev()
+        s.record()
+        graph.replay()
+        e.record()
+        torch.cuda.synchronize()
+        out["launch"] = f"{args.iters} launches in one CUDA graph"
+        out["ms"] = s.elapsed_time(e) / args.iters
+        key = "GB/s" if "bytes" in out else "TFLOP/s"
+        out[key] = (out["bytes"] / out["ms"] / 1e6) if "bytes" in out else (out["flops"] / out["ms"] / 1e9)
+        assert _lib.device_status(clear=False) == 0
+        print(json.dumps(out))
+        return
     s, e = ev(), ev()
     s.record()
     for _ in range(args.iters):
@@ -671,6 +691,7 @@ def main():
     ap.add_argument("--tokens", type=int, default=6384, help="--only attn with --segments 1: segment length")
     ap.add_argument("--segments", type=int, default=1, help="--only attn: 1 = one segment, else ragged 1374-8k sweep")
     ap.add_argument("--iters", type=int, default=3, help="--only: timed launches")
+    ap.add_argument("--graph", action="store_true", help="--only: time the launches inside one CUDA graph (no host cost)")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)

@@ -66,8 +66,8 @@ def lib() -> C.CDLL:
     l.come_unmerge_strided.argtypes = [vp, vp, i64, i64, i32, vp, i64, vp]
     l.come_attn_varlen_fwd.argtypes = [vp, vp, vp, i32, i64, i32, i32, i64, i64, i64, vp, vp, i32, i32, f32, vp, i64,
                                        vp, i32, vp]
-    l.come_attn_varlen_fwd_rows.argtypes = [vp, vp, vp, i32, i64, i64, i64, i32, i32, i64, i64, i64, vp, vp, i32, i32, f32, vp,
-                                            i64, vp, i32, vp]
+    l.come_attn_varlen_fwd_rows.argtypes = [vp, vp, vp, i32, i64, i64, i64, i32, i32, i64, i64, i64, vp, vp, i32, i32, vp, f32,
+                                            vp, i64, vp, i32, vp]
     l.come_qkv_prepare.argtypes = [vp, i32, i64, i32, i32, vp, vp, vp, vp, f32, vp, vp, vp, i64, vp, vp, vp]
     l.come_packed_positions.argtypes = [vp, vp, i64, C.POINTER(Layout), vp, vp]
     l.come_device_status.argtypes = [C.POINTER(C.c_uint32), i32]

@@ -92,8 +92,8 @@ using namespace come;
 static int attn_dispatch(const void *q_dev, const void *k_dev, const void *v_dev, int dtype, int64_t total,
                          int64_t q_begin, int64_t q_rows, int num_heads, int head_dim, int64_t q_row_stride,
                          int64_t k_row_stride, int64_t v_row_stride, const void *bias_dev, const int32_t *cu_seqlens_dev,
-                         int num_segments, int max_seqlen, float softmax_scale, void *out_dev, int64_t out_row_stride,
-                         float *lse_dev, int backend, void *stream) {
+                         int num_segments, int max_seqlen, const int32_t *max_seqlen_dev, float softmax_scale, void *out_dev,
+                         int64_t out_row_stride, float *lse_dev, int backend, void *stream) {
     COME_REQUIRE(dtype == COME_F16 || dtype == COME_BF16, "FlashAttention only support fp16 and bf16 data type");
     COME_REQUIRE(num_segments > 0, "batch size must be positive");
     COME_REQUIRE(total >= 0 && num_heads > 0, "total must be >= 0 and num_heads > 0");
@@ -115,7 +115,7 @@ static int attn_dispatch(const void *q_dev, const void *k_dev, const void *v_dev
     a.q = q_dev; a.k = k_dev; a.v = v_dev; a.bias = bias_dev; a.cu = cu_seqlens_dev; a.out = out_dev; a.lse = lse_dev;
     a.dtype = dtype; a.total = total; a.q_begin = q_begin; a.q_end = q_begin + q_rows; a.H = num_heads; a.D = head_dim;
     a.q_rs = q_row_stride; a.k_rs = k_row_stride; a.v_rs = v_row_stride; a.o_rs = out_row_stride;
-    a.nseg = num_segments; a.max_seqlen = max_seqlen; a.scale = softmax_scale;
+    a.nseg = num_segments; a.max_seqlen = max_seqlen; a.max_seqlen_dev = max_seqlen_dev; a.scale = softmax_scale;
 
     const bool tc_ok = attn_sm100_supported(a);
     if (backend == 2 && !tc_ok) {
@@ -138,7 +138,7 @@ extern "C" int come_attn_varlen_fwd(const void *q_dev, const void *k_dev, const 
                                     int num_segments, int max_seqlen, float softmax_scale, void *out_dev,
                                     int64_t out_row_stride, float *lse_dev, int backend, void *stream) {
     return attn_dispatch(q_dev, k_dev, v_dev, dtype, total, 0, total, num_heads, head_dim, q_row_stride, k_row_stride,
-                         v_row_stride, bias_dev, cu_seqlens_dev, num_segments, max_seqlen, softmax_scale, out_dev,
+                         v_row_stride, bias_dev, cu_seqlens_dev, num_segments, max_seqlen, nullptr, softmax_scale, out_dev,
                          out_row_stride, lse_dev, backend, stream);
 }
 
@@ -146,9 +146,9 @@ extern "C" int come_attn_varlen_fwd_rows(const void *q_dev, const void *k_dev, c
                                          int64_t q_row_begin, int64_t q_rows, int num_heads, int head_dim,
                                          int64_t q_row_stride, int64_t k_row_stride, int64_t v_row_stride,
                                          const void *bias_dev, const int32_t *cu_seqlens_dev, int num_segments,
-                                         int max_seqlen, float softmax_scale, void *out_dev, int64_t out_row_stride,
-                                         float *lse_dev, int backend, void *stream) {
+                                         int max_seqlen, const int32_t *max_seqlen_dev, float softmax_scale, void *out_dev,
+                                         int64_t out_row_stride, float *lse_dev, int backend, void *stream) {
     return attn_dispatch(q_dev, k_dev, v_dev, dtype, total, q_row_begin, q_rows, num_heads, head_dim, q_row_stride,
-                         k_row_stride, v_row_stride, bias_dev, cu_seqlens_dev, num_segments, max_seqlen, softmax_scale,
-                         out_dev, out_row_stride, lse_dev, backend, stream);
+                         k_row_stride, v_row_stride, bias_dev, cu_seqlens_dev, num_segments, max_seqlen, max_seqlen_dev,
+                         softmax_scale, out_dev, out_row_stride, lse_dev, backend, stream);
 }

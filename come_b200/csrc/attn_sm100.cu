@@ -53,11 +53,12 @@ constexpr uint32_t kPolyPairs = COME_POLY_MASK;
 constexpr float kMasked = -3.0e38f;        // "minus infinity" of a masked key, still finite in bfloat16
 
 struct SharedStorage {
-    alignas(1024) uint8_t q[2][kTileBytes];
+    alignas(1024) uint8_t q[2][2][kTileBytes];            // [query tile][buffer]: the next item's Q is loaded ahead
     alignas(1024) uint8_t kv[kStages][kTileBytes];
     alignas(1024) uint8_t q_slab[kTileBytes];             // columns 0,1 = 1.0, rest 0: the A side of the bias step
     alignas(1024) uint8_t k_slab[kSlabStages][kTileBytes];  // columns 0,1 = bias/scale (hi, lo): the B side
-    alignas(8) uint64_t q_full[2];
+    alignas(8) uint64_t q_full[2][2];                     // [query tile][buffer]
+    uint64_t q_empty[2][2];
     uint64_t q_slab_full;
     uint64_t kv_full[kStages];
     uint64_t kv_empty[kStages];
@@ -70,6 +71,8 @@ struct SharedStorage {
     uint32_t tmem_base;
     volatile uint32_t abort_flag;
 };
+
+static_assert(sizeof(SharedStorage) + 1024 <= 227 * 1024, "shared storage exceeds the 227 KB a CTA may use");
 
 // ---- PTX wrappers ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -346,30 +349,62 @@ enum : uint32_t {
     kErrSFull = 1u << 5, kErrSEmpty = 1u << 6, kErrPFull = 1u << 7, kErrODone = 1u << 8,
 };
 
+// One work item = the (up to) two 128-row query tiles [q_row0, q_row0 + 256) of one (segment, head).
+struct WorkItem {
+    int head, s0, s1;   // head, key range of the segment
+    int q_row0, q_hi;   // first query row of the item, end of the query rows this launch owns in the segment
+    int n_mt, n_kv;     // active query tiles (1 or 2), key tiles
+    bool ragged_tail;   // the last key tile is partial
+    bool valid;
+};
+
+__device__ __forceinline__ WorkItem decode_item(int item, int nblk_x, int nseg, const int *__restrict__ cu, int q_begin, int q_end) {
+    WorkItem w;
+    const int bx = item % nblk_x;
+    const int rest = item / nblk_x;
+    const int seg = rest % nseg;
+    w.head = rest / nseg;
+    w.s0 = cu[seg];
+    w.s1 = cu[seg + 1];
+    const int seg_len = w.s1 - w.s0;
+    // Query rows of this launch: global rows [q_begin, q_end) (the whole packed sequence for plain self-attention; a
+    // slice when the query rows are sharded).  q / out / lse are indexed by (global row - q_begin); k / v by global row.
+    const int q_lo = max(w.s0, q_begin);
+    w.q_hi = min(w.s1, q_end);
+    w.q_row0 = q_lo + bx * (2 * kBlockM);
+    w.valid = w.q_row0 < w.q_hi;
+    w.n_mt = (w.q_row0 + kBlockM < w.q_hi) ? 2 : 1;  // query tiles with at least one valid row
+    w.n_kv = (seg_len + kBlockN - 1) / kBlockN;
+    w.ragged_tail = (seg_len % kBlockN) != 0;
+    return w;
+}
+
+// Persistent kernel: one CTA per SM walks the work items item = blockIdx.x, blockIdx.x + gridDim.x, ...  Every role
+// runs the same item loop on its own; the barriers' phases simply keep counting across items, so the producer
+// streams the next item's K/V (and, once the last Q K^T of the current item has completed, its Q) while the softmax
+// groups are still finishing the current one.
 template <bool kBF16>
 __global__ void __launch_bounds__(kThreads, 1)
 attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                       const __grid_constant__ CUtensorMap map_v, const void *__restrict__ bias_ptr,
                       const int *__restrict__ cu, float scale_log2, float inv_scale, void *__restrict__ out_ptr, int64_t o_rs,
-                      float *__restrict__ lse, int q_begin, int q_end, unsigned int *__restrict__ status) {
+                      float *__restrict__ lse, int q_begin, int q_end, int nblk_x, int nseg, int num_heads,
+                      const int *__restrict__ max_len_dev, unsigned int *__restrict__ status) {
     using T = typename std::conditional<kBF16, __nv_bfloat16, __half>::type;
     extern __shared__ uint8_t smem_raw[];
     SharedStorage &sh = *reinterpret_cast<SharedStorage *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
 
-    const int seg = blockIdx.y, head = blockIdx.z;
-    const int s0 = cu[seg], s1 = cu[seg + 1];
-    const int seg_len = s1 - s0;
-    // Query rows of this launch: global rows [q_begin, q_end) (the whole packed sequence for plain self-attention; a
-    // slice when the query rows are sharded).  q / out / lse are indexed by (global row - q_begin); k / v by global row.
-    const int q_lo = max(s0, q_begin), q_hi = min(s1, q_end);
-    const int q_row0 = q_lo + blockIdx.x * (2 * kBlockM);
-    if (q_row0 >= q_hi) return;  // uniform for the CTA, nothing allocated yet
-    const int n_mt = (q_row0 + kBlockM < q_hi) ? 2 : 1;  // query tiles with at least one valid row
-    const int n_kv = (seg_len + kBlockN - 1) / kBlockN;
+    // The host sizes the work list from an upper bound of the longest segment.  A caller that cannot read the true
+    // length back (a captured graph serving every merge mask) passes a loose bound plus the true one in device memory:
+    // the work list then shrinks to the query blocks that can exist, and the round-robin over CTAs stays balanced.
+    if (max_len_dev != nullptr) {
+        const int m = min(max(*max_len_dev, 0), q_end - q_begin);
+        nblk_x = min(nblk_x, (m + 2 * kBlockM - 1) / (2 * kBlockM));
+    }
+    const int total_items = nblk_x * nseg * num_heads;
     const bool has_bias = bias_ptr != nullptr;
-    const bool ragged_tail = (seg_len % kBlockN) != 0;
     // a key tile needs the bias step when there is a bias, or when it is the partial last tile (masking)
-    auto uses_slab = [&](int j) { return has_bias || (ragged_tail && j == n_kv - 1); };
+    auto uses_slab = [&](const WorkItem &w, int j) { return has_bias || (w.ragged_tail && j == w.n_kv - 1); };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (warp == 0) PROF_TRACE(2, 0, 0);  // kernel entry
@@ -378,7 +413,10 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         // an earlier CTA that gave up leaves the status word raised: later CTAs then skip their work
         sh.abort_flag = (*(volatile unsigned int *)status != 0) ? 1u : 0u;
         for (int i = 0; i < 2; ++i) {
-            mbar_init(&sh.q_full[i], 1);
+            for (int b = 0; b < 2; ++b) {
+                mbar_init(&sh.q_full[i][b], 1);
+                mbar_init(&sh.q_empty[i][b], 1);
+            }
             mbar_init(&sh.s_full[i], 1);
             mbar_init(&sh.p_full[i], kBlockM);
             mbar_init(&sh.o_done[i], 1);
@@ -386,11 +424,11 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         }
         for (int i = 0; i < kStages; ++i) {
             mbar_init(&sh.kv_full[i], 1);
-            mbar_init(&sh.kv_empty[i], n_mt);  // released by the issuer of every active query tile
+            mbar_init(&sh.kv_empty[i], 2);  // released by both issuer warps (an idle one arrives without an MMA)
         }
         for (int i = 0; i < kSlabStages; ++i) {
             mbar_init(&sh.slab_full[i], 1);
-            mbar_init(&sh.slab_empty[i], n_mt);
+            mbar_init(&sh.slab_empty[i], 2);
         }
         mbar_init(&sh.q_slab_full, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -416,12 +454,6 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
         const T *bias = reinterpret_cast<const T *>(bias_ptr);
         bool ok = true;
-        if (lane == 0) {
-            for (int t = 0; t < n_mt; ++t) {
-                mbar_arrive_expect_tx(&sh.q_full[t], kTileBytes);
-                tma_load_3d(sh.q[t], &map_q, 0, head, q_row0 - q_begin + t * kBlockM, &sh.q_full[t]);
-            }
-        }
         {   // the constant A side of the bias step: columns 0 and 1 are 1.0.  Both slabs are bfloat16 whatever the
             // q/k/v dtype (the bias step is an MMA instruction of its own): bias/scale and the mask value need its range.
             const uint32_t ones = pack2<true>(1.0f, 1.0f);
@@ -432,75 +464,126 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             __syncwarp();
             if (lane == 0) mbar_arrive(&sh.q_slab_full);
         }
-        int it = 0;       // K/V ring position, advanced once per K or V tile in the order K0 V0 K1 V1 ...
-        int slab_it = 0;  // bias slab ring position, advanced once per key tile that uses the bias step
-        for (int j = 0; j < n_kv && ok; ++j) {
-            if (uses_slab(j)) {
-                const int bs = slab_it % kSlabStages;
-                ok = mbar_wait(&sh.slab_empty[bs], ((slab_it / kSlabStages) & 1) ^ 1, sh, status, kErrSlabEmpty);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-                const uint32_t ks = smem_u32(sh.k_slab[bs]);
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const int r = lane * 4 + i;
-                    const int key = s0 + j * kBlockN + r;
-                    float hi = kMasked, lo = 0.0f;
-                    if (key < s1) {
-                        const float b = has_bias ? Elem<T>::to_f32(bias[key]) * inv_scale : 0.0f;
-                        hi = __bfloat162float(__float2bfloat16_rn(b));
-                        lo = b - hi;
-                    }
-                    slab_write_row(ks, r, pack2<true>(hi, lo));
-                }
-                fence_proxy_async();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&sh.slab_full[bs]);
-                ++slab_it;
-            }
+        int it = 0;            // K/V ring position, advanced once per K or V tile in the order K0 V0 K1 V1 ...
+        int slab_it = 0;       // bias slab ring position, advanced once per key tile that uses the bias step
+        int q_uses[2] = {0, 0};  // items that loaded query tile t so far (buffer and phase of q_full / q_empty)
+        for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+            const WorkItem w = decode_item(item, nblk_x, nseg, cu, q_begin, q_end);
+            if (!w.valid) continue;
             if (lane == 0) {
-#pragma unroll
-                for (int kv = 0; kv < 2 && ok; ++kv) {  // K tile, then V tile of the same keys
-                    const int stage = (it + kv) % kStages;
-                    ok = mbar_wait(&sh.kv_empty[stage], (((it + kv) / kStages) & 1) ^ 1, sh, status, kErrKvEmpty);
+                for (int t = 0; t < w.n_mt && ok; ++t) {
+                    // Use n of query tile t goes to buffer n & 1, which is free once the last Q K^T of use n - 2 has completed:
+                    // the query tiles of the next item are in flight while the current item is still being computed.
+                    const int n = q_uses[t], b = n & 1;
+                    if (n >= 2) ok = mbar_wait(&sh.q_empty[t][b], ((n >> 1) - 1) & 1, sh, status, kErrQFull);
                     if (ok) {
-                        mbar_arrive_expect_tx(&sh.kv_full[stage], kTileBytes);
-                        tma_load_3d(sh.kv[stage], kv == 0 ? &map_k : &map_v, 0, head, s0 + j * kBlockN, &sh.kv_full[stage]);
+                        mbar_arrive_expect_tx(&sh.q_full[t][b], kTileBytes);
+                        tma_load_3d(sh.q[t][b], &map_q, 0, w.head, w.q_row0 - q_begin + t * kBlockM, &sh.q_full[t][b]);
                     }
                 }
             }
+            for (int t = 0; t < w.n_mt; ++t) ++q_uses[t];
             ok = __all_sync(0xffffffffu, ok);
-            it += 2;
+            for (int j = 0; j < w.n_kv && ok; ++j) {
+                if (uses_slab(w, j)) {
+                    const int bs = slab_it % kSlabStages;
+                    ok = mbar_wait(&sh.slab_empty[bs], ((slab_it / kSlabStages) & 1) ^ 1, sh, status, kErrSlabEmpty);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
+                    const uint32_t ks = smem_u32(sh.k_slab[bs]);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int r = lane * 4 + i;
+                        const int key = w.s0 + j * kBlockN + r;
+                        float hi = kMasked, lo = 0.0f;
+                        if (key < w.s1) {
+                            const float b = has_bias ? Elem<T>::to_f32(bias[key]) * inv_scale : 0.0f;
+                            hi = __bfloat162float(__float2bfloat16_rn(b));
+                            lo = b - hi;
+                        }
+                        slab_write_row(ks, r, pack2<true>(hi, lo));
+                    }
+                    fence_proxy_async();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&sh.slab_full[bs]);
+                    ++slab_it;
+                }
+                if (lane == 0) {
+#pragma unroll
+                    for (int kv = 0; kv < 2 && ok; ++kv) {  // K tile, then V tile of the same keys
+                        const int stage = (it + kv) % kStages;
+                        ok = mbar_wait(&sh.kv_empty[stage], (((it + kv) / kStages) & 1) ^ 1, sh, status, kErrKvEmpty);
+                        if (ok) {
+                            mbar_arrive_expect_tx(&sh.kv_full[stage], kTileBytes);
+                            tma_load_3d(sh.kv[stage], kv == 0 ? &map_k : &map_v, 0, w.head, w.s0 + j * kBlockN, &sh.kv_full[stage]);
+                        }
+                    }
+                }
+                ok = __all_sync(0xffffffffu, ok);
+                it += 2;
+            }
         }
     } else if (warp == 9 || warp == 10) {
         // ===== MMA issuer of query tile t (all lanes run the loop, one elected lane issues) ================
         asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
         const int t = warp - 9;
-        if (t < n_mt) {
-            constexpr uint32_t idesc_qk = make_idesc(kBF16, kBlockM, kBlockN, false);
-            constexpr uint32_t idesc_slab = make_idesc(true, kBlockM, kBlockN, false);
-            constexpr uint32_t idesc_pv = make_idesc(kBF16, kBlockM, kHeadDim, true);
-            const uint64_t q_desc = make_smem_desc(smem_u32(sh.q[t]));
-            const uint64_t q_slab_desc = make_smem_desc(smem_u32(sh.q_slab));
-            const uint64_t kv_desc0 = make_smem_desc(smem_u32(sh.kv[0]));       // slot i: + i * (kTileBytes >> 4)
-            const uint64_t k_slab_desc0 = make_smem_desc(smem_u32(sh.k_slab[0]));
-            const uint32_t s_tmem = tmem + t * kBlockN;
-            const uint32_t o_tmem = tmem + 256 + t * kHeadDim;
-            const uint32_t p_tmem = tmem + 384 + t * 64;
-            bool ok = mbar_wait(&sh.q_full[t], 0, sh, status, kErrQFull);
-            if (ok) ok = mbar_wait(&sh.q_slab_full, 0, sh, status, kErrQFull);
+        constexpr uint32_t idesc_qk = make_idesc(kBF16, kBlockM, kBlockN, false);
+        constexpr uint32_t idesc_slab = make_idesc(true, kBlockM, kBlockN, false);
+        constexpr uint32_t idesc_pv = make_idesc(kBF16, kBlockM, kHeadDim, true);
+        const uint64_t q_desc0 = make_smem_desc(smem_u32(sh.q[t][0]));  // buffer b: + b * (kTileBytes >> 4)
+        const uint64_t q_slab_desc = make_smem_desc(smem_u32(sh.q_slab));
+        const uint64_t kv_desc0 = make_smem_desc(smem_u32(sh.kv[0]));       // slot i: + i * (kTileBytes >> 4)
+        const uint64_t k_slab_desc0 = make_smem_desc(smem_u32(sh.k_slab[0]));
+        const uint32_t s_tmem = tmem + t * kBlockN;
+        const uint32_t o_tmem = tmem + 256 + t * kHeadDim;
+        const uint32_t p_tmem = tmem + 384 + t * 64;
+        bool ok = mbar_wait(&sh.q_slab_full, 0, sh, status, kErrQFull);
+        ok = __all_sync(0xffffffffu, ok);
+        int it = 0;        // K/V ring position at the start of the current item (same count as the producer's)
+        int slab_it = 0;   // bias slab ring position
+        int step = 0;      // key tiles this query tile has processed so far (phase of s_full / s_empty / p_full / o_done)
+        int q_uses = 0;    // items in which this query tile was active (phase of q_full / q_empty)
+        for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+            const WorkItem w = decode_item(item, nblk_x, nseg, cu, q_begin, q_end);
+            if (!w.valid) continue;
+            if (t >= w.n_mt) {
+                // This query tile is empty in this item: release the K/V and slab slots without using them, so that the
+                // rings' arrival counts do not depend on the item.
+                for (int j = 0; j < w.n_kv && ok; ++j) {
+#pragma unroll
+                    for (int kv = 0; kv < 2 && ok; ++kv) {
+                        const int x = it + 2 * j + kv, slot = x % kStages;
+                        ok = mbar_wait(&sh.kv_full[slot], (x / kStages) & 1, sh, status, kErrKvFull);
+                        ok = __all_sync(0xffffffffu, ok);
+                        if (ok && lane == 0) mbar_arrive(&sh.kv_empty[slot]);
+                    }
+                    if (ok && uses_slab(w, j)) {
+                        const int bs = slab_it % kSlabStages;
+                        ok = mbar_wait(&sh.slab_full[bs], (slab_it / kSlabStages) & 1, sh, status, kErrSlabFull);
+                        ok = __all_sync(0xffffffffu, ok);
+                        if (ok && lane == 0) mbar_arrive(&sh.slab_empty[bs]);
+                        ++slab_it;
+                    }
+                }
+                it += 2 * w.n_kv;
+                continue;
+            }
+            const int qb = q_uses & 1;
+            ok = mbar_wait(&sh.q_full[t][qb], (q_uses >> 1) & 1, sh, status, kErrQFull);
             ok = __all_sync(0xffffffffu, ok);
-            int slab_it = 0;
+            if (!ok) break;
+            const uint64_t q_desc = q_desc0 + (uint64_t)(qb * (kTileBytes >> 4));
             // S(0), then per key tile j: S(j+1) = Q K_(j+1)^T as soon as the softmax group has read S(j) into registers,
-            // and O += P(j) V_j as soon as P(j) is staged.  Ring slot of K_j is 2j, of V_j is 2j+1.  The other query
-            // tile's issuer runs the same loop independently.
+            // and O += P(j) V_j as soon as P(j) is staged.  Ring slot of K_j is 2j, of V_j is 2j+1 (from `it`).  The other
+            // query tile's issuer runs the same loop independently.
             auto issue_s = [&](int jj) -> bool {  // jj = key tile whose scores are produced
-                const int k_it = 2 * jj, k_slot = k_it % kStages;
-                const bool slab = uses_slab(jj);
+                const int k_it = it + 2 * jj, k_slot = k_it % kStages;
+                const bool slab = uses_slab(w, jj);
                 const int bs = slab_it % kSlabStages;
                 bool good = mbar_wait(&sh.kv_full[k_slot], (k_it / kStages) & 1, sh, status, kErrKvFull);
                 if (good && slab) good = mbar_wait(&sh.slab_full[bs], (slab_it / kSlabStages) & 1, sh, status, kErrSlabFull);
-                if (good && jj > 0) good = mbar_wait(&sh.s_empty[t], (jj - 1) & 1, sh, status, kErrSEmpty);
+                // the softmax group must have pulled the previous scores (also those of the previous item) out of S
+                if (good && step + jj > 0) good = mbar_wait(&sh.s_empty[t], (step + jj - 1) & 1, sh, status, kErrSEmpty);
                 good = __all_sync(0xffffffffu, good);
                 if (!good) return false;
                 tc_fence_after();
@@ -516,17 +599,18 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     tc_commit(&sh.slab_empty[bs]);
                     ++slab_it;
                 }
+                if (jj == w.n_kv - 1) tc_commit(&sh.q_empty[t][qb]);  // the item's last use of the query tile
                 return true;
             };
-            if (ok) ok = issue_s(0);
-            for (int j = 0; j < n_kv && ok; ++j) {
-                if (j + 1 < n_kv) {
+            ok = issue_s(0);
+            for (int j = 0; j < w.n_kv && ok; ++j) {
+                if (j + 1 < w.n_kv) {
                     ok = issue_s(j + 1);
                     if (!ok) break;
                 }
-                const int v_it = 2 * j + 1, v_slot = v_it % kStages;
+                const int v_it = it + 2 * j + 1, v_slot = v_it % kStages;
                 ok = mbar_wait(&sh.kv_full[v_slot], (v_it / kStages) & 1, sh, status, kErrKvFull);
-                if (ok) ok = mbar_wait(&sh.p_full[t], j & 1, sh, status, kErrPFull);
+                if (ok) ok = mbar_wait(&sh.p_full[t], (step + j) & 1, sh, status, kErrPFull);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tc_fence_after();
@@ -542,11 +626,14 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 tc_commit(&sh.o_done[t]);
                 tc_commit(&sh.kv_empty[v_slot]);
             }
+            it += 2 * w.n_kv;
+            step += w.n_kv;
+            ++q_uses;
         }
         __syncwarp();
     } else if (warp == 11) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");  // spare warp of the producer / issuer warpgroup
-    } else if (warp < 4 * n_mt) {
+    } else {
         // ===== softmax group of query tile t ================================================================
         asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
         const int t = warp >> 2;
@@ -555,143 +642,150 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         const uint32_t s_tmem = tmem + lane_addr + t * kBlockN;
         const uint32_t o_tmem = tmem + lane_addr + 256 + t * kHeadDim;
         const uint32_t p_tmem = tmem + lane_addr + 384 + t * 64;
-        const int row = q_row0 + t * kBlockM + r;
-        float m_ref = -INFINITY, l = 0.0f;  // reference max (log2 units, scale applied) and running sum
         bool ok = true;
+        int step = 0;  // key tiles processed so far by this query tile: phase of s_full / s_empty / p_full / o_done
+        for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+            const WorkItem w = decode_item(item, nblk_x, nseg, cu, q_begin, q_end);
+            if (!w.valid || t >= w.n_mt) continue;
+            const int n_kv = w.n_kv;
+            const int row = w.q_row0 + t * kBlockM + r;
+            float m_ref = -INFINITY, l = 0.0f;  // reference max (log2 units, scale applied) and running sum
 #ifdef COME_ATTN_PROFILE
-        const long long prof_loop_t0 = clock64();
+            const long long prof_loop_t0 = clock64();
 #endif
 
-        for (int j = 0; j < n_kv && ok; ++j) {
-            if ((warp & 3) == 0) PROF_TRACE(t, j, 0);
-            ok = mbar_wait(&sh.s_full[t], j & 1, sh, status, kErrSFull);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            tc_fence_after();
-            if ((warp & 3) == 0) PROF_TRACE(t, j, 1);
-            // The whole 128-score row is pulled into registers at once, which frees S for the next Q K^T right away;
-            // the row is then turned into probabilities 32 columns at a time.
-            uint32_t srow[4][32];
-            tmem_ld32(s_tmem + 0, srow[0]);
-            tmem_ld32(s_tmem + 32, srow[1]);
-            tmem_ld32(s_tmem + 64, srow[2]);
-            tmem_ld32(s_tmem + 96, srow[3]);
-            tc_wait_ld();
-            if ((warp & 3) == 0) PROF_TRACE(t, j, 4);
-            tc_fence_before();
-            mbar_arrive(&sh.s_empty[t]);
-            bool o_ready = (j == 0);  // P V of the previous key tile complete: O stable, P buffer free
-            // Row max over all 128 scores first: eight independent 3-input chains (16 scores each) keep the ALU pipe fed,
-            // and the rare rescale is decided once per key tile, so the exponentials below are one straight-line block.
-            float mx[8];
-#pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                const uint32_t *e = &srow[c >> 1][(c & 1) * 16];
-                float m = max3(__uint_as_float(e[0]), __uint_as_float(e[1]), __uint_as_float(e[2]));
-#pragma unroll
-                for (int i = 3; i < 15; i += 2) m = max3(m, __uint_as_float(e[i]), __uint_as_float(e[i + 1]));
-                mx[c] = fmaxf(m, __uint_as_float(e[15]));
-            }
-            const float t_max = max3(max3(mx[0], mx[1], mx[2]), max3(mx[3], mx[4], mx[5]), fmaxf(mx[6], mx[7])) * scale_log2;
-            const bool need = t_max > m_ref + kRescaleThreshold;  // always true on the first key tile (m_ref = -inf)
-            if (__any_sync(0xffffffffu, need)) {
-                float alpha = 1.0f;
-                if (need) {
-                    alpha = (m_ref == -INFINITY) ? 0.0f : fast_exp2(m_ref - t_max);
-                    m_ref = t_max;
-                    l *= alpha;
+            for (int j = 0; j < n_kv && ok; ++j) {
+                if ((warp & 3) == 0) PROF_TRACE(t, j, 0);
+                ok = mbar_wait(&sh.s_full[t], (step + j) & 1, sh, status, kErrSFull);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tc_fence_after();
+                if ((warp & 3) == 0) PROF_TRACE(t, j, 1);
+                // The whole 128-score row is pulled into registers at once, which frees S for the next Q K^T right away;
+                // the row is then turned into probabilities 32 columns at a time.
+                uint32_t srow[4][32];
+                tmem_ld32(s_tmem + 0, srow[0]);
+                tmem_ld32(s_tmem + 32, srow[1]);
+                tmem_ld32(s_tmem + 64, srow[2]);
+                tmem_ld32(s_tmem + 96, srow[3]);
+                tc_wait_ld();
+                if ((warp & 3) == 0) PROF_TRACE(t, j, 4);
+                tc_fence_before();
+                mbar_arrive(&sh.s_empty[t]);
+                bool o_ready = (j == 0);  // P V of the previous key tile complete: O stable, P buffer free
+                // Row max over all 128 scores first: eight independent 3-input chains (16 scores each) keep the ALU pipe fed,
+                // and the rare rescale is decided once per key tile, so the exponentials below are one straight-line block.
+                float mx[8];
+    #pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    const uint32_t *e = &srow[c >> 1][(c & 1) * 16];
+                    float m = max3(__uint_as_float(e[0]), __uint_as_float(e[1]), __uint_as_float(e[2]));
+    #pragma unroll
+                    for (int i = 3; i < 15; i += 2) m = max3(m, __uint_as_float(e[i]), __uint_as_float(e[i + 1]));
+                    mx[c] = fmaxf(m, __uint_as_float(e[15]));
                 }
-                if (j > 0) {  // rescale what earlier key tiles accumulated
-                    ok = mbar_wait(&sh.o_done[t], (j - 1) & 1, sh, status, kErrODone);
-                    ok = __all_sync(0xffffffffu, ok);
-                    if (!ok) break;
-                    tc_fence_after();
-                    o_ready = true;
-                    rescale_staged<kBF16>(o_tmem, p_tmem, alpha, true, 0);
-                }
-            }
-            // p = 2^(s * scale*log2e - m_ref), two scores per instruction; a share of the pairs takes the polynomial
-            // route so that the special-function unit and the FMA pipe split the exponentials.
-            const f32x2_t scale2 = pack_f32x2(scale_log2, scale_log2), neg_m2 = pack_f32x2(-m_ref, -m_ref);
-            f32x2_t sum2 = pack_f32x2(0.0f, 0.0f);
-            auto quarter = [&](const uint32_t(&a)[32], uint32_t(&pk)[16]) {
-#pragma unroll
-                for (int pair = 0; pair < 16; ++pair) {
-                    const f32x2_t x2 = fma_f32x2(pack_f32x2(__uint_as_float(a[2 * pair]), __uint_as_float(a[2 * pair + 1])), scale2, neg_m2);
-                    float x0, x1, p0, p1;
-                    unpack_f32x2(x2, x0, x1);
-                    if ((kPolyPairs >> pair) & 1u) {
-                        exp2_poly_x2(x0, x1, p0, p1);
-                    } else {
-                        p0 = fast_exp2(x0);
-                        p1 = fast_exp2(x1);
+                const float t_max = max3(max3(mx[0], mx[1], mx[2]), max3(mx[3], mx[4], mx[5]), fmaxf(mx[6], mx[7])) * scale_log2;
+                const bool need = t_max > m_ref + kRescaleThreshold;  // always true on the first key tile (m_ref = -inf)
+                if (__any_sync(0xffffffffu, need)) {
+                    float alpha = 1.0f;
+                    if (need) {
+                        alpha = (m_ref == -INFINITY) ? 0.0f : fast_exp2(m_ref - t_max);
+                        m_ref = t_max;
+                        l *= alpha;
                     }
-                    sum2 = add_f32x2(sum2, pack_f32x2(p0, p1));
-                    pk[pair] = pack2<kBF16>(p0, p1);
+                    if (j > 0) {  // rescale what earlier key tiles accumulated
+                        ok = mbar_wait(&sh.o_done[t], (step + j - 1) & 1, sh, status, kErrODone);
+                        ok = __all_sync(0xffffffffu, ok);
+                        if (!ok) break;
+                        tc_fence_after();
+                        o_ready = true;
+                        rescale_staged<kBF16>(o_tmem, p_tmem, alpha, true, 0);
+                    }
                 }
-            };
-            {
-                uint32_t pk[16];
-                quarter(srow[0], pk);
-                if (!o_ready) {  // the P buffer is free once P V of the previous key tile has completed
-                    ok = mbar_wait(&sh.o_done[t], (j - 1) & 1, sh, status, kErrODone);
-                    ok = __all_sync(0xffffffffu, ok);
-                    if (!ok) break;
-                    tc_fence_after();
+                // p = 2^(s * scale*log2e - m_ref), two scores per instruction; a share of the pairs takes the polynomial
+                // route so that the special-function unit and the FMA pipe split the exponentials.
+                const f32x2_t scale2 = pack_f32x2(scale_log2, scale_log2), neg_m2 = pack_f32x2(-m_ref, -m_ref);
+                f32x2_t sum2 = pack_f32x2(0.0f, 0.0f);
+                auto quarter = [&](const uint32_t(&a)[32], uint32_t(&pk)[16]) {
+    #pragma unroll
+                    for (int pair = 0; pair < 16; ++pair) {
+                        const f32x2_t x2 = fma_f32x2(pack_f32x2(__uint_as_float(a[2 * pair]), __uint_as_float(a[2 * pair + 1])), scale2, neg_m2);
+                        float x0, x1, p0, p1;
+                        unpack_f32x2(x2, x0, x1);
+                        if ((kPolyPairs >> pair) & 1u) {
+                            exp2_poly_x2(x0, x1, p0, p1);
+                        } else {
+                            p0 = fast_exp2(x0);
+                            p1 = fast_exp2(x1);
+                        }
+                        sum2 = add_f32x2(sum2, pack_f32x2(p0, p1));
+                        pk[pair] = pack2<kBF16>(p0, p1);
+                    }
+                };
+                {
+                    uint32_t pk[16];
+                    quarter(srow[0], pk);
+                    if (!o_ready) {  // the P buffer is free once P V of the previous key tile has completed
+                        ok = mbar_wait(&sh.o_done[t], (step + j - 1) & 1, sh, status, kErrODone);
+                        ok = __all_sync(0xffffffffu, ok);
+                        if (!ok) break;
+                        tc_fence_after();
+                    }
+                    tmem_st16(p_tmem, pk);  // 32 keys -> 16 columns of 16-bit pairs
+                    if ((warp & 3) == 0) PROF_TRACE(t, j, 5);
                 }
-                tmem_st16(p_tmem, pk);  // 32 keys -> 16 columns of 16-bit pairs
-                if ((warp & 3) == 0) PROF_TRACE(t, j, 5);
+    #pragma unroll
+                for (int q = 1; q < 4; ++q) {
+                    uint32_t pk[16];
+                    quarter(srow[q], pk);
+                    tmem_st16(p_tmem + 16 * q, pk);
+                    if ((warp & 3) == 0 && q < 3) PROF_TRACE(t, j, 5 + q);
+                }
+                {
+                    float s_lo, s_hi;
+                    unpack_f32x2(sum2, s_lo, s_hi);
+                    l += s_lo + s_hi;
+                }
+                if (!ok) break;
+                if ((warp & 3) == 0) PROF_TRACE(t, j, 2);
+                tc_wait_st();
+                tc_fence_before();
+                mbar_arrive(&sh.p_full[t]);
+                if ((warp & 3) == 0) PROF_TRACE(t, j, 3);
             }
-#pragma unroll
-            for (int q = 1; q < 4; ++q) {
-                uint32_t pk[16];
-                quarter(srow[q], pk);
-                tmem_st16(p_tmem + 16 * q, pk);
-                if ((warp & 3) == 0 && q < 3) PROF_TRACE(t, j, 5 + q);
-            }
-            {
-                float s_lo, s_hi;
-                unpack_f32x2(sum2, s_lo, s_hi);
-                l += s_lo + s_hi;
-            }
-            if (!ok) break;
-            if ((warp & 3) == 0) PROF_TRACE(t, j, 2);
-            tc_wait_st();
-            tc_fence_before();
-            mbar_arrive(&sh.p_full[t]);
-            if ((warp & 3) == 0) PROF_TRACE(t, j, 3);
-        }
 
 #ifdef COME_ATTN_PROFILE
-        prof_add(15, prof_loop_t0);
+            prof_add(15, prof_loop_t0);
 #endif
-        if (warp == 0) PROF_TRACE(2, 0, 2);  // key loop done
-        if (ok) {
-            ok = mbar_wait(&sh.o_done[t], (n_kv - 1) & 1, sh, status, kErrODone);
-            ok = __all_sync(0xffffffffu, ok);
-        }
-        if (ok) {
-            tc_fence_after();
-            uint32_t o[2][32];
-            tmem_ld32(o_tmem + 0, o[0]);
-            tmem_ld32(o_tmem + 32, o[1]);
-            tc_wait_ld();
-            if (row < q_hi) {
-                const float inv = 1.0f / l;
-                uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<T *>(out_ptr) + (int64_t)(row - q_begin) * o_rs + (int64_t)head * kHeadDim);
-#pragma unroll
-                for (int c = 0; c < 2; ++c)
-#pragma unroll
-                    for (int i = 0; i < 32; i += 8) {
-                        uint4 v;
-                        v.x = pack2<kBF16>(__uint_as_float(o[c][i + 0]) * inv, __uint_as_float(o[c][i + 1]) * inv);
-                        v.y = pack2<kBF16>(__uint_as_float(o[c][i + 2]) * inv, __uint_as_float(o[c][i + 3]) * inv);
-                        v.z = pack2<kBF16>(__uint_as_float(o[c][i + 4]) * inv, __uint_as_float(o[c][i + 5]) * inv);
-                        v.w = pack2<kBF16>(__uint_as_float(o[c][i + 6]) * inv, __uint_as_float(o[c][i + 7]) * inv);
-                        dst[(c * 32 + i) / 8] = v;
-                    }
-                if (lse) lse[(int64_t)head * (q_end - q_begin) + (row - q_begin)] = (m_ref + log2f(l)) * kLn2;
+            if (warp == 0) PROF_TRACE(2, 0, 2);  // key loop done
+            if (ok) {
+                ok = mbar_wait(&sh.o_done[t], (step + n_kv - 1) & 1, sh, status, kErrODone);
+                ok = __all_sync(0xffffffffu, ok);
             }
+            if (ok) {
+                tc_fence_after();
+                uint32_t o[2][32];
+                tmem_ld32(o_tmem + 0, o[0]);
+                tmem_ld32(o_tmem + 32, o[1]);
+                tc_wait_ld();  // O is in registers: the next item's first P V may overwrite the accumulator
+                if (row < w.q_hi) {
+                    const float inv = 1.0f / l;
+                    uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<T *>(out_ptr) + (int64_t)(row - q_begin) * o_rs + (int64_t)w.head * kHeadDim);
+#pragma unroll
+                    for (int c = 0; c < 2; ++c)
+#pragma unroll
+                        for (int i = 0; i < 32; i += 8) {
+                            uint4 v;
+                            v.x = pack2<kBF16>(__uint_as_float(o[c][i + 0]) * inv, __uint_as_float(o[c][i + 1]) * inv);
+                            v.y = pack2<kBF16>(__uint_as_float(o[c][i + 2]) * inv, __uint_as_float(o[c][i + 3]) * inv);
+                            v.z = pack2<kBF16>(__uint_as_float(o[c][i + 4]) * inv, __uint_as_float(o[c][i + 5]) * inv);
+                            v.w = pack2<kBF16>(__uint_as_float(o[c][i + 6]) * inv, __uint_as_float(o[c][i + 7]) * inv);
+                            dst[(c * 32 + i) / 8] = v;
+                        }
+                    if (lse) lse[(int64_t)w.head * (q_end - q_begin) + (row - q_begin)] = (m_ref + log2f(l)) * kLn2;
+                }
+            }
+            step += n_kv;
         }
     }
 
@@ -798,17 +892,25 @@ int attn_sm100_launch(const AttnArgs &a, cudaStream_t stream) {
     const size_t smem = sizeof(SharedStorage) + 1024;
     const int64_t q_rows = a.q_end - a.q_begin;
     const int64_t span = a.max_seqlen < q_rows ? a.max_seqlen : q_rows;  // most query rows any segment can own here
-    dim3 grid((unsigned)((span + 2 * kBlockM - 1) / (2 * kBlockM)), a.nseg, a.H);
+    const int nblk_x = (int)((span + 2 * kBlockM - 1) / (2 * kBlockM));
+    const int64_t items = (int64_t)nblk_x * a.nseg * a.H;
+    if (items <= 0) return COME_OK;
+    if (items >= (1ll << 31)) {
+        set_error("come_attn_varlen_fwd: %lld work items do not fit 32 bits", (long long)items);
+        return COME_ERR_ARG;
+    }
+    const int sms = sm_count();
+    const unsigned grid = (unsigned)(items < sms ? items : sms);  // persistent: one CTA per SM walks the items
     const float scale_log2 = a.scale * kLog2e;
     const float inv_scale = 1.0f / a.scale;
     if (a.dtype == COME_BF16) {
         if (!attr_done(0)) COME_CUDA(cudaFuncSetAttribute(attn_fwd_sm100_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         attn_fwd_sm100_kernel<true><<<grid, kThreads, smem, stream>>>(mq, mk, mv, a.bias, a.cu, scale_log2, inv_scale, a.out, a.o_rs, a.lse,
-                                                                     (int)a.q_begin, (int)a.q_end, status);
+                                                                     (int)a.q_begin, (int)a.q_end, nblk_x, a.nseg, a.H, a.max_seqlen_dev, status);
     } else {
         if (!attr_done(1)) COME_CUDA(cudaFuncSetAttribute(attn_fwd_sm100_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         attn_fwd_sm100_kernel<false><<<grid, kThreads, smem, stream>>>(mq, mk, mv, a.bias, a.cu, scale_log2, inv_scale, a.out, a.o_rs, a.lse,
-                                                                      (int)a.q_begin, (int)a.q_end, status);
+                                                                      (int)a.q_begin, (int)a.q_end, nblk_x, a.nseg, a.H, a.max_seqlen_dev, status);
     }
     return check_launch("come_attn_varlen_fwd (tcgen05 kernel)");
 }

@@ -15,6 +15,7 @@ struct AttnArgs {
     int H, D;
     int64_t q_rs, k_rs, v_rs, o_rs;  // row strides in elements
     int nseg, max_seqlen;
+    const int *max_seqlen_dev;  // optional device-resident bound of the longest segment (tightens the work list)
     float scale;
 };
 

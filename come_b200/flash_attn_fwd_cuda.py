@@ -158,7 +158,8 @@ def varlen_fwd_w_perkey_bias(q, k, v, out_, cu_seqlens_q, cu_seqlens_k, seqused_
                  window_size_left, window_size_right, softcap, return_softmax, gen_)
 
 
-def varlen_fwd_rows(q_rows, k, v, cu_seqlens, max_seqlen, perkey_bias, softmax_scale, row_begin, out_=None):
+def varlen_fwd_rows(q_rows, k, v, cu_seqlens, max_seqlen, perkey_bias, softmax_scale, row_begin, out_=None,
+                    max_seqlen_dev=None):
     """Attention of a slice of the query rows against all keys / values (no counterpart in the reference: the
     per-GPU piece of global attention sharded by query rows).
 
@@ -192,5 +193,6 @@ def varlen_fwd_rows(q_rows, k, v, cu_seqlens, max_seqlen, perkey_bias, softmax_s
         _lib.check(_lib.lib().come_attn_varlen_fwd_rows(
             ptr(q_rows), ptr(k), ptr(v), dtype_code(q_rows.dtype), total, int(row_begin), rows, num_heads, head_size,
             q_rows.stride(0), k.stride(0), v.stride(0), ptr(perkey_bias), ptr(cu_seqlens), cu_seqlens.numel() - 1,
-            int(max_seqlen), float(softmax_scale), ptr(out), out.stride(0), ptr(lse), _backend, stream_ptr(q_rows.device)))
+            int(max_seqlen), ptr(max_seqlen_dev), float(softmax_scale), ptr(out), out.stride(0), ptr(lse), _backend,
+            stream_ptr(q_rows.device)))
     return [out, lse]

@@ -68,6 +68,7 @@ class StaticScene:
         self.seg_max = e((1,), dtype=torch.int32, device=d)
         self.bias = e((rows,), dtype=dt, device=d)
         self.cu_global = torch.zeros((self.scenes + 1,), dtype=torch.int32, device=d)
+        self.global_max = e((1,), dtype=torch.int32, device=d)  # longest scene (global-attention segment), device side
         self.ratios = torch.full((frames,), float(threshold), dtype=torch.float32, device=d)
         self.ws_bytes = int(_lib.lib().come_merge_plan_workspace_bytes(frames))
         self.ws = e((self.ws_bytes,), dtype=torch.uint8, device=d)
@@ -98,17 +99,21 @@ class StaticScene:
         torch.log(self.weight, out=self._bias32)
         self.bias.copy_(self._bias32)
         self.cu_global.copy_(self.offsets[:: self.fps])  # scene boundaries = every frames_per_scene-th frame offset
+        torch.amax(self.cu_global[1:] - self.cu_global[:-1], dim=0, keepdim=True, out=self.global_max)
         q, k, v = self.qkv[:, 0], self.qkv[:, 1], self.qkv[:, 2]
         for kind in self.layer_kinds:
             _lib.check(lib.come_merge(ptr(self.x), code, self.frames, self.C, C.byref(self.layout), ptr(self.mask),
                                       ptr(self.group_prefix), ptr(self.offsets), ptr(self.merged), st))
+            # host-side bound = the unmerged worst case (the graph serves every mask); the true longest segment, which
+            # the plan kernel left in device memory, trims the kernel's work list to the query blocks that exist
             if kind == "global":
-                cu, nseg, max_len = self.cu_global, self.scenes, self.fps * self.N
+                cu, nseg, max_len, max_dev = self.cu_global, self.scenes, self.fps * self.N, self.global_max
             else:
-                cu, nseg, max_len = self.offsets, self.frames, self.N
-            _lib.check(lib.come_attn_varlen_fwd(ptr(q), ptr(k), ptr(v), code, self.rows_max, self.H, self.D, q.stride(0),
-                                                k.stride(0), v.stride(0), ptr(self.bias), ptr(cu), nseg, max_len,
-                                                self.scale, ptr(self.attn), self.attn.stride(0), ptr(self.lse), 0, st))
+                cu, nseg, max_len, max_dev = self.offsets, self.frames, self.N, self.seg_max
+            _lib.check(lib.come_attn_varlen_fwd_rows(ptr(q), ptr(k), ptr(v), code, self.rows_max, 0, self.rows_max, self.H,
+                                                     self.D, q.stride(0), k.stride(0), v.stride(0), ptr(self.bias), ptr(cu),
+                                                     nseg, max_len, ptr(max_dev), self.scale, ptr(self.attn),
+                                                     self.attn.stride(0), ptr(self.lse), 0, st))
             _lib.check(lib.come_unmerge(ptr(self.attn), ptr(self.rev), self.rows_max, self.C, code, ptr(self.out), st))
 
     def capture(self) -> "StaticScene":

@@ -186,12 +186,17 @@ int come_attn_varlen_fwd(const void *q_dev, const void *k_dev, const void *v_dev
  * `total` packed tokens.  This is the per-GPU piece of global attention sharded by query rows: every GPU attends
  * its own rows to the all-gathered keys and values.  No counterpart in the reference (single GPU only); with
  * q_row_begin = 0 and q_rows = total it is come_attn_varlen_fwd.
+ *   max_seqlen_dev  optional (may be NULL): one int32 in device memory, the true longest segment.  max_seqlen (host) must
+ *                   still be an upper bound; a caller that cannot read the true value back (a captured graph that
+ *                   serves every merge mask) passes its worst case there and the value the plan kernel wrote
+ *                   (come_merge_plan's seg_max_dev) here, so that the kernel's work list holds no empty query blocks.
  */
 int come_attn_varlen_fwd_rows(const void *q_dev, const void *k_dev, const void *v_dev, int dtype, int64_t total,
                               int64_t q_row_begin, int64_t q_rows, int num_heads, int head_dim, int64_t q_row_stride,
                               int64_t k_row_stride, int64_t v_row_stride, const void *bias_dev,
-                              const int32_t *cu_seqlens_dev, int num_segments, int max_seqlen, float softmax_scale,
-                              void *out_dev, int64_t out_row_stride, float *lse_dev, int backend, void *stream);
+                              const int32_t *cu_seqlens_dev, int num_segments, int max_seqlen,
+                              const int32_t *max_seqlen_dev, float softmax_scale, void *out_dev, int64_t out_row_stride,
+                              float *lse_dev, int backend, void *stream);
 
 /*
  * Pre-attention preparation of the packed qkv tensor [total, 3, num_heads, head_dim], in place, one pass:
