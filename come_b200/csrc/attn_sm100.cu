@@ -32,13 +32,21 @@ namespace come {
 
 namespace {
 
+constexpr int kTiles = 3;         // query tiles (128 rows each) per CTA and work item, one softmax warpgroup each
 constexpr int kBlockM = 128;
-constexpr int kBlockN = 128;
+constexpr int kBlockN = 64;       // keys per step
 constexpr int kHeadDim = 64;
-constexpr int kStages = 6;       // K/V ring slots, 16 KiB each
-constexpr int kSlabStages = 3;   // bias slab ring slots, 16 KiB each (only two 16-byte chunks per row are used)
-constexpr int kThreads = 384;   // 8 softmax warps, producer, two MMA issuers (one per query tile), one spare
-constexpr int kTileBytes = kBlockN * kHeadDim * 2;  // 16384
+constexpr int kStages = 8;        // K/V ring slots, 8 KiB each
+constexpr int kSlabStages = 3;    // bias slab ring slots, 8 KiB each (only two 16-byte chunks per row are used)
+constexpr int kProducerWarp = 4 * kTiles;      // warps 0 .. 4*kTiles-1 are the softmax groups
+constexpr int kIssuerWarp0 = kProducerWarp + 1;  // one MMA issuer warp per query tile
+constexpr int kThreads = 32 * (kIssuerWarp0 + kTiles);  // 512: three softmax warpgroups + one producer / issuer warpgroup
+constexpr int kQTileBytes = kBlockM * kHeadDim * 2;   // 16384
+constexpr int kKvTileBytes = kBlockN * kHeadDim * 2;  // 8192
+// Tensor-memory columns: S_t (scores, float32) | O_t (accumulator, float32) | P_t (probabilities, 16-bit pairs)
+constexpr uint32_t kTmemS = 0, kTmemO = kTiles * kBlockN, kTmemP = kTmemO + kTiles * kHeadDim;
+static_assert(kTmemP + kTiles * (kBlockN / 2) <= 512, "tensor memory holds 512 columns");
+static_assert(kThreads % 128 == 0, "setmaxnreg works on whole warpgroups");
 constexpr uint32_t kTmemCols = 512;
 constexpr long long kWaitTicks = 1ll << 29;
 constexpr float kLog2e = 1.4426950408889634f;
@@ -53,21 +61,21 @@ constexpr uint32_t kPolyPairs = COME_POLY_MASK;
 constexpr float kMasked = -3.0e38f;        // "minus infinity" of a masked key, still finite in bfloat16
 
 struct SharedStorage {
-    alignas(1024) uint8_t q[2][2][kTileBytes];            // [query tile][buffer]: the next item's Q is loaded ahead
-    alignas(1024) uint8_t kv[kStages][kTileBytes];
-    alignas(1024) uint8_t q_slab[kTileBytes];             // columns 0,1 = 1.0, rest 0: the A side of the bias step
-    alignas(1024) uint8_t k_slab[kSlabStages][kTileBytes];  // columns 0,1 = bias/scale (hi, lo): the B side
-    alignas(8) uint64_t q_full[2][2];                     // [query tile][buffer]
-    uint64_t q_empty[2][2];
+    alignas(1024) uint8_t q[kTiles][2][kQTileBytes];        // [query tile][buffer]: the next item's Q is loaded ahead
+    alignas(1024) uint8_t kv[kStages][kKvTileBytes];
+    alignas(1024) uint8_t q_slab[kQTileBytes];              // columns 0,1 = 1.0, rest 0: the A side of the bias step
+    alignas(1024) uint8_t k_slab[kSlabStages][kKvTileBytes];  // columns 0,1 = bias/scale (hi, lo): the B side
+    alignas(8) uint64_t q_full[kTiles][2];                  // [query tile][buffer]
+    uint64_t q_empty[kTiles][2];
     uint64_t q_slab_full;
     uint64_t kv_full[kStages];
     uint64_t kv_empty[kStages];
     uint64_t slab_full[kSlabStages];
     uint64_t slab_empty[kSlabStages];
-    uint64_t s_full[2];
-    uint64_t p_full[2];
-    uint64_t o_done[2];
-    uint64_t s_empty[2];
+    uint64_t s_full[kTiles];
+    uint64_t p_full[kTiles];
+    uint64_t o_done[kTiles];
+    uint64_t s_empty[kTiles];
     uint32_t tmem_base;
     volatile uint32_t abort_flag;
 };
@@ -97,44 +105,13 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Optional cycle accounting of the barrier waits of CTA (0,0,0) (build with -DCOME_ATTN_PROFILE; development aid):
-// slot = bit index of the wait's error code (+16 for the second softmax group); slot 15 / 31 = softmax loop total.
-#ifdef COME_ATTN_PROFILE
-__device__ unsigned long long g_attn_timers[32];
-__device__ long long g_attn_trace[4][16][8];  // [role: wg0, wg1, mma t0, mma t1][step][event]
-#define PROF_TRACE(role, step, ev)                                                                      \
-    do {                                                                                                \
-        if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (threadIdx.x & 31) == 0 && (step) < 16) \
-            g_attn_trace[role][step][ev] = clock64();                                                   \
-    } while (0)
-__device__ __forceinline__ void prof_add(int slot, long long t0) {
-    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (threadIdx.x & 31) == 0 && (threadIdx.x < 32 || threadIdx.x >= 128))
-        atomicAdd(&g_attn_timers[slot + ((threadIdx.x >= 128 && threadIdx.x < 256) ? 16 : 0)], (unsigned long long)(clock64() - t0));
-}
-#else
-#define PROF_TRACE(role, step, ev) do {} while (0)
-#endif
-
 // Bounded wait.  Returns false (and raises the abort flag + the device status word) when it gives up.
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, SharedStorage &sh, unsigned int *status,
                                           uint32_t code) {
-#ifdef COME_ATTN_PROFILE
-    const long long t0 = clock64();
-    if (mbar_try_wait(bar, parity)) {
-        prof_add(__ffs((int)code) - 1, t0);
-        return true;
-    }
-#else
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
-#endif
     while (true) {
-        if (mbar_try_wait(bar, parity)) {
-#ifdef COME_ATTN_PROFILE
-            prof_add(__ffs((int)code) - 1, t0);
-#endif
-            return true;
-        }
+        if (mbar_try_wait(bar, parity)) return true;
         if (sh.abort_flag != 0) return false;
         if (clock64() - t0 > kWaitTicks) {
             sh.abort_flag = 1;
@@ -285,43 +262,19 @@ template <bool kBF16> __device__ __forceinline__ uint32_t pack2(float lo, float 
     }
 }
 
-// Rare path of the softmax: a row's running max grew by more than the threshold, so everything accumulated against
-// the old reference max is scaled by alpha = 2^(old - new): the output accumulator (if earlier key tiles exist) and
-// the quarters of this tile's probabilities already staged in TMEM.  Kept out of line: inlined four times into the
-// unrolled quarter loop it doubles the hot loop's code size for a path taken a handful of times per row.
-template <bool kBF16>
-__device__ __noinline__ void rescale_staged(uint32_t o_tmem, uint32_t p_tmem, float alpha, bool scale_o, int staged_quarters) {
-    if (scale_o) {
-        uint32_t o[2][32];
-        tmem_ld32(o_tmem + 0, o[0]);
-        tmem_ld32(o_tmem + 32, o[1]);
-        tc_wait_ld();
+// Multiplies the 64 float32 accumulator columns of this thread's row by alpha (the rare rescale when a row's running
+// max grew past the threshold).  Out of line: inlined it would only bloat the hot loop.
+__device__ __noinline__ void scale_accumulator(uint32_t o_tmem, float alpha) {
+    uint32_t o[2][32];
+    tmem_ld32(o_tmem + 0, o[0]);
+    tmem_ld32(o_tmem + 32, o[1]);
+    tc_wait_ld();
 #pragma unroll
-        for (int c = 0; c < 2; ++c)
+    for (int c = 0; c < 2; ++c)
 #pragma unroll
-            for (int i = 0; i < 32; ++i) o[c][i] = __float_as_uint(__uint_as_float(o[c][i]) * alpha);
-        tmem_st32(o_tmem + 0, o[0]);
-        tmem_st32(o_tmem + 32, o[1]);
-    }
-    for (int qq = 0; qq < staged_quarters; ++qq) {
-        uint32_t st[16];
-        tc_wait_st();
-        tmem_ld16(p_tmem + 16 * qq, st);
-        tc_wait_ld();
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            float lo, hi;
-            if constexpr (kBF16) {
-                const float2 f = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162 *>(&st[i]));
-                lo = f.x; hi = f.y;
-            } else {
-                const float2 f = __half22float2(*reinterpret_cast<__half2 *>(&st[i]));
-                lo = f.x; hi = f.y;
-            }
-            st[i] = pack2<kBF16>(lo * alpha, hi * alpha);
-        }
-        tmem_st16(p_tmem + 16 * qq, st);
-    }
+        for (int i = 0; i < 32; ++i) o[c][i] = __float_as_uint(__uint_as_float(o[c][i]) * alpha);
+    tmem_st32(o_tmem + 0, o[0]);
+    tmem_st32(o_tmem + 32, o[1]);
 }
 
 // Shared-memory matrix descriptor of a tile whose rows are 128 bytes wide and 128-byte swizzled (what a TMA
@@ -349,11 +302,11 @@ enum : uint32_t {
     kErrSFull = 1u << 5, kErrSEmpty = 1u << 6, kErrPFull = 1u << 7, kErrODone = 1u << 8,
 };
 
-// One work item = the (up to) two 128-row query tiles [q_row0, q_row0 + 256) of one (segment, head).
+// One work item = the (up to) kTiles 128-row query tiles [q_row0, q_row0 + kTiles * 128) of one (segment, head).
 struct WorkItem {
     int head, s0, s1;   // head, key range of the segment
     int q_row0, q_hi;   // first query row of the item, end of the query rows this launch owns in the segment
-    int n_mt, n_kv;     // active query tiles (1 or 2), key tiles
+    int n_mt, n_kv;     // active query tiles (1 .. kTiles), key tiles
     bool ragged_tail;   // the last key tile is partial
     bool valid;
 };
@@ -371,9 +324,9 @@ __device__ __forceinline__ WorkItem decode_item(int item, int nblk_x, int nseg, 
     // slice when the query rows are sharded).  q / out / lse are indexed by (global row - q_begin); k / v by global row.
     const int q_lo = max(w.s0, q_begin);
     w.q_hi = min(w.s1, q_end);
-    w.q_row0 = q_lo + bx * (2 * kBlockM);
+    w.q_row0 = q_lo + bx * (kTiles * kBlockM);
     w.valid = w.q_row0 < w.q_hi;
-    w.n_mt = (w.q_row0 + kBlockM < w.q_hi) ? 2 : 1;  // query tiles with at least one valid row
+    w.n_mt = min(kTiles, (w.q_hi - w.q_row0 + kBlockM - 1) / kBlockM);  // query tiles with at least one valid row
     w.n_kv = (seg_len + kBlockN - 1) / kBlockN;
     w.ragged_tail = (seg_len % kBlockN) != 0;
     return w;
@@ -399,7 +352,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     // the work list then shrinks to the query blocks that can exist, and the round-robin over CTAs stays balanced.
     if (max_len_dev != nullptr) {
         const int m = min(max(*max_len_dev, 0), q_end - q_begin);
-        nblk_x = min(nblk_x, (m + 2 * kBlockM - 1) / (2 * kBlockM));
+        nblk_x = min(nblk_x, (m + kTiles * kBlockM - 1) / (kTiles * kBlockM));
     }
     const int total_items = nblk_x * nseg * num_heads;
     const bool has_bias = bias_ptr != nullptr;
@@ -407,12 +360,11 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     auto uses_slab = [&](const WorkItem &w, int j) { return has_bias || (w.ragged_tail && j == w.n_kv - 1); };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    if (warp == 0) PROF_TRACE(2, 0, 0);  // kernel entry
 
     if (threadIdx.x == 0) {
         // an earlier CTA that gave up leaves the status word raised: later CTAs then skip their work
         sh.abort_flag = (*(volatile unsigned int *)status != 0) ? 1u : 0u;
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < kTiles; ++i) {
             for (int b = 0; b < 2; ++b) {
                 mbar_init(&sh.q_full[i][b], 1);
                 mbar_init(&sh.q_empty[i][b], 1);
@@ -424,16 +376,16 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         }
         for (int i = 0; i < kStages; ++i) {
             mbar_init(&sh.kv_full[i], 1);
-            mbar_init(&sh.kv_empty[i], 2);  // released by both issuer warps (an idle one arrives without an MMA)
+            mbar_init(&sh.kv_empty[i], kTiles);  // released by every issuer warp (an idle one arrives without an MMA)
         }
         for (int i = 0; i < kSlabStages; ++i) {
             mbar_init(&sh.slab_full[i], 1);
-            mbar_init(&sh.slab_empty[i], 2);
+            mbar_init(&sh.slab_empty[i], kTiles);
         }
         mbar_init(&sh.q_slab_full, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 9) {
+    if (warp == kIssuerWarp0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh.tmem_base)), "r"(kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -441,15 +393,14 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = sh.tmem_base;
-    // Register budget: the producer / issuer warpgroup needs few registers and hands its share to the two softmax
-    // warpgroups, which keep a whole 128-score row live (8 x 32 x 224 + 4 x 32 x 56 = 64512 <= 65536).
-    // (each role branch below starts with its setmaxnreg; the whole of warpgroup 2 = warps 8-11 must release.)
-    if (warp == 0) PROF_TRACE(2, 0, 1);  // set-up done
+    // Register budget: the producer / issuer warpgroup needs few registers and hands its share to the three softmax
+    // warpgroups (12 x 32 x 152 + 4 x 32 x 56 = 65536).  Each role branch below starts with its setmaxnreg; every warp
+    // of a warpgroup has to execute it.
     const bool dead = sh.abort_flag != 0;  // read after the barrier: uniform for the CTA
 
     if (dead) {
         // fall through to the common exit
-    } else if (warp == 8) {
+    } else if (warp == kProducerWarp) {
         // ===== producer =====================================================================================
         asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
         const T *bias = reinterpret_cast<const T *>(bias_ptr);
@@ -466,7 +417,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         }
         int it = 0;            // K/V ring position, advanced once per K or V tile in the order K0 V0 K1 V1 ...
         int slab_it = 0;       // bias slab ring position, advanced once per key tile that uses the bias step
-        int q_uses[2] = {0, 0};  // items that loaded query tile t so far (buffer and phase of q_full / q_empty)
+        int q_uses[kTiles] = {};  // items that loaded query tile t so far (buffer and phase of q_full / q_empty)
         for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
             const WorkItem w = decode_item(item, nblk_x, nseg, cu, q_begin, q_end);
             if (!w.valid) continue;
@@ -477,7 +428,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     const int n = q_uses[t], b = n & 1;
                     if (n >= 2) ok = mbar_wait(&sh.q_empty[t][b], ((n >> 1) - 1) & 1, sh, status, kErrQFull);
                     if (ok) {
-                        mbar_arrive_expect_tx(&sh.q_full[t][b], kTileBytes);
+                        mbar_arrive_expect_tx(&sh.q_full[t][b], kQTileBytes);
                         tma_load_3d(sh.q[t][b], &map_q, 0, w.head, w.q_row0 - q_begin + t * kBlockM, &sh.q_full[t][b]);
                     }
                 }
@@ -492,8 +443,8 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     if (!ok) break;
                     const uint32_t ks = smem_u32(sh.k_slab[bs]);
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const int r = lane * 4 + i;
+                    for (int i = 0; i < kBlockN / 32; ++i) {
+                        const int r = lane * (kBlockN / 32) + i;
                         const int key = w.s0 + j * kBlockN + r;
                         float hi = kMasked, lo = 0.0f;
                         if (key < w.s1) {
@@ -514,7 +465,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                         const int stage = (it + kv) % kStages;
                         ok = mbar_wait(&sh.kv_empty[stage], (((it + kv) / kStages) & 1) ^ 1, sh, status, kErrKvEmpty);
                         if (ok) {
-                            mbar_arrive_expect_tx(&sh.kv_full[stage], kTileBytes);
+                            mbar_arrive_expect_tx(&sh.kv_full[stage], kKvTileBytes);
                             tma_load_3d(sh.kv[stage], kv == 0 ? &map_k : &map_v, 0, w.head, w.s0 + j * kBlockN, &sh.kv_full[stage]);
                         }
                     }
@@ -523,20 +474,20 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 it += 2;
             }
         }
-    } else if (warp == 9 || warp == 10) {
+    } else if (warp >= kIssuerWarp0) {
         // ===== MMA issuer of query tile t (all lanes run the loop, one elected lane issues) ================
         asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
-        const int t = warp - 9;
+        const int t = warp - kIssuerWarp0;
         constexpr uint32_t idesc_qk = make_idesc(kBF16, kBlockM, kBlockN, false);
         constexpr uint32_t idesc_slab = make_idesc(true, kBlockM, kBlockN, false);
         constexpr uint32_t idesc_pv = make_idesc(kBF16, kBlockM, kHeadDim, true);
-        const uint64_t q_desc0 = make_smem_desc(smem_u32(sh.q[t][0]));  // buffer b: + b * (kTileBytes >> 4)
+        const uint64_t q_desc0 = make_smem_desc(smem_u32(sh.q[t][0]));  // buffer b: + b * (kQTileBytes >> 4)
         const uint64_t q_slab_desc = make_smem_desc(smem_u32(sh.q_slab));
-        const uint64_t kv_desc0 = make_smem_desc(smem_u32(sh.kv[0]));       // slot i: + i * (kTileBytes >> 4)
+        const uint64_t kv_desc0 = make_smem_desc(smem_u32(sh.kv[0]));       // slot i: + i * (kKvTileBytes >> 4)
         const uint64_t k_slab_desc0 = make_smem_desc(smem_u32(sh.k_slab[0]));
-        const uint32_t s_tmem = tmem + t * kBlockN;
-        const uint32_t o_tmem = tmem + 256 + t * kHeadDim;
-        const uint32_t p_tmem = tmem + 384 + t * 64;
+        const uint32_t s_tmem = tmem + kTmemS + t * kBlockN;
+        const uint32_t o_tmem = tmem + kTmemO + t * kHeadDim;
+        const uint32_t p_tmem = tmem + kTmemP + t * (kBlockN / 2);
         bool ok = mbar_wait(&sh.q_slab_full, 0, sh, status, kErrQFull);
         ok = __all_sync(0xffffffffu, ok);
         int it = 0;        // K/V ring position at the start of the current item (same count as the producer's)
@@ -572,7 +523,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             ok = mbar_wait(&sh.q_full[t][qb], (q_uses >> 1) & 1, sh, status, kErrQFull);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
-            const uint64_t q_desc = q_desc0 + (uint64_t)(qb * (kTileBytes >> 4));
+            const uint64_t q_desc = q_desc0 + (uint64_t)(qb * (kQTileBytes >> 4));
             // S(0), then per key tile j: S(j+1) = Q K_(j+1)^T as soon as the softmax group has read S(j) into registers,
             // and O += P(j) V_j as soon as P(j) is staged.  Ring slot of K_j is 2j, of V_j is 2j+1 (from `it`).  The other
             // query tile's issuer runs the same loop independently.
@@ -587,12 +538,12 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 good = __all_sync(0xffffffffu, good);
                 if (!good) return false;
                 tc_fence_after();
-                const uint64_t k_desc = kv_desc0 + (uint64_t)(k_slot * (kTileBytes >> 4));
+                const uint64_t k_desc = kv_desc0 + (uint64_t)(k_slot * (kKvTileBytes >> 4));
                 tc_mma_ss(s_tmem, q_desc + 0, k_desc + 0, idesc_qk, 0u);
                 tc_mma_ss(s_tmem, q_desc + 2, k_desc + 2, idesc_qk, 1u);
                 tc_mma_ss(s_tmem, q_desc + 4, k_desc + 4, idesc_qk, 1u);
                 tc_mma_ss(s_tmem, q_desc + 6, k_desc + 6, idesc_qk, 1u);
-                if (slab) tc_mma_ss(s_tmem, q_slab_desc, k_slab_desc0 + (uint64_t)(bs * (kTileBytes >> 4)), idesc_slab, 1u);
+                if (slab) tc_mma_ss(s_tmem, q_slab_desc, k_slab_desc0 + (uint64_t)(bs * (kKvTileBytes >> 4)), idesc_slab, 1u);
                 tc_commit(&sh.s_full[t]);
                 tc_commit(&sh.kv_empty[k_slot]);
                 if (slab) {
@@ -614,15 +565,11 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tc_fence_after();
-                const uint64_t v_desc = kv_desc0 + (uint64_t)(v_slot * (kTileBytes >> 4));
-                tc_mma_ts(o_tmem, p_tmem + 0, v_desc + 0 * 128, idesc_pv, j > 0 ? 1u : 0u);
-                tc_mma_ts(o_tmem, p_tmem + 8, v_desc + 1 * 128, idesc_pv, 1u);
-                tc_mma_ts(o_tmem, p_tmem + 16, v_desc + 2 * 128, idesc_pv, 1u);
-                tc_mma_ts(o_tmem, p_tmem + 24, v_desc + 3 * 128, idesc_pv, 1u);
-                tc_mma_ts(o_tmem, p_tmem + 32, v_desc + 4 * 128, idesc_pv, 1u);
-                tc_mma_ts(o_tmem, p_tmem + 40, v_desc + 5 * 128, idesc_pv, 1u);
-                tc_mma_ts(o_tmem, p_tmem + 48, v_desc + 6 * 128, idesc_pv, 1u);
-                tc_mma_ts(o_tmem, p_tmem + 56, v_desc + 7 * 128, idesc_pv, 1u);
+                const uint64_t v_desc = kv_desc0 + (uint64_t)(v_slot * (kKvTileBytes >> 4));
+                // 16 keys per instruction: 8 columns of 16-bit pairs of P, 16 rows (2048 bytes) of the V tile
+#pragma unroll
+                for (int i = 0; i < kBlockN / 16; ++i)
+                    tc_mma_ts(o_tmem, p_tmem + 8 * i, v_desc + (uint64_t)(i * 128), idesc_pv, (j > 0 || i > 0) ? 1u : 0u);
                 tc_commit(&sh.o_done[t]);
                 tc_commit(&sh.kv_empty[v_slot]);
             }
@@ -631,17 +578,15 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             ++q_uses;
         }
         __syncwarp();
-    } else if (warp == 11) {
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");  // spare warp of the producer / issuer warpgroup
     } else {
         // ===== softmax group of query tile t ================================================================
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 152;");
         const int t = warp >> 2;
         const int r = threadIdx.x & 127;                          // row inside the tile == TMEM lane
         const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
-        const uint32_t s_tmem = tmem + lane_addr + t * kBlockN;
-        const uint32_t o_tmem = tmem + lane_addr + 256 + t * kHeadDim;
-        const uint32_t p_tmem = tmem + lane_addr + 384 + t * 64;
+        const uint32_t s_tmem = tmem + lane_addr + kTmemS + t * kBlockN;
+        const uint32_t o_tmem = tmem + lane_addr + kTmemO + t * kHeadDim;
+        const uint32_t p_tmem = tmem + lane_addr + kTmemP + t * (kBlockN / 2);
         bool ok = true;
         int step = 0;  // key tiles processed so far by this query tile: phase of s_full / s_empty / p_full / o_done
         for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
@@ -650,41 +595,34 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             const int n_kv = w.n_kv;
             const int row = w.q_row0 + t * kBlockM + r;
             float m_ref = -INFINITY, l = 0.0f;  // reference max (log2 units, scale applied) and running sum
-#ifdef COME_ATTN_PROFILE
-            const long long prof_loop_t0 = clock64();
-#endif
 
             for (int j = 0; j < n_kv && ok; ++j) {
-                if ((warp & 3) == 0) PROF_TRACE(t, j, 0);
                 ok = mbar_wait(&sh.s_full[t], (step + j) & 1, sh, status, kErrSFull);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tc_fence_after();
-                if ((warp & 3) == 0) PROF_TRACE(t, j, 1);
-                // The whole 128-score row is pulled into registers at once, which frees S for the next Q K^T right away;
-                // the row is then turned into probabilities 32 columns at a time.
-                uint32_t srow[4][32];
-                tmem_ld32(s_tmem + 0, srow[0]);
-                tmem_ld32(s_tmem + 32, srow[1]);
-                tmem_ld32(s_tmem + 64, srow[2]);
-                tmem_ld32(s_tmem + 96, srow[3]);
+                // The whole row of kBlockN scores is pulled into registers at once, which frees S for the next Q K^T right
+                // away; the row is then turned into probabilities 32 columns at a time.
+                constexpr int kQuarters = kBlockN / 32;
+                uint32_t srow[kQuarters][32];
+#pragma unroll
+                for (int q = 0; q < kQuarters; ++q) tmem_ld32(s_tmem + 32 * q, srow[q]);
                 tc_wait_ld();
-                if ((warp & 3) == 0) PROF_TRACE(t, j, 4);
                 tc_fence_before();
                 mbar_arrive(&sh.s_empty[t]);
                 bool o_ready = (j == 0);  // P V of the previous key tile complete: O stable, P buffer free
-                // Row max over all 128 scores first: eight independent 3-input chains (16 scores each) keep the ALU pipe fed,
-                // and the rare rescale is decided once per key tile, so the exponentials below are one straight-line block.
-                float mx[8];
-    #pragma unroll
-                for (int c = 0; c < 8; ++c) {
+                // Row max over all scores first: independent 3-input chains of 16 scores keep the ALU pipe fed, and the
+                // rare rescale is decided once per key tile, so the exponentials below are one straight-line block.
+                float t_max = -INFINITY;
+#pragma unroll
+                for (int c = 0; c < 2 * kQuarters; ++c) {
                     const uint32_t *e = &srow[c >> 1][(c & 1) * 16];
                     float m = max3(__uint_as_float(e[0]), __uint_as_float(e[1]), __uint_as_float(e[2]));
-    #pragma unroll
+#pragma unroll
                     for (int i = 3; i < 15; i += 2) m = max3(m, __uint_as_float(e[i]), __uint_as_float(e[i + 1]));
-                    mx[c] = fmaxf(m, __uint_as_float(e[15]));
+                    t_max = max3(t_max, m, __uint_as_float(e[15]));
                 }
-                const float t_max = max3(max3(mx[0], mx[1], mx[2]), max3(mx[3], mx[4], mx[5]), fmaxf(mx[6], mx[7])) * scale_log2;
+                t_max *= scale_log2;
                 const bool need = t_max > m_ref + kRescaleThreshold;  // always true on the first key tile (m_ref = -inf)
                 if (__any_sync(0xffffffffu, need)) {
                     float alpha = 1.0f;
@@ -699,7 +637,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                         if (!ok) break;
                         tc_fence_after();
                         o_ready = true;
-                        rescale_staged<kBF16>(o_tmem, p_tmem, alpha, true, 0);
+                        scale_accumulator(o_tmem, alpha);
                     }
                 }
                 // p = 2^(s * scale*log2e - m_ref), two scores per instruction; a share of the pairs takes the polynomial
@@ -707,7 +645,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 const f32x2_t scale2 = pack_f32x2(scale_log2, scale_log2), neg_m2 = pack_f32x2(-m_ref, -m_ref);
                 f32x2_t sum2 = pack_f32x2(0.0f, 0.0f);
                 auto quarter = [&](const uint32_t(&a)[32], uint32_t(&pk)[16]) {
-    #pragma unroll
+#pragma unroll
                     for (int pair = 0; pair < 16; ++pair) {
                         const f32x2_t x2 = fma_f32x2(pack_f32x2(__uint_as_float(a[2 * pair]), __uint_as_float(a[2 * pair + 1])), scale2, neg_m2);
                         float x0, x1, p0, p1;
@@ -732,14 +670,12 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                         tc_fence_after();
                     }
                     tmem_st16(p_tmem, pk);  // 32 keys -> 16 columns of 16-bit pairs
-                    if ((warp & 3) == 0) PROF_TRACE(t, j, 5);
                 }
-    #pragma unroll
-                for (int q = 1; q < 4; ++q) {
+#pragma unroll
+                for (int q = 1; q < kQuarters; ++q) {
                     uint32_t pk[16];
                     quarter(srow[q], pk);
                     tmem_st16(p_tmem + 16 * q, pk);
-                    if ((warp & 3) == 0 && q < 3) PROF_TRACE(t, j, 5 + q);
                 }
                 {
                     float s_lo, s_hi;
@@ -747,17 +683,11 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     l += s_lo + s_hi;
                 }
                 if (!ok) break;
-                if ((warp & 3) == 0) PROF_TRACE(t, j, 2);
                 tc_wait_st();
                 tc_fence_before();
                 mbar_arrive(&sh.p_full[t]);
-                if ((warp & 3) == 0) PROF_TRACE(t, j, 3);
             }
 
-#ifdef COME_ATTN_PROFILE
-            prof_add(15, prof_loop_t0);
-#endif
-            if (warp == 0) PROF_TRACE(2, 0, 2);  // key loop done
             if (ok) {
                 ok = mbar_wait(&sh.o_done[t], (step + n_kv - 1) & 1, sh, status, kErrODone);
                 ok = __all_sync(0xffffffffu, ok);
@@ -790,15 +720,13 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     }
 
     // ===== common exit ==========================================================================================
-    if (warp == 0) PROF_TRACE(2, 0, 3);  // output stored
     tc_fence_before();
     __syncthreads();
-    if (warp == 0) PROF_TRACE(2, 1, 0);  // all roles done
     if (sh.abort_flag != 0) {
         // give loads that may still be in flight time to land before the shared memory is released
         for (int i = 0; i < 64; ++i) __nanosleep(1000);
     }
-    if (warp == 9) {
+    if (warp == kIssuerWarp0) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
     }
@@ -823,8 +751,8 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
-// [total, H, 64] view with arbitrary row stride; box = 128 rows x 1 head x 64 elements, 128-byte swizzle.
-int make_map(CUtensorMap *map, const void *base, int dtype, int64_t total, int H, int64_t row_stride) {
+// [total, H, 64] view with arbitrary row stride; box = box_rows rows x 1 head x 64 elements, 128-byte swizzle.
+int make_map(CUtensorMap *map, const void *base, int dtype, int64_t total, int H, int64_t row_stride, int box_rows) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) {
         set_error("cuTensorMapEncodeTiled is not available from the CUDA driver");
@@ -832,7 +760,7 @@ int make_map(CUtensorMap *map, const void *base, int dtype, int64_t total, int H
     }
     cuuint64_t dims[3] = {(cuuint64_t)kHeadDim, (cuuint64_t)H, (cuuint64_t)total};
     cuuint64_t strides[2] = {(cuuint64_t)kHeadDim * 2, (cuuint64_t)row_stride * 2};
-    cuuint32_t box[3] = {(cuuint32_t)kHeadDim, 1, (cuuint32_t)kBlockN};
+    cuuint32_t box[3] = {(cuuint32_t)kHeadDim, 1, (cuuint32_t)box_rows};
     cuuint32_t estr[3] = {1, 1, 1};
     CUresult r = fn(map, dtype == COME_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
                     const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -845,19 +773,6 @@ int make_map(CUtensorMap *map, const void *base, int dtype, int64_t total, int H
 }
 
 }  // namespace
-
-#ifdef COME_ATTN_PROFILE
-extern "C" int come_debug_attn_timers(unsigned long long *host32, int clear) {
-    cudaDeviceSynchronize();
-    cudaMemcpyFromSymbol(host32, g_attn_timers, sizeof(unsigned long long) * 32);
-    cudaMemcpyFromSymbol(host32 + 32, g_attn_trace, sizeof(g_attn_trace));
-    if (clear) {
-        unsigned long long z[32] = {0};
-        cudaMemcpyToSymbol(g_attn_timers, z, sizeof(z));
-    }
-    return 0;
-}
-#endif
 
 bool attn_sm100_supported(const AttnArgs &a) {
     if (a.D != kHeadDim) return false;
@@ -886,13 +801,13 @@ int attn_sm100_launch(const AttnArgs &a, cudaStream_t stream) {
     if (!status) return COME_ERR_CUDA;
     CUtensorMap mq, mk, mv;
     int rc;
-    if ((rc = make_map(&mq, a.q, a.dtype, a.q_end - a.q_begin, a.H, a.q_rs)) != COME_OK) return rc;
-    if ((rc = make_map(&mk, a.k, a.dtype, a.total, a.H, a.k_rs)) != COME_OK) return rc;
-    if ((rc = make_map(&mv, a.v, a.dtype, a.total, a.H, a.v_rs)) != COME_OK) return rc;
+    if ((rc = make_map(&mq, a.q, a.dtype, a.q_end - a.q_begin, a.H, a.q_rs, kBlockM)) != COME_OK) return rc;
+    if ((rc = make_map(&mk, a.k, a.dtype, a.total, a.H, a.k_rs, kBlockN)) != COME_OK) return rc;
+    if ((rc = make_map(&mv, a.v, a.dtype, a.total, a.H, a.v_rs, kBlockN)) != COME_OK) return rc;
     const size_t smem = sizeof(SharedStorage) + 1024;
     const int64_t q_rows = a.q_end - a.q_begin;
     const int64_t span = a.max_seqlen < q_rows ? a.max_seqlen : q_rows;  // most query rows any segment can own here
-    const int nblk_x = (int)((span + 2 * kBlockM - 1) / (2 * kBlockM));
+    const int nblk_x = (int)((span + kTiles * kBlockM - 1) / (kTiles * kBlockM));
     const int64_t items = (int64_t)nblk_x * a.nseg * a.H;
     if (items <= 0) return COME_OK;
     if (items >= (1ll << 31)) {
