@@ -1,23 +1,24 @@
 // Variable-length biased attention forward on Blackwell tensor cores (sm_100a): tcgen05.mma with TMEM
 // accumulators, TMA-fed 128-byte-swizzled Q/K/V tiles, warp-specialised roles.
 //
-// One CTA owns up to two 128-row query tiles of one (segment, head) and walks the segment's keys 128 at a time.
-//   warps 0-3 / 4-7 : softmax group of query tile 0 / 1.  Thread r owns score row r (TMEM lane r).  Per key tile it
-//                     pulls the 128 scores into registers (S is free for the next Q K^T at once), then works 32
-//                     columns at a time: row max with 3-input max, packed float32x2 arithmetic, a third of the
-//                     exponentials on the FMA pipe (cubic polynomial) instead of the special-function unit,
-//                     p = exp2(s * scale*log2e - m) with one FFMA + one MUFU per score, writes p back to TMEM as
-//                     16-bit pairs (the A operand of P V) and rescales the accumulator only when the running max
-//                     grew by more than 2^8 (exact: the final normalisation uses the same reference max).
-//   warp 8          : producer.  Issues the TMA loads of Q, K and V and stages, per key tile, a "bias slab": a
-//                     128-byte-swizzled tile whose first two columns hold bias/scale split into a high and a low
-//                     16-bit part (a large negative number past the segment end, which masks the ragged tail).
-//   warps 9, 10     : MMA issuer of query tile 0 / 1 (one elected lane issues).  S = Q K^T takes four K=16 steps
+// Persistent kernel: one CTA per SM walks the work items; a work item is the (up to) three 128-row query tiles of one
+// (segment, head), whose keys are walked 64 at a time.  Barrier phases keep counting across items.
+//   warps 0-3 / 4-7 / 8-11 : softmax group of query tile 0 / 1 / 2.  Thread r owns score row r (TMEM lane r).  Per key
+//                     tile it pulls the 64 scores into registers (S is free for the next Q K^T at once), takes the row
+//                     max with 3-input max, then p = exp2(s * scale*log2e - m) in packed float32x2 arithmetic, 5 of 16
+//                     exponentials on the FMA pipe (cubic polynomial) instead of the special-function unit, writes p
+//                     back to TMEM as 16-bit pairs (the A operand of P V) and rescales the accumulator only when the
+//                     running max grew by more than 2^8 (exact: the final normalisation uses the same reference max).
+//   warp 12         : producer.  Issues the TMA loads of Q (double-buffered across items), K and V and stages, per key
+//                     tile, a "bias slab": a 128-byte-swizzled tile whose first two columns hold bias/scale split into
+//                     a high and a low 16-bit part (a large negative number past the segment end, which masks the
+//                     ragged tail).
+//   warps 13, 14, 15 : MMA issuer of query tile 0 / 1 / 2 (one elected lane issues).  S = Q K^T takes four K=16 steps
 //                     over the head dimension plus one K=16 step [1 1 0 ...] x [bias_hi bias_lo 0 ...]^T that adds
 //                     the per-key bias inside the tensor core; O += P V reads P from TMEM and V (N-major) from
 //                     shared memory.  S(j+1) is issued as soon as the softmax group holds S(j) in registers, P V as
-//                     soon as P(j) is staged, so a softmax group never waits for its own tile's scores.
-// TMEM columns: S0 [0,128) S1 [128,256) O0 [256,320) O1 [320,384) P0 [384,448) P1 [448,512).
+//                     soon as P(j) is staged.
+// TMEM columns: S_t [64 t, 64 t + 64), O_t [192 + 64 t, ...), P_t [384 + 32 t, ...), t = 0, 1, 2.
 //
 // Every wait on an mbarrier is bounded: after ~2^29 clock ticks the waiter raises the CTA's abort flag and the
 // library's device status word, every role falls through to the common exit, TMEM is released and the kernel
@@ -53,7 +54,8 @@ constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 // Which of the 16 score pairs of a 32-column quarter take the polynomial exp2 (bit i = pair i); the rest use the
-// special-function unit.  5 of 16 balanced the two pipes best in measurements.
+// special-function unit.  5 of 16 balanced the two pipes best in measurements of the two-tile predecessor; with three
+// tiles in flight shares from 0 to 6 of 16 measure within 2 % of each other.
 #ifndef COME_POLY_MASK
 #define COME_POLY_MASK 0x4924u
 #endif

@@ -555,6 +555,129 @@ static int launch_unmerge(const void *merged, const int64_t *rev, int64_t total,
     return check_launch("come_unmerge");
 }
 
+// ---- unmerge fused with the block's residual update -----------------------------------------------------------------
+// out[i, :] = residual[i, :] + scale[:] * merged[rev[i], :], evaluated like the tensor expression in the element type:
+// the product is rounded to T (skipped without a scale), then the sum is rounded to T.
+template <typename T, int VEC>
+__device__ __forceinline__ typename VecIO<T, VEC>::V residual_update(const typename VecIO<T, VEC>::V &u,
+                                                                      const typename VecIO<T, VEC>::V &r, const float (&g)[VEC],
+                                                                      bool has_scale) {
+    using IO = VecIO<T, VEC>;
+    float fu[VEC], fr[VEC];
+    IO::unpack(u, fu);
+    IO::unpack(r, fr);
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+        float t = fu[i];
+        if (has_scale) t = Elem<T>::to_f32(Elem<T>::from_f32(__fmul_rn(t, g[i])));
+        fr[i] = __fadd_rn(fr[i], t);
+    }
+    return IO::pack(fr);
+}
+
+// Rows of at most 256 vectors whose count divides 256: a thread keeps its column (and its slice of the scale) for all the
+// rows it visits; kRowBatch row gathers and residual loads in flight per thread.
+template <typename T, int VEC>
+__global__ void __launch_bounds__(kUnmergeThreads)
+unmerge_residual_rows_kernel(const T *__restrict__ merged, const int64_t *__restrict__ rev, int total, int Cv,
+                             const T *__restrict__ residual, const T *__restrict__ scale, T *__restrict__ out) {
+    using IO = VecIO<T, VEC>;
+    using V = typename IO::V;
+    const V *m = reinterpret_cast<const V *>(merged);
+    const V *res = reinterpret_cast<const V *>(residual);
+    V *o = reinterpret_cast<V *>(out);
+    const int rows_per_group = kUnmergeThreads / Cv;
+    const int sub = threadIdx.x / Cv, v = threadIdx.x - sub * Cv;
+    const int rows_per_round = rows_per_group * kRowBatch;
+    float g[VEC];
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) g[i] = 1.0f;
+    if (scale) IO::unpack(reinterpret_cast<const V *>(scale)[v], g);
+    for (int row0 = blockIdx.x * rows_per_round; row0 < total; row0 += gridDim.x * rows_per_round) {
+        int64_t src[kRowBatch];
+        V r[kRowBatch], u[kRowBatch];
+#pragma unroll
+        for (int k = 0; k < kRowBatch; ++k) {
+            const int row = row0 + k * rows_per_group + sub;
+            if (row < total) {
+                src[k] = __ldg(rev + row);
+                r[k] = ld_stream(res + (int64_t)row * Cv + v);
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < kRowBatch; ++k)
+            if (row0 + k * rows_per_group + sub < total) u[k] = m[src[k] * Cv + v];
+#pragma unroll
+        for (int k = 0; k < kRowBatch; ++k) {
+            const int row = row0 + k * rows_per_group + sub;
+            if (row < total) st_stream(o + (int64_t)row * Cv + v, residual_update<T, VEC>(u[k], r[k], g, scale != nullptr));
+        }
+    }
+}
+
+// Any row width (and the scalar path for unaligned pointers): flat loop over the vectors of the output.
+template <typename T, int VEC>
+__global__ void __launch_bounds__(kUnmergeThreads)
+unmerge_residual_kernel(const T *__restrict__ merged, const int64_t *__restrict__ rev, int64_t total, int64_t Cv,
+                        const T *__restrict__ residual, const T *__restrict__ scale, T *__restrict__ out) {
+    using IO = VecIO<T, VEC>;
+    using V = typename IO::V;
+    const V *m = reinterpret_cast<const V *>(merged);
+    const V *res = reinterpret_cast<const V *>(residual);
+    V *o = reinterpret_cast<V *>(out);
+    const int64_t n = total * Cv;
+    for (int64_t i = (int64_t)blockIdx.x * kUnmergeThreads + threadIdx.x; i < n; i += (int64_t)gridDim.x * kUnmergeThreads) {
+        const int64_t row = i / Cv, v = i - row * Cv;
+        float g[VEC];
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) g[k] = 1.0f;
+        if (scale) IO::unpack(reinterpret_cast<const V *>(scale)[v], g);
+        st_stream(o + i, residual_update<T, VEC>(m[__ldg(rev + row) * Cv + v], ld_stream(res + i), g, scale != nullptr));
+    }
+}
+
+template <typename T>
+static int launch_unmerge_residual(const void *merged, const int64_t *rev, int64_t total, int64_t C, const void *residual,
+                                   const void *scale, void *out, cudaStream_t st) {
+    constexpr int VEC = 16 / sizeof(T);
+    const auto al = [](const void *p) { return (uintptr_t)p % 16 == 0; };
+    const bool vec_ok = C % VEC == 0 && al(merged) && al(residual) && al(out) && (!scale || al(scale));
+    const int64_t Cv = vec_ok ? C / VEC : C;
+    const int64_t max_blocks = (int64_t)sm_count() * 8;
+    if (vec_ok && Cv <= kUnmergeThreads && kUnmergeThreads % Cv == 0 && total < (1ll << 31)) {
+        const int rows_per_round = (kUnmergeThreads / (int)Cv) * kRowBatch;
+        int64_t blocks = (total + rows_per_round - 1) / rows_per_round;
+        if (blocks > max_blocks) blocks = max_blocks;
+        unmerge_residual_rows_kernel<T, VEC><<<(unsigned)blocks, kUnmergeThreads, 0, st>>>(
+            (const T *)merged, rev, (int)total, (int)Cv, (const T *)residual, (const T *)scale, (T *)out);
+        return check_launch("come_unmerge_residual");
+    }
+    int64_t blocks = (total * Cv + kUnmergeThreads - 1) / kUnmergeThreads;
+    if (blocks > max_blocks) blocks = max_blocks;
+    if (vec_ok)
+        unmerge_residual_kernel<T, VEC><<<(unsigned)blocks, kUnmergeThreads, 0, st>>>(
+            (const T *)merged, rev, total, Cv, (const T *)residual, (const T *)scale, (T *)out);
+    else
+        unmerge_residual_kernel<T, 1><<<(unsigned)blocks, kUnmergeThreads, 0, st>>>(
+            (const T *)merged, rev, total, Cv, (const T *)residual, (const T *)scale, (T *)out);
+    return check_launch("come_unmerge_residual");
+}
+
+extern "C" int come_unmerge_residual(const void *merged_dev, const int64_t *rev_id_dev, int64_t total, int64_t channels,
+                                     int dtype, const void *residual_dev, const void *scale_dev, void *out_dev,
+                                     void *stream) {
+    COME_REQUIRE(total >= 0 && channels >= 0, "total and channels must be >= 0");
+    COME_REQUIRE(dtype == COME_F32 || dtype == COME_F16 || dtype == COME_BF16, "unknown dtype %d", dtype);
+    if (total == 0 || channels == 0) return COME_OK;
+    COME_REQUIRE(merged_dev && rev_id_dev && residual_dev && out_dev, "merged / rev_id / residual / out must not be NULL");
+    cudaStream_t st = (cudaStream_t)stream;
+    switch (dtype) {
+        case COME_F32: return launch_unmerge_residual<float>(merged_dev, rev_id_dev, total, channels, residual_dev, scale_dev, out_dev, st);
+        case COME_F16: return launch_unmerge_residual<__half>(merged_dev, rev_id_dev, total, channels, residual_dev, scale_dev, out_dev, st);
+        default: return launch_unmerge_residual<__nv_bfloat16>(merged_dev, rev_id_dev, total, channels, residual_dev, scale_dev, out_dev, st);
+    }
+}
+
 extern "C" int come_unmerge_strided(const void *merged_dev, const int64_t *rev_id_dev, int64_t total, int64_t channels,
                                     int dtype, void *out_dev, int64_t out_row_stride, void *stream) {
     COME_REQUIRE(total >= 0 && channels >= 0, "total and channels must be >= 0");

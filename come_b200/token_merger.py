@@ -209,6 +209,34 @@ class MergePlan:
         """packed ``[P, C]`` -> ``[frames * N, C]``."""
         return co_me_cuext.co_me_token_split_cuda(merged, self.rev_id, merged.shape[-1])
 
+    def split_add(self, merged: torch.Tensor, residual: torch.Tensor, scale: Optional[torch.Tensor] = None,
+                  out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``residual + scale * split(merged)`` in one pass (``come_unmerge_residual``): the unmerge, the LayerScale
+        and the residual add that close an attention block (``x = x + ls1(attn(norm1(x)))``,
+        ``src/thirdparty/vggt/layers/block.py:73,90``).  ``residual`` is ``[frames * N, C]`` (any leading shape with that
+        many rows), ``scale`` ``[C]`` or None; ``out`` may be ``residual`` itself."""
+        require_cuda(merged, "merged")
+        require_cuda(residual, "residual")
+        rows = self.frames * self.tokens_per_frame
+        Cc = merged.shape[-1]
+        if merged.dim() != 2 or merged.shape[0] != self.total:
+            raise ValueError(f"Expected merged [{self.total}, C], got {tuple(merged.shape)}")
+        if residual.numel() != rows * Cc or residual.dtype != merged.dtype:
+            raise ValueError(f"Expected residual with {rows} x {Cc} elements of {merged.dtype}, got {tuple(residual.shape)} {residual.dtype}")
+        if scale is not None and (scale.shape != (Cc,) or scale.dtype != merged.dtype):
+            raise ValueError(f"Expected scale [{Cc}] of {merged.dtype}")
+        merged, residual = merged.contiguous(), residual.contiguous()
+        if out is None:
+            out = torch.empty_like(residual)
+        elif out.shape != residual.shape or out.dtype != residual.dtype or not out.is_contiguous():
+            raise ValueError("out must be contiguous and match residual")
+        with torch.cuda.device(merged.device):
+            _lib.check(_lib.lib().come_unmerge_residual(ptr(merged), ptr(self.rev_id), rows, Cc,
+                                                        dtype_code(merged.dtype, "merged"), ptr(residual),
+                                                        ptr(None if scale is None else scale.contiguous()), ptr(out),
+                                                        stream_ptr(merged.device)))
+        return out
+
     def split_concat(self, *merged: torch.Tensor) -> torch.Tensor:
         """Unmerge several packed ``[P, C_k]`` tensors side by side into one ``[frames * N, sum(C_k)]`` tensor:
         the ``torch.cat((split(frame_tokens), split(global_tokens)), dim=-1)`` of a retained layer

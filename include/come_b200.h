@@ -160,6 +160,18 @@ int come_unmerge_strided(const void *merged_dev, const int64_t *rev_id_dev, int6
                          void *out_dev, int64_t out_row_stride, void *stream);
 
 /*
+ * Unmerge fused with the residual update of a transformer block:
+ *   out[i, c] = residual[i, c] + scale[c] * merged[rev_id[i], c]
+ * evaluated in the element type like the tensor expression (product rounded, then sum rounded; scale_dev may be NULL
+ * = no product).  Replaces split() followed by LayerScale and the residual add of the block the attention sits in
+ * (src/accelerate/vggt/direct.py:117-118 -> src/thirdparty/vggt/layers/block.py:73,90 `x + ls1(attn(norm1(x)))`,
+ * LayerScale = x * gamma, src/thirdparty/vggt/layers/layer_scale.py:21-22): one pass instead of three over the dense
+ * tokens.  out_dev may alias residual_dev (every element is read before it is written by the same thread).
+ */
+int come_unmerge_residual(const void *merged_dev, const int64_t *rev_id_dev, int64_t total, int64_t channels, int dtype,
+                          const void *residual_dev, const void *scale_dev, void *out_dev, void *stream);
+
+/*
  * Variable-length attention forward with an optional additive per-key bias:
  *   out[s:e, h] = softmax(q[s:e, h] k[s:e, h]^T * softmax_scale + bias[s:e][None, :]) v[s:e, h]
  * for every packed segment [cu_seqlens[i], cu_seqlens[i+1]) and head h; non-causal, no dropout.

@@ -17,6 +17,7 @@ __all__ = [
     "merge_plan",
     "token_merge",
     "token_split",
+    "token_split_residual",
     "block_perm_2d",
     "token_merge_2d",
     "ragged_layout_2d",
@@ -129,6 +130,16 @@ def token_split(merged: np.ndarray, rev_id: np.ndarray) -> np.ndarray:
 # --------------------------------------------------------------------------------------------------------
 # 2-D merge
 # --------------------------------------------------------------------------------------------------------
+def token_split_residual(merged: np.ndarray, rev_id: np.ndarray, residual: np.ndarray, scale=None, kind: str = "f32"):
+    """``x + ls1(split(attn_out))``: the unmerge followed by LayerScale (``x * gamma``,
+    ``src/thirdparty/vggt/layers/layer_scale.py:21-22``) and the residual add of the block
+    (``src/thirdparty/vggt/layers/block.py:73,90``), each tensor operation rounded to the element type ``kind``."""
+    u = np.asarray(merged, np.float32)[np.asarray(rev_id, np.int64)]
+    if scale is not None:
+        u = _round_like((u * np.asarray(scale, np.float32)[None, :]).astype(np.float32), kind)
+    return _round_like((np.asarray(residual, np.float32).reshape(u.shape) + u).astype(np.float32), kind)
+
+
 def block_perm_2d(H: int, W: int, gh: int, gw: int) -> np.ndarray:
     """Row-major patch index of every (window, in-window) slot, windows in raster order.
 

@@ -240,3 +240,44 @@ def test_query_row_slices_match_full_attention(backend, which, seq_lens, cuts):
         torch.testing.assert_close(out, full[a:b], atol=0, rtol=0)
         torch.testing.assert_close(lse, full_lse[:, a:b], atol=0, rtol=0)
     _check_status()
+
+
+def test_tile_boundary_lengths(backend):
+    """Segment lengths on and around the kernel's tile sizes (64 keys per step, 128-row query tiles, 384-row work items):
+    every combination of one, two or three active query tiles and of a full or ragged last key tile, and more work items
+    than SMs so that CTAs of the persistent kernel carry their barrier phases across several items."""
+    from come_b200 import flash_attn as api, flash_attn_fwd_cuda as fa
+    backend(fa.BACKEND_TCGEN05)
+    rng = np.random.default_rng(12)
+    lengths = [1, 63, 64, 65, 127, 128, 129, 383, 384, 385, 512, 513, 769, 2, 640, 256]
+    H, D, P = 12, 64, sum([1, 63, 64, 65, 127, 128, 129, 383, 384, 385, 512, 513, 769, 2, 640, 256])
+    qkv = gi.round_kind(rng.standard_normal((P, 3, H, D), dtype=np.float32), "bf16")
+    weight = np.where(rng.random(P) < 0.3, np.float32(9), np.float32(1))
+    bias = gi.round_kind(np.log(weight), "bf16")
+    cu = np.zeros(len(lengths) + 1, np.int32)
+    cu[1:] = np.cumsum(lengths)
+    out = api.flash_attn_varlen_qkvpacked_func_w_perkey_bias(to_dev(qkv, "bf16"), torch.from_numpy(cu).cuda(), max(lengths),
+                                                             perkey_bias=to_dev(bias, "bf16"), softmax_scale=D ** -0.5)
+    want, _ = clib.attention_bias(qkv, bias, cu, D ** -0.5)
+    assert np.abs(to_np(out) - want).max() <= 2e-2
+    _check_status()
+
+
+def test_device_side_longest_segment(backend):
+    """A loose host-side max_seqlen plus the true longest segment in device memory (what a captured graph passes) gives
+    the same result, bit for bit, as the exact host-side bound; a device value larger than the host bound is clamped."""
+    from come_b200 import flash_attn_fwd_cuda as fa
+    backend(fa.BACKEND_TCGEN05)
+    rng = np.random.default_rng(13)
+    lengths = [700, 420, 901, 130]
+    H, D, P = 4, 64, 2151
+    qkv = to_dev(gi.round_kind(rng.standard_normal((P, 3, H, D), dtype=np.float32), "bf16"), "bf16")
+    bias = to_dev(np.zeros(P, np.float32), "bf16")
+    cu = torch.tensor(np.concatenate([[0], np.cumsum(lengths)]), dtype=torch.int32, device="cuda")
+    q, k, v = qkv[:, 0], qkv[:, 1], qkv[:, 2]
+    exact, lse0 = fa.varlen_fwd_rows(q, k, v, cu, max(lengths), bias, D ** -0.5, 0)
+    for dev_value in (max(lengths), 10 ** 6):
+        md = torch.tensor([dev_value], dtype=torch.int32, device="cuda")
+        loose, lse1 = fa.varlen_fwd_rows(q, k, v, cu, P, bias, D ** -0.5, 0, max_seqlen_dev=md)
+        assert torch.equal(exact, loose) and torch.equal(lse0, lse1)
+    _check_status()

@@ -302,3 +302,30 @@ def test_split_concat(kind, widths):
     got = to_np(plan.split_concat(*[to_dev(p, kind) for p in parts]))
     want = np.concatenate([orc.token_split(p, rev) for p in parts], axis=1)
     np.testing.assert_array_equal(got, want)
+
+
+@pytest.mark.parametrize("kind,C,with_scale", [("bf16", 1024, True), ("f32", 1024, True), ("f16", 1024, False),
+                                                ("bf16", 24, True), ("f32", 7, True), ("bf16", 2048 + 8, True)])
+def test_split_add_residual(kind, C, with_scale):
+    """Unmerge fused with LayerScale and the residual add, bit for bit against the oracle's three separate tensor
+    operations in the element type; also in place (out = residual)."""
+    import torch
+    from come_b200 import _lib
+    from come_b200.token_merger import MergePlan
+    from gpu_util import to_dev, to_np
+    import golden_inputs as gi
+    from oracle import come_oracle as orc
+    rng = np.random.default_rng(C)
+    mask = rng.random((3, 144)) < 0.5
+    plan = MergePlan(torch.from_numpy(mask).cuda(), _lib.Layout.two_d(5, 37, 37, 3, 3))
+    _o, _off, rev, _w = orc.token_merge_2d_ragged(np.zeros((3, 1374, 1), np.float32), 5, 3, 3, 37, 37, mask)
+    merged = gi.round_kind(rng.standard_normal((plan.total, C), dtype=np.float32), kind)
+    x = gi.round_kind(rng.standard_normal((3 * 1374, C), dtype=np.float32), kind)
+    gamma = gi.round_kind(0.01 + 0.5 * rng.random(C, dtype=np.float32), kind) if with_scale else None
+    want = orc.token_split_residual(merged, rev, x, gamma, kind)
+    xd = to_dev(x, kind)
+    got = plan.split_add(to_dev(merged, kind), xd.reshape(3, 1374, C), None if gamma is None else to_dev(gamma, kind))
+    assert got.shape == (3, 1374, C)
+    np.testing.assert_array_equal(to_np(got).reshape(-1, C), want)
+    plan.split_add(to_dev(merged, kind), xd, None if gamma is None else to_dev(gamma, kind), out=xd)  # in place
+    np.testing.assert_array_equal(to_np(xd), want)
