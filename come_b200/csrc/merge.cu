@@ -332,6 +332,216 @@ merge_kernel(const T *__restrict__ tokens, const uint8_t *__restrict__ mask, con
     }
 }
 
+// ---- merge fused with the LayerNorm in front of it ---------------------------------------------------------------
+// out = merge(LayerNorm(tokens)): every source row is normalised over its C channels (float32 statistics and affine map,
+// result rounded to T like the module's output tensor), then merged windows average their G normalised rows.  One
+// thread group of `tpg` threads (a power of two >= the vectors per row) owns a unit; a thread holds its 16-byte vector
+// of every row of the unit in registers, so the tokens are read once.
+//
+// Summation order of a row's statistics (fixed, so that the CPU oracle can follow it bit for bit): inside a thread left to
+// right over its VEC channels, then a butterfly over the 32 lanes (neighbours first), then left to right over the warps of
+// the group.  The squares are accumulated with fused multiply-adds.
+constexpr int kLnMaxRows = 9;  // rows per unit the fused kernel keeps in registers (3 x 3 windows)
+
+__device__ __forceinline__ void group_barrier(int groups, int grp, int tpg) {
+    if (groups == 1) __syncthreads();
+    else asm volatile("bar.sync %0, %1;" ::"r"(grp + 1), "r"(tpg) : "memory");
+}
+
+template <typename T, int VEC>
+__global__ void __launch_bounds__(kMergeThreads, 2)
+merge_layernorm_kernel(const T *__restrict__ tokens, const uint8_t *__restrict__ mask, const int *__restrict__ group_prefix,
+                       const int *__restrict__ offsets, FrameLayout L, int frames, int Cv, int groups,
+                       const T *__restrict__ gamma, const T *__restrict__ beta, float eps, T *__restrict__ out) {
+    using IO = VecIO<T, VEC>;
+    using V = typename IO::V;
+    extern __shared__ int s_ln_raw[];
+    const int G = L.G;
+    const int tpg = kMergeThreads / groups, warps_pg = tpg / 32;
+    const int grp = threadIdx.x / tpg, tig = threadIdx.x - grp * tpg;
+    const int wig = tig >> 5, lane = tig & 31;
+    int *s_src = s_ln_raw + grp * G;                                              // [groups][G]
+    float *s_red = reinterpret_cast<float *>(s_ln_raw + groups * G) + grp * (kLnMaxRows * 8);  // [groups][rows][warps <= 8]
+    const int prefix_units = (L.prefix + G - 1) / G;
+    const int units_per_frame = prefix_units + L.M;
+    const int n_units = frames * units_per_frame;
+    const bool has_col = tig < Cv;  // a group may be wider than a row (rows of 96, 192, ... vectors)
+    const float fC = (float)(Cv * VEC), fG = (float)G;
+    float g[VEC], b[VEC];
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) g[i] = b[i] = 0.0f;
+    if (has_col) {
+        IO::unpack(reinterpret_cast<const V *>(gamma)[tig], g);
+        IO::unpack(reinterpret_cast<const V *>(beta)[tig], b);
+    }
+
+    // Sum of one value per thread over the group's row, for all rows of the unit at once: butterfly inside the warp,
+    // warp totals through shared memory, every thread then adds the warp totals left to right.
+    auto row_totals = [&](float (&part)[kLnMaxRows], int rows) {
+#pragma unroll
+        for (int r = 0; r < kLnMaxRows; ++r) {
+#pragma unroll
+            for (int m = 1; m < 32; m <<= 1) part[r] = __fadd_rn(part[r], __shfl_xor_sync(0xffffffffu, part[r], m));
+        }
+        group_barrier(groups, grp, tpg);  // the previous use of s_red is over
+        if (lane == 0) {
+#pragma unroll
+            for (int r = 0; r < kLnMaxRows; ++r)
+                if (r < rows) s_red[r * 8 + wig] = part[r];
+        }
+        group_barrier(groups, grp, tpg);
+#pragma unroll
+        for (int r = 0; r < kLnMaxRows; ++r) {
+            if (r < rows) {
+                float t = s_red[r * 8];
+                for (int w = 1; w < warps_pg; ++w) t = __fadd_rn(t, s_red[r * 8 + w]);
+                part[r] = t;
+            }
+        }
+    };
+
+    for (int u0 = blockIdx.x * groups; u0 < n_units; u0 += gridDim.x * groups) {
+        const int u = u0 + grp;
+        const bool active = u < n_units;  // the last round may leave some groups without a unit (they still meet the barriers)
+        const int bfr = active ? u / units_per_frame : 0;
+        const int unit = active ? u - bfr * units_per_frame : 0;
+        const int base = offsets[bfr];
+        int r0 = 0, rows = 0, dst = 0;
+        bool merged = false;
+        if (active) {
+            if (unit < prefix_units) {
+                r0 = unit * G;
+                rows = min(G, L.prefix - r0);
+                dst = base + r0;
+            } else {
+                const int m = unit - prefix_units;
+                r0 = L.prefix + m * G;
+                rows = G;
+                dst = base + L.prefix + group_prefix[(size_t)bfr * L.M + m];
+                merged = mask[(size_t)bfr * L.M + m] != 0;
+            }
+        }
+        group_barrier(groups, grp, tpg);  // previous unit's s_src no longer read
+        for (int r = tig; r < rows; r += tpg) s_src[r] = L.src_token(r0 + r);
+        group_barrier(groups, grp, tpg);
+        const V *src_base = reinterpret_cast<const V *>(tokens) + (int64_t)bfr * L.N * Cv;
+
+        V x[kLnMaxRows];
+#pragma unroll
+        for (int r = 0; r < kLnMaxRows; ++r)
+            if (r < rows && has_col) x[r] = ld_stream(src_base + (int64_t)s_src[r] * Cv + tig);
+        float part[kLnMaxRows], mean[kLnMaxRows];
+#pragma unroll
+        for (int r = 0; r < kLnMaxRows; ++r) {
+            part[r] = 0.0f;
+            if (r < rows && has_col) {
+                float f[VEC];
+                IO::unpack(x[r], f);
+                float t = f[0];
+#pragma unroll
+                for (int i = 1; i < VEC; ++i) t = __fadd_rn(t, f[i]);
+                part[r] = t;
+            }
+        }
+        row_totals(part, rows);
+#pragma unroll
+        for (int r = 0; r < kLnMaxRows; ++r) {
+            mean[r] = (r < rows) ? __fdiv_rn(part[r], fC) : 0.0f;
+            part[r] = 0.0f;
+            if (r < rows && has_col) {
+                float f[VEC];
+                IO::unpack(x[r], f);
+                float d0 = __fsub_rn(f[0], mean[r]);
+                float t = __fmul_rn(d0, d0);
+#pragma unroll
+                for (int i = 1; i < VEC; ++i) {
+                    const float d = __fsub_rn(f[i], mean[r]);
+                    t = __fmaf_rn(d, d, t);
+                }
+                part[r] = t;
+            }
+        }
+        row_totals(part, rows);
+        if (has_col) {
+            float acc[VEC];
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) acc[i] = 0.0f;
+            V *dst_base = reinterpret_cast<V *>(out) + (int64_t)dst * Cv + tig;
+#pragma unroll
+            for (int r = 0; r < kLnMaxRows; ++r) {
+                if (r < rows) {
+                    const float rstd = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(part[r], fC), eps)));
+                    float f[VEC];
+                    IO::unpack(x[r], f);
+#pragma unroll
+                    for (int i = 0; i < VEC; ++i) {
+                        const float y = __fmaf_rn(g[i], __fmul_rn(rstd, __fsub_rn(f[i], mean[r])), b[i]);
+                        f[i] = Elem<T>::to_f32(Elem<T>::from_f32(y));  // the normalised tensor lives in T
+                    }
+                    if (merged) {
+#pragma unroll
+                        for (int i = 0; i < VEC; ++i) acc[i] = __fadd_rn(acc[i], f[i]);
+                    } else {
+                        st_stream(dst_base + (int64_t)r * Cv, IO::pack(f));
+                    }
+                }
+            }
+            if (merged) {
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) acc[i] = __fdiv_rn(acc[i], fG);
+                st_stream(dst_base, IO::pack(acc));
+            }
+        }
+    }
+}
+
+template <typename T>
+static int launch_merge_layernorm(const void *tokens, int64_t frames, int64_t C, const FrameLayout &L, const uint8_t *mask,
+                                  const int32_t *gp, const int32_t *off, const void *gamma, const void *beta, float eps,
+                                  void *out, cudaStream_t st) {
+    constexpr int VEC = 16 / sizeof(T);
+    const auto al = [](const void *p) { return (uintptr_t)p % 16 == 0; };
+    if (C % VEC != 0 || C / VEC > kMergeThreads || !al(tokens) || !al(out) || !al(gamma) || !al(beta) || L.G > kLnMaxRows) {
+        set_error("come_merge_layernorm needs 16-byte aligned tensors, channels a multiple of %d and at most %d, group size <= %d "
+                  "(got channels %lld, group size %d)", VEC, VEC * kMergeThreads, kLnMaxRows, (long long)C, L.G);
+        return COME_ERR_UNSUPPORTED;
+    }
+    const int Cv = (int)(C / VEC);
+    int tpg = 32;
+    while (tpg < Cv) tpg <<= 1;
+    const int groups = kMergeThreads / tpg;
+    const int prefix_units = (L.prefix + L.G - 1) / L.G;
+    const int64_t n_units = frames * (int64_t)(prefix_units + L.M);
+    if (n_units == 0) return COME_OK;
+    const size_t smem = (size_t)groups * L.G * sizeof(int) + (size_t)groups * kLnMaxRows * 8 * sizeof(float);
+    const int64_t n_ctas = (n_units + groups - 1) / groups;
+    const int64_t max_blocks = (int64_t)sm_count() * 8;
+    merge_layernorm_kernel<T, VEC><<<(unsigned)(n_ctas < max_blocks ? n_ctas : max_blocks), kMergeThreads, smem, st>>>(
+        (const T *)tokens, mask, gp, off, L, (int)frames, Cv, groups, (const T *)gamma, (const T *)beta, eps, (T *)out);
+    return check_launch("come_merge_layernorm");
+}
+
+extern "C" int come_merge_layernorm(const void *tokens_dev, int dtype, int64_t frames, int64_t channels,
+                                    const come_layout_t *layout, const void *gamma_dev, const void *beta_dev, float eps,
+                                    const uint8_t *mask_dev, const int32_t *group_prefix_dev, const int32_t *offsets_dev,
+                                    void *out_dev, void *stream) {
+    FrameLayout L;
+    int rc = make_layout(layout, &L);
+    if (rc != COME_OK) return rc;
+    COME_REQUIRE(frames >= 0 && channels >= 0, "frames and channels must be >= 0");
+    COME_REQUIRE(dtype == COME_F32 || dtype == COME_F16 || dtype == COME_BF16, "unknown dtype %d", dtype);
+    COME_REQUIRE(frames * (int64_t)L.N < (1ll << 31), "frames * tokens_per_frame must fit int32 row indices");
+    if (frames == 0 || channels == 0) return COME_OK;
+    COME_REQUIRE(tokens_dev && out_dev && offsets_dev && gamma_dev && beta_dev, "tokens / out / offsets / gamma / beta must not be NULL");
+    COME_REQUIRE(L.M == 0 || (mask_dev && group_prefix_dev), "mask / group_prefix must not be NULL");
+    cudaStream_t st = (cudaStream_t)stream;
+    switch (dtype) {
+        case COME_F32: return launch_merge_layernorm<float>(tokens_dev, frames, channels, L, mask_dev, group_prefix_dev, offsets_dev, gamma_dev, beta_dev, eps, out_dev, st);
+        case COME_F16: return launch_merge_layernorm<__half>(tokens_dev, frames, channels, L, mask_dev, group_prefix_dev, offsets_dev, gamma_dev, beta_dev, eps, out_dev, st);
+        default: return launch_merge_layernorm<__nv_bfloat16>(tokens_dev, frames, channels, L, mask_dev, group_prefix_dev, offsets_dev, gamma_dev, beta_dev, eps, out_dev, st);
+    }
+}
+
 // ---- unmerge ------------------------------------------------------------------------------------------------------
 constexpr int kUnmergeThreads = 256;
 constexpr int kUnmergeBatch = 4;

@@ -205,6 +205,28 @@ class MergePlan:
                                              stream_ptr(tokens.device)))
         return out
 
+    def merge_layernorm(self, tokens: torch.Tensor, norm: torch.nn.LayerNorm) -> torch.Tensor:
+        """``merge(norm(tokens))`` in one pass over the dense tokens (``come_merge_layernorm``): the block's ``norm1``
+        followed by the merge of the per-layer mode (``src/thirdparty/vggt/layers/block.py:73``,
+        ``src/accelerate/vggt/direct.py:97-101``).  ``tokens [frames, N, C]`` -> packed ``[P, C]``."""
+        require_cuda(tokens, "tokens")
+        if tokens.dim() != 3 or tokens.shape[0] != self.frames or tokens.shape[1] != self.tokens_per_frame:
+            raise ValueError(f"Expected tokens [{self.frames}, {self.tokens_per_frame}, C], got {tuple(tokens.shape)}")
+        Cc = tokens.shape[2]
+        if not isinstance(norm, torch.nn.LayerNorm) or tuple(norm.normalized_shape) != (Cc,):
+            raise NotImplementedError("merge_layernorm needs an nn.LayerNorm over the channel dimension")
+        tokens = tokens.contiguous()
+        dev, dt = tokens.device, tokens.dtype
+        w = (norm.weight if norm.weight is not None else torch.ones(Cc, device=dev)).detach().to(device=dev, dtype=dt).contiguous()
+        b = (norm.bias if norm.bias is not None else torch.zeros(Cc, device=dev)).detach().to(device=dev, dtype=dt).contiguous()
+        out = torch.empty((self.total, Cc), dtype=dt, device=dev)
+        with torch.cuda.device(dev):
+            _lib.check(_lib.lib().come_merge_layernorm(ptr(tokens), dtype_code(dt, "tokens"), self.frames, Cc,
+                                                       C.byref(self.layout), ptr(w), ptr(b), float(norm.eps),
+                                                       ptr(self._mask_u8), ptr(self.group_prefix), ptr(self.offsets_i32),
+                                                       ptr(out), stream_ptr(dev)))
+        return out
+
     def split(self, merged: torch.Tensor) -> torch.Tensor:
         """packed ``[P, C]`` -> ``[frames * N, C]``."""
         return co_me_cuext.co_me_token_split_cuda(merged, self.rev_id, merged.shape[-1])

@@ -142,6 +142,19 @@ int come_merge(const void *tokens_dev, int dtype, int64_t frames, int64_t channe
                void *out_dev, void *stream);
 
 /*
+ * Merge fused with the LayerNorm in front of it: out = merge(LayerNorm_C(tokens)), tokens read once.  Every source row is
+ * normalised over its `channels` values (float32 statistics, y = gamma * (x - mean) * rstd + beta, rounded to dtype like
+ * the module's output tensor), then merged windows average their normalised rows as come_merge does.  Replaces
+ * block.norm1 followed by token_merger.merge of the per-layer mode (src/thirdparty/vggt/layers/block.py:73 ->
+ * src/accelerate/vggt/direct.py:97-101).  gamma / beta: [channels] in dtype.  Needs 16-byte aligned pointers, channels a
+ * multiple of 16 bytes and at most 256 such vectors (1024 float32 / 2048 16-bit channels), group size <= 9; anything
+ * else returns COME_ERR_UNSUPPORTED (run the LayerNorm and come_merge separately).
+ */
+int come_merge_layernorm(const void *tokens_dev, int dtype, int64_t frames, int64_t channels, const come_layout_t *layout,
+                         const void *gamma_dev, const void *beta_dev, float eps, const uint8_t *mask_dev,
+                         const int32_t *group_prefix_dev, const int32_t *offsets_dev, void *out_dev, void *stream);
+
+/*
  * Unmerge: out[i, :] = merged[rev_id[i], :].
  * Replaces token_split_gather_kernel{_vec4,} (src/cuda_extension/co_me/src/kernel_token_merge.cu:195-233,
  * host :354-398); fallback index_select (src/accelerate/token_merger/co_me.py:241-254).

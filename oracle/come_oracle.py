@@ -30,6 +30,7 @@ __all__ = [
     "max_seqlen",
     "rope_tables",
     "layer_norm_heads",
+    "layer_norm_rows",
     "rope_2d",
     "qkv_prepare",
     "packed_positions",
@@ -420,6 +421,66 @@ def layer_norm_heads(x: np.ndarray, gamma: np.ndarray, beta: np.ndarray, eps: fl
     mean = (_sum_lanes_of_8(x) * inv_d).astype(np.float32)
     d = (x - mean[..., None]).astype(np.float32)
     var = (_sumsq_lanes_of_8(d) * inv_d).astype(np.float32)
+    rstd = (np.float32(1.0) / np.sqrt((var + np.float32(eps)).astype(np.float32))).astype(np.float32)
+    y = (rstd[..., None] * d).astype(np.float32)
+    y = _fma32(np.broadcast_to(gamma.astype(np.float32), y.shape), y, np.broadcast_to(beta.astype(np.float32), y.shape))
+    return _round_like(y, kind)
+
+
+def _row_total(part: np.ndarray) -> np.ndarray:
+    """Total of per-thread partial sums ``part[..., threads]`` (threads a multiple of 32) in the order of the fused
+    LayerNorm + merge kernel: pairwise tree over the 32 lanes of every warp (neighbours first), then left to right over
+    the warps."""
+    t = part.reshape(part.shape[:-1] + (part.shape[-1] // 32, 32)).astype(np.float32)
+    while t.shape[-1] > 1:
+        t = (t[..., 0::2] + t[..., 1::2]).astype(np.float32)
+    t = t[..., 0]
+    acc = t[..., 0].copy()
+    for w in range(1, t.shape[-1]):
+        acc = (acc + t[..., w]).astype(np.float32)
+    return acc
+
+
+def layer_norm_rows(x: np.ndarray, gamma: np.ndarray, beta: np.ndarray, eps: float, kind: str = "bf16"):
+    """``nn.LayerNorm(C)`` over the channels of dense tokens ``x[..., C]`` held in the element type ``kind`` -- the
+    block's ``norm1`` in front of the attention (``src/thirdparty/vggt/layers/block.py:73``), whose output the per-layer
+    mode merges (``src/accelerate/vggt/direct.py:97-101``).
+
+    float32 statistics and affine map, result rounded to the element type: ``mean = sum(x) / C``,
+    ``var = sum((x - mean)^2) / C`` (two passes, squares accumulated by fused multiply-adds),
+    ``rstd = 1 / sqrt(var + eps)``, ``y = fma(gamma, rstd * (x - mean), beta)``.  The sums run in the fused CUDA kernel's
+    order: a thread owns 16 bytes of consecutive channels (summed left to right), threads are padded to a power of two
+    >= 32, then :func:`_row_total`.  PyTorch's kernels use other orders, which moves a result by at most one unit in the
+    last place of the element type.
+    """
+    x = x.astype(np.float32)
+    C = x.shape[-1]
+    vec = 4 if kind == "f32" else 8
+    assert C % vec == 0
+    cv = C // vec
+    threads = 32
+    while threads < cv:
+        threads *= 2
+    lead = x.shape[:-1]
+
+    def per_thread(v, square):
+        r = v.reshape(lead + (cv, vec))
+        if square:
+            acc = (r[..., 0] * r[..., 0]).astype(np.float32)
+            for i in range(1, vec):
+                acc = _fma32(r[..., i], r[..., i], acc)
+        else:
+            acc = r[..., 0].copy()
+            for i in range(1, vec):
+                acc = (acc + r[..., i]).astype(np.float32)
+        out = np.zeros(lead + (threads,), np.float32)
+        out[..., :cv] = acc
+        return out
+
+    fC = np.float32(C)
+    mean = (_row_total(per_thread(x, False)) / fC).astype(np.float32)
+    d = (x - mean[..., None]).astype(np.float32)
+    var = (_row_total(per_thread(d, True)) / fC).astype(np.float32)
     rstd = (np.float32(1.0) / np.sqrt((var + np.float32(eps)).astype(np.float32))).astype(np.float32)
     y = (rstd[..., None] * d).astype(np.float32)
     y = _fma32(np.broadcast_to(gamma.astype(np.float32), y.shape), y, np.broadcast_to(beta.astype(np.float32), y.shape))

@@ -163,3 +163,28 @@ def position_mask(i: int, case) -> np.ndarray:
     frames, H, W, gh, gw, _s = case
     rng = np.random.default_rng(7900 + i)
     return rng.random((frames, (H // gh) * (W // gw))) < 0.5
+
+
+# ---- LayerNorm + merge (the block's norm1 followed by the merge of the per-layer mode) --------------------------
+LN_MERGE_CASES = [  # (frames, H, W, gh, gw, start_index, C, dtype): grids the reference's 2-D merger accepts
+    (2, 6, 6, 3, 3, 5, 1024, "bf16"),
+    (2, 6, 9, 3, 3, 1, 256, "f32"),
+    (1, 4, 6, 2, 2, 0, 1536, "f16"),
+]
+LN_MERGE_EPS = 1e-6  # the ViT blocks' LayerNorm eps
+
+
+def ln_merge_inputs(i: int, case):
+    frames, H, W, gh, gw, start, C, kind = case
+    rng = np.random.default_rng(8100 + i)
+    x = round_kind(rng.standard_normal((frames, start + H * W, C), dtype=np.float32) * np.float32(1.7) + np.float32(0.2), kind)
+    gamma = round_kind(np.float32(1.0) + np.float32(0.2) * rng.standard_normal(C, dtype=np.float32), kind)
+    beta = round_kind(np.float32(0.1) * rng.standard_normal(C, dtype=np.float32), kind)
+    mask = rng.random((frames, (H // gh) * (W // gw))) < 0.5
+    return x, gamma, beta, mask
+
+
+def ln_merge_tolerance(kind: str) -> float:
+    """Bound against the reference's CPU run: PyTorch sums the LayerNorm statistics in another order, which moves a
+    normalised value by at most one unit in the last place of the element type."""
+    return {"bf16": 2.0 ** -7, "f16": 2.0 ** -10, "f32": 4e-6}[kind]

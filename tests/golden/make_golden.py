@@ -29,7 +29,7 @@ from reference_cases import RANDOM_CONFIGS_1D, RANDOM_CONFIGS_2D, ATTENTION_CASE
 from golden_inputs import (  # noqa: E402
     merge1d_inputs, merge2d_inputs, select_inputs, SELECT_CASES, attention_inputs, EXTRA_ATTENTION_CASES,
     cfg1_inputs, summarize_rows, PREPARE_CASES, PREPARE_EPS, PREPARE_MAX_POSITION, prepare_inputs, POSITION_CASES,
-    position_mask,
+    position_mask, LN_MERGE_CASES, LN_MERGE_EPS, ln_merge_inputs, ln_merge_tolerance,
 )
 
 
@@ -240,6 +240,27 @@ def main():
         assert np.array_equal(orc.packed_positions(mask, start, H, W, gh, gw), ref_pos), ("positions", case)
         store[f"pos{i}"] = ref_pos.astype(np.int16)
     np.savez_compressed(os.path.join(HERE, "prepare.npz"), **store)
+
+    # ---- LayerNorm + merge: nn.LayerNorm on CPU, then the reference's 2-D merge of its output ---------------------
+    store = {}
+    for i, case in enumerate(LN_MERGE_CASES):
+        frames, H, W, gh, gw, start, C, kind = case
+        dt = {"bf16": torch.bfloat16, "f16": torch.float16, "f32": torch.float32}[kind]
+        x, gamma, beta, mask = ln_merge_inputs(i, case)
+        ln = torch.nn.LayerNorm(C, eps=LN_MERGE_EPS).to(dt)
+        with torch.no_grad():
+            ln.weight.copy_(t(gamma))
+            ln.bias.copy_(t(beta))
+            y = ln(t(x).to(dt))
+        with CUDAExtension.disable():
+            jag, _rev = co_me_2d.func_token_merge_2d(y, start, gh, gw, H, W, t(mask))
+        ref = jag.tokens[0].float().numpy()
+        ours, _o, _r, _w = orc.token_merge_2d(orc.layer_norm_rows(x, gamma, beta, LN_MERGE_EPS, kind), start, gh, gw, H, W, mask)
+        ours = orc._round_like(ours, kind)
+        tol = ln_merge_tolerance(kind)
+        assert np.allclose(ours, ref, rtol=tol, atol=tol), ("ln+merge", case, np.abs(ours - ref).max())
+        store.update({f"l{i}_out_{k}": v for k, v in summarize_rows(ref, 7).items()})
+    np.savez_compressed(os.path.join(HERE, "ln_merge.npz"), **store)
 
     # ---- standalone op chain of the headline configuration (8 x 1374 tokens, 37x37 grid, 3x3 windows) ----
     tokens, conf = cfg1_inputs()

@@ -329,3 +329,57 @@ def test_split_add_residual(kind, C, with_scale):
     np.testing.assert_array_equal(to_np(got).reshape(-1, C), want)
     plan.split_add(to_dev(merged, kind), xd, None if gamma is None else to_dev(gamma, kind), out=xd)  # in place
     np.testing.assert_array_equal(to_np(xd), want)
+
+
+@pytest.mark.parametrize("idx", range(3))
+def test_merge_layernorm_fixture_and_oracle(golden_dir, idx):
+    """LayerNorm fused into the merge: bit for bit against the oracle (same summation order), within one unit in the last
+    place against nn.LayerNorm + the reference's merge (fixture)."""
+    import torch
+    from come_b200 import _lib
+    from come_b200.token_merger import MergePlan
+    from gpu_util import TORCH_DTYPE, to_dev, to_np
+    import golden_inputs as gi
+    from oracle import come_oracle as orc
+    z = np.load(os.path.join(golden_dir, "ln_merge.npz"))
+    case = gi.LN_MERGE_CASES[idx]
+    frames, H, W, gh, gw, start, C, kind = case
+    x, gamma, beta, mask = gi.ln_merge_inputs(idx, case)
+    ln = torch.nn.LayerNorm(C, eps=gi.LN_MERGE_EPS).cuda().to(TORCH_DTYPE[kind])
+    with torch.no_grad():
+        ln.weight.copy_(to_dev(gamma, kind))
+        ln.bias.copy_(to_dev(beta, kind))
+    plan = MergePlan(torch.from_numpy(mask).cuda(), _lib.Layout.two_d(start, H, W, gh, gw))
+    got = to_np(plan.merge_layernorm(to_dev(x, kind), ln))
+    want, _off, _rev, _w = orc.token_merge_2d(orc.layer_norm_rows(x, gamma, beta, gi.LN_MERGE_EPS, kind), start, gh, gw, H, W, mask)
+    np.testing.assert_array_equal(got, orc._round_like(want, kind))
+    tol = gi.ln_merge_tolerance(kind)
+    gi.check_rows(got, z, f"l{idx}_out_", rtol=tol, atol=tol)
+
+
+def test_merge_layernorm_headline_shape():
+    """8 x 1374 x 1024 bfloat16 on the ragged 37 x 37 grid: fused kernel == LayerNorm oracle + merge oracle, bit for bit;
+    shapes the fused kernel does not take are refused."""
+    import torch
+    from come_b200 import _lib
+    from come_b200.token_merger import MergePlan
+    from gpu_util import to_dev, to_np
+    import golden_inputs as gi
+    from oracle import come_oracle as orc
+    rng = np.random.default_rng(77)
+    frames, C = 3, 1024
+    x = gi.round_kind(rng.standard_normal((frames, 1374, C), dtype=np.float32) * 3 - 1, "bf16")
+    gamma = gi.round_kind(1 + 0.3 * rng.standard_normal(C, dtype=np.float32), "bf16")
+    beta = gi.round_kind(0.2 * rng.standard_normal(C, dtype=np.float32), "bf16")
+    mask = rng.random((frames, 144)) < 0.5
+    ln = torch.nn.LayerNorm(C, eps=1e-6).cuda().bfloat16()
+    with torch.no_grad():
+        ln.weight.copy_(to_dev(gamma, "bf16"))
+        ln.bias.copy_(to_dev(beta, "bf16"))
+    plan = MergePlan(torch.from_numpy(mask).cuda(), _lib.Layout.two_d(5, 37, 37, 3, 3))
+    got = to_np(plan.merge_layernorm(to_dev(x, "bf16"), ln))
+    want, _off, _rev, _w = orc.token_merge_2d_ragged(orc.layer_norm_rows(x, gamma, beta, 1e-6, "bf16"), 5, 3, 3, 37, 37, mask)
+    np.testing.assert_array_equal(got, orc._round_like(want, "bf16"))
+    wide = torch.zeros(frames, 1374, 4096, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(NotImplementedError):
+        plan.merge_layernorm(wide, torch.nn.LayerNorm(4096).cuda().bfloat16())

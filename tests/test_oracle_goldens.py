@@ -205,3 +205,15 @@ def test_positions_are_window_centres():
                 assert tuple(pos[row]) == (3 * (y // 3) + 2, 3 * (x // 3) + 2) and w[row] == 9
             else:
                 assert tuple(pos[row]) == (y + 1, x + 1) and w[row] == 1
+
+
+@pytest.mark.parametrize("idx", range(len(gi.LN_MERGE_CASES)))
+def test_ln_merge_fixture(golden_dir, idx):
+    """LayerNorm over the channels followed by the 2-D merge, against nn.LayerNorm + the reference's merge on CPU."""
+    z = _load(golden_dir, "ln_merge.npz")
+    case = gi.LN_MERGE_CASES[idx]
+    frames, H, W, gh, gw, start, C, kind = case
+    x, gamma, beta, mask = gi.ln_merge_inputs(idx, case)
+    out, _off, _rev, _w = orc.token_merge_2d(orc.layer_norm_rows(x, gamma, beta, gi.LN_MERGE_EPS, kind), start, gh, gw, H, W, mask)
+    tol = gi.ln_merge_tolerance(kind)
+    gi.check_rows(orc._round_like(out, kind), z, f"l{idx}_out_", rtol=tol, atol=tol)
