@@ -49,3 +49,25 @@ class DirectAttention(torch.nn.Module):
         pos: Optional[torch.Tensor] = plan.positions() if use_pos else None
         out = self.attn_op(jag, pos=pos, max_seqlen=max_seqlen)
         return plan.split(out.tokens.squeeze(0)).view(*input_shape).to(input_dtype)
+
+    def forward_residual(self, x: torch.Tensor, plan: MergePlan, frames_per_scene: int, norm1: torch.nn.LayerNorm,
+                         ls1_gamma: Optional[torch.Tensor] = None, use_pos: bool = True) -> torch.Tensor:
+        """The whole attention branch of a block, ``x + ls1(attn(norm1(x)))`` (``src/thirdparty/vggt/layers/block.py:73,90``),
+        with the dense tokens read once and written once: ``norm1`` runs inside the merge (``come_merge_layernorm``), the
+        unmerge applies LayerScale and adds the residual (``come_unmerge_residual``).  ``x`` must already be in the run
+        dtype (the block's tensors in the reference's per-layer mode are)."""
+        if x.dtype != self.attn_op.run_dtype:
+            raise RuntimeError(f"forward_residual expects tokens in {self.attn_op.run_dtype}, got {x.dtype}")
+        input_shape = x.shape
+        C = x.shape[-1]
+        dense = x.reshape(plan.frames, plan.tokens_per_frame, C)
+        merged = plan.merge_layernorm(dense, norm1)
+        if self.is_global:
+            offset = plan.offset[::frames_per_scene]
+            max_seqlen = plan.total if plan.frames == frames_per_scene else None
+        else:
+            offset, max_seqlen = plan.offset, plan.max_seqlen
+        jag = JaggedTokens(tokens=merged.unsqueeze(0), weight=plan.weight, offset=offset)
+        out = self.attn_op(jag, pos=plan.positions() if use_pos else None, max_seqlen=max_seqlen)
+        gamma = None if ls1_gamma is None else ls1_gamma.detach().to(device=x.device, dtype=x.dtype)
+        return plan.split_add(out.tokens.squeeze(0), dense, gamma).view(*input_shape)

@@ -212,3 +212,44 @@ def test_direct_attention_block(is_global):
     want = orc.token_split(to_np(proj), rev).reshape(x_in.shape)
     err = np.abs(to_np(y) - want).max()
     assert err <= 2e-2, err
+
+
+def test_direct_attention_residual_branch():
+    """x + ls1(attn(norm1(x))) through the fused kernels (LayerNorm inside the merge, LayerScale + residual inside the
+    unmerge) against the oracle chain around the same two GEMMs."""
+    from come_b200 import _lib
+    from come_b200.direct import DirectAttention
+    from come_b200.token_merger import MergePlan
+    torch.manual_seed(6)
+    dim, heads, S, Hg, Wg = 128, 2, 2, 6, 6
+    rng = np.random.default_rng(31)
+    mask = rng.random((S, 4)) < 0.5
+    plan = MergePlan(torch.from_numpy(mask).cuda(), _lib.Layout.two_d(5, Hg, Wg, 3, 3))
+    N = 5 + Hg * Wg
+    mod = DirectAttention(_Attention(dim, heads).cuda(), is_global=False).eval()
+    norm1 = torch.nn.LayerNorm(dim, eps=1e-6).cuda().bfloat16()
+    with torch.no_grad():
+        norm1.weight.copy_(torch.from_numpy(1 + 0.2 * rng.standard_normal(dim, dtype=np.float32)).cuda())
+        norm1.bias.copy_(torch.from_numpy(0.1 * rng.standard_normal(dim, dtype=np.float32)).cuda())
+    gamma = torch.from_numpy(gi.round_kind(0.5 * rng.random(dim, dtype=np.float32), "bf16")).cuda().bfloat16()
+    xb = gi.round_kind(rng.standard_normal((S, N, dim), dtype=np.float32), "bf16")
+    x = to_dev(xb, "bf16")
+    with torch.no_grad():
+        y = mod.forward_residual(x, plan, S, norm1, gamma)
+    assert y.shape == x.shape and y.dtype == torch.bfloat16
+    a = mod.attn_op.attn
+    normed = orc.layer_norm_rows(xb, to_np(norm1.weight), to_np(norm1.bias), 1e-6, "bf16")
+    merged, off, rev, w = orc.token_merge_2d_ragged(normed, 5, 3, 3, Hg, Wg, mask)
+    merged = gi.round_kind(merged, "bf16")
+    P = merged.shape[0]
+    with torch.no_grad():
+        qkv = a.qkv(torch.from_numpy(merged).cuda().bfloat16()).reshape(P, 3, heads, dim // heads)
+    cos_t, sin_t = orc.rope_tables(dim // heads // 2, 256, 100.0, "bf16")
+    prepared = orc.qkv_prepare(to_np(qkv), to_np(a.q_norm.weight), to_np(a.q_norm.bias), to_np(a.k_norm.weight),
+                               to_np(a.k_norm.bias), a.q_norm.eps, orc.packed_positions(mask, 5, Hg, Wg, 3, 3), cos_t, sin_t, "bf16")
+    att, _ = orc.attention_bias(prepared[:, 0], prepared[:, 1], prepared[:, 2], orc.perkey_bias_from_weight(w, "bf16"),
+                                off.astype(np.int32), a.scale)
+    with torch.no_grad():
+        proj = a.proj(torch.from_numpy(att.reshape(P, dim)).cuda().bfloat16())
+    want = orc.token_split_residual(to_np(proj), rev, xb.reshape(-1, dim), to_np(gamma), "bf16").reshape(S, N, dim)
+    assert np.abs(to_np(y) - want).max() <= 2e-2
