@@ -614,7 +614,7 @@ def run_only(args):
     g = torch.Generator(device=dev).manual_seed(0)
     ev = lambda: torch.cuda.Event(enable_timing=True)  # noqa: E731
     out = {"only": args.only}
-    if args.only in ("merge", "unmerge"):
+    if args.only in ("merge", "unmerge", "merge_ln", "unmerge_res"):
         dt = {"f32": torch.float32, "bf16": torch.bfloat16}[args.dtype]
         x = torch.randn((args.frames, N_TOK, CH), device=dev, generator=g).to(dt)
         mask = torch.rand((args.frames, N_WIN), device=dev, generator=g) < 0.5
@@ -623,6 +623,13 @@ def run_only(args):
         es = x.element_size()
         if args.only == "merge":
             fn, nbytes = (lambda: plan.merge(x)), args.frames * N_TOK * CH * es + plan.total * CH * es + args.frames * N_WIN + (args.frames + 1) * 4
+        elif args.only == "merge_ln":  # LayerNorm over the channels fused into the merge: same traffic + gamma / beta
+            ln = torch.nn.LayerNorm(CH, eps=1e-6).to(dev).to(dt)
+            fn, nbytes = (lambda: plan.merge_layernorm(x, ln)), args.frames * N_TOK * CH * es + plan.total * CH * es + args.frames * N_WIN + (args.frames + 1) * 4 + 2 * CH * es
+        elif args.only == "unmerge_res":  # unmerge + LayerScale + residual add: one more dense read
+            gamma = torch.rand(CH, device=dev, generator=g).to(dt)
+            res = x.reshape(-1, CH)
+            fn, nbytes = (lambda: plan.split_add(merged, res, gamma)), plan.total * CH * es + args.frames * N_TOK * 8 + 2 * args.frames * N_TOK * CH * es + CH * es
         else:
             fn, nbytes = (lambda: plan.split(merged)), plan.total * CH * es + args.frames * N_TOK * 8 + args.frames * N_TOK * CH * es
         out.update(frames=args.frames, dtype=args.dtype, bytes=nbytes)
@@ -728,7 +735,7 @@ def run_only(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--only", choices=["attn", "merge", "unmerge", "prepare", "direct"], help="run one kernel family on one size and exit")
+    ap.add_argument("--only", choices=["attn", "merge", "unmerge", "merge_ln", "unmerge_res", "prepare", "direct"], help="run one kernel family on one size and exit")
     ap.add_argument("--frames", type=int, default=100, help="--only merge/unmerge: frames")
     ap.add_argument("--dtype", default="f32", choices=["f32", "bf16"], help="--only merge/unmerge: element type")
     ap.add_argument("--tokens", type=int, default=6384, help="--only attn with --segments 1: segment length")

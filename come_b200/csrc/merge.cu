@@ -336,11 +336,13 @@ merge_kernel(const T *__restrict__ tokens, const uint8_t *__restrict__ mask, con
 // out = merge(LayerNorm(tokens)): every source row is normalised over its C channels (float32 statistics and affine map,
 // result rounded to T like the module's output tensor), then merged windows average their G normalised rows.  One
 // thread group of `tpg` threads (a power of two >= the vectors per row) owns a unit; a thread holds its 16-byte vector
-// of every row of the unit in registers, so the tokens are read once.
+// of every row of the unit in registers as float32 pairs, so the tokens are read once.
 //
-// Summation order of a row's statistics (fixed, so that the CPU oracle can follow it bit for bit): inside a thread left to
-// right over its VEC channels, then a butterfly over the 32 lanes (neighbours first), then left to right over the warps of
-// the group.  The squares are accumulated with fused multiply-adds.
+// Summation order of a row's statistics (fixed, so that the CPU oracle can follow it bit for bit): inside a thread the
+// even and the odd channels of its vector are summed left to right as two chains (packed two-lane adds) and the chains
+// added; the threads' partial sums go through shared memory, where one warp per row adds, for every lane position, the
+// partials of the group's warps left to right and then runs a butterfly over the 32 lanes (neighbours first).  The
+// squares are accumulated with fused multiply-adds.  The same warp turns the totals into mean and 1/sqrt(var + eps).
 constexpr int kLnMaxRows = 9;  // rows per unit the fused kernel keeps in registers (3 x 3 windows)
 
 __device__ __forceinline__ void group_barrier(int groups, int grp, int tpg) {
@@ -348,56 +350,109 @@ __device__ __forceinline__ void group_barrier(int groups, int grp, int tpg) {
     else asm volatile("bar.sync %0, %1;" ::"r"(grp + 1), "r"(tpg) : "memory");
 }
 
+template <typename T, int VEC> struct PairIO;  // 16-byte vector <-> VEC/2 float32 pairs
+template <> struct PairIO<float, 4> {
+    static __device__ __forceinline__ void unpack(const float4 &v, f32x2_t (&p)[2]) {
+        p[0] = pack_f32x2(v.x, v.y);
+        p[1] = pack_f32x2(v.z, v.w);
+    }
+    static __device__ __forceinline__ float4 pack(const f32x2_t (&p)[2]) {
+        float4 v;
+        unpack_f32x2(p[0], v.x, v.y);
+        unpack_f32x2(p[1], v.z, v.w);
+        return v;
+    }
+    static __device__ __forceinline__ f32x2_t round_pair(f32x2_t p) { return p; }
+};
+// 16-bit pairs <-> float32 pairs on 32-bit words (no address-taken arrays: everything stays in registers).
+__device__ __forceinline__ float2 word_to_f32(uint32_t w, __half) { return __half22float2(*reinterpret_cast<const __half2 *>(&w)); }
+__device__ __forceinline__ float2 word_to_f32(uint32_t w, __nv_bfloat16) {
+    return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));  // a bfloat16 is the top half of a float32
+}
+__device__ __forceinline__ uint32_t f32_to_word(float lo, float hi, __half) {
+    const __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t *>(&v);
+}
+__device__ __forceinline__ uint32_t f32_to_word(float lo, float hi, __nv_bfloat16) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t *>(&v);
+}
+template <typename T> struct PairIO16 {
+    static __device__ __forceinline__ void unpack(const uint4 &v, f32x2_t (&p)[4]) {
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 f = word_to_f32(w[j], T());
+            p[j] = pack_f32x2(f.x, f.y);
+        }
+    }
+    static __device__ __forceinline__ uint4 pack(const f32x2_t (&p)[4]) {
+        uint32_t w[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            float lo, hi;
+            unpack_f32x2(p[j], lo, hi);
+            w[j] = f32_to_word(lo, hi, T());
+        }
+        return make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    static __device__ __forceinline__ f32x2_t round_pair(f32x2_t p) {
+        float lo, hi;
+        unpack_f32x2(p, lo, hi);
+        const float2 f = word_to_f32(f32_to_word(lo, hi, T()), T());
+        return pack_f32x2(f.x, f.y);
+    }
+};
+template <> struct PairIO<__half, 8> : PairIO16<__half> {};
+template <> struct PairIO<__nv_bfloat16, 8> : PairIO16<__nv_bfloat16> {};
+
 template <typename T, int VEC>
 __global__ void __launch_bounds__(kMergeThreads, 2)
 merge_layernorm_kernel(const T *__restrict__ tokens, const uint8_t *__restrict__ mask, const int *__restrict__ group_prefix,
                        const int *__restrict__ offsets, FrameLayout L, int frames, int Cv, int groups,
                        const T *__restrict__ gamma, const T *__restrict__ beta, float eps, T *__restrict__ out) {
     using IO = VecIO<T, VEC>;
+    using PIO = PairIO<T, VEC>;
     using V = typename IO::V;
+    constexpr int NP = VEC / 2;  // float32 pairs per thread and row
     extern __shared__ int s_ln_raw[];
     const int G = L.G;
     const int tpg = kMergeThreads / groups, warps_pg = tpg / 32;
     const int grp = threadIdx.x / tpg, tig = threadIdx.x - grp * tpg;
     const int wig = tig >> 5, lane = tig & 31;
-    int *s_src = s_ln_raw + grp * G;                                              // [groups][G]
-    float *s_red = reinterpret_cast<float *>(s_ln_raw + groups * G) + grp * (kLnMaxRows * 8);  // [groups][rows][warps <= 8]
+    // shared memory: [groups][G] source tokens | [groups][kLnMaxRows][tpg] partial sums | [groups][kLnMaxRows] row statistic
+    int *s_src = s_ln_raw + grp * G;
+    float *s_part = reinterpret_cast<float *>(s_ln_raw + groups * G) + grp * (kLnMaxRows * tpg);
+    float *s_stat = reinterpret_cast<float *>(s_ln_raw + groups * G) + groups * (kLnMaxRows * tpg) + grp * kLnMaxRows;
     const int prefix_units = (L.prefix + G - 1) / G;
     const int units_per_frame = prefix_units + L.M;
     const int n_units = frames * units_per_frame;
     const bool has_col = tig < Cv;  // a group may be wider than a row (rows of 96, 192, ... vectors)
     const float fC = (float)(Cv * VEC), fG = (float)G;
-    float g[VEC], b[VEC];
-#pragma unroll
-    for (int i = 0; i < VEC; ++i) g[i] = b[i] = 0.0f;
+    V g_raw = V(), b_raw = V();  // this thread's gamma / beta, kept packed (unpacked where used: registers are tight)
     if (has_col) {
-        IO::unpack(reinterpret_cast<const V *>(gamma)[tig], g);
-        IO::unpack(reinterpret_cast<const V *>(beta)[tig], b);
+        g_raw = reinterpret_cast<const V *>(gamma)[tig];
+        b_raw = reinterpret_cast<const V *>(beta)[tig];
     }
 
-    // Sum of one value per thread over the group's row, for all rows of the unit at once: butterfly inside the warp,
-    // warp totals through shared memory, every thread then adds the warp totals left to right.
-    auto row_totals = [&](float (&part)[kLnMaxRows], int rows) {
+    // Row totals of one partial sum per thread, for all rows of the unit at once; `finish` turns a row's total into the
+    // statistic every thread then reads back (mean after the first pass, 1/sqrt(var + eps) after the second).
+    auto row_statistics = [&](float (&part)[kLnMaxRows], int rows, auto finish) {
+        group_barrier(groups, grp, tpg);  // the previous use of s_part / s_stat is over
 #pragma unroll
-        for (int r = 0; r < kLnMaxRows; ++r) {
+        for (int r = 0; r < kLnMaxRows; ++r)
+            if (r < rows) s_part[r * tpg + tig] = part[r];
+        group_barrier(groups, grp, tpg);
+        for (int r = wig; r < rows; r += warps_pg) {
+            float t = s_part[r * tpg + lane];
+            for (int w = 1; w < warps_pg; ++w) t = __fadd_rn(t, s_part[r * tpg + w * 32 + lane]);
 #pragma unroll
-            for (int m = 1; m < 32; m <<= 1) part[r] = __fadd_rn(part[r], __shfl_xor_sync(0xffffffffu, part[r], m));
-        }
-        group_barrier(groups, grp, tpg);  // the previous use of s_red is over
-        if (lane == 0) {
-#pragma unroll
-            for (int r = 0; r < kLnMaxRows; ++r)
-                if (r < rows) s_red[r * 8 + wig] = part[r];
+            for (int m = 1; m < 32; m <<= 1) t = __fadd_rn(t, __shfl_xor_sync(0xffffffffu, t, m));
+            if (lane == 0) s_stat[r] = finish(t);
         }
         group_barrier(groups, grp, tpg);
 #pragma unroll
-        for (int r = 0; r < kLnMaxRows; ++r) {
-            if (r < rows) {
-                float t = s_red[r * 8];
-                for (int w = 1; w < warps_pg; ++w) t = __fadd_rn(t, s_red[r * 8 + w]);
-                part[r] = t;
-            }
-        }
+        for (int r = 0; r < kLnMaxRows; ++r) part[r] = (r < rows) ? s_stat[r] : 0.0f;
     };
 
     for (int u0 = blockIdx.x * groups; u0 < n_units; u0 += gridDim.x * groups) {
@@ -426,70 +481,74 @@ merge_layernorm_kernel(const T *__restrict__ tokens, const uint8_t *__restrict__
         group_barrier(groups, grp, tpg);
         const V *src_base = reinterpret_cast<const V *>(tokens) + (int64_t)bfr * L.N * Cv;
 
-        V x[kLnMaxRows];
+        V raw[kLnMaxRows];
 #pragma unroll
         for (int r = 0; r < kLnMaxRows; ++r)
-            if (r < rows && has_col) x[r] = ld_stream(src_base + (int64_t)s_src[r] * Cv + tig);
-        float part[kLnMaxRows], mean[kLnMaxRows];
+            if (r < rows && has_col) raw[r] = ld_stream(src_base + (int64_t)s_src[r] * Cv + tig);
+        f32x2_t x[kLnMaxRows][NP];
+        float stat[kLnMaxRows];
 #pragma unroll
         for (int r = 0; r < kLnMaxRows; ++r) {
-            part[r] = 0.0f;
-            if (r < rows && has_col) {
-                float f[VEC];
-                IO::unpack(x[r], f);
-                float t = f[0];
+            stat[r] = 0.0f;
 #pragma unroll
-                for (int i = 1; i < VEC; ++i) t = __fadd_rn(t, f[i]);
-                part[r] = t;
+            for (int j = 0; j < NP; ++j) x[r][j] = 0ull;
+            if (r < rows && has_col) {
+                PIO::unpack(raw[r], x[r]);
+                f32x2_t acc = x[r][0];
+#pragma unroll
+                for (int j = 1; j < NP; ++j) acc = add_f32x2(acc, x[r][j]);
+                float even, odd;
+                unpack_f32x2(acc, even, odd);
+                stat[r] = __fadd_rn(even, odd);
             }
         }
-        row_totals(part, rows);
+        row_statistics(stat, rows, [&](float total) { return __fdiv_rn(total, fC); });
 #pragma unroll
         for (int r = 0; r < kLnMaxRows; ++r) {
-            mean[r] = (r < rows) ? __fdiv_rn(part[r], fC) : 0.0f;
-            part[r] = 0.0f;
+            const f32x2_t neg_mean = pack_f32x2(-stat[r], -stat[r]);
+            stat[r] = 0.0f;
             if (r < rows && has_col) {
-                float f[VEC];
-                IO::unpack(x[r], f);
-                float d0 = __fsub_rn(f[0], mean[r]);
-                float t = __fmul_rn(d0, d0);
 #pragma unroll
-                for (int i = 1; i < VEC; ++i) {
-                    const float d = __fsub_rn(f[i], mean[r]);
-                    t = __fmaf_rn(d, d, t);
-                }
-                part[r] = t;
+                for (int j = 0; j < NP; ++j) x[r][j] = add_f32x2(x[r][j], neg_mean);  // x - mean
+                f32x2_t acc = mul_f32x2(x[r][0], x[r][0]);
+#pragma unroll
+                for (int j = 1; j < NP; ++j) acc = fma_f32x2(x[r][j], x[r][j], acc);  // explicit: never a separate mul + add
+                float even, odd;
+                unpack_f32x2(acc, even, odd);
+                stat[r] = __fadd_rn(even, odd);
             }
         }
-        row_totals(part, rows);
+        row_statistics(stat, rows, [&](float total) { return __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(total, fC), eps))); });
         if (has_col) {
-            float acc[VEC];
+            f32x2_t acc[NP], g2[NP], b2[NP];
+            PIO::unpack(g_raw, g2);
+            PIO::unpack(b_raw, b2);
 #pragma unroll
-            for (int i = 0; i < VEC; ++i) acc[i] = 0.0f;
+            for (int j = 0; j < NP; ++j) acc[j] = 0ull;
             V *dst_base = reinterpret_cast<V *>(out) + (int64_t)dst * Cv + tig;
 #pragma unroll
             for (int r = 0; r < kLnMaxRows; ++r) {
                 if (r < rows) {
-                    const float rstd = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(part[r], fC), eps)));
-                    float f[VEC];
-                    IO::unpack(x[r], f);
+                    const f32x2_t rstd2 = pack_f32x2(stat[r], stat[r]);
 #pragma unroll
-                    for (int i = 0; i < VEC; ++i) {
-                        const float y = __fmaf_rn(g[i], __fmul_rn(rstd, __fsub_rn(f[i], mean[r])), b[i]);
-                        f[i] = Elem<T>::to_f32(Elem<T>::from_f32(y));  // the normalised tensor lives in T
-                    }
+                    for (int j = 0; j < NP; ++j) x[r][j] = fma_f32x2(g2[j], mul_f32x2(rstd2, x[r][j]), b2[j]);
                     if (merged) {
+                        // the normalised tensor lives in T: its rounded values are what the window mean sums
 #pragma unroll
-                        for (int i = 0; i < VEC; ++i) acc[i] = __fadd_rn(acc[i], f[i]);
+                        for (int j = 0; j < NP; ++j) acc[j] = add_f32x2(acc[j], PIO::round_pair(x[r][j]));
                     } else {
-                        st_stream(dst_base + (int64_t)r * Cv, IO::pack(f));
+                        st_stream(dst_base + (int64_t)r * Cv, PIO::pack(x[r]));
                     }
                 }
             }
             if (merged) {
 #pragma unroll
-                for (int i = 0; i < VEC; ++i) acc[i] = __fdiv_rn(acc[i], fG);
-                st_stream(dst_base, IO::pack(acc));
+                for (int j = 0; j < NP; ++j) {
+                    float lo, hi;
+                    unpack_f32x2(acc[j], lo, hi);
+                    acc[j] = pack_f32x2(__fdiv_rn(lo, fG), __fdiv_rn(hi, fG));
+                }
+                st_stream(dst_base, PIO::pack(acc));
             }
         }
     }
@@ -513,7 +572,7 @@ static int launch_merge_layernorm(const void *tokens, int64_t frames, int64_t C,
     const int prefix_units = (L.prefix + L.G - 1) / L.G;
     const int64_t n_units = frames * (int64_t)(prefix_units + L.M);
     if (n_units == 0) return COME_OK;
-    const size_t smem = (size_t)groups * L.G * sizeof(int) + (size_t)groups * kLnMaxRows * 8 * sizeof(float);
+    const size_t smem = (size_t)groups * L.G * sizeof(int) + (size_t)groups * kLnMaxRows * (tpg + 1) * sizeof(float);
     const int64_t n_ctas = (n_units + groups - 1) / groups;
     const int64_t max_blocks = (int64_t)sm_count() * 8;
     merge_layernorm_kernel<T, VEC><<<(unsigned)(n_ctas < max_blocks ? n_ctas : max_blocks), kMergeThreads, smem, st>>>(

@@ -429,16 +429,15 @@ def layer_norm_heads(x: np.ndarray, gamma: np.ndarray, beta: np.ndarray, eps: fl
 
 def _row_total(part: np.ndarray) -> np.ndarray:
     """Total of per-thread partial sums ``part[..., threads]`` (threads a multiple of 32) in the order of the fused
-    LayerNorm + merge kernel: pairwise tree over the 32 lanes of every warp (neighbours first), then left to right over
-    the warps."""
+    LayerNorm + merge kernel: for every lane position the partials of the group's warps are added left to right, then a
+    pairwise tree runs over the 32 lane positions (neighbours first)."""
     t = part.reshape(part.shape[:-1] + (part.shape[-1] // 32, 32)).astype(np.float32)
-    while t.shape[-1] > 1:
-        t = (t[..., 0::2] + t[..., 1::2]).astype(np.float32)
-    t = t[..., 0]
-    acc = t[..., 0].copy()
-    for w in range(1, t.shape[-1]):
-        acc = (acc + t[..., w]).astype(np.float32)
-    return acc
+    acc = t[..., 0, :].copy()
+    for w in range(1, t.shape[-2]):
+        acc = (acc + t[..., w, :]).astype(np.float32)
+    while acc.shape[-1] > 1:
+        acc = (acc[..., 0::2] + acc[..., 1::2]).astype(np.float32)
+    return acc[..., 0]
 
 
 def layer_norm_rows(x: np.ndarray, gamma: np.ndarray, beta: np.ndarray, eps: float, kind: str = "bf16"):
@@ -449,9 +448,9 @@ def layer_norm_rows(x: np.ndarray, gamma: np.ndarray, beta: np.ndarray, eps: flo
     float32 statistics and affine map, result rounded to the element type: ``mean = sum(x) / C``,
     ``var = sum((x - mean)^2) / C`` (two passes, squares accumulated by fused multiply-adds),
     ``rstd = 1 / sqrt(var + eps)``, ``y = fma(gamma, rstd * (x - mean), beta)``.  The sums run in the fused CUDA kernel's
-    order: a thread owns 16 bytes of consecutive channels (summed left to right), threads are padded to a power of two
-    >= 32, then :func:`_row_total`.  PyTorch's kernels use other orders, which moves a result by at most one unit in the
-    last place of the element type.
+    order: a thread owns 16 bytes of consecutive channels, whose even and odd members are summed left to right as two
+    chains and the chains added; threads are padded to a power of two >= 32, then :func:`_row_total`.  PyTorch's kernels
+    use other orders, which moves a result by at most one unit in the last place of the element type.
     """
     x = x.astype(np.float32)
     C = x.shape[-1]
@@ -464,17 +463,17 @@ def layer_norm_rows(x: np.ndarray, gamma: np.ndarray, beta: np.ndarray, eps: flo
     lead = x.shape[:-1]
 
     def per_thread(v, square):
-        r = v.reshape(lead + (cv, vec))
+        r = v.reshape(lead + (cv, vec // 2, 2))
         if square:
-            acc = (r[..., 0] * r[..., 0]).astype(np.float32)
-            for i in range(1, vec):
-                acc = _fma32(r[..., i], r[..., i], acc)
+            acc = (r[..., 0, :] * r[..., 0, :]).astype(np.float32)
+            for i in range(1, vec // 2):
+                acc = _fma32(r[..., i, :], r[..., i, :], acc)
         else:
-            acc = r[..., 0].copy()
-            for i in range(1, vec):
-                acc = (acc + r[..., i]).astype(np.float32)
+            acc = r[..., 0, :].copy()
+            for i in range(1, vec // 2):
+                acc = (acc + r[..., i, :]).astype(np.float32)
         out = np.zeros(lead + (threads,), np.float32)
-        out[..., :cv] = acc
+        out[..., :cv] = (acc[..., 0] + acc[..., 1]).astype(np.float32)
         return out
 
     fC = np.float32(C)
