@@ -42,12 +42,15 @@ constexpr int kSlabStages = 3;    // bias slab ring slots, 8 KiB each (only two 
 constexpr int kProducerWarp = 4 * kTiles;      // warps 0 .. 4*kTiles-1 are the softmax groups
 constexpr int kIssuerWarp0 = kProducerWarp + 1;  // one MMA issuer warp per query tile
 constexpr int kThreads = 32 * (kIssuerWarp0 + kTiles);  // 512: three softmax warpgroups + one producer / issuer warpgroup
+// Launches with this many segments enumerate only the query blocks that exist (a prefix table in shared memory)
+constexpr int kMinPrefixSegs = 16, kMaxPrefixSegs = 2048;
 constexpr int kQTileBytes = kBlockM * kHeadDim * 2;   // 16384
 constexpr int kKvTileBytes = kBlockN * kHeadDim * 2;  // 8192
 // Tensor-memory columns: S_t (scores, float32) | O_t (accumulator, float32) | P_t (probabilities, 16-bit pairs)
 constexpr uint32_t kTmemS = 0, kTmemO = kTiles * kBlockN, kTmemP = kTmemO + kTiles * kHeadDim;
 static_assert(kTmemP + kTiles * (kBlockN / 2) <= 512, "tensor memory holds 512 columns");
 static_assert(kThreads % 128 == 0, "setmaxnreg works on whole warpgroups");
+static_assert(kMaxPrefixSegs % kThreads == 0, "every thread scans the same number of segments");
 constexpr uint32_t kTmemCols = 512;
 constexpr long long kWaitTicks = 1ll << 29;
 constexpr float kLog2e = 1.4426950408889634f;
@@ -80,9 +83,13 @@ struct SharedStorage {
     uint64_t s_empty[kTiles];
     uint32_t tmem_base;
     volatile uint32_t abort_flag;
+    int scan_warp[kThreads / 32];
 };
+// Launches that use the prefix table get (kMaxPrefixSegs + 1) ints of dynamic shared memory behind SharedStorage:
+// table[s] = query blocks of the segments before s (this launch's rows).
+constexpr size_t kPrefixTableBytes = sizeof(int) * (kMaxPrefixSegs + 1);
 
-static_assert(sizeof(SharedStorage) + 1024 <= 227 * 1024, "shared storage exceeds the 227 KB a CTA may use");
+static_assert(sizeof(SharedStorage) + kPrefixTableBytes + 1024 <= 227 * 1024, "shared storage exceeds the 227 KB a CTA may use");
 
 // ---- PTX wrappers ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -313,12 +320,38 @@ struct WorkItem {
     bool valid;
 };
 
-__device__ __forceinline__ WorkItem decode_item(int item, int nblk_x, int nseg, const int *__restrict__ cu, int q_begin, int q_end) {
+// Query blocks of segment `seg` that hold rows of this launch.
+__device__ __forceinline__ int segment_blocks(int seg, const int *__restrict__ cu, int q_begin, int q_end) {
+    const int rows = min(cu[seg + 1], q_end) - max(cu[seg], q_begin);
+    return rows > 0 ? (rows + kTiles * kBlockM - 1) / (kTiles * kBlockM) : 0;
+}
+
+// Item -> (head, segment, query block).  With a prefix table (seg_prefix != nullptr) the items are exactly the query
+// blocks that exist, in (head, segment, block) order; without it every segment gets `nblk_x` slots and the surplus ones
+// are skipped as invalid.
+template <bool kPrefix>
+__device__ __forceinline__ WorkItem decode_item(int item, int nblk_x, int nseg, const int *__restrict__ cu, int q_begin, int q_end,
+                                                const int *seg_prefix) {
     WorkItem w;
-    const int bx = item % nblk_x;
-    const int rest = item / nblk_x;
-    const int seg = rest % nseg;
-    w.head = rest / nseg;
+    int bx, seg;
+    if constexpr (kPrefix) {
+        const int per_head = seg_prefix[nseg];
+        w.head = item / per_head;
+        const int r = item - w.head * per_head;
+        int lo = 0, hi = nseg;  // last segment whose prefix is <= r
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (seg_prefix[mid] <= r) lo = mid;
+            else hi = mid;
+        }
+        seg = lo;
+        bx = r - seg_prefix[seg];
+    } else {
+        bx = item % nblk_x;
+        const int rest = item / nblk_x;
+        seg = rest % nseg;
+        w.head = rest / nseg;
+    }
     w.s0 = cu[seg];
     w.s1 = cu[seg + 1];
     const int seg_len = w.s1 - w.s0;
@@ -338,7 +371,8 @@ __device__ __forceinline__ WorkItem decode_item(int item, int nblk_x, int nseg, 
 // runs the same item loop on its own; the barriers' phases simply keep counting across items, so the producer
 // streams the next item's K/V (and, once the last Q K^T of the current item has completed, its Q) while the softmax
 // groups are still finishing the current one.
-template <bool kBF16>
+// kPrefix selects the work list at compile time, so that launches with few segments carry none of the table's code.
+template <bool kBF16, bool kPrefix>
 __global__ void __launch_bounds__(kThreads, 1)
 attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                       const __grid_constant__ CUtensorMap map_v, const void *__restrict__ bias_ptr,
@@ -356,7 +390,43 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         const int m = min(max(*max_len_dev, 0), q_end - q_begin);
         nblk_x = min(nblk_x, (m + kTiles * kBlockM - 1) / (kTiles * kBlockM));
     }
-    const int total_items = nblk_x * nseg * num_heads;
+    // Work list.  Launches with many segments (kMinPrefixSegs .. kMaxPrefixSegs): every CTA scans the segments' query-block
+    // counts into shared memory and the items are exactly the blocks that exist.  With ragged segments a list with one
+    // slot per (segment, maximal block index) unbalances the round-robin: the empty slots all carry the same block index,
+    // and 148 CTAs is a multiple of 4 blocks per segment (0.81 balance on 64 ragged segments, 0.95 without the empty
+    // slots).  Launches with few segments keep the slot list: the scan would cost them ~1.5 us for nothing.
+    constexpr bool use_prefix = kPrefix;  // the host instantiates and sizes the shared memory by the segment count
+    int *prefix_table = reinterpret_cast<int *>(reinterpret_cast<uint8_t *>(&sh) + sizeof(SharedStorage));
+    if constexpr (kPrefix) {
+        constexpr int kPer = kMaxPrefixSegs / kThreads;  // consecutive segments per thread
+        int local[kPer], sum = 0;
+#pragma unroll
+        for (int i = 0; i < kPer; ++i) {
+            const int sg = threadIdx.x * kPer + i;
+            local[i] = sg < nseg ? segment_blocks(sg, cu, q_begin, q_end) : 0;
+            sum += local[i];
+        }
+        int incl = sum;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int v = __shfl_up_sync(0xffffffffu, incl, d);
+            if ((threadIdx.x & 31) >= d) incl += v;
+        }
+        if ((threadIdx.x & 31) == 31) sh.scan_warp[threadIdx.x >> 5] = incl;
+        __syncthreads();
+        int before = incl - sum;
+        for (int wq = 0; wq < (int)(threadIdx.x >> 5); ++wq) before += sh.scan_warp[wq];
+#pragma unroll
+        for (int i = 0; i < kPer; ++i) {
+            const int sg = threadIdx.x * kPer + i;
+            if (sg <= nseg) prefix_table[sg] = before;
+            before += local[i];
+        }
+        if (nseg == kMaxPrefixSegs && threadIdx.x == kThreads - 1) prefix_table[kMaxPrefixSegs] = before;  // the grand total
+        __syncthreads();
+    }
+    const int *seg_prefix = use_prefix ? prefix_table : nullptr;
+    const int total_items = use_prefix ? prefix_table[nseg] * num_heads : nblk_x * nseg * num_heads;
     const bool has_bias = bias_ptr != nullptr;
     // a key tile needs the bias step when there is a bias, or when it is the partial last tile (masking)
     auto uses_slab = [&](const WorkItem &w, int j) { return has_bias || (w.ragged_tail && j == w.n_kv - 1); };
@@ -421,7 +491,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         int slab_it = 0;       // bias slab ring position, advanced once per key tile that uses the bias step
         int q_uses[kTiles] = {};  // items that loaded query tile t so far (buffer and phase of q_full / q_empty)
         for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
-            const WorkItem w = decode_item(item, nblk_x, nseg, cu, q_begin, q_end);
+            const WorkItem w = decode_item<kPrefix>(item, nblk_x, nseg, cu, q_begin, q_end, seg_prefix);
             if (!w.valid) continue;
             if (lane == 0) {
                 for (int t = 0; t < w.n_mt && ok; ++t) {
@@ -497,7 +567,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         int step = 0;      // key tiles this query tile has processed so far (phase of s_full / s_empty / p_full / o_done)
         int q_uses = 0;    // items in which this query tile was active (phase of q_full / q_empty)
         for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
-            const WorkItem w = decode_item(item, nblk_x, nseg, cu, q_begin, q_end);
+            const WorkItem w = decode_item<kPrefix>(item, nblk_x, nseg, cu, q_begin, q_end, seg_prefix);
             if (!w.valid) continue;
             if (t >= w.n_mt) {
                 // This query tile is empty in this item: release the K/V and slab slots without using them, so that the
@@ -592,7 +662,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         bool ok = true;
         int step = 0;  // key tiles processed so far by this query tile: phase of s_full / s_empty / p_full / o_done
         for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
-            const WorkItem w = decode_item(item, nblk_x, nseg, cu, q_begin, q_end);
+            const WorkItem w = decode_item<kPrefix>(item, nblk_x, nseg, cu, q_begin, q_end, seg_prefix);
             if (!w.valid || t >= w.n_mt) continue;
             const int n_kv = w.n_kv;
             const int row = w.q_row0 + t * kBlockM + r;
@@ -790,7 +860,7 @@ bool attn_sm100_supported(const AttnArgs &a) {
 // The shared-memory opt-in of a kernel is set once per device and dtype (not again on every launch, so that
 // launches stay cheap and legal inside a stream capture).  Returns whether it was already done and marks it done.
 static bool attr_done(int which) {
-    static bool done[64][2];
+    static bool done[64][4];
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
     const bool was = done[dev][which];
@@ -806,7 +876,8 @@ int attn_sm100_launch(const AttnArgs &a, cudaStream_t stream) {
     if ((rc = make_map(&mq, a.q, a.dtype, a.q_end - a.q_begin, a.H, a.q_rs, kBlockM)) != COME_OK) return rc;
     if ((rc = make_map(&mk, a.k, a.dtype, a.total, a.H, a.k_rs, kBlockN)) != COME_OK) return rc;
     if ((rc = make_map(&mv, a.v, a.dtype, a.total, a.H, a.v_rs, kBlockN)) != COME_OK) return rc;
-    const size_t smem = sizeof(SharedStorage) + 1024;
+    const bool with_table = a.nseg >= kMinPrefixSegs && a.nseg <= kMaxPrefixSegs;
+    const size_t smem = sizeof(SharedStorage) + 1024 + (with_table ? kPrefixTableBytes : 0);
     const int64_t q_rows = a.q_end - a.q_begin;
     const int64_t span = a.max_seqlen < q_rows ? a.max_seqlen : q_rows;  // most query rows any segment can own here
     const int nblk_x = (int)((span + kTiles * kBlockM - 1) / (kTiles * kBlockM));
@@ -820,15 +891,22 @@ int attn_sm100_launch(const AttnArgs &a, cudaStream_t stream) {
     const unsigned grid = (unsigned)(items < sms ? items : sms);  // persistent: one CTA per SM walks the items
     const float scale_log2 = a.scale * kLog2e;
     const float inv_scale = 1.0f / a.scale;
+#define COME_ATTN_LAUNCH(BF16, PREFIX, SLOT)                                                                                   \
+    do {                                                                                                                       \
+        if (!attr_done(SLOT))                                                                                                  \
+            COME_CUDA(cudaFuncSetAttribute(attn_fwd_sm100_kernel<BF16, PREFIX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+        attn_fwd_sm100_kernel<BF16, PREFIX><<<grid, kThreads, smem, stream>>>(mq, mk, mv, a.bias, a.cu, scale_log2, inv_scale, a.out, \
+                                                                              a.o_rs, a.lse, (int)a.q_begin, (int)a.q_end, nblk_x,   \
+                                                                              a.nseg, a.H, a.max_seqlen_dev, status);               \
+    } while (0)
     if (a.dtype == COME_BF16) {
-        if (!attr_done(0)) COME_CUDA(cudaFuncSetAttribute(attn_fwd_sm100_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        attn_fwd_sm100_kernel<true><<<grid, kThreads, smem, stream>>>(mq, mk, mv, a.bias, a.cu, scale_log2, inv_scale, a.out, a.o_rs, a.lse,
-                                                                     (int)a.q_begin, (int)a.q_end, nblk_x, a.nseg, a.H, a.max_seqlen_dev, status);
+        if (with_table) COME_ATTN_LAUNCH(true, true, 0);
+        else COME_ATTN_LAUNCH(true, false, 1);
     } else {
-        if (!attr_done(1)) COME_CUDA(cudaFuncSetAttribute(attn_fwd_sm100_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        attn_fwd_sm100_kernel<false><<<grid, kThreads, smem, stream>>>(mq, mk, mv, a.bias, a.cu, scale_log2, inv_scale, a.out, a.o_rs, a.lse,
-                                                                      (int)a.q_begin, (int)a.q_end, nblk_x, a.nseg, a.H, a.max_seqlen_dev, status);
+        if (with_table) COME_ATTN_LAUNCH(false, true, 2);
+        else COME_ATTN_LAUNCH(false, false, 3);
     }
+#undef COME_ATTN_LAUNCH
     return check_launch("come_attn_varlen_fwd (tcgen05 kernel)");
 }
 

@@ -281,3 +281,24 @@ def test_device_side_longest_segment(backend):
         loose, lse1 = fa.varlen_fwd_rows(q, k, v, cu, P, bias, D ** -0.5, 0, max_seqlen_dev=md)
         assert torch.equal(exact, loose) and torch.equal(lse0, lse1)
     _check_status()
+
+
+@pytest.mark.parametrize("nseg", [15, 16, 1500, 2048, 2100])
+def test_many_short_segments(backend, nseg):
+    """Thousands of short segments: around the size of the kernel's shared-memory table of per-segment query-block counts
+    (2048 entries; more segments fall back to a work list with empty slots).  Checked against the CUDA-core kernel."""
+    from come_b200 import flash_attn as api, flash_attn_fwd_cuda as fa
+    rng = np.random.default_rng(nseg)
+    lengths = rng.integers(1, 40, size=nseg)
+    lengths[7] = 700  # one long segment among them
+    P, H, D = int(lengths.sum()), 2, 64
+    qkv = to_dev(gi.round_kind(rng.standard_normal((P, 3, H, D), dtype=np.float32), "bf16"), "bf16")
+    bias = to_dev(gi.round_kind(np.log(np.where(rng.random(P) < 0.3, 9.0, 1.0)).astype(np.float32), "bf16"), "bf16")
+    cu = torch.tensor(np.concatenate([[0], np.cumsum(lengths)]), dtype=torch.int32, device="cuda")
+    outs = []
+    for which in (fa.BACKEND_TCGEN05, fa.BACKEND_CUDA_CORE):
+        backend(which)
+        outs.append(api.flash_attn_varlen_qkvpacked_func_w_perkey_bias(qkv, cu, int(lengths.max()), perkey_bias=bias,
+                                                                       softmax_scale=D ** -0.5).float())
+    assert (outs[0] - outs[1]).abs().max().item() <= 2e-2
+    _check_status()
