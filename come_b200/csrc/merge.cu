@@ -247,8 +247,11 @@ template <typename V> __device__ __forceinline__ void st_stream(V *p, const V &v
 template <> __device__ __forceinline__ void st_stream<__half>(__half *p, const __half &v) { *p = v; }
 template <> __device__ __forceinline__ void st_stream<__nv_bfloat16>(__nv_bfloat16 *p, const __nv_bfloat16 &v) { *p = v; }
 
-template <typename T, int VEC>
-__global__ void __launch_bounds__(kMergeThreads, 2)
+// INFLIGHT = rows whose loads are issued before the first add / store, MINB = CTAs per SM the registers are held to:
+// (9, 2) streams best on launches of several waves; (5, 4) doubles the resident CTAs, which is what a launch of one or
+// two waves (a single 8-frame scene) needs to hide its three dependent memory round trips per unit.
+template <typename T, int VEC, int INFLIGHT, int MINB>
+__global__ void __launch_bounds__(kMergeThreads, MINB)
 merge_kernel(const T *__restrict__ tokens, const uint8_t *__restrict__ mask, const int *__restrict__ group_prefix,
              const int *__restrict__ offsets, FrameLayout L, int frames, int64_t C, int groups, T *__restrict__ out) {
     using IO = VecIO<T, VEC>;
@@ -300,13 +303,13 @@ merge_kernel(const T *__restrict__ tokens, const uint8_t *__restrict__ mask, con
                 float acc[VEC];
 #pragma unroll
                 for (int i = 0; i < VEC; ++i) acc[i] = 0.0f;
-                for (int g0 = 0; g0 < rows; g0 += kMaxInFlight) {
-                    V buf[kMaxInFlight];
+                for (int g0 = 0; g0 < rows; g0 += INFLIGHT) {
+                    V buf[INFLIGHT];
 #pragma unroll
-                    for (int i = 0; i < kMaxInFlight; ++i)
+                    for (int i = 0; i < INFLIGHT; ++i)
                         if (g0 + i < rows) buf[i] = ld_stream(src_base + (int64_t)s_src[g0 + i] * Cv + v);
 #pragma unroll
-                    for (int i = 0; i < kMaxInFlight; ++i)
+                    for (int i = 0; i < INFLIGHT; ++i)
                         if (g0 + i < rows) {
                             float f[VEC];
                             IO::unpack(buf[i], f);
@@ -318,13 +321,13 @@ merge_kernel(const T *__restrict__ tokens, const uint8_t *__restrict__ mask, con
                 for (int j = 0; j < VEC; ++j) acc[j] = __fdiv_rn(acc[j], fG);
                 st_stream(dst_base + v, IO::pack(acc));
             } else {
-                for (int g0 = 0; g0 < rows; g0 += kMaxInFlight) {
-                    V buf[kMaxInFlight];
+                for (int g0 = 0; g0 < rows; g0 += INFLIGHT) {
+                    V buf[INFLIGHT];
 #pragma unroll
-                    for (int i = 0; i < kMaxInFlight; ++i)
+                    for (int i = 0; i < INFLIGHT; ++i)
                         if (g0 + i < rows) buf[i] = ld_stream(src_base + (int64_t)s_src[g0 + i] * Cv + v);
 #pragma unroll
-                    for (int i = 0; i < kMaxInFlight; ++i)
+                    for (int i = 0; i < INFLIGHT; ++i)
                         if (g0 + i < rows) st_stream(dst_base + (int64_t)(g0 + i) * Cv + v, buf[i]);
                 }
             }
@@ -776,10 +779,13 @@ static int launch_merge(const void *tokens, int64_t frames, int64_t C, const Fra
     const size_t smem = (size_t)L.G * sizeof(int) * (size_t)groups;
     const int64_t n_ctas = (n_units + groups - 1) / groups;
     const unsigned grid = (unsigned)(n_ctas < max_blocks ? n_ctas : max_blocks);
-    if (vec_ok)
-        merge_kernel<T, VEC><<<grid, kMergeThreads, smem, st>>>((const T *)tokens, mask, gp, off, L, (int)frames, C, groups, (T *)out);
+    const bool small = n_ctas <= (int64_t)sm_count() * 6;  // at most ~three waves of the two-CTA-per-SM variant
+    if (vec_ok && small)
+        merge_kernel<T, VEC, 5, 4><<<grid, kMergeThreads, smem, st>>>((const T *)tokens, mask, gp, off, L, (int)frames, C, groups, (T *)out);
+    else if (vec_ok)
+        merge_kernel<T, VEC, kMaxInFlight, 2><<<grid, kMergeThreads, smem, st>>>((const T *)tokens, mask, gp, off, L, (int)frames, C, groups, (T *)out);
     else
-        merge_kernel<T, 1><<<grid, kMergeThreads, smem, st>>>((const T *)tokens, mask, gp, off, L, (int)frames, C, groups, (T *)out);
+        merge_kernel<T, 1, kMaxInFlight, 2><<<grid, kMergeThreads, smem, st>>>((const T *)tokens, mask, gp, off, L, (int)frames, C, groups, (T *)out);
     return check_launch("come_merge");
 }
 
