@@ -2,6 +2,8 @@
 //
 // All three data kernels are HBM-bandwidth bound.  They move 16-byte vectors, keep a full window's loads
 // in flight per thread before the first add, and run as persistent grid-stride loops sized to the SM count.
+#include <type_traits>
+
 #include "come_internal.cuh"
 
 #include <mutex>
@@ -409,7 +411,9 @@ template <typename T> struct PairIO16 {
 template <> struct PairIO<__half, 8> : PairIO16<__half> {};
 template <> struct PairIO<__nv_bfloat16, 8> : PairIO16<__nv_bfloat16> {};
 
-template <typename T, int VEC>
+// TPG > 0: the thread-group size is a compile-time constant equal to the vectors per row (every thread has a column,
+// shared-memory offsets are constants, the warp loops unroll); TPG == 0: any row width, sizes at run time.
+template <typename T, int VEC, int TPG>
 __global__ void __launch_bounds__(kMergeThreads, 2)
 merge_layernorm_kernel(const T *__restrict__ tokens, const uint8_t *__restrict__ mask, const int *__restrict__ group_prefix,
                        const int *__restrict__ offsets, FrameLayout L, int frames, int Cv, int groups,
@@ -420,7 +424,8 @@ merge_layernorm_kernel(const T *__restrict__ tokens, const uint8_t *__restrict__
     constexpr int NP = VEC / 2;  // float32 pairs per thread and row
     extern __shared__ int s_ln_raw[];
     const int G = L.G;
-    const int tpg = kMergeThreads / groups, warps_pg = tpg / 32;
+    const int tpg = TPG > 0 ? TPG : kMergeThreads / groups, warps_pg = tpg / 32;
+    if (TPG > 0) groups = kMergeThreads / TPG;
     const int grp = threadIdx.x / tpg, tig = threadIdx.x - grp * tpg;
     const int wig = tig >> 5, lane = tig & 31;
     // shared memory: [groups][G] source tokens | [groups][kLnMaxRows][tpg] partial sums | [groups][kLnMaxRows] row statistic
@@ -430,7 +435,7 @@ merge_layernorm_kernel(const T *__restrict__ tokens, const uint8_t *__restrict__
     const int prefix_units = (L.prefix + G - 1) / G;
     const int units_per_frame = prefix_units + L.M;
     const int n_units = frames * units_per_frame;
-    const bool has_col = tig < Cv;  // a group may be wider than a row (rows of 96, 192, ... vectors)
+    const bool has_col = TPG > 0 || tig < Cv;  // a run-time group may be wider than a row (rows of 96, 192, ... vectors)
     const float fC = (float)(Cv * VEC), fG = (float)G;
     V g_raw = V(), b_raw = V();  // this thread's gamma / beta, kept packed (unpacked where used: registers are tight)
     if (has_col) {
@@ -440,7 +445,7 @@ merge_layernorm_kernel(const T *__restrict__ tokens, const uint8_t *__restrict__
 
     // Row totals of one partial sum per thread, for all rows of the unit at once; `finish` turns a row's total into the
     // statistic every thread then reads back (mean after the first pass, 1/sqrt(var + eps) after the second).
-    auto row_statistics = [&](float (&part)[kLnMaxRows], int rows, auto finish) {
+    auto row_statistics = [&](float (&part)[kLnMaxRows], const int rows, auto finish) {
         group_barrier(groups, grp, tpg);  // the previous use of s_part / s_stat is over
 #pragma unroll
         for (int r = 0; r < kLnMaxRows; ++r)
@@ -482,12 +487,18 @@ merge_layernorm_kernel(const T *__restrict__ tokens, const uint8_t *__restrict__
         group_barrier(groups, grp, tpg);  // previous unit's s_src no longer read
         for (int r = tig; r < rows; r += tpg) s_src[r] = L.src_token(r0 + r);
         group_barrier(groups, grp, tpg);
+        // A unit of kLnMaxRows rows (every 3 x 3 window) takes the copy of the body below in which the row count is a
+        // constant: no per-row predicates are left.
+        const bool full = (rows == kLnMaxRows);
+        auto process = [&](auto full_tag) {
+        constexpr bool FULL = decltype(full_tag)::value;
+        const int n_rows = FULL ? kLnMaxRows : rows;
         const V *src_base = reinterpret_cast<const V *>(tokens) + (int64_t)bfr * L.N * Cv;
 
         V raw[kLnMaxRows];
 #pragma unroll
         for (int r = 0; r < kLnMaxRows; ++r)
-            if (r < rows && has_col) raw[r] = ld_stream(src_base + (int64_t)s_src[r] * Cv + tig);
+            if ((FULL || r < n_rows) && has_col) raw[r] = ld_stream(src_base + (int64_t)s_src[r] * Cv + tig);
         f32x2_t x[kLnMaxRows][NP];
         float stat[kLnMaxRows];
 #pragma unroll
@@ -495,7 +506,7 @@ merge_layernorm_kernel(const T *__restrict__ tokens, const uint8_t *__restrict__
             stat[r] = 0.0f;
 #pragma unroll
             for (int j = 0; j < NP; ++j) x[r][j] = 0ull;
-            if (r < rows && has_col) {
+            if ((FULL || r < n_rows) && has_col) {
                 PIO::unpack(raw[r], x[r]);
                 f32x2_t acc = x[r][0];
 #pragma unroll
@@ -505,12 +516,12 @@ merge_layernorm_kernel(const T *__restrict__ tokens, const uint8_t *__restrict__
                 stat[r] = __fadd_rn(even, odd);
             }
         }
-        row_statistics(stat, rows, [&](float total) { return __fdiv_rn(total, fC); });
+        row_statistics(stat, n_rows, [&](float total) { return __fdiv_rn(total, fC); });
 #pragma unroll
         for (int r = 0; r < kLnMaxRows; ++r) {
             const f32x2_t neg_mean = pack_f32x2(-stat[r], -stat[r]);
             stat[r] = 0.0f;
-            if (r < rows && has_col) {
+            if ((FULL || r < n_rows) && has_col) {
 #pragma unroll
                 for (int j = 0; j < NP; ++j) x[r][j] = add_f32x2(x[r][j], neg_mean);  // x - mean
                 f32x2_t acc = mul_f32x2(x[r][0], x[r][0]);
@@ -521,7 +532,7 @@ merge_layernorm_kernel(const T *__restrict__ tokens, const uint8_t *__restrict__
                 stat[r] = __fadd_rn(even, odd);
             }
         }
-        row_statistics(stat, rows, [&](float total) { return __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(total, fC), eps))); });
+        row_statistics(stat, n_rows, [&](float total) { return __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(total, fC), eps))); });
         if (has_col) {
             f32x2_t acc[NP], g2[NP], b2[NP];
             PIO::unpack(g_raw, g2);
@@ -531,7 +542,7 @@ merge_layernorm_kernel(const T *__restrict__ tokens, const uint8_t *__restrict__
             V *dst_base = reinterpret_cast<V *>(out) + (int64_t)dst * Cv + tig;
 #pragma unroll
             for (int r = 0; r < kLnMaxRows; ++r) {
-                if (r < rows) {
+                if ((FULL || r < n_rows)) {
                     const f32x2_t rstd2 = pack_f32x2(stat[r], stat[r]);
 #pragma unroll
                     for (int j = 0; j < NP; ++j) x[r][j] = fma_f32x2(g2[j], mul_f32x2(rstd2, x[r][j]), b2[j]);
@@ -554,6 +565,9 @@ merge_layernorm_kernel(const T *__restrict__ tokens, const uint8_t *__restrict__
                 st_stream(dst_base, PIO::pack(acc));
             }
         }
+        };  // process
+        if (full) process(std::true_type{});
+        else process(std::false_type{});
     }
 }
 
@@ -578,8 +592,18 @@ static int launch_merge_layernorm(const void *tokens, int64_t frames, int64_t C,
     const size_t smem = (size_t)groups * L.G * sizeof(int) + (size_t)groups * kLnMaxRows * (tpg + 1) * sizeof(float);
     const int64_t n_ctas = (n_units + groups - 1) / groups;
     const int64_t max_blocks = (int64_t)sm_count() * 8;
-    merge_layernorm_kernel<T, VEC><<<(unsigned)(n_ctas < max_blocks ? n_ctas : max_blocks), kMergeThreads, smem, st>>>(
-        (const T *)tokens, mask, gp, off, L, (int)frames, Cv, groups, (const T *)gamma, (const T *)beta, eps, (T *)out);
+    const unsigned grid = (unsigned)(n_ctas < max_blocks ? n_ctas : max_blocks);
+#define COME_LN_LAUNCH(TPG)                                                                                            \
+    merge_layernorm_kernel<T, VEC, TPG><<<grid, kMergeThreads, smem, st>>>((const T *)tokens, mask, gp, off, L, (int)frames, Cv, \
+                                                                           groups, (const T *)gamma, (const T *)beta, eps, (T *)out)
+    switch (Cv == tpg ? tpg : 0) {  // rows that fill their thread group exactly take a compile-time group size
+        case 32: COME_LN_LAUNCH(32); break;
+        case 64: COME_LN_LAUNCH(64); break;
+        case 128: COME_LN_LAUNCH(128); break;
+        case 256: COME_LN_LAUNCH(256); break;
+        default: COME_LN_LAUNCH(0); break;
+    }
+#undef COME_LN_LAUNCH
     return check_launch("come_merge_layernorm");
 }
 
