@@ -10,7 +10,13 @@ Host side in Python/PyTorch (device memory, streams), compute in ``libcome_b200.
 * :mod:`come_b200.qkv`                  -- ``prepare_packed_self_attention_qkv`` (q/k LayerNorm + 2-D RoPE + bias in
   one kernel), ``RotaryPositionEmbedding2D``
 * :mod:`come_b200.token_merger`         -- ``JaggedTokens``, ``func_token_merge[_2d]``, ``func_token_split``,
-  ``MergePlan``, ``select_windows`` and the 2-D merger class
+  ``MergePlan`` (merge, split, ``merge_layernorm``, ``split_add``, ``split_concat``, ``positions``), ``select_windows``
+  and the 2-D merger class
+* :mod:`come_b200.bias_attention`       -- ``JaggedAttention_w_Bias`` (the reference's attention wrapper module)
+* :mod:`come_b200.direct`               -- ``DirectAttention``: the per-layer replacement of ``block.attn.forward``
+* :mod:`come_b200.chain`                -- the standalone operator chain of a scene, also sharded by frame over GPUs
+* :mod:`come_b200.static_scene`         -- the chain as one CUDA graph with no device-to-host read
+* :mod:`come_b200.dist`                 -- frame / row sharding helpers and the K/V row all-gather
 """
 from . import _lib  # noqa: F401
 
