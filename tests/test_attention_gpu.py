@@ -302,3 +302,20 @@ def test_many_short_segments(backend, nseg):
                                                                        softmax_scale=D ** -0.5).float())
     assert (outs[0] - outs[1]).abs().max().item() <= 2e-2
     _check_status()
+
+
+def test_very_long_segment(backend):
+    """One segment of 24,700 tokens (193 query-tile rows, 386 key steps per work item), checked against the CUDA-core kernel
+    (the CPU oracle would take minutes)."""
+    from come_b200 import flash_attn as api, flash_attn_fwd_cuda as fa
+    rng = np.random.default_rng(99)
+    P, H, D = 24700, 1, 64
+    qkv = to_dev(gi.round_kind(rng.standard_normal((P, 3, H, D), dtype=np.float32), "bf16"), "bf16")
+    bias = to_dev(gi.round_kind(np.log(np.where(rng.random(P) < 0.3, 9.0, 1.0)).astype(np.float32), "bf16"), "bf16")
+    cu = torch.tensor([0, P], dtype=torch.int32, device="cuda")
+    outs = []
+    for which in (fa.BACKEND_TCGEN05, fa.BACKEND_CUDA_CORE):
+        backend(which)
+        outs.append(api.flash_attn_varlen_qkvpacked_func_w_perkey_bias(qkv, cu, P, perkey_bias=bias, softmax_scale=D ** -0.5).float())
+    assert (outs[0] - outs[1]).abs().max().item() <= 2e-2
+    _check_status()
