@@ -763,18 +763,27 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 tc_wait_ld();  // O is in registers: the next item's first P V may overwrite the accumulator
                 if (row < w.q_hi) {
                     const float inv = 1.0f / l;
-                    uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<T *>(out_ptr) + (int64_t)(row - q_begin) * o_rs + (int64_t)w.head * kHeadDim);
+                    // The row's 64 outputs as 32 packed words, written with 32-byte stores where the address allows it:
+                    // a warp's store then covers whole 32-byte sectors of its 32 rows instead of halves.
+                    uint32_t pk[32];
 #pragma unroll
                     for (int c = 0; c < 2; ++c)
 #pragma unroll
-                        for (int i = 0; i < 32; i += 8) {
-                            uint4 v;
-                            v.x = pack2<kBF16>(__uint_as_float(o[c][i + 0]) * inv, __uint_as_float(o[c][i + 1]) * inv);
-                            v.y = pack2<kBF16>(__uint_as_float(o[c][i + 2]) * inv, __uint_as_float(o[c][i + 3]) * inv);
-                            v.z = pack2<kBF16>(__uint_as_float(o[c][i + 4]) * inv, __uint_as_float(o[c][i + 5]) * inv);
-                            v.w = pack2<kBF16>(__uint_as_float(o[c][i + 6]) * inv, __uint_as_float(o[c][i + 7]) * inv);
-                            dst[(c * 32 + i) / 8] = v;
-                        }
+                        for (int i = 0; i < 32; i += 2)
+                            pk[c * 16 + i / 2] = pack2<kBF16>(__uint_as_float(o[c][i]) * inv, __uint_as_float(o[c][i + 1]) * inv);
+                    T *dst_row = reinterpret_cast<T *>(out_ptr) + (int64_t)(row - q_begin) * o_rs + (int64_t)w.head * kHeadDim;
+                    if ((reinterpret_cast<uintptr_t>(dst_row) & 31) == 0) {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 8)
+                            asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst_row + 2 * i),
+                                         "r"(pk[i]), "r"(pk[i + 1]), "r"(pk[i + 2]), "r"(pk[i + 3]), "r"(pk[i + 4]), "r"(pk[i + 5]),
+                                         "r"(pk[i + 6]), "r"(pk[i + 7])
+                                         : "memory");
+                    } else {
+                        uint4 *dst = reinterpret_cast<uint4 *>(dst_row);
+#pragma unroll
+                        for (int i = 0; i < 32; i += 4) dst[i / 4] = make_uint4(pk[i], pk[i + 1], pk[i + 2], pk[i + 3]);
+                    }
                     if (lse) lse[(int64_t)w.head * (q_end - q_begin) + (row - q_begin)] = (m_ref + log2f(l)) * kLn2;
                 }
             }
