@@ -6,7 +6,7 @@ attention layers, 3x3 windows at a 50 % merge ratio), plus merge/unmerge GB/s an
     python bench.py --gpus N --steps K --warmup W            # this library (one scene per rank and step)
     python bench.py --impl reference ...                     # the CPU restatement of the reference path (rank 0)
 
-Prints ONE JSON line (rank 0).  Inputs are synthetic (seeded); see DESIGN.md for what each field means.
+Prints ONE JSON line (rank 0).  Inputs are synthetic (seeded).
 """
 from __future__ import annotations
 
@@ -362,7 +362,7 @@ def run_gpu(args):
             "roofline": {"kernel": "attn_fwd_sm100_kernel (48 launches/scene: 24 frame + 24 global)", "bound": "tensor",
                          "achieved": achieved, "peak": pk["tflops"], "unit": "TFLOP/s", "frac": achieved / pk["tflops"],
                          "peak_source": pk["source"] + " burst cuBLAS bf16",
-                         "traffic": 39.9e6, "traffic_note": "DRAM bytes of one global-layer launch (ncu, profiles/attn_fwd_sm100_global_1seg6456.md): qkv read once",
+                         "traffic": 39.9e6, "traffic_note": "DRAM bytes of one global-layer launch (ncu capture of the 6456-token shape): qkv read once",
                          "timing": "CUDA events around a graph of one scene's 24 frame / 24 global launches (device time)",
                          "frame_tflops": (n_f * flops_frame / args.steps) / (family_ms["frame"] * 1e-3) / 1e12,
                          "global_tflops": (n_g * flops_global / args.steps) / (family_ms["global"] * 1e-3) / 1e12,

@@ -76,7 +76,7 @@ def import_file(root: str, rel: str, name: str):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of a checkout of the reference project")
     args = ap.parse_args()
     import torch
 
