@@ -733,9 +733,79 @@ def run_only(args):
     print(json.dumps(out))
 
 
+def run_aggregator(args):
+    """End-to-end driver in the form of the reference's benchmark (``src/bench.py:13-46``): the unmerged model and the
+    accelerated model are run over the same synthetic scenes inside ``Timer.range`` and the timer's table is printed.
+    The model is the alternating-attention stack of a VGGT-1B-shaped aggregator with seeded random weights in bf16
+    (24 frame + 24 global blocks, width 1024, 16 heads, q/k norm, rotary embedding, LayerScale, MLP ratio 4); the patch
+    encoder and the heads are outside.  A scene's work in the accelerated arm: confidence head (seeded 2-layer MLP) ->
+    window selection -> merge plan -> merge -> 48 blocks on packed tokens -> unmerge of the retained layers.
+    GEMMs are PyTorch's (cuBLAS); everything else on the packed tokens is this library's kernels."""
+    import torch
+    from come_b200 import _lib
+    from come_b200.fused import CapturedForward, FusedAggregator
+    from come_b200.timer import Timer
+    from come_b200.token_merger import MergePlan, select_windows
+    from come_b200.vggt_arch import AggregatorCore
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    S = 8 if args.frames == 100 else args.frames  # 100 is the flag's default, meant for the merge kernels
+    core = AggregatorCore(depth=args.depth).to(dev).bfloat16()
+    model = FusedAggregator(core)
+    captured = CapturedForward(model)
+    torch.manual_seed(0)
+    head = torch.nn.Sequential(torch.nn.Linear(CH, 128), torch.nn.GELU(), torch.nn.Linear(128, 1)).to(dev).bfloat16().eval()
+    layout = _lib.Layout.two_d(START, GRID, GRID, WIN, WIN)
+    g = torch.Generator(device=dev).manual_seed(0)
+    scenes = [torch.randn((1, S, N_TOK, CH), device=dev, generator=g).bfloat16() for _ in range(args.iters)]
+
+    def plan_of(tokens):
+        conf = head(tokens[:, :, START:, :]).reshape(1, S * GRID * GRID)
+        mask = select_windows(conf, 1, S, GRID, GRID, WIN, WIN, 0.5, "pairwise-rank", "batch")
+        return MergePlan(mask, layout)
+
+    arms = {
+        "Reference Model": lambda t: model.forward_unmerged(t),
+        "Accelerated Model": lambda t: model(t, plan_of(t)),
+        "Accelerated Model (CUDA graph)": lambda t: captured(t, plan_of(t)),
+    }
+    Timer.reset()
+    with torch.no_grad():
+        for name, fn in arms.items():
+            Timer.activate(False)
+            for t in scenes[:2]:  # warm-up (and graph capture) outside the table
+                fn(t)
+            torch.cuda.synchronize()
+            Timer.activate()
+            for t in scenes:
+                with Timer.range(name):
+                    fn(t)
+            torch.cuda.synchronize()
+        packed = [plan_of(t).total for t in scenes]
+    Timer.activate(False)
+    entries = {e.name: e for e in Timer.results()}
+    print(Timer.report(), file=sys.stderr)
+    assert _lib.device_status(clear=False) == 0
+    P = float(np.mean(packed))
+    blocks = 2 * args.depth
+    gemm = lambda rows: blocks * 2.0 * rows * CH * CH * 12  # qkv 3, proj 1, fc1 4, fc2 4  # noqa: E731
+    attn = lambda rows: args.depth * 4.0 * HDIM * HEADS * (rows * rows + S * (rows / S) ** 2)  # noqa: E731
+    print(json.dumps({
+        "only": "aggregator", "frames": S, "blocks": blocks, "scenes": len(scenes), "dtype": "bf16",
+        "packed_tokens_mean": P, "dense_tokens": S * N_TOK, "graphs_captured": len(captured._graphs),
+        "ms_per_scene": {k: round(v.P50, 3) for k, v in entries.items()},
+        "speedup_vs_unmerged": {k: round(entries["Reference Model"].P50 / v.P50, 3) for k, v in entries.items()},
+        "tflop_per_scene": {"unmerged": round((gemm(S * N_TOK) + attn(S * N_TOK)) / 1e12, 2),
+                            "merged": round((gemm(P) + attn(P)) / 1e12, 2)},
+        "timer": "CUDA events around each scene (src/utility/timer.py form), median over the scenes",
+    }))
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--only", choices=["attn", "merge", "unmerge", "merge_ln", "unmerge_res", "prepare", "direct"], help="run one kernel family on one size and exit")
+    ap.add_argument("--only", choices=["attn", "merge", "unmerge", "merge_ln", "unmerge_res", "prepare", "direct", "aggregator"],
+                    help="run one kernel family on one size and exit; aggregator = the end-to-end model driver")
+    ap.add_argument("--depth", type=int, default=24, help="--only aggregator: frame/global block pairs")
     ap.add_argument("--frames", type=int, default=100, help="--only merge/unmerge: frames")
     ap.add_argument("--dtype", default="f32", choices=["f32", "bf16"], help="--only merge/unmerge: element type")
     ap.add_argument("--tokens", type=int, default=6384, help="--only attn with --segments 1: segment length")
@@ -753,7 +823,9 @@ def main():
     ap.add_argument("--no-micro", action="store_true", help="skip the kernel-level sweep")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     args = ap.parse_args()
-    if args.only:
+    if args.only == "aggregator":
+        run_aggregator(args)
+    elif args.only:
         run_only(args)
     elif args.impl == "reference":
         run_reference(args)

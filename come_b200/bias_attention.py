@@ -12,20 +12,18 @@ from typing import Literal, Optional
 
 import torch
 
-from .flash_attn import flash_attn_varlen_qkvpacked_func_w_perkey_bias, infer_flash_attn_varlen_max_seqlen
+from .flash_attn import (flash_attn_varlen_qkvpacked_func, flash_attn_varlen_qkvpacked_func_w_perkey_bias,
+                         infer_flash_attn_varlen_max_seqlen)
 from .qkv import RotaryPositionEmbedding2D, prepare_packed_self_attention_qkv
 from .token_merger import JaggedTokens
 
 __all__ = ["JaggedAttention_w_Bias"]
 
 
-class JaggedAttention_w_Bias(torch.nn.Module):
-    """``original_attn`` is an attention block with the attributes the reference's wrapper reads: ``qkv`` and
-    ``proj`` (``nn.Linear``), ``q_norm`` / ``k_norm`` (``nn.LayerNorm(head_dim)`` or ``nn.Identity``), ``rope``
-    (an object with ``base_frequency``, or None), ``num_heads``, ``head_dim``, ``scale``."""
+class _JaggedAttentionBase(torch.nn.Module):
+    """What the two attention wrappers share: dtype handling, the rotary tables and the forward pass."""
 
-    def __init__(self, original_attn: torch.nn.Module, run_dtype: Literal["bf16", "fp16"],
-                 backend: Literal["flash_attn", "flex_attn"] = "flash_attn"):
+    def __init__(self, original_attn: torch.nn.Module, run_dtype: str):
         super().__init__()
         if run_dtype == "bf16":
             self.run_dtype = torch.bfloat16
@@ -33,9 +31,6 @@ class JaggedAttention_w_Bias(torch.nn.Module):
             self.run_dtype = torch.float16
         else:
             raise ValueError(f"FlashAttention can only run on fp16/bf16, get {run_dtype}")
-        if backend != "flash_attn":
-            raise NotImplementedError(f"backend {backend!r}: only the CUDA attention kernel is provided")
-        self.backend = backend
         self.attn = original_attn.to(dtype=self.run_dtype)
         rope = getattr(original_attn, "rope", None)
         if rope is None or isinstance(rope, RotaryPositionEmbedding2D):
@@ -43,24 +38,51 @@ class JaggedAttention_w_Bias(torch.nn.Module):
         else:  # the model's own rotary module: only its base frequency matters
             self._rope = RotaryPositionEmbedding2D(frequency=float(rope.base_frequency))
 
-    def forward(self, x: JaggedTokens, pos: Optional[torch.Tensor] = None, *, max_seqlen: Optional[int] = None) -> JaggedTokens:
-        """``max_seqlen`` (keyword, optional) is the longest segment if the caller already knows it, e.g. from a
-        merge plan; without it the reference's device-to-host read is performed."""
+    def _forward(self, x: JaggedTokens, pos: Optional[torch.Tensor], max_seqlen: Optional[int], use_bias: bool) -> JaggedTokens:
         attn = self.attn
         if self.training and getattr(getattr(attn, "attn_drop", None), "p", 0.0) > 0.0:
             raise NotImplementedError("attention dropout is not supported (inference path)")
         tokens = x.tokens.squeeze(0)  # (P, C)
         P, C = tokens.shape
         qkv = attn.qkv(tokens).reshape(P, 3, attn.num_heads, attn.head_dim)
-        qkv, perkey_bias = prepare_packed_self_attention_qkv(qkv, attn.q_norm, attn.k_norm, self._rope, pos, self.run_dtype,
-                                                             weight=x.weight)
+        prepared = prepare_packed_self_attention_qkv(qkv, attn.q_norm, attn.k_norm, self._rope, pos, self.run_dtype,
+                                                     weight=x.weight if use_bias else None)
         cu_seqlens = x.offset.to(torch.int32)
+        max_seqlen_dev = None
+        if max_seqlen is None:
+            max_seqlen, max_seqlen_dev = x.max_seqlen, x.max_seqlen_dev
         if max_seqlen is None:
             max_seqlen = infer_flash_attn_varlen_max_seqlen(cu_seqlens)
-        out = flash_attn_varlen_qkvpacked_func_w_perkey_bias(qkv, cu_seqlens, max_seqlen, perkey_bias=perkey_bias,
-                                                             dropout_p=0.0, softmax_scale=attn.scale)
+        if use_bias:
+            qkv, perkey_bias = prepared
+            out = flash_attn_varlen_qkvpacked_func_w_perkey_bias(qkv, cu_seqlens, max_seqlen, perkey_bias=perkey_bias,
+                                                                 dropout_p=0.0, softmax_scale=attn.scale,
+                                                                 max_seqlen_dev=max_seqlen_dev)
+        else:
+            out = flash_attn_varlen_qkvpacked_func(prepared, cu_seqlens, max_seqlen, dropout_p=0.0,
+                                                   softmax_scale=attn.scale, max_seqlen_dev=max_seqlen_dev)
         out = attn.proj(out.reshape(P, C))
         proj_drop = getattr(attn, "proj_drop", None)
         if proj_drop is not None:
             out = proj_drop(out)
-        return JaggedTokens(tokens=out.unsqueeze(0), weight=x.weight, offset=x.offset)
+        return JaggedTokens(tokens=out.unsqueeze(0), weight=x.weight, offset=x.offset, max_seqlen=x.max_seqlen,
+                            max_seqlen_dev=x.max_seqlen_dev)
+
+
+class JaggedAttention_w_Bias(_JaggedAttentionBase):
+    """``original_attn`` is an attention block with the attributes the reference's wrapper reads: ``qkv`` and
+    ``proj`` (``nn.Linear``), ``q_norm`` / ``k_norm`` (``nn.LayerNorm(head_dim)`` or ``nn.Identity``), ``rope``
+    (an object with ``base_frequency``, or None), ``num_heads``, ``head_dim``, ``scale``."""
+
+    def __init__(self, original_attn: torch.nn.Module, run_dtype: Literal["bf16", "fp16"],
+                 backend: Literal["flash_attn", "flex_attn"] = "flash_attn"):
+        super().__init__(original_attn, run_dtype)
+        if backend != "flash_attn":
+            raise NotImplementedError(f"backend {backend!r}: only the CUDA attention kernel is provided")
+        self.backend = backend
+
+    def forward(self, x: JaggedTokens, pos: Optional[torch.Tensor] = None, *, max_seqlen: Optional[int] = None) -> JaggedTokens:
+        """``max_seqlen`` (keyword, optional) is the longest segment if the caller already knows it, e.g. from a
+        merge plan; ``x.max_seqlen`` / ``x.max_seqlen_dev`` serve the same purpose; without any of them the
+        reference's device-to-host read is performed."""
+        return self._forward(x, pos, max_seqlen, use_bias=True)

@@ -43,7 +43,7 @@ def _pad_head(t: torch.Tensor, head_size_og: int) -> torch.Tensor:
 class _VarlenQKVPacked(torch.autograd.Function):
     @staticmethod
     def forward(ctx, qkv, cu_seqlens, max_seqlen, perkey_bias, has_bias, dropout_p, softmax_scale, causal,
-                window_size, softcap, alibi_slopes, return_softmax):
+                window_size, softcap, alibi_slopes, return_softmax, max_seqlen_dev=None):
         if softmax_scale is None:
             softmax_scale = qkv.shape[-1] ** (-0.5)
         q, k, v = qkv[:, 0].detach(), qkv[:, 1].detach(), qkv[:, 2].detach()
@@ -54,10 +54,11 @@ class _VarlenQKVPacked(torch.autograd.Function):
         if has_bias:
             out_padded, softmax_lse, S_dmask, rng_state = _C.varlen_fwd_w_perkey_bias(
                 q, k, v, None, cu_seqlens, cu_seqlens, None, None, None, alibi_slopes, perkey_bias,
-                max_seqlen, max_seqlen, *common)
+                max_seqlen, max_seqlen, *common, max_seqlen_dev=max_seqlen_dev)
         else:
             out_padded, softmax_lse, S_dmask, rng_state = _C.varlen_fwd(
-                q, k, v, None, cu_seqlens, cu_seqlens, None, None, None, alibi_slopes, max_seqlen, max_seqlen, *common)
+                q, k, v, None, cu_seqlens, cu_seqlens, None, None, None, alibi_slopes, max_seqlen, max_seqlen, *common,
+                max_seqlen_dev=max_seqlen_dev)
         ctx.mark_non_differentiable(softmax_lse, S_dmask, rng_state)
         out = out_padded[..., :head_size_og]
         return out if not return_softmax else (out, softmax_lse, S_dmask)
@@ -80,6 +81,8 @@ def flash_attn_varlen_qkvpacked_func(
     alibi_slopes: Optional[torch.Tensor] = None,
     deterministic: bool = False,
     return_attn_probs: bool = False,
+    *,
+    max_seqlen_dev: Optional[torch.Tensor] = None,
 ):
     """Attention over packed variable-length segments.
 
@@ -90,12 +93,14 @@ def flash_attn_varlen_qkvpacked_func(
         softmax_scale: defaults to ``1 / sqrt(headdim)``.
         dropout_p, causal, window_size, softcap, alibi_slopes: accepted for signature compatibility; any value
             other than the inference defaults raises ``NotImplementedError``.
+        max_seqlen_dev (keyword only, not in the reference): one-element int32 device tensor with the exact longest
+            segment when ``max_seqlen`` is only an upper bound (launches of fixed shape, e.g. inside a CUDA graph).
     Return:
         out ``(total, nheads, headdim)``; with ``return_attn_probs`` also ``softmax_lse (nheads, total)`` and an
         empty probabilities tensor.
     """
     return _VarlenQKVPacked.apply(qkv, cu_seqlens, max_seqlen, None, False, dropout_p, softmax_scale, causal,
-                                  tuple(window_size), softcap, alibi_slopes, return_attn_probs)
+                                  tuple(window_size), softcap, alibi_slopes, return_attn_probs, max_seqlen_dev)
 
 
 def flash_attn_varlen_qkvpacked_func_w_perkey_bias(
@@ -111,6 +116,8 @@ def flash_attn_varlen_qkvpacked_func_w_perkey_bias(
     alibi_slopes: Optional[torch.Tensor] = None,
     deterministic: bool = False,
     return_attn_probs: bool = False,
+    *,
+    max_seqlen_dev: Optional[torch.Tensor] = None,
 ):
     """Same as :func:`flash_attn_varlen_qkvpacked_func` with an additive per-key bias on the scaled scores:
     ``softmax(Q @ K.T * scale + perkey_bias[kv_idx]) @ V``.
@@ -119,4 +126,4 @@ def flash_attn_varlen_qkvpacked_func_w_perkey_bias(
         perkey_bias: ``(total,)`` tensor, same dtype as ``qkv``, indexed like the packed K/V rows.
     """
     return _VarlenQKVPacked.apply(qkv, cu_seqlens, max_seqlen, perkey_bias, True, dropout_p, softmax_scale, causal,
-                                  tuple(window_size), softcap, alibi_slopes, return_attn_probs)
+                                  tuple(window_size), softcap, alibi_slopes, return_attn_probs, max_seqlen_dev)

@@ -32,7 +32,7 @@ def _unsupported(what: str):
 
 def _impl(q, k, v, out_, cu_seqlens_q, cu_seqlens_k, seqused_k, leftpad_k, block_table, alibi_slopes, perkey_bias,
           max_seqlen_q, max_seqlen_k, p_dropout, softmax_scale, zero_tensors, is_causal, window_size_left,
-          window_size_right, softcap, return_softmax, gen_):
+          window_size_right, softcap, return_softmax, gen_, max_seqlen_dev=None):
     if q.dtype not in (torch.float16, torch.bfloat16):
         raise RuntimeError("FlashAttention only support fp16 and bf16 data type")
     if k.dtype != q.dtype:
@@ -132,30 +132,41 @@ def _impl(q, k, v, out_, cu_seqlens_q, cu_seqlens_k, seqused_k, leftpad_k, block
 
     q, k, v = head_packed(q), head_packed(k), head_packed(v)
     with torch.cuda.device(q.device):
-        _lib.check(_lib.lib().come_attn_varlen_fwd(
-            ptr(q), ptr(k), ptr(v), dtype_code(q.dtype), total_q, num_heads, head_size, q.stride(0), k.stride(0),
-            v.stride(0), ptr(bias), ptr(cu_seqlens_q), batch_size, int(max_seqlen_q), float(softmax_scale), ptr(out),
-            out.stride(0), ptr(softmax_lse), _backend, stream_ptr(q.device)))
+        if max_seqlen_dev is None:
+            _lib.check(_lib.lib().come_attn_varlen_fwd(
+                ptr(q), ptr(k), ptr(v), dtype_code(q.dtype), total_q, num_heads, head_size, q.stride(0), k.stride(0),
+                v.stride(0), ptr(bias), ptr(cu_seqlens_q), batch_size, int(max_seqlen_q), float(softmax_scale),
+                ptr(out), out.stride(0), ptr(softmax_lse), _backend, stream_ptr(q.device)))
+        else:  # max_seqlen_q is an upper bound; the exact longest segment is read on the device
+            if max_seqlen_dev.dtype != torch.int32 or not max_seqlen_dev.is_cuda or max_seqlen_dev.numel() != 1:
+                raise RuntimeError("max_seqlen_dev must be a one-element int32 CUDA tensor")
+            _lib.check(_lib.lib().come_attn_varlen_fwd_rows(
+                ptr(q), ptr(k), ptr(v), dtype_code(q.dtype), total_q, 0, total_q, num_heads, head_size, q.stride(0),
+                k.stride(0), v.stride(0), ptr(bias), ptr(cu_seqlens_q), batch_size, int(max_seqlen_q),
+                ptr(max_seqlen_dev), float(softmax_scale), ptr(out), out.stride(0), ptr(softmax_lse), _backend,
+                stream_ptr(q.device)))
     return [out, softmax_lse, p, rng_state]
 
 
 def varlen_fwd(q, k, v, out_, cu_seqlens_q, cu_seqlens_k, seqused_k, leftpad_k, block_table, alibi_slopes,
                max_seqlen_q, max_seqlen_k, p_dropout, softmax_scale, zero_tensors, is_causal, window_size_left,
-               window_size_right, softcap, return_softmax, gen_):
-    """Forward pass (variable length); see ``flash_api.cpp:538-567``."""
+               window_size_right, softcap, return_softmax, gen_, *, max_seqlen_dev=None):
+    """Forward pass (variable length); see ``flash_api.cpp:538-567``.  ``max_seqlen_dev`` (keyword, not in the
+    reference): exact longest segment as a one-element int32 device tensor when ``max_seqlen_q`` is only a bound."""
     return _impl(q, k, v, out_, cu_seqlens_q, cu_seqlens_k, seqused_k, leftpad_k, block_table, alibi_slopes, None,
                  max_seqlen_q, max_seqlen_k, p_dropout, softmax_scale, zero_tensors, is_causal, window_size_left,
-                 window_size_right, softcap, return_softmax, gen_)
+                 window_size_right, softcap, return_softmax, gen_, max_seqlen_dev)
 
 
 def varlen_fwd_w_perkey_bias(q, k, v, out_, cu_seqlens_q, cu_seqlens_k, seqused_k, leftpad_k, block_table,
                              alibi_slopes, perkey_bias, max_seqlen_q, max_seqlen_k, p_dropout, softmax_scale,
                              zero_tensors, is_causal, window_size_left, window_size_right, softcap, return_softmax,
-                             gen_):
-    """Forward pass (variable length) with a per-key additive bias; see ``flash_api.cpp:570-599``."""
+                             gen_, *, max_seqlen_dev=None):
+    """Forward pass (variable length) with a per-key additive bias; see ``flash_api.cpp:570-599``.
+    ``max_seqlen_dev`` as in :func:`varlen_fwd`."""
     return _impl(q, k, v, out_, cu_seqlens_q, cu_seqlens_k, seqused_k, leftpad_k, block_table, alibi_slopes,
                  perkey_bias, max_seqlen_q, max_seqlen_k, p_dropout, softmax_scale, zero_tensors, is_causal,
-                 window_size_left, window_size_right, softcap, return_softmax, gen_)
+                 window_size_left, window_size_right, softcap, return_softmax, gen_, max_seqlen_dev)
 
 
 def varlen_fwd_rows(q_rows, k, v, cu_seqlens, max_seqlen, perkey_bias, softmax_scale, row_begin, out_=None,

@@ -1,0 +1,193 @@
+"""The merged ("fused") forward pass of the alternating-attention aggregator, mirroring the forward the reference
+patches into ``Aggregator`` (``src/accelerate/vggt/fused.py:95-167``): tokens are merged ONCE after the encoder, all
+frame and global blocks run on the packed tokens, and only the retained layers are unmerged for the heads.
+
+Against the reference's closure:
+
+* the merge context is a :class:`~come_b200.token_merger.MergePlan` (one device-to-host read per scene); the packed
+  positions come from the plan (``come_packed_positions``) instead of a second merge of a bfloat16 position tensor
+  (``fused.py:113-129``);
+* a retained layer is unmerged straight into its half of the concatenated ``[B, S, N, 2C]`` tensor
+  (``come_unmerge_strided``) instead of two splits and a ``torch.cat`` (``fused.py:157-167``);
+* every attention call gets the longest segment from the plan, so the block loop has no device-to-host read and can
+  be captured in a CUDA graph (:class:`CapturedForward`), one graph per packed length.
+
+The encoder, the heads and the confidence predictor are not part of this module: it starts from the dense tokens
+``[B, S, N, C]`` the aggregator assembles (``fused.py:103-126``) and a merge mask.
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from .block import JaggedBlock, JaggedBlock_w_Bias
+from .token_merger import JaggedTokens, MergePlan
+
+__all__ = ["FusedAggregator", "CapturedForward", "fused_accelerate"]
+
+
+class FusedAggregator(torch.nn.Module):
+    """``aggregator`` provides ``frame_blocks``, ``global_blocks``, ``aa_order``, ``aa_block_size``, ``aa_block_num``,
+    ``retain_layers`` (None = all) and ``patch_start_idx`` (``src/thirdparty/vggt/models/aggregator.py:76-131``)."""
+
+    def __init__(self, aggregator: torch.nn.Module, use_attn_bias_correction: bool = True, attn_dtype: str = "bf16"):
+        super().__init__()
+        block_fn = JaggedBlock_w_Bias if use_attn_bias_correction else JaggedBlock
+        self.aggregator = aggregator
+        self.frame_blocks = torch.nn.ModuleList([block_fn(b, attn_dtype) for b in aggregator.frame_blocks])
+        self.global_blocks = torch.nn.ModuleList([block_fn(b, attn_dtype) for b in aggregator.global_blocks])
+        # the same blocks without the count bias, for tokens that were never merged
+        self.plain_frame_blocks = torch.nn.ModuleList([JaggedBlock(b, attn_dtype) for b in aggregator.frame_blocks])
+        self.plain_global_blocks = torch.nn.ModuleList([JaggedBlock(b, attn_dtype) for b in aggregator.global_blocks])
+        self.aa_order = list(aggregator.aa_order)
+        self.aa_block_size = int(aggregator.aa_block_size)
+        self.aa_block_num = int(aggregator.aa_block_num)
+        self.retain_layers = aggregator.retain_layers
+        self.patch_start_idx = int(aggregator.patch_start_idx)
+
+    # ------------------------------------------------------------------------------------------------------
+    def _run(self, x: JaggedTokens, pos: torch.Tensor, frame_view, global_view, frame_blocks, global_blocks, unmerge):
+        """The alternating loop (``fused.py:137-169``).  ``frame_view`` / ``global_view`` re-segment a JaggedTokens,
+        ``unmerge(frame_tokens, global_tokens)`` produces a retained layer's output."""
+        block_idx = frame_idx = globe_idx = 0
+        output: Dict[int, torch.Tensor] = {}
+        for _ in range(self.aa_block_num):
+            frame_intermediate, globe_intermediate = [], []
+            for attn_type in self.aa_order:
+                if attn_type == "frame":
+                    x = frame_view(x)
+                    for _ in range(self.aa_block_size):
+                        x = frame_blocks[frame_idx](x, pos=pos)
+                        frame_intermediate.append(x)
+                        frame_idx += 1
+                elif attn_type == "global":
+                    x = global_view(x)
+                    for _ in range(self.aa_block_size):
+                        x = global_blocks[globe_idx](x, pos=pos)
+                        globe_intermediate.append(x)
+                        globe_idx += 1
+                else:
+                    raise ValueError(f"Unknown attention type: {attn_type}")
+            for i in range(self.aa_block_size):
+                if self.retain_layers is None or block_idx in self.retain_layers:
+                    output[block_idx] = unmerge(frame_intermediate[i].tokens.squeeze(0),
+                                                globe_intermediate[i].tokens.squeeze(0))
+                block_idx += 1
+        return output
+
+    def forward(self, tokens: torch.Tensor, plan: MergePlan, static_shapes: bool = False
+                ) -> Tuple[Dict[int, torch.Tensor], int]:
+        """``tokens [B, S, N, C]`` dense; ``plan`` the merge plan of its ``B*S`` frames.  Returns the retained layers
+        ``{block index: [B, S, N, 2C]}`` (frame and global tokens side by side) and ``patch_start_idx``.
+
+        With ``static_shapes`` nothing launched depends on the segment lengths inside ``plan`` -- launches are sized
+        for the unmerged lengths and read the real ones on the device -- so the same launch sequence serves every
+        plan with the same packed length: the form a CUDA graph captures."""
+        B, S, N, C = tokens.shape
+        if plan.frames != B * S or plan.tokens_per_frame != N:
+            raise ValueError(f"plan covers {plan.frames} frames of {plan.tokens_per_frame} tokens, tokens are {tuple(tokens.shape)}")
+        merged = plan.merge(tokens.reshape(B * S, N, C))
+        pos = plan.positions()
+        frame_offset = plan.offset
+        global_offset = plan.offset[::S].contiguous()
+        if static_shapes:
+            frame_max, frame_max_dev = N, plan.seg_max
+            global_max = S * N
+            global_max_dev = (global_offset[1:] - global_offset[:-1]).max().to(torch.int32).reshape(1)
+        else:
+            frame_max, frame_max_dev = plan.max_seqlen, None
+            global_max, global_max_dev = (plan.total, None) if B == 1 else (None, None)
+
+        def frame_view(x: JaggedTokens) -> JaggedTokens:
+            return JaggedTokens(x.tokens, x.weight, frame_offset, frame_max, frame_max_dev)
+
+        def global_view(x: JaggedTokens) -> JaggedTokens:
+            return JaggedTokens(x.tokens, x.weight, global_offset, global_max, global_max_dev)
+
+        def unmerge(frame_tokens: torch.Tensor, global_tokens: torch.Tensor) -> torch.Tensor:
+            return plan.split_concat(frame_tokens, global_tokens).view(B, S, N, 2 * C)
+
+        x = JaggedTokens(tokens=merged.unsqueeze(0), weight=plan.weight, offset=frame_offset)
+        output = self._run(x, pos, frame_view, global_view, self.frame_blocks, self.global_blocks, unmerge)
+        return output, self.patch_start_idx
+
+    def forward_unmerged(self, tokens: torch.Tensor, pos: Optional[torch.Tensor] = None
+                         ) -> Tuple[Dict[int, torch.Tensor], int]:
+        """The same stack on the dense tokens, nothing merged and no count bias: the model the accelerated one is
+        compared with.  ``pos [B*S*N, 2]`` int64 (y, x); by default specials at (0, 0) and patch (y, x) at
+        (y + 1, x + 1) on a square grid (``src/thirdparty/vggt/models/aggregator.py:217-229``)."""
+        B, S, N, C = tokens.shape
+        dev = tokens.device
+        if pos is None:
+            side = int(round((N - self.patch_start_idx) ** 0.5))
+            if side * side != N - self.patch_start_idx:
+                raise ValueError("pass pos for a patch grid that is not square")
+            yy, xx = torch.meshgrid(torch.arange(1, side + 1, device=dev), torch.arange(1, side + 1, device=dev), indexing="ij")
+            frame_pos = torch.cat([torch.zeros(self.patch_start_idx, 2, dtype=torch.int64, device=dev),
+                                   torch.stack([yy.reshape(-1), xx.reshape(-1)], dim=-1)], dim=0)
+            pos = frame_pos.repeat(B * S, 1)
+        frame_offset = torch.arange(0, B * S * N + 1, N, device=dev, dtype=torch.int64)
+        global_offset = frame_offset[::S].contiguous()
+        weight = torch.ones(B * S * N, dtype=torch.float32, device=dev)
+
+        def frame_view(x: JaggedTokens) -> JaggedTokens:
+            return JaggedTokens(x.tokens, x.weight, frame_offset, N)
+
+        def global_view(x: JaggedTokens) -> JaggedTokens:
+            return JaggedTokens(x.tokens, x.weight, global_offset, S * N)
+
+        def unmerge(frame_tokens: torch.Tensor, global_tokens: torch.Tensor) -> torch.Tensor:
+            return torch.cat((frame_tokens, global_tokens), dim=-1).view(B, S, N, 2 * C)
+
+        x = JaggedTokens(tokens=tokens.reshape(1, B * S * N, C), weight=weight, offset=frame_offset)
+        output = self._run(x, pos, frame_view, global_view, self.plain_frame_blocks, self.plain_global_blocks, unmerge)
+        return output, self.patch_start_idx
+
+
+def fused_accelerate(aggregator: torch.nn.Module, use_attn_bias_correction: bool = True) -> FusedAggregator:
+    """Counterpart of the reference's ``fused_accelerate(model, token_merger, encoder_layer, use_attn_bias_correction)``
+    (``fused.py:18-21``) for the aggregator alone: wraps its blocks, bf16 attention as in ``fused.py:78,91,94``."""
+    return FusedAggregator(aggregator, use_attn_bias_correction=use_attn_bias_correction, attn_dtype="bf16")
+
+
+class CapturedForward:
+    """Replays :meth:`FusedAggregator.forward` from CUDA graphs, one per (input shape, packed length).
+
+    Per scene: the plan is built eagerly (two small kernels and its one host read, which yields the packed length and
+    picks the graph), copied into the static plan the graph was captured with, the tokens are copied into the static
+    input, and the graph is replayed.  The returned tensors are the graph's static outputs: valid until the next call
+    with the same packed length.
+    """
+
+    def __init__(self, model: FusedAggregator, warmup: int = 2):
+        self.model, self.warmup = model, int(warmup)
+        self._graphs: Dict[tuple, tuple] = {}
+
+    def __call__(self, tokens: torch.Tensor, plan: MergePlan) -> Tuple[Dict[int, torch.Tensor], int]:
+        key = (tuple(tokens.shape), tokens.dtype, plan.total)
+        entry = self._graphs.get(key)
+        if entry is None:
+            entry = self._capture(tokens, plan)
+            self._graphs[key] = entry
+        graph, static_tokens, static_plan, output = entry
+        static_tokens.copy_(tokens)
+        static_plan.load(plan, keep_derived=True)
+        graph.replay()
+        return output, self.model.patch_start_idx
+
+    @torch.no_grad()
+    def _capture(self, tokens: torch.Tensor, plan: MergePlan):
+        static_tokens = tokens.clone()
+        static_plan = MergePlan(plan.mask.clone(), plan.layout)
+        side = torch.cuda.Stream(device=tokens.device)
+        side.wait_stream(torch.cuda.current_stream(tokens.device))
+        with torch.cuda.stream(side):  # warm-up outside the capture: lazy initialisations, cuBLAS workspaces
+            for _ in range(self.warmup):
+                self.model(static_tokens, static_plan, static_shapes=True)
+        torch.cuda.current_stream(tokens.device).wait_stream(side)
+        static_plan._positions = None  # recomputed inside the graph, into memory the graph owns
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            output, _ = self.model(static_tokens, static_plan, static_shapes=True)
+        return graph, static_tokens, static_plan, output

@@ -35,13 +35,21 @@ __all__ = [
 @dataclass
 class JaggedTokens:
     """Packed variable-length tokens: ``tokens [1, P, C]``, ``weight [P]`` (tokens represented by each row),
-    ``offset [M+1]`` int64 segment boundaries."""
+    ``offset [M+1]`` int64 segment boundaries.
+
+    Two optional fields, absent from the reference's container, let a caller that already knows the longest segment
+    spare the attention modules their device-to-host read (``flash_attn/__init__.py:33``): ``max_seqlen`` (an upper
+    bound on the host) and ``max_seqlen_dev`` (the exact value as a one-element int32 device tensor; it lets a launch
+    sized for the bound skip the query blocks no segment reaches).  Both are None unless set."""
     tokens: torch.Tensor
     weight: torch.Tensor
     offset: torch.Tensor
+    max_seqlen: Optional[int] = None
+    max_seqlen_dev: Optional[torch.Tensor] = None
 
     def apply(self, func: Callable[[torch.Tensor], torch.Tensor]) -> "JaggedTokens":
-        return JaggedTokens(tokens=func(self.tokens), weight=self.weight, offset=self.offset)
+        return JaggedTokens(tokens=func(self.tokens), weight=self.weight, offset=self.offset,
+                            max_seqlen=self.max_seqlen, max_seqlen_dev=self.max_seqlen_dev)
 
     def add_suffix(self, suffix: torch.Tensor) -> "JaggedTokens":
         """Append ``T`` dense tokens (weight 1) to each of the ``M`` segments; ``suffix`` is ``(M, T, C)``."""
@@ -155,6 +163,7 @@ class MergePlan:
         self._mask_u8 = self.mask.view(torch.uint8)
         self.group_prefix, self.offsets_i32, self.rev_id, weight_full, seg_max = co_me_cuext.merge_plan_raw(
             self._mask_u8, layout, self.tokens_per_frame)
+        self.seg_max = seg_max  # [1] int32 on the device: the longest frame after merging
         if self.frames > 0:
             host = torch.stack([self.offsets_i32[-1], seg_max[0]]).tolist()  # the single synchronising read
             self.total, self.max_seqlen = int(host[0]), int(host[1])
@@ -164,6 +173,20 @@ class MergePlan:
         self.offset = self.offsets_i32.long()
         self._bias = {}
         self._positions = None
+
+    def load(self, other: "MergePlan", keep_derived: bool = False) -> None:
+        """Overwrite this plan's device tensors with ``other``'s, keeping their addresses (a captured CUDA graph that
+        reads this plan then sees the new scene).  Both plans must pack to the same number of rows.  The cached derived
+        tensors (positions, bias) are dropped unless ``keep_derived``: a captured graph that recomputes them in place
+        on every replay keeps them."""
+        if (other.frames, other.tokens_per_frame, other.total) != (self.frames, self.tokens_per_frame, self.total):
+            raise ValueError(f"plans differ in shape: {other.frames} frames / {other.total} rows against "
+                             f"{self.frames} / {self.total}")
+        for name in ("mask", "group_prefix", "offsets_i32", "rev_id", "weight", "offset", "seg_max"):
+            getattr(self, name).copy_(getattr(other, name))
+        self.max_seqlen = other.max_seqlen
+        if not keep_derived:
+            self._bias, self._positions = {}, None
 
     # -- derived, cached ---------------------------------------------------------------------------------
     def perkey_bias(self, dtype: torch.dtype) -> torch.Tensor:

@@ -34,6 +34,9 @@ __all__ = [
     "rope_2d",
     "qkv_prepare",
     "packed_positions",
+    "gelu_erf",
+    "jagged_block",
+    "fused_aggregator",
 ]
 
 
@@ -543,3 +546,102 @@ def packed_positions(mask: np.ndarray, start_index: int, H: int, W: int, gh: int
     pos = np.broadcast_to(p, (B,) + p.shape)
     merged, _off, _rev, _w = token_merge_2d_ragged(_round_like(pos, "bf16"), start_index, gh, gw, H, W, mask)
     return np.trunc(_round_like(merged, "bf16")).astype(np.int64)
+
+
+# --------------------------------------------------------------------------------------------------------
+# transformer block over packed tokens and the merged forward pass of the alternating-attention aggregator
+# --------------------------------------------------------------------------------------------------------
+def gelu_erf(x: np.ndarray) -> np.ndarray:
+    """``nn.GELU()`` with its default exact form ``0.5 * x * (1 + erf(x / sqrt(2)))`` (the activation of the MLP,
+    ``src/thirdparty/vggt/layers/mlp.py:18,31``), evaluated in float64 and returned as float32."""
+    from math import erf
+    x64 = np.asarray(x, dtype=np.float64)
+    return (0.5 * x64 * (1.0 + np.vectorize(erf, otypes=[np.float64])(x64 / np.sqrt(2.0)))).astype(np.float32)
+
+
+def _layer_norm_f32(x: np.ndarray, gamma: np.ndarray, beta: np.ndarray, eps: float) -> np.ndarray:
+    x64 = np.asarray(x, dtype=np.float64)
+    mean = x64.mean(axis=-1, keepdims=True)
+    var = ((x64 - mean) ** 2).mean(axis=-1, keepdims=True)
+    return ((x64 - mean) / np.sqrt(var + eps) * gamma.astype(np.float64) + beta.astype(np.float64)).astype(np.float32)
+
+
+def jagged_block(x, weight, cu_seqlens, pos, p, num_heads, cos_t, sin_t, use_bias=True):
+    """One transformer block on packed tokens ``x [P, C]``: ``JaggedBlock_w_Bias.forward``
+    (``src/accelerate/vggt/module/block.py:58-81``) around ``JaggedAttention_w_Bias.forward``
+    (``src/accelerate/vggt/module/bias_attention.py:100-137``):
+
+        x = x + ls1 * proj(attention(prepare(qkv(norm1(x))), bias = log(weight)))
+        x = x + ls2 * fc2(gelu(fc1(norm2(x))))
+
+    in float32 throughout (the reference rounds the attention branch to bfloat16; the difference is what the
+    tolerance of a comparison against this function has to cover).  ``p`` maps parameter names to float32 arrays:
+    ``norm1.weight/bias, attn.qkv.weight/bias, attn.q_norm.weight/bias, attn.k_norm.weight/bias, attn.proj.weight/bias,
+    ls1.gamma, norm2.weight/bias, mlp.fc1.weight/bias, mlp.fc2.weight/bias, ls2.gamma`` (the norm and LayerScale
+    entries may be absent), plus ``eps`` values ``norm_eps`` and ``qk_norm_eps``.  ``cos_t`` / ``sin_t`` are the rotary
+    tables of :func:`rope_tables` (None: no rotary embedding); ``use_bias=False`` gives the block without the count
+    bias (``block.py:18-43``).
+    """
+    x = np.asarray(x, dtype=np.float32)
+    P, C = x.shape
+    D = C // num_heads
+    eps = float(p.get("norm_eps", 1e-5))
+    h = _layer_norm_f32(x, p["norm1.weight"], p["norm1.bias"], eps)
+    qkv = (h @ p["attn.qkv.weight"].T + p["attn.qkv.bias"]).astype(np.float32).reshape(P, 3, num_heads, D)
+    has_qk_norm = "attn.q_norm.weight" in p
+    qkv = qkv_prepare(qkv, p.get("attn.q_norm.weight"), p.get("attn.q_norm.bias"), p.get("attn.k_norm.weight"),
+                      p.get("attn.k_norm.bias"), float(p.get("qk_norm_eps", 1e-5)) if has_qk_norm else 0.0,
+                      pos if cos_t is not None else None, cos_t, sin_t, kind="f32")
+    bias = np.log(np.asarray(weight, dtype=np.float32)) if use_bias else None
+    out, _ = attention_bias(qkv[:, 0], qkv[:, 1], qkv[:, 2], bias, cu_seqlens, D ** -0.5)
+    out = (out.reshape(P, C) @ p["attn.proj.weight"].T + p["attn.proj.bias"]).astype(np.float32)
+    x = x + out * p.get("ls1.gamma", np.float32(1.0))
+    h = _layer_norm_f32(x, p["norm2.weight"], p["norm2.bias"], eps)
+    h = gelu_erf(h @ p["mlp.fc1.weight"].T + p["mlp.fc1.bias"])
+    h = (h @ p["mlp.fc2.weight"].T + p["mlp.fc2.bias"]).astype(np.float32)
+    return (x + h * p.get("ls2.gamma", np.float32(1.0))).astype(np.float32)
+
+
+def fused_aggregator(tokens, mask, start_index, H, W, gh, gw, frame_params, global_params, num_heads, retain_layers=None,
+                     aa_order=("frame", "global"), aa_block_size=1, rope_base=100.0, rope_kind="bf16",
+                     use_bias=True):
+    """Merged forward pass of the aggregator (``src/accelerate/vggt/fused.py:95-167``): merge the dense tokens
+    ``[B, S, N, C]`` once, run the alternating frame / global blocks on the packed tokens -- frame blocks attend inside
+    a frame, global blocks inside a scene (``fused.py:141-149``) -- and unmerge the retained layers to
+    ``[B, S, N, 2C]`` (frame tokens and global tokens side by side, ``fused.py:157-167``).  ``frame_params`` /
+    ``global_params`` are lists of the dictionaries :func:`jagged_block` takes; ``rope_base <= 0`` disables the
+    rotary embedding; its tables are built in ``rope_kind`` as the model does in its run dtype.
+    Returns ``{block index: array}``."""
+    tokens = np.asarray(tokens, dtype=np.float32)
+    B, S, N, C = tokens.shape
+    mask = np.asarray(mask, dtype=bool)
+    x, offsets, rev, weight = token_merge_2d_ragged(tokens.reshape(B * S, N, C), start_index, gh, gw, H, W, mask)
+    pos = packed_positions(mask, start_index, H, W, gh, gw)
+    cos_t = sin_t = None
+    if rope_base > 0:
+        cos_t, sin_t = rope_tables(C // num_heads // 2, int(max(H, W)) + 2, rope_base, rope_kind)
+    frame_cu = np.asarray(offsets, dtype=np.int64)
+    global_cu = frame_cu[::S]
+    depth = len(frame_params)
+    block_idx = frame_idx = globe_idx = 0
+    output = {}
+    for _ in range(depth // aa_block_size):
+        frame_mid, globe_mid = [], []
+        for kind in aa_order:
+            for _ in range(aa_block_size):
+                if kind == "frame":
+                    x = jagged_block(x, weight, frame_cu, pos, frame_params[frame_idx], num_heads, cos_t, sin_t, use_bias)
+                    frame_mid.append(x)
+                    frame_idx += 1
+                elif kind == "global":
+                    x = jagged_block(x, weight, global_cu, pos, global_params[globe_idx], num_heads, cos_t, sin_t, use_bias)
+                    globe_mid.append(x)
+                    globe_idx += 1
+                else:
+                    raise ValueError(f"Unknown attention type: {kind}")
+        for i in range(aa_block_size):
+            if retain_layers is None or block_idx in retain_layers:
+                both = np.concatenate([token_split(frame_mid[i], rev), token_split(globe_mid[i], rev)], axis=-1)
+                output[block_idx] = both.reshape(B, S, N, 2 * C)
+            block_idx += 1
+    return output

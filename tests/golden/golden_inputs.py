@@ -188,3 +188,60 @@ def ln_merge_tolerance(kind: str) -> float:
     """Bound against the reference's CPU run: PyTorch sums the LayerNorm statistics in another order, which moves a
     normalised value by at most one unit in the last place of the element type."""
     return {"bf16": 2.0 ** -7, "f16": 2.0 ** -10, "f32": 4e-6}[kind]
+
+
+# transformer block on unmerged tokens: the reference's own ``Block`` (float32, CPU) pins the block arithmetic of the
+# oracle (norms, qkv order, q/k norm, rotary embedding, attention, projection, LayerScale, MLP with exact GELU)
+BLOCK_CASES = [  # (frames, grid side, start_index, C, heads, mlp_ratio, qk_norm, rope, layer-scale init)
+    (2, 6, 5, 128, 2, 4.0, True, True, 0.5),
+    (3, 5, 1, 64, 1, 2.0, False, True, None),
+    (1, 7, 5, 128, 4, 4.0, True, False, 1.0),
+]
+BLOCK_TOLERANCE = 2e-5  # float32 against float32, different summation orders
+BLOCK_PARAM_NAMES = ("norm1.weight", "norm1.bias", "attn.qkv.weight", "attn.qkv.bias", "attn.q_norm.weight",
+                     "attn.q_norm.bias", "attn.k_norm.weight", "attn.k_norm.bias", "attn.proj.weight", "attn.proj.bias",
+                     "ls1.gamma", "norm2.weight", "norm2.bias", "mlp.fc1.weight", "mlp.fc1.bias", "mlp.fc2.weight",
+                     "mlp.fc2.bias", "ls2.gamma")
+
+
+def block_param_shapes(C: int, heads: int, mlp_ratio: float, qk_norm: bool, ls_init) -> dict:
+    D, hidden = C // heads, int(C * mlp_ratio)
+    shapes = {"norm1.weight": (C,), "norm1.bias": (C,), "attn.qkv.weight": (3 * C, C), "attn.qkv.bias": (3 * C,),
+              "attn.proj.weight": (C, C), "attn.proj.bias": (C,), "norm2.weight": (C,), "norm2.bias": (C,),
+              "mlp.fc1.weight": (hidden, C), "mlp.fc1.bias": (hidden,), "mlp.fc2.weight": (C, hidden), "mlp.fc2.bias": (C,)}
+    if qk_norm:
+        shapes.update({"attn.q_norm.weight": (D,), "attn.q_norm.bias": (D,), "attn.k_norm.weight": (D,), "attn.k_norm.bias": (D,)})
+    if ls_init:
+        shapes.update({"ls1.gamma": (C,), "ls2.gamma": (C,)})
+    return {k: shapes[k] for k in BLOCK_PARAM_NAMES if k in shapes}
+
+
+def block_params(rng, C: int, heads: int, mlp_ratio: float, qk_norm: bool, ls_init, kind: str = "f32") -> dict:
+    """Seeded parameters of one block: weight matrices ~ N(0, 1/fan_in), norm gains around 1, LayerScale around its
+    init value, small biases; rounded to ``kind``."""
+    p = {}
+    for name, shape in block_param_shapes(C, heads, mlp_ratio, qk_norm, ls_init).items():
+        r = rng.standard_normal(shape, dtype=np.float32)
+        if len(shape) == 2:
+            v = r / np.float32(np.sqrt(shape[1]))
+        elif name.endswith("gamma"):
+            v = np.float32(ls_init) * (np.float32(1.0) + np.float32(0.1) * r)
+        elif "norm" in name and name.endswith("weight"):
+            v = np.float32(1.0) + np.float32(0.1) * r
+        else:
+            v = np.float32(0.05) * r
+        p[name] = round_kind(v.astype(np.float32), kind)
+    return p
+
+
+def block_inputs(i: int, case):
+    frames, side, start, C, heads, mlp_ratio, qk_norm, rope, ls_init = case
+    rng = np.random.default_rng(9300 + i)
+    N = start + side * side
+    x = rng.standard_normal((frames, N, C), dtype=np.float32)
+    params = block_params(rng, C, heads, mlp_ratio, qk_norm, ls_init)
+    ys, xs = np.meshgrid(np.arange(side), np.arange(side), indexing="ij")
+    pos = np.zeros((N, 2), np.int64)
+    pos[start:, 0] = ys.reshape(-1) + 1
+    pos[start:, 1] = xs.reshape(-1) + 1
+    return x, params, np.broadcast_to(pos, (frames, N, 2)).copy()

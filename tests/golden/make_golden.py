@@ -29,7 +29,8 @@ from reference_cases import RANDOM_CONFIGS_1D, RANDOM_CONFIGS_2D, ATTENTION_CASE
 from golden_inputs import (  # noqa: E402
     merge1d_inputs, merge2d_inputs, select_inputs, SELECT_CASES, attention_inputs, EXTRA_ATTENTION_CASES,
     cfg1_inputs, summarize_rows, PREPARE_CASES, PREPARE_EPS, PREPARE_MAX_POSITION, prepare_inputs, POSITION_CASES,
-    position_mask, LN_MERGE_CASES, LN_MERGE_EPS, ln_merge_inputs, ln_merge_tolerance,
+    position_mask, LN_MERGE_CASES, LN_MERGE_EPS, ln_merge_inputs, ln_merge_tolerance, BLOCK_CASES, BLOCK_TOLERANCE,
+    block_inputs,
 )
 
 
@@ -261,6 +262,31 @@ def main():
         assert np.allclose(ours, ref, rtol=tol, atol=tol), ("ln+merge", case, np.abs(ours - ref).max())
         store.update({f"l{i}_out_{k}": v for k, v in summarize_rows(ref, 7).items()})
     np.savez_compressed(os.path.join(HERE, "ln_merge.npz"), **store)
+
+    # ---- transformer block on unmerged tokens: the reference model's own Block in float32 -------------------------
+    from src.thirdparty.vggt.layers.block import Block as RefBlock
+    store = {}
+    for i, case in enumerate(BLOCK_CASES):
+        frames, side, start, C, heads, mlp_ratio, qk_norm, use_rope, ls_init = case
+        x, params, pos = block_inputs(i, case)
+        rope = ref_rope.RotaryPositionEmbedding2D(frequency=100.0) if use_rope else None
+        blk = RefBlock(dim=C, num_heads=heads, mlp_ratio=mlp_ratio, init_values=ls_init, qk_norm=qk_norm, rope=rope).eval()
+        state = blk.state_dict()
+        assert set(state) == set(params), (sorted(state), sorted(params))
+        blk.load_state_dict({k: t(v) for k, v in params.items()})
+        with torch.no_grad():
+            ref = blk(t(x), pos=t(pos) if use_rope else None).numpy()
+        N = x.shape[1]
+        cos_t = sin_t = None
+        if use_rope:
+            cos_t, sin_t = orc.rope_tables(C // heads // 2, side + 1, 100.0, "f32")
+        cu = np.arange(frames + 1, dtype=np.int64) * N
+        ours = orc.jagged_block(x.reshape(-1, C), np.ones(frames * N, np.float32), cu, pos.reshape(-1, 2),
+                                dict(params, norm_eps=blk.norm1.eps, qk_norm_eps=1e-5), heads, cos_t, sin_t)
+        assert np.allclose(ours, ref.reshape(-1, C), rtol=BLOCK_TOLERANCE, atol=BLOCK_TOLERANCE), (
+            "block", case, np.abs(ours - ref.reshape(-1, C)).max())
+        store.update({f"b{i}_out_{k}": v for k, v in summarize_rows(ref.reshape(-1, C), 5).items()})
+    np.savez_compressed(os.path.join(HERE, "block.npz"), **store)
 
     # ---- standalone op chain of the headline configuration (8 x 1374 tokens, 37x37 grid, 3x3 windows) ----
     tokens, conf = cfg1_inputs()

@@ -1,0 +1,163 @@
+"""GPU parity of the merged forward pass of the aggregator (blocks over packed tokens, retained layers unmerged)
+against the float32 oracle chain, plus the properties that hold at any size."""
+import numpy as np
+import pytest
+import torch
+
+import oracle.come_oracle as orc
+from tests.golden import golden_inputs as gi
+from tests.gpu_util import to_np
+
+pytestmark = pytest.mark.gpu
+
+
+def _small_model(rng, depth, C, heads, ls_init, dtype):
+    """An AggregatorCore whose parameters are the seeded ones of the golden helpers (rounded to bfloat16, so that the
+    oracle and the device hold the same numbers), plus the per-block parameter dictionaries for the oracle."""
+    from come_b200.vggt_arch import AggregatorCore
+    core = AggregatorCore(embed_dim=C, depth=depth, num_heads=heads, mlp_ratio=2.0, init_values=ls_init,
+                          retain_layers=None, patch_start_idx=5)
+    params = {"frame": [], "global": []}
+    for kind, blocks in (("frame", core.frame_blocks), ("global", core.global_blocks)):
+        for blk in blocks:
+            p = gi.block_params(rng, C, heads, 2.0, True, ls_init, kind="bf16")
+            blk.load_state_dict({k: torch.from_numpy(v) for k, v in p.items()})
+            params[kind].append(dict(p, norm_eps=blk.norm1.eps, qk_norm_eps=blk.attn.q_norm.eps))
+    return core.cuda().to(dtype).eval(), params
+
+
+def _relative_error(a: np.ndarray, b: np.ndarray) -> float:
+    return float(np.linalg.norm(a.astype(np.float64) - b.astype(np.float64)) / np.linalg.norm(b.astype(np.float64)))
+
+
+# bfloat16 activations through `depth` pairs of blocks against float32 arithmetic: every block rounds its branches to
+# 8 bits of mantissa (relative 2^-9 per element); errors of independent roundings add in quadrature.
+FUSED_REL_TOL = 2e-2
+FUSED_ABS_TOL = 0.15  # worst single element, activations of magnitude ~1-4
+
+
+@pytest.mark.parametrize("B,S,side,ratio", [(1, 3, 7, 0.5), (2, 2, 6, 0.5), (1, 2, 7, 0.0), (1, 4, 7, 1.0)])
+def test_fused_forward_against_oracle(B, S, side, ratio):
+    from come_b200 import _lib
+    from come_b200.fused import FusedAggregator
+    from come_b200.token_merger import MergePlan
+    rng = np.random.default_rng(100 + 10 * B + S)
+    C, heads, depth, start = 128, 2, 2, 5
+    N = start + side * side
+    M = (side // 3) ** 2
+    core, params = _small_model(rng, depth, C, heads, 0.5, torch.bfloat16)
+    model = FusedAggregator(core)
+    tokens = gi.round_kind(rng.standard_normal((B, S, N, C), dtype=np.float32), "bf16")
+    mask = rng.random((B * S, M)) < ratio
+    plan = MergePlan(torch.from_numpy(mask).cuda(), _lib.Layout.two_d(start, side, side, 3, 3))
+    with torch.no_grad():
+        out, patch_start = model(torch.from_numpy(tokens).cuda().bfloat16(), plan)
+    assert patch_start == start and sorted(out) == list(range(depth))
+    ref = orc.fused_aggregator(tokens, mask, start, side, side, 3, 3, params["frame"], params["global"], heads)
+    for layer in range(depth):
+        got = to_np(out[layer])
+        assert got.shape == (B, S, N, 2 * C) and out[layer].dtype == torch.bfloat16
+        assert _relative_error(got, ref[layer]) < FUSED_REL_TOL, (layer, _relative_error(got, ref[layer]))
+        assert np.abs(got - ref[layer]).max() < FUSED_ABS_TOL, (layer, np.abs(got - ref[layer]).max())
+
+
+def test_fused_forward_float32_stream():
+    """A float32 model keeps its residual stream, norms and MLP in float32 and only the attention branch in bfloat16,
+    as the reference's block does (the casts around the attention module)."""
+    from come_b200 import _lib
+    from come_b200.fused import FusedAggregator
+    from come_b200.token_merger import MergePlan
+    rng = np.random.default_rng(5)
+    C, heads, depth, start, side, B, S = 128, 2, 1, 5, 6, 1, 2
+    N, M = start + side * side, 4
+    core, params = _small_model(rng, depth, C, heads, 0.5, torch.float32)
+    model = FusedAggregator(core)
+    tokens = rng.standard_normal((B, S, N, C), dtype=np.float32)
+    mask = rng.random((B * S, M)) < 0.5
+    plan = MergePlan(torch.from_numpy(mask).cuda(), _lib.Layout.two_d(start, side, side, 3, 3))
+    old = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        with torch.no_grad():
+            out, _ = model(torch.from_numpy(tokens).cuda(), plan)
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = old
+    ref = orc.fused_aggregator(tokens, mask, start, side, side, 3, 3, params["frame"], params["global"], heads)
+    assert out[0].dtype == torch.float32
+    assert _relative_error(to_np(out[0]), ref[0]) < 6e-3  # one bfloat16 attention branch per block, two blocks
+
+
+def test_nothing_merged_equals_unmerged_model():
+    """With an all-False mask the accelerated model runs the unmerged model's arithmetic on a permuted token order
+    (log 1 = 0 bias); attention is equivariant under the permutation, so the outputs agree to bfloat16 rounding of
+    differently ordered sums."""
+    from come_b200 import _lib
+    from come_b200.fused import FusedAggregator
+    from come_b200.token_merger import MergePlan
+    rng = np.random.default_rng(9)
+    C, heads, depth, start, side, B, S = 128, 2, 2, 5, 7, 1, 3
+    N, M = start + side * side, 4
+    core, _ = _small_model(rng, depth, C, heads, 0.5, torch.bfloat16)
+    model = FusedAggregator(core)
+    tokens = torch.from_numpy(rng.standard_normal((B, S, N, C), dtype=np.float32)).cuda().bfloat16()
+    plan = MergePlan(torch.zeros(B * S, M, dtype=torch.bool, device="cuda"), _lib.Layout.two_d(start, side, side, 3, 3))
+    with torch.no_grad():
+        merged_out, _ = model(tokens, plan)
+        dense_out, _ = model.forward_unmerged(tokens)
+    for layer in range(depth):
+        assert _relative_error(to_np(merged_out[layer]), to_np(dense_out[layer])) < 1e-2
+
+
+@pytest.mark.parametrize("B,S", [(1, 3), (2, 2)])
+def test_captured_forward_replays_new_scenes(B, S):
+    """The CUDA-graph replay gives the eager result bit for bit, also for a second scene with another mask of the same
+    packed length (other segment lengths), and captures a second graph for another packed length."""
+    from come_b200 import _lib
+    from come_b200.fused import CapturedForward, FusedAggregator
+    from come_b200.token_merger import MergePlan
+    rng = np.random.default_rng(11)
+    C, heads, depth, start, side = 128, 2, 2, 5, 7
+    N, M = start + side * side, 4
+    core, _ = _small_model(rng, depth, C, heads, 0.5, torch.bfloat16)
+    model = FusedAggregator(core)
+    captured = CapturedForward(model)
+    layout = _lib.Layout.two_d(start, side, side, 3, 3)
+    masks = []
+    for merged_per_frame in ([2] * (B * S), [1] + [3] + [2] * (B * S - 2), [1] * (B * S)):
+        m = np.zeros((B * S, M), bool)
+        for f, k in enumerate(merged_per_frame):
+            m[f, rng.permutation(M)[:k]] = True
+        masks.append(m)
+    for i, m in enumerate(masks):
+        tokens = torch.from_numpy(rng.standard_normal((B, S, N, C), dtype=np.float32)).cuda().bfloat16()
+        plan = MergePlan(torch.from_numpy(m).cuda(), layout)
+        with torch.no_grad():
+            eager, _ = model(tokens, MergePlan(torch.from_numpy(m).cuda(), layout))
+            replay, _ = captured(tokens, plan)
+        for layer in eager:
+            assert torch.equal(eager[layer], replay[layer]), (i, layer)
+    assert len(captured._graphs) == 2  # the first two masks pack to the same length
+
+
+def test_timer_ranges():
+    from come_b200.timer import Timer
+    Timer.reset()
+    Timer.activate()
+    try:
+        x = torch.ones(1 << 20, device="cuda")
+        for _ in range(3):
+            with Timer.range("fill"):
+                x.mul_(2.0)
+        with Timer.range("other"):
+            x.add_(1.0)
+        entries = {e.name: e for e in Timer.results()}
+        assert entries["fill"].count == 3 and entries["other"].count == 1
+        assert 0.0 < entries["fill"].P50 <= entries["fill"].P90 <= entries["fill"].P99
+        report = Timer.report()
+        assert "Median (ms)" in report and "fill" in report
+    finally:
+        Timer.activate(False)
+        Timer.reset()
+    with Timer.range("inactive"):
+        pass
+    assert Timer.results() == []

@@ -217,3 +217,50 @@ def test_ln_merge_fixture(golden_dir, idx):
     out, _off, _rev, _w = orc.token_merge_2d(orc.layer_norm_rows(x, gamma, beta, gi.LN_MERGE_EPS, kind), start, gh, gw, H, W, mask)
     tol = gi.ln_merge_tolerance(kind)
     gi.check_rows(orc._round_like(out, kind), z, f"l{idx}_out_", rtol=tol, atol=tol)
+
+
+@pytest.mark.parametrize("idx", range(len(gi.BLOCK_CASES)))
+def test_block_fixture(golden_dir, idx):
+    """One transformer block on unmerged tokens against the reference model's own Block (float32, CPU)."""
+    z = _load(golden_dir, "block.npz")
+    case = gi.BLOCK_CASES[idx]
+    frames, side, start, C, heads, mlp_ratio, qk_norm, use_rope, ls_init = case
+    x, params, pos = gi.block_inputs(idx, case)
+    N = x.shape[1]
+    cos_t = sin_t = None
+    if use_rope:
+        cos_t, sin_t = orc.rope_tables(C // heads // 2, side + 1, 100.0, "f32")
+    cu = np.arange(frames + 1, dtype=np.int64) * N
+    out = orc.jagged_block(x.reshape(-1, C), np.ones(frames * N, np.float32), cu, pos.reshape(-1, 2),
+                           dict(params, norm_eps=1e-5, qk_norm_eps=1e-5), heads, cos_t, sin_t)
+    gi.check_rows(out, z, f"b{idx}_out_", rtol=gi.BLOCK_TOLERANCE, atol=gi.BLOCK_TOLERANCE)
+
+
+def test_fused_aggregator_without_merging_is_the_block_chain():
+    """With an all-False mask the merged forward pass is the plain alternating chain of blocks on the dense tokens
+    (in the ragged layout's order), and a retained layer is [frame tokens | global tokens]."""
+    rng = np.random.default_rng(77)
+    B, S, side, start, C, heads = 1, 2, 4, 2, 32, 1
+    N = start + side * side
+    tokens = rng.standard_normal((B, S, N, C), dtype=np.float32)
+    fp = [gi.block_params(rng, C, heads, 2.0, True, 0.5) for _ in range(2)]
+    gp = [gi.block_params(rng, C, heads, 2.0, True, 0.5) for _ in range(2)]
+    mask = np.zeros((B * S, 4), bool)
+    out = orc.fused_aggregator(tokens, mask, start, side, side, 2, 2, fp, gp, heads, retain_layers={1})
+    assert sorted(out) == [1] and out[1].shape == (B, S, N, 2 * C)
+    # the same chain by hand, in the dense order (the attention is permutation-equivariant given the positions)
+    ys, xs = np.meshgrid(np.arange(side), np.arange(side), indexing="ij")
+    pos = np.zeros((N, 2), np.int64)
+    pos[start:, 0], pos[start:, 1] = ys.reshape(-1) + 1, xs.reshape(-1) + 1
+    pos = np.tile(pos, (B * S, 1))
+    cos_t, sin_t = orc.rope_tables(C // heads // 2, side + 2, 100.0, "bf16")
+    ones = np.ones(B * S * N, np.float32)
+    frame_cu = np.arange(B * S + 1) * N
+    global_cu = np.arange(B + 1) * S * N
+    x = tokens.reshape(-1, C)
+    for layer in range(2):
+        x = orc.jagged_block(x, ones, frame_cu, pos, fp[layer], heads, cos_t, sin_t)
+        frame_x = x
+        x = orc.jagged_block(x, ones, global_cu, pos, gp[layer], heads, cos_t, sin_t)
+    expect = np.concatenate([frame_x, x], axis=-1).reshape(B, S, N, 2 * C)
+    np.testing.assert_allclose(out[1], expect, rtol=2e-5, atol=2e-5)
