@@ -669,6 +669,18 @@ def run_only(args):
         gemm_flops = 48 * 2.0 * plan.total * CH * 4 * CH
         out.update(frames=frames, tokens=plan.total, layers=48, launch="CUDA graph of 48 layers",
                    flops=gemm_flops + sum(4.0 * L * L * HDIM * HEADS for L in ([plan.total] * 24 + [plan.total / frames] * 24 * frames)))
+    elif args.only == "residual_ln":
+        # LayerScale + residual add + LayerNorm on the packed rows of `frames` half-merged frames: x and the branch are
+        # read once, the updated stream and its normalised copy written once
+        from come_b200.block import residual_layernorm
+        dt = {"f32": torch.float32, "bf16": torch.bfloat16}[args.dtype]
+        rows = args.frames * (N_TOK - 8 * (N_WIN // 2))
+        x = torch.randn((rows, CH), device=dev, generator=g).to(dt)
+        br = torch.randn((rows, CH), device=dev, generator=g).to(dt)
+        gamma = torch.rand(CH, device=dev, generator=g).to(dt)
+        ln = torch.nn.LayerNorm(CH, eps=1e-6).to(dev).to(dt)
+        fn = lambda: residual_layernorm(x, br, gamma, ln)  # noqa: E731
+        out.update(frames=args.frames, tokens=rows, dtype=args.dtype, bytes=4 * rows * CH * x.element_size() + 3 * CH * x.element_size())
     elif args.only == "prepare":
         # q/k LayerNorm + 2-D rotary embedding + log(count) bias on the packed rows of `frames` half-merged frames
         from come_b200.qkv import RotaryPositionEmbedding2D, prepare_packed_self_attention_qkv
@@ -769,6 +781,9 @@ def run_aggregator(args):
         "Accelerated Model": lambda t: model(t, plan_of(t)),
         "Accelerated Model (CUDA graph)": lambda t: captured(t, plan_of(t)),
     }
+    if args.arms:
+        wanted = {"reference": "Reference Model", "accelerated": "Accelerated Model", "graph": "Accelerated Model (CUDA graph)"}
+        arms = {wanted[a]: arms[wanted[a]] for a in args.arms.split(",")}
     Timer.reset()
     with torch.no_grad():
         for name, fn in arms.items():
@@ -794,7 +809,8 @@ def run_aggregator(args):
         "only": "aggregator", "frames": S, "blocks": blocks, "scenes": len(scenes), "dtype": "bf16",
         "packed_tokens_mean": P, "dense_tokens": S * N_TOK, "graphs_captured": len(captured._graphs),
         "ms_per_scene": {k: round(v.P50, 3) for k, v in entries.items()},
-        "speedup_vs_unmerged": {k: round(entries["Reference Model"].P50 / v.P50, 3) for k, v in entries.items()},
+        "speedup_vs_unmerged": ({k: round(entries["Reference Model"].P50 / v.P50, 3) for k, v in entries.items()}
+                                if "Reference Model" in entries else None),
         "tflop_per_scene": {"unmerged": round((gemm(S * N_TOK) + attn(S * N_TOK)) / 1e12, 2),
                             "merged": round((gemm(P) + attn(P)) / 1e12, 2)},
         "timer": "CUDA events around each scene (src/utility/timer.py form), median over the scenes",
@@ -803,9 +819,10 @@ def run_aggregator(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--only", choices=["attn", "merge", "unmerge", "merge_ln", "unmerge_res", "prepare", "direct", "aggregator"],
+    ap.add_argument("--only", choices=["attn", "merge", "unmerge", "merge_ln", "unmerge_res", "prepare", "residual_ln", "direct", "aggregator"],
                     help="run one kernel family on one size and exit; aggregator = the end-to-end model driver")
     ap.add_argument("--depth", type=int, default=24, help="--only aggregator: frame/global block pairs")
+    ap.add_argument("--arms", default="", help="--only aggregator: comma list of reference, accelerated, graph (default all)")
     ap.add_argument("--frames", type=int, default=100, help="--only merge/unmerge: frames")
     ap.add_argument("--dtype", default="f32", choices=["f32", "bf16"], help="--only merge/unmerge: element type")
     ap.add_argument("--tokens", type=int, default=6384, help="--only attn with --segments 1: segment length")

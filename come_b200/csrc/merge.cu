@@ -977,6 +977,153 @@ extern "C" int come_unmerge_residual(const void *merged_dev, const int64_t *rev_
     }
 }
 
+// ---- residual update fused with the LayerNorm behind it (packed rows, no gather) --------------------------------------
+// x_out = x + scale * branch  (LayerScale and the residual add that close a sub-block; each tensor operation rounded to T)
+// normed = LayerNorm(x_out)   (the norm that opens the next sub-block)
+// One warp owns a row: lane l holds the 16-byte vectors l, l + 32, ... of the row (NV of them), so both tensors are read
+// once, statistics need shuffles only and no barrier is met.  Summation order of the statistics = the fused LayerNorm +
+// merge kernel's with "vector j of lane l" in the place of "warp j of the thread group": inside a vector the even / odd
+// chains, vectors of a lane left to right, then a butterfly over the lanes (neighbours first).
+constexpr int kRowWarps = 8;
+
+template <typename T, int VEC, int NV>
+__global__ void __launch_bounds__(kRowWarps * 32, NV >= 8 ? 1 : (NV >= 4 ? 2 : 3))  // a row's float32 copy stays in registers
+residual_layernorm_kernel(const T *__restrict__ x, const T *__restrict__ branch, const T *__restrict__ scale, int rows, int Cv,
+                          const T *__restrict__ gamma, const T *__restrict__ beta, float eps, T *__restrict__ x_out,
+                          T *__restrict__ normed) {
+    using IO = VecIO<T, VEC>;
+    using PIO = PairIO<T, VEC>;
+    using V = typename IO::V;
+    constexpr int NP = VEC / 2;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const float fC = (float)(Cv * VEC);
+    for (int row = blockIdx.x * kRowWarps + warp; row < rows; row += gridDim.x * kRowWarps) {
+        const int64_t base = (int64_t)row * Cv;
+        V rx[NV], rb[NV];
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+            const int v = j * 32 + lane;
+            if (v < Cv) {
+                rx[j] = ld_stream(reinterpret_cast<const V *>(x) + base + v);
+                if (branch) rb[j] = ld_stream(reinterpret_cast<const V *>(branch) + base + v);
+            }
+        }
+        if (branch) {
+#pragma unroll
+            for (int j = 0; j < NV; ++j) {
+                const int v = j * 32 + lane;
+                if (v < Cv) {
+                    float g[VEC];
+#pragma unroll
+                    for (int i = 0; i < VEC; ++i) g[i] = 1.0f;
+                    if (scale) IO::unpack(reinterpret_cast<const V *>(scale)[v], g);
+                    rx[j] = residual_update<T, VEC>(rb[j], rx[j], g, scale != nullptr);
+                    if (x_out) st_stream(reinterpret_cast<V *>(x_out) + base + v, rx[j]);
+                }
+            }
+        }
+        if (!normed) continue;
+        f32x2_t d[NV][NP];
+        float total = 0.0f;
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+            float part = 0.0f;
+#pragma unroll
+            for (int k = 0; k < NP; ++k) d[j][k] = 0ull;
+            if (j * 32 + lane < Cv) {
+                PIO::unpack(rx[j], d[j]);
+                f32x2_t acc = d[j][0];
+#pragma unroll
+                for (int k = 1; k < NP; ++k) acc = add_f32x2(acc, d[j][k]);
+                float even, odd;
+                unpack_f32x2(acc, even, odd);
+                part = __fadd_rn(even, odd);
+            }
+            total = (j == 0) ? part : __fadd_rn(total, part);
+        }
+#pragma unroll
+        for (int m = 1; m < 32; m <<= 1) total = __fadd_rn(total, __shfl_xor_sync(0xffffffffu, total, m));
+        const float mean = __fdiv_rn(total, fC);
+        const f32x2_t neg_mean = pack_f32x2(-mean, -mean);
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+            float part = 0.0f;
+            if (j * 32 + lane < Cv) {
+#pragma unroll
+                for (int k = 0; k < NP; ++k) d[j][k] = add_f32x2(d[j][k], neg_mean);
+                f32x2_t acc = mul_f32x2(d[j][0], d[j][0]);
+#pragma unroll
+                for (int k = 1; k < NP; ++k) acc = fma_f32x2(d[j][k], d[j][k], acc);  // explicit: never a separate mul + add
+                float even, odd;
+                unpack_f32x2(acc, even, odd);
+                part = __fadd_rn(even, odd);
+            }
+            total = (j == 0) ? part : __fadd_rn(total, part);
+        }
+#pragma unroll
+        for (int m = 1; m < 32; m <<= 1) total = __fadd_rn(total, __shfl_xor_sync(0xffffffffu, total, m));
+        const float rstd = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(total, fC), eps)));
+        const f32x2_t rstd2 = pack_f32x2(rstd, rstd);
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+            const int v = j * 32 + lane;
+            if (v < Cv) {
+                f32x2_t g2[NP], b2[NP];
+                PIO::unpack(__ldg(reinterpret_cast<const V *>(gamma) + v), g2);
+                PIO::unpack(__ldg(reinterpret_cast<const V *>(beta) + v), b2);
+#pragma unroll
+                for (int k = 0; k < NP; ++k) d[j][k] = fma_f32x2(g2[k], mul_f32x2(rstd2, d[j][k]), b2[k]);
+                st_stream(reinterpret_cast<V *>(normed) + base + v, PIO::pack(d[j]));
+            }
+        }
+    }
+}
+
+template <typename T>
+static int launch_residual_layernorm(const void *x, const void *branch, const void *scale, int64_t rows, int64_t C,
+                                     const void *gamma, const void *beta, float eps, void *x_out, void *normed, cudaStream_t st) {
+    constexpr int VEC = 16 / sizeof(T);
+    const auto al = [](const void *p) { return !p || (uintptr_t)p % 16 == 0; };
+    if (C % VEC != 0 || C / VEC > 256 || !al(x) || !al(branch) || !al(scale) || !al(gamma) || !al(beta) || !al(x_out) || !al(normed)) {
+        set_error("come_residual_layernorm needs 16-byte aligned tensors and channels a multiple of %d, at most %d (got %lld)",
+                  VEC, VEC * 256, (long long)C);
+        return COME_ERR_UNSUPPORTED;
+    }
+    const int Cv = (int)(C / VEC);
+    int64_t blocks = (rows + kRowWarps - 1) / kRowWarps;
+    const int64_t max_blocks = (int64_t)sm_count() * 6;  // a few resident waves, then the grid strides
+    if (blocks > max_blocks) blocks = max_blocks;
+#define COME_RLN_LAUNCH(NV)                                                                                                  \
+    residual_layernorm_kernel<T, VEC, NV><<<(unsigned)blocks, kRowWarps * 32, 0, st>>>(                                       \
+        (const T *)x, (const T *)branch, (const T *)scale, (int)rows, Cv, (const T *)gamma, (const T *)beta, eps, (T *)x_out, (T *)normed)
+    if (Cv <= 32) COME_RLN_LAUNCH(1);
+    else if (Cv <= 64) COME_RLN_LAUNCH(2);
+    else if (Cv <= 128) COME_RLN_LAUNCH(4);
+    else COME_RLN_LAUNCH(8);
+#undef COME_RLN_LAUNCH
+    return check_launch("come_residual_layernorm");
+}
+
+extern "C" int come_residual_layernorm(const void *x_dev, const void *branch_dev, const void *scale_dev, int64_t rows,
+                                       int64_t channels, int dtype, const void *gamma_dev, const void *beta_dev, float eps,
+                                       void *x_out_dev, void *normed_dev, void *stream) {
+    COME_REQUIRE(rows >= 0 && channels >= 0, "rows and channels must be >= 0");
+    COME_REQUIRE(dtype == COME_F32 || dtype == COME_F16 || dtype == COME_BF16, "unknown dtype %d", dtype);
+    COME_REQUIRE(rows < (1ll << 31), "rows must fit int32");
+    if (rows == 0 || channels == 0) return COME_OK;
+    COME_REQUIRE(x_dev != nullptr, "x must not be NULL");
+    COME_REQUIRE(branch_dev || !scale_dev, "scale without a branch");
+    COME_REQUIRE(!branch_dev || x_out_dev || normed_dev, "nothing to write");
+    COME_REQUIRE(!normed_dev || (gamma_dev && beta_dev), "gamma / beta must not be NULL when normed is requested");
+    COME_REQUIRE(branch_dev || normed_dev, "without a branch there is only the LayerNorm to compute: normed must not be NULL");
+    cudaStream_t st = (cudaStream_t)stream;
+    switch (dtype) {
+        case COME_F32: return launch_residual_layernorm<float>(x_dev, branch_dev, scale_dev, rows, channels, gamma_dev, beta_dev, eps, x_out_dev, normed_dev, st);
+        case COME_F16: return launch_residual_layernorm<__half>(x_dev, branch_dev, scale_dev, rows, channels, gamma_dev, beta_dev, eps, x_out_dev, normed_dev, st);
+        default: return launch_residual_layernorm<__nv_bfloat16>(x_dev, branch_dev, scale_dev, rows, channels, gamma_dev, beta_dev, eps, x_out_dev, normed_dev, st);
+    }
+}
+
 extern "C" int come_unmerge_strided(const void *merged_dev, const int64_t *rev_id_dev, int64_t total, int64_t channels,
                                     int dtype, void *out_dev, int64_t out_row_stride, void *stream) {
     COME_REQUIRE(total >= 0 && channels >= 0, "total and channels must be >= 0");

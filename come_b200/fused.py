@@ -9,6 +9,8 @@ Against the reference's closure:
   (``fused.py:113-129``);
 * a retained layer is unmerged straight into its half of the concatenated ``[B, S, N, 2C]`` tensor
   (``come_unmerge_strided``) instead of two splits and a ``torch.cat`` (``fused.py:157-167``);
+* when the token stream is already in the attention dtype, each ``LayerScale -> residual add -> LayerNorm`` between two
+  GEMMs of the blocks (``module/block.py:66-79``) is one kernel (``come_residual_layernorm``) instead of three;
 * every attention call gets the longest segment from the plan, so the block loop has no device-to-host read and can
   be captured in a CUDA graph (:class:`CapturedForward`), one graph per packed length.
 
@@ -21,7 +23,7 @@ from typing import Dict, Optional, Tuple
 
 import torch
 
-from .block import JaggedBlock, JaggedBlock_w_Bias
+from .block import JaggedBlock, JaggedBlock_w_Bias, forward_fused, fusable, residual_layernorm
 from .token_merger import JaggedTokens, MergePlan
 
 __all__ = ["FusedAggregator", "CapturedForward", "fused_accelerate"]
@@ -31,8 +33,13 @@ class FusedAggregator(torch.nn.Module):
     """``aggregator`` provides ``frame_blocks``, ``global_blocks``, ``aa_order``, ``aa_block_size``, ``aa_block_num``,
     ``retain_layers`` (None = all) and ``patch_start_idx`` (``src/thirdparty/vggt/models/aggregator.py:76-131``)."""
 
-    def __init__(self, aggregator: torch.nn.Module, use_attn_bias_correction: bool = True, attn_dtype: str = "bf16"):
+    def __init__(self, aggregator: torch.nn.Module, use_attn_bias_correction: bool = True, attn_dtype: str = "bf16",
+                 fuse_elementwise: bool = True):
+        """``fuse_elementwise``: run every ``LayerScale -> residual add -> LayerNorm`` of the blocks as one kernel
+        (:func:`come_b200.block.forward_fused`) when the model allows it (token stream in the attention dtype, plain
+        LayerNorm / LayerScale modules); otherwise, and when off, the blocks run module by module as in the reference."""
         super().__init__()
+        self.fuse_elementwise = bool(fuse_elementwise)
         block_fn = JaggedBlock_w_Bias if use_attn_bias_correction else JaggedBlock
         self.aggregator = aggregator
         self.frame_blocks = torch.nn.ModuleList([block_fn(b, attn_dtype) for b in aggregator.frame_blocks])
@@ -50,25 +57,37 @@ class FusedAggregator(torch.nn.Module):
     def _run(self, x: JaggedTokens, pos: torch.Tensor, frame_view, global_view, frame_blocks, global_blocks, unmerge):
         """The alternating loop (``fused.py:137-169``).  ``frame_view`` / ``global_view`` re-segment a JaggedTokens,
         ``unmerge(frame_tokens, global_tokens)`` produces a retained layer's output."""
-        block_idx = frame_idx = globe_idx = 0
+        order = []  # the blocks in execution order (the fused path hands each block the next one's norm1)
+        fi = gi = 0
+        for _ in range(self.aa_block_num):
+            for attn_type in self.aa_order:
+                if attn_type not in ("frame", "global"):
+                    raise ValueError(f"Unknown attention type: {attn_type}")
+                for _ in range(self.aa_block_size):
+                    if attn_type == "frame":
+                        order.append(frame_blocks[fi])
+                        fi += 1
+                    else:
+                        order.append(global_blocks[gi])
+                        gi += 1
+        fused = self.fuse_elementwise and bool(order) and all(fusable(w, x.tokens.dtype) for w in order)
+        normed = None
+        if fused:
+            _, normed = residual_layernorm(x.tokens.squeeze(0), None, None, order[0].block.norm1)
+        step = block_idx = 0
         output: Dict[int, torch.Tensor] = {}
         for _ in range(self.aa_block_num):
             frame_intermediate, globe_intermediate = [], []
             for attn_type in self.aa_order:
-                if attn_type == "frame":
-                    x = frame_view(x)
-                    for _ in range(self.aa_block_size):
-                        x = frame_blocks[frame_idx](x, pos=pos)
-                        frame_intermediate.append(x)
-                        frame_idx += 1
-                elif attn_type == "global":
-                    x = global_view(x)
-                    for _ in range(self.aa_block_size):
-                        x = global_blocks[globe_idx](x, pos=pos)
-                        globe_intermediate.append(x)
-                        globe_idx += 1
-                else:
-                    raise ValueError(f"Unknown attention type: {attn_type}")
+                x = frame_view(x) if attn_type == "frame" else global_view(x)
+                for _ in range(self.aa_block_size):
+                    if fused:
+                        next_norm = order[step + 1].block.norm1 if step + 1 < len(order) else None
+                        x, normed = forward_fused(order[step], x, normed, pos, next_norm)
+                    else:
+                        x = order[step](x, pos=pos)
+                    (frame_intermediate if attn_type == "frame" else globe_intermediate).append(x)
+                    step += 1
             for i in range(self.aa_block_size):
                 if self.retain_layers is None or block_idx in self.retain_layers:
                     output[block_idx] = unmerge(frame_intermediate[i].tokens.squeeze(0),

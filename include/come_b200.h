@@ -185,6 +185,22 @@ int come_unmerge_residual(const void *merged_dev, const int64_t *rev_id_dev, int
                           const void *residual_dev, const void *scale_dev, void *out_dev, void *stream);
 
 /*
+ * Residual update of a transformer sub-block fused with the LayerNorm that opens the next one, on packed rows [rows, C]:
+ *   x_out  = x + scale * branch          (LayerScale, then the residual add; product rounded, then sum rounded)
+ *   normed = LayerNorm(x_out) * gamma + beta   (float32 statistics, result rounded to the element type)
+ * i.e. `x = x + ls(branch)` followed by `norm(x)` of the jagged block (src/accelerate/vggt/module/block.py:66-79:
+ * `.apply(self.block.ls1)`, `residual_x + attn_x.tokens`, `.apply(self.block.norm2)`; the same pair closes the MLP
+ * sub-block and opens the next block's norm1): one read of x and branch and one write of each result instead of three
+ * elementwise passes.  Optional parts: branch_dev NULL = LayerNorm of x alone (x_out_dev ignored); scale_dev NULL = no
+ * LayerScale; normed_dev NULL = residual update only; x_out_dev NULL = the updated stream is not stored.
+ * x_out_dev may alias x_dev and normed_dev may alias branch_dev (a row is read completely before it is written).
+ * Channels: a multiple of 16 bytes, at most 4096 bytes per row.
+ */
+int come_residual_layernorm(const void *x_dev, const void *branch_dev, const void *scale_dev, int64_t rows, int64_t channels,
+                            int dtype, const void *gamma_dev, const void *beta_dev, float eps, void *x_out_dev,
+                            void *normed_dev, void *stream);
+
+/*
  * Variable-length attention forward with an optional additive per-key bias:
  *   out[s:e, h] = softmax(q[s:e, h] k[s:e, h]^T * softmax_scale + bias[s:e][None, :]) v[s:e, h]
  * for every packed segment [cu_seqlens[i], cu_seqlens[i+1]) and head h; non-causal, no dropout.

@@ -31,6 +31,7 @@ __all__ = [
     "rope_tables",
     "layer_norm_heads",
     "layer_norm_rows",
+    "residual_layer_norm",
     "rope_2d",
     "qkv_prepare",
     "packed_positions",
@@ -487,6 +488,22 @@ def layer_norm_rows(x: np.ndarray, gamma: np.ndarray, beta: np.ndarray, eps: flo
     y = (rstd[..., None] * d).astype(np.float32)
     y = _fma32(np.broadcast_to(gamma.astype(np.float32), y.shape), y, np.broadcast_to(beta.astype(np.float32), y.shape))
     return _round_like(y, kind)
+
+
+def residual_layer_norm(x, branch, scale, gamma, beta, eps: float, kind: str = "bf16"):
+    """``x = x + ls(branch)`` followed by ``norm(x)`` on packed rows, the pair of steps between two sub-blocks of the
+    jagged block (``src/accelerate/vggt/module/block.py:66-79``): LayerScale ``branch * scale``
+    (``src/thirdparty/vggt/layers/layer_scale.py:21-22``) rounded to the element type, the residual sum rounded to the
+    element type, then :func:`layer_norm_rows` of the result.  ``branch`` None: the norm of ``x`` alone; ``scale`` None:
+    no LayerScale; ``gamma`` None: no norm.  Returns ``(x_out, normed)`` (``normed`` None without a norm)."""
+    x_out = np.asarray(x, np.float32)
+    if branch is not None:
+        t = np.asarray(branch, np.float32)
+        if scale is not None:
+            t = _round_like((t * np.asarray(scale, np.float32)).astype(np.float32), kind)
+        x_out = _round_like((x_out + t).astype(np.float32), kind)
+    normed = None if gamma is None else layer_norm_rows(x_out, np.asarray(gamma, np.float32), np.asarray(beta, np.float32), eps, kind)
+    return x_out, normed
 
 
 def rope_2d(x: np.ndarray, pos: np.ndarray, cos_t: np.ndarray, sin_t: np.ndarray, kind: str = "bf16"):

@@ -161,3 +161,105 @@ def test_timer_ranges():
     with Timer.range("inactive"):
         pass
     assert Timer.results() == []
+
+
+# ---- come_residual_layernorm: bit-exact against the oracle ------------------------------------------------------
+RLN_CASES = [  # (rows, C, dtype, has_branch, has_scale, has_norm)
+    (37, 1024, "bf16", True, True, True),
+    (37, 1024, "f16", True, True, True),
+    (19, 1024, "f32", True, True, True),   # 256 vectors per row: eight per lane
+    (50, 2048, "bf16", True, True, True),
+    (33, 384, "bf16", True, True, True),   # 48 vectors: the second vector of a lane exists for half the lanes
+    (64, 128, "f16", True, False, True),
+    (21, 64, "f32", True, True, False),    # residual update alone
+    (40, 1024, "bf16", False, False, True),  # LayerNorm alone
+    (1, 8, "bf16", True, True, True),
+]
+
+
+def _rln_inputs(i, case):
+    rows, C, kind, has_branch, has_scale, has_norm = case
+    rng = np.random.default_rng(4000 + i)
+    r = lambda a: gi.round_kind(a.astype(np.float32), kind)  # noqa: E731
+    x = r(rng.standard_normal((rows, C), dtype=np.float32) * 1.5 + 0.3)
+    branch = r(rng.standard_normal((rows, C), dtype=np.float32) * 2.0) if has_branch else None
+    scale = r(0.5 * rng.random(C, dtype=np.float32) + 0.01) if has_scale else None
+    gamma = r(1.0 + 0.2 * rng.standard_normal(C, dtype=np.float32)) if has_norm else None
+    beta = r(0.1 * rng.standard_normal(C, dtype=np.float32)) if has_norm else None
+    return x, branch, scale, gamma, beta
+
+
+@pytest.mark.parametrize("idx", range(len(RLN_CASES)))
+def test_residual_layernorm_bit_exact(idx):
+    from come_b200.block import residual_layernorm
+    from tests.gpu_util import TORCH_DTYPE, to_dev
+    case = RLN_CASES[idx]
+    rows, C, kind, has_branch, has_scale, has_norm = case
+    x, branch, scale, gamma, beta = _rln_inputs(idx, case)
+    norm = None
+    if has_norm:
+        norm = torch.nn.LayerNorm(C, eps=1e-6).cuda().to(TORCH_DTYPE[kind])
+        with torch.no_grad():
+            norm.weight.copy_(to_dev(gamma, kind))
+            norm.bias.copy_(to_dev(beta, kind))
+    dev = lambda a: None if a is None else to_dev(a, kind)  # noqa: E731
+    x_out, normed = residual_layernorm(dev(x), dev(branch), dev(scale), norm)
+    ref_x, ref_n = orc.residual_layer_norm(x, branch, scale, gamma, beta, 1e-6, kind)
+    assert np.array_equal(to_np(x_out), ref_x)
+    if has_norm:
+        assert np.array_equal(to_np(normed), ref_n)
+        # and within one unit in the last place of PyTorch's own LayerNorm on the same rows
+        with torch.no_grad():
+            theirs = to_np(norm(to_dev(ref_x, kind)))
+        ulp = {"bf16": 2.0 ** -7, "f16": 2.0 ** -10, "f32": 2.0 ** -20}[kind]
+        assert np.all(np.abs(theirs - ref_n) <= ulp * np.maximum(np.abs(ref_n), 1.0))
+    else:
+        assert normed is None
+
+
+def test_residual_layernorm_in_place_and_errors():
+    from come_b200 import _lib
+    from come_b200._torch_util import ptr, stream_ptr
+    from come_b200.block import residual_layernorm
+    from tests.gpu_util import to_dev
+    case = (300, 1024, "bf16", True, True, True)
+    x, branch, scale, gamma, beta = _rln_inputs(99, case)
+    ref_x, ref_n = orc.residual_layer_norm(x, branch, scale, gamma, beta, 1e-5, "bf16")
+    dx, db, ds, dg, dbeta = (to_dev(a, "bf16") for a in (x, branch, scale, gamma, beta))
+    # x_out over x and normed over branch: a row is read completely before it is written
+    _lib.check(_lib.lib().come_residual_layernorm(ptr(dx), ptr(db), ptr(ds), 300, 1024, _lib.COME_BF16, ptr(dg), ptr(dbeta),
+                                                  1e-5, ptr(dx), ptr(db), stream_ptr(dx.device)))
+    assert np.array_equal(to_np(dx), ref_x) and np.array_equal(to_np(db), ref_n)
+    with pytest.raises(NotImplementedError):  # 8200 bytes per row
+        residual_layernorm(torch.zeros(4, 4100, device="cuda", dtype=torch.bfloat16), None, None,
+                           torch.nn.LayerNorm(4100).cuda().bfloat16())
+    with pytest.raises(ValueError):
+        residual_layernorm(dx, None, None, None)
+    with pytest.raises(ValueError):
+        residual_layernorm(dx, db[:10], None, None)
+    assert _lib.device_status() == 0
+
+
+def test_fused_elementwise_path_matches_module_path():
+    """The aggregator with the fused LayerScale + residual + LayerNorm kernels against the module-by-module path:
+    same arithmetic except the summation order inside the LayerNorm statistics."""
+    from come_b200 import _lib
+    from come_b200.fused import FusedAggregator
+    from come_b200.token_merger import MergePlan
+    rng = np.random.default_rng(13)
+    C, heads, depth, start, side, B, S = 128, 2, 3, 5, 7, 1, 3
+    N, M = start + side * side, 4
+    core, params = _small_model(rng, depth, C, heads, 0.5, torch.bfloat16)
+    fused, plain = FusedAggregator(core), FusedAggregator(core, fuse_elementwise=False)
+    tokens = gi.round_kind(rng.standard_normal((B, S, N, C), dtype=np.float32), "bf16")
+    mask = rng.random((B * S, M)) < 0.5
+    plan = MergePlan(torch.from_numpy(mask).cuda(), _lib.Layout.two_d(start, side, side, 3, 3))
+    t = torch.from_numpy(tokens).cuda().bfloat16()
+    with torch.no_grad():
+        a, _ = fused(t, plan)
+        b, _ = plain(t, plan)
+    ref = orc.fused_aggregator(tokens, mask, start, side, side, 3, 3, params["frame"], params["global"], heads)
+    for layer in range(depth):
+        assert _relative_error(to_np(a[layer]), to_np(b[layer])) < 5e-3
+        assert _relative_error(to_np(a[layer]), ref[layer]) < FUSED_REL_TOL
+        assert _relative_error(to_np(b[layer]), ref[layer]) < FUSED_REL_TOL
