@@ -13,6 +13,13 @@ Host side in Python/PyTorch (device memory, streams), compute in ``libcome_b200.
   ``MergePlan`` (merge, split, ``merge_layernorm``, ``split_add``, ``split_concat``, ``positions``), ``select_windows``
   and the 2-D merger class
 * :mod:`come_b200.bias_attention`       -- ``JaggedAttention_w_Bias`` (the reference's attention wrapper module)
+* :mod:`come_b200.plain_attention`      -- ``JaggedAttention`` (the same without the count bias)
+* :mod:`come_b200.block`                -- ``JaggedBlock`` / ``JaggedBlock_w_Bias`` and the block with LayerScale + residual
+  add + LayerNorm fused (``residual_layernorm``, ``forward_fused``)
+* :mod:`come_b200.fused`                -- ``FusedAggregator``: the merged forward pass of the alternating-attention
+  stack, ``CapturedForward``: its CUDA-graph replay
+* :mod:`come_b200.timer`                -- ``Timer`` (named CUDA-event ranges and their percentile table)
+* :mod:`come_b200.vggt_arch`            -- seeded random VGGT-shaped blocks for tests and benchmarks
 * :mod:`come_b200.direct`               -- ``DirectAttention``: the per-layer replacement of ``block.attn.forward``
 * :mod:`come_b200.chain`                -- the standalone operator chain of a scene, also sharded by frame over GPUs
 * :mod:`come_b200.static_scene`         -- the chain as one CUDA graph with no device-to-host read
