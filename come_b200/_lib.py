@@ -18,7 +18,7 @@ COME_SCOPE_BATCH, COME_SCOPE_FRAME = 0, 1
 EXPORTS = (
     "come_version", "come_last_error", "come_layout_info", "come_select_windows", "come_select_windows_ratios",
     "come_merge_plan_workspace_bytes", "come_merge_plan", "come_merge_plan_static", "come_merge", "come_merge_layernorm", "come_unmerge",
-    "come_unmerge_strided", "come_unmerge_residual", "come_residual_layernorm",
+    "come_unmerge_strided", "come_unmerge_residual", "come_residual_layernorm", "come_suffix_add", "come_suffix_split",
     "come_attn_varlen_fwd", "come_attn_varlen_fwd_rows", "come_qkv_prepare", "come_packed_positions",
     "come_device_status",
 )
@@ -67,6 +67,8 @@ def lib() -> C.CDLL:
     l.come_unmerge_strided.argtypes = [vp, vp, i64, i64, i32, vp, i64, vp]
     l.come_unmerge_residual.argtypes = [vp, vp, i64, i64, i32, vp, vp, vp, vp]
     l.come_residual_layernorm.argtypes = [vp, vp, vp, i64, i64, i32, vp, vp, f32, vp, vp, vp]
+    l.come_suffix_add.argtypes = [vp, vp, vp, i64, i64, i64, i32, vp, i64, vp, vp, vp, vp]
+    l.come_suffix_split.argtypes = [vp, vp, vp, i64, i64, i64, i32, i64, vp, vp, vp, vp, vp]
     l.come_attn_varlen_fwd.argtypes = [vp, vp, vp, i32, i64, i32, i32, i64, i64, i64, vp, vp, i32, i32, f32, vp, i64,
                                        vp, i32, vp]
     l.come_attn_varlen_fwd_rows.argtypes = [vp, vp, vp, i32, i64, i64, i64, i32, i32, i64, i64, i64, vp, vp, i32, i32, vp, f32,

@@ -1148,6 +1148,126 @@ extern "C" int come_unmerge(const void *merged_dev, const int64_t *rev_id_dev, i
     return come_unmerge_strided(merged_dev, rev_id_dev, total, channels, dtype, out_dev, channels, stream);
 }
 
+// ---- suffix tokens of jagged segments ---------------------------------------------------------------------------------
+// add: every segment of a packed sequence gets T dense rows appended (weight 1); split: the inverse.  Segment m of the longer
+// sequence starts at offset[m] + m * T, so neither direction needs the other's offsets in memory.  One warp per output row:
+// every lane finds the row's segment by the same binary search over the M + 1 offsets (they stay in L1), then the lanes copy the
+// row's vectors, four loads in flight each.
+template <typename V, bool SPLIT>
+__global__ void __launch_bounds__(kRowWarps * 32)
+suffix_rows_kernel(const V *__restrict__ tokens, const float *__restrict__ weight, const int64_t *__restrict__ offset, int segments,
+                   int64_t rows_out, int Cv, int T, const V *__restrict__ suffix_in, V *__restrict__ out_tokens,
+                   float *__restrict__ out_weight, int64_t *__restrict__ out_offset, V *__restrict__ suffix_out) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = (int64_t)blockIdx.x * kRowWarps + (threadIdx.x >> 5), n_warps = (int64_t)gridDim.x * kRowWarps;
+    // offsets of the result: longer by m * T (add) or shorter by m * T (split)
+    for (int64_t i = warp * 32 + lane; i <= segments; i += n_warps * 32) out_offset[i] = offset[i] + (SPLIT ? -i : i) * (int64_t)T;
+    const int64_t shift = SPLIT ? -(int64_t)T : (int64_t)T;  // out_start(m) = offset[m] + m * shift
+    // rows of the packed result, then (split only) the segments x T suffix rows
+    const int64_t n_rows = rows_out + (SPLIT ? (int64_t)segments * T : 0);
+    for (int64_t r = warp; r < n_rows; r += n_warps) {
+        const V *src;
+        V *dst;
+        float w = 1.0f;
+        bool has_w = false;
+        if (r < rows_out) {
+            int lo = 0, hi = segments;  // the segment with out_start(lo) <= r < out_start(lo + 1)
+            while (hi - lo > 1) {
+                const int mid = (lo + hi) >> 1;
+                if (__ldg(offset + mid) + mid * shift <= r) lo = mid;
+                else hi = mid;
+            }
+            const int64_t seg_begin = __ldg(offset + lo), local = r - (seg_begin + lo * shift);
+            dst = out_tokens + r * Cv;
+            has_w = true;
+            if (SPLIT) {  // row `local` of segment lo, whose old rows are all kept up to the new length
+                src = tokens + (seg_begin + local) * Cv;
+                w = __ldg(weight + seg_begin + local);
+            } else {
+                const int64_t old_len = __ldg(offset + lo + 1) - seg_begin;
+                if (local < old_len) {
+                    src = tokens + (seg_begin + local) * Cv;
+                    w = __ldg(weight + seg_begin + local);
+                } else {
+                    src = suffix_in + ((int64_t)lo * T + (local - old_len)) * Cv;
+                }
+            }
+        } else {  // split: suffix row t of segment m = the row T - t before the segment's old end
+            const int64_t k = r - rows_out;
+            const int m = (int)(k / T), t = (int)(k - (int64_t)m * T);
+            src = tokens + (__ldg(offset + m + 1) - T + t) * Cv;
+            dst = suffix_out + k * Cv;
+        }
+        if (has_w && lane == 0) out_weight[r] = w;
+        for (int v0 = lane; v0 < Cv; v0 += 128) {
+            V tmp[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (v0 + 32 * j < Cv) tmp[j] = ld_stream(src + v0 + 32 * j);
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (v0 + 32 * j < Cv) st_stream(dst + v0 + 32 * j, tmp[j]);
+        }
+    }
+}
+
+template <typename V, bool SPLIT>
+static int launch_suffix(const void *tokens, const float *weight, const int64_t *offset, int64_t segments, int64_t rows_out,
+                         int64_t Cv, int64_t T, const void *suffix_in, void *out_tokens, float *out_weight, int64_t *out_offset,
+                         void *suffix_out, cudaStream_t st) {
+    const int64_t n_rows = rows_out + (SPLIT ? segments * T : 0);
+    int64_t blocks = ((n_rows > segments + 1 ? n_rows : segments / 32 + 1) + kRowWarps - 1) / kRowWarps;
+    const int64_t max_blocks = (int64_t)sm_count() * 8;
+    if (blocks > max_blocks) blocks = max_blocks;
+    if (blocks < 1) blocks = 1;
+    suffix_rows_kernel<V, SPLIT><<<(unsigned)blocks, kRowWarps * 32, 0, st>>>(
+        (const V *)tokens, weight, offset, (int)segments, rows_out, (int)Cv, (int)T, (const V *)suffix_in, (V *)out_tokens, out_weight,
+        out_offset, (V *)suffix_out);
+    return check_launch(SPLIT ? "come_suffix_split" : "come_suffix_add");
+}
+
+template <bool SPLIT>
+static int suffix_dispatch(const void *tokens, const float *weight, const int64_t *offset, int64_t segments, int64_t total,
+                           int64_t channels, int dtype, int64_t T, const void *suffix_in, void *out_tokens, float *out_weight,
+                           int64_t *out_offset, void *suffix_out, void *stream) {
+    COME_REQUIRE(segments >= 0 && total >= 0 && channels >= 0 && T >= 0, "segments, total, channels and suffix_len must be >= 0");
+    COME_REQUIRE(dtype == COME_F32 || dtype == COME_F16 || dtype == COME_BF16, "unknown dtype %d", dtype);
+    COME_REQUIRE(segments < (1ll << 31) && T < (1ll << 31), "segments and suffix_len must fit int32");
+    COME_REQUIRE(offset && out_offset, "offset / out_offset must not be NULL");
+    COME_REQUIRE(segments > 0 || total == 0, "tokens without segments");
+    const int64_t rows_out = SPLIT ? total - segments * T : total + segments * T;
+    COME_REQUIRE(rows_out >= 0, "cannot strip %lld tokens from each of %lld segments (total tokens = %lld)", (long long)T,
+                 (long long)segments, (long long)total);
+    const bool moves = channels > 0 && (rows_out > 0 || (SPLIT && segments * T > 0));
+    COME_REQUIRE(!moves || (tokens || total == 0), "tokens must not be NULL");
+    COME_REQUIRE(rows_out == 0 || (out_weight && (weight || total == 0)), "weight / out_weight must not be NULL");
+    COME_REQUIRE(!moves || rows_out == 0 || out_tokens, "out_tokens must not be NULL");
+    COME_REQUIRE(!moves || segments * T == 0 || (SPLIT ? suffix_out != nullptr : suffix_in != nullptr), "suffix must not be NULL");
+    cudaStream_t st = (cudaStream_t)stream;
+    const size_t row_bytes = (size_t)channels * dtype_size(dtype);
+    const auto al = [](const void *p, size_t a) { return (uintptr_t)p % a == 0; };
+    const void *sfx = SPLIT ? suffix_out : suffix_in;
+    if (row_bytes % 16 == 0 && al(tokens, 16) && al(out_tokens, 16) && al(sfx, 16))
+        return launch_suffix<uint4, SPLIT>(tokens, weight, offset, segments, rows_out, row_bytes / 16, T, suffix_in, out_tokens, out_weight, out_offset, suffix_out, st);
+    if (row_bytes % 4 == 0 && al(tokens, 4) && al(out_tokens, 4) && al(sfx, 4))
+        return launch_suffix<uint32_t, SPLIT>(tokens, weight, offset, segments, rows_out, row_bytes / 4, T, suffix_in, out_tokens, out_weight, out_offset, suffix_out, st);
+    return launch_suffix<uint16_t, SPLIT>(tokens, weight, offset, segments, rows_out, row_bytes / 2, T, suffix_in, out_tokens, out_weight, out_offset, suffix_out, st);
+}
+
+extern "C" int come_suffix_add(const void *tokens_dev, const float *weight_dev, const int64_t *offset_dev, int64_t segments,
+                               int64_t total, int64_t channels, int dtype, const void *suffix_dev, int64_t suffix_len,
+                               void *out_tokens_dev, float *out_weight_dev, int64_t *out_offset_dev, void *stream) {
+    return suffix_dispatch<false>(tokens_dev, weight_dev, offset_dev, segments, total, channels, dtype, suffix_len, suffix_dev,
+                                  out_tokens_dev, out_weight_dev, out_offset_dev, nullptr, stream);
+}
+
+extern "C" int come_suffix_split(const void *tokens_dev, const float *weight_dev, const int64_t *offset_dev, int64_t segments,
+                                 int64_t total, int64_t channels, int dtype, int64_t suffix_len, void *out_tokens_dev,
+                                 float *out_weight_dev, int64_t *out_offset_dev, void *suffix_out_dev, void *stream) {
+    return suffix_dispatch<true>(tokens_dev, weight_dev, offset_dev, segments, total, channels, dtype, suffix_len, nullptr,
+                                 out_tokens_dev, out_weight_dev, out_offset_dev, suffix_out_dev, stream);
+}
+
 extern "C" int come_device_status(uint32_t *value, int clear) {
     COME_REQUIRE(value != nullptr, "value is NULL");
     unsigned int v = 0;

@@ -51,13 +51,32 @@ class JaggedTokens:
         return JaggedTokens(tokens=func(self.tokens), weight=self.weight, offset=self.offset,
                             max_seqlen=self.max_seqlen, max_seqlen_dev=self.max_seqlen_dev)
 
+    def _on_device_path(self) -> bool:
+        """The suffix kernels serve CUDA tensors in the library's layouts; anything else (CPU tensors, other weight or
+        offset dtypes) takes the PyTorch indexing below, as in the reference."""
+        return (self.tokens.is_cuda and self.weight.is_cuda and self.offset.is_cuda and self.weight.dtype == torch.float32
+                and self.offset.dtype == torch.int64 and self.tokens.dtype in (torch.float32, torch.float16, torch.bfloat16))
+
     def add_suffix(self, suffix: torch.Tensor) -> "JaggedTokens":
-        """Append ``T`` dense tokens (weight 1) to each of the ``M`` segments; ``suffix`` is ``(M, T, C)``."""
+        """Append ``T`` dense tokens (weight 1) to each of the ``M`` segments; ``suffix`` is ``(M, T, C)``
+        (``src/interface/token_merger.py:23-58``).  CUDA tensors: one kernel (``come_suffix_add``)."""
         M = self.offset.shape[0] - 1
         if suffix.shape[0] != M:
             raise ValueError(f"suffix batch dim ({suffix.shape[0]}) must match segment count ({M})")
         T, Cc = suffix.shape[1], suffix.shape[2]
         P_old = self.tokens.shape[1]
+        if self._on_device_path() and suffix.is_cuda and suffix.dtype == self.tokens.dtype and Cc == self.tokens.shape[2]:
+            dev = self.tokens.device
+            tokens, weight, offset = self.tokens[0].contiguous(), self.weight.contiguous(), self.offset.contiguous()
+            suffix = suffix.contiguous()
+            new_tokens = torch.empty(1, P_old + M * T, Cc, device=dev, dtype=tokens.dtype)
+            new_weight = torch.empty(P_old + M * T, device=dev, dtype=torch.float32)
+            new_offset = torch.empty_like(offset)
+            with torch.cuda.device(dev):
+                _lib.check(_lib.lib().come_suffix_add(ptr(tokens), ptr(weight), ptr(offset), M, P_old, Cc,
+                                                      dtype_code(tokens.dtype, "tokens"), ptr(suffix), T, ptr(new_tokens),
+                                                      ptr(new_weight), ptr(new_offset), stream_ptr(dev)))
+            return JaggedTokens(tokens=new_tokens, weight=new_weight, offset=new_offset)
         dev = self.offset.device
         seg_len = self.offset[1:] - self.offset[:-1]
         seg_id = torch.repeat_interleave(torch.arange(M, device=dev), seg_len, output_size=P_old)
@@ -72,7 +91,9 @@ class JaggedTokens:
         return JaggedTokens(tokens=new_tokens, weight=new_weight, offset=new_offset)
 
     def split_suffix(self, count: int) -> Tuple["JaggedTokens", torch.Tensor]:
-        """Remove the last ``count`` tokens of every segment (inverse of :meth:`add_suffix`)."""
+        """Remove the last ``count`` tokens of every segment (inverse of :meth:`add_suffix`,
+        ``src/interface/token_merger.py:60-100``).  CUDA tensors: one kernel (``come_suffix_split``) after the
+        reference's check of the segment lengths (a device-to-host read, as there)."""
         M = self.offset.shape[0] - 1
         T, Cc = count, self.tokens.shape[2]
         P_old = self.tokens.shape[1]
@@ -84,6 +105,18 @@ class JaggedTokens:
         seg_len = orig_offset[1:] - orig_offset[:-1]
         if (seg_len < 0).any():
             raise ValueError(f"count={T} exceeds the length of at least one segment")
+        if self._on_device_path():
+            tdev = self.tokens.device
+            tokens, weight, offset = self.tokens[0].contiguous(), self.weight.contiguous(), self.offset.contiguous()
+            new_tokens = torch.empty(1, P_new, Cc, device=tdev, dtype=tokens.dtype)
+            new_weight = torch.empty(P_new, device=tdev, dtype=torch.float32)
+            new_offset = torch.empty_like(offset)
+            suffix = torch.empty(M, T, Cc, device=tdev, dtype=tokens.dtype)
+            with torch.cuda.device(tdev):
+                _lib.check(_lib.lib().come_suffix_split(ptr(tokens), ptr(weight), ptr(offset), M, P_old, Cc,
+                                                        dtype_code(tokens.dtype, "tokens"), T, ptr(new_tokens),
+                                                        ptr(new_weight), ptr(new_offset), ptr(suffix), stream_ptr(tdev)))
+            return JaggedTokens(tokens=new_tokens, weight=new_weight, offset=new_offset), suffix
         tail = (self.offset[1:, None] - T + torch.arange(T, device=dev)[None, :]).reshape(-1)
         suffix = self.tokens[0, tail].reshape(M, T, Cc)
         seg_id = torch.repeat_interleave(torch.arange(M, device=dev), seg_len, output_size=P_new)

@@ -201,6 +201,27 @@ int come_residual_layernorm(const void *x_dev, const void *branch_dev, const voi
                             void *normed_dev, void *stream);
 
 /*
+ * Suffix tokens of jagged segments (ITokenMerger.JaggedTokens.add_suffix / split_suffix,
+ * src/interface/token_merger.py:23-100; used around the MapAnything blocks, src/accelerate/ma/fused.py:186-214).
+ *
+ * come_suffix_add: every one of the `segments` segments of the packed tokens [total, channels] (offset int64
+ * [segments + 1], weight float32 [total]) is extended by its `suffix_len` rows of suffix [segments, suffix_len, channels],
+ * weight 1: out_tokens [total + segments * suffix_len, channels], out_weight, out_offset[m] = offset[m] + m * suffix_len.
+ * come_suffix_split: the inverse: the last `suffix_len` rows of every segment go to suffix_out
+ * [segments, suffix_len, channels], the rest is packed again; out_offset[m] = offset[m] - m * suffix_len.  The caller
+ * checks that every segment holds at least suffix_len rows (the reference raises ValueError after reading the lengths
+ * back, token_merger.py:79-83); the library only checks the total.
+ * The reference builds both from arange / searchsorted / index_copy_ / index_select: about ten launches and two extra
+ * passes over the tokens; here one launch moves every row once.
+ */
+int come_suffix_add(const void *tokens_dev, const float *weight_dev, const int64_t *offset_dev, int64_t segments,
+                    int64_t total, int64_t channels, int dtype, const void *suffix_dev, int64_t suffix_len,
+                    void *out_tokens_dev, float *out_weight_dev, int64_t *out_offset_dev, void *stream);
+int come_suffix_split(const void *tokens_dev, const float *weight_dev, const int64_t *offset_dev, int64_t segments,
+                      int64_t total, int64_t channels, int dtype, int64_t suffix_len, void *out_tokens_dev,
+                      float *out_weight_dev, int64_t *out_offset_dev, void *suffix_out_dev, void *stream);
+
+/*
  * Variable-length attention forward with an optional additive per-key bias:
  *   out[s:e, h] = softmax(q[s:e, h] k[s:e, h]^T * softmax_scale + bias[s:e][None, :]) v[s:e, h]
  * for every packed segment [cu_seqlens[i], cu_seqlens[i+1]) and head h; non-causal, no dropout.

@@ -35,6 +35,8 @@ __all__ = [
     "rope_2d",
     "qkv_prepare",
     "packed_positions",
+    "jagged_add_suffix",
+    "jagged_split_suffix",
     "gelu_erf",
     "jagged_block",
     "fused_aggregator",
@@ -662,3 +664,42 @@ def fused_aggregator(tokens, mask, start_index, H, W, gh, gw, frame_params, glob
                 output[block_idx] = both.reshape(B, S, N, 2 * C)
             block_idx += 1
     return output
+
+
+# --------------------------------------------------------------------------------------------------------
+# suffix tokens of jagged segments
+# --------------------------------------------------------------------------------------------------------
+def jagged_add_suffix(tokens, weight, offset, suffix):
+    """``JaggedTokens.add_suffix`` (``src/interface/token_merger.py:23-58``): segment ``m`` of the packed ``tokens [P, C]``
+    is followed by its ``T`` rows of ``suffix [M, T, C]``, each with weight 1.  Returns ``(tokens, weight, offset)``."""
+    tokens, weight = np.asarray(tokens), np.asarray(weight)
+    offset = np.asarray(offset, dtype=np.int64)
+    M, T = suffix.shape[0], suffix.shape[1]
+    if M != offset.size - 1:
+        raise ValueError(f"suffix batch dim ({M}) must match segment count ({offset.size - 1})")
+    rows, wts = [], []
+    for m in range(M):
+        rows += [tokens[offset[m]:offset[m + 1]], np.asarray(suffix[m], dtype=tokens.dtype)]
+        wts += [weight[offset[m]:offset[m + 1]], np.ones(T, dtype=weight.dtype)]
+    C = tokens.shape[1]
+    return (np.concatenate(rows, axis=0) if rows else np.zeros((0, C), tokens.dtype),
+            np.concatenate(wts) if wts else np.zeros(0, weight.dtype), offset + np.arange(M + 1, dtype=np.int64) * T)
+
+
+def jagged_split_suffix(tokens, weight, offset, count: int):
+    """``JaggedTokens.split_suffix`` (``src/interface/token_merger.py:60-100``): the inverse of
+    :func:`jagged_add_suffix`.  Returns ``(tokens, weight, offset, suffix [M, count, C])``; ``ValueError`` when a
+    segment is shorter than ``count``."""
+    tokens, weight = np.asarray(tokens), np.asarray(weight)
+    offset = np.asarray(offset, dtype=np.int64)
+    M, T, C = offset.size - 1, int(count), tokens.shape[1]
+    if tokens.shape[0] - M * T < 0:
+        raise ValueError(f"Cannot strip {T} tokens from each of {M} segments (total tokens = {tokens.shape[0]})")
+    new_offset = offset - np.arange(M + 1, dtype=np.int64) * T
+    if np.any(np.diff(new_offset) < 0):
+        raise ValueError(f"count={T} exceeds the length of at least one segment")
+    keep = [tokens[offset[m]:offset[m + 1] - T] for m in range(M)]
+    wts = [weight[offset[m]:offset[m + 1] - T] for m in range(M)]
+    suffix = np.stack([tokens[offset[m + 1] - T:offset[m + 1]] for m in range(M)]) if M else np.zeros((0, T, C), tokens.dtype)
+    return (np.concatenate(keep, axis=0) if keep else np.zeros((0, C), tokens.dtype),
+            np.concatenate(wts) if wts else np.zeros(0, weight.dtype), new_offset, suffix)

@@ -245,3 +245,25 @@ def block_inputs(i: int, case):
     pos[start:, 0] = ys.reshape(-1) + 1
     pos[start:, 1] = xs.reshape(-1) + 1
     return x, params, np.broadcast_to(pos, (frames, N, 2)).copy()
+
+
+# suffix tokens of jagged segments: (segment lengths, suffix length T, channels)
+SUFFIX_CASES = [
+    ([3], 1, 1),
+    ([2, 1], 2, 1),
+    ([1, 3, 2], 1, 2),
+    ([5, 0, 7, 1], 3, 8),      # an empty segment
+    ([40, 33, 61], 4, 136),    # rows of 17 sixteen-byte vectors in bfloat16
+    ([9, 12], 0, 16),          # nothing appended
+]
+
+
+def suffix_inputs(i: int, case):
+    lens, T, C = case
+    rng = np.random.default_rng(9700 + i)
+    P = int(sum(lens))
+    tokens = rng.standard_normal((P, C), dtype=np.float32)
+    weight = rng.choice(np.array([1.0, 4.0, 9.0], np.float32), size=P)
+    offset = np.concatenate([[0], np.cumsum(lens)]).astype(np.int64)
+    suffix = rng.standard_normal((len(lens), T, C), dtype=np.float32)
+    return tokens, weight, offset, suffix

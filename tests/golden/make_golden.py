@@ -30,7 +30,7 @@ from golden_inputs import (  # noqa: E402
     merge1d_inputs, merge2d_inputs, select_inputs, SELECT_CASES, attention_inputs, EXTRA_ATTENTION_CASES,
     cfg1_inputs, summarize_rows, PREPARE_CASES, PREPARE_EPS, PREPARE_MAX_POSITION, prepare_inputs, POSITION_CASES,
     position_mask, LN_MERGE_CASES, LN_MERGE_EPS, ln_merge_inputs, ln_merge_tolerance, BLOCK_CASES, BLOCK_TOLERANCE,
-    block_inputs,
+    block_inputs, SUFFIX_CASES, suffix_inputs,
 )
 
 
@@ -287,6 +287,25 @@ def main():
             "block", case, np.abs(ours - ref.reshape(-1, C)).max())
         store.update({f"b{i}_out_{k}": v for k, v in summarize_rows(ref.reshape(-1, C), 5).items()})
     np.savez_compressed(os.path.join(HERE, "block.npz"), **store)
+
+    # ---- suffix tokens: the reference's own JaggedTokens.add_suffix / split_suffix -----------------------------------
+    from src.interface.token_merger import ITokenMerger
+    store = {}
+    for i, case in enumerate(SUFFIX_CASES):
+        tokens, weight, offset, suffix = suffix_inputs(i, case)
+        jag = ITokenMerger.JaggedTokens(tokens=t(tokens)[None], weight=t(weight), offset=t(offset))
+        ext = jag.add_suffix(t(suffix))
+        o_tok, o_w, o_off = orc.jagged_add_suffix(tokens, weight, offset, suffix)
+        assert np.array_equal(o_tok, ext.tokens[0].numpy()) and np.array_equal(o_w, ext.weight.numpy()), ("suffix", case)
+        assert np.array_equal(o_off, ext.offset.numpy()), ("suffix", case)
+        back, suf = ext.split_suffix(case[1])
+        b_tok, b_w, b_off, b_suf = orc.jagged_split_suffix(o_tok, o_w, o_off, case[1])
+        assert np.array_equal(b_tok, back.tokens[0].numpy()) and np.array_equal(b_w, back.weight.numpy()), ("split", case)
+        assert np.array_equal(b_off, back.offset.numpy()) and np.array_equal(b_suf, suf.numpy()), ("split", case)
+        assert np.array_equal(b_tok, tokens) and np.array_equal(b_suf, suffix)
+        store[f"s{i}_tokens"], store[f"s{i}_weight"], store[f"s{i}_offset"] = (
+            ext.tokens[0].numpy(), ext.weight.numpy().astype(np.uint8), ext.offset.numpy().astype(np.int32))
+    np.savez_compressed(os.path.join(HERE, "suffix.npz"), **store)
 
     # ---- standalone op chain of the headline configuration (8 x 1374 tokens, 37x37 grid, 3x3 windows) ----
     tokens, conf = cfg1_inputs()

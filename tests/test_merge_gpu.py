@@ -14,7 +14,7 @@ import torch
 
 import golden_inputs as gi
 import reference_cases as rc
-from gpu_util import to_dev, to_np
+from gpu_util import TORCH_DTYPE, to_dev, to_np
 from oracle import clib, come_oracle as orc
 
 pytestmark = pytest.mark.gpu
@@ -291,7 +291,7 @@ def test_split_concat(kind, widths):
     import torch
     from come_b200 import _lib
     from come_b200.token_merger import MergePlan
-    from gpu_util import to_dev, to_np
+    from gpu_util import TORCH_DTYPE, to_dev, to_np
     import golden_inputs as gi
     from oracle import come_oracle as orc
     rng = np.random.default_rng(sum(widths))
@@ -312,7 +312,7 @@ def test_split_add_residual(kind, C, with_scale):
     import torch
     from come_b200 import _lib
     from come_b200.token_merger import MergePlan
-    from gpu_util import to_dev, to_np
+    from gpu_util import TORCH_DTYPE, to_dev, to_np
     import golden_inputs as gi
     from oracle import come_oracle as orc
     rng = np.random.default_rng(C)
@@ -363,7 +363,7 @@ def test_merge_layernorm_headline_shape():
     import torch
     from come_b200 import _lib
     from come_b200.token_merger import MergePlan
-    from gpu_util import to_dev, to_np
+    from gpu_util import TORCH_DTYPE, to_dev, to_np
     import golden_inputs as gi
     from oracle import come_oracle as orc
     rng = np.random.default_rng(77)
@@ -383,3 +383,58 @@ def test_merge_layernorm_headline_shape():
     wide = torch.zeros(frames, 1374, 4096, device="cuda", dtype=torch.bfloat16)
     with pytest.raises(NotImplementedError):
         plan.merge_layernorm(wide, torch.nn.LayerNorm(4096).cuda().bfloat16())
+
+
+# ---- suffix tokens of jagged segments (come_suffix_add / come_suffix_split) ----------------------------------------
+@pytest.mark.parametrize("kind", ["f32", "bf16", "f16"])
+@pytest.mark.parametrize("idx", range(len(gi.SUFFIX_CASES)))
+def test_suffix_kernels_against_fixture(golden_dir, idx, kind):
+    from come_b200.token_merger import JaggedTokens
+    z = np.load(os.path.join(golden_dir, "suffix.npz"))
+    case = gi.SUFFIX_CASES[idx]
+    tokens, weight, offset, suffix = gi.suffix_inputs(idx, case)
+    tokens, suffix = gi.round_kind(tokens, kind), gi.round_kind(suffix, kind)
+    jag = JaggedTokens(tokens=to_dev(tokens, kind)[None], weight=to_dev(weight), offset=torch.from_numpy(offset).cuda())
+    ext = jag.add_suffix(to_dev(suffix, kind))
+    ref_tok, ref_w, ref_off = orc.jagged_add_suffix(tokens, weight, offset, suffix)
+    assert ext.tokens.dtype == TORCH_DTYPE[kind] and ext.offset.dtype == torch.int64
+    assert np.array_equal(to_np(ext.tokens[0]), ref_tok) and np.array_equal(to_np(ext.weight), ref_w)
+    assert np.array_equal(to_np(ext.offset), ref_off)
+    assert np.array_equal(to_np(ext.weight), z[f"s{idx}_weight"].astype(np.float32))
+    assert np.array_equal(to_np(ext.offset), z[f"s{idx}_offset"].astype(np.int64))
+    if kind == "f32":
+        assert np.array_equal(to_np(ext.tokens[0]), z[f"s{idx}_tokens"])
+    back, suf = ext.split_suffix(case[1])
+    assert np.array_equal(to_np(back.tokens[0]), tokens) and np.array_equal(to_np(back.weight), weight)
+    assert np.array_equal(to_np(back.offset), offset) and np.array_equal(to_np(suf), suffix)
+    assert suf.shape == suffix.shape
+
+
+def test_suffix_kernels_large_and_errors():
+    """Frame-sized segments (the packed tokens of 8 half-merged frames + 4 suffix tokens each) against the PyTorch
+    indexing path of the same container on CPU; errors as in the reference."""
+    from come_b200 import _lib
+    from come_b200.token_merger import JaggedTokens
+    rng = np.random.default_rng(3)
+    lens = [1374 - 8 * int(k) for k in rng.integers(0, 73, size=8)]
+    P, C, T = sum(lens), 1024, 4
+    tokens = gi.round_kind(rng.standard_normal((P, C), dtype=np.float32), "bf16")
+    weight = rng.choice(np.array([1.0, 9.0], np.float32), size=P)
+    offset = np.concatenate([[0], np.cumsum(lens)]).astype(np.int64)
+    suffix = gi.round_kind(rng.standard_normal((8, T, C), dtype=np.float32), "bf16")
+    cpu = JaggedTokens(torch.from_numpy(tokens).bfloat16()[None], torch.from_numpy(weight), torch.from_numpy(offset))
+    gpu = JaggedTokens(cpu.tokens.cuda(), cpu.weight.cuda(), cpu.offset.cuda())
+    ext_cpu, ext_gpu = cpu.add_suffix(torch.from_numpy(suffix).bfloat16()), gpu.add_suffix(torch.from_numpy(suffix).bfloat16().cuda())
+    for a, b in ((ext_cpu.tokens, ext_gpu.tokens), (ext_cpu.weight, ext_gpu.weight), (ext_cpu.offset, ext_gpu.offset)):
+        assert torch.equal(a, b.cpu())
+    back_gpu, suf_gpu = ext_gpu.split_suffix(T)
+    assert torch.equal(back_gpu.tokens.cpu(), cpu.tokens) and torch.equal(suf_gpu.cpu(), torch.from_numpy(suffix).bfloat16())
+    assert torch.equal(back_gpu.offset.cpu(), cpu.offset) and torch.equal(back_gpu.weight.cpu(), cpu.weight)
+    with pytest.raises(ValueError):
+        gpu.add_suffix(torch.zeros(7, T, C, device="cuda", dtype=torch.bfloat16))
+    with pytest.raises(ValueError):
+        gpu.split_suffix(P)  # more than the total
+    short = JaggedTokens(gpu.tokens[:, :6], gpu.weight[:6], torch.tensor([0, 5, 6], device="cuda"))
+    with pytest.raises(ValueError):
+        short.split_suffix(2)  # 4 <= 6 in total, but the second segment holds one token
+    assert _lib.device_status() == 0

@@ -264,3 +264,31 @@ def test_fused_aggregator_without_merging_is_the_block_chain():
         x = orc.jagged_block(x, ones, global_cu, pos, gp[layer], heads, cos_t, sin_t)
     expect = np.concatenate([frame_x, x], axis=-1).reshape(B, S, N, 2 * C)
     np.testing.assert_allclose(out[1], expect, rtol=2e-5, atol=2e-5)
+
+
+@pytest.mark.parametrize("idx", range(len(gi.SUFFIX_CASES)))
+def test_suffix_fixture(golden_dir, idx):
+    """add_suffix / split_suffix of the jagged container against the reference's own class on CPU."""
+    z = _load(golden_dir, "suffix.npz")
+    case = gi.SUFFIX_CASES[idx]
+    tokens, weight, offset, suffix = gi.suffix_inputs(idx, case)
+    tok, w, off = orc.jagged_add_suffix(tokens, weight, offset, suffix)
+    assert np.array_equal(tok, z[f"s{idx}_tokens"]) and np.array_equal(w, z[f"s{idx}_weight"].astype(np.float32))
+    assert np.array_equal(off, z[f"s{idx}_offset"].astype(np.int64))
+    b_tok, b_w, b_off, b_suf = orc.jagged_split_suffix(tok, w, off, case[1])
+    assert np.array_equal(b_tok, tokens) and np.array_equal(b_w, weight)
+    assert np.array_equal(b_off, offset) and np.array_equal(b_suf, suffix)
+
+
+def test_suffix_known_answers_and_errors():
+    """The literal cases of the reference's suffix test (two segments [a, b | c], T = 2) and its error conditions."""
+    tok, w, off = orc.jagged_add_suffix(np.array([[1.], [2.], [3.]], np.float32), np.array([4., 1., 1.], np.float32), [0, 2, 3],
+                                        np.array([[[10.], [20.]], [[30.], [40.]]], np.float32))
+    assert tok[:, 0].tolist() == [1., 2., 10., 20., 3., 30., 40.]
+    assert w.tolist() == [4., 1., 1., 1., 1., 1., 1.] and off.tolist() == [0, 4, 7]
+    with pytest.raises(ValueError):
+        orc.jagged_add_suffix(tok, w, off, np.zeros((3, 1, 1), np.float32))
+    with pytest.raises(ValueError):
+        orc.jagged_split_suffix(tok, w, off, 4)       # more than the total
+    with pytest.raises(ValueError):  # 4 <= 6 in total, but the second segment holds one token
+        orc.jagged_split_suffix(np.zeros((6, 1), np.float32), np.ones(6, np.float32), [0, 5, 6], 2)
