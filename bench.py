@@ -381,6 +381,11 @@ def run_gpu(args):
         }
         if world == 1 and not args.no_micro:
             line["kernels"] = micro(torch, dev, pk)
+            # the whole alternating-attention stack (48 blocks with their cuBLAS GEMMs) around the same kernels,
+            # merged against unmerged: the reference's own end-to-end comparison (src/bench.py), 5 scenes per arm
+            agg = aggregator_measure(FRAMES, 24, 5, report=False)
+            agg.pop("only")
+            line["aggregator_model"] = agg
         if world == 1 and not args.no_cpu:
             v, cores, sample, detail = cpu_chain_sample()
             line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample,
@@ -745,7 +750,7 @@ def run_only(args):
     print(json.dumps(out))
 
 
-def run_aggregator(args):
+def aggregator_measure(S, depth, iters, arms_wanted="", report=True):
     """End-to-end driver in the form of the reference's benchmark (``src/bench.py:13-46``): the unmerged model and the
     accelerated model are run over the same synthetic scenes inside ``Timer.range`` and the timer's table is printed.
     The model is the alternating-attention stack of a VGGT-1B-shaped aggregator with seeded random weights in bf16
@@ -761,15 +766,14 @@ def run_aggregator(args):
     from come_b200.vggt_arch import AggregatorCore
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
-    S = 8 if args.frames == 100 else args.frames  # 100 is the flag's default, meant for the merge kernels
-    core = AggregatorCore(depth=args.depth).to(dev).bfloat16()
+    core = AggregatorCore(depth=depth).to(dev).bfloat16()
     model = FusedAggregator(core)
     captured = CapturedForward(model)
     torch.manual_seed(0)
     head = torch.nn.Sequential(torch.nn.Linear(CH, 128), torch.nn.GELU(), torch.nn.Linear(128, 1)).to(dev).bfloat16().eval()
     layout = _lib.Layout.two_d(START, GRID, GRID, WIN, WIN)
     g = torch.Generator(device=dev).manual_seed(0)
-    scenes = [torch.randn((1, S, N_TOK, CH), device=dev, generator=g).bfloat16() for _ in range(args.iters)]
+    scenes = [torch.randn((1, S, N_TOK, CH), device=dev, generator=g).bfloat16() for _ in range(iters)]
 
     def plan_of(tokens):
         conf = head(tokens[:, :, START:, :]).reshape(1, S * GRID * GRID)
@@ -781,9 +785,9 @@ def run_aggregator(args):
         "Accelerated Model": lambda t: model(t, plan_of(t)),
         "Accelerated Model (CUDA graph)": lambda t: captured(t, plan_of(t)),
     }
-    if args.arms:
+    if arms_wanted:
         wanted = {"reference": "Reference Model", "accelerated": "Accelerated Model", "graph": "Accelerated Model (CUDA graph)"}
-        arms = {wanted[a]: arms[wanted[a]] for a in args.arms.split(",")}
+        arms = {wanted[a]: arms[wanted[a]] for a in arms_wanted.split(",")}
     Timer.reset()
     with torch.no_grad():
         for name, fn in arms.items():
@@ -799,13 +803,15 @@ def run_aggregator(args):
         packed = [plan_of(t).total for t in scenes]
     Timer.activate(False)
     entries = {e.name: e for e in Timer.results()}
-    print(Timer.report(), file=sys.stderr)
+    if report:
+        print(Timer.report(), file=sys.stderr)
+    Timer.reset()
     assert _lib.device_status(clear=False) == 0
     P = float(np.mean(packed))
-    blocks = 2 * args.depth
+    blocks = 2 * depth
     gemm = lambda rows: blocks * 2.0 * rows * CH * CH * 12  # qkv 3, proj 1, fc1 4, fc2 4  # noqa: E731
-    attn = lambda rows: args.depth * 4.0 * HDIM * HEADS * (rows * rows + S * (rows / S) ** 2)  # noqa: E731
-    print(json.dumps({
+    attn = lambda rows: depth * 4.0 * HDIM * HEADS * (rows * rows + S * (rows / S) ** 2)  # noqa: E731
+    return {
         "only": "aggregator", "frames": S, "blocks": blocks, "scenes": len(scenes), "dtype": "bf16",
         "packed_tokens_mean": P, "dense_tokens": S * N_TOK, "graphs_captured": len(captured._graphs),
         "ms_per_scene": {k: round(v.P50, 3) for k, v in entries.items()},
@@ -814,7 +820,12 @@ def run_aggregator(args):
         "tflop_per_scene": {"unmerged": round((gemm(S * N_TOK) + attn(S * N_TOK)) / 1e12, 2),
                             "merged": round((gemm(P) + attn(P)) / 1e12, 2)},
         "timer": "CUDA events around each scene (src/utility/timer.py form), median over the scenes",
-    }))
+    }
+
+
+def run_aggregator(args):
+    S = 8 if args.frames == 100 else args.frames  # 100 is the flag's default, meant for the merge kernels
+    print(json.dumps(aggregator_measure(S, args.depth, args.iters, args.arms)))
 
 
 def main():

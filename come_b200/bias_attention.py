@@ -38,6 +38,32 @@ class _JaggedAttentionBase(torch.nn.Module):
         else:  # the model's own rotary module: only its base frequency matters
             self._rope = RotaryPositionEmbedding2D(frequency=float(rope.base_frequency))
 
+    def _attend_local(self, x: JaggedTokens, prepared, max_seqlen: Optional[int], use_bias: bool) -> torch.Tensor:
+        cu_seqlens = x.offset.to(torch.int32)
+        max_seqlen_dev = None
+        if max_seqlen is None:
+            max_seqlen, max_seqlen_dev = x.max_seqlen, x.max_seqlen_dev
+        if max_seqlen is None:
+            max_seqlen = infer_flash_attn_varlen_max_seqlen(cu_seqlens)
+        if use_bias:
+            qkv, perkey_bias = prepared
+            return flash_attn_varlen_qkvpacked_func_w_perkey_bias(qkv, cu_seqlens, max_seqlen, perkey_bias=perkey_bias,
+                                                                  dropout_p=0.0, softmax_scale=self.attn.scale,
+                                                                  max_seqlen_dev=max_seqlen_dev)
+        return flash_attn_varlen_qkvpacked_func(prepared, cu_seqlens, max_seqlen, dropout_p=0.0,
+                                                softmax_scale=self.attn.scale, max_seqlen_dev=max_seqlen_dev)
+
+    def _attend_all_ranks(self, x: JaggedTokens, prepared, use_bias: bool) -> torch.Tensor:
+        """These tokens are this rank's rows of one segment spread over the ranks: gather the prepared key / value rows
+        of all ranks (the only exchange of the path) and attend the local query rows to them."""
+        from .flash_attn_fwd_cuda import varlen_fwd_rows
+        ex = x.exchange
+        qkv = prepared[0] if use_bias else prepared
+        kv_all = ex.gather(qkv[:, 1:].contiguous())
+        out, _lse = varlen_fwd_rows(qkv[:, 0], kv_all[:, 0], kv_all[:, 1], ex.cu_seqlens, ex.total,
+                                    ex.bias(qkv.dtype) if use_bias else None, self.attn.scale, ex.row_begin)
+        return out
+
     def _forward(self, x: JaggedTokens, pos: Optional[torch.Tensor], max_seqlen: Optional[int], use_bias: bool) -> JaggedTokens:
         attn = self.attn
         if self.training and getattr(getattr(attn, "attn_drop", None), "p", 0.0) > 0.0:
@@ -47,26 +73,16 @@ class _JaggedAttentionBase(torch.nn.Module):
         qkv = attn.qkv(tokens).reshape(P, 3, attn.num_heads, attn.head_dim)
         prepared = prepare_packed_self_attention_qkv(qkv, attn.q_norm, attn.k_norm, self._rope, pos, self.run_dtype,
                                                      weight=x.weight if use_bias else None)
-        cu_seqlens = x.offset.to(torch.int32)
-        max_seqlen_dev = None
-        if max_seqlen is None:
-            max_seqlen, max_seqlen_dev = x.max_seqlen, x.max_seqlen_dev
-        if max_seqlen is None:
-            max_seqlen = infer_flash_attn_varlen_max_seqlen(cu_seqlens)
-        if use_bias:
-            qkv, perkey_bias = prepared
-            out = flash_attn_varlen_qkvpacked_func_w_perkey_bias(qkv, cu_seqlens, max_seqlen, perkey_bias=perkey_bias,
-                                                                 dropout_p=0.0, softmax_scale=attn.scale,
-                                                                 max_seqlen_dev=max_seqlen_dev)
+        if x.exchange is not None:
+            out = self._attend_all_ranks(x, prepared, use_bias)
         else:
-            out = flash_attn_varlen_qkvpacked_func(prepared, cu_seqlens, max_seqlen, dropout_p=0.0,
-                                                   softmax_scale=attn.scale, max_seqlen_dev=max_seqlen_dev)
+            out = self._attend_local(x, prepared, max_seqlen, use_bias)
         out = attn.proj(out.reshape(P, C))
         proj_drop = getattr(attn, "proj_drop", None)
         if proj_drop is not None:
             out = proj_drop(out)
         return JaggedTokens(tokens=out.unsqueeze(0), weight=x.weight, offset=x.offset, max_seqlen=x.max_seqlen,
-                            max_seqlen_dev=x.max_seqlen_dev)
+                            max_seqlen_dev=x.max_seqlen_dev, exchange=x.exchange)
 
 
 class JaggedAttention_w_Bias(_JaggedAttentionBase):

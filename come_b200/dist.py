@@ -12,7 +12,7 @@ from typing import List, Optional, Sequence, Tuple
 import torch
 import torch.distributed as dist
 
-__all__ = ["shard_range", "rows_per_rank", "gather_rows"]
+__all__ = ["shard_range", "rows_per_rank", "gather_rows", "GlobalExchange"]
 
 
 def shard_range(n_items: int, world: int, rank: int) -> Tuple[int, int]:
@@ -75,3 +75,42 @@ def gather_rows(local: torch.Tensor, rows: Sequence[int], group: Optional[dist.P
     for r in range(world):
         views[r].copy_(stage[r * most: r * most + rows[r]])
     return out
+
+
+class GlobalExchange:
+    """What a rank needs to run global attention on ITS packed rows of a scene whose frames are spread over the ranks:
+    the row counts of all ranks, where its own rows start, the per-key bias of all rows (the plan of the whole scene is
+    replicated, so this needs no communication) and the gather of the key / value rows.
+
+    ``gather`` defaults to :func:`gather_rows` over ``group``; tests pass their own to stand in for the other ranks.
+    """
+
+    def __init__(self, rows: Sequence[int], rank: int, weight_all: torch.Tensor, group: Optional[dist.ProcessGroup] = None,
+                 gather=None):
+        self.rows = [int(n) for n in rows]
+        self.rank = int(rank)
+        self.total = int(sum(self.rows))
+        self.row_begin = int(sum(self.rows[: self.rank]))
+        if weight_all.shape != (self.total,):
+            raise ValueError(f"weight_all must hold {self.total} counts, got {tuple(weight_all.shape)}")
+        self.weight_all = weight_all
+        self.cu_seqlens = torch.tensor([0, self.total], dtype=torch.int32, device=weight_all.device)
+        self.group = group
+        self._gather = gather
+        self._bias = {}
+
+    def bias(self, dtype: torch.dtype) -> torch.Tensor:
+        """``log(count)`` of every packed row of the scene in the attention dtype."""
+        if dtype not in self._bias:
+            self._bias[dtype] = self.weight_all.log().to(dtype)
+        return self._bias[dtype]
+
+    def gather(self, local: torch.Tensor) -> torch.Tensor:
+        """``[rows[rank], ...]`` of this rank -> ``[total, ...]`` of all ranks, in this GPU's memory."""
+        if local.shape[0] != self.rows[self.rank]:
+            raise ValueError(f"rank {self.rank} holds {local.shape[0]} rows, expected {self.rows[self.rank]}")
+        if self._gather is not None:
+            return self._gather(local, self.rows, self.rank)
+        if len(self.rows) == 1:
+            return local
+        return gather_rows(local, self.rows, self.group)

@@ -26,7 +26,7 @@ import torch
 from .block import JaggedBlock, JaggedBlock_w_Bias, forward_fused, fusable, residual_layernorm
 from .token_merger import JaggedTokens, MergePlan
 
-__all__ = ["FusedAggregator", "CapturedForward", "fused_accelerate"]
+__all__ = ["FusedAggregator", "ShardedFusedAggregator", "CapturedForward", "fused_accelerate"]
 
 
 class FusedAggregator(torch.nn.Module):
@@ -161,6 +161,63 @@ class FusedAggregator(torch.nn.Module):
 
         x = JaggedTokens(tokens=tokens.reshape(1, B * S * N, C), weight=weight, offset=frame_offset)
         output = self._run(x, pos, frame_view, global_view, self.plain_frame_blocks, self.plain_global_blocks, unmerge)
+        return output, self.patch_start_idx
+
+
+class ShardedFusedAggregator(FusedAggregator):
+    """The merged forward pass of ONE scene whose frames are spread over the ranks of a process group (one process per
+    GPU): every rank merges, runs and unmerges its own contiguous range of frames.  Everything row-wise (norms, GEMMs,
+    MLP, LayerScale, residuals) and the frame blocks need no other rank; a global block all-gathers the prepared key /
+    value rows of the packed tokens -- the only exchange -- and attends the local query rows to all of them
+    (:class:`come_b200.dist.GlobalExchange`).  The merge mask of all frames is replicated, so every rank derives the
+    packed row counts of all ranks without a collective.
+    """
+
+    def __init__(self, aggregator: torch.nn.Module, frames_total: int, world: int, rank: int, group=None, gather=None,
+                 use_attn_bias_correction: bool = True, attn_dtype: str = "bf16", fuse_elementwise: bool = True):
+        """``gather(local, rows, rank)`` replaces the process group's all-gather (single-process tests); by default the
+        rows travel through :func:`come_b200.dist.gather_rows` over ``group``."""
+        super().__init__(aggregator, use_attn_bias_correction, attn_dtype, fuse_elementwise)
+        from .dist import shard_range
+        self.frames_total, self.world, self.rank = int(frames_total), int(world), int(rank)
+        self.group, self._gather = group, gather
+        self.f_lo, self.f_hi = shard_range(self.frames_total, self.world, self.rank)
+
+    def build_plans(self, mask_all: torch.Tensor, layout) -> Tuple[MergePlan, MergePlan]:
+        """``mask_all [frames_total, M]`` (the same on every rank) -> (plan of the whole scene, plan of this rank's
+        frames)."""
+        if mask_all.shape[0] != self.frames_total:
+            raise ValueError(f"mask covers {mask_all.shape[0]} frames, the scene has {self.frames_total}")
+        return MergePlan(mask_all, layout), MergePlan(mask_all[self.f_lo:self.f_hi].contiguous(), layout)
+
+    def forward(self, tokens_local: torch.Tensor, global_plan: MergePlan, local_plan: MergePlan
+                ) -> Tuple[Dict[int, torch.Tensor], int]:
+        """``tokens_local [1, frames_local, N, C]``: this rank's frames ``[f_lo, f_hi)``.  Returns the retained layers of
+        those frames, ``{block index: [1, frames_local, N, 2C]}``."""
+        from .dist import GlobalExchange, rows_per_rank
+        B, S_local, N, C = tokens_local.shape
+        if B != 1 or S_local != self.f_hi - self.f_lo or local_plan.frames != S_local or global_plan.frames != self.frames_total:
+            raise ValueError(f"rank {self.rank} owns frames [{self.f_lo}, {self.f_hi}) of one scene, got tokens {tuple(tokens_local.shape)}")
+        rows = rows_per_rank(global_plan.offset.tolist(), self.world)
+        if rows[self.rank] != local_plan.total:
+            raise ValueError("the local plan is not this rank's slice of the scene's plan")
+        exchange = GlobalExchange(rows, self.rank, global_plan.weight, self.group, self._gather)
+        merged = local_plan.merge(tokens_local.reshape(S_local, N, C))
+        pos = local_plan.positions()
+        frame_offset = local_plan.offset
+        scene_offset = torch.tensor([0, local_plan.total], dtype=torch.int64, device=tokens_local.device)
+
+        def frame_view(x: JaggedTokens) -> JaggedTokens:
+            return JaggedTokens(x.tokens, x.weight, frame_offset, local_plan.max_seqlen)
+
+        def global_view(x: JaggedTokens) -> JaggedTokens:
+            return JaggedTokens(x.tokens, x.weight, scene_offset, exchange=exchange)
+
+        def unmerge(frame_tokens: torch.Tensor, global_tokens: torch.Tensor) -> torch.Tensor:
+            return local_plan.split_concat(frame_tokens, global_tokens).view(1, S_local, N, 2 * C)
+
+        x = JaggedTokens(tokens=merged.unsqueeze(0), weight=local_plan.weight, offset=frame_offset)
+        output = self._run(x, pos, frame_view, global_view, self.frame_blocks, self.global_blocks, unmerge)
         return output, self.patch_start_idx
 
 

@@ -40,16 +40,21 @@ class JaggedTokens:
     Two optional fields, absent from the reference's container, let a caller that already knows the longest segment
     spare the attention modules their device-to-host read (``flash_attn/__init__.py:33``): ``max_seqlen`` (an upper
     bound on the host) and ``max_seqlen_dev`` (the exact value as a one-element int32 device tensor; it lets a launch
-    sized for the bound skip the query blocks no segment reaches).  Both are None unless set."""
+    sized for the bound skip the query blocks no segment reaches).  Both are None unless set.
+
+    ``exchange`` (None unless set, also absent from the reference) marks tokens that are one rank's rows of a segment
+    spread over several GPUs: a :class:`come_b200.dist.GlobalExchange`, which the attention modules use to attend these
+    rows to the keys / values of all ranks."""
     tokens: torch.Tensor
     weight: torch.Tensor
     offset: torch.Tensor
     max_seqlen: Optional[int] = None
     max_seqlen_dev: Optional[torch.Tensor] = None
+    exchange: Optional[Any] = None
 
     def apply(self, func: Callable[[torch.Tensor], torch.Tensor]) -> "JaggedTokens":
         return JaggedTokens(tokens=func(self.tokens), weight=self.weight, offset=self.offset,
-                            max_seqlen=self.max_seqlen, max_seqlen_dev=self.max_seqlen_dev)
+                            max_seqlen=self.max_seqlen, max_seqlen_dev=self.max_seqlen_dev, exchange=self.exchange)
 
     def _on_device_path(self) -> bool:
         """The suffix kernels serve CUDA tensors in the library's layouts; anything else (CPU tensors, other weight or
