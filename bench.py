@@ -554,6 +554,96 @@ def run_frames100(args):
         dist.destroy_process_group()
 
 
+def run_model100(args):
+    """The alternating-attention stack (48 blocks with their GEMMs) on ONE scene of 100 frames sharded by frame over the
+    ranks (`ShardedFusedAggregator`): everything row-wise and the frame blocks are local, a global block all-gathers the
+    prepared K/V rows of the packed tokens.  Strong scaling: the scene is fixed."""
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    from come_b200 import _lib
+    from come_b200.fused import ShardedFusedAggregator
+    from come_b200.token_merger import select_windows
+    from come_b200.vggt_arch import AggregatorCore
+    frames = 100
+    pk = peaks()
+    core = AggregatorCore(depth=24).to(dev).bfloat16()  # seeded: the same weights on every rank
+    model = ShardedFusedAggregator(core, frames, world, rank)
+    layout = _lib.Layout.two_d(START, GRID, GRID, WIN, WIN)
+    g = torch.Generator(device="cpu").manual_seed(4321)
+    conf = torch.rand((1, frames * GRID * GRID), generator=g).bfloat16().to(dev)  # replicated
+    n_local = model.f_hi - model.f_lo
+    gl = torch.Generator(device=dev).manual_seed(100 + rank)
+    x = torch.randn((1, n_local, N_TOK, CH), device=dev, generator=gl).bfloat16()
+    ev = lambda: torch.cuda.Event(enable_timing=True)  # noqa: E731
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    plans = []
+
+    def step():
+        mask = select_windows(conf, 1, frames, GRID, GRID, WIN, WIN, 0.5, "pairwise-rank", "frame")
+        gp, lp = model.build_plans(mask, layout)
+        plans[:] = [gp, lp]
+        with torch.no_grad():
+            out, _ = model(x, gp, lp)
+        return out
+
+    for _ in range(min(args.warmup, 3)):
+        step()
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    s, e = ev(), ev()
+    s.record()
+    for _ in range(args.steps):
+        step()
+    e.record()
+    barrier()
+    ms = torch.tensor([s.elapsed_time(e)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    clocks = sampler.stop() if rank == 0 else None
+    assert _lib.device_status(clear=False) == 0
+    if rank == 0:
+        per_scene = ms.item() / args.steps
+        gp = plans[0]
+        P = gp.total
+        seg = (gp.offset[1:] - gp.offset[:-1]).tolist()
+        attn_flops = 24 * (sum(4.0 * L * L * HDIM * HEADS for L in seg) + 4.0 * P * P * HDIM * HEADS)
+        gemm_flops = 48 * 2.0 * P * CH * CH * 12
+        kv_bytes = P * 2 * HEADS * HDIM * 2
+        print(json.dumps({
+            "metric": "come_vggt_aggregator_ms_per_scene_100f", "value": per_scene, "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_scene, "higher_is_better": False,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic (seeded)",
+            "config": {"workload": "VGGT-1B-shaped alternating-attention stack (48 blocks incl. qkv / proj / MLP GEMMs, seeded "
+                                   "random bf16 weights) on one scene of 100 frames x 518x518, 3x3 windows at 50 % per frame",
+                       "merged_tokens": P, "frames_per_s": frames / per_scene * 1e3,
+                       "parallelism": f"frames sharded over {world} GPU(s); global blocks all-gather {kv_bytes / 1e6:.0f} MB of "
+                                      f"prepared K/V per block over NCCL",
+                       "l2": "inputs larger than L2"},
+            "tflop_per_scene": {"attention": attn_flops / 1e12, "gemm": gemm_flops / 1e12},
+            "tflops_aggregate": (attn_flops + gemm_flops) / (per_scene * 1e-3) / 1e12,
+            "frac_of_bf16_peak_per_gpu": (attn_flops + gemm_flops) / (per_scene * 1e-3) / 1e12 / world / pk["tflops"],
+            "clocks": clocks,
+        }))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def micro(torch, dev, pk):
     """Kernel-level numbers on inputs larger than L2: 100-frame fp32 merge / unmerge (GB/s) and the 64-segment
     ragged biased-attention sweep (TFLOP/s)."""
@@ -844,10 +934,11 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="come_b200", choices=["come_b200", "reference"])
-    ap.add_argument("--workload", default="scenes8", choices=["scenes8", "frames100", "batch256x4"],
+    ap.add_argument("--workload", default="scenes8", choices=["scenes8", "frames100", "batch256x4", "model100"],
                     help="scenes8: one independent 8-frame scene per GPU (default); frames100: ONE 100-frame scene whose "
                          "frames are sharded over the GPUs, global attention over all-gathered K/V; batch256x4: 256 independent "
-                         "4-frame scenes with per-frame merge ratios ~U(0.25,0.75), sharded by scene, reported as scenes/s")
+                         "4-frame scenes with per-frame merge ratios ~U(0.25,0.75), sharded by scene, reported as scenes/s; model100: the "
+                         "100-frame scene through the whole alternating-attention stack (with its GEMMs), sharded by frame")
     ap.add_argument("--no-micro", action="store_true", help="skip the kernel-level sweep")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     args = ap.parse_args()
@@ -863,6 +954,8 @@ def main():
     elif args.workload == "frames100":
         args.warmup = max(args.warmup, 3)
         run_frames100(args)
+    elif args.workload == "model100":
+        run_model100(args)
     else:
         args.warmup = max(args.warmup, 3)
         run_gpu(args)

@@ -265,3 +265,119 @@ def test_fused_elementwise_path_matches_module_path():
         assert _relative_error(to_np(a[layer]), to_np(b[layer])) < 1e-2
         assert _relative_error(to_np(a[layer]), ref[layer]) < FUSED_REL_TOL
         assert _relative_error(to_np(b[layer]), ref[layer]) < FUSED_REL_TOL
+
+
+# ---- one scene sharded by frame over ranks ----------------------------------------------------------------------------
+def _sharded_case(rng, frames, side=7, C=128, heads=2, depth=2, start=5):
+    N, M = start + side * side, (side // 3) ** 2
+    core, _ = _small_model(rng, depth, C, heads, 0.5, torch.bfloat16)
+    tokens = torch.from_numpy(rng.standard_normal((1, frames, N, C), dtype=np.float32)).bfloat16()
+    mask = torch.from_numpy(rng.random((frames, M)) < 0.5)
+    return core, tokens, mask, (start, side, side, 3, 3)
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_sharded_aggregator_emulated_ranks(world):
+    """Ranks emulated by host threads on one GPU: each runs ShardedFusedAggregator on its frames, and the K/V gather is a
+    rendezvous between the threads (nothing on the device waits for anything).  Every rank's retained layers must equal
+    its frames of the single-GPU result up to the rounding of differently tiled GEMMs."""
+    import threading
+    from come_b200 import _lib
+    from come_b200.fused import FusedAggregator, ShardedFusedAggregator
+    from come_b200.token_merger import MergePlan
+    rng = np.random.default_rng(17)
+    frames = 5
+    core, tokens, mask, lay = _sharded_case(rng, frames)
+    layout = _lib.Layout.two_d(*lay)
+    tokens, mask = tokens.cuda(), mask.cuda()
+    with torch.no_grad():
+        whole, _ = FusedAggregator(core)(tokens, MergePlan(mask, layout))
+    barrier = threading.Barrier(world)
+    slots = [None] * world
+    results, errors = [None] * world, []
+
+    def gather(local, rows, rank):  # every rank deposits its rows, waits for the others, reads all
+        slots[rank] = local
+        barrier.wait(timeout=120)
+        out = torch.cat(slots, dim=0)
+        barrier.wait(timeout=120)  # nobody overwrites a slot before everyone has read it
+        return out
+
+    def run(rank):
+        try:
+            torch.cuda.set_device(0)
+            model = ShardedFusedAggregator(core, frames, world, rank, gather=gather)
+            gp, lp = model.build_plans(mask, layout)
+            with torch.no_grad():
+                out, _ = model(tokens[:, model.f_lo:model.f_hi], gp, lp)
+            results[rank] = (model.f_lo, model.f_hi, out)
+        except Exception as e:  # noqa: BLE001
+            errors.append((rank, repr(e)))
+            barrier.abort()
+
+    threads = [threading.Thread(target=run, args=(r,)) for r in range(world)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join(timeout=300)
+    assert not errors, errors
+    torch.cuda.synchronize()
+    covered = 0
+    for lo, hi, out in results:
+        covered += hi - lo
+        for layer, ref in whole.items():
+            assert out[layer].shape == ref[:, lo:hi].shape
+            assert _relative_error(to_np(out[layer]), to_np(ref[:, lo:hi])) < 1e-2, (lo, hi, layer)
+    assert covered == frames
+
+
+def _sharded_worker(rank, world, port, q_out):
+    import os
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from come_b200 import _lib
+        from come_b200.fused import ShardedFusedAggregator
+        rng = np.random.default_rng(17)
+        core, tokens, mask, lay = _sharded_case(rng, 5)
+        core = core.to(dev)
+        model = ShardedFusedAggregator(core, 5, world, rank)
+        gp, lp = model.build_plans(mask.to(dev), _lib.Layout.two_d(*lay))
+        with torch.no_grad():
+            out, _ = model(tokens[:, model.f_lo:model.f_hi].to(dev), gp, lp)
+        q_out.put((rank, model.f_lo, model.f_hi, {k: v.float().cpu().numpy() for k, v in out.items()}))
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_sharded_aggregator_two_gpus():
+    """Two processes, one GPU each, NCCL all-gather of the K/V rows: against the single-GPU result."""
+    import socket
+    import torch.multiprocessing as mp
+    from come_b200 import _lib
+    from come_b200.fused import FusedAggregator
+    from come_b200.token_merger import MergePlan
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    q_out = ctx.Queue()
+    procs = [ctx.Process(target=_sharded_worker, args=(r, 2, port, q_out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [q_out.get(timeout=300) for _ in range(2)]
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    rng = np.random.default_rng(17)
+    core, tokens, mask, lay = _sharded_case(rng, 5)
+    with torch.no_grad():
+        whole, _ = FusedAggregator(core)(tokens.cuda(), MergePlan(mask.cuda(), _lib.Layout.two_d(*lay)))
+    for rank, lo, hi, out in results:
+        for layer, ref in whole.items():
+            assert _relative_error(out[layer], to_np(ref[:, lo:hi])) < 1e-2, (rank, layer)
