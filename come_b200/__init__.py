@@ -17,13 +17,13 @@ Host side in Python/PyTorch (device memory, streams), compute in ``libcome_b200.
 * :mod:`come_b200.block`                -- ``JaggedBlock`` / ``JaggedBlock_w_Bias`` and the block with LayerScale + residual
   add + LayerNorm fused (``residual_layernorm``, ``forward_fused``)
 * :mod:`come_b200.fused`                -- ``FusedAggregator``: the merged forward pass of the alternating-attention
-  stack, ``CapturedForward``: its CUDA-graph replay
+  stack, ``CapturedForward``: its CUDA-graph replay, ``ShardedFusedAggregator``: one scene sharded by frame over GPUs
 * :mod:`come_b200.timer`                -- ``Timer`` (named CUDA-event ranges and their percentile table)
 * :mod:`come_b200.vggt_arch`            -- seeded random VGGT-shaped blocks for tests and benchmarks
 * :mod:`come_b200.direct`               -- ``DirectAttention``: the per-layer replacement of ``block.attn.forward``
 * :mod:`come_b200.chain`                -- the standalone operator chain of a scene, also sharded by frame over GPUs
 * :mod:`come_b200.static_scene`         -- the chain as one CUDA graph with no device-to-host read
-* :mod:`come_b200.dist`                 -- frame / row sharding helpers and the K/V row all-gather
+* :mod:`come_b200.dist`                 -- frame / row sharding helpers, the K/V row all-gather, ``GlobalExchange``
 """
 from . import _lib  # noqa: F401
 
