@@ -64,3 +64,51 @@ def test_gather_rows_uneven_gloo(rows):
         assert p.exitcode == 0
     results = dict(q.get(timeout=10) for _ in range(2))
     assert results == {0: True, 1: True}
+
+
+def _exchange_worker(rank, world, port, rows, q):
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from come_b200.dist import GlobalExchange
+        total = sum(rows)
+        weight_all = torch.where(torch.arange(total) % 3 == 0, 9.0, 1.0)
+        ex = GlobalExchange(rows, rank, weight_all)
+        local = torch.arange(rows[rank] * 4, dtype=torch.float32).reshape(rows[rank], 2, 2) + 100 * rank
+        got = ex.gather(local)
+        want = torch.cat([torch.arange(rows[r] * 4, dtype=torch.float32).reshape(rows[r], 2, 2) + 100 * r for r in range(world)])
+        ok = torch.equal(got, want) and ex.row_begin == sum(rows[:rank]) and ex.total == total
+        ok = ok and ex.cu_seqlens.tolist() == [0, total] and torch.equal(ex.bias(torch.float32), weight_all.log())
+        q.put((rank, ok))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_global_exchange_gloo():
+    """The exchange object of a frame-sharded global block over two gloo ranks: row bookkeeping, replicated bias, gather."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_exchange_worker, args=(r, 2, port, [5, 3], q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    assert dict(q.get(timeout=10) for _ in range(2)) == {0: True, 1: True}
+
+
+def test_global_exchange_checks_and_custom_gather():
+    from come_b200.dist import GlobalExchange
+    w = torch.ones(7)
+    calls = []
+    ex = GlobalExchange([3, 4], 1, w, gather=lambda local, rows, rank: calls.append((tuple(local.shape), rows, rank)) or torch.zeros(7, 2))
+    assert ex.row_begin == 3 and ex.gather(torch.zeros(4, 2)).shape == (7, 2) and calls == [((4, 2), [3, 4], 1)]
+    with pytest.raises(ValueError):
+        ex.gather(torch.zeros(3, 2))       # not this rank's row count
+    with pytest.raises(ValueError):
+        GlobalExchange([3, 4], 0, torch.ones(6))
+    single = GlobalExchange([7], 0, w)
+    t = torch.zeros(7, 2)
+    assert single.gather(t) is t           # one rank: nothing to exchange
