@@ -39,7 +39,7 @@ class _JaggedAttentionBase(torch.nn.Module):
             self._rope = RotaryPositionEmbedding2D(frequency=float(rope.base_frequency))
 
     def _attend_local(self, x: JaggedTokens, prepared, max_seqlen: Optional[int], use_bias: bool) -> torch.Tensor:
-        cu_seqlens = x.offset.to(torch.int32)
+        cu_seqlens = x.cu_seqlens if x.cu_seqlens is not None else x.offset.to(torch.int32)
         max_seqlen_dev = None
         if max_seqlen is None:
             max_seqlen, max_seqlen_dev = x.max_seqlen, x.max_seqlen_dev
@@ -82,7 +82,7 @@ class _JaggedAttentionBase(torch.nn.Module):
         if proj_drop is not None:
             out = proj_drop(out)
         return JaggedTokens(tokens=out.unsqueeze(0), weight=x.weight, offset=x.offset, max_seqlen=x.max_seqlen,
-                            max_seqlen_dev=x.max_seqlen_dev, exchange=x.exchange)
+                            max_seqlen_dev=x.max_seqlen_dev, exchange=x.exchange, cu_seqlens=x.cu_seqlens)
 
 
 class JaggedAttention_w_Bias(_JaggedAttentionBase):

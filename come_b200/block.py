@@ -120,8 +120,8 @@ def forward_fused(wrapper: _JaggedBlockBase, x: JaggedTokens, normed: torch.Tens
     the LayerNorm statistics."""
     block = wrapper.block
     P, Cc = x.tokens.shape[1], x.tokens.shape[2]
-    attn_x = wrapper.attn(JaggedTokens(normed.unsqueeze(0), x.weight, x.offset, x.max_seqlen, x.max_seqlen_dev, x.exchange), pos=pos)
+    attn_x = wrapper.attn(JaggedTokens(normed.unsqueeze(0), x.weight, x.offset, x.max_seqlen, x.max_seqlen_dev, x.exchange, x.cu_seqlens), pos=pos)
     stream, h = residual_layernorm(x.tokens.reshape(P, Cc), attn_x.tokens.reshape(P, Cc), _layer_scale_gamma(block.ls1)[1], block.norm2)
     mlp_x = block.mlp(h)
     stream, next_normed = residual_layernorm(stream, mlp_x, _layer_scale_gamma(block.ls2)[1], next_norm)
-    return JaggedTokens(stream.unsqueeze(0), x.weight, x.offset, x.max_seqlen, x.max_seqlen_dev, x.exchange), next_normed
+    return JaggedTokens(stream.unsqueeze(0), x.weight, x.offset, x.max_seqlen, x.max_seqlen_dev, x.exchange, x.cu_seqlens), next_normed

@@ -118,11 +118,13 @@ class FusedAggregator(torch.nn.Module):
             frame_max, frame_max_dev = plan.max_seqlen, None
             global_max, global_max_dev = (plan.total, None) if B == 1 else (None, None)
 
+        frame_cu, global_cu = plan.cu_seqlens(1), plan.cu_seqlens(S)  # the plan's int32 offsets: no cast per block
+
         def frame_view(x: JaggedTokens) -> JaggedTokens:
-            return JaggedTokens(x.tokens, x.weight, frame_offset, frame_max, frame_max_dev)
+            return JaggedTokens(x.tokens, x.weight, frame_offset, frame_max, frame_max_dev, cu_seqlens=frame_cu)
 
         def global_view(x: JaggedTokens) -> JaggedTokens:
-            return JaggedTokens(x.tokens, x.weight, global_offset, global_max, global_max_dev)
+            return JaggedTokens(x.tokens, x.weight, global_offset, global_max, global_max_dev, cu_seqlens=global_cu)
 
         def unmerge(frame_tokens: torch.Tensor, global_tokens: torch.Tensor) -> torch.Tensor:
             return plan.split_concat(frame_tokens, global_tokens).view(B, S, N, 2 * C)

@@ -51,10 +51,12 @@ class JaggedTokens:
     max_seqlen: Optional[int] = None
     max_seqlen_dev: Optional[torch.Tensor] = None
     exchange: Optional[Any] = None
+    cu_seqlens: Optional[torch.Tensor] = None  # ``offset`` as int32, when the caller keeps it (spares a cast per block)
 
     def apply(self, func: Callable[[torch.Tensor], torch.Tensor]) -> "JaggedTokens":
         return JaggedTokens(tokens=func(self.tokens), weight=self.weight, offset=self.offset,
-                            max_seqlen=self.max_seqlen, max_seqlen_dev=self.max_seqlen_dev, exchange=self.exchange)
+                            max_seqlen=self.max_seqlen, max_seqlen_dev=self.max_seqlen_dev, exchange=self.exchange,
+                            cu_seqlens=self.cu_seqlens)
 
     def _on_device_path(self) -> bool:
         """The suffix kernels serve CUDA tensors in the library's layouts; anything else (CPU tensors, other weight or
