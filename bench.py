@@ -840,14 +840,16 @@ def run_only(args):
     print(json.dumps(out))
 
 
-def aggregator_measure(S, depth, iters, arms_wanted="", report=True):
+def aggregator_measure(S, depth, iters, arms_wanted="", report=True, B=1, ragged=False):
     """End-to-end driver in the form of the reference's benchmark (``src/bench.py:13-46``): the unmerged model and the
     accelerated model are run over the same synthetic scenes inside ``Timer.range`` and the timer's table is printed.
     The model is the alternating-attention stack of a VGGT-1B-shaped aggregator with seeded random weights in bf16
     (24 frame + 24 global blocks, width 1024, 16 heads, q/k norm, rotary embedding, LayerScale, MLP ratio 4); the patch
     encoder and the heads are outside.  A scene's work in the accelerated arm: confidence head (seeded 2-layer MLP) ->
     window selection -> merge plan -> merge -> 48 blocks on packed tokens -> unmerge of the retained layers.
-    GEMMs are PyTorch's (cuBLAS); everything else on the packed tokens is this library's kernels."""
+    GEMMs are PyTorch's (cuBLAS); everything else on the packed tokens is this library's kernels.
+    ``B`` independent scenes per call (frame blocks attend inside a frame, global blocks inside a scene); ``ragged``:
+    every frame gets its own merge ratio ~U(0.25, 0.75), so the packed lengths differ from frame to frame."""
     import torch
     from come_b200 import _lib
     from come_b200.fused import CapturedForward, FusedAggregator
@@ -863,11 +865,15 @@ def aggregator_measure(S, depth, iters, arms_wanted="", report=True):
     head = torch.nn.Sequential(torch.nn.Linear(CH, 128), torch.nn.GELU(), torch.nn.Linear(128, 1)).to(dev).bfloat16().eval()
     layout = _lib.Layout.two_d(START, GRID, GRID, WIN, WIN)
     g = torch.Generator(device=dev).manual_seed(0)
-    scenes = [torch.randn((1, S, N_TOK, CH), device=dev, generator=g).bfloat16() for _ in range(iters)]
+    scenes = [torch.randn((B, S, N_TOK, CH), device=dev, generator=g).bfloat16() for _ in range(iters)]
+    ratios = (0.25 + 0.5 * torch.rand(B * S, device=dev, generator=g)) if ragged else None
 
     def plan_of(tokens):
-        conf = head(tokens[:, :, START:, :]).reshape(1, S * GRID * GRID)
-        mask = select_windows(conf, 1, S, GRID, GRID, WIN, WIN, 0.5, "pairwise-rank", "batch")
+        conf = head(tokens[:, :, START:, :]).reshape(B, S * GRID * GRID)
+        if ragged:
+            mask = select_windows(conf, B, S, GRID, GRID, WIN, WIN, ratios, "pairwise-rank", "frame")
+        else:
+            mask = select_windows(conf, B, S, GRID, GRID, WIN, WIN, 0.5, "pairwise-rank", "batch")
         return MergePlan(mask, layout)
 
     arms = {
@@ -897,14 +903,16 @@ def aggregator_measure(S, depth, iters, arms_wanted="", report=True):
         print(Timer.report(), file=sys.stderr)
     Timer.reset()
     assert _lib.device_status(clear=False) == 0
-    P = float(np.mean(packed))
+    P = float(np.mean(packed)) / B  # per scene
     blocks = 2 * depth
     gemm = lambda rows: blocks * 2.0 * rows * CH * CH * 12  # qkv 3, proj 1, fc1 4, fc2 4  # noqa: E731
     attn = lambda rows: depth * 4.0 * HDIM * HEADS * (rows * rows + S * (rows / S) ** 2)  # noqa: E731
     return {
-        "only": "aggregator", "frames": S, "blocks": blocks, "scenes": len(scenes), "dtype": "bf16",
+        "only": "aggregator", "frames": S, "scenes_per_call": B, "merge_ratio": "per frame ~U(0.25, 0.75)" if ragged else 0.5,
+        "blocks": blocks, "calls": len(scenes), "dtype": "bf16",
         "packed_tokens_mean": P, "dense_tokens": S * N_TOK, "graphs_captured": len(captured._graphs),
-        "ms_per_scene": {k: round(v.P50, 3) for k, v in entries.items()},
+        "ms_per_scene": {k: round(v.P50 / B, 3) for k, v in entries.items()},
+        "scenes_per_s": {k: round(B / v.P50 * 1e3, 1) for k, v in entries.items()},
         "speedup_vs_unmerged": ({k: round(entries["Reference Model"].P50 / v.P50, 3) for k, v in entries.items()}
                                 if "Reference Model" in entries else None),
         "tflop_per_scene": {"unmerged": round((gemm(S * N_TOK) + attn(S * N_TOK)) / 1e12, 2),
@@ -915,7 +923,7 @@ def aggregator_measure(S, depth, iters, arms_wanted="", report=True):
 
 def run_aggregator(args):
     S = 8 if args.frames == 100 else args.frames  # 100 is the flag's default, meant for the merge kernels
-    print(json.dumps(aggregator_measure(S, args.depth, args.iters, args.arms)))
+    print(json.dumps(aggregator_measure(S, args.depth, args.iters, args.arms, B=args.scenes, ragged=args.ragged)))
 
 
 def main():
@@ -923,6 +931,8 @@ def main():
     ap.add_argument("--only", choices=["attn", "merge", "unmerge", "merge_ln", "unmerge_res", "prepare", "residual_ln", "direct", "aggregator"],
                     help="run one kernel family on one size and exit; aggregator = the end-to-end model driver")
     ap.add_argument("--depth", type=int, default=24, help="--only aggregator: frame/global block pairs")
+    ap.add_argument("--scenes", type=int, default=1, help="--only aggregator: independent scenes per call")
+    ap.add_argument("--ragged", action="store_true", help="--only aggregator: per-frame merge ratios ~U(0.25, 0.75)")
     ap.add_argument("--arms", default="", help="--only aggregator: comma list of reference, accelerated, graph (default all)")
     ap.add_argument("--frames", type=int, default=100, help="--only merge/unmerge: frames")
     ap.add_argument("--dtype", default="f32", choices=["f32", "bf16"], help="--only merge/unmerge: element type")

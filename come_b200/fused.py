@@ -116,7 +116,9 @@ class FusedAggregator(torch.nn.Module):
             global_max_dev = (global_offset[1:] - global_offset[:-1]).max().to(torch.int32).reshape(1)
         else:
             frame_max, frame_max_dev = plan.max_seqlen, None
-            global_max, global_max_dev = (plan.total, None) if B == 1 else (None, None)
+            # several scenes: one read of the longest scene per forward pass (not one per global block)
+            global_max = plan.total if B == 1 else int((global_offset[1:] - global_offset[:-1]).max().item())
+            global_max_dev = None
 
         frame_cu, global_cu = plan.cu_seqlens(1), plan.cu_seqlens(S)  # the plan's int32 offsets: no cast per block
 
