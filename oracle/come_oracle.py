@@ -6,8 +6,10 @@ product package, which must fail loudly when its CUDA library is missing.
 
 Every function cites the reference file (paths relative to the reference project root) it restates.
 Pinned against the reference: the committed fixtures under ``tests/golden`` were produced by importing the
-reference's own PyTorch implementation on CPU (``tests/golden/make_golden.py``) and against the literal
-known-answer cases of the reference's test-suite (``tests/golden/reference_cases.py``).
+reference's own PyTorch implementation on CPU (``tests/golden/make_golden.py``: the merge / split functions, the
+2-D merger, ``build_ctx``, ``prepare_packed_self_attention_qkv`` with the rotary module, the model's ``Block`` and the
+``JaggedTokens`` suffix methods) and against the literal known-answer cases of the reference's test-suite
+(``tests/golden/reference_cases.py``).
 """
 from __future__ import annotations
 
