@@ -106,6 +106,9 @@ def cpu_chain_sample(frames=FRAMES, attn_rows=1024):
     slice: frame layers on 1 head x 1 frame x all rows, the global layer on 1 head x `attn_rows` query rows against
     all keys.  The slices are scaled to all heads / frames / rows and summed over the 48 layers."""
     from oracle import clib
+    # all the host threads this process may use: a multi-process launcher exports OMP_NUM_THREADS=1 for its workers,
+    # which would time the CPU path on one core
+    clib.set_num_threads(len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1))
     rng = np.random.default_rng(0)
     tokens = rng.standard_normal((frames, N_TOK, CH), dtype=np.float32)
     conf = rng.random((1, frames * GRID * GRID), dtype=np.float32)

@@ -33,6 +33,11 @@ def num_threads() -> int:
     return int(lib().orc_num_threads())
 
 
+def set_num_threads(n: int) -> None:
+    """OpenMP threads of the following calls."""
+    lib().orc_set_num_threads(C.c_int(int(n)))
+
+
 def layout2d(start, H, W, gh, gw):
     src = np.empty(start + H * W, np.int64)
     prefix = lib().orc_layout2d(C.c_int64(start), C.c_int64(H), C.c_int64(W), C.c_int64(gh), C.c_int64(gw), _p(src))

@@ -198,6 +198,15 @@ void orc_attention(const float *q, const float *k, const float *v, int64_t row_s
         }
 }
 
+/* Number of OpenMP threads of the following calls (a launcher may have exported OMP_NUM_THREADS=1 for its workers). */
+void orc_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 int orc_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();
