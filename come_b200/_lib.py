@@ -12,7 +12,7 @@ LIB_PATH = os.path.join(HERE, "libcome_b200.so")
 
 COME_F32, COME_F16, COME_BF16 = 0, 1, 2
 COME_OK, COME_ERR_ARG, COME_ERR_CUDA, COME_ERR_UNSUPPORTED, COME_ERR_DEVICE = 0, -1, -2, -3, -4
-COME_SELECT_RANK, COME_SELECT_ABS = 0, 1
+COME_SELECT_RANK, COME_SELECT_ABS, COME_SELECT_ZSCORE = 0, 1, 2
 COME_SCOPE_BATCH, COME_SCOPE_FRAME = 0, 1
 
 EXPORTS = (

@@ -27,6 +27,7 @@
 
 #include <cuda.h>
 
+#include <mutex>
 #include <type_traits>
 
 namespace come {
@@ -65,6 +66,31 @@ constexpr float kRescaleThreshold = 8.0f;  // log2 units
 constexpr uint32_t kPolyPairs = COME_POLY_MASK;
 constexpr float kMasked = -3.0e38f;        // "minus infinity" of a masked key, still finite in bfloat16
 
+// Development builds (-DCOME_ATTN_TRACE) accumulate, per warp, the clocks spent in each kind of wait of the key loop and
+// leave them in a device array that come_debug_attn_trace() copies out; normal builds carry none of it.
+#ifdef COME_ATTN_TRACE
+constexpr int kTraceSlots = 12;
+__device__ unsigned long long g_attn_trace[256 * (kThreads / 32) * kTraceSlots];
+#define TRACE_DECL() long long tr_acc[kTraceSlots] = {}; long long tr_t = 0; (void)tr_t
+#define TRACE_BEGIN() tr_t = clock64()
+#define TRACE_END(slot) tr_acc[slot] += clock64() - tr_t
+#define TRACE_COUNT(slot, n) tr_acc[slot] += (n)
+#define TRACE_STAMP(slot, cond) do { if (cond) tr_acc[slot] = clock64(); } while (0)
+#define TRACE_FLUSH()                                                                                          \
+    do {                                                                                                       \
+        if ((threadIdx.x & 31) == 0 && blockIdx.x < 256)                                                       \
+            for (int i__ = 0; i__ < kTraceSlots; ++i__)                                                        \
+                g_attn_trace[(blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5)) * kTraceSlots + i__] = (unsigned long long)tr_acc[i__]; \
+    } while (0)
+#else
+#define TRACE_DECL()
+#define TRACE_BEGIN()
+#define TRACE_END(slot)
+#define TRACE_COUNT(slot, n)
+#define TRACE_STAMP(slot, cond)
+#define TRACE_FLUSH()
+#endif
+
 struct SharedStorage {
     alignas(1024) uint8_t q[kTiles][2][kQTileBytes];        // [query tile][buffer]: the next item's Q is loaded ahead
     alignas(1024) uint8_t kv[kStages][kKvTileBytes];
@@ -82,6 +108,7 @@ struct SharedStorage {
     uint64_t o_done[kTiles];
     uint64_t s_empty[kTiles];
     uint32_t tmem_base;
+    uint32_t pipe_lock;  // held by the issuer warp that is feeding the tensor pipe (see pipe_acquire)
     volatile uint32_t abort_flag;
     int scan_warp[kThreads / 32];
 };
@@ -128,6 +155,32 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, Shared
             return false;
         }
     }
+}
+
+// The three issuer warps feed one tensor pipe.  Two warps that issue at the same time have their instructions
+// interleaved by the hardware, so both groups finish late and the two query tiles stay in lock step, colliding again
+// at every key tile.  With the lock a group (the Q K^T of a key tile, or its P V) is issued as a whole: the warp that
+// comes second is delayed once by the first one's group and from then on the tiles run out of phase, each finding the
+// pipe free when its turn comes.  Bounded like every other wait of the kernel.
+__device__ __forceinline__ bool pipe_acquire(SharedStorage &sh, unsigned int *status, uint32_t code, int lane) {
+    bool ok = true;
+    if (lane == 0) {
+        const long long t0 = clock64();
+        while (atomicCAS(&sh.pipe_lock, 0u, 1u) != 0u) {
+            if (sh.abort_flag != 0) { ok = false; break; }
+            if (clock64() - t0 > kWaitTicks) {
+                sh.abort_flag = 1;
+                atomicOr(status, code);
+                ok = false;
+                break;
+            }
+        }
+    }
+    return __all_sync(0xffffffffu, ok);
+}
+__device__ __forceinline__ void pipe_release(SharedStorage &sh, int lane) {
+    __syncwarp();
+    if (lane == 0) atomicExch(&sh.pipe_lock, 0u);
 }
 
 __device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *map, int c0, int c1, int c2, uint64_t *bar) {
@@ -299,7 +352,7 @@ __host__ __device__ constexpr uint32_t make_idesc(bool bf16, int M, int N, bool 
 
 enum : uint32_t {
     kErrQFull = 1u << 0, kErrKvFull = 1u << 1, kErrKvEmpty = 1u << 2, kErrSlabFull = 1u << 3, kErrSlabEmpty = 1u << 4,
-    kErrSFull = 1u << 5, kErrSEmpty = 1u << 6, kErrPFull = 1u << 7, kErrODone = 1u << 8,
+    kErrSFull = 1u << 5, kErrSEmpty = 1u << 6, kErrPFull = 1u << 7, kErrODone = 1u << 8, kErrPipeLock = 1u << 9,
 };
 
 // One work item = the (up to) kTiles 128-row query tiles [q_row0, q_row0 + kTiles * 128) of one (segment, head).
@@ -427,6 +480,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     if (threadIdx.x == 0) {
         // an earlier CTA that gave up leaves the status word raised: later CTAs then skip their work
         sh.abort_flag = (*(volatile unsigned int *)status != 0) ? 1u : 0u;
+        sh.pipe_lock = 0u;
         for (int i = 0; i < kTiles; ++i) {
             for (int b = 0; b < 2; ++b) {
                 mbar_init(&sh.q_full[i][b], 1);
@@ -557,6 +611,10 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         int slab_it = 0;   // bias slab ring position
         int step = 0;      // key tiles this query tile has processed so far (phase of s_full / s_empty / p_full / o_done)
         int q_uses = 0;    // items in which this query tile was active (phase of q_full / q_empty)
+        TRACE_DECL();
+#ifdef COME_ATTN_TRACE
+        const long long tr_start = clock64();
+#endif
         for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
             const WorkItem w = decode_item<kPrefix>(item, nblk_x, nseg, cu, q_begin, q_end, seg_prefix);
             if (!w.valid) continue;
@@ -594,12 +652,20 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 const int k_it = it + 2 * jj, k_slot = k_it % kStages;
                 const bool slab = uses_slab(w, jj);
                 const int bs = slab_it % kSlabStages;
+                TRACE_BEGIN();
                 bool good = mbar_wait(&sh.kv_full[k_slot], (k_it / kStages) & 1, sh, status, kErrKvFull);
                 if (good && slab) good = mbar_wait(&sh.slab_full[bs], (slab_it / kSlabStages) & 1, sh, status, kErrSlabFull);
+                TRACE_END(0);
+                TRACE_BEGIN();
                 // the softmax group must have pulled the previous scores (also those of the previous item) out of S
                 if (good && step + jj > 0) good = mbar_wait(&sh.s_empty[t], (step + jj - 1) & 1, sh, status, kErrSEmpty);
+                TRACE_END(1);
+                TRACE_STAMP(8, step + jj == 65);
                 good = __all_sync(0xffffffffu, good);
                 if (!good) return false;
+#ifdef COME_PIPE_LOCK
+                if (!pipe_acquire(sh, status, kErrPipeLock, lane)) return false;
+#endif
                 tc_fence_after();
                 const uint64_t k_desc = kv_desc0 + (uint64_t)(k_slot * (kKvTileBytes >> 4));
                 tc_mma_ss(s_tmem, q_desc + 0, k_desc + 0, idesc_qk, 0u);
@@ -614,6 +680,10 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     ++slab_it;
                 }
                 if (jj == w.n_kv - 1) tc_commit(&sh.q_empty[t][qb]);  // the item's last use of the query tile
+#ifdef COME_PIPE_LOCK
+                pipe_release(sh, lane);
+#endif
+                TRACE_STAMP(11, step + jj == 65);
                 return true;
             };
             ok = issue_s(0);
@@ -623,10 +693,20 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     if (!ok) break;
                 }
                 const int v_it = it + 2 * j + 1, v_slot = v_it % kStages;
+                TRACE_BEGIN();
                 ok = mbar_wait(&sh.kv_full[v_slot], (v_it / kStages) & 1, sh, status, kErrKvFull);
+                TRACE_END(2);
+                TRACE_BEGIN();
                 if (ok) ok = mbar_wait(&sh.p_full[t], (step + j) & 1, sh, status, kErrPFull);
+                TRACE_END(3);
+                TRACE_COUNT(5, 1);
+                TRACE_STAMP(9, step + j == 64);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
+#ifdef COME_PIPE_LOCK
+                ok = pipe_acquire(sh, status, kErrPipeLock, lane);
+                if (!ok) break;
+#endif
                 tc_fence_after();
                 const uint64_t v_desc = kv_desc0 + (uint64_t)(v_slot * (kKvTileBytes >> 4));
                 // 16 keys per instruction: 8 columns of 16-bit pairs of P, 16 rows (2048 bytes) of the V tile
@@ -635,11 +715,19 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     tc_mma_ts(o_tmem, p_tmem + 8 * i, v_desc + (uint64_t)(i * 128), idesc_pv, (j > 0 || i > 0) ? 1u : 0u);
                 tc_commit(&sh.o_done[t]);
                 tc_commit(&sh.kv_empty[v_slot]);
+#ifdef COME_PIPE_LOCK
+                pipe_release(sh, lane);
+#endif
+                TRACE_STAMP(10, step + j == 64);
             }
             it += 2 * w.n_kv;
             step += w.n_kv;
             ++q_uses;
         }
+#ifdef COME_ATTN_TRACE
+        tr_acc[4] = clock64() - tr_start;
+#endif
+        TRACE_FLUSH();
         __syncwarp();
     } else {
         // ===== softmax group of query tile t ================================================================
@@ -652,6 +740,10 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         const uint32_t p_tmem = tmem + lane_addr + kTmemP + t * (kBlockN / 2);
         bool ok = true;
         int step = 0;  // key tiles processed so far by this query tile: phase of s_full / s_empty / p_full / o_done
+        TRACE_DECL();
+#ifdef COME_ATTN_TRACE
+        const long long tr_start = clock64();
+#endif
         for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
             const WorkItem w = decode_item<kPrefix>(item, nblk_x, nseg, cu, q_begin, q_end, seg_prefix);
             if (!w.valid || t >= w.n_mt) continue;
@@ -660,10 +752,16 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             float m_ref = -INFINITY, l = 0.0f;  // reference max (log2 units, scale applied) and running sum
 
             for (int j = 0; j < n_kv && ok; ++j) {
+                TRACE_BEGIN();
                 ok = mbar_wait(&sh.s_full[t], (step + j) & 1, sh, status, kErrSFull);
+                TRACE_END(0);
+                TRACE_COUNT(5, 1);
+                TRACE_STAMP(8, step + j == 64);
+                TRACE_STAMP(9, step + j == 65);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tc_fence_after();
+                TRACE_BEGIN();
                 // The whole row of kBlockN scores is pulled into registers at once, which frees S for the next Q K^T right
                 // away; the row is then turned into probabilities 32 columns at a time.
                 constexpr int kQuarters = kBlockN / 32;
@@ -671,6 +769,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
 #pragma unroll
                 for (int q = 0; q < kQuarters; ++q) tmem_ld32(s_tmem + 32 * q, srow[q]);
                 tc_wait_ld();
+                TRACE_END(1);
                 tc_fence_before();
                 mbar_arrive(&sh.s_empty[t]);
                 bool o_ready = (j == 0);  // P V of the previous key tile complete: O stable, P buffer free
@@ -727,7 +826,9 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     uint32_t pk[16];
                     quarter(srow[0], pk);
                     if (!o_ready) {  // the P buffer is free once P V of the previous key tile has completed
+                        TRACE_BEGIN();
                         ok = mbar_wait(&sh.o_done[t], (step + j - 1) & 1, sh, status, kErrODone);
+                        TRACE_END(2);
                         ok = __all_sync(0xffffffffu, ok);
                         if (!ok) break;
                         tc_fence_after();
@@ -746,15 +847,21 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     l += s_lo + s_hi;
                 }
                 if (!ok) break;
+                TRACE_BEGIN();
                 tc_wait_st();
+                TRACE_END(3);
                 tc_fence_before();
                 mbar_arrive(&sh.p_full[t]);
+                TRACE_STAMP(10, step + j == 64);
             }
 
+            TRACE_BEGIN();
             if (ok) {
                 ok = mbar_wait(&sh.o_done[t], (step + n_kv - 1) & 1, sh, status, kErrODone);
                 ok = __all_sync(0xffffffffu, ok);
             }
+            TRACE_END(6);
+            TRACE_BEGIN();
             if (ok) {
                 tc_fence_after();
                 uint32_t o[2][32];
@@ -787,8 +894,13 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     if (lse) lse[(int64_t)w.head * (q_end - q_begin) + (row - q_begin)] = (m_ref + log2f(l)) * kLn2;
                 }
             }
+            TRACE_END(7);
             step += n_kv;
         }
+#ifdef COME_ATTN_TRACE
+        tr_acc[4] = clock64() - tr_start;
+#endif
+        TRACE_FLUSH();
     }
 
     // ===== common exit ==========================================================================================
@@ -810,21 +922,46 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 EncodeTiledFn encode_fn() {
+    static std::once_flag once;
     static EncodeTiledFn fn = nullptr;
-    static bool tried = false;
-    if (!tried) {
-        tried = true;
+    std::call_once(once, [] {
         void *p = nullptr;
         cudaDriverEntryPointQueryResult qres;
         if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
             qres == cudaDriverEntryPointSuccess)
             fn = (EncodeTiledFn)p;
-    }
+    });
     return fn;
 }
 
 // [total, H, 64] view with arbitrary row stride; box = box_rows rows x 1 head x 64 elements, 128-byte swizzle.
+// A tensor map is a pure function of these arguments (it holds an address, not a snapshot of memory), so each host
+// thread keeps the last few it encoded: a model that calls attention layer after layer on the same buffers encodes
+// them once instead of three times per launch.
+struct MapKey {
+    const void *base;
+    int64_t total, row_stride;
+    int dtype, H, box_rows;
+    bool operator==(const MapKey &o) const {
+        return base == o.base && total == o.total && row_stride == o.row_stride && dtype == o.dtype && H == o.H && box_rows == o.box_rows;
+    }
+};
+constexpr int kMapCacheSlots = 16;
+struct MapCache {
+    MapKey key[kMapCacheSlots];
+    CUtensorMap map[kMapCacheSlots];
+    bool used[kMapCacheSlots];
+    int next;
+};
+
 int make_map(CUtensorMap *map, const void *base, int dtype, int64_t total, int H, int64_t row_stride, int box_rows) {
+    thread_local MapCache cache = {};
+    const MapKey key{base, total, row_stride, dtype, H, box_rows};
+    for (int i = 0; i < kMapCacheSlots; ++i)
+        if (cache.used[i] && cache.key[i] == key) {
+            *map = cache.map[i];
+            return COME_OK;
+        }
     EncodeTiledFn fn = encode_fn();
     if (!fn) {
         set_error("cuTensorMapEncodeTiled is not available from the CUDA driver");
@@ -841,6 +978,11 @@ int make_map(CUtensorMap *map, const void *base, int dtype, int64_t total, int H
         set_error("cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
         return COME_ERR_CUDA;
     }
+    const int slot = cache.next;
+    cache.next = (slot + 1) % kMapCacheSlots;
+    cache.key[slot] = key;
+    cache.map[slot] = *map;
+    cache.used[slot] = true;
     return COME_OK;
 }
 
@@ -857,15 +999,24 @@ bool attn_sm100_supported(const AttnArgs &a) {
     return true;
 }
 
-// The shared-memory opt-in of a kernel is set once per device and dtype (not again on every launch, so that
-// launches stay cheap and legal inside a stream capture).  Returns whether it was already done and marks it done.
-static bool attr_done(int which) {
+// The shared-memory opt-in of a kernel is set once per device and instantiation (not again on every launch, so that
+// launches stay cheap and legal inside a stream capture).  Host threads may race to the first launch: the flag is
+// raised only after cudaFuncSetAttribute has succeeded, under a mutex, so no thread launches before the opt-in exists
+// and a failed attempt is retried by the next launch.
+template <typename Kernel> static int ensure_smem_optin(Kernel kernel, int slot, size_t smem) {
+    static std::mutex mu;
     static bool done[64][4];
     int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
-    const bool was = done[dev][which];
-    done[dev][which] = true;
-    return was;
+    COME_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) {
+        set_error("come_attn_varlen_fwd: device ordinal %d is out of the supported range", dev);
+        return COME_ERR_ARG;
+    }
+    std::lock_guard<std::mutex> lock(mu);
+    if (done[dev][slot]) return COME_OK;
+    COME_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    done[dev][slot] = true;
+    return COME_OK;
 }
 
 int attn_sm100_launch(const AttnArgs &a, cudaStream_t stream) {
@@ -893,8 +1044,7 @@ int attn_sm100_launch(const AttnArgs &a, cudaStream_t stream) {
     const float inv_scale = 1.0f / a.scale;
 #define COME_ATTN_LAUNCH(BF16, PREFIX, SLOT)                                                                                   \
     do {                                                                                                                       \
-        if (!attr_done(SLOT))                                                                                                  \
-            COME_CUDA(cudaFuncSetAttribute(attn_fwd_sm100_kernel<BF16, PREFIX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+        if ((rc = ensure_smem_optin(attn_fwd_sm100_kernel<BF16, PREFIX>, SLOT, smem)) != COME_OK) return rc;                    \
         attn_fwd_sm100_kernel<BF16, PREFIX><<<grid, kThreads, smem, stream>>>(mq, mk, mv, a.bias, a.cu, scale_log2, inv_scale, a.out, \
                                                                               a.o_rs, a.lse, (int)a.q_begin, (int)a.q_end, nblk_x,   \
                                                                               a.nseg, a.H, a.max_seqlen_dev, status);               \
@@ -911,3 +1061,12 @@ int attn_sm100_launch(const AttnArgs &a, cudaStream_t stream) {
 }
 
 }  // namespace come
+
+#ifdef COME_ATTN_TRACE
+// Development builds only: copies the per-warp wait counters of the last attention launch to host memory.
+extern "C" int come_debug_attn_trace(unsigned long long *host_out, int n_words) {
+    const size_t bytes = sizeof(unsigned long long) * (size_t)n_words;
+    if (bytes > sizeof(come::g_attn_trace)) return COME_ERR_ARG;
+    return cudaMemcpyFromSymbol(host_out, come::g_attn_trace, bytes) == cudaSuccess ? COME_OK : COME_ERR_CUDA;
+}
+#endif

@@ -12,6 +12,10 @@ constexpr int kSelectThreads = 512;
 constexpr int kSelectMaxWindows = 32768;
 
 template <typename T> __device__ __forceinline__ float round_store(float x) { return Elem<T>::to_f32(Elem<T>::from_f32(x)); }
+template <typename T> static float dtype_round_host(float x);
+template <> float dtype_round_host<float>(float x) { return x; }
+template <> float dtype_round_host<__half>(float x) { return __half2float(__float2half_rn(x)); }
+template <> float dtype_round_host<__nv_bfloat16>(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 
 // Mean confidence of window m of frame f: float32 sum over the window row by row, divided by its size,
 // rounded to the confidence dtype (a tensor of that dtype holds the mean in the reference).
@@ -84,7 +88,60 @@ __global__ void select_abs_kernel(const T *__restrict__ conf, int64_t n_windows,
                                   float thr, uint8_t *__restrict__ mask) {
     const int Wm = W / gw, M = (H / gh) * Wm;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_windows; i += (int64_t)gridDim.x * blockDim.x)
-        mask[i] = window_mean<T>(conf, i / M, (int)(i % M), H, W, gh, gw, Wm) < thr ? 1 : 0;
+        mask[i] = window_mean<T>(conf, i / M, (int)(i % M), H, W, gh, gw, Wm) < thr ? 1 : 0;  // thr already rounded to T
+}
+
+// Block-wide sum of doubles (every thread returns the total).  `scratch` holds one double per warp.
+__device__ __forceinline__ double block_sum_f64(double v, double *scratch) {
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(0xffffffffu, v, d);
+    __syncthreads();  // scratch may still be read by the previous call
+    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
+    __syncthreads();
+    double total = 0.0;
+    for (int w = 0; w < kSelectThreads / 32; ++w) total += scratch[w];
+    return total;
+}
+
+// Z-normalised selection (the reference's "mse" confidence mode): per batch element, x -> (x - mean) / (std + 1e-3) with
+// the unbiased standard deviation, then the window mean of the normalised values against the threshold.  Every tensor
+// operation of the reference's expression rounds to the confidence dtype; mean and variance are accumulated in float64.
+// One CTA per batch element.
+template <typename T>
+__global__ void __launch_bounds__(kSelectThreads)
+select_zscore_kernel(const T *__restrict__ conf, int frames_per_batch, int H, int W, int gh, int gw, float thr,
+                     uint8_t *__restrict__ mask) {
+    __shared__ double s_part[kSelectThreads / 32];
+    const int Wm = W / gw, M = (H / gh) * Wm;
+    const int64_t n = (int64_t)frames_per_batch * H * W;
+    const T *x = conf + (int64_t)blockIdx.x * n;
+    double acc = 0.0;
+    for (int64_t i = threadIdx.x; i < n; i += kSelectThreads) acc += (double)Elem<T>::to_f32(x[i]);
+    const double mean64 = block_sum_f64(acc, s_part) / (double)n;
+    acc = 0.0;
+    for (int64_t i = threadIdx.x; i < n; i += kSelectThreads) {
+        const double d = (double)Elem<T>::to_f32(x[i]) - mean64;
+        acc += d * d;
+    }
+    const double var64 = block_sum_f64(acc, s_part) / (double)(n - 1);  // n == 1: 0 / 0 = NaN, nothing is merged
+    const float mean = round_store<T>((float)mean64);
+    const float sd = round_store<T>((float)sqrt(var64));
+    const float den = round_store<T>(__fadd_rn(sd, 1e-3f));
+    const float thr_t = round_store<T>(thr);  // a tensor compared with a number: the number is rounded to the tensor's dtype
+    const int64_t f0 = (int64_t)blockIdx.x * frames_per_batch;
+    for (int i = threadIdx.x; i < frames_per_batch * M; i += kSelectThreads) {
+        const int f = i / M, m = i - f * M;
+        const int wy = m / Wm, wx = m - wy * Wm;
+        const T *p = x + (int64_t)f * H * W + (int64_t)(wy * gh) * W + wx * gw;
+        float sum = 0.0f;
+        for (int iy = 0; iy < gh; ++iy)
+            for (int ix = 0; ix < gw; ++ix) {
+                const float c = round_store<T>(__fsub_rn(Elem<T>::to_f32(p[iy * W + ix]), mean));
+                sum = __fadd_rn(sum, round_store<T>(__fdiv_rn(c, den)));
+            }
+        const float v = round_store<T>(__fdiv_rn(sum, (float)(gh * gw)));
+        mask[f0 * M + i] = v < thr_t ? 1 : 0;
+    }
 }
 
 template <typename T>
@@ -95,7 +152,13 @@ static int launch_select(const void *conf, int64_t batch, int64_t S, int H, int 
         const int64_t n = batch * S * M;
         int64_t blocks = (n + 255) / 256;
         if (blocks > 4 * sm_count()) blocks = 4 * sm_count();
-        select_abs_kernel<T><<<(unsigned)blocks, 256, 0, st>>>((const T *)conf, n, H, W, gh, gw, thr, mask);
+        // a tensor compared with a Python number: the number is first rounded to the tensor's dtype
+        const float thr_t = dtype_round_host<T>(thr);
+        select_abs_kernel<T><<<(unsigned)blocks, 256, 0, st>>>((const T *)conf, n, H, W, gh, gw, thr_t, mask);
+        return check_launch("come_select_windows");
+    }
+    if (mode == COME_SELECT_ZSCORE) {
+        select_zscore_kernel<T><<<(unsigned)batch, kSelectThreads, 0, st>>>((const T *)conf, (int)S, H, W, gh, gw, thr, mask);
         return check_launch("come_select_windows");
     }
     const int64_t groups = scope == COME_SCOPE_BATCH ? batch : batch * S;
@@ -124,7 +187,8 @@ static int select_impl(const void *conf_dev, int dtype, int64_t batch, int64_t f
     COME_REQUIRE(grid_h > 0 && grid_w > 0 && group_h > 0 && group_w > 0, "grid and window sizes must be positive");
     COME_REQUIRE(group_h <= grid_h && group_w <= grid_w, "window larger than the grid");
     COME_REQUIRE(dtype == COME_F32 || dtype == COME_F16 || dtype == COME_BF16, "unknown dtype %d", dtype);
-    COME_REQUIRE(mode == COME_SELECT_RANK || mode == COME_SELECT_ABS, "unknown selection mode %d", mode);
+    COME_REQUIRE(mode == COME_SELECT_RANK || mode == COME_SELECT_ABS || mode == COME_SELECT_ZSCORE, "unknown selection mode %d", mode);
+    COME_REQUIRE(frames_per_batch * (int64_t)grid_h * grid_w < (1ll << 31), "a batch element holds too many confidences");
     COME_REQUIRE(scope == COME_SCOPE_BATCH || scope == COME_SCOPE_FRAME, "unknown selection scope %d", scope);
     COME_REQUIRE(thr_per_group == nullptr || mode == COME_SELECT_RANK, "per-group thresholds need the ranking mode");
     if (mode == COME_SELECT_RANK && !thr_per_group)

@@ -393,18 +393,20 @@ def func_token_merge_2d(tokens: torch.Tensor, start_index: int, group_h: int, gr
     return plan.jagged(tokens), plan.rev_id
 
 
+_SELECT_MODES = {"pairwise-rank": _lib.COME_SELECT_RANK, "abs_mse": _lib.COME_SELECT_ABS, "mse": _lib.COME_SELECT_ZSCORE}
+
+
 def select_windows(confidence: torch.Tensor, B: int, S: int, H: int, W: int, group_h: int, group_w: int,
                    threshold, mode: str = "pairwise-rank", scope: str = "batch") -> torch.Tensor:
     """Per-patch confidence ``[B, S*H*W]`` -> bool merge mask ``[B*S, M]``.
 
-    ``mode``: ``"pairwise-rank"`` (``mean < quantile(mean, threshold)``) or ``"abs_mse"`` (``mean < threshold``);
-    ``scope``: ``"batch"`` ranks all windows of a batch element together (2-D merger class), ``"frame"`` ranks
-    per frame (1-D merger class).  The z-normalised ``"mse"`` mode of the reference is not provided.
+    ``mode``: ``"pairwise-rank"`` (``mean < quantile(mean, threshold)``), ``"abs_mse"`` (``mean < threshold``) or
+    ``"mse"`` (the confidences of a batch element are z-normalised, ``(x - mean) / (std + 1e-3)``, before the window
+    mean is compared with the threshold); ``scope``: ``"batch"`` ranks all windows of a batch element together (2-D
+    merger class), ``"frame"`` ranks per frame (1-D merger class); only the ranking mode looks at it.
     """
     require_cuda(confidence, "confidence")
-    if mode == "mse":
-        raise NotImplementedError("the z-normalised 'mse' confidence mode is not provided by come_b200")
-    if mode not in ("pairwise-rank", "abs_mse"):
+    if mode not in _SELECT_MODES:
         raise ValueError(f"unknown confidence mode {mode!r}")
     if scope not in ("batch", "frame"):
         raise ValueError(f"unknown scope {scope!r}")
@@ -432,7 +434,7 @@ def select_windows(confidence: torch.Tensor, B: int, S: int, H: int, W: int, gro
     with torch.cuda.device(conf.device):
         _lib.check(_lib.lib().come_select_windows(
             ptr(conf), dtype_code(conf.dtype, "confidence"), B, S, H, W, group_h, group_w, float(threshold),
-            _lib.COME_SELECT_RANK if mode == "pairwise-rank" else _lib.COME_SELECT_ABS,
+            _SELECT_MODES[mode],
             _lib.COME_SCOPE_BATCH if scope == "batch" else _lib.COME_SCOPE_FRAME, ptr(mask), stream_ptr(conf.device)))
     return mask
 

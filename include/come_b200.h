@@ -36,7 +36,7 @@ enum {
 };
 
 /* selection modes / scopes of come_select_windows */
-enum { COME_SELECT_RANK = 0, COME_SELECT_ABS = 1 };
+enum { COME_SELECT_RANK = 0, COME_SELECT_ABS = 1, COME_SELECT_ZSCORE = 2 };
 enum { COME_SCOPE_BATCH = 0, COME_SCOPE_FRAME = 1 };
 
 /*
@@ -69,9 +69,16 @@ int come_layout_info(const come_layout_t *layout, int64_t *n_groups, int64_t *to
  *   mask_dev   [batch * frames_per_batch, M] uint8 (0/1), M = floor(grid_h/group_h) * floor(grid_w/group_w)
  *   mode       COME_SELECT_RANK: mask = mean < quantile(mean, threshold) (linear interpolation, float32);
  *              COME_SELECT_ABS : mask = mean < threshold
+ *              COME_SELECT_ZSCORE: the confidences of a batch element are first normalised, (x - mean) / (std + 1e-3)
+ *                                with the unbiased standard deviation over all its frames (co_me_2d.py:274-281,
+ *                                co_me.py:54-59), then mask = mean of the normalised window < threshold; scope is ignored
+ *              In the last two modes the threshold is rounded to dtype before the comparison, as PyTorch does when a
+ *              tensor is compared with a Python number.
  *   scope      COME_SCOPE_BATCH: one quantile per batch element over all its frames (2-D merger class);
  *              COME_SCOPE_FRAME: one quantile per frame (1-D merger class, standalone op chain)
  * At most 32768 windows per quantile group.
+ * A NaN confidence: the reference's quantile of a group that holds a NaN is NaN and nothing of that group is merged; here
+ * the sort leaves a NaN where it stands and the threshold is unspecified.  Callers must pass finite confidences.
  */
 int come_select_windows(const void *conf_dev, int dtype, int64_t batch, int64_t frames_per_batch, int grid_h,
                         int grid_w, int group_h, int group_w, float threshold, int mode, int scope,

@@ -78,7 +78,7 @@ def select_windows(conf, B, S, H, W, gh, gw, threshold, mode="pairwise-rank", sc
     M = (H // gh) * (W // gw)
     mask = np.empty((B * S, M), np.uint8)
     rc = lib().orc_select(_p(conf), C.c_int64(B), C.c_int64(S), C.c_int64(H), C.c_int64(W), C.c_int64(gh),
-                          C.c_int64(gw), C.c_float(threshold), C.c_int({"pairwise-rank": 0, "abs_mse": 1}[mode]),
+                          C.c_int64(gw), C.c_float(threshold), C.c_int({"pairwise-rank": 0, "abs_mse": 1, "mse": 2}[mode]),
                           C.c_int({"batch": 0, "frame": 1}[scope]), C.c_int(_KIND[kind]), None, _p(mask))
     if rc != 0:
         raise MemoryError("orc_select")

@@ -121,13 +121,35 @@ static float quantile_linear(const float *v, int64_t n, float q, float *scratch)
     if (w < 0.5f) return fmaf(w, d, a);
     return fmaf(w - 1.0f, d, b);
 }
-/* mode 0 = ranking (quantile), 1 = absolute threshold. scope 0 = quantile over all S*M windows of a batch
- * element, 1 = over the M windows of each frame. conf [B, S*H*W] float32 carrying `kind`-precision values. */
-int orc_select(const float *conf, int64_t B, int64_t S, int64_t H, int64_t W, int64_t gh, int64_t gw,
+/* mode 0 = ranking (quantile), 1 = absolute threshold, 2 = absolute threshold on confidences z-normalised per batch
+ * element: (x - mean) / (std + 1e-3), unbiased std, every tensor operation rounded to `kind`, mean and variance
+ * accumulated in float64 (co_me_2d.py:274-281, co_me.py:54-59). scope 0 = quantile over all S*M windows of a batch
+ * element, 1 = over the M windows of each frame. conf [B, S*H*W] float32 carrying `kind`-precision values.
+ * In modes 1 and 2 the threshold is rounded to `kind` first (a tensor compared with a Python number). */
+int orc_select(const float *conf_in, int64_t B, int64_t S, int64_t H, int64_t W, int64_t gh, int64_t gw,
                float thr, int mode, int scope, int kind, float *means_out, uint8_t *mask) {
     int64_t Hm = H / gh, Wm = W / gw, M = Hm * Wm, F = B * S;
     float *means = means_out ? means_out : (float *)malloc((size_t)(F * M) * sizeof(float));
     if (!means) return -1;
+    const float *conf = conf_in;
+    float *norm = NULL;
+    if (mode == 2) {
+        const int64_t n = S * H * W;
+        norm = (float *)malloc((size_t)(B * n) * sizeof(float));
+        if (!norm) return -1;
+        for (int64_t b = 0; b < B; ++b) {
+            const float *x = conf_in + b * n;
+            double sum = 0.0, sq = 0.0;
+            for (int64_t i = 0; i < n; ++i) sum += (double)x[i];
+            const double mean64 = sum / (double)n;
+            for (int64_t i = 0; i < n; ++i) sq += ((double)x[i] - mean64) * ((double)x[i] - mean64);
+            const float mean = round_kind((float)mean64, kind);
+            const float sd = round_kind((float)sqrt(n > 1 ? sq / (double)(n - 1) : NAN), kind);
+            const float den = round_kind(sd + 1e-3f, kind);
+            for (int64_t i = 0; i < n; ++i) norm[b * n + i] = round_kind(round_kind(x[i] - mean, kind) / den, kind);
+        }
+        conf = norm;
+    }
 #pragma omp parallel for schedule(static)
     for (int64_t f = 0; f < F; ++f)
         for (int64_t m = 0; m < M; ++m) {
@@ -138,8 +160,9 @@ int orc_select(const float *conf, int64_t B, int64_t S, int64_t H, int64_t W, in
                     acc = acc + conf[f * H * W + (wy * gh + iy) * W + wx * gw + ix];
             means[f * M + m] = round_kind(acc / (float)(gh * gw), kind);
         }
-    if (mode == 1) {
-        for (int64_t i = 0; i < F * M; ++i) mask[i] = means[i] < thr;
+    if (mode == 1 || mode == 2) {
+        const float thr_k = round_kind(thr, kind);
+        for (int64_t i = 0; i < F * M; ++i) mask[i] = means[i] < thr_k;
     } else {
         int64_t groups = scope == 0 ? B : F, n = scope == 0 ? S * M : M;
         float *scratch = (float *)malloc((size_t)n * sizeof(float));
@@ -151,6 +174,7 @@ int orc_select(const float *conf, int64_t B, int64_t S, int64_t H, int64_t W, in
         free(scratch);
     }
     if (!means_out) free(means);
+    free(norm);
     return 0;
 }
 

@@ -273,6 +273,25 @@ def quantile_linear(values: np.ndarray, q: float) -> np.float32:
     return np.float32(np.float64(np.float32(w - np.float32(1.0))) * np.float64(d) + np.float64(b))
 
 
+def z_normalise(conf: np.ndarray, kind: str = "f32") -> np.ndarray:
+    """``(x - mean) / (std + 1e-3)`` per batch element, ``conf [B, n]`` (``co_me_2d.py:275-278``, ``co_me.py:56-57``).
+
+    Every tensor operation of the expression rounds to the confidence dtype ``kind``: the mean, the unbiased
+    standard deviation, ``std + 1e-3``, the difference and the quotient.  Mean and standard deviation are accumulated
+    in float64 here (PyTorch sums a float32 tensor in float32 with a cascade whose order depends on the vector width and
+    the thread count; both round to the same 16-bit value, a float32 result can differ in its last bits).
+    """
+    x = np.asarray(conf, dtype=np.float32)
+    n = x.shape[-1]
+    x64 = x.astype(np.float64)
+    mean64 = x64.sum(axis=-1, keepdims=True) / n
+    var64 = ((x64 - mean64) ** 2).sum(axis=-1, keepdims=True) / (n - 1) if n > 1 else np.full_like(mean64, np.nan)
+    mean = _round_like(mean64.astype(np.float32), kind)
+    std = _round_like(np.sqrt(var64).astype(np.float32), kind)
+    den = _round_like(std + np.float32(1e-3), kind)
+    return _round_like(_round_like(x - mean, kind) / den, kind)
+
+
 def select_windows(conf, B, S, H, W, gh, gw, threshold, mode="pairwise-rank", scope="batch", kind="f32"):
     """Merge mask ``[B*S, M]`` from per-patch confidence ``[B, S*H*W]``.
 
@@ -287,13 +306,12 @@ def select_windows(conf, B, S, H, W, gh, gw, threshold, mode="pairwise-rank", sc
     """
     conf = np.asarray(conf, dtype=np.float32).reshape(B, S * H * W)
     if mode == "mse":
-        mu = conf.mean(axis=-1, keepdims=True, dtype=np.float32)
-        sd = conf.std(axis=-1, keepdims=True, ddof=1, dtype=np.float32)
-        conf = _round_like((conf - mu) / (sd + np.float32(1e-3)), kind)
+        conf = z_normalise(conf, kind)
     means = window_means(conf.reshape(B * S, H * W), H, W, gh, gw, kind)  # [B*S, M]
     M = means.shape[1]
     if mode in ("abs_mse", "mse"):
-        return means < np.float32(threshold)
+        # a tensor compared with a Python number: the number is first rounded to the tensor's dtype
+        return means < _round_like(np.float32(threshold), kind)
     if mode != "pairwise-rank":
         raise ValueError(mode)
     per_group = np.ndim(threshold) > 0  # one quantile level per group (per-frame merge ratios of the ragged batch)

@@ -77,6 +77,13 @@ SELECT_CASES = {
     "rank2d_thr1": dict(B=1, S=2, H=6, W=6, gh=3, gw=3, thr=1.0, mode="pairwise-rank", cls="2d", kind="bf16"),
     "rank2d_100f_bf16": dict(B=1, S=100, H=36, W=36, gh=3, gw=3, thr=0.5, mode="pairwise-rank", cls="2d", kind="bf16"),
     "abs2d_bf16": dict(B=2, S=2, H=9, W=9, gh=3, gw=3, thr=0.45, mode="abs_mse", cls="2d", kind="bf16"),
+    # a threshold that is not a bfloat16 number: the comparison rounds it to the tensor's dtype first
+    "abs2d_thr_rounded_bf16": dict(B=1, S=3, H=36, W=36, gh=3, gw=3, thr=0.501, mode="abs_mse", cls="2d", kind="bf16"),
+    # z-normalised mode: (x - mean) / (std + 1e-3) per batch element, then the window mean against the threshold
+    "mse2d_bf16": dict(B=2, S=4, H=36, W=36, gh=3, gw=3, thr=-0.2, mode="mse", cls="2d", kind="bf16"),
+    "mse2d_f16": dict(B=1, S=5, H=12, W=18, gh=2, gw=3, thr=0.31, mode="mse", cls="2d", kind="f16"),
+    "mse2d_f32": dict(B=2, S=3, H=12, W=12, gh=3, gw=3, thr=0.0, mode="mse", cls="2d", kind="f32"),
+    "mse1d_bf16": dict(B=2, S=3, H=6, W=18, gh=1, gw=9, thr=0.1, mode="mse", cls="1d", kind="bf16"),
     "rank1d_bf16": dict(B=2, S=3, H=6, W=18, gh=1, gw=9, thr=0.5, mode="pairwise-rank", cls="1d", kind="bf16"),
     "rank1d_f16": dict(B=1, S=4, H=4, W=16, gh=1, gw=4, thr=0.25, mode="pairwise-rank", cls="1d", kind="f16"),
 }

@@ -286,7 +286,8 @@ def test_device_side_longest_segment(backend):
 @pytest.mark.parametrize("nseg", [15, 16, 1500, 2048, 2100])
 def test_many_short_segments(backend, nseg):
     """Thousands of short segments: around the size of the kernel's shared-memory table of per-segment query-block counts
-    (2048 entries; more segments fall back to a work list with empty slots).  Checked against the CUDA-core kernel."""
+    (2048 entries; more segments fall back to a work list with empty slots).  Checked against the fp32 CPU oracle and
+    against the CUDA-core kernel."""
     from come_b200 import flash_attn as api, flash_attn_fwd_cuda as fa
     rng = np.random.default_rng(nseg)
     lengths = rng.integers(1, 40, size=nseg)
@@ -301,6 +302,65 @@ def test_many_short_segments(backend, nseg):
         outs.append(api.flash_attn_varlen_qkvpacked_func_w_perkey_bias(qkv, cu, int(lengths.max()), perkey_bias=bias,
                                                                        softmax_scale=D ** -0.5).float())
     assert (outs[0] - outs[1]).abs().max().item() <= 2e-2
+    want, _ = clib.attention_bias(to_np(qkv), to_np(bias), cu.cpu().numpy(), D ** -0.5)
+    for got in outs:
+        assert np.abs(got.cpu().numpy() - want).max() <= 2e-2
+    _check_status()
+
+
+def test_kernel_sweep_configuration_full_shape(backend):
+    """The kernel-sweep configuration at its real shape: 64 packed segments of 1374 - 8k tokens (k ~ U{0..72}), 16 heads,
+    head_dim 64, counts {1, 9} laid out in merge order, bias = log(count).  64 segments run the instantiation of the
+    tensor-core kernel that enumerates its work items from a per-segment table (16 to 2048 segments); the result is
+    compared with the fp32 CPU oracle on every row and head, bar 2e-2 absolute."""
+    from come_b200 import flash_attn as api, flash_attn_fwd_cuda as fa
+    backend(fa.BACKEND_TCGEN05)
+    rng = np.random.default_rng(0)
+    lengths = [1374 - 8 * int(k) for k in rng.integers(0, 73, size=64)]
+    H, D = 16, 64
+    qkv, count, cu = _merge_like_inputs(rng, lengths, H, D, "bf16")
+    bias32 = np.log(count)
+    out, lse, _ = api.flash_attn_varlen_qkvpacked_func_w_perkey_bias(
+        to_dev(qkv, "bf16"), torch.from_numpy(cu).cuda(), max(lengths), perkey_bias=to_dev(bias32, "bf16"),
+        softmax_scale=D ** -0.5, return_attn_probs=True)
+    want, want_lse = clib.attention_bias(qkv, bias32, cu, D ** -0.5)
+    assert np.abs(to_np(out) - want).max() <= 2e-2
+    np.testing.assert_allclose(to_np(lse), want_lse, atol=1e-2, rtol=1e-3)  # the device bias is log(9) rounded to bfloat16
+    _check_status()
+
+
+def test_global_segment_of_100_frames_sampled_rows(backend):
+    """One global segment of 79,800 packed tokens (100 half-merged frames): the full launch and a launch on a slice of the
+    query rows that does not start at row 0, compared with the fp32 CPU oracle on sampled query rows -- the first query
+    tile, rows around a 384-row work-item boundary, rows around the start of the slice and the ragged last tile (896 rows
+    x 2 heads against all 79,800 keys)."""
+    from come_b200 import flash_attn_fwd_cuda as fa
+    backend(fa.BACKEND_TCGEN05)
+    rng = np.random.default_rng(100)
+    P, H, D = 79800, 2, 64
+    qkv = gi.round_kind(rng.standard_normal((P, 3, H, D), dtype=np.float32), "bf16")
+    count = np.where(rng.random(P) < 0.11, np.float32(9), np.float32(1))
+    bias32 = np.log(count)
+    cu_np = np.array([0, P], np.int32)
+    cu = torch.from_numpy(cu_np).cuda()
+    t, b = to_dev(qkv, "bf16"), to_dev(bias32, "bf16")
+    full, full_lse = fa.varlen_fwd_rows(t[:, 0], t[:, 1], t[:, 2], cu, P, b, D ** -0.5, 0)
+    lo, hi = 30000, 40100  # a rank's share of the rows: neither end on a tile boundary of the full launch
+    part, part_lse = fa.varlen_fwd_rows(t[lo:hi, 0].contiguous(), t[:, 1], t[:, 2], cu, P, b, D ** -0.5, lo)
+    full_np, part_np, full_lse_np, part_lse_np = to_np(full), to_np(part), to_np(full_lse), to_np(part_lse)
+    last_tile = (P // 128) * 128
+    samples = [(0, 128), (384 * 100 - 64, 384 * 100 + 64), (lo, lo + 128), (lo + 384 * 3 - 64, lo + 384 * 3 + 64),
+               (hi - 128, hi), (last_tile - 128, P)]
+    checked = 0
+    for a, e in samples:
+        want, want_lse = clib.attention_bias(qkv, bias32, cu_np, D ** -0.5, a, e)
+        assert np.abs(full_np[a:e] - want[a:e]).max() <= 2e-2, (a, e)
+        np.testing.assert_allclose(full_lse_np[:, a:e], want_lse[:, a:e], atol=1e-2, rtol=1e-3)
+        if a >= lo and e <= hi:
+            assert np.abs(part_np[a - lo:e - lo] - want[a:e]).max() <= 2e-2, (a, e)
+            np.testing.assert_allclose(part_lse_np[:, a - lo:e - lo], want_lse[:, a:e], atol=1e-2, rtol=1e-3)
+        checked += e - a
+    assert checked >= 512
     _check_status()
 
 

@@ -39,9 +39,11 @@ def test_select_random_vs_oracle(kind, scope, thr):
     want = clib.select_windows(conf, B, S, H, W, gh, gw, thr, "pairwise-rank", scope, kind)
     got = select_windows(to_dev(conf, kind), B, S, H, W, gh, gw, thr, "pairwise-rank", scope)
     np.testing.assert_array_equal(to_np(got), want)
-    want = clib.select_windows(conf, B, S, H, W, gh, gw, thr, "abs_mse", scope, kind)
-    got = select_windows(to_dev(conf, kind), B, S, H, W, gh, gw, thr, "abs_mse", scope)
-    np.testing.assert_array_equal(to_np(got), want)
+    # thresholds that are not numbers of the 16-bit types: the comparison rounds them to the confidence dtype
+    for mode, level in (("abs_mse", thr), ("abs_mse", thr * 0.9 + 0.0413), ("mse", thr * 2.0 - 1.0), ("mse", 0.0413)):
+        want = clib.select_windows(conf, B, S, H, W, gh, gw, level, mode, scope, kind)
+        got = select_windows(to_dev(conf, kind), B, S, H, W, gh, gw, level, mode, scope)
+        np.testing.assert_array_equal(to_np(got), want)
 
 
 def test_select_largest_group():
@@ -62,5 +64,13 @@ def test_select_rejects_bad_arguments():
     conf = torch.zeros((1, 36), device="cuda")
     with pytest.raises(ValueError, match="threshold in"):
         select_windows(conf, 1, 1, 6, 6, 3, 3, 1.5)
-    with pytest.raises(NotImplementedError):
-        select_windows(conf, 1, 1, 6, 6, 3, 3, 0.5, mode="mse")
+    with pytest.raises(ValueError, match="unknown confidence mode"):
+        select_windows(conf, 1, 1, 6, 6, 3, 3, 0.5, mode="l1")
+
+
+def test_select_zscore_single_confidence_merges_nothing():
+    """One confidence per batch element: the unbiased standard deviation is NaN and no window is selected, as in the
+    reference's tensor expression."""
+    from come_b200.token_merger import select_windows
+    mask = select_windows(torch.full((3, 1), 0.25, device="cuda"), 3, 1, 1, 1, 1, 1, 10.0, mode="mse")
+    assert tuple(mask.shape) == (3, 1) and not mask.any().item()
