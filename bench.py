@@ -1,10 +1,11 @@
 #!/usr/bin/env python3
 """Benchmark of the Co-Me hot path on B200: ms/scene of the merge -> biased attention -> unmerge chain at the
-VGGT-1B shapes (8 frames of 518x518: 1374 tokens x 1024 channels per frame, 16 heads x 64, 24 frame + 24 global
-attention layers, 3x3 windows at a 50 % merge ratio), plus merge/unmerge GB/s and biased-attention TFLOP/s.
+VGGT-1B shapes (100 frames of 518x518: 1374 tokens x 1024 channels per frame, 16 heads x 64, 24 frame + 24 global
+attention layers, 3x3 windows at a 50 % merge ratio; the 8-frame scene as the extra key `scene8`), plus merge/unmerge
+GB/s and biased-attention TFLOP/s.
 
-    python bench.py --gpus N --steps K --warmup W            # this library (one scene per rank and step)
-    python bench.py --impl reference ...                     # the CPU restatement of the reference path (rank 0)
+    python bench.py --gpus N --steps K --warmup W            # this library: ONE 100-frame scene per step, frames sharded over the N GPUs
+    python bench.py --impl reference ...                     # the CPU restatement of the reference path (rank 0), a bounded sample
 
 Prints ONE JSON line (rank 0).  Inputs are synthetic (seeded).
 """
@@ -28,8 +29,12 @@ FRAMES, GRID, WIN, START, CH, HEADS, HDIM = 8, 37, 3, 5, 1024, 16, 64
 N_TOK = START + GRID * GRID  # 1374
 N_WIN = (GRID // WIN) ** 2   # 144
 LAYERS = ["frame", "global"] * 24
-METRIC = "come_vggt_hot_path_ms_per_scene_8f"
 UNIT = "ms/scene"
+FRAMES_BY_WORKLOAD = {"frames100": 100, "frames8": 8}
+
+
+def metric_name(frames):
+    return f"come_vggt_hot_path_ms_per_scene_{frames}f"
 
 
 def workload_name(frames=FRAMES):
@@ -99,63 +104,98 @@ class ClockSampler:
 
 
 # ---- CPU restatement of the reference path (oracle) ---------------------------------------------------------
-def cpu_chain_sample(frames=FRAMES, attn_rows=1024):
-    """One bounded sample of the scene chain on the host cores with the C oracle (all OpenMP threads).
+class CpuSceneSample:
+    """A bounded sample of one scene of the operator chain on the host cores with the C oracle (all OpenMP threads).
 
-    Times a full merge and a full unmerge (float32, the dtype of the reference's CPU path), and attention on a
-    slice: frame layers on 1 head x 1 frame x all rows, the global layer on 1 head x `attn_rows` query rows against
-    all keys.  The slices are scaled to all heads / frames / rows and summed over the 48 layers."""
-    from oracle import clib
-    # all the host threads this process may use: a multi-process launcher exports OMP_NUM_THREADS=1 for its workers,
-    # which would time the CPU path on one core
-    clib.set_num_threads(len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1))
-    rng = np.random.default_rng(0)
-    tokens = rng.standard_normal((frames, N_TOK, CH), dtype=np.float32)
-    conf = rng.random((1, frames * GRID * GRID), dtype=np.float32)
-    t0 = time.perf_counter()
-    mask = clib.select_windows(conf, 1, frames, GRID, GRID, WIN, WIN, 0.5, "pairwise-rank", "frame")
-    t_sel = time.perf_counter() - t0
-    t0 = time.perf_counter()
-    out, off, rev, w = clib.token_merge_2d(tokens, START, WIN, WIN, GRID, GRID, mask)
-    t_merge = time.perf_counter() - t0
-    t0 = time.perf_counter()
-    clib.token_split(out, rev)
-    t_unmerge = time.perf_counter() - t0
-    P = out.shape[0]
-    L0 = int(off[1] - off[0])
-    bias = np.log(w)
-    qkv1 = rng.standard_normal((P, 3, 1, HDIM), dtype=np.float32)
-    t0 = time.perf_counter()
-    clib.attention_bias(qkv1[:L0], bias[:L0], np.array([0, L0], np.int32), HDIM ** -0.5)
-    t_frame = (time.perf_counter() - t0) * HEADS * frames
-    t0 = time.perf_counter()
-    clib.attention_bias(qkv1, bias, np.array([0, P], np.int32), HDIM ** -0.5, 0, attn_rows)
-    t_global = (time.perf_counter() - t0) * HEADS * (P / attn_rows)
-    per_scene = t_sel + 24 * (t_merge + t_frame + t_unmerge) + 24 * (t_merge + t_global + t_unmerge)
-    detail = dict(select_ms=t_sel * 1e3, merge_ms=t_merge * 1e3, unmerge_ms=t_unmerge * 1e3,
-                  attn_frame_layer_ms=t_frame * 1e3, attn_global_layer_ms=t_global * 1e3)
-    sample = (f"1 scene-sample: full select+merge+unmerge (fp32, {frames}x{N_TOK}x{CH}); attention on 1 head: one frame "
-              f"segment (all rows) and the global segment ({attn_rows} of {P} query rows), scaled to {HEADS} heads / "
-              f"{frames} frames / all rows and x24 layers each")
-    return per_scene * 1e3, clib.num_threads(), sample, detail
+    Every ``run()`` times, in float32 (the dtype of the reference's CPU path): the selection, a full merge and a full
+    unmerge of all frames, the frame attention of ``frame_sample`` whole frames with all heads, and the global attention
+    of ONE head on ``attn_rows`` query rows against all keys.  The frame figure is scaled by ``frames / frame_sample``
+    and the global figure by ``heads * rows / attn_rows``; both are summed over the 24 + 24 layers.  The scene figure is
+    therefore an extrapolation (``extrapolated`` in the report) and ``sample_s`` says how many seconds were timed."""
+
+    def __init__(self, frames, attn_rows=512, frame_sample=8):
+        from oracle import clib
+        self.clib, self.frames, self.attn_rows = clib, frames, attn_rows
+        self.frame_sample = min(frames, frame_sample)
+        # all the host threads this process may use: a multi-process launcher exports OMP_NUM_THREADS=1 for its workers,
+        # which would time the CPU path on one core
+        clib.set_num_threads(len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1))
+        rng = np.random.default_rng(0)
+        self.tokens = rng.standard_normal((frames, N_TOK, CH), dtype=np.float32)
+        self.conf = rng.random((1, frames * GRID * GRID), dtype=np.float32)
+        mask = clib.select_windows(self.conf, 1, frames, GRID, GRID, WIN, WIN, 0.5, "pairwise-rank", "frame")
+        _, off, _, w = clib.token_merge_2d(self.tokens[:1], START, WIN, WIN, GRID, GRID, mask[:1])
+        self.P = int(frames * N_TOK - 8 * mask.sum())
+        # attention inputs: all heads for the sampled frames, one head for the global slice
+        self.qkv_frames = rng.standard_normal((self.frame_sample * N_TOK, 3, HEADS, HDIM), dtype=np.float32)
+        self.qkv_1head = rng.standard_normal((self.P, 3, 1, HDIM), dtype=np.float32)
+
+    def run(self):
+        clib, frames = self.clib, self.frames
+        t_all = time.perf_counter()
+        t0 = time.perf_counter()
+        mask = clib.select_windows(self.conf, 1, frames, GRID, GRID, WIN, WIN, 0.5, "pairwise-rank", "frame")
+        t_sel = time.perf_counter() - t0
+        t0 = time.perf_counter()
+        out, off, rev, w = clib.token_merge_2d(self.tokens, START, WIN, WIN, GRID, GRID, mask)
+        t_merge = time.perf_counter() - t0
+        t0 = time.perf_counter()
+        clib.token_split(out, rev)
+        t_unmerge = time.perf_counter() - t0
+        P = out.shape[0]
+        bias = np.log(w)
+        fs = self.frame_sample
+        cu_f = off[: fs + 1].astype(np.int32)
+        t0 = time.perf_counter()
+        clib.attention_bias(self.qkv_frames[: cu_f[-1]], bias[: cu_f[-1]], cu_f, HDIM ** -0.5)
+        t_frame = (time.perf_counter() - t0) * (frames / fs)
+        rows = min(self.attn_rows, P)
+        t0 = time.perf_counter()
+        clib.attention_bias(self.qkv_1head[:P], bias, np.array([0, P], np.int32), HDIM ** -0.5, 0, rows)
+        t_global = (time.perf_counter() - t0) * HEADS * (P / rows)
+        sample_s = time.perf_counter() - t_all
+        n_f = sum(1 for k in LAYERS if k == "frame")
+        n_g = len(LAYERS) - n_f
+        per_scene = t_sel + len(LAYERS) * (t_merge + t_unmerge) + n_f * t_frame + n_g * t_global
+        detail = dict(select_ms=t_sel * 1e3, merge_ms=t_merge * 1e3, unmerge_ms=t_unmerge * 1e3,
+                      attn_frame_layer_ms=t_frame * 1e3, attn_global_layer_ms=t_global * 1e3)
+        return per_scene * 1e3, sample_s, detail
+
+    def describe(self):
+        return (f"per step: select + merge + unmerge of all {self.frames} frames (fp32, {self.frames}x{N_TOK}x{CH}), frame "
+                f"attention of {self.frame_sample} whole frames x {HEADS} heads (scaled by {self.frames}/{self.frame_sample}), "
+                f"global attention of 1 head x {min(self.attn_rows, self.P)} of {self.P} query rows against all keys (scaled to "
+                f"{HEADS} heads and all rows); x24 frame + x24 global layers")
+
+
+def cpu_baseline_report(frames, steps, warmup=0):
+    """``steps`` samples of the CPU path (median), as the ``cpu_baseline`` object of the JSON line."""
+    sample = CpuSceneSample(frames)
+    vals, secs, detail = [], [], {}
+    for i in range(warmup + steps):
+        v, s_, detail = sample.run()
+        if i >= warmup:
+            vals.append(v)
+            secs.append(s_)
+    return {"value": statistics.median(vals), "unit": UNIT, "cores": sample.clib.num_threads(), "kind": "port",
+            "extrapolated": True, "sample_s": sum(secs), "samples": len(vals), "sample": sample.describe(), "detail": detail,
+            "note": "C/OpenMP restatement of the reference's PyTorch fallback (float32); a reported baseline, extrapolated "
+                    "from the timed sample, not a measurement of the whole scene"}
 
 
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    vals = []
-    detail = {}
-    for i in range(args.warmup + args.steps):
-        v, cores, sample, detail = cpu_chain_sample(attn_rows=256)
-        if i >= args.warmup:
-            vals.append(v)
-    val = statistics.median(vals)
+    frames = FRAMES_BY_WORKLOAD[args.workload]
+    rep = cpu_baseline_report(frames, args.steps, args.warmup)
+    val = rep["value"]
     line = {
-        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": val, "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
-        "dtype": "f32", "data": "synthetic (seeded)", "config": {"workload": workload_name()},
-        "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample, "detail": detail},
+        "impl": "reference", "metric": metric_name(frames), "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": val, "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic (seeded)", "config": {"workload": workload_name(frames)},
+        "extrapolated": True, "kind": "port", "sample_s": rep["sample_s"],
+        "cpu_baseline": rep,
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -163,10 +203,9 @@ def run_reference(args):
 
 
 # ---- GPU arm ---------------------------------------------------------------------------------------------------
-def run_gpu(args):
+def init_ranks():
     import torch
     import torch.distributed as dist
-
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -175,104 +214,275 @@ def run_gpu(args):
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
+    return torch, dist, world, rank, local, dev
 
+
+def sharded_check(torch, dist, world, rank, dev):
+    """Before anything is timed at N > 1: a small scene (one frame layer + one global layer) run sharded over the ranks
+    and unsharded on every rank.  With the exchange in line the sharded frames must equal the unsharded ones bit for bit;
+    with the exchange hidden behind attention to the local keys the global layer may differ by the rounding of the two
+    partial outputs (bar 2e-2 absolute).  Raises on a mismatch on any rank."""
+    from come_b200.chain import ShardedOpChain
+    frames, C, H, D = max(8, world), 256, 4, 64
+    g = torch.Generator(device="cpu").manual_seed(5)
+    x = torch.randn((frames, N_TOK, C), generator=g).bfloat16().to(dev)
+    conf = torch.rand((1, frames * GRID * GRID), generator=g).bfloat16().to(dev)
+    q = torch.randn((frames * N_TOK, H, D), generator=g).bfloat16().to(dev)
+    kv = torch.randn((frames * N_TOK, 2, H, D), generator=g).bfloat16().to(dev)
+    kinds = ["frame", "global"]
+    whole = ShardedOpChain(frames, None, START, GRID, GRID, WIN, WIN, 0.5, H, D, kinds)
+    whole.world, whole.rank, whole.f_lo, whole.f_hi = 1, 0, 0, frames  # every rank computes the whole scene for itself
+    gp, lp = whole.build_plans(conf)
+    P = lp.total
+    want = [whole.layer(gp, lp, x, q[:P].contiguous(), kv[:P].contiguous(), k) for k in kinds]
+    res = {"rows": P, "frames": frames}
+    ok = True
+    for overlap in (False, True):
+        chain = ShardedOpChain(frames, None, START, GRID, GRID, WIN, WIN, 0.5, H, D, kinds, overlap=overlap)
+        gp, lp = chain.build_plans(conf)
+        r0, r1 = chain.row_begin, chain.row_begin + lp.total
+        diffs = []
+        for kind, ref in zip(kinds, want):
+            got = chain.layer(gp, lp, x[chain.f_lo:chain.f_hi], q[r0:r1].contiguous(), kv[r0:r1].contiguous(), kind)
+            diffs.append(float((got.float() - ref[chain.f_lo:chain.f_hi].float()).abs().max().item()) if got.numel() else 0.0)
+        t = torch.tensor(diffs, dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        worst = t.tolist()
+        if overlap:
+            res["overlapped_max_abs_diff"] = {"frame": worst[0], "global": worst[1], "bar_global": 2e-2}
+            ok = ok and worst[0] == 0.0 and worst[1] <= 2e-2
+        else:
+            res["in_line_bit_exact"] = worst[0] == 0.0 and worst[1] == 0.0
+            ok = ok and res["in_line_bit_exact"]
+    res["ok"] = bool(ok)
+    if not ok:
+        raise RuntimeError(f"sharded scene differs from the unsharded one: {res}")
+    return res
+
+
+def run_frames(args):
+    """The default arm: ONE scene of 100 frames (137,400 tokens before merging) sharded by frame over the ranks.  Frame
+    layers are local; a global layer all-gathers the merged K/V rows over NCCL on a side stream while the local query rows
+    attend to the local keys, then attends them to the gathered rows and merges the two results (strong scaling: the
+    scene is fixed, more GPUs shorten it).  At N = 1 there is no exchange and the global layer is one launch."""
+    torch, dist, world, rank, local, dev = init_ranks()
     from come_b200 import _lib
-    from come_b200.chain import CoMeOpChain
-    from come_b200.flash_attn import flash_attn_varlen_qkvpacked_func_w_perkey_bias as attn_fn
-
+    from come_b200.chain import ShardedOpChain
+    frames = FRAMES_BY_WORKLOAD[args.workload]
     pk = peaks()
-    chain = CoMeOpChain(FRAMES, START, GRID, GRID, WIN, WIN, 0.5, HEADS, HDIM, LAYERS, scope="frame")
-    g = torch.Generator(device="cpu").manual_seed(1234 + rank)
-    x_host = torch.randn((FRAMES, N_TOK, CH), generator=g).bfloat16().pin_memory()
-    conf_host = torch.rand((1, FRAMES * GRID * GRID), generator=g).bfloat16().pin_memory()
-    qkv_host = torch.randn((FRAMES * N_TOK, 3, HEADS, HDIM), generator=g).bfloat16().pin_memory()
-    out_host = torch.empty((FRAMES, N_TOK, CH), dtype=torch.bfloat16).pin_memory()
-    x, conf, qkv_buf = x_host.to(dev), conf_host.to(dev), qkv_host.to(dev)
-    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)  # > 126 MB L2
-
+    check = sharded_check(torch, dist, world, rank, dev) if world > 1 else None
+    chain = ShardedOpChain(frames, None, START, GRID, GRID, WIN, WIN, 0.5, HEADS, HDIM, LAYERS, overlap=(world > 1 and not args.no_overlap))
+    g = torch.Generator(device="cpu").manual_seed(4321)
+    conf_host = torch.rand((1, frames * GRID * GRID), generator=g).bfloat16().pin_memory()  # replicated on every rank
+    conf = conf_host.to(dev)
+    gp, lp = chain.build_plans(conf)
+    n_local = chain.f_hi - chain.f_lo
+    P, P_local = gp.total, lp.total
+    # this rank's inputs start in pinned host memory (the end-to-end region copies them in every step)
+    gl = torch.Generator(device="cpu").manual_seed(100 + rank)
+    x_host = torch.empty((n_local, N_TOK, CH), dtype=torch.bfloat16).pin_memory()
+    q_host = torch.empty((P_local, HEADS, HDIM), dtype=torch.bfloat16).pin_memory()
+    kv_host = torch.empty((P_local, 2, HEADS, HDIM), dtype=torch.bfloat16).pin_memory()
+    for t_ in (x_host, q_host, kv_host):  # drawn in slices: a float32 draw of the whole tensor would double the host memory
+        flat = t_.view(-1)
+        for i in range(0, flat.numel(), 1 << 24):
+            flat[i:i + (1 << 24)] = torch.randn(min(1 << 24, flat.numel() - i), generator=gl).bfloat16()
+    out_host = torch.empty((n_local, N_TOK, CH), dtype=torch.bfloat16).pin_memory()
+    x, q, kv = x_host.to(dev), q_host.to(dev), kv_host.to(dev)
     ev = lambda: torch.cuda.Event(enable_timing=True)  # noqa: E731
-
-    def step_resident(timers=None):
-        """One scene with inputs resident in HBM.  With `timers`, every kernel family is bracketed by events."""
-        plan = chain.build_plan(conf)
-        qkv = qkv_buf[: plan.total]
-        bias = plan.perkey_bias(torch.bfloat16)
-        out = None
-        for kind in LAYERS:
-            cu, ml = (plan.cu_seqlens(FRAMES), plan.total) if kind == "global" else (plan.cu_seqlens(1), plan.max_seqlen)
-            if timers is not None:
-                e = [ev() for _ in range(4)]
-                e[0].record()
-            merged = plan.merge(x)
-            if timers is not None:
-                e[1].record()
-            a = attn_fn(qkv, cu, ml, perkey_bias=bias, softmax_scale=chain.scale)
-            if timers is not None:
-                e[2].record()
-            out = plan.split(a.reshape(plan.total, CH))
-            if timers is not None:
-                e[3].record()
-                timers.append((kind, e))
-            del merged
-        return plan, out
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(args.warmup):
-        step_resident()
+    def step(x_, conf_, q_, kv_, timers=None):
+        gp_, lp_ = chain.build_plans(conf_)
+        out = None
+        for kind in LAYERS:
+            if timers is None:
+                out = chain.layer(gp_, lp_, x_, q_, kv_, kind)
+            else:
+                out = chain.layer(gp_, lp_, x_, q_, kv_, kind, timers=timers)
+        return out
+
+    for _ in range(max(args.warmup, 3)):
+        step(x, conf, q, kv)
     barrier()
     if _lib.device_status(clear=False) != 0:
         raise RuntimeError("attention kernel raised the device status word during warm-up")
-
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
         time.sleep(0.3)
-    # ---- timed region 0 (-> `value`): the captured scene graph, inputs resident, per-step device time ----------------
+    # ---- timed region 0 (-> `value`): inputs resident in HBM --------------------------------------------------------
+    s, e = ev(), ev()
+    s.record()
+    for _ in range(args.steps):
+        step(x, conf, q, kv)
+    e.record()
+    barrier()
+    resident_ms = s.elapsed_time(e)
+    # ---- timed region 1 (-> `e2e`): the same step through the same public calls with HOST buffers: this rank's inputs are
+    # copied from pinned host memory and its restored tokens are copied back, inside the timed region, every step ------
+    h2d = (x_host.numel() + q_host.numel() + kv_host.numel() + conf_host.numel()) * 2
+    d2h = out_host.numel() * 2
+    s, e = ev(), ev()
+    barrier()
+    s.record()
+    for _ in range(args.steps):
+        xd, cd = x_host.to(dev, non_blocking=True), conf_host.to(dev, non_blocking=True)
+        qd, kvd = q_host.to(dev, non_blocking=True), kv_host.to(dev, non_blocking=True)
+        out = step(xd, cd, qd, kvd)
+        out_host.copy_(out.reshape(out_host.shape), non_blocking=True)
+    e.record()
+    barrier()
+    e2e_ms = s.elapsed_time(e)
+    clocks = sampler.stop() if rank == 0 else None
+    if _lib.device_status(clear=False) != 0:
+        raise RuntimeError("attention kernel raised the device status word during the timed region")
+    # ---- instrumented steps (not part of `value`): CUDA events around every kernel family of every layer, and on the side
+    # stream around the all-gather -------------------------------------------------------------------------------------
+    timers = []
+    if chain.exchange is not None:
+        chain.exchange.events = []
+    n_inst = 2
+    for _ in range(n_inst):
+        step(x, conf, q, kv, timers)
+    barrier()
+    fam = {"merge": 0.0, "frame_attn": 0.0, "global_attn": 0.0, "unmerge": 0.0}
+    for kind, e4 in timers:
+        fam["merge"] += e4[0].elapsed_time(e4[1]) / n_inst
+        fam["frame_attn" if kind == "frame" else "global_attn"] += e4[1].elapsed_time(e4[2]) / n_inst
+        fam["unmerge"] += e4[2].elapsed_time(e4[3]) / n_inst
+    split = {f"{k}_ms": v for k, v in fam.items()}
+    exch = chain.exchange.events if chain.exchange is not None and chain.exchange.events else []
+    if exch:
+        gather_ms = [a.elapsed_time(b) for a, b, _, _ in exch]
+        exposed = [max(0.0, c.elapsed_time(b)) for _, b, c, _ in exch]  # gather still running when the local attention ended
+        local_ms = [a.elapsed_time(c) for a, _, c, _ in exch]
+        split.update(allgather_ms_per_global_layer=statistics.mean(gather_ms), allgather_exposed_ms_per_global_layer=statistics.mean(exposed),
+                     local_keys_attn_ms_per_global_layer=statistics.mean(local_ms))
+    vals = torch.tensor([resident_ms, e2e_ms] + [split[k] for k in sorted(split)], dtype=torch.float64, device=dev)
+    rows_t = torch.tensor([P_local, -P_local], dtype=torch.int64, device=dev)
+    if world > 1:
+        dist.all_reduce(vals, op=dist.ReduceOp.MAX)
+        dist.all_reduce(rows_t, op=dist.ReduceOp.MAX)
+    resident_ms, e2e_ms = vals[0].item(), vals[1].item()
+    split = {k: vals[2 + i].item() for i, k in enumerate(sorted(split))}  # max over ranks of every entry
+    split["rows_per_rank"] = [int(-rows_t[1].item()), int(rows_t[0].item())]
+
+    if rank == 0:
+        per_scene = resident_ms / args.steps
+        seg = (gp.offset[1:] - gp.offset[:-1]).tolist()
+        n_f = sum(1 for k in LAYERS if k == "frame")
+        n_g = len(LAYERS) - n_f
+        flops_frame, flops_global = sum(4.0 * L * L * HDIM * HEADS for L in seg), 4.0 * P * P * HDIM * HEADS
+        attn_flops = n_f * flops_frame + n_g * flops_global                 # the whole scene, all ranks together
+        attn_ms = split["frame_attn_ms"] + split["global_attn_ms"]          # slowest rank, per scene
+        achieved = attn_flops / world / (attn_ms * 1e-3) / 1e12             # per GPU
+        es = 2
+        merge_bytes = n_local * N_TOK * CH * es + P_local * CH * es + n_local * N_WIN + (n_local + 1) * 4
+        unmerge_bytes = P_local * CH * es + n_local * N_TOK * 8 + n_local * N_TOK * CH * es
+        kv_bytes = P * 2 * HEADS * HDIM * 2
+        items = -(-split["rows_per_rank"][1] // 384) * HEADS
+        line = {
+            "metric": metric_name(frames), "value": per_scene, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": per_scene, "higher_is_better": False, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic (seeded)",
+            "config": {"workload": workload_name(frames), "merged_tokens": P, "frames_per_s": frames / per_scene * 1e3,
+                       "parallelism": (f"frames sharded over {world} GPU(s); frame layers local; a global layer all-gathers "
+                                       f"{kv_bytes / 1e6:.0f} MB of merged K/V over NCCL"
+                                       + (" on a side stream while the local query rows attend to the local keys, then attends "
+                                          "them to the gathered rows and merges the two results from their log-sum-exps"
+                                          if chain.overlap and world > 1 else " in line")),
+                       "l2": "inputs larger than L2 (the merged K/V of one layer alone is 327 MB)",
+                       "launch": "kernel by kernel from Python (a step is hundreds of ms of device time)"},
+            "roofline": {"kernel": f"attn_fwd_sm100_kernel ({n_f} frame + {n_g} global layers per scene)", "bound": "tensor",
+                         "achieved": achieved, "peak": pk["tflops_sustained"], "unit": "TFLOP/s",
+                         "frac": achieved / pk["tflops_sustained"],
+                         "peak_source": pk["source"] + " cuBLAS bf16, sustained loop (steps of this workload keep the GPU at its power cap for seconds)",
+                         "frac_of_burst_peak": achieved / pk["tflops"],
+                         "per": "GPU (slowest rank)", "traffic": None,
+                         "traffic_note": "the 100-frame launch is too long for an ncu capture; profiles/ holds the capture of the 6456-token launch (qkv read once)",
+                         "timing": "CUDA events around every attention call of 2 instrumented scenes (launches of 0.2 to 33 ms: host cost is hidden)",
+                         "frame_tflops": n_f * flops_frame / world / (split["frame_attn_ms"] * 1e-3) / 1e12,
+                         "global_tflops": n_g * flops_global / world / (split["global_attn_ms"] * 1e-3) / 1e12,
+                         "work_items_per_cta_global": items / 148.0,
+                         "share_of_scene": attn_ms / per_scene},
+            "roofline_merge": {"bound": "hbm", "achieved": merge_bytes * len(LAYERS) / (split["merge_ms"] * 1e-3) / 1e9,
+                               "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": merge_bytes * len(LAYERS) / (split["merge_ms"] * 1e-3) / 1e9 / pk["hbm_gbs"],
+                               "per": "GPU", "bytes_per_launch": merge_bytes},
+            "roofline_unmerge": {"bound": "hbm", "achieved": unmerge_bytes * len(LAYERS) / (split["unmerge_ms"] * 1e-3) / 1e9,
+                                 "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": unmerge_bytes * len(LAYERS) / (split["unmerge_ms"] * 1e-3) / 1e9 / pk["hbm_gbs"],
+                                 "per": "GPU", "bytes_per_launch": unmerge_bytes},
+            "split": split,
+            "e2e": {"value": e2e_ms / args.steps, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "note": "per rank: its frames, its q / k / v rows and the replicated confidences in, its restored tokens out"},
+            "gpu_launches": (5 + n_f * 3 + n_g * (5 if (chain.overlap and world > 1) else 3)) * args.steps,
+            "clocks": clocks,
+        }
+        if check is not None:
+            line["sharded_check"] = check
+        if world == 1 and not args.no_scene8:
+            line["scene8"] = scene8_measure(torch, dev, pk, max(5, args.steps))
+        if world == 1 and not args.no_micro:
+            line["kernels"] = micro(torch, dev, pk)
+            # the whole alternating-attention stack (48 blocks with their cuBLAS GEMMs) around the same kernels,
+            # merged against unmerged: the reference's own end-to-end comparison (src/bench.py), 5 scenes per arm
+            agg = aggregator_measure(8, 24, 5, report=False)
+            agg.pop("only")
+            line["aggregator_model"] = agg
+        if world == 1 and not args.no_cpu:
+            line["cpu_baseline"] = cpu_baseline_report(frames, 3)
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def scene8_measure(torch, dev, pk, steps):
+    """The 8-frame scene of the same chain on one GPU (48 x (merge + attention + unmerge), one selection + plan), as ONE
+    CUDA graph: ms/scene with inputs resident (L2 flushed between steps), end to end with host buffers, and device time
+    per kernel family."""
+    from come_b200 import _lib
+    from come_b200.chain import CoMeOpChain
+    from come_b200.flash_attn import flash_attn_varlen_qkvpacked_func_w_perkey_bias as attn_fn
     from come_b200.static_scene import StaticScene
-    scene = StaticScene(FRAMES, CH, START, GRID, GRID, WIN, WIN, 0.5, HEADS, HDIM, LAYERS, "frame", torch.bfloat16, dev).capture()
+    F8 = 8
+    chain = CoMeOpChain(F8, START, GRID, GRID, WIN, WIN, 0.5, HEADS, HDIM, LAYERS, scope="frame")
+    g = torch.Generator(device="cpu").manual_seed(1234)
+    x_host = torch.randn((F8, N_TOK, CH), generator=g).bfloat16().pin_memory()
+    conf_host = torch.rand((1, F8 * GRID * GRID), generator=g).bfloat16().pin_memory()
+    qkv_host = torch.randn((F8 * N_TOK, 3, HEADS, HDIM), generator=g).bfloat16().pin_memory()
+    out_host = torch.empty((F8, N_TOK, CH), dtype=torch.bfloat16).pin_memory()
+    x, conf, qkv_buf = x_host.to(dev), conf_host.to(dev), qkv_host.to(dev)
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)  # > 126 MB L2
+    ev = lambda: torch.cuda.Event(enable_timing=True)  # noqa: E731
+    scene = StaticScene(F8, CH, START, GRID, GRID, WIN, WIN, 0.5, HEADS, HDIM, LAYERS, "frame", torch.bfloat16, dev).capture()
     for _ in range(3):
         scene.run(x_host, conf_host, qkv_host)
-    barrier()
+    torch.cuda.synchronize()
     graph_ev = []
-    for _ in range(args.steps):
+    for _ in range(steps):
         flush.fill_(1)  # L2 flush between timed iterations (outside the per-step events)
         s, e = ev(), ev()
         s.record()
         scene.run()
         e.record()
         graph_ev.append((s, e))
-    barrier()
-    graph_ms = sum(s.elapsed_time(e) for s, e in graph_ev)
-    # ---- timed region 1 (-> `roofline`): the same scene launched kernel by kernel, each kernel family bracketed by
-    # CUDA events on the launching stream (the graph cannot be bracketed from inside) -------------------------------
-    step_ev, timers = [], []
-    barrier()
-    plan = None
-    for _ in range(args.steps):
-        flush.fill_(1)  # L2 flush between timed iterations (outside the per-step events)
-        s, e = ev(), ev()
-        s.record()
-        plan, _ = step_resident(timers)
-        e.record()
-        step_ev.append((s, e))
-    barrier()
-    step_ms = [s.elapsed_time(e) for s, e in step_ev]
-    total_ms = sum(step_ms)
-    # ---- timed region 1b (-> `roofline.achieved`): device time per kernel family.  Launched one by one from Python the
-    # short kernels are host-bound (~60 us per attention call), so each family's launches of one scene are captured into
-    # a graph of their own, on the scene's real tensors, and timed by events around the replay.
-    qkv_p, bias_p = qkv_buf[: plan.total], plan.perkey_bias(torch.bfloat16)
-    merged_p = plan.merge(x)
-    attn_p = attn_fn(qkv_p, plan.cu_seqlens(1), plan.max_seqlen, perkey_bias=bias_p, softmax_scale=chain.scale).reshape(plan.total, CH)
+    torch.cuda.synchronize()
+    graph_ms = sum(s.elapsed_time(e) for s, e in graph_ev) / steps
+    # device time per kernel family: each family's launches of one scene captured into a graph of their own
+    plan = chain.build_plan(conf)
+    P = plan.total
+    qkv_p, bias_p = qkv_buf[:P], plan.perkey_bias(torch.bfloat16)
+    attn_p = attn_fn(qkv_p, plan.cu_seqlens(1), plan.max_seqlen, perkey_bias=bias_p, softmax_scale=chain.scale).reshape(P, CH)
     n_f = sum(1 for k in LAYERS if k != "global")
     n_g = len(LAYERS) - n_f
     families = {
         "frame": (n_f, lambda: attn_fn(qkv_p, plan.cu_seqlens(1), plan.max_seqlen, perkey_bias=bias_p, softmax_scale=chain.scale)),
-        "global": (n_g, lambda: attn_fn(qkv_p, plan.cu_seqlens(FRAMES), plan.total, perkey_bias=bias_p, softmax_scale=chain.scale)),
+        "global": (n_g, lambda: attn_fn(qkv_p, plan.cu_seqlens(F8), P, perkey_bias=bias_p, softmax_scale=chain.scale)),
         "merge": (len(LAYERS), lambda: plan.merge(x)),
         "unmerge": (len(LAYERS), lambda: plan.split(attn_p)),
     }
@@ -285,8 +495,8 @@ def run_gpu(args):
             for _ in range(count):
                 fn()
         gr.replay()
-        acc = 0.0
-        for _ in range(max(3, args.steps // 4)):
+        acc, reps = 0.0, max(3, steps // 4)
+        for _ in range(reps):
             flush.fill_(1)
             s, e = ev(), ev()
             s.record()
@@ -294,108 +504,52 @@ def run_gpu(args):
             e.record()
             torch.cuda.synchronize()
             acc += s.elapsed_time(e)
-        family_ms[name] = acc / max(3, args.steps // 4)  # ms per scene spent in this family
+        family_ms[name] = acc / reps
         del gr
-    del merged_p
-    # ---- timed region 2: end to end through the public API with host buffers --------------------------------------
-    h2d = x_host.numel() * 2 + conf_host.numel() * 2 + qkv_host.numel() * 2
+    # end to end: every scene's inputs start in pinned host memory and its result ends there; the copies of scene k+1 /
+    # k-1 run on a side stream while scene k computes (StaticScene.stage / run_staged), as a serving loop would
+    h2d = (x_host.numel() + conf_host.numel() + qkv_host.numel()) * 2
     d2h = out_host.numel() * 2
-    # Every scene's inputs start in pinned host memory and its result ends there; the copies of scene k+1 / k-1 run on a
-    # side stream while scene k computes (StaticScene.stage / run_staged), as a serving loop would.
-    scene.stage(x_host, conf_host, qkv_host)
-    scene.stage(x_host, conf_host, qkv_host)
-    scene.run_staged(out_host)
-    scene.run_staged(out_host)
+    for _ in range(2):
+        scene.stage(x_host, conf_host, qkv_host)
+    for _ in range(2):
+        scene.run_staged(out_host)
     scene.drain()
-    barrier()
+    torch.cuda.synchronize()
     s, e = ev(), ev()
     s.record()
     scene.stage(x_host, conf_host, qkv_host)
-    for k in range(args.steps):
-        if k + 1 < args.steps:
-            scene.stage(x_host, conf_host, qkv_host)  # pinned host -> device, side stream
-        scene.run_staged(out_host)                     # graph on this stream; device -> pinned host on the side stream
+    for k in range(steps):
+        if k + 1 < steps:
+            scene.stage(x_host, conf_host, qkv_host)
+        scene.run_staged(out_host)
     torch.cuda.current_stream().wait_stream(scene._copy_stream)
     e.record()
-    barrier()
-    e2e_ms = s.elapsed_time(e)
-    clocks = sampler.stop() if rank == 0 else None
+    torch.cuda.synchronize()
+    e2e_ms = s.elapsed_time(e) / steps
     if _lib.device_status(clear=False) != 0:
-        raise RuntimeError("attention kernel raised the device status word during the timed region")
-
-    t = torch.tensor([total_ms, e2e_ms, graph_ms], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    total_ms, e2e_ms, graph_ms = t.tolist()
-    scenes = args.steps * world
-    value = graph_ms / scenes
-    eager_value = total_ms / scenes
-    e2e_value = e2e_ms / scenes
-
-    if rank == 0:
-        P = plan.total
-        seg = (plan.offset[1:] - plan.offset[:-1]).tolist()
-        flops_frame = sum(4.0 * L * L * HDIM * HEADS for L in seg)
-        flops_global = 4.0 * P * P * HDIM * HEADS
-        t_attn = {"frame": 0.0, "global": 0.0}
-        t_merge = t_unmerge = 0.0
-        for kind, e4 in timers:
-            t_merge += e4[0].elapsed_time(e4[1])
-            t_attn[kind] += e4[1].elapsed_time(e4[2])
-            t_unmerge += e4[2].elapsed_time(e4[3])
-        n_layers = len(timers)
-        n_f = sum(1 for k, _ in timers if k == "frame")
-        n_g = n_layers - n_f
-        attn_flops = n_f * flops_frame + n_g * flops_global
-        attn_ms = t_attn["frame"] + t_attn["global"]
-        eager_achieved = attn_flops / (attn_ms * 1e-3) / 1e12
-        scene_flops = (n_f * flops_frame + n_g * flops_global) / args.steps  # timers hold args.steps scenes
-        dev_attn_ms = family_ms["frame"] + family_ms["global"]
-        achieved = scene_flops / (dev_attn_ms * 1e-3) / 1e12
-        merge_bytes = FRAMES * N_TOK * CH * 2 + P * CH * 2 + FRAMES * N_WIN + (FRAMES + 1) * 4
-        unmerge_bytes = P * CH * 2 + FRAMES * N_TOK * 8 + FRAMES * N_TOK * CH * 2
-        line = {
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": graph_ms / args.steps, "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
-            "dtype": "bf16", "data": "synthetic (seeded)",
-            "config": {"workload": workload_name(), "merged_tokens": P, "l2": "flushed between timed steps (256 MB write)",
-                       "launch": "one CUDA graph per scene (StaticScene): worst-case grids, no device-to-host read",
-                       "eager_ms_per_scene": eager_value,
-                       "parallelism": f"one independent scene per GPU x {world}"},
-            "roofline": {"kernel": "attn_fwd_sm100_kernel (48 launches/scene: 24 frame + 24 global)", "bound": "tensor",
-                         "achieved": achieved, "peak": pk["tflops"], "unit": "TFLOP/s", "frac": achieved / pk["tflops"],
-                         "peak_source": pk["source"] + " burst cuBLAS bf16",
-                         "traffic": 39.9e6, "traffic_note": "DRAM bytes of one global-layer launch (ncu capture of the 6456-token shape): qkv read once",
-                         "timing": "CUDA events around a graph of one scene's 24 frame / 24 global launches (device time)",
-                         "frame_tflops": (n_f * flops_frame / args.steps) / (family_ms["frame"] * 1e-3) / 1e12,
-                         "global_tflops": (n_g * flops_global / args.steps) / (family_ms["global"] * 1e-3) / 1e12,
-                         "avg_launch_ms": dev_attn_ms / len(LAYERS),
-                         "launched_one_by_one_tflops": eager_achieved,
-                         "share_of_scene": dev_attn_ms / sum(family_ms.values())},
-            "roofline_merge": {"bound": "hbm", "achieved": merge_bytes * len(LAYERS) / (family_ms["merge"] * 1e-3) / 1e9,
-                               "peak": pk["hbm_gbs"], "unit": "GB/s",
-                               "note": "bf16, 35.6 MB per launch (launch-latency sized: 5 us at the copy peak); the `kernels` entry is the HBM figure"},
-            "roofline_unmerge": {"bound": "hbm", "achieved": unmerge_bytes * len(LAYERS) / (family_ms["unmerge"] * 1e-3) / 1e9,
-                                 "peak": pk["hbm_gbs"], "unit": "GB/s"},
-            "scene_ms_by_family": family_ms,
-            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-            "gpu_launches": scene.launches_per_scene * args.steps,
-            "clocks": clocks,
-        }
-        if world == 1 and not args.no_micro:
-            line["kernels"] = micro(torch, dev, pk)
-            # the whole alternating-attention stack (48 blocks with their cuBLAS GEMMs) around the same kernels,
-            # merged against unmerged: the reference's own end-to-end comparison (src/bench.py), 5 scenes per arm
-            agg = aggregator_measure(FRAMES, 24, 5, report=False)
-            agg.pop("only")
-            line["aggregator_model"] = agg
-        if world == 1 and not args.no_cpu:
-            v, cores, sample, detail = cpu_chain_sample()
-            line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample,
-                                    "detail": detail}
-        print(json.dumps(line))
-    if world > 1:
-        dist.destroy_process_group()
+        raise RuntimeError("attention kernel raised the device status word in the 8-frame scene")
+    seg = (plan.offset[1:] - plan.offset[:-1]).tolist()
+    flops_frame, flops_global = sum(4.0 * L * L * HDIM * HEADS for L in seg), 4.0 * P * P * HDIM * HEADS
+    attn_ms = family_ms["frame"] + family_ms["global"]
+    achieved = (n_f * flops_frame + n_g * flops_global) / (attn_ms * 1e-3) / 1e12
+    merge_bytes = F8 * N_TOK * CH * 2 + P * CH * 2 + F8 * N_WIN + (F8 + 1) * 4
+    unmerge_bytes = P * CH * 2 + F8 * N_TOK * 8 + F8 * N_TOK * CH * 2
+    return {
+        "metric": "come_vggt_hot_path_ms_per_scene_8f", "value": graph_ms, "unit": UNIT, "steps": steps,
+        "workload": workload_name(F8), "merged_tokens": P, "launch": "one CUDA graph per scene (StaticScene): worst-case grids, no device-to-host read",
+        "l2": "flushed between timed steps (256 MB write)",
+        "e2e": {"value": e2e_ms, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "scene_ms_by_family": family_ms,
+        "roofline": {"bound": "tensor", "achieved": achieved, "peak": pk["tflops"], "unit": "TFLOP/s", "frac": achieved / pk["tflops"],
+                     "peak_source": pk["source"] + " burst cuBLAS bf16",
+                     "frame_tflops": n_f * flops_frame / (family_ms["frame"] * 1e-3) / 1e12,
+                     "global_tflops": n_g * flops_global / (family_ms["global"] * 1e-3) / 1e12,
+                     "timing": "CUDA events around a graph of one scene's 24 frame / 24 global launches (device time)"},
+        "merge_gbs": merge_bytes * len(LAYERS) / (family_ms["merge"] * 1e-3) / 1e9,
+        "unmerge_gbs": unmerge_bytes * len(LAYERS) / (family_ms["unmerge"] * 1e-3) / 1e9,
+        "gpu_launches": scene.launches_per_scene * steps,
+    }
 
 
 def run_batch(args):
@@ -469,88 +623,6 @@ def run_batch(args):
                        "l2": "inputs larger than L2 (GBs per rank)"},
             "attention_tflops_aggregate": flops / (per_step * 1e-3) / 1e12,
             "gpu_launches": scene.launches_per_scene * args.steps, "clocks": clocks,
-        }
-        print(json.dumps(line))
-    if world > 1:
-        dist.destroy_process_group()
-
-
-def run_frames100(args):
-    """ONE scene of 100 frames (137,400 tokens before merging) sharded by frame over the ranks.  Frame layers are
-    local; a global layer all-gathers the merged K/V rows over NCCL and attends the local query rows to all keys
-    (strong scaling: the scene is fixed, more GPUs shorten it)."""
-    import torch
-    import torch.distributed as dist
-
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
-    from come_b200 import _lib
-    from come_b200.chain import ShardedOpChain
-    frames = 100
-    pk = peaks()
-    chain = ShardedOpChain(frames, None, START, GRID, GRID, WIN, WIN, 0.5, HEADS, HDIM, LAYERS)
-    g = torch.Generator(device="cpu").manual_seed(4321)
-    conf = torch.rand((1, frames * GRID * GRID), generator=g).bfloat16().to(dev)  # replicated
-    gp, lp = chain.build_plans(conf)
-    n_local = chain.f_hi - chain.f_lo
-    gl = torch.Generator(device=dev).manual_seed(100 + rank)
-    x = torch.randn((n_local, N_TOK, CH), device=dev, generator=gl).bfloat16()
-    q = torch.randn((lp.total, HEADS, HDIM), device=dev, generator=gl).bfloat16()
-    kv = torch.randn((lp.total, 2, HEADS, HDIM), device=dev, generator=gl).bfloat16()
-    ev = lambda: torch.cuda.Event(enable_timing=True)  # noqa: E731
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    def step():
-        chain.build_plans(conf)
-        out = None
-        for kind in LAYERS:
-            out = chain.layer(gp, lp, x, q, kv, kind)
-        return out
-
-    for _ in range(min(args.warmup, 3)):
-        step()
-    barrier()
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
-    s, e = ev(), ev()
-    s.record()
-    for _ in range(args.steps):
-        step()
-    e.record()
-    barrier()
-    ms = torch.tensor([s.elapsed_time(e)], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-    clocks = sampler.stop() if rank == 0 else None
-    assert _lib.device_status(clear=False) == 0
-    if rank == 0:
-        per_scene = ms.item() / args.steps
-        P = gp.total
-        seg = (gp.offset[1:] - gp.offset[:-1]).tolist()
-        flops = 24 * (sum(4.0 * L * L * HDIM * HEADS for L in seg) + 4.0 * P * P * HDIM * HEADS)
-        kv_bytes = P * 2 * HEADS * HDIM * 2
-        line = {
-            "metric": "come_vggt_hot_path_ms_per_scene_100f", "value": per_scene, "unit": UNIT, "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_scene, "higher_is_better": False,
-            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic (seeded)",
-            "config": {"workload": workload_name(frames), "merged_tokens": P, "frames_per_s": frames / per_scene * 1e3,
-                       "parallelism": f"frames sharded over {world} GPU(s); frame layers local, global layers all-gather "
-                                      f"{kv_bytes / 1e6:.0f} MB of merged K/V per layer over NCCL",
-                       "l2": "inputs larger than L2 (merged K/V of one layer alone is > 126 MB)"},
-            "attention_tflops_aggregate": flops / (per_scene * 1e-3) / 1e12,
-            "attention_frac_of_bf16_peak_per_gpu": flops / (per_scene * 1e-3) / 1e12 / world / pk["tflops"],
-            "gpu_launches": (3 + 2 * 3 + 3 * len(LAYERS)) * args.steps, "clocks": clocks,
         }
         print(json.dumps(line))
     if world > 1:
@@ -947,11 +1019,13 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="come_b200", choices=["come_b200", "reference"])
-    ap.add_argument("--workload", default="scenes8", choices=["scenes8", "frames100", "batch256x4", "model100"],
-                    help="scenes8: one independent 8-frame scene per GPU (default); frames100: ONE 100-frame scene whose "
-                         "frames are sharded over the GPUs, global attention over all-gathered K/V; batch256x4: 256 independent "
+    ap.add_argument("--workload", default="frames100", choices=["frames100", "frames8", "batch256x4", "model100"],
+                    help="frames100 (default): ONE 100-frame scene whose frames are sharded over the GPUs, global attention over "
+                         "all-gathered K/V; frames8: the same for an 8-frame scene (quick runs); batch256x4: 256 independent "
                          "4-frame scenes with per-frame merge ratios ~U(0.25,0.75), sharded by scene, reported as scenes/s; model100: the "
                          "100-frame scene through the whole alternating-attention stack (with its GEMMs), sharded by frame")
+    ap.add_argument("--no-overlap", action="store_true", help="N > 1: all-gather in line instead of behind attention to the local keys")
+    ap.add_argument("--no-scene8", action="store_true", help="skip the 8-frame scene (extra key scene8)")
     ap.add_argument("--no-micro", action="store_true", help="skip the kernel-level sweep")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     args = ap.parse_args()
@@ -964,14 +1038,10 @@ def main():
     elif args.workload == "batch256x4":
         args.warmup = max(args.warmup, 3)
         run_batch(args)
-    elif args.workload == "frames100":
-        args.warmup = max(args.warmup, 3)
-        run_frames100(args)
     elif args.workload == "model100":
         run_model100(args)
     else:
-        args.warmup = max(args.warmup, 3)
-        run_gpu(args)
+        run_frames(args)
 
 
 if __name__ == "__main__":

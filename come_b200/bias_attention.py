@@ -56,13 +56,9 @@ class _JaggedAttentionBase(torch.nn.Module):
     def _attend_all_ranks(self, x: JaggedTokens, prepared, use_bias: bool) -> torch.Tensor:
         """These tokens are this rank's rows of one segment spread over the ranks: gather the prepared key / value rows
         of all ranks (the only exchange of the path) and attend the local query rows to them."""
-        from .flash_attn_fwd_cuda import varlen_fwd_rows
         ex = x.exchange
         qkv = prepared[0] if use_bias else prepared
-        kv_all = ex.gather(qkv[:, 1:].contiguous())
-        out, _lse = varlen_fwd_rows(qkv[:, 0], kv_all[:, 0], kv_all[:, 1], ex.cu_seqlens, ex.total,
-                                    ex.bias(qkv.dtype) if use_bias else None, self.attn.scale, ex.row_begin)
-        return out
+        return ex.attend(qkv[:, 0], qkv[:, 1:], self.attn.scale, use_bias)
 
     def _forward(self, x: JaggedTokens, pos: Optional[torch.Tensor], max_seqlen: Optional[int], use_bias: bool) -> JaggedTokens:
         attn = self.attn

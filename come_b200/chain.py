@@ -82,13 +82,18 @@ class ShardedOpChain:
 
     def __init__(self, frames_total: int, group=None, start_index: int = 5, grid_h: int = 37, grid_w: int = 37,
                  group_h: int = 3, group_w: int = 3, threshold: float = 0.5, num_heads: int = 16, head_dim: int = 64,
-                 layer_kinds: Optional[Sequence[str]] = None):
+                 layer_kinds: Optional[Sequence[str]] = None, overlap: bool = False, world: Optional[int] = None,
+                 rank: Optional[int] = None):
+        """``overlap``: hide the key / value exchange of a global layer behind attention to the local keys
+        (:class:`come_b200.dist.GlobalExchange`); the result then differs from the single-GPU one by the rounding of two
+        partial outputs.  Off: bit-identical to the single-GPU chain.  ``world`` / ``rank`` default to the process
+        group's; ``world=1`` runs the whole scene on this GPU whatever the group is."""
         import torch.distributed as dist
 
         from .dist import shard_range
         self.group = group
-        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
-        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.world = int(world) if world is not None else (dist.get_world_size(group) if dist.is_initialized() else 1)
+        self.rank = int(rank) if rank is not None else (dist.get_rank(group) if dist.is_initialized() and self.world > 1 else 0)
         self.frames_total = frames_total
         self.f_lo, self.f_hi = shard_range(frames_total, self.world, self.rank)
         self.layout = _lib.Layout.two_d(start_index, grid_h, grid_w, group_h, group_w)
@@ -97,6 +102,8 @@ class ShardedOpChain:
         self.num_heads, self.head_dim = num_heads, head_dim
         self.scale = head_dim ** -0.5
         self.layer_kinds = list(layer_kinds) if layer_kinds is not None else ["frame", "global"] * 24
+        self.overlap = bool(overlap)
+        self.exchange = None
 
     def build_plans(self, confidence_all: torch.Tensor):
         """``confidence_all [1, frames_total * H * W]`` (replicated) -> ``(global_plan, local_plan)``."""
@@ -110,23 +117,39 @@ class ShardedOpChain:
         self.row_begin = int(offsets[self.f_lo])
         assert self.rows[self.rank] == local_plan.total
         self.cu_global = torch.tensor([0, global_plan.total], dtype=torch.int32, device=mask_all.device)
+        from .dist import GlobalExchange
+        keep = self.exchange
+        self.exchange = GlobalExchange(self.rows, self.rank, global_plan.weight, self.group, overlap=self.overlap)
+        if keep is not None and keep.rows == self.exchange.rows:  # same packing: keep the side stream and the gather buffer
+            self.exchange._side, self.exchange._buf, self.exchange.events = keep._side, keep._buf, keep.events
+            if keep._side is not None:
+                self.exchange._cu_local = keep._cu_local
         return global_plan, local_plan
 
     def layer(self, global_plan: MergePlan, local_plan: MergePlan, x_local: torch.Tensor, q_local: torch.Tensor,
-              kv_local: torch.Tensor, kind: str) -> torch.Tensor:
+              kv_local: torch.Tensor, kind: str, timers: Optional[list] = None) -> torch.Tensor:
         """``x_local [frames_local, N, C]``; ``q_local [P_local, heads, head_dim]`` and ``kv_local [P_local, 2, heads,
-        head_dim]`` stand in for the projections of the merged local tokens."""
-        from .dist import gather_rows
+        head_dim]`` stand in for the projections of the merged local tokens.  ``timers``: a list that receives
+        ``(kind, [4 CUDA events])`` bracketing merge, attention and unmerge on the current stream."""
         from .flash_attn_fwd_cuda import varlen_fwd_rows
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)] if timers is not None else None
+        if ev:
+            ev[0].record()
         merged = local_plan.merge(x_local)
+        if ev:
+            ev[1].record()
         dtype = q_local.dtype
         if kind == "frame":
             out, _ = varlen_fwd_rows(q_local, kv_local[:, 0], kv_local[:, 1], local_plan.cu_seqlens(1), local_plan.max_seqlen,
                                      local_plan.perkey_bias(dtype), self.scale, 0)
         else:
-            kv_all = gather_rows(kv_local, self.rows, self.group) if self.world > 1 else kv_local
-            out, _ = varlen_fwd_rows(q_local, kv_all[:, 0], kv_all[:, 1], self.cu_global, global_plan.total,
-                                     global_plan.perkey_bias(dtype), self.scale, self.row_begin)
+            out = self.exchange.attend(q_local, kv_local, self.scale, use_bias=True)
+        if ev:
+            ev[2].record()
         del merged
         y = out.reshape(local_plan.total, self.num_heads * self.head_dim)
-        return local_plan.split(y).reshape(self.f_hi - self.f_lo, local_plan.tokens_per_frame, -1)
+        restored = local_plan.split(y).reshape(self.f_hi - self.f_lo, local_plan.tokens_per_frame, -1)
+        if ev:
+            ev[3].record()
+            timers.append((kind, ev))
+        return restored

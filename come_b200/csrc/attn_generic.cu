@@ -14,13 +14,15 @@ template <typename T>
 __global__ void __launch_bounds__(kGenericWarps * 32)
 attn_generic_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *__restrict__ v, int64_t q_rs,
                     int64_t k_rs, int64_t v_rs, const T *__restrict__ bias, const int *__restrict__ cu, int H, int D,
-                    float scale, T *__restrict__ out, int64_t o_rs, float *__restrict__ lse, int q_begin, int q_end) {
+                    float scale, T *__restrict__ out, int64_t o_rs, float *__restrict__ lse, int q_begin, int q_end,
+                    int kv_total, int q_free) {
     __shared__ float s_q[kGenericWarps][kGenericMaxD];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int seg = blockIdx.y, h = blockIdx.z;
-    const int s0 = cu[seg], s1 = cu[seg + 1];
-    const int row = max(s0, q_begin) + blockIdx.x * kGenericWarps + warp;  // global row; q / out / lse hold rows [q_begin, q_end)
-    if (row >= min(s1, q_end)) return;  // whole warp leaves together
+    const int s0 = cu ? cu[seg] : 0, s1 = cu ? cu[seg + 1] : kv_total;
+    // global row; q / out / lse hold rows [q_begin, q_end).  q_free: one segment that every query row attends to
+    const int row = (q_free ? q_begin : max(s0, q_begin)) + blockIdx.x * kGenericWarps + warp;
+    if (row >= (q_free ? q_end : min(s1, q_end))) return;  // whole warp leaves together
 
     const T *qrow = q + (int64_t)(row - q_begin) * q_rs + (int64_t)h * D;
     for (int d = lane; d < D; d += 32) s_q[warp][d] = Elem<T>::to_f32(qrow[d]);
@@ -77,12 +79,45 @@ attn_generic_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *_
 template <typename T>
 static int launch_generic(const void *q, const void *k, const void *v, int64_t q_rs, int64_t k_rs, int64_t v_rs,
                           const void *bias, const int *cu, int nseg, int max_seqlen, int H, int D, float scale, void *out,
-                          int64_t o_rs, float *lse, int64_t q_begin, int64_t q_end, cudaStream_t st) {
-    const int64_t span = max_seqlen < q_end - q_begin ? max_seqlen : q_end - q_begin;
+                          int64_t o_rs, float *lse, int64_t q_begin, int64_t q_end, int64_t kv_total, bool q_free, cudaStream_t st) {
+    const int64_t span = (!q_free && max_seqlen < q_end - q_begin) ? max_seqlen : q_end - q_begin;
     dim3 grid((unsigned)((span + kGenericWarps - 1) / kGenericWarps), nseg, H);
     attn_generic_kernel<T><<<grid, kGenericWarps * 32, 0, st>>>((const T *)q, (const T *)k, (const T *)v, q_rs, k_rs, v_rs,
-                                                                (const T *)bias, cu, H, D, scale, (T *)out, o_rs, lse, (int)q_begin, (int)q_end);
+                                                                (const T *)bias, cu, H, D, scale, (T *)out, o_rs, lse, (int)q_begin, (int)q_end,
+                                                                (int)kv_total, q_free ? 1 : 0);
     return check_launch("come_attn_varlen_fwd (CUDA-core kernel)");
+}
+
+// out = (w_a * out_a + w_b * out_b) / (w_a + w_b) with w_x = exp(lse_x - max(lse_a, lse_b)): the exact merge of two
+// attention results over disjoint key sets.  A thread owns 8 consecutive features (16 bytes) of a (row, head).
+template <typename T>
+__global__ void __launch_bounds__(256)
+attn_combine_kernel(const T *__restrict__ oa, const float *__restrict__ la, const T *__restrict__ ob,
+                    const float *__restrict__ lb, int64_t rows, int H, int D, T *__restrict__ out, float *__restrict__ lse_out) {
+    const int per_head = D / 8;
+    const int64_t n = rows * H * per_head;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t rh = i / per_head;  // row * H + head
+        const int64_t row = rh / H;
+        const int h = (int)(rh - row * H);
+        const float a = la[(int64_t)h * rows + row], b = lb[(int64_t)h * rows + row];
+        const float m = fmaxf(a, b);
+        float wa = 0.0f, wb = 0.0f, inv = 0.0f;
+        if (m > -INFINITY) {  // both key sets empty: the row stays zero
+            wa = expf(a - m);
+            wb = expf(b - m);
+            inv = 1.0f / (wa + wb);
+        }
+        const uint4 va = reinterpret_cast<const uint4 *>(oa)[i], vb = reinterpret_cast<const uint4 *>(ob)[i];
+        const T *xa = reinterpret_cast<const T *>(&va), *xb = reinterpret_cast<const T *>(&vb);
+        uint4 vo;
+        T *xo = reinterpret_cast<T *>(&vo);
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+            xo[e] = Elem<T>::from_f32((wa * Elem<T>::to_f32(xa[e]) + wb * Elem<T>::to_f32(xb[e])) * inv);
+        reinterpret_cast<uint4 *>(out)[i] = vo;
+        if (lse_out && (i - rh * per_head) == 0) lse_out[(int64_t)h * rows + row] = (m > -INFINITY) ? m + logf(wa + wb) : -INFINITY;
+    }
 }
 
 }  // namespace come
@@ -93,12 +128,13 @@ static int attn_dispatch(const void *q_dev, const void *k_dev, const void *v_dev
                          int64_t q_begin, int64_t q_rows, int num_heads, int head_dim, int64_t q_row_stride,
                          int64_t k_row_stride, int64_t v_row_stride, const void *bias_dev, const int32_t *cu_seqlens_dev,
                          int num_segments, int max_seqlen, const int32_t *max_seqlen_dev, float softmax_scale, void *out_dev,
-                         int64_t out_row_stride, float *lse_dev, int backend, void *stream) {
+                         int64_t out_row_stride, float *lse_dev, int backend, void *stream, bool q_free = false) {
     COME_REQUIRE(dtype == COME_F16 || dtype == COME_BF16, "FlashAttention only support fp16 and bf16 data type");
     COME_REQUIRE(num_segments > 0, "batch size must be positive");
     COME_REQUIRE(total >= 0 && num_heads > 0, "total must be >= 0 and num_heads > 0");
-    COME_REQUIRE(q_begin >= 0 && q_rows >= 0 && q_begin + q_rows <= total, "query rows [%lld, %lld) must lie inside [0, %lld)",
+    COME_REQUIRE(q_begin >= 0 && q_rows >= 0 && (q_free || q_begin + q_rows <= total), "query rows [%lld, %lld) must lie inside [0, %lld)",
                  (long long)q_begin, (long long)(q_begin + q_rows), (long long)total);
+    COME_REQUIRE(q_rows < (1ll << 31), "query rows must fit int32");
     COME_REQUIRE(head_dim > 0 && head_dim <= 256, "FlashAttention forward only supports head dimension at most 256");
     COME_REQUIRE(head_dim % 8 == 0, "query, key, value, and out_ must have a head_size that is a multiple of 8");
     COME_REQUIRE(max_seqlen >= 0, "max_seqlen must be >= 0");
@@ -108,7 +144,7 @@ static int attn_dispatch(const void *q_dev, const void *k_dev, const void *v_dev
                  "row strides must cover num_heads * head_dim elements");
     COME_REQUIRE(total < (1ll << 31), "total tokens must fit int32");
     if (total == 0 || max_seqlen == 0 || q_rows == 0) return COME_OK;
-    COME_REQUIRE(q_dev && k_dev && v_dev && out_dev && cu_seqlens_dev, "q / k / v / out / cu_seqlens must not be NULL");
+    COME_REQUIRE(q_dev && k_dev && v_dev && out_dev && (cu_seqlens_dev || q_free), "q / k / v / out / cu_seqlens must not be NULL");
     cudaStream_t st = (cudaStream_t)stream;
 
     AttnArgs a;
@@ -116,6 +152,7 @@ static int attn_dispatch(const void *q_dev, const void *k_dev, const void *v_dev
     a.dtype = dtype; a.total = total; a.q_begin = q_begin; a.q_end = q_begin + q_rows; a.H = num_heads; a.D = head_dim;
     a.q_rs = q_row_stride; a.k_rs = k_row_stride; a.v_rs = v_row_stride; a.o_rs = out_row_stride;
     a.nseg = num_segments; a.max_seqlen = max_seqlen; a.max_seqlen_dev = max_seqlen_dev; a.scale = softmax_scale;
+    a.q_free = q_free;
 
     const bool tc_ok = attn_sm100_supported(a);
     if (backend == 2 && !tc_ok) {
@@ -126,10 +163,10 @@ static int attn_dispatch(const void *q_dev, const void *k_dev, const void *v_dev
     if (dtype == COME_F16)
         return launch_generic<__half>(q_dev, k_dev, v_dev, q_row_stride, k_row_stride, v_row_stride, bias_dev, cu_seqlens_dev,
                                       num_segments, max_seqlen, num_heads, head_dim, softmax_scale, out_dev, out_row_stride,
-                                      lse_dev, a.q_begin, a.q_end, st);
+                                      lse_dev, a.q_begin, a.q_end, total, q_free, st);
     return launch_generic<__nv_bfloat16>(q_dev, k_dev, v_dev, q_row_stride, k_row_stride, v_row_stride, bias_dev,
                                          cu_seqlens_dev, num_segments, max_seqlen, num_heads, head_dim, softmax_scale,
-                                         out_dev, out_row_stride, lse_dev, a.q_begin, a.q_end, st);
+                                         out_dev, out_row_stride, lse_dev, a.q_begin, a.q_end, total, q_free, st);
 }
 
 extern "C" int come_attn_varlen_fwd(const void *q_dev, const void *k_dev, const void *v_dev, int dtype, int64_t total,
@@ -151,4 +188,46 @@ extern "C" int come_attn_varlen_fwd_rows(const void *q_dev, const void *k_dev, c
     return attn_dispatch(q_dev, k_dev, v_dev, dtype, total, q_row_begin, q_rows, num_heads, head_dim, q_row_stride,
                          k_row_stride, v_row_stride, bias_dev, cu_seqlens_dev, num_segments, max_seqlen, max_seqlen_dev,
                          softmax_scale, out_dev, out_row_stride, lse_dev, backend, stream);
+}
+
+
+extern "C" int come_attn_cross_fwd(const void *q_dev, const void *k_dev, const void *v_dev, int dtype, int64_t q_rows,
+                                   int64_t kv_rows, int num_heads, int head_dim, int64_t q_row_stride, int64_t k_row_stride,
+                                   int64_t v_row_stride, const void *bias_dev, float softmax_scale, void *out_dev,
+                                   int64_t out_row_stride, float *lse_dev, int backend, void *stream) {
+    COME_REQUIRE(kv_rows > 0 || q_rows == 0, "come_attn_cross_fwd needs at least one key");
+    const int max_len = (int)(kv_rows < (1ll << 31) ? kv_rows : 0);
+    return attn_dispatch(q_dev, k_dev, v_dev, dtype, kv_rows, 0, q_rows, num_heads, head_dim, q_row_stride, k_row_stride,
+                         v_row_stride, bias_dev, nullptr, 1, max_len, nullptr, softmax_scale, out_dev, out_row_stride,
+                         lse_dev, backend, stream, true);
+}
+
+extern "C" int come_attn_combine(const void *out_a_dev, const float *lse_a_dev, const void *out_b_dev, const float *lse_b_dev,
+                                 int dtype, int64_t rows, int num_heads, int head_dim, void *out_dev, float *lse_out_dev,
+                                 void *stream) {
+    COME_REQUIRE(dtype == COME_F16 || dtype == COME_BF16, "come_attn_combine: dtype must be COME_F16 or COME_BF16");
+    COME_REQUIRE(rows >= 0 && num_heads > 0 && head_dim > 0 && head_dim % 8 == 0, "come_attn_combine: bad shape");
+    if (rows == 0) return COME_OK;
+    COME_REQUIRE(out_a_dev && out_b_dev && lse_a_dev && lse_b_dev && out_dev, "come_attn_combine: NULL pointer");
+    auto al16 = [](const void *p) { return ((uintptr_t)p & 15) == 0; };
+    COME_REQUIRE(al16(out_a_dev) && al16(out_b_dev) && al16(out_dev), "come_attn_combine: outputs must be 16-byte aligned");
+    const int64_t n = rows * num_heads * (head_dim / 8);
+    int64_t blocks = (n + 255) / 256;
+    const int64_t cap = (int64_t)sm_count() * 8;
+    if (blocks > cap) blocks = cap;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dtype == COME_F16)
+        attn_combine_kernel<__half><<<(unsigned)blocks, 256, 0, st>>>((const __half *)out_a_dev, lse_a_dev, (const __half *)out_b_dev,
+                                                                    lse_b_dev, rows, num_heads, head_dim, (__half *)out_dev, lse_out_dev);
+    else
+        attn_combine_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, st>>>((const __nv_bfloat16 *)out_a_dev, lse_a_dev,
+                                                                           (const __nv_bfloat16 *)out_b_dev, lse_b_dev, rows,
+                                                                           num_heads, head_dim, (__nv_bfloat16 *)out_dev, lse_out_dev);
+    return check_launch("come_attn_combine");
+}
+
+extern "C" int come_attn_set_cta_limit(int max_ctas) {
+    COME_REQUIRE(max_ctas >= 0, "come_attn_set_cta_limit: max_ctas must be >= 0");
+    attn_sm100_set_cta_limit(max_ctas);
+    return COME_OK;
 }

@@ -108,7 +108,6 @@ struct SharedStorage {
     uint64_t o_done[kTiles];
     uint64_t s_empty[kTiles];
     uint32_t tmem_base;
-    uint32_t pipe_lock;  // held by the issuer warp that is feeding the tensor pipe (see pipe_acquire)
     volatile uint32_t abort_flag;
     int scan_warp[kThreads / 32];
 };
@@ -157,32 +156,6 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, Shared
     }
 }
 
-// The three issuer warps feed one tensor pipe.  Two warps that issue at the same time have their instructions
-// interleaved by the hardware, so both groups finish late and the two query tiles stay in lock step, colliding again
-// at every key tile.  With the lock a group (the Q K^T of a key tile, or its P V) is issued as a whole: the warp that
-// comes second is delayed once by the first one's group and from then on the tiles run out of phase, each finding the
-// pipe free when its turn comes.  Bounded like every other wait of the kernel.
-__device__ __forceinline__ bool pipe_acquire(SharedStorage &sh, unsigned int *status, uint32_t code, int lane) {
-    bool ok = true;
-    if (lane == 0) {
-        const long long t0 = clock64();
-        while (atomicCAS(&sh.pipe_lock, 0u, 1u) != 0u) {
-            if (sh.abort_flag != 0) { ok = false; break; }
-            if (clock64() - t0 > kWaitTicks) {
-                sh.abort_flag = 1;
-                atomicOr(status, code);
-                ok = false;
-                break;
-            }
-        }
-    }
-    return __all_sync(0xffffffffu, ok);
-}
-__device__ __forceinline__ void pipe_release(SharedStorage &sh, int lane) {
-    __syncwarp();
-    if (lane == 0) atomicExch(&sh.pipe_lock, 0u);
-}
-
 __device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *map, int c0, int c1, int c2, uint64_t *bar) {
     asm volatile(
         "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
@@ -195,30 +168,25 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
-// The three wrappers below are called by ALL lanes of an issuer warp in warp-uniform control flow; one elected lane
-// executes the instruction.  Keeping the surrounding address arithmetic uniform is what lets the issue loop keep
-// up with the tensor core (a divergent single-thread loop measured ~70 clocks per instruction, this form ~30-60).
-__device__ __forceinline__ void tc_commit(uint64_t *bar) {
-    asm volatile(
-        "{\n\t.reg .pred e;\n\telect.sync _|e, 0xffffffff;\n\t"
-        "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}"
-        ::"r"(smem_u32(bar)) : "memory");
+// The issuer warps run their loops in warp-uniform control flow; for a group of instructions (the Q K^T of a key tile
+// with its commits, or its P V) one lane is elected once and issues the whole group.  Electing per instruction (every
+// lane evaluating the operands, one lane executing) measured 3-5 % slower: an issuer warp shares its scheduler with
+// three softmax warps, and every instruction it does not issue shortens the time from "P is staged" to "P V is queued".
+__device__ __forceinline__ bool elect_one() {
+    uint32_t e;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(e));
+    return e != 0;
 }
-// D[tmem] (+)= A[smem] * B[smem]
-__device__ __forceinline__ void tc_mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p, e;\n\telect.sync _|e, 0xffffffff;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
+__device__ __forceinline__ void tc_commit_1(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-// D[tmem] (+)= A[tmem] * B[smem]
-__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p, e;\n\telect.sync _|e, 0xffffffff;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
+__device__ __forceinline__ void tc_mma_ss_1(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_mma_ts_1(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+                 ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
 
 // 32 lanes x 32 consecutive 32-bit columns: thread i of the warp receives lane (base lane + i).
@@ -352,7 +320,7 @@ __host__ __device__ constexpr uint32_t make_idesc(bool bf16, int M, int N, bool 
 
 enum : uint32_t {
     kErrQFull = 1u << 0, kErrKvFull = 1u << 1, kErrKvEmpty = 1u << 2, kErrSlabFull = 1u << 3, kErrSlabEmpty = 1u << 4,
-    kErrSFull = 1u << 5, kErrSEmpty = 1u << 6, kErrPFull = 1u << 7, kErrODone = 1u << 8, kErrPipeLock = 1u << 9,
+    kErrSFull = 1u << 5, kErrSEmpty = 1u << 6, kErrPFull = 1u << 7, kErrODone = 1u << 8,
 };
 
 // One work item = the (up to) kTiles 128-row query tiles [q_row0, q_row0 + kTiles * 128) of one (segment, head).
@@ -373,9 +341,11 @@ __device__ __forceinline__ int segment_blocks(int seg, const int *__restrict__ c
 // Item -> (head, segment, query block).  With a prefix table (seg_prefix != nullptr) the items are exactly the query
 // blocks that exist, in (head, segment, block) order; without it every segment gets `nblk_x` slots and the surplus ones
 // are skipped as invalid.
+// q_free: the launch has one segment whose keys all query rows [q_begin, q_end) attend to, whether or not those rows lie
+// inside the segment (attention of this GPU's rows to keys gathered from other GPUs); cu may then be NULL = [0, kv_total].
 template <bool kPrefix>
 __device__ __forceinline__ WorkItem decode_item(int item, int nblk_x, int nseg, const int *__restrict__ cu, int q_begin, int q_end,
-                                                const int *seg_prefix) {
+                                                const int *seg_prefix, int kv_total, bool q_free) {
     WorkItem w;
     int bx, seg;
     if constexpr (kPrefix) {
@@ -396,13 +366,13 @@ __device__ __forceinline__ WorkItem decode_item(int item, int nblk_x, int nseg, 
         seg = rest % nseg;
         w.head = rest / nseg;
     }
-    w.s0 = cu[seg];
-    w.s1 = cu[seg + 1];
+    w.s0 = cu ? cu[seg] : 0;
+    w.s1 = cu ? cu[seg + 1] : kv_total;
     const int seg_len = w.s1 - w.s0;
     // Query rows of this launch: global rows [q_begin, q_end) (the whole packed sequence for plain self-attention; a
     // slice when the query rows are sharded).  q / out / lse are indexed by (global row - q_begin); k / v by global row.
-    const int q_lo = max(w.s0, q_begin);
-    w.q_hi = min(w.s1, q_end);
+    const int q_lo = q_free ? q_begin : max(w.s0, q_begin);
+    w.q_hi = q_free ? q_end : min(w.s1, q_end);
     w.q_row0 = q_lo + bx * (kTiles * kBlockM);
     w.valid = w.q_row0 < w.q_hi;
     w.n_mt = min(kTiles, (w.q_hi - w.q_row0 + kBlockM - 1) / kBlockM);  // query tiles with at least one valid row
@@ -422,7 +392,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                       const __grid_constant__ CUtensorMap map_v, const void *__restrict__ bias_ptr,
                       const int *__restrict__ cu, float scale_log2, float inv_scale, void *__restrict__ out_ptr, int64_t o_rs,
                       float *__restrict__ lse, int q_begin, int q_end, int nblk_x, int nseg, int num_heads,
-                      const int *__restrict__ max_len_dev, unsigned int *__restrict__ status) {
+                      const int *__restrict__ max_len_dev, unsigned int *__restrict__ status, int kv_total, int q_free_flag) {
     using T = typename std::conditional<kBF16, __nv_bfloat16, __half>::type;
     extern __shared__ uint8_t smem_raw[];
     SharedStorage &sh = *reinterpret_cast<SharedStorage *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -472,6 +442,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     const int *seg_prefix = use_prefix ? prefix_table : nullptr;
     const int total_items = use_prefix ? prefix_table[nseg] * num_heads : nblk_x * nseg * num_heads;
     const bool has_bias = bias_ptr != nullptr;
+    const bool q_free = q_free_flag != 0;
     // a key tile needs the bias step when there is a bias, or when it is the partial last tile (masking)
     auto uses_slab = [&](const WorkItem &w, int j) { return has_bias || (w.ragged_tail && j == w.n_kv - 1); };
 
@@ -480,7 +451,6 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     if (threadIdx.x == 0) {
         // an earlier CTA that gave up leaves the status word raised: later CTAs then skip their work
         sh.abort_flag = (*(volatile unsigned int *)status != 0) ? 1u : 0u;
-        sh.pipe_lock = 0u;
         for (int i = 0; i < kTiles; ++i) {
             for (int b = 0; b < 2; ++b) {
                 mbar_init(&sh.q_full[i][b], 1);
@@ -536,7 +506,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         int slab_it = 0;       // bias slab ring position, advanced once per key tile that uses the bias step
         int q_uses[kTiles] = {};  // items that loaded query tile t so far (buffer and phase of q_full / q_empty)
         for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
-            const WorkItem w = decode_item<kPrefix>(item, nblk_x, nseg, cu, q_begin, q_end, seg_prefix);
+            const WorkItem w = decode_item<kPrefix>(item, nblk_x, nseg, cu, q_begin, q_end, seg_prefix, kv_total, q_free);
             if (!w.valid) continue;
             if (lane == 0) {
                 for (int t = 0; t < w.n_mt && ok; ++t) {
@@ -616,7 +586,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         const long long tr_start = clock64();
 #endif
         for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
-            const WorkItem w = decode_item<kPrefix>(item, nblk_x, nseg, cu, q_begin, q_end, seg_prefix);
+            const WorkItem w = decode_item<kPrefix>(item, nblk_x, nseg, cu, q_begin, q_end, seg_prefix, kv_total, q_free);
             if (!w.valid) continue;
             if (t >= w.n_mt) {
                 // This query tile is empty in this item: release the K/V and slab slots without using them, so that the
@@ -648,77 +618,84 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             // S(0), then per key tile j: S(j+1) = Q K_(j+1)^T as soon as the softmax group has read S(j) into registers,
             // and O += P(j) V_j as soon as P(j) is staged.  Ring slot of K_j is 2j, of V_j is 2j+1 (from `it`).  The other
             // query tile's issuer runs the same loop independently.
-            auto issue_s = [&](int jj) -> bool {  // jj = key tile whose scores are produced
+            // S(jj) = Q K_jj^T (+ the bias step): what it waits for, and its instructions
+            auto wait_s = [&](int jj) -> bool {
                 const int k_it = it + 2 * jj, k_slot = k_it % kStages;
-                const bool slab = uses_slab(w, jj);
                 const int bs = slab_it % kSlabStages;
                 TRACE_BEGIN();
                 bool good = mbar_wait(&sh.kv_full[k_slot], (k_it / kStages) & 1, sh, status, kErrKvFull);
-                if (good && slab) good = mbar_wait(&sh.slab_full[bs], (slab_it / kSlabStages) & 1, sh, status, kErrSlabFull);
+                if (good && uses_slab(w, jj)) good = mbar_wait(&sh.slab_full[bs], (slab_it / kSlabStages) & 1, sh, status, kErrSlabFull);
                 TRACE_END(0);
                 TRACE_BEGIN();
                 // the softmax group must have pulled the previous scores (also those of the previous item) out of S
                 if (good && step + jj > 0) good = mbar_wait(&sh.s_empty[t], (step + jj - 1) & 1, sh, status, kErrSEmpty);
                 TRACE_END(1);
                 TRACE_STAMP(8, step + jj == 65);
-                good = __all_sync(0xffffffffu, good);
-                if (!good) return false;
-#ifdef COME_PIPE_LOCK
-                if (!pipe_acquire(sh, status, kErrPipeLock, lane)) return false;
-#endif
-                tc_fence_after();
-                const uint64_t k_desc = kv_desc0 + (uint64_t)(k_slot * (kKvTileBytes >> 4));
-                tc_mma_ss(s_tmem, q_desc + 0, k_desc + 0, idesc_qk, 0u);
-                tc_mma_ss(s_tmem, q_desc + 2, k_desc + 2, idesc_qk, 1u);
-                tc_mma_ss(s_tmem, q_desc + 4, k_desc + 4, idesc_qk, 1u);
-                tc_mma_ss(s_tmem, q_desc + 6, k_desc + 6, idesc_qk, 1u);
-                if (slab) tc_mma_ss(s_tmem, q_slab_desc, k_slab_desc0 + (uint64_t)(bs * (kKvTileBytes >> 4)), idesc_slab, 1u);
-                tc_commit(&sh.s_full[t]);
-                tc_commit(&sh.kv_empty[k_slot]);
-                if (slab) {
-                    tc_commit(&sh.slab_empty[bs]);
-                    ++slab_it;
-                }
-                if (jj == w.n_kv - 1) tc_commit(&sh.q_empty[t][qb]);  // the item's last use of the query tile
-#ifdef COME_PIPE_LOCK
-                pipe_release(sh, lane);
-#endif
-                TRACE_STAMP(11, step + jj == 65);
-                return true;
+                return __all_sync(0xffffffffu, good);
             };
-            ok = issue_s(0);
-            for (int j = 0; j < w.n_kv && ok; ++j) {
-                if (j + 1 < w.n_kv) {
-                    ok = issue_s(j + 1);
-                    if (!ok) break;
+            auto emit_s = [&](int jj) {
+                const int k_it = it + 2 * jj, k_slot = k_it % kStages;
+                const bool slab = uses_slab(w, jj);
+                const int bs = slab_it % kSlabStages;
+                const uint64_t k_desc = kv_desc0 + (uint64_t)(k_slot * (kKvTileBytes >> 4));
+                if (elect_one()) {  // one lane issues the whole group: a single election and branch instead of one per instruction
+                    tc_mma_ss_1(s_tmem, q_desc + 0, k_desc + 0, idesc_qk, 0u);
+                    tc_mma_ss_1(s_tmem, q_desc + 2, k_desc + 2, idesc_qk, 1u);
+                    tc_mma_ss_1(s_tmem, q_desc + 4, k_desc + 4, idesc_qk, 1u);
+                    tc_mma_ss_1(s_tmem, q_desc + 6, k_desc + 6, idesc_qk, 1u);
+                    if (slab) tc_mma_ss_1(s_tmem, q_slab_desc, k_slab_desc0 + (uint64_t)(bs * (kKvTileBytes >> 4)), idesc_slab, 1u);
+                    tc_commit_1(&sh.s_full[t]);
+                    tc_commit_1(&sh.kv_empty[k_slot]);
+                    if (slab) tc_commit_1(&sh.slab_empty[bs]);
+                    if (jj == w.n_kv - 1) tc_commit_1(&sh.q_empty[t][qb]);
                 }
+                __syncwarp();
+                if (slab) ++slab_it;
+                TRACE_STAMP(11, step + jj == 65);
+            };
+            // O += P(j) V_j: what it waits for, and its instructions
+            auto wait_pv = [&](int j) -> bool {
                 const int v_it = it + 2 * j + 1, v_slot = v_it % kStages;
                 TRACE_BEGIN();
-                ok = mbar_wait(&sh.kv_full[v_slot], (v_it / kStages) & 1, sh, status, kErrKvFull);
+                bool good = mbar_wait(&sh.kv_full[v_slot], (v_it / kStages) & 1, sh, status, kErrKvFull);
                 TRACE_END(2);
                 TRACE_BEGIN();
-                if (ok) ok = mbar_wait(&sh.p_full[t], (step + j) & 1, sh, status, kErrPFull);
+                if (good) good = mbar_wait(&sh.p_full[t], (step + j) & 1, sh, status, kErrPFull);
                 TRACE_END(3);
                 TRACE_COUNT(5, 1);
                 TRACE_STAMP(9, step + j == 64);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-#ifdef COME_PIPE_LOCK
-                ok = pipe_acquire(sh, status, kErrPipeLock, lane);
-                if (!ok) break;
-#endif
-                tc_fence_after();
+                return __all_sync(0xffffffffu, good);
+            };
+            auto emit_pv = [&](int j) {
+                const int v_it = it + 2 * j + 1, v_slot = v_it % kStages;
                 const uint64_t v_desc = kv_desc0 + (uint64_t)(v_slot * (kKvTileBytes >> 4));
                 // 16 keys per instruction: 8 columns of 16-bit pairs of P, 16 rows (2048 bytes) of the V tile
+                if (elect_one()) {
 #pragma unroll
-                for (int i = 0; i < kBlockN / 16; ++i)
-                    tc_mma_ts(o_tmem, p_tmem + 8 * i, v_desc + (uint64_t)(i * 128), idesc_pv, (j > 0 || i > 0) ? 1u : 0u);
-                tc_commit(&sh.o_done[t]);
-                tc_commit(&sh.kv_empty[v_slot]);
-#ifdef COME_PIPE_LOCK
-                pipe_release(sh, lane);
-#endif
+                    for (int i = 0; i < kBlockN / 16; ++i)
+                        tc_mma_ts_1(o_tmem, p_tmem + 8 * i, v_desc + (uint64_t)(i * 128), idesc_pv, (j > 0 || i > 0) ? 1u : 0u);
+                    tc_commit_1(&sh.o_done[t]);
+                    tc_commit_1(&sh.kv_empty[v_slot]);
+                }
+                __syncwarp();
                 TRACE_STAMP(10, step + j == 64);
+            };
+            ok = wait_s(0);
+            if (ok) {
+                tc_fence_after();
+                emit_s(0);
+            }
+            for (int j = 0; j < w.n_kv && ok; ++j) {
+                if (j + 1 < w.n_kv) {
+                    ok = wait_s(j + 1);
+                    if (!ok) break;
+                    tc_fence_after();
+                    emit_s(j + 1);
+                }
+                ok = wait_pv(j);
+                if (!ok) break;
+                tc_fence_after();
+                emit_pv(j);
             }
             it += 2 * w.n_kv;
             step += w.n_kv;
@@ -745,7 +722,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         const long long tr_start = clock64();
 #endif
         for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
-            const WorkItem w = decode_item<kPrefix>(item, nblk_x, nseg, cu, q_begin, q_end, seg_prefix);
+            const WorkItem w = decode_item<kPrefix>(item, nblk_x, nseg, cu, q_begin, q_end, seg_prefix, kv_total, q_free);
             if (!w.valid || t >= w.n_mt) continue;
             const int n_kv = w.n_kv;
             const int row = w.q_row0 + t * kBlockM + r;
@@ -1019,6 +996,10 @@ template <typename Kernel> static int ensure_smem_optin(Kernel kernel, int slot,
     return COME_OK;
 }
 
+// Upper bound on the CTAs of the persistent kernel for launches issued by this host thread (0 = one per SM).
+static thread_local int t_cta_limit = 0;
+void attn_sm100_set_cta_limit(int max_ctas) { t_cta_limit = max_ctas > 0 ? max_ctas : 0; }
+
 int attn_sm100_launch(const AttnArgs &a, cudaStream_t stream) {
     unsigned int *status = status_word_dev();
     if (!status) return COME_ERR_CUDA;
@@ -1027,10 +1008,10 @@ int attn_sm100_launch(const AttnArgs &a, cudaStream_t stream) {
     if ((rc = make_map(&mq, a.q, a.dtype, a.q_end - a.q_begin, a.H, a.q_rs, kBlockM)) != COME_OK) return rc;
     if ((rc = make_map(&mk, a.k, a.dtype, a.total, a.H, a.k_rs, kBlockN)) != COME_OK) return rc;
     if ((rc = make_map(&mv, a.v, a.dtype, a.total, a.H, a.v_rs, kBlockN)) != COME_OK) return rc;
-    const bool with_table = a.nseg >= kMinPrefixSegs && a.nseg <= kMaxPrefixSegs;
+    const bool with_table = !a.q_free && a.nseg >= kMinPrefixSegs && a.nseg <= kMaxPrefixSegs;
     const size_t smem = sizeof(SharedStorage) + 1024 + (with_table ? kPrefixTableBytes : 0);
     const int64_t q_rows = a.q_end - a.q_begin;
-    const int64_t span = a.max_seqlen < q_rows ? a.max_seqlen : q_rows;  // most query rows any segment can own here
+    const int64_t span = a.q_free ? q_rows : (a.max_seqlen < q_rows ? a.max_seqlen : q_rows);  // most query rows any segment can own here
     const int nblk_x = (int)((span + kTiles * kBlockM - 1) / (kTiles * kBlockM));
     const int64_t items = (int64_t)nblk_x * a.nseg * a.H;
     if (items <= 0) return COME_OK;
@@ -1038,7 +1019,8 @@ int attn_sm100_launch(const AttnArgs &a, cudaStream_t stream) {
         set_error("come_attn_varlen_fwd: %lld work items do not fit 32 bits", (long long)items);
         return COME_ERR_ARG;
     }
-    const int sms = sm_count();
+    int sms = sm_count();
+    if (t_cta_limit > 0 && t_cta_limit < sms) sms = t_cta_limit;
     const unsigned grid = (unsigned)(items < sms ? items : sms);  // persistent: one CTA per SM walks the items
     const float scale_log2 = a.scale * kLog2e;
     const float inv_scale = 1.0f / a.scale;
@@ -1047,7 +1029,8 @@ int attn_sm100_launch(const AttnArgs &a, cudaStream_t stream) {
         if ((rc = ensure_smem_optin(attn_fwd_sm100_kernel<BF16, PREFIX>, SLOT, smem)) != COME_OK) return rc;                    \
         attn_fwd_sm100_kernel<BF16, PREFIX><<<grid, kThreads, smem, stream>>>(mq, mk, mv, a.bias, a.cu, scale_log2, inv_scale, a.out, \
                                                                               a.o_rs, a.lse, (int)a.q_begin, (int)a.q_end, nblk_x,   \
-                                                                              a.nseg, a.H, a.max_seqlen_dev, status);               \
+                                                                              a.nseg, a.H, a.max_seqlen_dev, status, (int)a.total,   \
+                                                                              a.q_free ? 1 : 0);                                     \
     } while (0)
     if (a.dtype == COME_BF16) {
         if (with_table) COME_ATTN_LAUNCH(true, true, 0);

@@ -17,10 +17,13 @@ struct AttnArgs {
     int nseg, max_seqlen;
     const int *max_seqlen_dev;  // optional device-resident bound of the longest segment (tightens the work list)
     float scale;
+    bool q_free;  // one segment; every query row attends to all of its keys wherever the row lies (cu may be NULL = [0, total])
 };
 
 // True when the tensor-core kernel can take the problem (head_dim 64, TMA-compatible addresses and strides).
 bool attn_sm100_supported(const AttnArgs &a);
+// Caps the CTAs of the following launches of the calling host thread (0 = one CTA per SM).
+void attn_sm100_set_cta_limit(int max_ctas);
 // Enqueues the tensor-core kernel; returns a COME_* code.
 int attn_sm100_launch(const AttnArgs &a, cudaStream_t stream);
 

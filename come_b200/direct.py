@@ -19,7 +19,7 @@ import torch
 from .bias_attention import JaggedAttention_w_Bias
 from .token_merger import JaggedTokens, MergePlan
 
-__all__ = ["DirectAttention"]
+__all__ = ["DirectAttention", "DirectMlp"]
 
 
 class DirectAttention(torch.nn.Module):
@@ -71,3 +71,35 @@ class DirectAttention(torch.nn.Module):
         out = self.attn_op(jag, pos=plan.positions() if use_pos else None, max_seqlen=max_seqlen)
         gamma = None if ls1_gamma is None else ls1_gamma.detach().to(device=x.device, dtype=x.dtype)
         return plan.split_add(out.tokens.squeeze(0), dense, gamma).view(*input_shape)
+
+
+class DirectMlp(torch.nn.Module):
+    """Drop-in for ``block.mlp.forward(x)`` in the per-layer mode (``src/accelerate/vggt/direct.py:148-168``): the MLP runs
+    on the merged tokens -- a merged window passes through ``fc1 -> act -> fc2`` once instead of ``G`` times -- and the
+    result is split back to the dense layout.  ``x`` is ``[B*S, N, C]`` or ``[B, S*N, C]`` as the aggregator passes it;
+    the result has the same shape and dtype.  The two GEMMs stay the module's own (PyTorch); merge and split are this
+    library's kernels driven by the scene's :class:`~come_b200.token_merger.MergePlan`."""
+
+    def __init__(self, original_mlp: torch.nn.Module):
+        super().__init__()
+        self.mlp = original_mlp
+
+    def forward(self, x: torch.Tensor, plan: MergePlan) -> torch.Tensor:
+        input_shape = x.shape
+        C = x.shape[-1]
+        merged = plan.merge(x.reshape(plan.frames, plan.tokens_per_frame, C))
+        out = self.mlp(merged.unsqueeze(0)).squeeze(0)
+        return plan.split(out.contiguous()).view(*input_shape)
+
+    def forward_residual(self, x: torch.Tensor, plan: MergePlan, norm2: torch.nn.LayerNorm,
+                         ls2_gamma: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """The whole MLP branch of a block, ``x + ls2(mlp(norm2(x)))`` (``src/thirdparty/vggt/layers/block.py:74,91``), with
+        the dense tokens read once and written once: ``norm2`` inside the merge, LayerScale and the residual add inside
+        the unmerge."""
+        input_shape = x.shape
+        C = x.shape[-1]
+        dense = x.reshape(plan.frames, plan.tokens_per_frame, C)
+        merged = plan.merge_layernorm(dense, norm2)
+        out = self.mlp(merged.unsqueeze(0)).squeeze(0)
+        gamma = None if ls2_gamma is None else ls2_gamma.detach().to(device=x.device, dtype=x.dtype)
+        return plan.split_add(out.contiguous(), dense, gamma).view(*input_shape)

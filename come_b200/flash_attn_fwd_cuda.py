@@ -13,7 +13,7 @@ import torch
 from . import _lib
 from ._torch_util import dtype_code, ptr, stream_ptr
 
-__all__ = ["varlen_fwd", "varlen_fwd_w_perkey_bias", "varlen_fwd_rows"]
+__all__ = ["varlen_fwd", "varlen_fwd_w_perkey_bias", "varlen_fwd_rows", "cross_fwd", "combine"]
 
 BACKEND_AUTO, BACKEND_CUDA_CORE, BACKEND_TCGEN05 = 0, 1, 2
 _backend = BACKEND_AUTO
@@ -24,6 +24,22 @@ def set_backend(backend: int) -> int:
     global _backend
     old, _backend = _backend, int(backend)
     return old
+
+
+class cta_limit:
+    """``with cta_limit(n):`` the tensor-core attention launches of this thread inside the block use at most ``n`` CTAs
+    (``come_attn_set_cta_limit``), leaving the other SMs to a kernel that runs beside them; ``n <= 0``: no limit."""
+
+    def __init__(self, max_ctas: int):
+        self.max_ctas = max(int(max_ctas), 0)
+
+    def __enter__(self):
+        _lib.check(_lib.lib().come_attn_set_cta_limit(self.max_ctas))
+        return self
+
+    def __exit__(self, *exc):
+        _lib.check(_lib.lib().come_attn_set_cta_limit(0))
+        return False
 
 
 def _unsupported(what: str):
@@ -206,4 +222,57 @@ def varlen_fwd_rows(q_rows, k, v, cu_seqlens, max_seqlen, perkey_bias, softmax_s
             q_rows.stride(0), k.stride(0), v.stride(0), ptr(perkey_bias), ptr(cu_seqlens), cu_seqlens.numel() - 1,
             int(max_seqlen), ptr(max_seqlen_dev), float(softmax_scale), ptr(out), out.stride(0), ptr(lse), _backend,
             stream_ptr(q_rows.device)))
+    return [out, lse]
+
+
+def cross_fwd(q_rows, k, v, perkey_bias, softmax_scale, out_=None):
+    """Attention of ``q_rows [rows, H, D]`` to ONE set of keys / values ``k`` / ``v`` ``[kv_rows, H, D]`` that need not
+    contain those rows (no counterpart in the reference): the piece of row-sharded global attention that runs on the
+    key / value rows gathered from the other GPUs.  ``perkey_bias`` ``[kv_rows]`` or ``None``.
+    Returns ``[out [rows, H, D], softmax_lse [H, rows]]``."""
+    if q_rows.dtype not in (torch.float16, torch.bfloat16):
+        raise RuntimeError("FlashAttention only support fp16 and bf16 data type")
+    if k.dtype != q_rows.dtype or v.dtype != q_rows.dtype:
+        raise RuntimeError("query, key and value must have the same dtype")
+    rows, num_heads, head_size = q_rows.shape
+    kv_rows = k.shape[0]
+    if tuple(k.shape) != (kv_rows, num_heads, head_size) or tuple(v.shape) != (kv_rows, num_heads, head_size):
+        raise RuntimeError("k / v must have shape (kv_rows, num_heads, head_size)")
+    if kv_rows == 0 and rows > 0:
+        raise RuntimeError("cross attention needs at least one key")
+    for t in (q_rows, k, v):
+        if not t.is_cuda:
+            raise RuntimeError("q / k / v must be on CUDA")
+        if t.stride(-1) != 1 or t.stride(1) != head_size:
+            raise RuntimeError("q / k / v must have adjacent heads and a contiguous last dimension")
+    if perkey_bias is not None and (perkey_bias.dtype != q_rows.dtype or tuple(perkey_bias.shape) != (kv_rows,)
+                                    or not perkey_bias.is_contiguous()):
+        raise RuntimeError("perkey_bias must be a contiguous (kv_rows,) tensor of the q/k/v dtype")
+    out = out_ if out_ is not None else torch.empty((rows, num_heads, head_size), dtype=q_rows.dtype, device=q_rows.device)
+    lse = torch.empty((num_heads, rows), dtype=torch.float32, device=q_rows.device)
+    with torch.cuda.device(q_rows.device):
+        _lib.check(_lib.lib().come_attn_cross_fwd(
+            ptr(q_rows), ptr(k), ptr(v), dtype_code(q_rows.dtype), rows, kv_rows, num_heads, head_size, q_rows.stride(0),
+            k.stride(0), v.stride(0), ptr(perkey_bias), float(softmax_scale), ptr(out), out.stride(0), ptr(lse), _backend,
+            stream_ptr(q_rows.device)))
+    return [out, lse]
+
+
+def combine(out_a, lse_a, out_b, lse_b, out_=None, lse_out=None):
+    """Merge two attention results of the same query rows over disjoint key sets from their log-sum-exps
+    (``come_attn_combine``).  ``out_* [rows, H, D]`` contiguous, ``lse_* [H, rows]`` float32; ``out_`` / ``lse_out`` may be
+    one of the inputs.  Returns ``[out, lse]``."""
+    rows, num_heads, head_size = out_a.shape
+    if out_b.shape != out_a.shape or out_b.dtype != out_a.dtype or out_a.dtype not in (torch.float16, torch.bfloat16):
+        raise RuntimeError("combine needs two fp16 / bf16 results of the same shape")
+    for t in (lse_a, lse_b):
+        if tuple(t.shape) != (num_heads, rows) or t.dtype != torch.float32 or not t.is_contiguous():
+            raise RuntimeError("lse must be a contiguous float32 (num_heads, rows) tensor")
+    if not out_a.is_contiguous() or not out_b.is_contiguous():
+        raise RuntimeError("combine needs contiguous results")
+    out = out_ if out_ is not None else torch.empty_like(out_a)
+    lse = lse_out if lse_out is not None else torch.empty_like(lse_a)
+    with torch.cuda.device(out_a.device):
+        _lib.check(_lib.lib().come_attn_combine(ptr(out_a), ptr(lse_a), ptr(out_b), ptr(lse_b), dtype_code(out_a.dtype), rows,
+                                                num_heads, head_size, ptr(out), ptr(lse), stream_ptr(out_a.device)))
     return [out, lse]

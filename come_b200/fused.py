@@ -178,10 +178,14 @@ class ShardedFusedAggregator(FusedAggregator):
     """
 
     def __init__(self, aggregator: torch.nn.Module, frames_total: int, world: int, rank: int, group=None, gather=None,
-                 use_attn_bias_correction: bool = True, attn_dtype: str = "bf16", fuse_elementwise: bool = True):
+                 use_attn_bias_correction: bool = True, attn_dtype: str = "bf16", fuse_elementwise: bool = True,
+                 overlap: bool = False):
         """``gather(local, rows, rank)`` replaces the process group's all-gather (single-process tests); by default the
-        rows travel through :func:`come_b200.dist.gather_rows` over ``group``."""
+        rows travel through :func:`come_b200.dist.gather_rows` over ``group``.  ``overlap``: hide that exchange behind
+        attention to the local keys (:class:`come_b200.dist.GlobalExchange`)."""
         super().__init__(aggregator, use_attn_bias_correction, attn_dtype, fuse_elementwise)
+        self.overlap = bool(overlap)
+        self._exchange = None
         from .dist import shard_range
         self.frames_total, self.world, self.rank = int(frames_total), int(world), int(rank)
         self.group, self._gather = group, gather
@@ -205,7 +209,11 @@ class ShardedFusedAggregator(FusedAggregator):
         rows = rows_per_rank(global_plan.offset.tolist(), self.world)
         if rows[self.rank] != local_plan.total:
             raise ValueError("the local plan is not this rank's slice of the scene's plan")
-        exchange = GlobalExchange(rows, self.rank, global_plan.weight, self.group, self._gather)
+        exchange = GlobalExchange(rows, self.rank, global_plan.weight, self.group, self._gather, overlap=self.overlap)
+        keep = self._exchange
+        if keep is not None and keep.rows == exchange.rows and keep._side is not None:  # keep the side stream and the buffer
+            exchange._side, exchange._buf, exchange._cu_local = keep._side, keep._buf, keep._cu_local
+        self._exchange = exchange
         merged = local_plan.merge(tokens_local.reshape(S_local, N, C))
         pos = local_plan.positions()
         frame_offset = local_plan.offset

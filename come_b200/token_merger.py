@@ -8,7 +8,8 @@
 * :class:`MergePlan` -- everything of a merge that depends on the mask only, computed once per ``build_ctx``
   (one device->host read for the packed length) and reused by every merge / split / attention call.
 * :func:`select_windows` -- the tensor code of ``build_ctx`` (``co_me_2d.py:268-298``, ``co_me.py:54-73``).
-* :class:`CoMe2DTokenMerger` -- ``ITokenMerger`` implementation with the reference's method names.
+* :class:`CoMe2DTokenMerger`, :class:`CoMeTokenMerger` -- the 2-D and the 1-D ``ITokenMerger`` implementations with the
+  reference's method names.
 
 Argument validation raises ``ValueError`` with the reference's messages before anything is launched.
 """
@@ -25,7 +26,7 @@ from ._torch_util import dtype_code, ptr, require_cuda, stream_ptr
 
 __all__ = [
     "JaggedTokens", "MergePlan", "func_token_merge", "func_token_split", "func_token_merge_2d", "select_windows",
-    "CoMe2DTokenMerger",
+    "CoMe2DTokenMerger", "CoMeTokenMerger",
 ]
 
 
@@ -440,8 +441,17 @@ def select_windows(confidence: torch.Tensor, B: int, S: int, H: int, W: int, gro
 
 
 # ---------------------------------------------------------------------------------------------------------
-# ITokenMerger-style class
+# ITokenMerger-style classes
 # ---------------------------------------------------------------------------------------------------------
+def _nvtx_range(name: str):
+    """NVTX range on CUDA builds (the reference brackets its predictor the same way), a no-op context otherwise."""
+    import contextlib
+    try:
+        return torch.cuda.nvtx.range(name)
+    except Exception:  # noqa: BLE001  (no NVTX in this build of PyTorch)
+        return contextlib.nullcontext()
+
+
 class CoMe2DTokenMerger:
     """2-D Co-Me merger with the reference's ``ITokenMerger`` method names
     (``src/interface/token_merger.py:102-116``, ``src/accelerate/token_merger/co_me_2d.py:214-352``).
@@ -469,7 +479,8 @@ class CoMe2DTokenMerger:
                 raise ValueError(f"H ({H}) must be divisible by group_h ({self.group_h})")
             if W % self.group_w != 0:
                 raise ValueError(f"W ({W}) must be divisible by group_w ({self.group_w})")
-        confidence = self.predictor(feature.permute(0, 1, 3, 4, 2).bfloat16(), BPHWC=(B, S, H, W, Cc)).squeeze(-1)
+        with _nvtx_range("confidence_predictor"):  # the range name of the reference (co_me_2d.py:264)
+            confidence = self.predictor(feature.permute(0, 1, 3, 4, 2).bfloat16(), BPHWC=(B, S, H, W, Cc)).squeeze(-1)
         mask = select_windows(confidence, B, S, H, W, self.group_h, self.group_w, self.threshold, self.conf_mode, "batch")
         plan = MergePlan(mask, _lib.Layout.two_d(self.start_idx, H, W, self.group_h, self.group_w))
         return (mask, (B, S, Cc, H, W), plan)
@@ -496,3 +507,55 @@ class CoMe2DTokenMerger:
         full = torch.zeros((B * S, H, W), dtype=torch.bool, device=mask.device)
         full[:, : Mh * self.group_h, : Mw * self.group_w] = m.reshape(B * S, Mh * self.group_h, Mw * self.group_w)
         return full.reshape(B, S, H, W)
+
+
+class CoMeTokenMerger:
+    """1-D Co-Me merger (``src/accelerate/token_merger/co_me.py:21-105``): groups of ``group_size`` CONSECUTIVE patch
+    tokens behind ``start_idx`` special tokens, the ranking threshold taken per frame.  Same ``ITokenMerger`` method
+    names and context layout as the reference: ``build_ctx`` returns ``(mask, (B, S, C, H, W), plan)`` -- the first two
+    entries are the reference's context, the third the cached :class:`MergePlan`.
+
+    ``predictor(feature_bshwc_bf16, BPHWC=(B, S, H, W, C)) -> confidence [B, S*H*W, 1]``.
+    """
+
+    def __init__(self, start_idx: int, group_size: int, threshold: float, predictor: Callable[..., torch.Tensor],
+                 conf_mode: str = "pairwise-rank"):
+        self.start_idx = start_idx
+        self.group_size = group_size
+        self.threshold = threshold
+        self.predictor = predictor
+        self.conf_mode = conf_mode
+
+    def build_ctx(self, feature: torch.Tensor) -> Any:
+        B, S, Cc, H, W = feature.shape
+        if (H * W) % self.group_size != 0:
+            raise ValueError(f"H * W ({H * W}) must be divisible by group_size ({self.group_size})")
+        with _nvtx_range("confidence_predictor"):
+            confidence = self.predictor(feature.permute(0, 1, 3, 4, 2).bfloat16(), BPHWC=(B, S, H, W, Cc)).squeeze(-1)
+        # consecutive groups of a frame = 1 x group_size windows of a (H*W / group_size) x group_size grid
+        M = (H * W) // self.group_size
+        mask = select_windows(confidence, B, S, M, self.group_size, 1, self.group_size, self.threshold, self.conf_mode, "frame")
+        plan = MergePlan(mask, _lib.Layout.one_d(self.start_idx, self.group_size, M))
+        return (mask, (B, S, Cc, H, W), plan)
+
+    def _plan_for(self, ctx, start_index: Optional[int]) -> MergePlan:
+        mask, _shape, plan = ctx
+        if start_index is None or start_index == self.start_idx:
+            return plan
+        return MergePlan(mask, _lib.Layout.one_d(start_index, self.group_size, mask.shape[1]))
+
+    def merge(self, ctx, tokens: torch.Tensor, stub: Any = None, *, start_index: Optional[int] = None):
+        """``tokens [B, S, N, C]`` -> ``(JaggedTokens, (rev_id, tokens.shape))``; ``stub`` is accepted and ignored, as in
+        the reference (``co_me.py:88-93``)."""
+        plan = self._plan_for(ctx, start_index)
+        return plan.jagged(tokens.flatten(0, 1)), (plan.rev_id, tokens.shape)
+
+    def split(self, ctx, stub: Any, tokens: JaggedTokens) -> torch.Tensor:
+        rev_id, shape_bsnc = stub
+        B, S, N, Cc = shape_bsnc
+        return func_token_split(tokens, rev_id, shape_bsnc).view(B, S, N, Cc)
+
+    def build_infer_mask(self, ctx) -> torch.Tensor:
+        """Per-patch bool mask ``[B, S, H, W]`` of the merged groups (``co_me.py:101-105``)."""
+        mask, (B, S, _, H, W), _plan = ctx
+        return mask.unsqueeze(-1).expand(-1, -1, self.group_size).reshape(B, S, H, W)

@@ -268,6 +268,39 @@ int come_attn_varlen_fwd_rows(const void *q_dev, const void *k_dev, const void *
                               float *lse_dev, int backend, void *stream);
 
 /*
+ * Attention of q_rows query rows to ONE set of kv_rows keys / values that need not contain them:
+ *   out[i, h] = softmax(q[i, h] k[:, h]^T * softmax_scale + bias[None, :]) v[:, h],   lse[h, i] likewise.
+ * No counterpart in the reference (single GPU only).  It is the second half of global attention sharded over GPUs with
+ * the exchange hidden behind compute: a GPU first attends its rows to its own keys (come_attn_varlen_fwd) while the other
+ * GPUs' keys / values are still in flight, then attends the same rows to the gathered remote keys with this call, and
+ * come_attn_combine merges the two results.  Layouts as in come_attn_varlen_fwd; bias_dev [kv_rows] or NULL.
+ */
+int come_attn_cross_fwd(const void *q_dev, const void *k_dev, const void *v_dev, int dtype, int64_t q_rows, int64_t kv_rows,
+                        int num_heads, int head_dim, int64_t q_row_stride, int64_t k_row_stride, int64_t v_row_stride,
+                        const void *bias_dev, float softmax_scale, void *out_dev, int64_t out_row_stride, float *lse_dev,
+                        int backend, void *stream);
+
+/*
+ * The tensor-core attention kernel is persistent: one CTA per SM walks the work list, and a CTA takes a whole SM.  A
+ * caller that runs a communication kernel next to it (the key / value all-gather of the next step on another stream)
+ * leaves that kernel some SMs with this call: the following attention launches OF THE CALLING HOST THREAD use at most
+ * max_ctas CTAs (0 = one per SM again).  Without it the attention CTAs that do not fit start only when the other kernel
+ * has finished, and the statically divided work list ends late.  No counterpart in the reference.
+ */
+int come_attn_set_cta_limit(int max_ctas);
+
+/*
+ * Exact merge of two attention results of the same query rows over DISJOINT key sets, from their log-sum-exps:
+ *   w_x = exp(lse_x - max(lse_a, lse_b));  out = (w_a out_a + w_b out_b) / (w_a + w_b);  lse_out = max + log(w_a + w_b)
+ * out_* [rows, num_heads, head_dim] contiguous in dtype (COME_F16 / COME_BF16), lse_* [num_heads, rows] float32;
+ * out_dev may alias out_a_dev or out_b_dev, lse_out_dev (may be NULL) may alias lse_a_dev or lse_b_dev.
+ * The inputs were rounded to dtype by the two attention launches, so the result differs from a single launch over all
+ * keys by that rounding (about 2^-9 relative for bfloat16), not bit for bit.  No counterpart in the reference.
+ */
+int come_attn_combine(const void *out_a_dev, const float *lse_a_dev, const void *out_b_dev, const float *lse_b_dev,
+                      int dtype, int64_t rows, int num_heads, int head_dim, void *out_dev, float *lse_out_dev, void *stream);
+
+/*
  * Pre-attention preparation of the packed qkv tensor [total, 3, num_heads, head_dim], in place, one pass:
  *   q, k <- LayerNorm over head_dim (affine gamma / beta; skipped when the four pointers are NULL)
  *   q, k <- 2-D rotary position embedding with integer positions pos[total, 2] = (y, x): the first head_dim/2

@@ -374,6 +374,18 @@ def attention_bias(q, k, v, bias, cu_seqlens, scale):
     return out, lse
 
 
+def attention_combine(out_a, lse_a, out_b, lse_b):
+    """Merge of two attention results of the same query rows over disjoint key sets: with ``w_x = exp(lse_x - m)``,
+    ``m = max(lse_a, lse_b)``: ``out = (w_a out_a + w_b out_b) / (w_a + w_b)``, ``lse = m + log(w_a + w_b)``.
+    ``out_* [rows, H, D]``, ``lse_* [H, rows]``; float32.  (Identity of the softmax over a union of key sets; the
+    reference has no such step, it never splits the keys.)"""
+    la, lb = np.asarray(lse_a, np.float32).T[:, :, None], np.asarray(lse_b, np.float32).T[:, :, None]
+    m = np.maximum(la, lb)
+    wa, wb = np.exp(la - m, dtype=np.float32), np.exp(lb - m, dtype=np.float32)
+    out = (wa * np.asarray(out_a, np.float32) + wb * np.asarray(out_b, np.float32)) / (wa + wb)
+    return out.astype(np.float32), (m + np.log(wa + wb))[:, :, 0].T.astype(np.float32)
+
+
 # --------------------------------------------------------------------------------------------------------
 # pre-attention preparation of the packed qkv tensor: q/k LayerNorm over the head dimension, 2-D rotary
 # position embedding, per-key bias

@@ -379,3 +379,52 @@ def test_very_long_segment(backend):
         outs.append(api.flash_attn_varlen_qkvpacked_func_w_perkey_bias(qkv, cu, P, perkey_bias=bias, softmax_scale=D ** -0.5).float())
     assert (outs[0] - outs[1]).abs().max().item() <= 2e-2
     _check_status()
+
+
+@pytest.mark.parametrize("which", ["cuda-core", "tcgen05"])
+@pytest.mark.parametrize("rows,kv_rows", [(300, 1000), (1000, 300), (129, 64), (5, 1)])
+def test_cross_attention_and_combine_match_full_attention(backend, which, rows, kv_rows):
+    """Keys split into the query rows' own block and a block that does not contain them: attention to the own block
+    (plain self-attention), attention to the other block (``cross_fwd``, more or fewer keys than query rows) and the merge
+    of the two from their log-sum-exps must reproduce attention over all keys -- against the fp32 oracle, bar 2e-2 -- and
+    the merge kernel must agree with the oracle's merge of the same two partial results."""
+    from come_b200 import flash_attn_fwd_cuda as fa
+    from oracle import come_oracle as orc
+    backend(fa.BACKEND_TCGEN05 if which == "tcgen05" else fa.BACKEND_CUDA_CORE)
+    H, D = 3, 64
+    rng = np.random.default_rng(rows * 7 + kv_rows)
+    P = rows + kv_rows
+    qkv = gi.round_kind(rng.standard_normal((P, 3, H, D), dtype=np.float32), "bf16")
+    bias = gi.round_kind(np.log(np.where(rng.random(P) < 0.2, 9.0, 1.0)).astype(np.float32), "bf16")
+    t, b = to_dev(qkv, "bf16"), to_dev(bias, "bf16")
+    scale = D ** -0.5
+    q_own = t[:rows, 0].contiguous()
+    cu_own = torch.tensor([0, rows], dtype=torch.int32, device="cuda")
+    o_own, l_own = fa.varlen_fwd_rows(q_own, t[:rows, 1], t[:rows, 2], cu_own, rows, b[:rows].contiguous(), scale, 0)
+    o_far, l_far = fa.cross_fwd(q_own, t[rows:, 1], t[rows:, 2], b[rows:].contiguous(), scale)
+    assert tuple(o_far.shape) == (rows, H, D) and tuple(l_far.shape) == (H, rows)
+    # the other block alone, against the oracle: queries = the first rows, keys = the second block
+    want_far = _oracle_cross(qkv[:rows, 0], qkv[rows:, 1], qkv[rows:, 2], bias[rows:], scale)
+    assert np.abs(to_np(o_far) - want_far[0]).max() <= 2e-2
+    np.testing.assert_allclose(to_np(l_far), want_far[1], atol=2e-3, rtol=1e-3)
+    out, lse = fa.combine(o_own, l_own, o_far, l_far)
+    want, want_lse = clib.attention_bias(qkv, bias, np.array([0, P], np.int32), scale, 0, rows)
+    assert np.abs(to_np(out) - want[:rows]).max() <= 2e-2
+    np.testing.assert_allclose(to_np(lse), want_lse[:, :rows], atol=2e-3, rtol=1e-3)
+    ref_out, ref_lse = orc.attention_combine(to_np(o_own), to_np(l_own), to_np(o_far), to_np(l_far))
+    np.testing.assert_allclose(to_np(out), ref_out, atol=0, rtol=2 ** -7)  # one rounding to bfloat16
+    np.testing.assert_allclose(to_np(lse), ref_lse, atol=1e-5, rtol=1e-6)
+    # in place: the merged result may overwrite the first partial result
+    fa.combine(o_own, l_own, o_far, l_far, out_=o_own, lse_out=l_own)
+    assert torch.equal(o_own, out) and torch.equal(l_own, lse)
+    _check_status()
+
+
+def _oracle_cross(q, k, v, bias, scale):
+    """fp32 attention of q [rows, H, D] to k / v [kv, H, D] with a per-key bias (numpy, small cases)."""
+    s = np.einsum("ihd,jhd->hij", q.astype(np.float64), k.astype(np.float64)) * scale + bias.astype(np.float64)[None, None, :]
+    m = s.max(axis=-1, keepdims=True)
+    p = np.exp(s - m)
+    l = p.sum(axis=-1, keepdims=True)
+    out = np.einsum("hij,jhd->ihd", p / l, v.astype(np.float64))
+    return out.astype(np.float32), (m + np.log(l))[:, :, 0].astype(np.float32)

@@ -40,6 +40,13 @@ def _worker(rank, world, port, rows, q):
         got = gather_rows(local, rows)
         want = torch.cat([torch.arange(rows[r] * 6, dtype=torch.float32).reshape(rows[r], 2, 3) + 1000 * r for r in range(world)])
         ok = torch.equal(got, want)
+        # remote-first order: the other ranks' blocks (rank + 1, ..., rank - 1) in front, the local block last
+        from come_b200.dist import block_order
+        order = block_order(world, rank, True)
+        got_rf = gather_rows(local, rows, remote_first=True)
+        want_rf = torch.cat([torch.arange(rows[r] * 6, dtype=torch.float32).reshape(rows[r], 2, 3) + 1000 * r for r in order])
+        ok = ok and order[-1] == rank and sorted(order) == list(range(world)) and torch.equal(got_rf, want_rf)
+        ok = ok and torch.equal(got_rf[sum(rows) - rows[rank]:], local)
         # an inconsistent row table is reported on the host before any collective is started
         try:
             gather_rows(local, list(rows) + [1])
@@ -112,3 +119,22 @@ def test_global_exchange_checks_and_custom_gather():
     single = GlobalExchange([7], 0, w)
     t = torch.zeros(7, 2)
     assert single.gather(t) is t           # one rank: nothing to exchange
+
+
+def test_block_order():
+    from come_b200.dist import block_order
+    assert block_order(4, 1, False) == [0, 1, 2, 3]
+    assert block_order(4, 1, True) == [2, 3, 0, 1]
+    assert block_order(1, 0, True) == [0]
+
+
+def test_exchange_bias_split_follows_the_remote_first_order():
+    """The per-key bias handed to the attention over the gathered remote rows is laid out like those rows."""
+    from come_b200.dist import GlobalExchange
+    rows = [3, 2, 4]
+    weight = torch.tensor([1., 9, 1, 9, 9, 1, 1, 9, 1])
+    ex = GlobalExchange(rows, 1, weight, overlap=True)
+    local, remote = ex.bias_local_remote(torch.float32)
+    assert torch.equal(local, weight[3:5].log())
+    assert torch.equal(remote, torch.cat([weight[5:9], weight[0:3]]).log())  # rank 2's rows, then rank 0's
+    assert ex.overlap and not GlobalExchange([9], 0, weight, overlap=True).overlap

@@ -276,11 +276,14 @@ def _sharded_case(rng, frames, side=7, C=128, heads=2, depth=2, start=5):
     return core, tokens, mask, (start, side, side, 3, 3)
 
 
+@pytest.mark.parametrize("overlap", [False, True])
 @pytest.mark.parametrize("world", [2, 3])
-def test_sharded_aggregator_emulated_ranks(world):
+def test_sharded_aggregator_emulated_ranks(world, overlap):
     """Ranks emulated by host threads on one GPU: each runs ShardedFusedAggregator on its frames, and the K/V gather is a
     rendezvous between the threads (nothing on the device waits for anything).  Every rank's retained layers must equal
-    its frames of the single-GPU result up to the rounding of differently tiled GEMMs."""
+    its frames of the single-GPU result up to the rounding of differently tiled GEMMs.  ``overlap``: the exchange runs
+    on a side stream while the rank attends to its own keys, the other ranks' keys are attended afterwards and the two
+    results are merged."""
     import threading
     from come_b200 import _lib
     from come_b200.fused import FusedAggregator, ShardedFusedAggregator
@@ -297,6 +300,7 @@ def test_sharded_aggregator_emulated_ranks(world):
     results, errors = [None] * world, []
 
     def gather(local, rows, rank):  # every rank deposits its rows, waits for the others, reads all
+        torch.cuda.current_stream().synchronize()  # the ranks' streams are not ordered among themselves: hand over finished rows
         slots[rank] = local
         barrier.wait(timeout=120)
         out = torch.cat(slots, dim=0)
@@ -306,7 +310,7 @@ def test_sharded_aggregator_emulated_ranks(world):
     def run(rank):
         try:
             torch.cuda.set_device(0)
-            model = ShardedFusedAggregator(core, frames, world, rank, gather=gather)
+            model = ShardedFusedAggregator(core, frames, world, rank, gather=gather, overlap=overlap)
             gp, lp = model.build_plans(mask, layout)
             with torch.no_grad():
                 out, _ = model(tokens[:, model.f_lo:model.f_hi], gp, lp)
@@ -331,7 +335,7 @@ def test_sharded_aggregator_emulated_ranks(world):
     assert covered == frames
 
 
-def _sharded_worker(rank, world, port, q_out):
+def _sharded_worker(rank, world, port, q_out, overlap=False):
     import os
     import torch.distributed as dist
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
@@ -344,7 +348,7 @@ def _sharded_worker(rank, world, port, q_out):
         rng = np.random.default_rng(17)
         core, tokens, mask, lay = _sharded_case(rng, 5)
         core = core.to(dev)
-        model = ShardedFusedAggregator(core, 5, world, rank)
+        model = ShardedFusedAggregator(core, 5, world, rank, overlap=overlap)
         gp, lp = model.build_plans(mask.to(dev), _lib.Layout.two_d(*lay))
         with torch.no_grad():
             out, _ = model(tokens[:, model.f_lo:model.f_hi].to(dev), gp, lp)
@@ -355,8 +359,10 @@ def _sharded_worker(rank, world, port, q_out):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_sharded_aggregator_two_gpus():
-    """Two processes, one GPU each, NCCL all-gather of the K/V rows: against the single-GPU result."""
+@pytest.mark.parametrize("overlap", [False, True])
+def test_sharded_aggregator_two_gpus(overlap):
+    """Two processes, one GPU each, NCCL all-gather of the K/V rows (in line, or on a side stream behind attention to
+    the local keys): against the single-GPU result."""
     import socket
     import torch.multiprocessing as mp
     from come_b200 import _lib
@@ -367,7 +373,7 @@ def test_sharded_aggregator_two_gpus():
         port = s.getsockname()[1]
     ctx = mp.get_context("spawn")
     q_out = ctx.Queue()
-    procs = [ctx.Process(target=_sharded_worker, args=(r, 2, port, q_out)) for r in range(2)]
+    procs = [ctx.Process(target=_sharded_worker, args=(r, 2, port, q_out, overlap)) for r in range(2)]
     for p in procs:
         p.start()
     results = [q_out.get(timeout=300) for _ in range(2)]

@@ -292,3 +292,23 @@ def test_suffix_known_answers_and_errors():
         orc.jagged_split_suffix(tok, w, off, 4)       # more than the total
     with pytest.raises(ValueError):  # 4 <= 6 in total, but the second segment holds one token
         orc.jagged_split_suffix(np.zeros((6, 1), np.float32), np.ones(6, np.float32), [0, 5, 6], 2)
+
+
+def test_attention_combine_is_attention_over_the_union_of_keys():
+    """The oracle's merge of two partial attention results reproduces attention over all keys (float32)."""
+    rng = np.random.default_rng(8)
+    P, rows, H, D = 90, 40, 2, 16
+    qkv = rng.standard_normal((P, 3, H, D), dtype=np.float32)
+    bias = np.log(np.where(rng.random(P) < 0.3, 9.0, 1.0)).astype(np.float32)
+    scale = D ** -0.5
+    full, full_lse = orc.attention_bias(qkv[:, 0], qkv[:, 1], qkv[:, 2], bias, np.array([0, P], np.int32), scale)
+    parts = []
+    for lo, hi in ((0, rows), (rows, P)):  # the first `rows` queries against each block of keys
+        s = np.einsum("ihd,jhd->hij", qkv[:rows, 0], qkv[lo:hi, 1]) * scale + bias[None, None, lo:hi]
+        m = s.max(-1, keepdims=True)
+        p = np.exp(s - m)
+        l = p.sum(-1, keepdims=True)
+        parts.append((np.einsum("hij,jhd->ihd", p / l, qkv[lo:hi, 2]).astype(np.float32), (m + np.log(l))[:, :, 0].astype(np.float32)))
+    out, lse = orc.attention_combine(parts[0][0], parts[0][1], parts[1][0], parts[1][1])
+    np.testing.assert_allclose(out, full[:rows], atol=2e-6, rtol=1e-5)
+    np.testing.assert_allclose(lse, full_lse[:, :rows], atol=2e-6, rtol=1e-5)

@@ -24,7 +24,7 @@ def _scene(frames, C, H, D, device):
     return x, conf, q, kv
 
 
-def _worker(rank, world, port, frames, q_out):
+def _worker(rank, world, port, frames, q_out, overlap):
     import torch.distributed as dist
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
@@ -34,7 +34,7 @@ def _worker(rank, world, port, frames, q_out):
         from come_b200.chain import ShardedOpChain
         C, H, D = 64 * 4, 4, 64
         x, conf, q, kv = _scene(frames, C, H, D, dev)
-        chain = ShardedOpChain(frames, num_heads=H, head_dim=D, layer_kinds=["frame", "global"])
+        chain = ShardedOpChain(frames, num_heads=H, head_dim=D, layer_kinds=["frame", "global"], overlap=overlap)
         gp, lp = chain.build_plans(conf)
         r0, r1 = chain.row_begin, chain.row_begin + lp.total
         outs = [chain.layer(gp, lp, x[chain.f_lo:chain.f_hi], q[r0:r1].contiguous(), kv[r0:r1].contiguous(), kind).cpu()
@@ -46,14 +46,17 @@ def _worker(rank, world, port, frames, q_out):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_sharded_chain_matches_single_gpu():
+@pytest.mark.parametrize("overlap", [False, True])
+def test_sharded_chain_matches_single_gpu(overlap):
+    """In line, the exchange changes nothing: bit-identical frames.  Overlapped (local keys first, the gathered keys
+    afterwards, merged from the log-sum-exps) the global layer differs by the rounding of the two partial outputs."""
     import torch.multiprocessing as mp
     from come_b200.chain import ShardedOpChain
     frames, C, H, D = 5, 256, 4, 64
     ctx = mp.get_context("spawn")
     q_out = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, frames, q_out)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, frames, q_out, overlap)) for r in range(2)]
     for p in procs:
         p.start()
     results = [q_out.get(timeout=300) for _ in range(2)]
@@ -67,5 +70,6 @@ def test_sharded_chain_matches_single_gpu():
     P = lp.total
     want = [single.layer(gp, lp, x, q[:P].contiguous(), kv[:P].contiguous(), kind).cpu() for kind in ("frame", "global")]
     for rank, f_lo, f_hi, outs in results:
-        for got, ref in zip(outs, want):
-            torch.testing.assert_close(got, ref[f_lo:f_hi], atol=0, rtol=0)
+        for kind, got, ref in zip(("frame", "global"), outs, want):
+            tol = 2e-2 if (overlap and kind == "global") else 0.0
+            torch.testing.assert_close(got, ref[f_lo:f_hi], atol=tol, rtol=0)
