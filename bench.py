@@ -105,7 +105,9 @@ class ClockSampler:
 
 # ---- CPU restatement of the reference path (oracle) ---------------------------------------------------------
 class CpuSceneSample:
-    """A bounded sample of one scene of the operator chain on the host cores with the C oracle (all OpenMP threads).
+    """A bounded sample of one scene of the operator chain on the host cores (all threads): selection, merge and unmerge
+    with the C oracle, attention with the PyTorch-operator restatement of the reference's float32 biased softmax (the
+    reference's fallback path is PyTorch; its matrix products run on PyTorch's BLAS).
 
     Every ``run()`` times, in float32 (the dtype of the reference's CPU path): the selection, a full merge and a full
     unmerge of all frames, the frame attention of ``frame_sample`` whole frames with all heads, and the global attention
@@ -114,12 +116,14 @@ class CpuSceneSample:
     therefore an extrapolation (``extrapolated`` in the report) and ``sample_s`` says how many seconds were timed."""
 
     def __init__(self, frames, attn_rows=512, frame_sample=8):
-        from oracle import clib
-        self.clib, self.frames, self.attn_rows = clib, frames, attn_rows
+        from oracle import clib, torch_path
+        self.clib, self.attn, self.frames, self.attn_rows = clib, torch_path, frames, attn_rows
         self.frame_sample = min(frames, frame_sample)
         # all the host threads this process may use: a multi-process launcher exports OMP_NUM_THREADS=1 for its workers,
         # which would time the CPU path on one core
-        clib.set_num_threads(len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1))
+        threads = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+        clib.set_num_threads(threads)
+        torch_path.set_num_threads(threads)
         rng = np.random.default_rng(0)
         self.tokens = rng.standard_normal((frames, N_TOK, CH), dtype=np.float32)
         self.conf = rng.random((1, frames * GRID * GRID), dtype=np.float32)
@@ -147,11 +151,11 @@ class CpuSceneSample:
         fs = self.frame_sample
         cu_f = off[: fs + 1].astype(np.int32)
         t0 = time.perf_counter()
-        clib.attention_bias(self.qkv_frames[: cu_f[-1]], bias[: cu_f[-1]], cu_f, HDIM ** -0.5)
+        self.attn.attention_bias(self.qkv_frames[: cu_f[-1]], bias[: cu_f[-1]], cu_f, HDIM ** -0.5)
         t_frame = (time.perf_counter() - t0) * (frames / fs)
         rows = min(self.attn_rows, P)
         t0 = time.perf_counter()
-        clib.attention_bias(self.qkv_1head[:P], bias, np.array([0, P], np.int32), HDIM ** -0.5, 0, rows)
+        self.attn.attention_bias(self.qkv_1head[:P], bias, np.array([0, P], np.int32), HDIM ** -0.5, 0, rows)
         t_global = (time.perf_counter() - t0) * HEADS * (P / rows)
         sample_s = time.perf_counter() - t_all
         n_f = sum(1 for k in LAYERS if k == "frame")
@@ -177,10 +181,10 @@ def cpu_baseline_report(frames, steps, warmup=0):
         if i >= warmup:
             vals.append(v)
             secs.append(s_)
-    return {"value": statistics.median(vals), "unit": UNIT, "cores": sample.clib.num_threads(), "kind": "port",
+    return {"value": statistics.median(vals), "unit": UNIT, "cores": sample.attn.num_threads(), "kind": "port",
             "extrapolated": True, "sample_s": sum(secs), "samples": len(vals), "sample": sample.describe(), "detail": detail,
-            "note": "C/OpenMP restatement of the reference's PyTorch fallback (float32); a reported baseline, extrapolated "
-                    "from the timed sample, not a measurement of the whole scene"}
+            "note": "restatement of the reference's PyTorch fallback (float32): merge / unmerge in C with OpenMP, attention with "
+                    "PyTorch CPU operators; a reported baseline, extrapolated from the timed sample, not a measurement of the whole scene"}
 
 
 def run_reference(args):
@@ -203,9 +207,16 @@ def run_reference(args):
 
 
 # ---- GPU arm ---------------------------------------------------------------------------------------------------
+COMM_SMS = 16  # SMs left to the all-gather kernel while attention to the local keys runs beside it
+
+
 def init_ranks():
     import torch
     import torch.distributed as dist
+    # An all-gather that runs beside the persistent attention kernel completes only when ALL its CTAs have run: keep their
+    # number within the SMs the attention launch leaves free (GlobalExchange.comm_sms), or the last ones wait for the
+    # attention kernel to end and nothing overlaps.
+    os.environ.setdefault("NCCL_MAX_CTAS", str(COMM_SMS))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -271,7 +282,8 @@ def run_frames(args):
     frames = FRAMES_BY_WORKLOAD[args.workload]
     pk = peaks()
     check = sharded_check(torch, dist, world, rank, dev) if world > 1 else None
-    chain = ShardedOpChain(frames, None, START, GRID, GRID, WIN, WIN, 0.5, HEADS, HDIM, LAYERS, overlap=(world > 1 and not args.no_overlap))
+    overlap = world > 1 and (args.overlap == "on" or (args.overlap == "auto" and world >= 4))
+    chain = ShardedOpChain(frames, None, START, GRID, GRID, WIN, WIN, 0.5, HEADS, HDIM, LAYERS, overlap=overlap)
     g = torch.Generator(device="cpu").manual_seed(4321)
     conf_host = torch.rand((1, frames * GRID * GRID), generator=g).bfloat16().pin_memory()  # replicated on every rank
     conf = conf_host.to(dev)
@@ -315,6 +327,7 @@ def run_frames(args):
     if rank == 0:
         sampler.start()
         time.sleep(0.3)
+    barrier()  # the other ranks wait for rank 0's sampler here, not inside the first all-gather of the timed region
     # ---- timed region 0 (-> `value`): inputs resident in HBM --------------------------------------------------------
     s, e = ev(), ev()
     s.record()
@@ -391,11 +404,12 @@ def run_frames(args):
             "warmup": max(args.warmup, 3), "ms_per_step": per_scene, "higher_is_better": False, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic (seeded)",
             "config": {"workload": workload_name(frames), "merged_tokens": P, "frames_per_s": frames / per_scene * 1e3,
-                       "parallelism": (f"frames sharded over {world} GPU(s); frame layers local; a global layer all-gathers "
+                       "parallelism": ("one GPU: the whole scene, no exchange" if world == 1 else
+                                       f"frames sharded over {world} GPUs; frame layers local; a global layer all-gathers "
                                        f"{kv_bytes / 1e6:.0f} MB of merged K/V over NCCL"
                                        + (" on a side stream while the local query rows attend to the local keys, then attends "
                                           "them to the gathered rows and merges the two results from their log-sum-exps"
-                                          if chain.overlap and world > 1 else " in line")),
+                                          if chain.overlap else " in line, then attends the local query rows to all keys")),
                        "l2": "inputs larger than L2 (the merged K/V of one layer alone is 327 MB)",
                        "launch": "kernel by kernel from Python (a step is hundreds of ms of device time)"},
             "roofline": {"kernel": f"attn_fwd_sm100_kernel ({n_f} frame + {n_g} global layers per scene)", "bound": "tensor",
@@ -433,6 +447,9 @@ def run_frames(args):
             agg = aggregator_measure(8, 24, 5, report=False)
             agg.pop("only")
             line["aggregator_model"] = agg
+            whole = model_measure(8, 5, report=False)
+            whole.pop("only")
+            line["model"] = whole
         if world == 1 and not args.no_cpu:
             line["cpu_baseline"] = cpu_baseline_report(frames, 3)
         print(json.dumps(line))
@@ -996,6 +1013,62 @@ def aggregator_measure(S, depth, iters, arms_wanted="", report=True, B=1, ragged
     }
 
 
+def model_measure(S, iters, arms_wanted="", report=True):
+    """The whole accelerated model in the form of the reference's benchmark (``src/bench.py:13-46``): images -> patch
+    encoder (ViT-L/14-reg shape, 24 blocks; the merge context is built after block 14 and blocks 15..23 run on the merged
+    tokens, ``src/accelerate/vggt/fused.py:40-94``) -> aggregator (24 + 24 blocks), seeded random bf16 weights, against
+    the same weights with nothing merged.  The prediction heads are outside.  GEMMs and the patch convolution are
+    PyTorch's; everything else on the tokens is this library's kernels."""
+    import torch
+    from come_b200 import _lib
+    from come_b200.fused import FusedModel
+    from come_b200.timer import Timer
+    from come_b200.vggt_arch import AggregatorCore, ConfidenceHead, PatchEncoderCore
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    enc = PatchEncoderCore().to(dev).bfloat16()
+    core = AggregatorCore(depth=24).to(dev).bfloat16()
+    head = ConfidenceHead().to(dev).bfloat16()
+    model = FusedModel(enc, core, head, encoder_layer=14, threshold=0.5).eval()
+    g = torch.Generator(device=dev).manual_seed(0)
+    scenes = [torch.rand((1, S, 3, 518, 518), device=dev, generator=g).bfloat16() for _ in range(iters)]
+    arms = {"Reference Model": model.forward_unmerged, "Accelerated Model": model}
+    if arms_wanted:
+        wanted = {"reference": "Reference Model", "accelerated": "Accelerated Model"}
+        arms = {wanted[a]: arms[wanted[a]] for a in arms_wanted.split(",") if a in wanted}
+    Timer.reset()
+    packed = []
+    with torch.no_grad():
+        for name, fn in arms.items():
+            Timer.activate(False)
+            for t in scenes[:2]:
+                fn(t)
+            torch.cuda.synchronize()
+            Timer.activate()
+            for i, t in enumerate(scenes):
+                with torch.cuda.nvtx.range(f"{'Ref' if name.startswith('Ref') else 'Acc'}:sample_{i}"), \
+                        torch.cuda.nvtx.range("inference"), Timer.range(name):
+                    fn(t)
+                if name == "Accelerated Model":
+                    packed.append(model.last_plan.total)
+            torch.cuda.synchronize()
+    Timer.activate(False)
+    entries = {e.name: e for e in Timer.results()}
+    if report:
+        print(Timer.report(), file=sys.stderr)
+    Timer.reset()
+    assert _lib.device_status(clear=False) == 0
+    return {
+        "only": "model", "frames": S, "dtype": "bf16", "calls": len(scenes), "encoder": "ViT-L/14-reg shape, 24 blocks, merge context after block 14",
+        "aggregator": "24 frame + 24 global blocks", "heads": "not included", "packed_tokens_mean": float(np.mean(packed)) if packed else None,
+        "dense_tokens": S * N_TOK,
+        "ms_per_scene": {k: round(v.P50, 3) for k, v in entries.items()},
+        "speedup_vs_unmerged": ({k: round(entries["Reference Model"].P50 / v.P50, 3) for k, v in entries.items()}
+                                if "Reference Model" in entries else None),
+        "timer": "CUDA events around each scene (src/utility/timer.py form), median over the scenes; launched from Python",
+    }
+
+
 def run_aggregator(args):
     S = 8 if args.frames == 100 else args.frames  # 100 is the flag's default, meant for the merge kernels
     print(json.dumps(aggregator_measure(S, args.depth, args.iters, args.arms, B=args.scenes, ragged=args.ragged)))
@@ -1003,8 +1076,9 @@ def run_aggregator(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--only", choices=["attn", "merge", "unmerge", "merge_ln", "unmerge_res", "prepare", "residual_ln", "direct", "aggregator"],
-                    help="run one kernel family on one size and exit; aggregator = the end-to-end model driver")
+    ap.add_argument("--only", choices=["attn", "merge", "unmerge", "merge_ln", "unmerge_res", "prepare", "residual_ln", "direct", "aggregator", "model"],
+                    help="run one kernel family on one size and exit; aggregator = the alternating-attention stack, merged against "
+                         "unmerged; model = the same comparison from the images on (patch encoder with its merge after block 14 + aggregator)")
     ap.add_argument("--depth", type=int, default=24, help="--only aggregator: frame/global block pairs")
     ap.add_argument("--scenes", type=int, default=1, help="--only aggregator: independent scenes per call")
     ap.add_argument("--ragged", action="store_true", help="--only aggregator: per-frame merge ratios ~U(0.25, 0.75)")
@@ -1024,12 +1098,17 @@ def main():
                          "all-gathered K/V; frames8: the same for an 8-frame scene (quick runs); batch256x4: 256 independent "
                          "4-frame scenes with per-frame merge ratios ~U(0.25,0.75), sharded by scene, reported as scenes/s; model100: the "
                          "100-frame scene through the whole alternating-attention stack (with its GEMMs), sharded by frame")
-    ap.add_argument("--no-overlap", action="store_true", help="N > 1: all-gather in line instead of behind attention to the local keys")
+    ap.add_argument("--overlap", default="auto", choices=["auto", "on", "off"],
+                    help="N > 1: hide the K/V all-gather of a global layer behind attention to the local keys (on), keep it in line "
+                         "(off), or decide by the world size (auto: on from 4 GPUs; with 2 the gather is 3 %% of a layer and the "
+                         "SMs left to it cost the local attention more than the overlap returns)")
     ap.add_argument("--no-scene8", action="store_true", help="skip the 8-frame scene (extra key scene8)")
     ap.add_argument("--no-micro", action="store_true", help="skip the kernel-level sweep")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     args = ap.parse_args()
-    if args.only == "aggregator":
+    if args.only == "model":
+        print(json.dumps(model_measure(8 if args.frames == 100 else args.frames, args.iters, args.arms)))
+    elif args.only == "aggregator":
         run_aggregator(args)
     elif args.only:
         run_only(args)

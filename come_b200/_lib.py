@@ -20,7 +20,7 @@ EXPORTS = (
     "come_merge_plan_workspace_bytes", "come_merge_plan", "come_merge_plan_static", "come_merge", "come_merge_layernorm", "come_unmerge",
     "come_unmerge_strided", "come_unmerge_residual", "come_residual_layernorm", "come_suffix_add", "come_suffix_split",
     "come_attn_varlen_fwd", "come_attn_varlen_fwd_rows", "come_attn_cross_fwd", "come_attn_combine", "come_attn_set_cta_limit", "come_qkv_prepare", "come_packed_positions",
-    "come_device_status",
+    "come_device_status", "come_selftest_bounded_wait",
 )
 
 
@@ -79,6 +79,7 @@ def lib() -> C.CDLL:
     l.come_qkv_prepare.argtypes = [vp, i32, i64, i32, i32, vp, vp, vp, vp, f32, vp, vp, vp, i64, vp, vp, vp]
     l.come_packed_positions.argtypes = [vp, vp, i64, C.POINTER(Layout), vp, vp]
     l.come_device_status.argtypes = [C.POINTER(C.c_uint32), i32]
+    l.come_selftest_bounded_wait.argtypes = [i64, vp, vp]
     for name in EXPORTS:
         fn = getattr(l, name)
         if name not in ("come_last_error", "come_merge_plan_workspace_bytes"):
@@ -104,6 +105,15 @@ def check(rc: int) -> None:
 
 
 def device_status(clear: bool = True) -> int:
+    """The device status word (0 = no kernel reported a problem); synchronises the device."""
+    v = C.c_uint32(0)
+    rc = lib().come_device_status(C.byref(v), 1 if clear else 0)
+    if rc not in (COME_OK, COME_ERR_DEVICE):
+        check(rc)
+    return int(v.value)
+
+
+def raise_on_device_error(clear: bool = True) -> None:
+    """RuntimeError with the library's description of the status word when a kernel reported a problem."""
     v = C.c_uint32(0)
     check(lib().come_device_status(C.byref(v), 1 if clear else 0))
-    return int(v.value)

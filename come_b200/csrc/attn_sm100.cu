@@ -140,20 +140,25 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait.  Returns false (and raises the abort flag + the device status word) when it gives up.
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, SharedStorage &sh, unsigned int *status,
-                                          uint32_t code) {
+// Bounded wait.  Returns false (and raises the abort flag + the device status word) when it gives up after `limit`
+// clock ticks, or when another waiter of the CTA has given up.
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t *bar, uint32_t parity, volatile uint32_t *abort_flag,
+                                                unsigned int *status, uint32_t code, long long limit) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     while (true) {
         if (mbar_try_wait(bar, parity)) return true;
-        if (sh.abort_flag != 0) return false;
-        if (clock64() - t0 > kWaitTicks) {
-            sh.abort_flag = 1;
+        if (*abort_flag != 0) return false;
+        if (clock64() - t0 > limit) {
+            *abort_flag = 1;
             atomicOr(status, code);
             return false;
         }
     }
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, SharedStorage &sh, unsigned int *status,
+                                          uint32_t code) {
+    return mbar_wait_limit(bar, parity, &sh.abort_flag, status, code, kWaitTicks);
 }
 
 __device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *map, int c0, int c1, int c2, uint64_t *bar) {
@@ -321,6 +326,7 @@ __host__ __device__ constexpr uint32_t make_idesc(bool bf16, int M, int N, bool 
 enum : uint32_t {
     kErrQFull = 1u << 0, kErrKvFull = 1u << 1, kErrKvEmpty = 1u << 2, kErrSlabFull = 1u << 3, kErrSlabEmpty = 1u << 4,
     kErrSFull = 1u << 5, kErrSEmpty = 1u << 6, kErrPFull = 1u << 7, kErrODone = 1u << 8,
+    kErrSelfTest = 1u << 15,  // raised by the wait self-test on purpose
 };
 
 // One work item = the (up to) kTiles 128-row query tiles [q_row0, q_row0 + kTiles * 128) of one (segment, head).
@@ -893,6 +899,23 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     }
 }
 
+// Self-test of the failure path: one CTA waits, with the attention kernel's own bounded wait, on a barrier that nothing
+// ever arrives at.  The wait gives up after `ticks` clocks, raises the CTA's abort flag and the device status word, and
+// the kernel returns normally; `waited_out` (optional) receives the clocks it waited.
+__global__ void selftest_wait_kernel(long long ticks, unsigned int *__restrict__ status, long long *__restrict__ waited_out) {
+    __shared__ alignas(8) uint64_t bar;
+    __shared__ uint32_t abort_flag;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        mbar_init(&bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    const long long t0 = clock64();
+    const bool ok = mbar_wait_limit(&bar, 0, &abort_flag, status, kErrSelfTest, ticks);
+    if (threadIdx.x == 0 && waited_out) *waited_out = ok ? -1 : clock64() - t0;
+}
+
 // ---- host side --------------------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
@@ -1044,6 +1067,14 @@ int attn_sm100_launch(const AttnArgs &a, cudaStream_t stream) {
 }
 
 }  // namespace come
+
+extern "C" int come_selftest_bounded_wait(int64_t ticks, int64_t *waited_dev, void *stream) {
+    COME_REQUIRE(ticks > 0 && ticks <= (1ll << 26), "come_selftest_bounded_wait: ticks must be in (0, 2^26] (a fraction of a second)");
+    unsigned int *status = come::status_word_dev();
+    if (!status) return COME_ERR_CUDA;
+    come::selftest_wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>((long long)ticks, status, (long long *)waited_dev);
+    return come::check_launch("come_selftest_bounded_wait");
+}
 
 #ifdef COME_ATTN_TRACE
 // Development builds only: copies the per-warp wait counters of the last attention launch to host memory.

@@ -6,6 +6,7 @@
 
 #include "come_internal.cuh"
 
+#include <cstdlib>
 #include <mutex>
 
 namespace come {
@@ -335,6 +336,206 @@ merge_kernel(const T *__restrict__ tokens, const uint8_t *__restrict__ mask, con
             }
         }
     }
+}
+
+
+// ---- merge through a shared-memory ring fed by bulk copies -----------------------------------------------------------
+// For rows that are multiples of 16 bytes and units (G rows) that fit the ring: one persistent CTA per SM; a producer lane
+// copies every unit's source rows global -> shared with plain bulk copies (cp.async.bulk, no tensor map: a 3 x 3 window
+// of a row-major grid is three runs of three consecutive tokens, a 1-D group is one run) into a ring several units deep,
+// so that ~150 KB per SM are in flight all the time instead of two CTAs alternating load / add / store phases.  Kept
+// windows and prefix rows leave the ring by a bulk copy shared -> global issued by a second lane (their packed rows are
+// consecutive); merged windows are summed from shared memory by four consumer warps in the fixed left-to-right order of
+// merge_kernel (float32 sum, IEEE division, one rounding) and stored from registers.  Every wait is bounded.
+constexpr int kBulkThreads = 192;       // warp 0: producer, warp 1: bulk stores, warps 2-5: consumers
+constexpr int kBulkConsumers = 128;
+constexpr int kBulkMaxStages = 8;
+constexpr long long kBulkWaitTicks = 1ll << 29;
+constexpr unsigned kErrMergeBulk = 1u << 17;  // device status bit of a wait that ran out in merge_bulk_kernel
+
+__device__ __forceinline__ uint32_t cvta_smem(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ bool bulk_try_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(cvta_smem(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool bulk_wait(uint64_t *bar, uint32_t parity, volatile uint32_t *abort_flag, unsigned int *status) {
+    if (bulk_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (true) {
+        if (bulk_try_wait(bar, parity)) return true;
+        if (*abort_flag != 0) return false;
+        if (clock64() - t0 > kBulkWaitTicks) {
+            *abort_flag = 1;
+            atomicOr(status, kErrMergeBulk);
+            return false;
+        }
+    }
+}
+
+template <typename T, int VEC>
+__global__ void __launch_bounds__(kBulkThreads, 1)
+merge_bulk_kernel(const T *__restrict__ tokens, const uint8_t *__restrict__ mask, const int *__restrict__ group_prefix,
+                  const int *__restrict__ offsets, FrameLayout L, int frames, int64_t C, int stages, T *__restrict__ out,
+                  unsigned int *__restrict__ status) {
+    using IO = VecIO<T, VEC>;
+    using V = typename IO::V;
+    extern __shared__ __align__(128) uint8_t bulk_smem[];
+    const int G = L.G;
+    const uint32_t row_bytes = (uint32_t)(C * sizeof(T));
+    const uint32_t stage_bytes = (uint32_t)G * row_bytes;
+    uint64_t *full = reinterpret_cast<uint64_t *>(bulk_smem + (size_t)stages * stage_bytes);
+    uint64_t *empty = full + stages;
+    volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(empty + stages);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        for (int i = 0; i < stages; ++i) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(cvta_smem(&full[i])), "r"(1));
+            // every unit is released by all consumer threads and by the store lane, whichever of them used it
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(cvta_smem(&empty[i])), "r"(kBulkConsumers + 1));
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    const int prefix_units = (L.prefix + G - 1) / G;
+    const int units_per_frame = prefix_units + L.M;
+    const int n_units = frames * units_per_frame;
+
+    // unit u -> frame, first merge-order row, rows, first packed row, merged?
+    auto decode = [&](int u, int &b, int &r0, int &rows, int &dst, bool &merged) {
+        b = u / units_per_frame;
+        const int unit = u - b * units_per_frame;
+        const int base = offsets[b];
+        merged = false;
+        if (unit < prefix_units) {
+            r0 = unit * G;
+            rows = min(G, L.prefix - r0);
+            dst = base + r0;
+        } else {
+            const int m = unit - prefix_units;
+            r0 = L.prefix + m * G;
+            rows = G;
+            dst = base + L.prefix + group_prefix[(size_t)b * L.M + m];
+            merged = mask[(size_t)b * L.M + m] != 0;
+        }
+    };
+
+    if (warp == 0) {
+        // ===== producer: one lane issues the bulk loads of every unit of this CTA =====
+        if (lane == 0) {
+            int k = 0;
+            for (int u = blockIdx.x; u < n_units; u += gridDim.x, ++k) {
+                const int stage = k % stages;
+                if (k >= stages && !bulk_wait(&empty[stage], ((k / stages) - 1) & 1, abort_flag, status)) break;
+                int b, r0, rows, dst;
+                bool merged;
+                decode(u, b, r0, rows, dst, merged);
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(cvta_smem(&full[stage])), "r"((uint32_t)rows * row_bytes) : "memory");
+                const uint8_t *frame = reinterpret_cast<const uint8_t *>(tokens) + (size_t)b * L.N * row_bytes;
+                uint8_t *dst_s = bulk_smem + (size_t)stage * stage_bytes;
+                int g = 0;
+                while (g < rows) {  // runs of consecutive source tokens travel as one copy
+                    const int t0 = L.src_token(r0 + g);
+                    int n = 1;
+                    while (g + n < rows && L.src_token(r0 + g + n) == t0 + n) ++n;
+                    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                                 ::"r"(cvta_smem(dst_s + (size_t)g * row_bytes)), "l"(frame + (size_t)t0 * row_bytes),
+                                   "r"((uint32_t)n * row_bytes), "r"(cvta_smem(&full[stage])) : "memory");
+                    g += n;
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ===== store lane: units that are copied unchanged leave the ring by one bulk store =====
+        if (lane == 0) {
+            int k = 0, pending_stage = -1;
+            for (int u = blockIdx.x; u < n_units; u += gridDim.x, ++k) {
+                const int stage = k % stages;
+                int b, r0, rows, dst;
+                bool merged;
+                decode(u, b, r0, rows, dst, merged);
+                if (merged) {  // the consumers' unit: nothing to store, release at once
+                    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(cvta_smem(&empty[stage])) : "memory");
+                    continue;
+                }
+                if (!bulk_wait(&full[stage], (k / stages) & 1, abort_flag, status)) break;
+                asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                             ::"l"(reinterpret_cast<uint8_t *>(out) + (size_t)dst * row_bytes),
+                               "r"(cvta_smem(bulk_smem + (size_t)stage * stage_bytes)), "r"((uint32_t)rows * row_bytes) : "memory");
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                if (pending_stage >= 0) {  // the store before this one has read its stage: hand it back
+                    asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(cvta_smem(&empty[pending_stage])) : "memory");
+                }
+                pending_stage = stage;
+            }
+            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+            if (pending_stage >= 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(cvta_smem(&empty[pending_stage])) : "memory");
+            asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // all stores complete before the CTA's shared memory goes away
+        }
+    } else {
+        // ===== consumers: window means =====
+        const int tid = threadIdx.x - 64;
+        const int64_t Cv = C / VEC;
+        const float fG = (float)G;
+        int k = 0;
+        for (int u = blockIdx.x; u < n_units; u += gridDim.x, ++k) {
+            const int stage = k % stages;
+            int b, r0, rows, dst;
+            bool merged;
+            decode(u, b, r0, rows, dst, merged);
+            if (merged) {
+                if (!bulk_wait(&full[stage], (k / stages) & 1, abort_flag, status)) break;
+                const V *src = reinterpret_cast<const V *>(bulk_smem + (size_t)stage * stage_bytes);
+                V *dst_row = reinterpret_cast<V *>(out) + (int64_t)dst * Cv;
+                for (int64_t v = tid; v < Cv; v += kBulkConsumers) {
+                    float acc[VEC];
+#pragma unroll
+                    for (int i = 0; i < VEC; ++i) acc[i] = 0.0f;
+                    for (int g = 0; g < rows; ++g) {
+                        float f[VEC];
+                        IO::unpack(src[(int64_t)g * Cv + v], f);
+#pragma unroll
+                        for (int j = 0; j < VEC; ++j) acc[j] = __fadd_rn(acc[j], f[j]);
+                    }
+#pragma unroll
+                    for (int j = 0; j < VEC; ++j) acc[j] = __fdiv_rn(acc[j], fG);
+                    st_stream(dst_row + v, IO::pack(acc));
+                }
+            }
+            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(cvta_smem(&empty[stage])) : "memory");
+        }
+    }
+}
+
+
+// The bulk-ring kernel can be switched off (COME_MERGE_BULK=0 in the environment, read once) to compare the two merge
+// kernels; they produce the same bits.
+static bool bulk_disabled() {
+    static const bool off = [] {
+        const char *v = getenv("COME_MERGE_BULK");
+        return v == nullptr || v[0] != '1';  // opt-in until the GPU comparison has been recorded
+    }();
+    return off;
+}
+
+// Shared-memory opt-in of the bulk-ring kernel: raised per device and instantiation when a launch needs more than before.
+template <typename T, int VEC> static int ensure_bulk_smem(size_t smem) {
+    static std::mutex mu;
+    static size_t have[64];
+    int dev = 0;
+    COME_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) {
+        set_error("come_merge: device ordinal %d is out of the supported range", dev);
+        return COME_ERR_ARG;
+    }
+    std::lock_guard<std::mutex> lock(mu);
+    if (have[dev] >= smem) return COME_OK;
+    COME_CUDA(cudaFuncSetAttribute(merge_bulk_kernel<T, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(220 * 1024)));
+    have[dev] = 220 * 1024;
+    return COME_OK;
 }
 
 // ---- merge fused with the LayerNorm in front of it ---------------------------------------------------------------
@@ -797,6 +998,26 @@ static int launch_merge(const void *tokens, int64_t frames, int64_t C, const Fra
     const int64_t max_blocks = (int64_t)sm_count() * 8;  // 8 resident CTAs of 256 threads per SM
     const bool vec_ok = (C % VEC == 0) && ((uintptr_t)tokens % 16 == 0) && ((uintptr_t)out % 16 == 0);
     const int64_t cv = vec_ok ? C / VEC : C;  // vectors per row as the launched kernel sees them
+    // Wide rows: the shared-memory ring fed by bulk copies (16-byte multiples, at least four units in the ring).
+    {
+        const size_t row_bytes = (size_t)C * sizeof(T), stage_bytes = (size_t)L.G * row_bytes;
+        const size_t budget = 200 * 1024;
+        int stages = stage_bytes ? (int)(budget / stage_bytes) : 0;
+        if (stages > kBulkMaxStages) stages = kBulkMaxStages;
+        const bool aligned = ((uintptr_t)tokens % 16 == 0) && ((uintptr_t)out % 16 == 0) && row_bytes % 16 == 0;
+        if (vec_ok && aligned && stages >= 4 && row_bytes >= 512 && !bulk_disabled()) {
+            unsigned int *status = status_word_dev();
+            if (!status) return COME_ERR_CUDA;
+            const size_t smem_bulk = (size_t)stages * stage_bytes + (size_t)stages * 2 * sizeof(uint64_t) + 16;
+            int rc = ensure_bulk_smem<T, VEC>(smem_bulk);
+            if (rc != COME_OK) return rc;
+            const int sms = sm_count();
+            const unsigned grid_b = (unsigned)(n_units < sms ? n_units : sms);
+            merge_bulk_kernel<T, VEC><<<grid_b, kBulkThreads, smem_bulk, st>>>((const T *)tokens, mask, gp, off, L, (int)frames, C, stages,
+                                                                                (T *)out, status);
+            return check_launch("come_merge (bulk ring)");
+        }
+    }
     int groups = 1;
     if (cv >= 32 && cv < kMergeThreads && kMergeThreads % cv == 0) groups = (int)(kMergeThreads / cv);
     while (groups > 1 && (size_t)L.G * sizeof(int) * groups > 48 * 1024) groups >>= 1;
@@ -1277,5 +1498,10 @@ extern "C" int come_device_status(uint32_t *value, int clear) {
     COME_CUDA(cudaMemcpy(&v, word, sizeof(v), cudaMemcpyDeviceToHost));
     *value = v;
     if (clear && v != 0) COME_CUDA(cudaMemset(word, 0, sizeof(v)));
+    if (v != 0) {
+        come::set_error("device status word 0x%08x: %s%s%s", v, (v & 0x1ffu) ? "a bounded wait of the attention kernel ran out; " : "",
+                        (v & 0x8000u) ? "the wait self-test ran; " : "", (v & 0x10000u) ? "a position outside the rotary table was clamped; " : "");
+        return COME_ERR_DEVICE;
+    }
     return COME_OK;
 }

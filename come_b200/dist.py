@@ -109,7 +109,10 @@ class GlobalExchange:
 
     def __init__(self, rows: Sequence[int], rank: int, weight_all: torch.Tensor, group: Optional[dist.ProcessGroup] = None,
                  gather=None, overlap: bool = False, comm_sms: int = 16):
-        """``comm_sms``: SMs left to the all-gather kernel while the attention to the local keys runs beside it."""
+        """``comm_sms``: SMs left to the all-gather kernel while the attention to the local keys runs beside it.  The
+        collective completes only when all its CTAs have run, so the communicator must not use more CTAs than that
+        (``NCCL_MAX_CTAS`` in the environment before the process group is created, or the ``max_ctas`` option of the NCCL
+        process group); otherwise its last CTAs wait for the attention kernel to end and nothing overlaps."""
         self.comm_sms = int(comm_sms)
         self.rows = [int(n) for n in rows]
         self.rank = int(rank)

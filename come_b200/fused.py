@@ -26,7 +26,7 @@ import torch
 from .block import JaggedBlock, JaggedBlock_w_Bias, forward_fused, fusable, residual_layernorm
 from .token_merger import JaggedTokens, MergePlan
 
-__all__ = ["FusedAggregator", "ShardedFusedAggregator", "CapturedForward", "fused_accelerate"]
+__all__ = ["FusedAggregator", "ShardedFusedAggregator", "CapturedForward", "fused_accelerate", "FusedModel", "run_blocks"]
 
 
 class FusedAggregator(torch.nn.Module):
@@ -231,6 +231,92 @@ class ShardedFusedAggregator(FusedAggregator):
         x = JaggedTokens(tokens=merged.unsqueeze(0), weight=local_plan.weight, offset=frame_offset)
         output = self._run(x, pos, frame_view, global_view, self.frame_blocks, self.global_blocks, unmerge)
         return output, self.patch_start_idx
+
+
+def run_blocks(wrappers, x: JaggedTokens, pos: Optional[torch.Tensor], fuse: bool = True) -> JaggedTokens:
+    """A plain sequence of jagged blocks (the patch encoder's), with the elementwise steps fused when the blocks allow it."""
+    wrappers = list(wrappers)
+    if not wrappers:
+        return x
+    if fuse and all(fusable(w, x.tokens.dtype) for w in wrappers):
+        _, normed = residual_layernorm(x.tokens.squeeze(0), None, None, wrappers[0].block.norm1)
+        for i, w in enumerate(wrappers):
+            nxt = wrappers[i + 1].block.norm1 if i + 1 < len(wrappers) else None
+            x, normed = forward_fused(w, x, normed, pos, nxt)
+        return x
+    for w in wrappers:
+        x = w(x, pos=pos)
+    return x
+
+
+class FusedModel(torch.nn.Module):
+    """The accelerated model from the images to the retained aggregator layers, in the shape of the reference's fused mode
+    (``src/accelerate/vggt/fused.py:40-94``): the patch encoder runs dense up to block ``encoder_layer``; its output
+    feeds the confidence predictor, the windows are selected and the tokens merged at once; the remaining encoder blocks
+    run on the packed tokens with the count bias; the tokens are split after the last encoder block, normed, given the
+    aggregator's camera and register tokens, merged again with the same plan, and the alternating-attention stack runs
+    as :class:`FusedAggregator`.  The prediction heads are outside (they consume the retained layers).
+
+    ``forward_unmerged`` runs the same weights with nothing merged: the model the accelerated one is compared with
+    (``src/bench.py:13-46``, "Reference Model" against "Accelerated Model")."""
+
+    def __init__(self, encoder: torch.nn.Module, aggregator: torch.nn.Module, predictor, encoder_layer: int = 14,
+                 group_h: int = 3, group_w: int = 3, threshold: float = 0.5, conf_mode: str = "pairwise-rank",
+                 use_attn_bias_correction: bool = True, attn_dtype: str = "bf16"):
+        super().__init__()
+        from .token_merger import CoMe2DTokenMerger
+        if not (0 <= encoder_layer < len(encoder.blocks)):
+            raise ValueError(f"encoder_layer {encoder_layer} outside the encoder's {len(encoder.blocks)} blocks")
+        self.encoder, self.predictor, self.encoder_layer = encoder, predictor, int(encoder_layer)
+        block_fn = JaggedBlock_w_Bias if use_attn_bias_correction else JaggedBlock
+        self.enc_dense = torch.nn.ModuleList([JaggedBlock(b, attn_dtype) for b in encoder.blocks])
+        self.enc_merged = torch.nn.ModuleList([block_fn(b, attn_dtype) for b in encoder.blocks[encoder_layer + 1:]])
+        self.aggregator = FusedAggregator(aggregator, use_attn_bias_correction, attn_dtype)
+        self.merger = CoMe2DTokenMerger(encoder.prefix_tokens, group_h, group_w, threshold, predictor, conf_mode)
+        self.last_plan: Optional[MergePlan] = None
+
+    def _dense_tokens(self, images: torch.Tensor):
+        B, S = images.shape[:2]
+        tokens = self.encoder.embed(images.flatten(0, 1))  # [B*S, N, C]
+        N = tokens.shape[1]
+        offset = torch.arange(0, B * S * N + 1, N, device=tokens.device, dtype=torch.int64)
+        weight = torch.ones(B * S * N, dtype=torch.float32, device=tokens.device)
+        x = JaggedTokens(tokens.reshape(1, B * S * N, -1), weight, offset, max_seqlen=N, cu_seqlens=offset.to(torch.int32))
+        return x, B, S, N
+
+    def forward(self, images: torch.Tensor) -> Tuple[Dict[int, torch.Tensor], int]:
+        """``images [B, S, 3, H, W]`` -> (retained layers ``{block index: [B, S, N, 2C]}``, ``patch_start_idx``)."""
+        enc = self.encoder
+        x, B, S, N = self._dense_tokens(images)
+        h, w = enc.grid
+        x = run_blocks(self.enc_dense[: self.encoder_layer + 1], x, None)
+        dense = x.tokens.reshape(B * S, N, -1)
+        start = enc.prefix_tokens
+        feature = dense[:, start:].permute(0, 2, 1).reshape(B, S, -1, h, w)  # [B, S, C, h, w] as the reference's hook builds it
+        ctx = self.merger.build_ctx(feature)
+        plan = ctx[2]
+        self.last_plan = plan
+        merged = plan.merge(dense)
+        xm = JaggedTokens(merged.unsqueeze(0), plan.weight, plan.offset, max_seqlen=plan.max_seqlen, cu_seqlens=plan.cu_seqlens(1))
+        xm = run_blocks(self.enc_merged, xm, None)
+        dense = enc.norm(plan.split(xm.tokens.squeeze(0)).reshape(B * S, N, -1))
+        tokens = self.aggregator.aggregator.assemble_tokens(dense[:, start:], B, S)
+        if tokens.shape[2] != N:
+            raise ValueError("the aggregator's special tokens must number the encoder's (one merge plan serves both)")
+        return self.aggregator(tokens.contiguous(), plan)
+
+    def forward_unmerged(self, images: torch.Tensor) -> Tuple[Dict[int, torch.Tensor], int]:
+        enc = self.encoder
+        x, B, S, N = self._dense_tokens(images)
+        x = run_blocks(self.enc_dense, x, None)
+        dense = enc.norm(x.tokens.reshape(B * S, N, -1))
+        tokens = self.aggregator.aggregator.assemble_tokens(dense[:, enc.prefix_tokens:], B, S)
+        h, w = enc.grid
+        dev = tokens.device
+        yy, xx = torch.meshgrid(torch.arange(1, h + 1, device=dev), torch.arange(1, w + 1, device=dev), indexing="ij")
+        frame_pos = torch.cat([torch.zeros(enc.prefix_tokens, 2, dtype=torch.int64, device=dev),
+                               torch.stack([yy.reshape(-1), xx.reshape(-1)], dim=-1)], dim=0)
+        return self.aggregator.forward_unmerged(tokens.contiguous(), frame_pos.repeat(B * S, 1))
 
 
 def fused_accelerate(aggregator: torch.nn.Module, use_attn_bias_correction: bool = True) -> FusedAggregator:

@@ -20,7 +20,7 @@ from torch import nn
 
 from .qkv import RotaryPositionEmbedding2D
 
-__all__ = ["LayerScale", "Mlp", "Attention", "Block", "AggregatorCore"]
+__all__ = ["LayerScale", "Mlp", "Attention", "Block", "AggregatorCore", "PatchEncoderCore", "ConfidenceHead"]
 
 
 class LayerScale(nn.Module):
@@ -94,15 +94,103 @@ class AggregatorCore(nn.Module):
         self.aa_block_num = depth // aa_block_size
         self.retain_layers = retain_layers
         self.patch_start_idx = patch_start_idx
+        # camera and register tokens: entry 0 for the first frame of a scene, entry 1 for the others
+        # (src/thirdparty/vggt/models/aggregator.py:117-126, slice_expand_and_flatten :335-360)
+        self.camera_token = nn.Parameter(torch.zeros(1, 2, 1, embed_dim))
+        self.register_token = nn.Parameter(torch.zeros(1, 2, patch_start_idx - 1, embed_dim))
         gen = torch.Generator().manual_seed(seed)
         with torch.no_grad():
             for name, p in self.named_parameters():
                 if name.endswith("gamma"):
                     continue  # LayerScale keeps its init value
-                if p.dim() == 2:
+                if name.endswith("_token"):
+                    p.copy_(torch.randn(p.shape, generator=gen) * 1e-1)
+                elif p.dim() == 2:
                     p.copy_(torch.randn(p.shape, generator=gen) * weight_std)
                 elif "norm" in name and name.endswith("weight"):
                     p.copy_(1.0 + 0.1 * torch.randn(p.shape, generator=gen))
                 else:
                     p.copy_(0.02 * torch.randn(p.shape, generator=gen))
         self.eval()
+
+    def assemble_tokens(self, patch_tokens: torch.Tensor, B: int, S: int) -> torch.Tensor:
+        """``patch_tokens [B*S, h*w, C]`` -> ``[B, S, patch_start_idx + h*w, C]`` with the camera and register tokens in
+        front of every frame (``aggregator.py:205-215``)."""
+        Cc = patch_tokens.shape[-1]
+
+        def expand(tok):  # [1, 2, X, C] -> [B*S, X, C]: entry 0 for frame 0 of every scene, entry 1 for the rest
+            first = tok[:, 0:1].expand(B, 1, -1, -1)
+            rest = tok[:, 1:2].expand(B, S - 1, -1, -1)
+            return torch.cat([first, rest], dim=1).reshape(B * S, -1, Cc)
+
+        cam, reg = expand(self.camera_token.to(patch_tokens.dtype)), expand(self.register_token.to(patch_tokens.dtype))
+        return torch.cat([cam, reg, patch_tokens], dim=1).reshape(B, S, -1, Cc)
+
+
+class PatchEncoderCore(nn.Module):
+    """Patch encoder in the shape of the ViT-L/14 with four register tokens that VGGT uses (``aggregator.py:76-101``:
+    DINOv2 ``vit_large``, patch 14, ``num_register_tokens=4``, LayerScale, no q/k norm, no rotary embedding): patch
+    embedding, class + register tokens, learned position embedding, ``depth`` blocks, final norm.  Random-initialised;
+    the blocks are evaluated by the jagged block wrappers like the aggregator's."""
+
+    def __init__(self, embed_dim: int = 1024, depth: int = 24, num_heads: int = 16, patch_size: int = 14, registers: int = 4,
+                 grid: Sequence[int] = (37, 37), mlp_ratio: float = 4.0, init_values: Optional[float] = 1.0, seed: int = 1,
+                 weight_std: float = 0.02):
+        super().__init__()
+        self.patch_size, self.registers, self.embed_dim = patch_size, registers, embed_dim
+        self.num_features = embed_dim
+        self.proj = nn.Conv2d(3, embed_dim, kernel_size=patch_size, stride=patch_size)
+        self.cls_token = nn.Parameter(torch.zeros(1, 1, embed_dim))
+        self.register_tokens = nn.Parameter(torch.zeros(1, registers, embed_dim))
+        self.pos_embed = nn.Parameter(torch.zeros(1, 1 + grid[0] * grid[1], embed_dim))  # class token + patches
+        self.grid = tuple(grid)
+        self.blocks = nn.ModuleList([Block(embed_dim, num_heads, mlp_ratio, init_values, qk_norm=False, rope=None)
+                                     for _ in range(depth)])
+        self.norm = nn.LayerNorm(embed_dim, eps=1e-6)
+        gen = torch.Generator().manual_seed(seed)
+        with torch.no_grad():
+            for name, p in self.named_parameters():
+                if name.endswith("gamma"):
+                    continue
+                if name in ("cls_token", "register_tokens", "pos_embed"):
+                    p.copy_(torch.randn(p.shape, generator=gen) * weight_std)
+                elif p.dim() >= 2:
+                    p.copy_(torch.randn(p.shape, generator=gen) * weight_std)
+                elif "norm" in name and name.endswith("weight"):
+                    p.copy_(1.0 + 0.1 * torch.randn(p.shape, generator=gen))
+                else:
+                    p.copy_(0.02 * torch.randn(p.shape, generator=gen))
+        self.eval()
+
+    @property
+    def prefix_tokens(self) -> int:
+        return 1 + self.registers
+
+    def embed(self, images: torch.Tensor) -> torch.Tensor:
+        """``images [F, 3, H, W]`` -> tokens ``[F, 1 + registers + h*w, C]``: class token, register tokens, patches."""
+        Fr, _, Hh, Ww = images.shape
+        h, w = Hh // self.patch_size, Ww // self.patch_size
+        if (h, w) != self.grid:
+            raise ValueError(f"images give a {h}x{w} patch grid, the position embedding was built for {self.grid}")
+        x = self.proj(images.to(self.proj.weight.dtype)).flatten(2).transpose(1, 2)  # [F, h*w, C]
+        x = torch.cat([self.cls_token.expand(Fr, -1, -1), x], dim=1) + self.pos_embed
+        return torch.cat([x[:, :1], self.register_tokens.expand(Fr, -1, -1), x[:, 1:]], dim=1)
+
+
+class ConfidenceHead(nn.Module):
+    """Seeded two-layer MLP ``C -> hidden -> 1`` on the patch tokens: the stand-in for the distilled confidence predictor
+    in the synthetic benchmark configurations.  Call signature of the reference's predictor
+    (``feature [B, S, H, W, C]``, ``BPHWC=...`` -> ``[B, S*H*W, 1]``)."""
+
+    def __init__(self, embed_dim: int = 1024, hidden: int = 128, seed: int = 2):
+        super().__init__()
+        self.fc1, self.act, self.fc2 = nn.Linear(embed_dim, hidden), nn.GELU(), nn.Linear(hidden, 1)
+        gen = torch.Generator().manual_seed(seed)
+        with torch.no_grad():
+            for p in self.parameters():
+                p.copy_(torch.randn(p.shape, generator=gen) * (0.05 if p.dim() == 2 else 0.01))
+        self.eval()
+
+    def forward(self, feature: torch.Tensor, BPHWC=None) -> torch.Tensor:
+        B = feature.shape[0]
+        return self.fc2(self.act(self.fc1(feature.to(self.fc1.weight.dtype)))).reshape(B, -1, 1)

@@ -337,9 +337,21 @@ int come_packed_positions(const uint8_t *mask_dev, const int64_t *rev_id_dev, in
 /*
  * Device status word: kernels that wait on hardware barriers give up after a bounded number of polls and
  * record a non-zero code here instead of hanging.  Reads it back (synchronises the device) and optionally
- * clears it.  Returns COME_OK with *value == 0 when no kernel reported a problem.
+ * clears it.  Returns COME_OK with *value == 0 when no kernel reported a problem, COME_ERR_DEVICE with the word in
+ * *value (and a message naming its bits) otherwise.  Bits 0-8: a wait of the attention kernel ran out (while the word is
+ * raised, attention launches return at once without touching their outputs); bit 15: the wait self-test below; bit 16: a
+ * position outside the rotary table was clamped by come_qkv_prepare.
  */
 int come_device_status(uint32_t *value, int clear);
+
+/*
+ * Self-test of the failure path, for deployments that want to see it work once: a one-CTA kernel waits, with the
+ * attention kernel's bounded wait, on a barrier that nothing arrives at; after `ticks` clocks (at most 2^26, a few
+ * hundredths of a second) the wait gives up, raises bit 15 of the device status word and the kernel returns normally.
+ * waited_dev (may be NULL): one int64 in device memory that receives the clocks waited.  Nothing faults or hangs; clear
+ * the word with come_device_status(&v, 1) afterwards.  No counterpart in the reference.
+ */
+int come_selftest_bounded_wait(int64_t ticks, int64_t *waited_dev, void *stream);
 
 #ifdef __cplusplus
 }

@@ -698,6 +698,70 @@ def fused_aggregator(tokens, mask, start_index, H, W, gh, gw, frame_params, glob
     return output
 
 
+def patch_embed(images, proj_weight, proj_bias, cls_token, register_tokens, pos_embed, patch: int):
+    """Patch embedding of a ViT with register tokens (``src/thirdparty/vggt/layers/vision_transformer.py``
+    ``prepare_tokens_with_masks``): non-overlapping ``patch x patch`` convolution, class token in front, learned position
+    embedding added to class + patch tokens, register tokens inserted behind the class token.
+    ``images [F, 3, H, W]`` -> ``[F, 1 + R + h*w, C]`` float32."""
+    images = np.asarray(images, np.float32)
+    Fr, Cin, Hh, Ww = images.shape
+    h, w = Hh // patch, Ww // patch
+    x = images[:, :, : h * patch, : w * patch].reshape(Fr, Cin, h, patch, w, patch).transpose(0, 2, 4, 1, 3, 5).reshape(Fr, h * w, -1)
+    Wm = np.asarray(proj_weight, np.float32).reshape(proj_weight.shape[0], -1)  # [C, 3 * patch * patch]
+    tok = (x @ Wm.T + np.asarray(proj_bias, np.float32)).astype(np.float32)
+    tok = np.concatenate([np.broadcast_to(cls_token, (Fr,) + cls_token.shape[1:]), tok], axis=1) + pos_embed
+    reg = np.broadcast_to(register_tokens, (Fr,) + register_tokens.shape[1:])
+    return np.concatenate([tok[:, :1], reg, tok[:, 1:]], axis=1).astype(np.float32)
+
+
+def fused_model(images, enc, enc_params, encoder_layer, head, agg_tokens, frame_params, global_params, num_heads, gh, gw,
+                threshold, retain_layers=None, rope_base=100.0, rope_kind="bf16", conf_kind="bf16", mask=None):
+    """The accelerated model from images to the retained aggregator layers (``src/accelerate/vggt/fused.py:40-94`` around
+    :func:`fused_aggregator`), float32: encoder blocks ``0 .. encoder_layer`` dense, confidence -> window selection over
+    the scene (``co_me_2d.py:268-298``) -> merge, encoder blocks ``encoder_layer + 1 ..`` on the packed tokens with the
+    count bias, split, final norm, camera / register tokens of the aggregator in front of the patch tokens, merged
+    forward pass of the aggregator with the same mask.
+
+    ``enc``: dict with ``proj.weight / proj.bias / cls_token / register_tokens / pos_embed / norm.weight / norm.bias``,
+    ``patch``, ``norm_eps``; ``enc_params``: list of block dictionaries (:func:`jagged_block`); ``head``: the two-layer
+    confidence MLP ``fc1.weight/bias, fc2.weight/bias``; ``agg_tokens``: ``camera_token [1,2,1,C]``, ``register_token
+    [1,2,R,C]``.  ``mask`` (optional) overrides the selection (a device run may select in lower precision).
+    Returns ``(layers, mask)``."""
+    images = np.asarray(images, np.float32)
+    B, S = images.shape[:2]
+    x = patch_embed(images.reshape((B * S,) + images.shape[2:]), enc["proj.weight"], enc["proj.bias"], enc["cls_token"],
+                    enc["register_tokens"], enc["pos_embed"], enc["patch"])
+    Fr, N, C = x.shape
+    start = 1 + enc["register_tokens"].shape[1]
+    h, w = images.shape[3] // enc["patch"], images.shape[4] // enc["patch"]
+    ones = np.ones(Fr * N, np.float32)
+    cu = np.arange(0, Fr * N + 1, N, dtype=np.int64)
+    flat = x.reshape(Fr * N, C)
+    for p in enc_params[: encoder_layer + 1]:
+        flat = jagged_block(flat, ones, cu, None, p, num_heads, None, None, use_bias=False)
+    dense = flat.reshape(Fr, N, C)
+    if mask is None:
+        feat = _round_like(dense[:, start:], conf_kind)
+        hid = gelu_erf(feat @ head["fc1.weight"].T + head["fc1.bias"])
+        conf = (hid @ head["fc2.weight"].T + head["fc2.bias"]).reshape(B, S * h * w)
+        mask = select_windows(_round_like(conf, conf_kind), B, S, h, w, gh, gw, threshold, "pairwise-rank", "batch", conf_kind)
+    merged, offsets, rev, weight = token_merge_2d_ragged(dense, start, gh, gw, h, w, mask)
+    for p in enc_params[encoder_layer + 1:]:
+        merged = jagged_block(merged, weight, np.asarray(offsets, np.int64), None, p, num_heads, None, None, use_bias=True)
+    dense = token_split(merged, rev).reshape(Fr, N, C)
+    dense = _layer_norm_f32(dense, enc["norm.weight"], enc["norm.bias"], float(enc.get("norm_eps", 1e-6)))
+
+    def expand(tok):  # [1, 2, X, C] -> [B*S, X, C]
+        first = np.broadcast_to(tok[:, 0:1], (B, 1) + tok.shape[2:])
+        rest = np.broadcast_to(tok[:, 1:2], (B, S - 1) + tok.shape[2:])
+        return np.concatenate([first, rest], axis=1).reshape((B * S,) + tok.shape[2:])
+
+    tokens = np.concatenate([expand(agg_tokens["camera_token"]), expand(agg_tokens["register_token"]), dense[:, start:]], axis=1)
+    layers = fused_aggregator(tokens.reshape(B, S, N, C), mask, start, h, w, gh, gw, frame_params, global_params, num_heads,
+                              retain_layers, rope_base=rope_base, rope_kind=rope_kind)
+    return layers, mask
+
+
 # --------------------------------------------------------------------------------------------------------
 # suffix tokens of jagged segments
 # --------------------------------------------------------------------------------------------------------

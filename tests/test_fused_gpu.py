@@ -387,3 +387,60 @@ def test_sharded_aggregator_two_gpus(overlap):
     for rank, lo, hi, out in results:
         for layer, ref in whole.items():
             assert _relative_error(out[layer], to_np(ref[:, lo:hi])) < 1e-2, (rank, layer)
+
+
+# ---- the whole accelerated model: encoder-side merge + aggregator ----------------------------------------------------
+def test_fused_model_against_oracle():
+    """2 dense + 2 merged encoder blocks and 2 + 2 aggregator blocks on two frames of a 6 x 7 patch grid, against the
+    float32 oracle chain (``oracle.fused_model``): the selection mask must be the oracle's (same bfloat16 confidences are
+    not guaranteed after two bfloat16 blocks, so the device mask is handed to the oracle and must merge something), the
+    retained layers agree within the bfloat16 tolerance; with a ratio of 0 the accelerated model equals the unmerged one."""
+    from come_b200.fused import FusedModel
+    from come_b200.vggt_arch import AggregatorCore, ConfidenceHead, PatchEncoderCore
+    rng = np.random.default_rng(77)
+    C, heads, patch, grid = 128, 2, 14, (6, 7)
+    enc = PatchEncoderCore(embed_dim=C, depth=4, num_heads=heads, patch_size=patch, registers=4, grid=grid, mlp_ratio=2.0,
+                           init_values=0.5)
+    enc_params = []
+    for blk in enc.blocks:
+        p = gi.block_params(rng, C, heads, 2.0, False, 0.5, kind="bf16")
+        blk.load_state_dict({k: torch.from_numpy(v) for k, v in p.items()})
+        enc_params.append(dict(p, norm_eps=blk.norm1.eps))
+    with torch.no_grad():  # parameters exactly representable in bfloat16, so that the oracle and the device hold the same numbers
+        for p_ in list(enc.parameters()):
+            p_.copy_(p_.bfloat16().float())
+    core, params = _small_model(rng, 2, C, heads, 0.5, torch.bfloat16)
+    head = ConfidenceHead(C, 32)
+    with torch.no_grad():
+        for p_ in head.parameters():
+            p_.copy_(p_.bfloat16().float())
+    f32 = lambda t: t.detach().float().cpu().numpy()  # noqa: E731
+    enc_np = {"proj.weight": f32(enc.proj.weight), "proj.bias": f32(enc.proj.bias), "cls_token": f32(enc.cls_token),
+              "register_tokens": f32(enc.register_tokens), "pos_embed": f32(enc.pos_embed), "norm.weight": f32(enc.norm.weight),
+              "norm.bias": f32(enc.norm.bias), "patch": patch, "norm_eps": enc.norm.eps}
+    head_np = {"fc1.weight": f32(head.fc1.weight), "fc1.bias": f32(head.fc1.bias), "fc2.weight": f32(head.fc2.weight),
+               "fc2.bias": f32(head.fc2.bias)}
+    tok_np = {"camera_token": f32(core.camera_token), "register_token": f32(core.register_token)}
+    B, S = 1, 2
+    images = gi.round_kind(rng.random((B, S, 3, grid[0] * patch, grid[1] * patch), dtype=np.float32), "bf16")
+    model = FusedModel(enc.cuda().bfloat16(), core, head.cuda().bfloat16(), encoder_layer=1, threshold=0.5)
+    with torch.no_grad():
+        out, start = model(torch.from_numpy(images).cuda().bfloat16())
+        mask = model.last_plan.mask.cpu().numpy()
+        plain, _ = model.forward_unmerged(torch.from_numpy(images).cuda().bfloat16())
+    assert start == 5 and 0 < mask.sum() < mask.size
+    ref, _ = orc.fused_model(images, enc_np, enc_params, 1, head_np, tok_np, params["frame"], params["global"], heads, 3, 3, 0.5,
+                             mask=mask)
+    ref_mask = orc.fused_model(images, enc_np, enc_params, 1, head_np, tok_np, params["frame"], params["global"], heads, 3, 3, 0.5)[1]
+    assert ref_mask.shape == mask.shape and ref_mask.sum() == mask.sum()  # the ranking merges the same number of windows
+    N = 5 + grid[0] * grid[1]
+    for layer in sorted(ref):
+        got = to_np(out[layer])
+        assert got.shape == (B, S, N, 2 * C)
+        assert _relative_error(got, ref[layer]) < 2 * FUSED_REL_TOL, (layer, _relative_error(got, ref[layer]))
+        assert to_np(plain[layer]).shape == got.shape
+    never = FusedModel(enc, core, head, encoder_layer=1, threshold=0.0)
+    with torch.no_grad():
+        same, _ = never(torch.from_numpy(images).cuda().bfloat16())
+    for layer in sorted(ref):
+        assert _relative_error(to_np(same[layer]), to_np(plain[layer])) < 1e-2

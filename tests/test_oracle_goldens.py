@@ -312,3 +312,23 @@ def test_attention_combine_is_attention_over_the_union_of_keys():
     out, lse = orc.attention_combine(parts[0][0], parts[0][1], parts[1][0], parts[1][1])
     np.testing.assert_allclose(out, full[:rows], atol=2e-6, rtol=1e-5)
     np.testing.assert_allclose(lse, full_lse[:, :rows], atol=2e-6, rtol=1e-5)
+
+
+def test_torch_cpu_attention_matches_the_c_oracle():
+    """The PyTorch-operator restatement of the biased attention (the timed CPU baseline) against the C oracle."""
+    from oracle import torch_path
+    rng = np.random.default_rng(12)
+    lengths = [5, 130, 64, 1]
+    P, H, D = sum(lengths), 3, 64
+    qkv = rng.standard_normal((P, 3, H, D), dtype=np.float32)
+    bias = np.log(np.where(rng.random(P) < 0.3, 9.0, 1.0)).astype(np.float32)
+    cu = np.concatenate([[0], np.cumsum(lengths)]).astype(np.int32)
+    for b in (bias, None):
+        want, want_lse = clib.attention_bias(qkv, b, cu, D ** -0.5)
+        got, got_lse = torch_path.attention_bias(qkv, b, cu, D ** -0.5)
+        np.testing.assert_allclose(got, want, atol=2e-6, rtol=1e-5)
+        np.testing.assert_allclose(got_lse, want_lse, atol=2e-6, rtol=1e-5)
+    part, part_lse = torch_path.attention_bias(qkv, bias, cu[:2 + 1][1:], D ** -0.5, 10, 50)  # rows 10..49 of the 130-row segment
+    full, full_lse = clib.attention_bias(qkv, bias, cu, D ** -0.5)
+    np.testing.assert_allclose(part[5 + 10:5 + 50], full[5 + 10:5 + 50], atol=2e-6, rtol=1e-5)
+    np.testing.assert_allclose(part_lse[:, 5 + 10:5 + 50], full_lse[:, 5 + 10:5 + 50], atol=2e-6, rtol=1e-5)
