@@ -347,9 +347,10 @@ merge_kernel(const T *__restrict__ tokens, const uint8_t *__restrict__ mask, con
 // windows and prefix rows leave the ring by a bulk copy shared -> global issued by a second lane (their packed rows are
 // consecutive); merged windows are summed from shared memory by four consumer warps in the fixed left-to-right order of
 // merge_kernel (float32 sum, IEEE division, one rounding) and stored from registers.  Every wait is bounded.
-constexpr int kBulkThreads = 192;       // warp 0: producer, warp 1: bulk stores, warps 2-5: consumers
+constexpr int kBulkThreads = 256;       // warps 0-1: producers, warps 2-3: bulk stores (one lane each), warps 4-7: consumers
+constexpr int kBulkLanes = 2;           // producers and store lanes work on alternate units: unit k belongs to lane k % 2
 constexpr int kBulkConsumers = 128;
-constexpr int kBulkMaxStages = 8;
+constexpr int kBulkMaxStages = 8;       // a multiple of kBulkLanes, see launch_merge
 constexpr long long kBulkWaitTicks = 1ll << 29;
 constexpr unsigned kErrMergeBulk = 1u << 17;  // device status bit of a wait that ran out in merge_bulk_kernel
 
@@ -374,6 +375,15 @@ __device__ __forceinline__ bool bulk_wait(uint64_t *bar, uint32_t parity, volati
     }
 }
 
+// What the producer publishes about a unit, in shared memory beside its stage: the other roles read it after the stage's
+// "full" barrier instead of decoding the unit from global memory themselves (three dependent loads per unit).
+struct BulkUnit {
+    int dst;      // first packed row
+    int rows;     // source rows in the stage
+    int merged;   // window mean (consumers) or plain copy (store lane)
+    int pad;
+};
+
 template <typename T, int VEC>
 __global__ void __launch_bounds__(kBulkThreads, 1)
 merge_bulk_kernel(const T *__restrict__ tokens, const uint8_t *__restrict__ mask, const int *__restrict__ group_prefix,
@@ -387,7 +397,8 @@ merge_bulk_kernel(const T *__restrict__ tokens, const uint8_t *__restrict__ mask
     const uint32_t stage_bytes = (uint32_t)G * row_bytes;
     uint64_t *full = reinterpret_cast<uint64_t *>(bulk_smem + (size_t)stages * stage_bytes);
     uint64_t *empty = full + stages;
-    volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(empty + stages);
+    BulkUnit *desc = reinterpret_cast<BulkUnit *>(empty + stages);
+    volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(desc + stages);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
         *abort_flag = 0;
@@ -402,68 +413,91 @@ merge_bulk_kernel(const T *__restrict__ tokens, const uint8_t *__restrict__ mask
     const int prefix_units = (L.prefix + G - 1) / G;
     const int units_per_frame = prefix_units + L.M;
     const int n_units = frames * units_per_frame;
+    const int my_units = blockIdx.x < n_units ? (n_units - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
 
-    // unit u -> frame, first merge-order row, rows, first packed row, merged?
-    auto decode = [&](int u, int &b, int &r0, int &rows, int &dst, bool &merged) {
-        b = u / units_per_frame;
-        const int unit = u - b * units_per_frame;
-        const int base = offsets[b];
-        merged = false;
-        if (unit < prefix_units) {
-            r0 = unit * G;
-            rows = min(G, L.prefix - r0);
-            dst = base + r0;
-        } else {
-            const int m = unit - prefix_units;
-            r0 = L.prefix + m * G;
-            rows = G;
-            dst = base + L.prefix + group_prefix[(size_t)b * L.M + m];
-            merged = mask[(size_t)b * L.M + m] != 0;
-        }
-    };
-
-    if (warp == 0) {
-        // ===== producer: one lane issues the bulk loads of every unit of this CTA =====
-        if (lane == 0) {
-            int k = 0;
-            for (int u = blockIdx.x; u < n_units; u += gridDim.x, ++k) {
-                const int stage = k % stages;
-                if (k >= stages && !bulk_wait(&empty[stage], ((k / stages) - 1) & 1, abort_flag, status)) break;
-                int b, r0, rows, dst;
-                bool merged;
-                decode(u, b, r0, rows, dst, merged);
-                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(cvta_smem(&full[stage])), "r"((uint32_t)rows * row_bytes) : "memory");
-                const uint8_t *frame = reinterpret_cast<const uint8_t *>(tokens) + (size_t)b * L.N * row_bytes;
-                uint8_t *dst_s = bulk_smem + (size_t)stage * stage_bytes;
-                int g = 0;
-                while (g < rows) {  // runs of consecutive source tokens travel as one copy
-                    const int t0 = L.src_token(r0 + g);
-                    int n = 1;
-                    while (g + n < rows && L.src_token(r0 + g + n) == t0 + n) ++n;
+    if (warp < kBulkLanes) {
+        // ===== producers: the 32 lanes decode 32 units at a time (their global loads overlap), then the units' bulk loads are
+        // issued in order; producer p owns the units k = p, p + 2, ... of this CTA =====
+        const int p = warp;
+        const int mine = my_units > p ? (my_units - p + kBulkLanes - 1) / kBulkLanes : 0;
+        bool ok = true;
+        for (int j0 = 0; j0 < mine && ok; j0 += 32) {
+            const int jj = j0 + lane;
+            int b = 0, r0 = 0, rows = 0, dst = 0, merged = 0;
+            if (jj < mine) {
+                const int u = blockIdx.x + (p + kBulkLanes * jj) * gridDim.x;
+                b = u / units_per_frame;
+                const int unit = u - b * units_per_frame;
+                const int base = offsets[b];
+                if (unit < prefix_units) {
+                    r0 = unit * G;
+                    rows = min(G, L.prefix - r0);
+                    dst = base + r0;
+                } else {
+                    const int m = unit - prefix_units;
+                    r0 = L.prefix + m * G;
+                    rows = G;
+                    dst = base + L.prefix + group_prefix[(size_t)b * L.M + m];
+                    merged = mask[(size_t)b * L.M + m] != 0;
+                }
+            }
+            const int n_here = min(32, mine - j0);
+            for (int i = 0; i < n_here && ok; ++i) {
+                const int k = p + kBulkLanes * (j0 + i), stage = k % stages;
+                const int ub = __shfl_sync(0xffffffffu, b, i), ur0 = __shfl_sync(0xffffffffu, r0, i);
+                const int urows = __shfl_sync(0xffffffffu, rows, i), udst = __shfl_sync(0xffffffffu, dst, i);
+                const int umerged = __shfl_sync(0xffffffffu, merged, i);
+                // Source token of every row of the unit, one row per lane (the index arithmetic divides several times), and
+                // the rows that start a run of consecutive tokens: a run travels as one copy, issued by the lane of its
+                // first row, so the copies of a unit are issued side by side.
+                const int tok = lane < urows ? L.src_token(ur0 + lane) : -1;
+                const int prev = __shfl_up_sync(0xffffffffu, tok, 1);
+                const bool is_start = lane < urows && (lane == 0 || tok != prev + 1);
+                const unsigned starts = __ballot_sync(0xffffffffu, is_start);
+                const unsigned above = lane < 31 ? (starts & ~((2u << lane) - 1u)) : 0u;
+                const int run_end = above != 0 ? __ffs(above) - 1 : urows;
+                if (lane == 0) {
+                    if (k >= stages) ok = bulk_wait(&empty[stage], ((k / stages) - 1) & 1, abort_flag, status);
+                    if (ok) {
+                        desc[stage] = BulkUnit{udst, urows, umerged, 0};  // ordered before the loads' completion by the arrive below
+                        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(cvta_smem(&full[stage])), "r"((uint32_t)urows * row_bytes) : "memory");
+                    }
+                }
+                ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;  // also orders the expect_tx in front of the copies below
+                if (ok && is_start) {
+                    const uint8_t *frame = reinterpret_cast<const uint8_t *>(tokens) + (size_t)ub * L.N * row_bytes;
+                    uint8_t *dst_s = bulk_smem + (size_t)stage * stage_bytes;
                     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                                 ::"r"(cvta_smem(dst_s + (size_t)g * row_bytes)), "l"(frame + (size_t)t0 * row_bytes),
-                                   "r"((uint32_t)n * row_bytes), "r"(cvta_smem(&full[stage])) : "memory");
-                    g += n;
+                                 ::"r"(cvta_smem(dst_s + (size_t)lane * row_bytes)), "l"(frame + (size_t)tok * row_bytes),
+                                   "r"((uint32_t)(run_end - lane) * row_bytes), "r"(cvta_smem(&full[stage])) : "memory");
                 }
             }
         }
-    } else if (warp == 1) {
-        // ===== store lane: units that are copied unchanged leave the ring by one bulk store =====
+    } else if (warp < 2 * kBulkLanes) {
+        // ===== store lanes: units that are copied unchanged leave the ring by one bulk store; store lane q owns the units
+        // k = q, q + 2, ... =====
         if (lane == 0) {
-            int k = 0, pending_stage = -1;
-            for (int u = blockIdx.x; u < n_units; u += gridDim.x, ++k) {
+            int pending_stage = -1;
+            for (int k = warp - kBulkLanes; k < my_units; k += kBulkLanes) {
                 const int stage = k % stages;
-                int b, r0, rows, dst;
-                bool merged;
-                decode(u, b, r0, rows, dst, merged);
-                if (merged) {  // the consumers' unit: nothing to store, release at once
+                // Every role waits for every unit's data before it releases the unit, also when the unit is not its own: a
+                // role that released units it does not use without waiting would run ahead, arrive for the stage's NEXT
+                // unit while the current one is still being read, and complete the phase early.
+                if (!bulk_wait(&full[stage], (k / stages) & 1, abort_flag, status)) break;
+                const BulkUnit d = desc[stage];
+                if (d.merged) {  // the consumers' unit: nothing to store
+                    if (pending_stage >= 0) {
+                        // no store follows at once: hand the last store's stage back now (the producer may need it soon)
+                        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(cvta_smem(&empty[pending_stage])) : "memory");
+                        pending_stage = -1;
+                    }
                     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(cvta_smem(&empty[stage])) : "memory");
                     continue;
                 }
-                if (!bulk_wait(&full[stage], (k / stages) & 1, abort_flag, status)) break;
                 asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
-                             ::"l"(reinterpret_cast<uint8_t *>(out) + (size_t)dst * row_bytes),
-                               "r"(cvta_smem(bulk_smem + (size_t)stage * stage_bytes)), "r"((uint32_t)rows * row_bytes) : "memory");
+                             ::"l"(reinterpret_cast<uint8_t *>(out) + (size_t)d.dst * row_bytes),
+                               "r"(cvta_smem(bulk_smem + (size_t)stage * stage_bytes)), "r"((uint32_t)d.rows * row_bytes) : "memory");
                 asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                 if (pending_stage >= 0) {  // the store before this one has read its stage: hand it back
                     asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
@@ -477,24 +511,21 @@ merge_bulk_kernel(const T *__restrict__ tokens, const uint8_t *__restrict__ mask
         }
     } else {
         // ===== consumers: window means =====
-        const int tid = threadIdx.x - 64;
+        const int tid = threadIdx.x - 2 * kBulkLanes * 32;
         const int64_t Cv = C / VEC;
         const float fG = (float)G;
-        int k = 0;
-        for (int u = blockIdx.x; u < n_units; u += gridDim.x, ++k) {
+        for (int k = 0; k < my_units; ++k) {
             const int stage = k % stages;
-            int b, r0, rows, dst;
-            bool merged;
-            decode(u, b, r0, rows, dst, merged);
-            if (merged) {
-                if (!bulk_wait(&full[stage], (k / stages) & 1, abort_flag, status)) break;
+            if (!bulk_wait(&full[stage], (k / stages) & 1, abort_flag, status)) break;  // see the store lane
+            const BulkUnit d = desc[stage];
+            if (d.merged) {
                 const V *src = reinterpret_cast<const V *>(bulk_smem + (size_t)stage * stage_bytes);
-                V *dst_row = reinterpret_cast<V *>(out) + (int64_t)dst * Cv;
+                V *dst_row = reinterpret_cast<V *>(out) + (int64_t)d.dst * Cv;
                 for (int64_t v = tid; v < Cv; v += kBulkConsumers) {
                     float acc[VEC];
 #pragma unroll
                     for (int i = 0; i < VEC; ++i) acc[i] = 0.0f;
-                    for (int g = 0; g < rows; ++g) {
+                    for (int g = 0; g < d.rows; ++g) {
                         float f[VEC];
                         IO::unpack(src[(int64_t)g * Cv + v], f);
 #pragma unroll
@@ -510,13 +541,12 @@ merge_bulk_kernel(const T *__restrict__ tokens, const uint8_t *__restrict__ mask
     }
 }
 
-
 // The bulk-ring kernel can be switched off (COME_MERGE_BULK=0 in the environment, read once) to compare the two merge
 // kernels; they produce the same bits.
 static bool bulk_disabled() {
     static const bool off = [] {
         const char *v = getenv("COME_MERGE_BULK");
-        return v == nullptr || v[0] != '1';  // opt-in until the GPU comparison has been recorded
+        return v != nullptr && v[0] == '0';
     }();
     return off;
 }
@@ -1004,11 +1034,18 @@ static int launch_merge(const void *tokens, int64_t frames, int64_t C, const Fra
         const size_t budget = 200 * 1024;
         int stages = stage_bytes ? (int)(budget / stage_bytes) : 0;
         if (stages > kBulkMaxStages) stages = kBulkMaxStages;
+        // A stage must always be filled by the same producer and drained by the same store lane (unit k belongs to lane
+        // k % kBulkLanes and sits in stage k % stages): a parity wait is only valid for a waiter that is at most one phase
+        // behind its barrier, and two lanes taking turns on a stage are not ordered against each other.
+        stages -= stages % kBulkLanes;
         const bool aligned = ((uintptr_t)tokens % 16 == 0) && ((uintptr_t)out % 16 == 0) && row_bytes % 16 == 0;
-        if (vec_ok && aligned && stages >= 4 && row_bytes >= 512 && !bulk_disabled()) {
+        // Few units per CTA (an 8-frame scene) with rows under 4 KB: the ring's fill and drain cost more than it returns
+        // (bfloat16, 8 frames: 11.9 us against 8.3 us of merge_kernel; 100 frames: 76.7 against 81.8 us; float32 wins at both).
+        const bool few_small = n_units < 16 * (int64_t)sm_count() && row_bytes < 4096;
+        if (vec_ok && aligned && stages >= 4 && row_bytes >= 512 && L.G <= 32 && !few_small && !bulk_disabled()) {
             unsigned int *status = status_word_dev();
             if (!status) return COME_ERR_CUDA;
-            const size_t smem_bulk = (size_t)stages * stage_bytes + (size_t)stages * 2 * sizeof(uint64_t) + 16;
+            const size_t smem_bulk = (size_t)stages * stage_bytes + (size_t)stages * (2 * sizeof(uint64_t) + sizeof(BulkUnit)) + 16;
             int rc = ensure_bulk_smem<T, VEC>(smem_bulk);
             if (rc != COME_OK) return rc;
             const int sms = sm_count();

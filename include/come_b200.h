@@ -242,6 +242,9 @@ int come_suffix_split(const void *tokens_dev, const float *weight_dev, const int
  *   max_seqlen    upper bound of the segment lengths (sizes the grid only)
  * head_dim 64 runs on the tcgen05 tensor-core kernel; other head dims (multiples of 8 up to 256) run on a
  * plain CUDA-core kernel.  `backend`: 0 = automatic, 1 = force the CUDA-core kernel, 2 = require tcgen05.
+ * k and v must be finite in the WHOLE packed buffer: the tensor-core kernel loads the partial last key tile of a segment
+ * together with the first rows of the next segment and masks them with probability 0, and 0 x Inf is NaN (rows past
+ * `total` are zero-filled by the hardware).
  */
 int come_attn_varlen_fwd(const void *q_dev, const void *k_dev, const void *v_dev, int dtype, int64_t total,
                          int num_heads, int head_dim, int64_t q_row_stride, int64_t k_row_stride,
