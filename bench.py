@@ -282,7 +282,7 @@ def run_frames(args):
     frames = FRAMES_BY_WORKLOAD[args.workload]
     pk = peaks()
     check = sharded_check(torch, dist, world, rank, dev) if world > 1 else None
-    overlap = world > 1 and (args.overlap == "on" or (args.overlap == "auto" and world >= 4))
+    overlap = world > 1 and args.overlap != "off"
     chain = ShardedOpChain(frames, None, START, GRID, GRID, WIN, WIN, 0.5, HEADS, HDIM, LAYERS, overlap=overlap)
     g = torch.Generator(device="cpu").manual_seed(4321)
     conf_host = torch.rand((1, frames * GRID * GRID), generator=g).bfloat16().pin_memory()  # replicated on every rank
@@ -328,14 +328,23 @@ def run_frames(args):
         sampler.start()
         time.sleep(0.3)
     barrier()  # the other ranks wait for rank 0's sampler here, not inside the first all-gather of the timed region
-    # ---- timed region 0 (-> `value`): inputs resident in HBM --------------------------------------------------------
+    # ---- timed region 0 (-> `value`, `roofline`, `split`): inputs resident in HBM; every kernel family of every layer is
+    # bracketed by CUDA events on the launching stream, and the all-gather by events on its side stream, in these same
+    # steps (a step is hundreds of milliseconds: the events cost nothing against it, and the split describes the very
+    # steps `value` is taken from) ----------------------------------------------------------------------------------
+    timers = []
+    if chain.exchange is not None:
+        chain.exchange.events = []
     s, e = ev(), ev()
     s.record()
     for _ in range(args.steps):
-        step(x, conf, q, kv)
+        step(x, conf, q, kv, timers)
     e.record()
     barrier()
     resident_ms = s.elapsed_time(e)
+    exch = list(chain.exchange.events) if chain.exchange is not None and chain.exchange.events else []
+    if chain.exchange is not None:
+        chain.exchange.events = None
     # ---- timed region 1 (-> `e2e`): the same step through the same public calls with HOST buffers: this rank's inputs are
     # copied from pinned host memory and its restored tokens are copied back, inside the timed region, every step ------
     h2d = (x_host.numel() + q_host.numel() + kv_host.numel() + conf_host.numel()) * 2
@@ -354,22 +363,13 @@ def run_frames(args):
     clocks = sampler.stop() if rank == 0 else None
     if _lib.device_status(clear=False) != 0:
         raise RuntimeError("attention kernel raised the device status word during the timed region")
-    # ---- instrumented steps (not part of `value`): CUDA events around every kernel family of every layer, and on the side
-    # stream around the all-gather -------------------------------------------------------------------------------------
-    timers = []
-    if chain.exchange is not None:
-        chain.exchange.events = []
-    n_inst = 2
-    for _ in range(n_inst):
-        step(x, conf, q, kv, timers)
-    barrier()
+    n_inst = args.steps
     fam = {"merge": 0.0, "frame_attn": 0.0, "global_attn": 0.0, "unmerge": 0.0}
     for kind, e4 in timers:
         fam["merge"] += e4[0].elapsed_time(e4[1]) / n_inst
         fam["frame_attn" if kind == "frame" else "global_attn"] += e4[1].elapsed_time(e4[2]) / n_inst
         fam["unmerge"] += e4[2].elapsed_time(e4[3]) / n_inst
     split = {f"{k}_ms": v for k, v in fam.items()}
-    exch = chain.exchange.events if chain.exchange is not None and chain.exchange.events else []
     if exch:
         gather_ms = [a.elapsed_time(b) for a, b, _, _ in exch]
         exposed = [max(0.0, c.elapsed_time(b)) for _, b, c, _ in exch]  # gather still running when the local attention ended
@@ -419,7 +419,7 @@ def run_frames(args):
                          "frac_of_burst_peak": achieved / pk["tflops"],
                          "per": "GPU (slowest rank)", "traffic": None,
                          "traffic_note": "the 100-frame launch is too long for an ncu capture; profiles/ holds the capture of the 6456-token launch (qkv read once)",
-                         "timing": "CUDA events around every attention call of 2 instrumented scenes (launches of 0.2 to 33 ms: host cost is hidden)",
+                         "timing": "CUDA events around every attention call of the timed steps themselves (launches of 0.2 to 33 ms: host cost is hidden)",
                          "frame_tflops": n_f * flops_frame / world / (split["frame_attn_ms"] * 1e-3) / 1e12,
                          "global_tflops": n_g * flops_global / world / (split["global_attn_ms"] * 1e-3) / 1e12,
                          "work_items_per_cta_global": items / 148.0,
@@ -1099,9 +1099,8 @@ def main():
                          "4-frame scenes with per-frame merge ratios ~U(0.25,0.75), sharded by scene, reported as scenes/s; model100: the "
                          "100-frame scene through the whole alternating-attention stack (with its GEMMs), sharded by frame")
     ap.add_argument("--overlap", default="auto", choices=["auto", "on", "off"],
-                    help="N > 1: hide the K/V all-gather of a global layer behind attention to the local keys (on), keep it in line "
-                         "(off), or decide by the world size (auto: on from 4 GPUs; with 2 the gather is 3 %% of a layer and the "
-                         "SMs left to it cost the local attention more than the overlap returns)")
+                    help="N > 1: hide the K/V all-gather of a global layer behind attention to the local keys (on, and auto), or keep "
+                         "it in line (off: the sharded result is then bit-identical to one GPU)")
     ap.add_argument("--no-scene8", action="store_true", help="skip the 8-frame scene (extra key scene8)")
     ap.add_argument("--no-micro", action="store_true", help="skip the kernel-level sweep")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
