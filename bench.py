@@ -417,8 +417,13 @@ def run_frames(args):
                          "frac": achieved / pk["tflops_sustained"],
                          "peak_source": pk["source"] + " cuBLAS bf16, sustained loop (steps of this workload keep the GPU at its power cap for seconds)",
                          "frac_of_burst_peak": achieved / pk["tflops"],
-                         "per": "GPU (slowest rank)", "traffic": None,
-                         "traffic_note": "the 100-frame launch is too long for an ncu capture; profiles/ holds the capture of the 6456-token launch (qkv read once)",
+                         "per": "GPU (slowest rank)",
+                         "traffic": 814.9e6 if (world == 1 and frames == 100) else None,
+                         "traffic_note": ("bytes per global-layer launch (80,672 merged tokens): dram__bytes_read.sum 658.3 MB + "
+                                          "dram__bytes_write.sum 156.6 MB from a one-pass ncu capture of that launch; algorithmic "
+                                          "660.9 MB = packed q / k / v once + output (the K / V re-reads of the 3376 work items are "
+                                          "served by L2)" if (world == 1 and frames == 100) else
+                                          "captured for the one-GPU 100-frame launch only (profiles/)"),
                          "timing": "CUDA events around every attention call of the timed steps themselves (launches of 0.2 to 33 ms: host cost is hidden)",
                          "frame_tflops": n_f * flops_frame / world / (split["frame_attn_ms"] * 1e-3) / 1e12,
                          "global_tflops": n_g * flops_global / world / (split["global_attn_ms"] * 1e-3) / 1e12,
