@@ -543,6 +543,14 @@ merge_bulk_kernel(const T *__restrict__ tokens, const uint8_t *__restrict__ mask
 
 // The bulk-ring kernel can be switched off (COME_MERGE_BULK=0 in the environment, read once) to compare the two merge
 // kernels; they produce the same bits.
+// COME_MERGE_LN_ROWS=0 in the environment keeps the thread-group LayerNorm + merge kernel for every row width (A/B runs).
+static bool ln_rows_disabled() {
+    static const bool off = [] {
+        const char *e = getenv("COME_MERGE_LN_ROWS");
+        return e != nullptr && e[0] == '0';
+    }();
+    return off;
+}
 static bool bulk_disabled() {
     static const bool off = [] {
         const char *v = getenv("COME_MERGE_BULK");
@@ -579,6 +587,7 @@ template <typename T, int VEC> static int ensure_bulk_smem(size_t smem) {
 // added; the threads' partial sums go through shared memory, where one warp per row adds, for every lane position, the
 // partials of the group's warps left to right and then runs a butterfly over the 32 lanes (neighbours first).  The
 // squares are accumulated with fused multiply-adds.  The same warp turns the totals into mean and 1/sqrt(var + eps).
+constexpr int kRowWarps = 8;   // warps per CTA of the warp-per-row kernels
 constexpr int kLnMaxRows = 9;  // rows per unit the fused kernel keeps in registers (3 x 3 windows)
 
 __device__ __forceinline__ void group_barrier(int groups, int grp, int tpg) {
@@ -656,7 +665,7 @@ merge_layernorm_kernel(const T *__restrict__ tokens, const uint8_t *__restrict__
     extern __shared__ int s_ln_raw[];
     const int G = L.G;
     const int tpg = TPG > 0 ? TPG : kMergeThreads / groups, warps_pg = tpg / 32;
-    if (TPG > 0) groups = kMergeThreads / TPG;
+    if constexpr (TPG > 0) groups = kMergeThreads / TPG;
     const int grp = threadIdx.x / tpg, tig = threadIdx.x - grp * tpg;
     const int wig = tig >> 5, lane = tig & 31;
     // shared memory: [groups][G] source tokens | [groups][kLnMaxRows][tpg] partial sums | [groups][kLnMaxRows] row statistic
@@ -802,6 +811,164 @@ merge_layernorm_kernel(const T *__restrict__ tokens, const uint8_t *__restrict__
     }
 }
 
+// The same operation with one WARP per unit: lane l holds the 16-byte vectors l, l + 32, ... of a row (NV of them), the
+// unit's rows are taken one after the other (the next row's loads are issued before the current row's arithmetic), the
+// statistics need shuffles only and no barrier is met inside the loop.  gamma and beta sit in shared memory as float32,
+// laid out so that a lane's 16-byte reads are conflict-free.  Summation order = the thread-group kernel's with "vector j
+// of lane l" in the place of "warp j of the group" (the order residual_layernorm_kernel uses as well), so both kernels
+// and the CPU oracle agree bit for bit.  FULL: the row fills its NV x 32 vectors exactly (no column guards).  A row
+// length that is a power of two divides the sums by multiplying with its exact reciprocal (the same float32 result).
+// Used for rows of at least 32 vectors; the thread-group kernel keeps the narrow rows.
+template <typename T, int VEC, int NV, bool FULL>
+__global__ void __launch_bounds__(kRowWarps * 32, (NV * VEC > 32) ? 1 : 2)  // 64 channels per lane need the whole register file
+merge_layernorm_rows_kernel(const T *__restrict__ tokens, const uint8_t *__restrict__ mask, const int *__restrict__ group_prefix,
+                            const int *__restrict__ offsets, FrameLayout L, int frames, int Cv, const T *__restrict__ gamma,
+                            const T *__restrict__ beta, float eps, T *__restrict__ out) {
+    using PIO = PairIO<T, VEC>;
+    using V = typename VecIO<T, VEC>::V;
+    constexpr int NP = VEC / 2;       // float32 pairs per vector
+    constexpr int NQ = (NP + 1) / 2;  // 16-byte chunks of float32 pairs per vector
+    // [gamma | beta][vector j of the lane][chunk q][lane] -> 16 bytes = the pairs 2q, 2q + 1 of that vector
+    __shared__ __align__(16) f32x2_t s_gb[2][NV][NQ][32][2];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int i = threadIdx.x; i < NV * 32; i += kRowWarps * 32) {
+        const int j = i >> 5, l = i & 31;
+        f32x2_t g2[NP], b2[NP];
+#pragma unroll
+        for (int k = 0; k < NP; ++k) g2[k] = b2[k] = 0ull;
+        if (FULL || i < Cv) {
+            PIO::unpack(reinterpret_cast<const V *>(gamma)[i], g2);
+            PIO::unpack(reinterpret_cast<const V *>(beta)[i], b2);
+        }
+#pragma unroll
+        for (int k = 0; k < NP; ++k) {
+            s_gb[0][j][k >> 1][l][k & 1] = g2[k];
+            s_gb[1][j][k >> 1][l][k & 1] = b2[k];
+        }
+    }
+    __syncthreads();
+    const int G = L.G;
+    const int prefix_units = (L.prefix + G - 1) / G;
+    const int units_per_frame = prefix_units + L.M;
+    const int n_units = frames * units_per_frame;
+    const int C = Cv * VEC;
+    const float fC = (float)C, fG = (float)G;
+    const bool pow2 = (C & (C - 1)) == 0;
+    const float inv_c = 1.0f / fC;  // exact when C is a power of two
+    auto over_c = [&](float t) { return pow2 ? __fmul_rn(t, inv_c) : __fdiv_rn(t, fC); };
+    auto has = [&](int j) { return FULL || j * 32 + lane < Cv; };
+
+    for (int u = blockIdx.x * kRowWarps + warp; u < n_units; u += gridDim.x * kRowWarps) {
+        const int bfr = u / units_per_frame, unit = u - bfr * units_per_frame;
+        const int base = offsets[bfr];
+        int r0, rows, dst;
+        bool merged = false;
+        if (unit < prefix_units) {
+            r0 = unit * G;
+            rows = min(G, L.prefix - r0);
+            dst = base + r0;
+        } else {
+            const int m = unit - prefix_units;
+            r0 = L.prefix + m * G;
+            rows = G;
+            dst = base + L.prefix + group_prefix[(size_t)bfr * L.M + m];
+            merged = mask[(size_t)bfr * L.M + m] != 0;
+        }
+        const int my_src = lane < rows ? L.src_token(r0 + lane) : 0;  // lane r knows where row r of the unit lives
+        const V *src_base = reinterpret_cast<const V *>(tokens) + (int64_t)bfr * L.N * Cv;
+        V *dst_base = reinterpret_cast<V *>(out) + (int64_t)dst * Cv;
+        auto load_row = [&](int r, V (&raw)[NV]) {
+            const V *row = src_base + (int64_t)__shfl_sync(0xffffffffu, my_src, r) * Cv;
+#pragma unroll
+            for (int j = 0; j < NV; ++j)
+                if (has(j)) raw[j] = ld_stream(row + j * 32 + lane);
+        };
+        V raw[NV];
+        load_row(0, raw);
+        f32x2_t acc[NV][NP];
+#pragma unroll
+        for (int j = 0; j < NV; ++j)
+#pragma unroll
+            for (int k = 0; k < NP; ++k) acc[j][k] = 0ull;
+        for (int r = 0; r < rows; ++r) {
+            f32x2_t d[NV][NP];
+            float total = 0.0f;
+#pragma unroll
+            for (int j = 0; j < NV; ++j) {
+                float part = 0.0f;
+                if (has(j)) {
+                    PIO::unpack(raw[j], d[j]);
+                    f32x2_t a = d[j][0];
+#pragma unroll
+                    for (int k = 1; k < NP; ++k) a = add_f32x2(a, d[j][k]);
+                    float even, odd;
+                    unpack_f32x2(a, even, odd);
+                    part = __fadd_rn(even, odd);
+                }
+                total = (j == 0) ? part : __fadd_rn(total, part);
+            }
+            if (r + 1 < rows) load_row(r + 1, raw);  // the next row is on its way while this one is normalised
+#pragma unroll
+            for (int m = 1; m < 32; m <<= 1) total = __fadd_rn(total, __shfl_xor_sync(0xffffffffu, total, m));
+            const float mean = over_c(total);
+            const f32x2_t neg_mean = pack_f32x2(-mean, -mean);
+#pragma unroll
+            for (int j = 0; j < NV; ++j) {
+                float part = 0.0f;
+                if (has(j)) {
+#pragma unroll
+                    for (int k = 0; k < NP; ++k) d[j][k] = add_f32x2(d[j][k], neg_mean);
+                    f32x2_t a = mul_f32x2(d[j][0], d[j][0]);
+#pragma unroll
+                    for (int k = 1; k < NP; ++k) a = fma_f32x2(d[j][k], d[j][k], a);  // explicit: never a separate mul + add
+                    float even, odd;
+                    unpack_f32x2(a, even, odd);
+                    part = __fadd_rn(even, odd);
+                }
+                total = (j == 0) ? part : __fadd_rn(total, part);
+            }
+#pragma unroll
+            for (int m = 1; m < 32; m <<= 1) total = __fadd_rn(total, __shfl_xor_sync(0xffffffffu, total, m));
+            const float rstd = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(over_c(total), eps)));
+            const f32x2_t rstd2 = pack_f32x2(rstd, rstd);
+#pragma unroll
+            for (int j = 0; j < NV; ++j) {
+                if (has(j)) {
+                    const int v = j * 32 + lane;
+#pragma unroll
+                    for (int q = 0; q < NQ; ++q) {
+                        const ulonglong2 g = *reinterpret_cast<const ulonglong2 *>(&s_gb[0][j][q][lane][0]);
+                        const ulonglong2 b = *reinterpret_cast<const ulonglong2 *>(&s_gb[1][j][q][lane][0]);
+                        d[j][2 * q] = fma_f32x2(g.x, mul_f32x2(rstd2, d[j][2 * q]), b.x);
+                        if (2 * q + 1 < NP) d[j][2 * q + 1] = fma_f32x2(g.y, mul_f32x2(rstd2, d[j][2 * q + 1]), b.y);
+                    }
+                    if (merged) {
+                        // the normalised tensor lives in T: its rounded values are what the window mean sums
+#pragma unroll
+                        for (int k = 0; k < NP; ++k) acc[j][k] = add_f32x2(acc[j][k], PIO::round_pair(d[j][k]));
+                    } else {
+                        st_stream(dst_base + (int64_t)r * Cv + v, PIO::pack(d[j]));
+                    }
+                }
+            }
+        }
+        if (merged) {
+#pragma unroll
+            for (int j = 0; j < NV; ++j) {
+                if (has(j)) {
+#pragma unroll
+                    for (int k = 0; k < NP; ++k) {
+                        float lo, hi;
+                        unpack_f32x2(acc[j][k], lo, hi);
+                        acc[j][k] = pack_f32x2(__fdiv_rn(lo, fG), __fdiv_rn(hi, fG));
+                    }
+                    st_stream(dst_base + j * 32 + lane, PIO::pack(acc[j]));
+                }
+            }
+        }
+    }
+}
+
 template <typename T>
 static int launch_merge_layernorm(const void *tokens, int64_t frames, int64_t C, const FrameLayout &L, const uint8_t *mask,
                                   const int32_t *gp, const int32_t *off, const void *gamma, const void *beta, float eps,
@@ -820,6 +987,26 @@ static int launch_merge_layernorm(const void *tokens, int64_t frames, int64_t C,
     const int prefix_units = (L.prefix + L.G - 1) / L.G;
     const int64_t n_units = frames * (int64_t)(prefix_units + L.M);
     if (n_units == 0) return COME_OK;
+    if (Cv >= 32 && !ln_rows_disabled()) {  // a warp per unit: no barriers, the next row's loads behind the current row's arithmetic
+        int64_t blocks = (n_units + kRowWarps - 1) / kRowWarps;
+        const int64_t cap = (int64_t)sm_count() * 8;
+        if (blocks > cap) blocks = cap;
+#define COME_LNR_LAUNCH(NV)                                                                                             \
+    do {                                                                                                                \
+        if (Cv == 32 * (NV))                                                                                            \
+            merge_layernorm_rows_kernel<T, VEC, NV, true><<<(unsigned)blocks, kRowWarps * 32, 0, st>>>(                 \
+                (const T *)tokens, mask, gp, off, L, (int)frames, Cv, (const T *)gamma, (const T *)beta, eps, (T *)out); \
+        else                                                                                                            \
+            merge_layernorm_rows_kernel<T, VEC, NV, false><<<(unsigned)blocks, kRowWarps * 32, 0, st>>>(                \
+                (const T *)tokens, mask, gp, off, L, (int)frames, Cv, (const T *)gamma, (const T *)beta, eps, (T *)out); \
+    } while (0)
+        if (Cv <= 32) COME_LNR_LAUNCH(1);
+        else if (Cv <= 64) COME_LNR_LAUNCH(2);
+        else if (Cv <= 128) COME_LNR_LAUNCH(4);
+        else COME_LNR_LAUNCH(8);
+#undef COME_LNR_LAUNCH
+        return check_launch("come_merge_layernorm");
+    }
     const size_t smem = (size_t)groups * L.G * sizeof(int) + (size_t)groups * kLnMaxRows * (tpg + 1) * sizeof(float);
     const int64_t n_ctas = (n_units + groups - 1) / groups;
     const int64_t max_blocks = (int64_t)sm_count() * 8;
@@ -1242,7 +1429,6 @@ extern "C" int come_unmerge_residual(const void *merged_dev, const int64_t *rev_
 // once, statistics need shuffles only and no barrier is met.  Summation order of the statistics = the fused LayerNorm +
 // merge kernel's with "vector j of lane l" in the place of "warp j of the thread group": inside a vector the even / odd
 // chains, vectors of a lane left to right, then a butterfly over the lanes (neighbours first).
-constexpr int kRowWarps = 8;
 
 template <typename T, int VEC, int NV>
 __global__ void __launch_bounds__(kRowWarps * 32, NV >= 8 ? 1 : (NV >= 4 ? 2 : 3))  // a row's float32 copy stays in registers
