@@ -210,13 +210,14 @@ def run_reference(args):
 COMM_SMS = 16  # SMs left to the all-gather kernel while attention to the local keys runs beside it
 
 
-def init_ranks():
+def init_ranks(cap_nccl_ctas=False):
     import torch
     import torch.distributed as dist
-    # An all-gather that runs beside the persistent attention kernel completes only when ALL its CTAs have run: keep their
-    # number within the SMs the attention launch leaves free (GlobalExchange.comm_sms), or the last ones wait for the
-    # attention kernel to end and nothing overlaps.
-    os.environ.setdefault("NCCL_MAX_CTAS", str(COMM_SMS))
+    if cap_nccl_ctas:
+        # An all-gather that runs beside the persistent attention kernel completes only when ALL its CTAs have run: keep
+        # their number within the SMs the attention launch leaves free (GlobalExchange.comm_sms), or the last ones wait for
+        # the attention kernel to end and nothing overlaps.
+        os.environ.setdefault("NCCL_MAX_CTAS", str(COMM_SMS))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -228,7 +229,7 @@ def init_ranks():
     return torch, dist, world, rank, local, dev
 
 
-def sharded_check(torch, dist, world, rank, dev):
+def sharded_check(torch, dist, world, rank, dev, transport="nccl", hidden=True):
     """Before anything is timed at N > 1: a small scene (one frame layer + one global layer) run sharded over the ranks
     and unsharded on every rank.  With the exchange in line the sharded frames must equal the unsharded ones bit for bit;
     with the exchange hidden behind attention to the local keys the global layer may differ by the rounding of the two
@@ -248,8 +249,8 @@ def sharded_check(torch, dist, world, rank, dev):
     want = [whole.layer(gp, lp, x, q[:P].contiguous(), kv[:P].contiguous(), k) for k in kinds]
     res = {"rows": P, "frames": frames}
     ok = True
-    for overlap in (False, True):
-        chain = ShardedOpChain(frames, None, START, GRID, GRID, WIN, WIN, 0.5, H, D, kinds, overlap=overlap)
+    for overlap in ((False, True) if hidden else (False,)):  # the hidden exchange is checked where the timed run uses it
+        chain = ShardedOpChain(frames, None, START, GRID, GRID, WIN, WIN, 0.5, H, D, kinds, overlap=overlap, transport=transport)
         gp, lp = chain.build_plans(conf)
         r0, r1 = chain.row_begin, chain.row_begin + lp.total
         diffs = []
@@ -261,7 +262,11 @@ def sharded_check(torch, dist, world, rank, dev):
         worst = t.tolist()
         if overlap:
             res["overlapped_max_abs_diff"] = {"frame": worst[0], "global": worst[1], "bar_global": 2e-2}
+            res["overlapped_transport"] = chain.exchange.transport
             ok = ok and worst[0] == 0.0 and worst[1] <= 2e-2
+            torch.cuda.synchronize()
+            dist.barrier()  # every rank has finished its pulls before anyone releases its window
+            chain.exchange.close()
         else:
             res["in_line_bit_exact"] = worst[0] == 0.0 and worst[1] == 0.0
             ok = ok and res["in_line_bit_exact"]
@@ -276,14 +281,21 @@ def run_frames(args):
     layers are local; a global layer all-gathers the merged K/V rows over NCCL on a side stream while the local query rows
     attend to the local keys, then attends them to the gathered rows and merges the two results (strong scaling: the
     scene is fixed, more GPUs shorten it).  At N = 1 there is no exchange and the global layer is one launch."""
-    torch, dist, world, rank, local, dev = init_ranks()
+    from come_b200.dist import hiding_exchange_pays
+    frames = FRAMES_BY_WORKLOAD[args.workload]
+    world_env = int(os.environ.get("WORLD_SIZE", "1"))
+    # auto: hide the exchange where the model of a global layer says it pays (2 to 4 GPUs for the 100-frame scene; on 8 the
+    # attention to the local keys is too short to cover an exchange that runs four times slower beside it)
+    rows_est = frames * (START + GRID * GRID - (GRID // WIN) ** 2 // 2 * (WIN * WIN - 1))  # half of the windows merged: 798 per frame
+    overlap = world_env > 1 and (args.overlap == "on" or (args.overlap == "auto" and
+                                                         hiding_exchange_pays(rows_est, world_env, 2 * HEADS * HDIM * 2, HEADS, HDIM)))
+    torch, dist, world, rank, local, dev = init_ranks(cap_nccl_ctas=overlap and args.transport == "nccl")
     from come_b200 import _lib
     from come_b200.chain import ShardedOpChain
-    frames = FRAMES_BY_WORKLOAD[args.workload]
     pk = peaks()
-    check = sharded_check(torch, dist, world, rank, dev) if world > 1 else None
-    overlap = world > 1 and args.overlap != "off"
-    chain = ShardedOpChain(frames, None, START, GRID, GRID, WIN, WIN, 0.5, HEADS, HDIM, LAYERS, overlap=overlap)
+    check = sharded_check(torch, dist, world, rank, dev, args.transport, hidden=overlap) if world > 1 else None
+    chain = ShardedOpChain(frames, None, START, GRID, GRID, WIN, WIN, 0.5, HEADS, HDIM, LAYERS, overlap=overlap,
+                           transport=args.transport)
     g = torch.Generator(device="cpu").manual_seed(4321)
     conf_host = torch.rand((1, frames * GRID * GRID), generator=g).bfloat16().pin_memory()  # replicated on every rank
     conf = conf_host.to(dev)
@@ -384,6 +396,10 @@ def run_frames(args):
     resident_ms, e2e_ms = vals[0].item(), vals[1].item()
     split = {k: vals[2 + i].item() for i, k in enumerate(sorted(split))}  # max over ranks of every entry
     split["rows_per_rank"] = [int(-rows_t[1].item()), int(rows_t[0].item())]
+    if exch:
+        split["exchange_transport"] = chain.exchange.transport
+        if chain.exchange.peer_error:
+            split["exchange_fallback_reason"] = chain.exchange.peer_error
 
     if rank == 0:
         per_scene = resident_ms / args.steps
@@ -404,9 +420,12 @@ def run_frames(args):
             "warmup": max(args.warmup, 3), "ms_per_step": per_scene, "higher_is_better": False, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic (seeded)",
             "config": {"workload": workload_name(frames), "merged_tokens": P, "frames_per_s": frames / per_scene * 1e3,
+                       "exchange": ("none" if world == 1 else ("hidden behind attention to the local keys" if chain.overlap else "in line")),
                        "parallelism": ("one GPU: the whole scene, no exchange" if world == 1 else
                                        f"frames sharded over {world} GPUs; frame layers local; a global layer all-gathers "
-                                       f"{kv_bytes / 1e6:.0f} MB of merged K/V over NCCL"
+                                       f"{kv_bytes / 1e6:.0f} MB of merged K/V "
+                                       + ("with copy-engine transfers out of peer-mapped windows" if (chain.overlap and chain.exchange.transport == "peer")
+                                          else "over NCCL")
                                        + (" on a side stream while the local query rows attend to the local keys, then attends "
                                           "them to the gathered rows and merges the two results from their log-sum-exps"
                                           if chain.overlap else " in line, then attends the local query rows to all keys")),
@@ -438,7 +457,7 @@ def run_frames(args):
             "split": split,
             "e2e": {"value": e2e_ms / args.steps, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "note": "per rank: its frames, its q / k / v rows and the replicated confidences in, its restored tokens out"},
-            "gpu_launches": (5 + n_f * 3 + n_g * (5 if (chain.overlap and world > 1) else 3)) * args.steps,
+            "gpu_launches": (5 + n_f * 3 + n_g * ((7 if chain.exchange.transport == "peer" else 5) if (chain.overlap and world > 1) else 3)) * args.steps,
             "clocks": clocks,
         }
         if check is not None:
@@ -1103,9 +1122,12 @@ def main():
                          "all-gathered K/V; frames8: the same for an 8-frame scene (quick runs); batch256x4: 256 independent "
                          "4-frame scenes with per-frame merge ratios ~U(0.25,0.75), sharded by scene, reported as scenes/s; model100: the "
                          "100-frame scene through the whole alternating-attention stack (with its GEMMs), sharded by frame")
+    ap.add_argument("--transport", default="peer", choices=["peer", "nccl"],
+                    help="transport of the hidden K/V exchange at N > 1: copy engines over peer-mapped windows, or an NCCL all-gather")
     ap.add_argument("--overlap", default="auto", choices=["auto", "on", "off"],
-                    help="N > 1: hide the K/V all-gather of a global layer behind attention to the local keys (on, and auto), or keep "
-                         "it in line (off: the sharded result is then bit-identical to one GPU)")
+                    help="N > 1: hide the K/V all-gather of a global layer behind attention to the local keys (on), keep it in line "
+                         "(off: the sharded result is then bit-identical to one GPU), or decide from a model of the layer (auto: "
+                         "hidden on 2 to 4 GPUs, in line on 8 for the 100-frame scene)")
     ap.add_argument("--no-scene8", action="store_true", help="skip the 8-frame scene (extra key scene8)")
     ap.add_argument("--no-micro", action="store_true", help="skip the kernel-level sweep")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")

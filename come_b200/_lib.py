@@ -21,7 +21,9 @@ EXPORTS = (
     "come_unmerge_strided", "come_unmerge_residual", "come_residual_layernorm", "come_suffix_add", "come_suffix_split",
     "come_attn_varlen_fwd", "come_attn_varlen_fwd_rows", "come_attn_cross_fwd", "come_attn_combine", "come_attn_set_cta_limit", "come_qkv_prepare", "come_packed_positions",
     "come_device_status", "come_selftest_bounded_wait",
+    "come_peer_alloc", "come_peer_open", "come_peer_close", "come_peer_free", "come_peer_copy", "come_peer_signal", "come_peer_wait",
 )
+COME_PEER_HANDLE_BYTES = 64
 
 
 class Layout(C.Structure):
@@ -80,6 +82,13 @@ def lib() -> C.CDLL:
     l.come_packed_positions.argtypes = [vp, vp, i64, C.POINTER(Layout), vp, vp]
     l.come_device_status.argtypes = [C.POINTER(C.c_uint32), i32]
     l.come_selftest_bounded_wait.argtypes = [i64, vp, vp]
+    l.come_peer_alloc.argtypes = [i64, C.POINTER(vp), vp]
+    l.come_peer_open.argtypes = [vp, C.POINTER(vp)]
+    l.come_peer_close.argtypes = [vp]
+    l.come_peer_free.argtypes = [vp]
+    l.come_peer_copy.argtypes = [vp, vp, i64, vp]
+    l.come_peer_signal.argtypes = [vp, i32, i32, i32, vp]
+    l.come_peer_wait.argtypes = [vp, i32, i32, i32, i64, vp]
     for name in EXPORTS:
         fn = getattr(l, name)
         if name not in ("come_last_error", "come_merge_plan_workspace_bytes"):

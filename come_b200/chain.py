@@ -83,11 +83,12 @@ class ShardedOpChain:
     def __init__(self, frames_total: int, group=None, start_index: int = 5, grid_h: int = 37, grid_w: int = 37,
                  group_h: int = 3, group_w: int = 3, threshold: float = 0.5, num_heads: int = 16, head_dim: int = 64,
                  layer_kinds: Optional[Sequence[str]] = None, overlap: bool = False, world: Optional[int] = None,
-                 rank: Optional[int] = None):
+                 rank: Optional[int] = None, transport: str = "nccl"):
         """``overlap``: hide the key / value exchange of a global layer behind attention to the local keys
         (:class:`come_b200.dist.GlobalExchange`); the result then differs from the single-GPU one by the rounding of two
-        partial outputs.  Off: bit-identical to the single-GPU chain.  ``world`` / ``rank`` default to the process
-        group's; ``world=1`` runs the whole scene on this GPU whatever the group is."""
+        partial outputs.  Off: bit-identical to the single-GPU chain.  ``transport`` of the hidden exchange: ``"nccl"`` or
+        ``"peer"`` (copy engines over peer-mapped windows, :class:`come_b200.dist.PeerGather`).  ``world`` / ``rank`` default
+        to the process group's; ``world=1`` runs the whole scene on this GPU whatever the group is."""
         import torch.distributed as dist
 
         from .dist import shard_range
@@ -103,6 +104,7 @@ class ShardedOpChain:
         self.scale = head_dim ** -0.5
         self.layer_kinds = list(layer_kinds) if layer_kinds is not None else ["frame", "global"] * 24
         self.overlap = bool(overlap)
+        self.transport = transport
         self.exchange = None
 
     def build_plans(self, confidence_all: torch.Tensor):
@@ -119,9 +121,11 @@ class ShardedOpChain:
         self.cu_global = torch.tensor([0, global_plan.total], dtype=torch.int32, device=mask_all.device)
         from .dist import GlobalExchange
         keep = self.exchange
-        self.exchange = GlobalExchange(self.rows, self.rank, global_plan.weight, self.group, overlap=self.overlap)
-        if keep is not None and keep.rows == self.exchange.rows:  # same packing: keep the side stream and the gather buffer
+        self.exchange = GlobalExchange(self.rows, self.rank, global_plan.weight, self.group, overlap=self.overlap,
+                                       transport=self.transport)
+        if keep is not None and keep.rows == self.exchange.rows:  # same packing: keep the side stream, the gather buffer and the windows
             self.exchange._side, self.exchange._buf, self.exchange.events = keep._side, keep._buf, keep.events
+            self.exchange._peer_gather, self.exchange.transport, self.exchange.peer_error = keep._peer_gather, keep.transport, keep.peer_error
             if keep._side is not None:
                 self.exchange._cu_local = keep._cu_local
         return global_plan, local_plan

@@ -1722,8 +1722,10 @@ extern "C" int come_device_status(uint32_t *value, int clear) {
     *value = v;
     if (clear && v != 0) COME_CUDA(cudaMemset(word, 0, sizeof(v)));
     if (v != 0) {
-        come::set_error("device status word 0x%08x: %s%s%s", v, (v & 0x1ffu) ? "a bounded wait of the attention kernel ran out; " : "",
-                        (v & 0x8000u) ? "the wait self-test ran; " : "", (v & 0x10000u) ? "a position outside the rotary table was clamped; " : "");
+        come::set_error("device status word 0x%08x: %s%s%s%s%s", v, (v & 0x1ffu) ? "a bounded wait of the attention kernel ran out; " : "",
+                        (v & 0x8000u) ? "the wait self-test ran; " : "", (v & 0x10000u) ? "a position outside the rotary table was clamped; " : "",
+                        (v & 0x20000u) ? "a bounded wait of the bulk-copy merge kernel ran out; " : "",
+                        (v & 0x40000u) ? "a wait for the other ranks' key / value rows ran out (come_peer_wait); " : "");
         return COME_ERR_DEVICE;
     }
     return COME_OK;

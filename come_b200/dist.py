@@ -4,6 +4,9 @@ The path shards naturally by frame: selection, merge, frame attention and unmerg
 frame.  Only global attention has an exchange step: every rank attends ITS packed rows to the keys / values of ALL
 ranks, so the merged K/V rows (and nothing else) are all-gathered once per global layer.  The gathered rows land in
 this GPU's own memory and are read from there by the attention kernel.
+
+Two transports: NCCL (:func:`gather_rows`) and, for the exchange that is hidden behind attention to the local keys,
+driver copies out of peer-mapped windows (:class:`PeerGather`), which leave the attention kernel all but two SMs.
 """
 from __future__ import annotations
 
@@ -12,7 +15,7 @@ from typing import List, Optional, Sequence, Tuple
 import torch
 import torch.distributed as dist
 
-__all__ = ["shard_range", "rows_per_rank", "gather_rows", "block_order", "GlobalExchange"]
+__all__ = ["shard_range", "rows_per_rank", "gather_rows", "block_order", "hiding_exchange_pays", "PeerGather", "GlobalExchange"]
 
 
 def shard_range(n_items: int, world: int, rank: int) -> Tuple[int, int]:
@@ -34,6 +37,30 @@ def rows_per_rank(frame_offsets: Sequence[int], world: int) -> List[int]:
         lo, hi = shard_range(frames, world, r)
         out.append(int(frame_offsets[hi]) - int(frame_offsets[lo]))
     return out
+
+
+def hiding_exchange_pays(total_rows: int, world: int, row_bytes: int, num_heads: int, head_dim: int,
+                         attn_tflops: float = 780.0, exchange_gbs: float = 380.0, exchange_hidden_gbs: float = 110.0) -> bool:
+    """Whether a global layer is shorter with its key / value exchange hidden behind attention to the local keys than with
+    the exchange in line, from a two-line model of the layer on one rank:
+
+    * in line:  ``bytes_in / exchange_gbs  +  attention(rows/world queries x all keys)``
+    * hidden:   ``max(attention(local queries x local keys), bytes_in / exchange_hidden_gbs)  +  attention(local queries x
+      remote keys)``
+
+    The defaults are what B200 nodes measured: the attention kernel sustains ~780 TFLOP/s; an exchange that has the GPU to
+    itself moves 360-470 GB/s into every GPU (NCCL or peer copies alike), one that runs beside the attention kernel
+    60-120 GB/s.  With 80,672 rows of 4 KB the model gives 8.9 against 8.6 ms per layer on 4 GPUs (measured 8.97 and 8.66):
+    hidden pays on 2 to 4 GPUs, where the attention to the local keys outlasts the slowed exchange; in line pays from 5 GPUs
+    on (on 8, 0.5 ms of local attention cannot cover a 2.6 ms exchange: 4.9 against 6.2 ms)."""
+    if world <= 1:
+        return False
+    local_rows = total_rows / world
+    bytes_in = (total_rows - local_rows) * row_bytes
+    t_attn = lambda q, k: 4.0 * q * k * head_dim * num_heads / (attn_tflops * 1e12)  # noqa: E731
+    in_line = bytes_in / (exchange_gbs * 1e9) + t_attn(local_rows, total_rows)
+    hidden = max(t_attn(local_rows, local_rows), bytes_in / (exchange_hidden_gbs * 1e9)) + t_attn(local_rows, total_rows - local_rows)
+    return hidden < in_line
 
 
 def gather_rows(local: torch.Tensor, rows: Sequence[int], group: Optional[dist.ProcessGroup] = None,
@@ -93,6 +120,155 @@ def block_order(world: int, rank: int, remote_first: bool) -> List[int]:
     return [(rank + 1 + i) % world for i in range(world)]
 
 
+class PeerGather:
+    """All-gather of row blocks of different heights through peer-mapped windows of one node (one process per GPU).
+
+    Every rank owns a window (two slots of ``max(rows)`` rows + one flag word per rank) that the other ranks map through a
+    CUDA IPC handle (``come_peer_alloc`` / ``come_peer_open``).  One exchange: :meth:`stage` copies the local block into
+    the own window; :meth:`exchange` tells the peers (``come_peer_signal``), waits until all of them have told us
+    (``come_peer_wait``: bounded, raises bit 18 of the device status word instead of hanging), then pulls the peers'
+    blocks with ``come_peer_copy`` (plain ``cudaMemcpyAsync`` calls on a few side streams).  Apart from the two one-CTA
+    kernels nothing of it occupies an SM, so a persistent attention kernel on the same GPU keeps all but two SMs (an NCCL
+    all-gather beside it needs its CTAs resident: 16 SMs in this package's set-up).  Measured on B200s: alone an exchange
+    moves 360-470 GB/s into every GPU; beside the attention kernel 60-120 GB/s (NCCL, these copies and a copy kernel of
+    this library on 4 to 16 SMs were all slowed alike), which is why hiding the exchange pays only while the attention to
+    the local keys is long enough (:func:`hiding_exchange_pays`).  Construction is collective over ``group`` (the handles
+    travel through ``all_gather_object``).  Two slots suffice: a rank that signals exchange k + 1 has finished its pulls
+    of exchange k.
+    """
+
+    def __init__(self, rows: Sequence[int], rank: int, row_bytes: int, device: torch.device,
+                 group: Optional[dist.ProcessGroup] = None, pull_streams: int = 2, wait_limit_s: float = 20.0):
+        import ctypes as C
+
+        from . import _lib
+        self._lib, self._C = _lib, C
+        lib = _lib.lib()
+        self.rows = [int(n) for n in rows]
+        self.world, self.rank = len(self.rows), int(rank)
+        self.row_bytes = int(row_bytes)
+        self.device = torch.device(device)
+        self.slot_bytes = -(-max(self.rows) * self.row_bytes // 256) * 256
+        self.flag_offset = 2 * self.slot_bytes
+        self.limit_ns = int(wait_limit_s * 1e9)
+        self.seq = 0
+        self._staged = None
+        self._own = None
+        self._peer = [None] * self.world
+        self.error = None  # why the transport could not be built (on this or another rank)
+        # Every rank runs every collective of the set-up whatever happened to it before, so that a failure on one rank
+        # cannot leave the others waiting; the ranks agree on the outcome at the end.
+        handle_bytes = None
+        with torch.cuda.device(self.device):
+            try:
+                own = C.c_void_p()
+                handle = (C.c_char * _lib.COME_PEER_HANDLE_BYTES)()
+                _lib.check(lib.come_peer_alloc(self.flag_offset + 256, C.byref(own), handle))
+                self._own = own.value
+                handle_bytes = bytes(handle.raw)
+            except Exception as e:  # noqa: BLE001
+                self.error = repr(e)
+            handles = [None] * self.world
+            dist.all_gather_object(handles, handle_bytes, group=group)
+            if self.error is None and any(h is None for h in handles):
+                self.error = "another rank could not allocate its window"
+            if self.error is None:
+                try:
+                    for p in range(self.world):
+                        if p == self.rank:
+                            self._peer[p] = self._own
+                            continue
+                        ptr = C.c_void_p()
+                        _lib.check(lib.come_peer_open(C.create_string_buffer(handles[p], _lib.COME_PEER_HANDLE_BYTES), C.byref(ptr)))
+                        self._peer[p] = ptr.value
+                except Exception as e:  # noqa: BLE001
+                    self.error = repr(e)
+            ok = torch.tensor([1 if self.error is None else 0], dtype=torch.int32, device=self.device)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)  # also: every window is mapped everywhere before the first signal
+            if int(ok.item()) != 1 and self.error is None:
+                self.error = "another rank could not map the windows"
+        self.ok = self.error is None
+        if not self.ok:
+            self.close()
+            return
+        self._flag_ptrs = torch.tensor([int(b) + self.flag_offset for b in self._peer], dtype=torch.int64, device=self.device)
+        self._streams = [torch.cuda.Stream(device=self.device) for _ in range(max(1, min(int(pull_streams), self.world - 1)))]
+
+    def close(self) -> None:
+        """Unmaps the peers' windows and frees the own one.  Collective in effect: call it on every rank, after the last
+        exchange has completed everywhere (e.g. behind a barrier)."""
+        lib = self._lib.lib()
+        with torch.cuda.device(self.device):
+            torch.cuda.synchronize(self.device)
+            for p, ptr in enumerate(self._peer):
+                if p != self.rank and ptr is not None:
+                    lib.come_peer_close(ptr)
+            if self._own is not None:
+                lib.come_peer_free(self._own)
+        self._own, self._peer = None, [None] * self.world
+
+    def stage(self, local: torch.Tensor) -> None:
+        """First half of an exchange, on the current stream: this rank's block goes into the next slot of its window.
+        (A same-device copy; issue it where the whole GPU is available, e.g. on the compute stream before the attention
+        launch the exchange is meant to hide behind.)"""
+        from ._torch_util import stream_ptr
+        n_local = self.rows[self.rank]
+        if local.shape[0] != n_local or not local.is_contiguous() or local[0].numel() * local.element_size() != self.row_bytes:
+            raise ValueError(f"rank {self.rank}: expected a contiguous block of {n_local} rows of {self.row_bytes} bytes")
+        self.seq += 1
+        slot = (self.seq & 1) * self.slot_bytes
+        self._lib.check(self._lib.lib().come_peer_copy(self._own + slot, local.data_ptr(), n_local * self.row_bytes, stream_ptr(self.device)))
+        self._staged = local
+
+    def exchange(self, out: torch.Tensor, remote_first: bool = False, include_local: bool = True) -> torch.Tensor:
+        """Second half, on the current stream (which must be ordered behind :meth:`stage`): signal, wait for the peers,
+        pull their blocks into ``out [sum(rows), ...]`` (block order of :func:`block_order`).  ``include_local=False``
+        leaves this rank's own block of ``out`` untouched (the caller attends to its local rows where they are)."""
+        from ._torch_util import stream_ptr
+        lib, check = self._lib.lib(), self._lib.check
+        local = self._staged
+        if local is None:
+            raise RuntimeError("exchange() without a staged block")
+        self._staged = None
+        if not out.is_contiguous() or out.shape[0] != sum(self.rows) or out.dtype != local.dtype or out.shape[1:] != local.shape[1:]:
+            raise ValueError("out must be a contiguous [sum(rows), ...] tensor of the blocks' dtype and row shape")
+        n_local = self.rows[self.rank]
+        seq = self.seq & 0x3fffffff
+        slot = (self.seq & 1) * self.slot_bytes
+        cur = torch.cuda.current_stream(self.device)
+        st = stream_ptr(self.device)
+        check(lib.come_peer_signal(self._flag_ptrs.data_ptr(), self.world, self.rank, seq, st))
+        check(lib.come_peer_wait(self._own + self.flag_offset, self.world, self.rank, seq, self.limit_ns, st))
+        ready = torch.cuda.Event()
+        ready.record(cur)
+        order = block_order(self.world, self.rank, remote_first)
+        at, starts = 0, {}
+        for r in order:
+            starts[r] = at
+            at += self.rows[r]
+        base = out.data_ptr()
+        if include_local:
+            check(lib.come_peer_copy(base + starts[self.rank] * self.row_bytes, local.data_ptr(), n_local * self.row_bytes, st))
+        used = []
+        for i, p in enumerate(r for r in order if r != self.rank):
+            s = self._streams[i % len(self._streams)]
+            if i < len(self._streams):
+                s.wait_event(ready)
+                used.append(s)
+            check(lib.come_peer_copy(base + starts[p] * self.row_bytes, self._peer[p] + slot, self.rows[p] * self.row_bytes, s.cuda_stream))
+        for s in used:
+            done = torch.cuda.Event()
+            done.record(s)
+            cur.wait_event(done)
+        return out
+
+    def gather(self, local: torch.Tensor, out: torch.Tensor, remote_first: bool = False) -> torch.Tensor:
+        """``local [rows[rank], ...]`` of every rank -> ``out [sum(rows), ...]``: :meth:`stage` + :meth:`exchange` on the
+        current stream."""
+        self.stage(local)
+        return self.exchange(out, remote_first=remote_first)
+
+
 class GlobalExchange:
     """What a rank needs to run global attention on ITS packed rows of a scene whose frames are spread over the ranks:
     the row counts of all ranks, where its own rows start, the per-key bias of all rows (the plan of the whole scene is
@@ -108,11 +284,21 @@ class GlobalExchange:
     """
 
     def __init__(self, rows: Sequence[int], rank: int, weight_all: torch.Tensor, group: Optional[dist.ProcessGroup] = None,
-                 gather=None, overlap: bool = False, comm_sms: int = 16):
-        """``comm_sms``: SMs left to the all-gather kernel while the attention to the local keys runs beside it.  The
-        collective completes only when all its CTAs have run, so the communicator must not use more CTAs than that
+                 gather=None, overlap: bool = False, comm_sms: int = 16, transport: str = "nccl"):
+        """``transport`` of the hidden exchange: ``"nccl"`` (an all-gather kernel beside the attention kernel) or ``"peer"``
+        (:class:`PeerGather`: copy engines, built at the first :meth:`attend`; when a rank cannot set it up, all ranks
+        fall back to NCCL together).  The in-line exchange (``overlap=False``) always uses NCCL.
+
+        ``comm_sms``: SMs left free while the attention to the local keys runs beside the exchange.  An NCCL collective
+        completes only when all its CTAs have run, so the communicator must not use more CTAs than that
         (``NCCL_MAX_CTAS`` in the environment before the process group is created, or the ``max_ctas`` option of the NCCL
-        process group); otherwise its last CTAs wait for the attention kernel to end and nothing overlaps."""
+        process group); otherwise its last CTAs wait for the attention kernel to end and nothing overlaps.  The peer
+        transport needs two SMs for its two small kernels."""
+        if transport not in ("nccl", "peer"):
+            raise ValueError(f"transport must be 'nccl' or 'peer', got {transport!r}")
+        self.transport = transport
+        self._peer_gather = None
+        self.peer_error = None
         self.comm_sms = int(comm_sms)
         self.rows = [int(n) for n in rows]
         self.rank = int(rank)
@@ -162,6 +348,22 @@ class GlobalExchange:
             return local
         return gather_rows(local, self.rows, self.group, out=out, remote_first=remote_first)
 
+    def close(self) -> None:
+        """Releases the peer windows, if any (call on every rank once the last exchange has completed everywhere)."""
+        if self._peer_gather is not None:
+            self._peer_gather.close()
+            self._peer_gather = None
+
+    def _setup_peer(self, kv: torch.Tensor) -> None:
+        """Builds the copy-engine transport (collective; the ranks agree on the outcome inside).  If any rank failed, the
+        exchange stays on NCCL on all of them and ``peer_error`` says why."""
+        pg = PeerGather(self.rows, self.rank, kv[0].numel() * kv.element_size(), kv.device, self.group)
+        if pg.ok:
+            self._peer_gather = pg
+        else:
+            self.transport = "nccl"
+            self.peer_error = pg.error
+
     def attend(self, q: torch.Tensor, kv: torch.Tensor, scale: float, use_bias: bool = True) -> torch.Tensor:
         """Global attention of this rank's query rows ``q [rows, H, D]`` to the keys / values of ALL ranks, of which this
         rank holds ``kv [rows, 2, H, D]`` (key rows ``kv[:, 0]``, value rows ``kv[:, 1]``).  Returns ``[rows, H, D]``."""
@@ -183,20 +385,28 @@ class GlobalExchange:
         if self._buf is None or tuple(self._buf.shape) != shape or self._buf.dtype != kv.dtype:
             self._buf = torch.empty(shape, dtype=kv.dtype, device=kv.device)  # reused by every global layer
         side = self._side
+        if self.transport == "peer" and self._gather is None and self._peer_gather is None:
+            self._setup_peer(kv)
+        if self._peer_gather is not None:
+            self._peer_gather.stage(kv)  # into this rank's window while the whole GPU is available (tens of microseconds)
         side.wait_stream(main)  # kv is ready, and the previous layer has finished reading the buffer
         ev = [torch.cuda.Event(enable_timing=self.events is not None) for _ in range(4)]
         with torch.cuda.stream(side):
             ev[0].record(side)
-            gathered = self.gather(kv, remote_first=True, out=self._buf)
+            if self._peer_gather is not None:
+                gathered = self._peer_gather.exchange(self._buf, remote_first=True, include_local=False)
+            else:
+                gathered = self.gather(kv, remote_first=True, out=self._buf)
             ev[1].record(side)
         kv.record_stream(side)
         bias_local, bias_remote = self.bias_local_remote(dtype) if use_bias else (None, None)
         sms = torch.cuda.get_device_properties(q.device).multi_processor_count
-        with cta_limit(sms - self.comm_sms if 0 < self.comm_sms < sms else 0):  # the gather's CTAs keep their SMs
+        free = 2 if self._peer_gather is not None else self.comm_sms
+        with cta_limit(sms - free if 0 < free < sms else 0):  # the exchange's kernels keep their SMs
             out, lse = varlen_fwd_rows(q, kv[:, 0], kv[:, 1], self._cu_local, n_local, bias_local, scale, 0)
         ev[2].record(main)
         main.wait_event(ev[1])
-        if gathered.data_ptr() != self._buf.data_ptr():  # a stand-in gather allocated its own result on the side stream
+        if self._peer_gather is None and gathered.data_ptr() != self._buf.data_ptr():  # a stand-in gather allocated its own result on the side stream
             gathered.record_stream(main)
         remote = gathered[:n_remote]
         out_r, lse_r = cross_fwd(q, remote[:, 0], remote[:, 1], bias_remote, scale)

@@ -343,7 +343,8 @@ int come_packed_positions(const uint8_t *mask_dev, const int64_t *rev_id_dev, in
  * clears it.  Returns COME_OK with *value == 0 when no kernel reported a problem, COME_ERR_DEVICE with the word in
  * *value (and a message naming its bits) otherwise.  Bits 0-8: a wait of the attention kernel ran out (while the word is
  * raised, attention launches return at once without touching their outputs); bit 15: the wait self-test below; bit 16: a
- * position outside the rotary table was clamped by come_qkv_prepare.
+ * position outside the rotary table was clamped by come_qkv_prepare; bit 17: a wait of the bulk-copy merge kernel ran out;
+ * bit 18: come_peer_wait gave up.
  */
 int come_device_status(uint32_t *value, int clear);
 
@@ -355,6 +356,35 @@ int come_device_status(uint32_t *value, int clear);
  * the word with come_device_status(&v, 1) afterwards.  No counterpart in the reference.
  */
 int come_selftest_bounded_wait(int64_t ticks, int64_t *waited_dev, void *stream);
+
+/*
+ * Exchange of row blocks between the GPUs of one node through peer-mapped memory (one process per GPU): the transport of
+ * the key / value all-gather of a global attention layer whose frames are sharded over the GPUs.  The reference has no
+ * multi-GPU inference path; these entry points have no counterpart there.
+ *
+ *   come_peer_alloc   cudaMalloc of a zeroed "window" on the current device + its CUDA IPC handle (COME_PEER_HANDLE_BYTES
+ *                     bytes, to be sent to the other processes by any host channel).
+ *   come_peer_open    maps another process's window (its handle) into this process; peer access is enabled lazily.
+ *   come_peer_close / come_peer_free   undo the two.
+ *   come_peer_copy    one cudaMemcpyAsync(dst, src, bytes) on `stream`; either side may be a mapped peer window: the driver
+ *                     moves the bytes over NVLink, no kernel of this library is involved.
+ *   come_peer_signal  one small kernel: for every rank p != rank a release store of `value` into word `rank` of p's flag
+ *                     array.  peer_flags_dev: device array of `world` pointers, entry p = the address of rank p's flag
+ *                     array (world int32 words inside p's window) as mapped in THIS process.
+ *   come_peer_wait    one small kernel: returns when every word p != rank of this rank's own flag array has reached `value`
+ *                     (written by the peers' come_peer_signal), or after limit_ns nanoseconds (at most 120 s), in which
+ *                     case bit 18 of the device status word is raised and the stream simply continues: nothing hangs.
+ * Usage per exchange k = 1, 2, ...: copy the local block into the own window (slot k & 1), signal k, wait k, copy the
+ * peers' blocks out of their windows.  Two slots suffice: a rank that signals k + 1 has finished its copies of exchange k.
+ */
+#define COME_PEER_HANDLE_BYTES 64
+int come_peer_alloc(int64_t bytes, void **ptr_out, void *handle_out);
+int come_peer_open(const void *handle, void **ptr_out);
+int come_peer_close(void *ptr);
+int come_peer_free(void *ptr);
+int come_peer_copy(void *dst, const void *src, int64_t bytes, void *stream);
+int come_peer_signal(void *const *peer_flags_dev, int world, int rank, int32_t value, void *stream);
+int come_peer_wait(const int32_t *flags_dev, int world, int rank, int32_t value, int64_t limit_ns, void *stream);
 
 #ifdef __cplusplus
 }

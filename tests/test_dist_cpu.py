@@ -138,3 +138,21 @@ def test_exchange_bias_split_follows_the_remote_first_order():
     assert torch.equal(local, weight[3:5].log())
     assert torch.equal(remote, torch.cat([weight[5:9], weight[0:3]]).log())  # rank 2's rows, then rank 0's
     assert ex.overlap and not GlobalExchange([9], 0, weight, overlap=True).overlap
+
+
+def test_hiding_the_exchange_pays_only_while_local_attention_is_long():
+    """The two-line model of a global layer: for the 100-frame scene (80,672 rows of 4 KB, 16 heads x 64) hiding the
+    exchange pays on 2 to 4 ranks and not on 8; never on one rank; never for a small scene, where no attention launch is
+    long enough to cover a slowed exchange; and a faster hidden exchange moves the boundary."""
+    from come_b200.dist import hiding_exchange_pays
+    big = dict(total_rows=80672, row_bytes=4096, num_heads=16, head_dim=64)
+    assert [hiding_exchange_pays(world=w, **big) for w in (1, 2, 4, 8)] == [False, True, True, False]
+    assert not hiding_exchange_pays(total_rows=6448, world=2, row_bytes=1024, num_heads=4, head_dim=64)
+    assert hiding_exchange_pays(world=8, exchange_hidden_gbs=380.0, **big)
+
+
+def test_global_exchange_rejects_unknown_transport():
+    import torch
+    from come_b200.dist import GlobalExchange
+    with pytest.raises(ValueError, match="transport"):
+        GlobalExchange([2, 2], 0, torch.ones(4), transport="carrier-pigeon")
