@@ -110,12 +110,14 @@ class CpuSceneSample:
     reference's fallback path is PyTorch; its matrix products run on PyTorch's BLAS).
 
     Every ``run()`` times, in float32 (the dtype of the reference's CPU path): the selection, a full merge and a full
-    unmerge of all frames, the frame attention of ``frame_sample`` whole frames with all heads, and the global attention
-    of ONE head on ``attn_rows`` query rows against all keys.  The frame figure is scaled by ``frames / frame_sample``
-    and the global figure by ``heads * rows / attn_rows``; both are summed over the 24 + 24 layers.  The scene figure is
-    therefore an extrapolation (``extrapolated`` in the report) and ``sample_s`` says how many seconds were timed."""
+    unmerge of all frames, the frame attention of ``frame_sample`` whole frames with all heads (all frames by default),
+    and the global attention of ``attn_heads`` heads on ``attn_rows`` query rows against all keys.  The frame figure is
+    scaled by ``frames / frame_sample`` and the global figure by ``heads / attn_heads * rows / attn_rows``; both are summed
+    over the 24 + 24 layers.  The scene figure is therefore an extrapolation (``extrapolated`` in the report) and
+    ``sample_s`` says how many seconds were timed (a few seconds per sample on 16 cores).  (The PyTorch expression
+    materialises the score matrix; ``oracle/torch_path.py`` walks the query rows in blocks that keep it under 1.5 GB.)"""
 
-    def __init__(self, frames, attn_rows=512, frame_sample=8):
+    def __init__(self, frames, attn_rows=8192, frame_sample=100, attn_heads=4):
         from oracle import clib, torch_path
         self.clib, self.attn, self.frames, self.attn_rows = clib, torch_path, frames, attn_rows
         self.frame_sample = min(frames, frame_sample)
@@ -132,7 +134,8 @@ class CpuSceneSample:
         self.P = int(frames * N_TOK - 8 * mask.sum())
         # attention inputs: all heads for the sampled frames, one head for the global slice
         self.qkv_frames = rng.standard_normal((self.frame_sample * N_TOK, 3, HEADS, HDIM), dtype=np.float32)
-        self.qkv_1head = rng.standard_normal((self.P, 3, 1, HDIM), dtype=np.float32)
+        self.attn_heads = min(HEADS, attn_heads)
+        self.qkv_heads = rng.standard_normal((self.P, 3, self.attn_heads, HDIM), dtype=np.float32)
 
     def run(self):
         clib, frames = self.clib, self.frames
@@ -155,8 +158,8 @@ class CpuSceneSample:
         t_frame = (time.perf_counter() - t0) * (frames / fs)
         rows = min(self.attn_rows, P)
         t0 = time.perf_counter()
-        self.attn.attention_bias(self.qkv_1head[:P], bias, np.array([0, P], np.int32), HDIM ** -0.5, 0, rows)
-        t_global = (time.perf_counter() - t0) * HEADS * (P / rows)
+        self.attn.attention_bias(self.qkv_heads[:P], bias, np.array([0, P], np.int32), HDIM ** -0.5, 0, rows)
+        t_global = (time.perf_counter() - t0) * (HEADS / self.attn_heads) * (P / rows)
         sample_s = time.perf_counter() - t_all
         n_f = sum(1 for k in LAYERS if k == "frame")
         n_g = len(LAYERS) - n_f
@@ -168,8 +171,8 @@ class CpuSceneSample:
     def describe(self):
         return (f"per step: select + merge + unmerge of all {self.frames} frames (fp32, {self.frames}x{N_TOK}x{CH}), frame "
                 f"attention of {self.frame_sample} whole frames x {HEADS} heads (scaled by {self.frames}/{self.frame_sample}), "
-                f"global attention of 1 head x {min(self.attn_rows, self.P)} of {self.P} query rows against all keys (scaled to "
-                f"{HEADS} heads and all rows); x24 frame + x24 global layers")
+                f"global attention of {self.attn_heads} heads x {min(self.attn_rows, self.P)} of {self.P} query rows against all keys "
+                f"(scaled to {HEADS} heads and all rows); x24 frame + x24 global layers")
 
 
 def cpu_baseline_report(frames, steps, warmup=0):
@@ -229,11 +232,18 @@ def init_ranks(cap_nccl_ctas=False):
     return torch, dist, world, rank, local, dev
 
 
-def sharded_check(torch, dist, world, rank, dev, transport="nccl", hidden=True):
+def _lib_status_clear():
+    from come_b200 import _lib
+    return _lib.device_status(clear=True)
+
+
+def sharded_check(torch, dist, world, rank, dev, transport="nccl", hidden=True, near_peers=0):
     """Before anything is timed at N > 1: a small scene (one frame layer + one global layer) run sharded over the ranks
     and unsharded on every rank.  With the exchange in line the sharded frames must equal the unsharded ones bit for bit;
     with the exchange hidden behind attention to the local keys the global layer may differ by the rounding of the two
-    partial outputs (bar 2e-2 absolute).  Raises on a mismatch on any rank."""
+    partial outputs (bar 2e-2 absolute).  Raises on a mismatch of the in-line form on any rank; a hidden form that fails
+    (an exception, a wait that ran out or a mismatch on any rank) is reported in ``hidden_failed`` and the caller falls
+    back to the in-line exchange."""
     from come_b200.chain import ShardedOpChain
     frames, C, H, D = max(8, world), 256, 4, 64
     g = torch.Generator(device="cpu").manual_seed(5)
@@ -250,26 +260,36 @@ def sharded_check(torch, dist, world, rank, dev, transport="nccl", hidden=True):
     res = {"rows": P, "frames": frames}
     ok = True
     for overlap in ((False, True) if hidden else (False,)):  # the hidden exchange is checked where the timed run uses it
-        chain = ShardedOpChain(frames, None, START, GRID, GRID, WIN, WIN, 0.5, H, D, kinds, overlap=overlap, transport=transport)
+        chain = ShardedOpChain(frames, None, START, GRID, GRID, WIN, WIN, 0.5, H, D, kinds, overlap=overlap, transport=transport,
+                               near_peers=near_peers if overlap else 0)
         gp, lp = chain.build_plans(conf)
         r0, r1 = chain.row_begin, chain.row_begin + lp.total
-        diffs = []
-        for kind, ref in zip(kinds, want):
-            got = chain.layer(gp, lp, x[chain.f_lo:chain.f_hi], q[r0:r1].contiguous(), kv[r0:r1].contiguous(), kind)
-            diffs.append(float((got.float() - ref[chain.f_lo:chain.f_hi].float()).abs().max().item()) if got.numel() else 0.0)
-        t = torch.tensor(diffs, dtype=torch.float64, device=dev)
+        diffs, failed = [], 0.0
+        try:
+            for kind, ref in zip(kinds, want):
+                got = chain.layer(gp, lp, x[chain.f_lo:chain.f_hi], q[r0:r1].contiguous(), kv[r0:r1].contiguous(), kind)
+                diffs.append(float((got.float() - ref[chain.f_lo:chain.f_hi].float()).abs().max().item()) if got.numel() else 0.0)
+            if _lib_status_clear() != 0:
+                failed = 1.0
+        except Exception as e:  # noqa: BLE001 - the ranks must still meet in the reduction below
+            if not overlap:
+                raise
+            failed, diffs = 1.0, [0.0, 0.0]
+            res["hidden_error"] = repr(e)
+        t = torch.tensor(diffs + [failed], dtype=torch.float64, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         worst = t.tolist()
         if overlap:
             res["overlapped_max_abs_diff"] = {"frame": worst[0], "global": worst[1], "bar_global": 2e-2}
             res["overlapped_transport"] = chain.exchange.transport
-            ok = ok and worst[0] == 0.0 and worst[1] <= 2e-2
+            res["near_peers"] = near_peers
+            res["hidden_failed"] = bool(worst[2] != 0.0 or worst[0] != 0.0 or worst[1] > 2e-2)
             torch.cuda.synchronize()
             dist.barrier()  # every rank has finished its pulls before anyone releases its window
             chain.exchange.close()
         else:
             res["in_line_bit_exact"] = worst[0] == 0.0 and worst[1] == 0.0
-            ok = ok and res["in_line_bit_exact"]
+            ok = ok and res["in_line_bit_exact"] and worst[2] == 0.0
     res["ok"] = bool(ok)
     if not ok:
         raise RuntimeError(f"sharded scene differs from the unsharded one: {res}")
@@ -281,21 +301,39 @@ def run_frames(args):
     layers are local; a global layer all-gathers the merged K/V rows over NCCL on a side stream while the local query rows
     attend to the local keys, then attends them to the gathered rows and merges the two results (strong scaling: the
     scene is fixed, more GPUs shorten it).  At N = 1 there is no exchange and the global layer is one launch."""
-    from come_b200.dist import hiding_exchange_pays
+    from come_b200.dist import hiding_exchange_pays, split_exchange_plan
     frames = FRAMES_BY_WORKLOAD[args.workload]
     world_env = int(os.environ.get("WORLD_SIZE", "1"))
-    # auto: hide the exchange where the model of a global layer says it pays (2 to 4 GPUs for the 100-frame scene; on 8 the
-    # attention to the local keys is too short to cover an exchange that runs four times slower beside it)
+    # auto: the form of the exchange that a model of a global layer says is shortest.  For the 100-frame scene: hidden behind
+    # the attention to the local keys on 2 to 4 GPUs; on 8 that attention is too short to cover an exchange that runs four
+    # times slower beside it, so three peers' blocks are fetched in line first (peer windows) or everything (NCCL).
     rows_est = frames * (START + GRID * GRID - (GRID // WIN) ** 2 // 2 * (WIN * WIN - 1))  # half of the windows merged: 798 per frame
-    overlap = world_env > 1 and (args.overlap == "on" or (args.overlap == "auto" and
-                                                         hiding_exchange_pays(rows_est, world_env, 2 * HEADS * HDIM * 2, HEADS, HDIM)))
+    shape = (rows_est, world_env, 2 * HEADS * HDIM * 2, HEADS, HDIM)
+    near_peers = 0
+    if world_env <= 1 or args.overlap == "off":
+        overlap = False
+    elif args.transport == "peer":
+        near_peers, overlap, _ = split_exchange_plan(*shape)
+        if args.near_peers >= 0:
+            near_peers, overlap = min(args.near_peers, world_env - 2), True
+        elif args.overlap == "on" and not overlap:
+            near_peers, overlap = 0, True
+        if not overlap:
+            near_peers = 0
+    else:
+        overlap = args.overlap == "on" or hiding_exchange_pays(*shape)
     torch, dist, world, rank, local, dev = init_ranks(cap_nccl_ctas=overlap and args.transport == "nccl")
     from come_b200 import _lib
     from come_b200.chain import ShardedOpChain
     pk = peaks()
-    check = sharded_check(torch, dist, world, rank, dev, args.transport, hidden=overlap) if world > 1 else None
+    check = sharded_check(torch, dist, world, rank, dev, args.transport, hidden=overlap, near_peers=near_peers) if world > 1 else None
+    fallback = None
+    if check is not None and check.get("hidden_failed"):
+        # the hidden exchange did not reproduce the unsharded scene on this box: the timed run keeps the exchange in line
+        fallback = check.get("hidden_error") or "the hidden exchange failed the sharded check"
+        overlap, near_peers = False, 0
     chain = ShardedOpChain(frames, None, START, GRID, GRID, WIN, WIN, 0.5, HEADS, HDIM, LAYERS, overlap=overlap,
-                           transport=args.transport)
+                           transport=args.transport, near_peers=near_peers)
     g = torch.Generator(device="cpu").manual_seed(4321)
     conf_host = torch.rand((1, frames * GRID * GRID), generator=g).bfloat16().pin_memory()  # replicated on every rank
     conf = conf_host.to(dev)
@@ -420,7 +458,9 @@ def run_frames(args):
             "warmup": max(args.warmup, 3), "ms_per_step": per_scene, "higher_is_better": False, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic (seeded)",
             "config": {"workload": workload_name(frames), "merged_tokens": P, "frames_per_s": frames / per_scene * 1e3,
-                       "exchange": ("none" if world == 1 else ("hidden behind attention to the local keys" if chain.overlap else "in line")),
+                       "exchange": ("none" if world == 1 else ("in line" + (f" (fallback: {fallback})" if fallback else "") if not chain.overlap else
+                                    ("hidden behind attention to the local keys" if near_peers == 0 else
+                                     f"{near_peers} peers' rows in line, the other {world - 1 - near_peers} hidden behind attention to the near keys"))),
                        "parallelism": ("one GPU: the whole scene, no exchange" if world == 1 else
                                        f"frames sharded over {world} GPUs; frame layers local; a global layer all-gathers "
                                        f"{kv_bytes / 1e6:.0f} MB of merged K/V "
@@ -1124,6 +1164,8 @@ def main():
                          "100-frame scene through the whole alternating-attention stack (with its GEMMs), sharded by frame")
     ap.add_argument("--transport", default="peer", choices=["peer", "nccl"],
                     help="transport of the hidden K/V exchange at N > 1: copy engines over peer-mapped windows, or an NCCL all-gather")
+    ap.add_argument("--near-peers", type=int, default=-1,
+                    help="peer transport: blocks of that many peers fetched in line before the hidden part (-1: from the layer model)")
     ap.add_argument("--overlap", default="auto", choices=["auto", "on", "off"],
                     help="N > 1: hide the K/V all-gather of a global layer behind attention to the local keys (on), keep it in line "
                          "(off: the sharded result is then bit-identical to one GPU), or decide from a model of the layer (auto: "

@@ -15,7 +15,7 @@ from typing import List, Optional, Sequence, Tuple
 import torch
 import torch.distributed as dist
 
-__all__ = ["shard_range", "rows_per_rank", "gather_rows", "block_order", "hiding_exchange_pays", "PeerGather", "GlobalExchange"]
+__all__ = ["shard_range", "rows_per_rank", "gather_rows", "block_order", "hiding_exchange_pays", "split_exchange_plan", "PeerGather", "GlobalExchange"]
 
 
 def shard_range(n_items: int, world: int, rank: int) -> Tuple[int, int]:
@@ -61,6 +61,30 @@ def hiding_exchange_pays(total_rows: int, world: int, row_bytes: int, num_heads:
     in_line = bytes_in / (exchange_gbs * 1e9) + t_attn(local_rows, total_rows)
     hidden = max(t_attn(local_rows, local_rows), bytes_in / (exchange_hidden_gbs * 1e9)) + t_attn(local_rows, total_rows - local_rows)
     return hidden < in_line
+
+
+def split_exchange_plan(total_rows: int, world: int, row_bytes: int, num_heads: int, head_dim: int,
+                        attn_tflops: float = 780.0, exchange_gbs: float = 380.0, exchange_hidden_gbs: float = 110.0):
+    """``(near_peers, hidden, ms)``: how to run the key / value exchange of a global layer, from the model of
+    :func:`hiding_exchange_pays` extended by one knob: the blocks of ``near_peers`` peers are fetched in line (fast, the GPU
+    has nothing else to do), the local rows then attend to those keys and their own while the other blocks arrive (slowed),
+    and to the rest afterwards.  ``near_peers = 0`` is the plain hidden exchange; ``hidden = False`` means that not hiding
+    anything (one in-line gather, one attention launch) is at least as short.  ``ms``: the modelled layer time of the choice.
+
+    100-frame scene (80,672 rows of 4 KB, 16 heads x 64): 2 to 4 GPUs -> ``(0, True)``; 8 GPUs -> ``(3, True)``: 0.32 ms in
+    line, then 2.07 ms of attention cover the 1.5 ms the other four blocks need: 4.5 ms per layer against 4.9 in line."""
+    if world <= 1:
+        return 0, False, 0.0
+    block = total_rows / world
+    t_attn = lambda k: 4.0 * block * k * head_dim * num_heads / (attn_tflops * 1e12)  # noqa: E731 - local queries x k keys
+    t_alone = lambda n: n * block * row_bytes / (exchange_gbs * 1e9)  # noqa: E731
+    t_slow = lambda n: n * block * row_bytes / (exchange_hidden_gbs * 1e9)  # noqa: E731
+    best = (world - 1, False, t_alone(world - 1) + t_attn(total_rows))
+    for a in range(world - 1):
+        t = t_alone(a) + max(t_attn((1 + a) * block), t_slow(world - 1 - a)) + t_attn((world - 1 - a) * block) + 0.00005
+        if t < best[2]:
+            best = (a, True, t)
+    return best[0], best[1], best[2] * 1e3
 
 
 def gather_rows(local: torch.Tensor, rows: Sequence[int], group: Optional[dist.ProcessGroup] = None,
@@ -220,25 +244,34 @@ class PeerGather:
         self._lib.check(self._lib.lib().come_peer_copy(self._own + slot, local.data_ptr(), n_local * self.row_bytes, stream_ptr(self.device)))
         self._staged = local
 
-    def exchange(self, out: torch.Tensor, remote_first: bool = False, include_local: bool = True) -> torch.Tensor:
-        """Second half, on the current stream (which must be ordered behind :meth:`stage`): signal, wait for the peers,
-        pull their blocks into ``out [sum(rows), ...]`` (block order of :func:`block_order`).  ``include_local=False``
-        leaves this rank's own block of ``out`` untouched (the caller attends to its local rows where they are)."""
+    def sync(self) -> None:
+        """Second step, on the current stream (which must be ordered behind :meth:`stage`): tell the peers that this rank's
+        block is in its window and wait (bounded) until all of them have said the same."""
+        from ._torch_util import stream_ptr
+        lib, check = self._lib.lib(), self._lib.check
+        if self._staged is None:
+            raise RuntimeError("sync() without a staged block")
+        seq = self.seq & 0x3fffffff
+        st = stream_ptr(self.device)
+        check(lib.come_peer_signal(self._flag_ptrs.data_ptr(), self.world, self.rank, seq, st))
+        check(lib.come_peer_wait(self._own + self.flag_offset, self.world, self.rank, seq, self.limit_ns, st))
+
+    def pull(self, out: torch.Tensor, remote_first: bool = False, include_local: bool = True,
+             peers: Optional[Sequence[int]] = None) -> torch.Tensor:
+        """Third step, on the current stream behind :meth:`sync`, as often as needed: copies the blocks of ``peers`` (default:
+        all the other ranks) out of their windows into their places in ``out [sum(rows), ...]`` (block order of
+        :func:`block_order`); ``include_local`` also copies this rank's own block into its place."""
         from ._torch_util import stream_ptr
         lib, check = self._lib.lib(), self._lib.check
         local = self._staged
         if local is None:
-            raise RuntimeError("exchange() without a staged block")
-        self._staged = None
+            raise RuntimeError("pull() without a staged block")
         if not out.is_contiguous() or out.shape[0] != sum(self.rows) or out.dtype != local.dtype or out.shape[1:] != local.shape[1:]:
             raise ValueError("out must be a contiguous [sum(rows), ...] tensor of the blocks' dtype and row shape")
         n_local = self.rows[self.rank]
-        seq = self.seq & 0x3fffffff
         slot = (self.seq & 1) * self.slot_bytes
         cur = torch.cuda.current_stream(self.device)
         st = stream_ptr(self.device)
-        check(lib.come_peer_signal(self._flag_ptrs.data_ptr(), self.world, self.rank, seq, st))
-        check(lib.come_peer_wait(self._own + self.flag_offset, self.world, self.rank, seq, self.limit_ns, st))
         ready = torch.cuda.Event()
         ready.record(cur)
         order = block_order(self.world, self.rank, remote_first)
@@ -249,8 +282,11 @@ class PeerGather:
         base = out.data_ptr()
         if include_local:
             check(lib.come_peer_copy(base + starts[self.rank] * self.row_bytes, local.data_ptr(), n_local * self.row_bytes, st))
+        wanted = [r for r in order if r != self.rank] if peers is None else [int(p) for p in peers]
+        if any(p == self.rank or not (0 <= p < self.world) for p in wanted):
+            raise ValueError(f"peers must be other ranks of the group, got {wanted}")
         used = []
-        for i, p in enumerate(r for r in order if r != self.rank):
+        for i, p in enumerate(wanted):
             s = self._streams[i % len(self._streams)]
             if i < len(self._streams):
                 s.wait_event(ready)
@@ -261,6 +297,11 @@ class PeerGather:
             done.record(s)
             cur.wait_event(done)
         return out
+
+    def exchange(self, out: torch.Tensor, remote_first: bool = False, include_local: bool = True) -> torch.Tensor:
+        """:meth:`sync` + :meth:`pull` of every peer's block on the current stream."""
+        self.sync()
+        return self.pull(out, remote_first=remote_first, include_local=include_local)
 
     def gather(self, local: torch.Tensor, out: torch.Tensor, remote_first: bool = False) -> torch.Tensor:
         """``local [rows[rank], ...]`` of every rank -> ``out [sum(rows), ...]``: :meth:`stage` + :meth:`exchange` on the
@@ -284,7 +325,7 @@ class GlobalExchange:
     """
 
     def __init__(self, rows: Sequence[int], rank: int, weight_all: torch.Tensor, group: Optional[dist.ProcessGroup] = None,
-                 gather=None, overlap: bool = False, comm_sms: int = 16, transport: str = "nccl"):
+                 gather=None, overlap: bool = False, comm_sms: int = 16, transport: str = "nccl", near_peers: int = 0):
         """``transport`` of the hidden exchange: ``"nccl"`` (an all-gather kernel beside the attention kernel) or ``"peer"``
         (:class:`PeerGather`: copy engines, built at the first :meth:`attend`; when a rank cannot set it up, all ranks
         fall back to NCCL together).  The in-line exchange (``overlap=False``) always uses NCCL.
@@ -293,9 +334,17 @@ class GlobalExchange:
         completes only when all its CTAs have run, so the communicator must not use more CTAs than that
         (``NCCL_MAX_CTAS`` in the environment before the process group is created, or the ``max_ctas`` option of the NCCL
         process group); otherwise its last CTAs wait for the attention kernel to end and nothing overlaps.  The peer
-        transport needs two SMs for its two small kernels."""
+        transport needs two SMs for its two small kernels.
+
+        ``near_peers`` (peer transport): the blocks of that many peers are pulled IN LINE first (at the speed of an
+        exchange that has the GPU to itself); the local rows then attend to those keys and the local ones together while
+        the remaining peers' blocks arrive, and to the remaining keys afterwards.  For many ranks, where the attention to
+        the local keys alone is too short to cover the slowed exchange (:func:`split_exchange_plan`)."""
         if transport not in ("nccl", "peer"):
             raise ValueError(f"transport must be 'nccl' or 'peer', got {transport!r}")
+        if not (0 <= int(near_peers) < max(1, len(rows))):
+            raise ValueError(f"near_peers must be in [0, world - 1), got {near_peers}")
+        self.near_peers = int(near_peers)
         self.transport = transport
         self._peer_gather = None
         self.peer_error = None
@@ -387,6 +436,8 @@ class GlobalExchange:
         side = self._side
         if self.transport == "peer" and self._gather is None and self._peer_gather is None:
             self._setup_peer(kv)
+        if self._peer_gather is not None and self.near_peers > 0:
+            return self._attend_two_phase(q, kv, scale, use_bias)
         if self._peer_gather is not None:
             self._peer_gather.stage(kv)  # into this rank's window while the whole GPU is available (tens of microseconds)
         side.wait_stream(main)  # kv is ready, and the previous layer has finished reading the buffer
@@ -411,6 +462,51 @@ class GlobalExchange:
         remote = gathered[:n_remote]
         out_r, lse_r = cross_fwd(q, remote[:, 0], remote[:, 1], bias_remote, scale)
         combine(out, lse, out_r, lse_r, out_=out, lse_out=lse)
+        ev[3].record(main)
+        if self.events is not None:
+            self.events.append(ev)
+        return out
+
+    def _attend_two_phase(self, q: torch.Tensor, kv: torch.Tensor, scale: float, use_bias: bool) -> torch.Tensor:
+        """Peer transport with ``near_peers`` > 0.  Gathered buffer, remote-first order: ``[far peers | near peers | local]``.
+        In line: the near peers' blocks and the local one.  Then the local rows attend to ``[near | local]`` while the far
+        peers' blocks arrive on the side stream, then to ``[far]``; the two results are merged from their log-sum-exps."""
+        from .flash_attn_fwd_cuda import combine, cross_fwd, cta_limit
+        pg, dtype = self._peer_gather, q.dtype
+        world = len(self.rows)
+        order = block_order(world, self.rank, True)  # [rank + 1, ..., rank - 1, rank]
+        far, near = order[: world - 1 - self.near_peers], order[world - 1 - self.near_peers: world - 1]
+        n_far = sum(self.rows[r] for r in far)
+        main, side = torch.cuda.current_stream(q.device), self._side
+        ev = [torch.cuda.Event(enable_timing=self.events is not None) for _ in range(4)]
+        pg.stage(kv)
+        side.wait_stream(main)  # kv is staged, and the previous layer has finished reading the buffer
+        with torch.cuda.stream(side):
+            ev[0].record(side)
+            pg.sync()
+            pg.pull(self._buf, remote_first=True, include_local=True, peers=near)
+            near_done = torch.cuda.Event()
+            near_done.record(side)
+            pg.pull(self._buf, remote_first=True, include_local=False, peers=far)
+            ev[1].record(side)
+        kv.record_stream(side)
+        main.wait_event(near_done)
+        if use_bias:
+            b_local, b_remote = self.bias_local_remote(dtype)
+            key = ("two-phase", dtype)
+            if key not in self._bias_split:
+                self._bias_split[key] = (torch.cat([b_remote[n_far:], b_local]).contiguous(), b_remote[:n_far].contiguous())
+            bias_near, bias_far = self._bias_split[key]
+        else:
+            bias_near = bias_far = None
+        sms = torch.cuda.get_device_properties(q.device).multi_processor_count
+        near_rows, far_rows = self._buf[n_far:], self._buf[:n_far]
+        with cta_limit(sms - 2):  # the far pulls run beside this launch
+            out, lse = cross_fwd(q, near_rows[:, 0], near_rows[:, 1], bias_near, scale)
+        ev[2].record(main)
+        main.wait_event(ev[1])
+        out_f, lse_f = cross_fwd(q, far_rows[:, 0], far_rows[:, 1], bias_far, scale)
+        combine(out, lse, out_f, lse_f, out_=out, lse_out=lse)
         ev[3].record(main)
         if self.events is not None:
             self.events.append(ev)

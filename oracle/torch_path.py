@@ -25,14 +25,18 @@ def attention_bias(qkv: np.ndarray, bias, cu_seqlens, scale: float, q_lo: int = 
         hi = e if (q_hi < 0 or a + q_hi > e) else a + q_hi
         if hi <= lo:
             continue
-        q = t[lo:hi, 0].transpose(0, 1)          # [H, rows, D]
         k = t[a:e, 1].transpose(0, 1)            # [H, L, D]
         v = t[a:e, 2].transpose(0, 1)
-        s = q @ k.transpose(1, 2) * scale
-        if b is not None:
-            s = s + b[a:e][None, None, :]
-        lse[:, lo:hi] = torch.logsumexp(s, dim=-1)
-        out[lo:hi] = (torch.softmax(s, dim=-1) @ v).transpose(0, 1)
+        # the expression materialises the score matrix: walk the query rows in blocks that keep it under ~1.5 GB
+        step = max(1, int(1.5e9 // (4 * H * max(e - a, 1))))
+        for r0 in range(lo, hi, step):
+            r1 = min(r0 + step, hi)
+            q = t[r0:r1, 0].transpose(0, 1)      # [H, rows, D]
+            s = q @ k.transpose(1, 2) * scale
+            if b is not None:
+                s = s + b[a:e][None, None, :]
+            lse[:, r0:r1] = torch.logsumexp(s, dim=-1)
+            out[r0:r1] = (torch.softmax(s, dim=-1) @ v).transpose(0, 1)
     return out.numpy(), lse.numpy()
 
 
