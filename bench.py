@@ -237,7 +237,7 @@ def _lib_status_clear():
     return _lib.device_status(clear=True)
 
 
-def sharded_check(torch, dist, world, rank, dev, transport="nccl", hidden=True, near_peers=0):
+def sharded_check(torch, dist, world, rank, dev, transport="nccl", hidden=True, pulls_first=False):
     """Before anything is timed at N > 1: a small scene (one frame layer + one global layer) run sharded over the ranks
     and unsharded on every rank.  With the exchange in line the sharded frames must equal the unsharded ones bit for bit;
     with the exchange hidden behind attention to the local keys the global layer may differ by the rounding of the two
@@ -261,7 +261,7 @@ def sharded_check(torch, dist, world, rank, dev, transport="nccl", hidden=True, 
     ok = True
     for overlap in ((False, True) if hidden else (False,)):  # the hidden exchange is checked where the timed run uses it
         chain = ShardedOpChain(frames, None, START, GRID, GRID, WIN, WIN, 0.5, H, D, kinds, overlap=overlap, transport=transport,
-                               near_peers=near_peers if overlap else 0)
+                               pulls_first=pulls_first and overlap)
         gp, lp = chain.build_plans(conf)
         r0, r1 = chain.row_begin, chain.row_begin + lp.total
         diffs, failed = [], 0.0
@@ -282,7 +282,7 @@ def sharded_check(torch, dist, world, rank, dev, transport="nccl", hidden=True, 
         if overlap:
             res["overlapped_max_abs_diff"] = {"frame": worst[0], "global": worst[1], "bar_global": 2e-2}
             res["overlapped_transport"] = chain.exchange.transport
-            res["near_peers"] = near_peers
+            res["pulls_first"] = bool(pulls_first)
             res["hidden_failed"] = bool(worst[2] != 0.0 or worst[0] != 0.0 or worst[1] > 2e-2)
             torch.cuda.synchronize()
             dist.barrier()  # every rank has finished its pulls before anyone releases its window
@@ -301,39 +301,36 @@ def run_frames(args):
     layers are local; a global layer all-gathers the merged K/V rows over NCCL on a side stream while the local query rows
     attend to the local keys, then attends them to the gathered rows and merges the two results (strong scaling: the
     scene is fixed, more GPUs shorten it).  At N = 1 there is no exchange and the global layer is one launch."""
-    from come_b200.dist import hiding_exchange_pays, split_exchange_plan
+    from come_b200.dist import hiding_exchange_pays, pulls_first_pays
     frames = FRAMES_BY_WORKLOAD[args.workload]
     world_env = int(os.environ.get("WORLD_SIZE", "1"))
     # auto: the form of the exchange that a model of a global layer says is shortest.  For the 100-frame scene: hidden behind
     # the attention to the local keys on 2 to 4 GPUs; on 8 that attention is too short to cover an exchange that runs four
-    # times slower beside it, so three peers' blocks are fetched in line first (peer windows) or everything (NCCL).
+    # times slower beside it: with peer windows the pulls then start first and the attention fills in behind them, with NCCL
+    # the exchange stays in line.
     rows_est = frames * (START + GRID * GRID - (GRID // WIN) ** 2 // 2 * (WIN * WIN - 1))  # half of the windows merged: 798 per frame
     shape = (rows_est, world_env, 2 * HEADS * HDIM * 2, HEADS, HDIM)
-    near_peers = 0
+    pulls_first = False
     if world_env <= 1 or args.overlap == "off":
         overlap = False
-    elif args.transport == "peer":
-        near_peers, overlap, _ = split_exchange_plan(*shape)
-        if args.near_peers >= 0:
-            near_peers, overlap = min(args.near_peers, world_env - 2), True
-        elif args.overlap == "on" and not overlap:
-            near_peers, overlap = 0, True
-        if not overlap:
-            near_peers = 0
+    elif args.overlap == "on" or hiding_exchange_pays(*shape):
+        overlap = True
     else:
-        overlap = args.overlap == "on" or hiding_exchange_pays(*shape)
+        overlap = pulls_first = args.transport == "peer" and pulls_first_pays(*shape)
+    if args.pulls_first != "auto" and overlap and args.transport == "peer":
+        pulls_first = args.pulls_first == "on"
     torch, dist, world, rank, local, dev = init_ranks(cap_nccl_ctas=overlap and args.transport == "nccl")
     from come_b200 import _lib
     from come_b200.chain import ShardedOpChain
     pk = peaks()
-    check = sharded_check(torch, dist, world, rank, dev, args.transport, hidden=overlap, near_peers=near_peers) if world > 1 else None
+    check = sharded_check(torch, dist, world, rank, dev, args.transport, hidden=overlap, pulls_first=pulls_first) if world > 1 else None
     fallback = None
     if check is not None and check.get("hidden_failed"):
         # the hidden exchange did not reproduce the unsharded scene on this box: the timed run keeps the exchange in line
         fallback = check.get("hidden_error") or "the hidden exchange failed the sharded check"
-        overlap, near_peers = False, 0
+        overlap = pulls_first = False
     chain = ShardedOpChain(frames, None, START, GRID, GRID, WIN, WIN, 0.5, HEADS, HDIM, LAYERS, overlap=overlap,
-                           transport=args.transport, near_peers=near_peers)
+                           transport=args.transport, pulls_first=pulls_first)
     g = torch.Generator(device="cpu").manual_seed(4321)
     conf_host = torch.rand((1, frames * GRID * GRID), generator=g).bfloat16().pin_memory()  # replicated on every rank
     conf = conf_host.to(dev)
@@ -459,8 +456,8 @@ def run_frames(args):
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic (seeded)",
             "config": {"workload": workload_name(frames), "merged_tokens": P, "frames_per_s": frames / per_scene * 1e3,
                        "exchange": ("none" if world == 1 else ("in line" + (f" (fallback: {fallback})" if fallback else "") if not chain.overlap else
-                                    ("hidden behind attention to the local keys" if near_peers == 0 else
-                                     f"{near_peers} peers' rows in line, the other {world - 1 - near_peers} hidden behind attention to the near keys"))),
+                                    ("hidden behind attention to the local keys" if not pulls_first else
+                                     "pulls started first, attention to the local keys fills in behind them"))),
                        "parallelism": ("one GPU: the whole scene, no exchange" if world == 1 else
                                        f"frames sharded over {world} GPUs; frame layers local; a global layer all-gathers "
                                        f"{kv_bytes / 1e6:.0f} MB of merged K/V "
@@ -1164,8 +1161,8 @@ def main():
                          "100-frame scene through the whole alternating-attention stack (with its GEMMs), sharded by frame")
     ap.add_argument("--transport", default="peer", choices=["peer", "nccl"],
                     help="transport of the hidden K/V exchange at N > 1: copy engines over peer-mapped windows, or an NCCL all-gather")
-    ap.add_argument("--near-peers", type=int, default=-1,
-                    help="peer transport: blocks of that many peers fetched in line before the hidden part (-1: from the layer model)")
+    ap.add_argument("--pulls-first", default="auto", choices=["auto", "on", "off"],
+                    help="peer transport, hidden exchange: launch the attention to the local keys only once the pulls are runnable")
     ap.add_argument("--overlap", default="auto", choices=["auto", "on", "off"],
                     help="N > 1: hide the K/V all-gather of a global layer behind attention to the local keys (on), keep it in line "
                          "(off: the sharded result is then bit-identical to one GPU), or decide from a model of the layer (auto: "

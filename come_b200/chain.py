@@ -83,12 +83,12 @@ class ShardedOpChain:
     def __init__(self, frames_total: int, group=None, start_index: int = 5, grid_h: int = 37, grid_w: int = 37,
                  group_h: int = 3, group_w: int = 3, threshold: float = 0.5, num_heads: int = 16, head_dim: int = 64,
                  layer_kinds: Optional[Sequence[str]] = None, overlap: bool = False, world: Optional[int] = None,
-                 rank: Optional[int] = None, transport: str = "nccl", near_peers: int = 0):
+                 rank: Optional[int] = None, transport: str = "nccl", pulls_first: bool = False):
         """``overlap``: hide the key / value exchange of a global layer behind attention to the local keys
         (:class:`come_b200.dist.GlobalExchange`); the result then differs from the single-GPU one by the rounding of two
         partial outputs.  Off: bit-identical to the single-GPU chain.  ``transport`` of the hidden exchange: ``"nccl"`` or
-        ``"peer"`` (pulls out of peer-mapped windows, :class:`come_b200.dist.PeerGather`; ``near_peers`` of the peers' blocks
-        fetched in line first, see :class:`come_b200.dist.GlobalExchange`).  ``world`` / ``rank`` default
+        ``"peer"`` (pulls out of peer-mapped windows, :class:`come_b200.dist.PeerGather`; ``pulls_first``: the pulls start
+        before the attention to the local keys gets the machine, see :class:`come_b200.dist.GlobalExchange`).  ``world`` / ``rank`` default
         to the process group's; ``world=1`` runs the whole scene on this GPU whatever the group is."""
         import torch.distributed as dist
 
@@ -106,7 +106,7 @@ class ShardedOpChain:
         self.layer_kinds = list(layer_kinds) if layer_kinds is not None else ["frame", "global"] * 24
         self.overlap = bool(overlap)
         self.transport = transport
-        self.near_peers = int(near_peers)
+        self.pulls_first = bool(pulls_first)
         self.exchange = None
 
     def build_plans(self, confidence_all: torch.Tensor):
@@ -124,7 +124,7 @@ class ShardedOpChain:
         from .dist import GlobalExchange
         keep = self.exchange
         self.exchange = GlobalExchange(self.rows, self.rank, global_plan.weight, self.group, overlap=self.overlap,
-                                       transport=self.transport, near_peers=self.near_peers if self.world > 1 else 0)
+                                       transport=self.transport, pulls_first=self.pulls_first)
         if keep is not None and keep.rows == self.exchange.rows:  # same packing: keep the side stream, the gather buffer and the windows
             self.exchange._side, self.exchange._buf, self.exchange.events = keep._side, keep._buf, keep.events
             self.exchange._peer_gather, self.exchange.transport, self.exchange.peer_error = keep._peer_gather, keep.transport, keep.peer_error

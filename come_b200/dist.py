@@ -15,7 +15,7 @@ from typing import List, Optional, Sequence, Tuple
 import torch
 import torch.distributed as dist
 
-__all__ = ["shard_range", "rows_per_rank", "gather_rows", "block_order", "hiding_exchange_pays", "split_exchange_plan", "PeerGather", "GlobalExchange"]
+__all__ = ["shard_range", "rows_per_rank", "gather_rows", "block_order", "hiding_exchange_pays", "pulls_first_pays", "PeerGather", "GlobalExchange"]
 
 
 def shard_range(n_items: int, world: int, rank: int) -> Tuple[int, int]:
@@ -63,28 +63,24 @@ def hiding_exchange_pays(total_rows: int, world: int, row_bytes: int, num_heads:
     return hidden < in_line
 
 
-def split_exchange_plan(total_rows: int, world: int, row_bytes: int, num_heads: int, head_dim: int,
-                        attn_tflops: float = 780.0, exchange_gbs: float = 380.0, exchange_hidden_gbs: float = 110.0):
-    """``(near_peers, hidden, ms)``: how to run the key / value exchange of a global layer, from the model of
-    :func:`hiding_exchange_pays` extended by one knob: the blocks of ``near_peers`` peers are fetched in line (fast, the GPU
-    has nothing else to do), the local rows then attend to those keys and their own while the other blocks arrive (slowed),
-    and to the rest afterwards.  ``near_peers = 0`` is the plain hidden exchange; ``hidden = False`` means that not hiding
-    anything (one in-line gather, one attention launch) is at least as short.  ``ms``: the modelled layer time of the choice.
-
-    100-frame scene (80,672 rows of 4 KB, 16 heads x 64): 2 to 4 GPUs -> ``(0, True)``; 8 GPUs -> ``(3, True)``: 0.32 ms in
-    line, then 2.07 ms of attention cover the 1.5 ms the other four blocks need: 4.5 ms per layer against 4.9 in line."""
+def pulls_first_pays(total_rows: int, world: int, row_bytes: int, num_heads: int, head_dim: int,
+                     attn_tflops: float = 780.0, exchange_gbs: float = 380.0, stolen: float = 0.3) -> bool:
+    """For the peer transport, where :func:`hiding_exchange_pays` says no: whether the layer is still shorter with the pulls
+    started BEFORE the attention to the local keys gets the machine (``GlobalExchange(pulls_first=True)``) than with the
+    exchange in line.  The driver's copies then take the SMs they want and run at their full speed, and the attention to the
+    local keys fills in behind them, delayed by about ``stolen`` of the exchange time (measured on 4 GPUs: a 0.77 ms exchange
+    instead of 2.1 ms, the local attention 2.43 instead of 2.20 ms).  Model: ``max(exchange, local attention + stolen x
+    exchange) + remote attention`` against ``exchange + attention``; 4.4 against 4.9 ms per layer for the 100-frame scene on
+    8 GPUs."""
     if world <= 1:
-        return 0, False, 0.0
+        return False
     block = total_rows / world
-    t_attn = lambda k: 4.0 * block * k * head_dim * num_heads / (attn_tflops * 1e12)  # noqa: E731 - local queries x k keys
-    t_alone = lambda n: n * block * row_bytes / (exchange_gbs * 1e9)  # noqa: E731
-    t_slow = lambda n: n * block * row_bytes / (exchange_hidden_gbs * 1e9)  # noqa: E731
-    best = (world - 1, False, t_alone(world - 1) + t_attn(total_rows))
-    for a in range(world - 1):
-        t = t_alone(a) + max(t_attn((1 + a) * block), t_slow(world - 1 - a)) + t_attn((world - 1 - a) * block) + 0.00005
-        if t < best[2]:
-            best = (a, True, t)
-    return best[0], best[1], best[2] * 1e3
+    bytes_in = (total_rows - block) * row_bytes
+    t_attn = lambda k: 4.0 * block * k * head_dim * num_heads / (attn_tflops * 1e12)  # noqa: E731
+    t_x = bytes_in / (exchange_gbs * 1e9)
+    in_line = t_x + t_attn(total_rows)
+    first = max(t_x, t_attn(block) + stolen * t_x) + t_attn(total_rows - block) + 0.00005
+    return first < in_line
 
 
 def gather_rows(local: torch.Tensor, rows: Sequence[int], group: Optional[dist.ProcessGroup] = None,
@@ -325,7 +321,7 @@ class GlobalExchange:
     """
 
     def __init__(self, rows: Sequence[int], rank: int, weight_all: torch.Tensor, group: Optional[dist.ProcessGroup] = None,
-                 gather=None, overlap: bool = False, comm_sms: int = 16, transport: str = "nccl", near_peers: int = 0):
+                 gather=None, overlap: bool = False, comm_sms: int = 16, transport: str = "nccl", pulls_first: bool = False):
         """``transport`` of the hidden exchange: ``"nccl"`` (an all-gather kernel beside the attention kernel) or ``"peer"``
         (:class:`PeerGather`: copy engines, built at the first :meth:`attend`; when a rank cannot set it up, all ranks
         fall back to NCCL together).  The in-line exchange (``overlap=False``) always uses NCCL.
@@ -336,15 +332,13 @@ class GlobalExchange:
         process group); otherwise its last CTAs wait for the attention kernel to end and nothing overlaps.  The peer
         transport needs two SMs for its two small kernels.
 
-        ``near_peers`` (peer transport): the blocks of that many peers are pulled IN LINE first (at the speed of an
-        exchange that has the GPU to itself); the local rows then attend to those keys and the local ones together while
-        the remaining peers' blocks arrive, and to the remaining keys afterwards.  For many ranks, where the attention to
-        the local keys alone is too short to cover the slowed exchange (:func:`split_exchange_plan`)."""
+        ``pulls_first`` (peer transport): the attention to the local keys is launched only once the peers have signalled, so
+        that the pulls and the attention become runnable together: the driver's copies then take the SMs they want and run
+        at the speed of an exchange that has the GPU to itself, and the attention fills in behind them.  For many ranks,
+        where the attention to the local keys is too short to cover a slowed exchange (:func:`pulls_first_pays`)."""
         if transport not in ("nccl", "peer"):
             raise ValueError(f"transport must be 'nccl' or 'peer', got {transport!r}")
-        if not (0 <= int(near_peers) < max(1, len(rows))):
-            raise ValueError(f"near_peers must be in [0, world - 1), got {near_peers}")
-        self.near_peers = int(near_peers)
+        self.pulls_first = bool(pulls_first)
         self.transport = transport
         self._peer_gather = None
         self.peer_error = None
@@ -436,20 +430,24 @@ class GlobalExchange:
         side = self._side
         if self.transport == "peer" and self._gather is None and self._peer_gather is None:
             self._setup_peer(kv)
-        if self._peer_gather is not None and self.near_peers > 0:
-            return self._attend_two_phase(q, kv, scale, use_bias)
         if self._peer_gather is not None:
             self._peer_gather.stage(kv)  # into this rank's window while the whole GPU is available (tens of microseconds)
         side.wait_stream(main)  # kv is ready, and the previous layer has finished reading the buffer
         ev = [torch.cuda.Event(enable_timing=self.events is not None) for _ in range(4)]
         with torch.cuda.stream(side):
             ev[0].record(side)
+            synced = None
             if self._peer_gather is not None:
-                gathered = self._peer_gather.exchange(self._buf, remote_first=True, include_local=False)
+                self._peer_gather.sync()
+                synced = torch.cuda.Event()
+                synced.record(side)
+                gathered = self._peer_gather.pull(self._buf, remote_first=True, include_local=False)
             else:
                 gathered = self.gather(kv, remote_first=True, out=self._buf)
             ev[1].record(side)
         kv.record_stream(side)
+        if synced is not None and self.pulls_first:
+            main.wait_event(synced)  # the pulls and the attention launch become runnable together
         bias_local, bias_remote = self.bias_local_remote(dtype) if use_bias else (None, None)
         sms = torch.cuda.get_device_properties(q.device).multi_processor_count
         free = 2 if self._peer_gather is not None else self.comm_sms
@@ -462,51 +460,6 @@ class GlobalExchange:
         remote = gathered[:n_remote]
         out_r, lse_r = cross_fwd(q, remote[:, 0], remote[:, 1], bias_remote, scale)
         combine(out, lse, out_r, lse_r, out_=out, lse_out=lse)
-        ev[3].record(main)
-        if self.events is not None:
-            self.events.append(ev)
-        return out
-
-    def _attend_two_phase(self, q: torch.Tensor, kv: torch.Tensor, scale: float, use_bias: bool) -> torch.Tensor:
-        """Peer transport with ``near_peers`` > 0.  Gathered buffer, remote-first order: ``[far peers | near peers | local]``.
-        In line: the near peers' blocks and the local one.  Then the local rows attend to ``[near | local]`` while the far
-        peers' blocks arrive on the side stream, then to ``[far]``; the two results are merged from their log-sum-exps."""
-        from .flash_attn_fwd_cuda import combine, cross_fwd, cta_limit
-        pg, dtype = self._peer_gather, q.dtype
-        world = len(self.rows)
-        order = block_order(world, self.rank, True)  # [rank + 1, ..., rank - 1, rank]
-        far, near = order[: world - 1 - self.near_peers], order[world - 1 - self.near_peers: world - 1]
-        n_far = sum(self.rows[r] for r in far)
-        main, side = torch.cuda.current_stream(q.device), self._side
-        ev = [torch.cuda.Event(enable_timing=self.events is not None) for _ in range(4)]
-        pg.stage(kv)
-        side.wait_stream(main)  # kv is staged, and the previous layer has finished reading the buffer
-        with torch.cuda.stream(side):
-            ev[0].record(side)
-            pg.sync()
-            pg.pull(self._buf, remote_first=True, include_local=True, peers=near)
-            near_done = torch.cuda.Event()
-            near_done.record(side)
-            pg.pull(self._buf, remote_first=True, include_local=False, peers=far)
-            ev[1].record(side)
-        kv.record_stream(side)
-        main.wait_event(near_done)
-        if use_bias:
-            b_local, b_remote = self.bias_local_remote(dtype)
-            key = ("two-phase", dtype)
-            if key not in self._bias_split:
-                self._bias_split[key] = (torch.cat([b_remote[n_far:], b_local]).contiguous(), b_remote[:n_far].contiguous())
-            bias_near, bias_far = self._bias_split[key]
-        else:
-            bias_near = bias_far = None
-        sms = torch.cuda.get_device_properties(q.device).multi_processor_count
-        near_rows, far_rows = self._buf[n_far:], self._buf[:n_far]
-        with cta_limit(sms - 2):  # the far pulls run beside this launch
-            out, lse = cross_fwd(q, near_rows[:, 0], near_rows[:, 1], bias_near, scale)
-        ev[2].record(main)
-        main.wait_event(ev[1])
-        out_f, lse_f = cross_fwd(q, far_rows[:, 0], far_rows[:, 1], bias_far, scale)
-        combine(out, lse, out_f, lse_f, out_=out, lse_out=lse)
         ev[3].record(main)
         if self.events is not None:
             self.events.append(ev)

@@ -149,6 +149,9 @@ def test_hiding_the_exchange_pays_only_while_local_attention_is_long():
     assert [hiding_exchange_pays(world=w, **big) for w in (1, 2, 4, 8)] == [False, True, True, False]
     assert not hiding_exchange_pays(total_rows=6448, world=2, row_bytes=1024, num_heads=4, head_dim=64)
     assert hiding_exchange_pays(world=8, exchange_hidden_gbs=380.0, **big)
+    from come_b200.dist import pulls_first_pays
+    assert pulls_first_pays(world=8, **big) and not pulls_first_pays(world=1, **big)
+    assert not pulls_first_pays(total_rows=6448, world=8, row_bytes=1024, num_heads=4, head_dim=64)  # nothing to hide behind
 
 
 def test_global_exchange_rejects_unknown_transport():

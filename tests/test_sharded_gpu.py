@@ -26,7 +26,7 @@ def _scene(frames, C, H, D, device):
 
 def _worker(rank, world, port, frames, q_out, mode):
     overlap, transport = mode != "inline", ("peer" if mode.startswith("overlap-peer") else "nccl")
-    near = 1 if mode == "overlap-peer-near1" else 0
+    pulls_first = mode == "overlap-peer-pulls-first"
     import torch.distributed as dist
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
@@ -37,7 +37,7 @@ def _worker(rank, world, port, frames, q_out, mode):
         C, H, D = 64 * 4, 4, 64
         x, conf, q, kv = _scene(frames, C, H, D, dev)
         chain = ShardedOpChain(frames, num_heads=H, head_dim=D, layer_kinds=["frame", "global"], overlap=overlap,
-                               transport=transport, near_peers=near)
+                               transport=transport, pulls_first=pulls_first)
         gp, lp = chain.build_plans(conf)
         r0, r1 = chain.row_begin, chain.row_begin + lp.total
         kinds = ("frame", "global", "global", "global")  # the global layer three times: both window slots and a reuse
@@ -53,16 +53,14 @@ def _worker(rank, world, port, frames, q_out, mode):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-@pytest.mark.parametrize("mode", ["inline", "overlap-nccl", "overlap-peer", "overlap-peer-near1"])
+@pytest.mark.parametrize("mode", ["inline", "overlap-nccl", "overlap-peer", "overlap-peer-pulls-first"])
 def test_sharded_chain_matches_single_gpu(mode):
     """In line, the exchange changes nothing: bit-identical frames.  Overlapped (local keys first, the gathered keys
     afterwards, merged from the log-sum-exps) the global layer differs by the rounding of the two partial outputs."""
     import torch.multiprocessing as mp
     from come_b200.chain import ShardedOpChain
     frames, C, H, D = 5, 256, 4, 64
-    world = 3 if mode == "overlap-peer-near1" else 2  # one peer's rows in line, the other's hidden: needs three ranks
-    if torch.cuda.device_count() < world:
-        pytest.skip(f"needs {world} GPUs")
+    world = 2
     ctx = mp.get_context("spawn")
     q_out = ctx.Queue()
     port = _free_port()
