@@ -147,13 +147,15 @@ class PeerGather:
     CUDA IPC handle (``come_peer_alloc`` / ``come_peer_open``).  One exchange: :meth:`stage` copies the local block into
     the own window; :meth:`exchange` tells the peers (``come_peer_signal``), waits until all of them have told us
     (``come_peer_wait``: bounded, raises bit 18 of the device status word instead of hanging), then pulls the peers'
-    blocks with ``come_peer_copy`` (plain ``cudaMemcpyAsync`` calls on a few side streams).  Apart from the two one-CTA
-    kernels nothing of it occupies an SM, so a persistent attention kernel on the same GPU keeps all but two SMs (an NCCL
+    blocks with ``come_peer_copy`` (plain ``cudaMemcpyAsync`` calls on a few side streams).  Nothing of this library but the
+    two one-CTA kernels occupies an SM, so a persistent attention kernel on the same GPU can keep all but two SMs (an NCCL
     all-gather beside it needs its CTAs resident: 16 SMs in this package's set-up).  Measured on B200s: alone an exchange
-    moves 360-470 GB/s into every GPU; beside the attention kernel 60-120 GB/s (NCCL, these copies and a copy kernel of
-    this library on 4 to 16 SMs were all slowed alike), which is why hiding the exchange pays only while the attention to
-    the local keys is long enough (:func:`hiding_exchange_pays`).  Construction is collective over ``group`` (the handles
-    travel through ``all_gather_object``).  Two slots suffice: a rank that signals exchange k + 1 has finished its pulls
+    moves 360-470 GB/s into every GPU; started while the attention kernel already holds the machine 60-120 GB/s (the
+    driver's peer copies behave like kernels that want SMs: NCCL, these copies and a copy kernel of this library on 4 to
+    16 SMs were all slowed alike), started together with it again 320-450 GB/s.  So the exchange hides behind a long
+    attention to the local keys (:func:`hiding_exchange_pays`) or is started together with a short one
+    (:func:`pulls_first_pays`).  Construction is collective over ``group`` (the handles travel through
+    ``all_gather_object``).  Two slots suffice: a rank that signals exchange k + 1 has finished its pulls
     of exchange k.
     """
 
