@@ -111,7 +111,7 @@ class ShardedOpChain:
 
     def build_plans(self, confidence_all: torch.Tensor):
         """``confidence_all [1, frames_total * H * W]`` (replicated) -> ``(global_plan, local_plan)``."""
-        from .dist import rows_per_rank
+        from .dist import rows_per_rank, shard_range
         H, W, gh, gw = self.grid
         mask_all = select_windows(confidence_all, 1, self.frames_total, H, W, gh, gw, self.threshold, "pairwise-rank", "frame")
         global_plan = MergePlan(mask_all, self.layout)
@@ -123,13 +123,13 @@ class ShardedOpChain:
         self.cu_global = torch.tensor([0, global_plan.total], dtype=torch.int32, device=mask_all.device)
         from .dist import GlobalExchange
         keep = self.exchange
+        # peer windows sized once for the largest block a rank can ever hold: all its frames unmerged
+        most_frames = max(shard_range(self.frames_total, self.world, r)[1] - shard_range(self.frames_total, self.world, r)[0]
+                          for r in range(self.world))
         self.exchange = GlobalExchange(self.rows, self.rank, global_plan.weight, self.group, overlap=self.overlap,
-                                       transport=self.transport, pulls_first=self.pulls_first)
-        if keep is not None and keep.rows == self.exchange.rows:  # same packing: keep the side stream, the gather buffer and the windows
-            self.exchange._side, self.exchange._buf, self.exchange.events = keep._side, keep._buf, keep.events
-            self.exchange._peer_gather, self.exchange.transport, self.exchange.peer_error = keep._peer_gather, keep.transport, keep.peer_error
-            if keep._side is not None:
-                self.exchange._cu_local = keep._cu_local
+                                       transport=self.transport, pulls_first=self.pulls_first,
+                                       peer_capacity_rows=most_frames * local_plan.tokens_per_frame)
+        self.exchange.adopt(keep)  # keep the side stream, the gather buffer and the windows across scenes
         return global_plan, local_plan
 
     def layer(self, global_plan: MergePlan, local_plan: MergePlan, x_local: torch.Tensor, q_local: torch.Tensor,

@@ -160,7 +160,11 @@ class PeerGather:
     """
 
     def __init__(self, rows: Sequence[int], rank: int, row_bytes: int, device: torch.device,
-                 group: Optional[dist.ProcessGroup] = None, pull_streams: int = 2, wait_limit_s: float = 20.0):
+                 group: Optional[dist.ProcessGroup] = None, pull_streams: int = 2, wait_limit_s: float = 20.0,
+                 capacity_rows: Optional[int] = None):
+        """``capacity_rows``: rows a slot of every window can hold (default: the largest block of ``rows``).  A caller whose
+        block heights change from scene to scene sizes the windows once for the largest block it can ever have and calls
+        :meth:`set_rows` per scene; all ranks must pass the same value."""
         import ctypes as C
 
         from . import _lib
@@ -170,7 +174,10 @@ class PeerGather:
         self.world, self.rank = len(self.rows), int(rank)
         self.row_bytes = int(row_bytes)
         self.device = torch.device(device)
-        self.slot_bytes = -(-max(self.rows) * self.row_bytes // 256) * 256
+        self.capacity_rows = int(capacity_rows) if capacity_rows is not None else max(self.rows)
+        if self.capacity_rows < max(self.rows):
+            raise ValueError(f"capacity_rows {self.capacity_rows} is smaller than the largest block {max(self.rows)}")
+        self.slot_bytes = -(-self.capacity_rows * self.row_bytes // 256) * 256
         self.flag_offset = 2 * self.slot_bytes
         self.limit_ns = int(wait_limit_s * 1e9)
         self.seq = 0
@@ -228,6 +235,13 @@ class PeerGather:
             if self._own is not None:
                 lib.come_peer_free(self._own)
         self._own, self._peer = None, [None] * self.world
+
+    def set_rows(self, rows: Sequence[int]) -> None:
+        """New block heights for the following exchanges (every rank calls it with the same list, between exchanges)."""
+        rows = [int(n) for n in rows]
+        if len(rows) != self.world or max(rows) > self.capacity_rows:
+            raise ValueError(f"need {self.world} block heights of at most {self.capacity_rows} rows, got {rows}")
+        self.rows = rows
 
     def stage(self, local: torch.Tensor) -> None:
         """First half of an exchange, on the current stream: this rank's block goes into the next slot of its window.
@@ -323,7 +337,8 @@ class GlobalExchange:
     """
 
     def __init__(self, rows: Sequence[int], rank: int, weight_all: torch.Tensor, group: Optional[dist.ProcessGroup] = None,
-                 gather=None, overlap: bool = False, comm_sms: int = 16, transport: str = "nccl", pulls_first: bool = False):
+                 gather=None, overlap: bool = False, comm_sms: int = 16, transport: str = "nccl", pulls_first: bool = False,
+                 peer_capacity_rows: Optional[int] = None):
         """``transport`` of the hidden exchange: ``"nccl"`` (an all-gather kernel beside the attention kernel) or ``"peer"``
         (:class:`PeerGather`: copy engines, built at the first :meth:`attend`; when a rank cannot set it up, all ranks
         fall back to NCCL together).  The in-line exchange (``overlap=False``) always uses NCCL.
@@ -341,6 +356,7 @@ class GlobalExchange:
         if transport not in ("nccl", "peer"):
             raise ValueError(f"transport must be 'nccl' or 'peer', got {transport!r}")
         self.pulls_first = bool(pulls_first)
+        self.peer_capacity_rows = peer_capacity_rows  # rows a window slot is sized for (default: the largest block now)
         self.transport = transport
         self._peer_gather = None
         self.peer_error = None
@@ -393,6 +409,31 @@ class GlobalExchange:
             return local
         return gather_rows(local, self.rows, self.group, out=out, remote_first=remote_first)
 
+    def adopt(self, previous: "GlobalExchange") -> None:
+        """Takes over the side stream, the gather buffer and the peer windows of the exchange object of the previous scene
+        (same ranks).  Windows that are too small for the new block heights are released and rebuilt at the next
+        :meth:`attend`; every rank adopts at the same point of its program."""
+        if previous is None or len(previous.rows) != len(self.rows):
+            return
+        self._side, self.events = previous._side, previous.events
+        if previous._side is not None:
+            self._cu_local = torch.tensor([0, self.rows[self.rank]], dtype=torch.int32, device=self.weight_all.device)
+        if previous._buf is not None and previous._buf.shape[0] == self.total:
+            self._buf = previous._buf
+        pg = previous._peer_gather
+        previous._peer_gather = None
+        if pg is None:
+            if previous.peer_error is not None:  # the transport could not be built before: do not try again every scene
+                self.transport, self.peer_error = previous.transport, previous.peer_error
+            return
+        if pg.capacity_rows >= max(self.rows):
+            pg.set_rows(self.rows)
+            self._peer_gather = pg
+        else:
+            torch.cuda.synchronize(pg.device)
+            dist.barrier(group=self.group)  # nobody still pulls out of a window that is about to go
+            pg.close()
+
     def close(self) -> None:
         """Releases the peer windows, if any (call on every rank once the last exchange has completed everywhere)."""
         if self._peer_gather is not None:
@@ -402,7 +443,8 @@ class GlobalExchange:
     def _setup_peer(self, kv: torch.Tensor) -> None:
         """Builds the copy-engine transport (collective; the ranks agree on the outcome inside).  If any rank failed, the
         exchange stays on NCCL on all of them and ``peer_error`` says why."""
-        pg = PeerGather(self.rows, self.rank, kv[0].numel() * kv.element_size(), kv.device, self.group)
+        pg = PeerGather(self.rows, self.rank, kv[0].numel() * kv.element_size(), kv.device, self.group,
+                        capacity_rows=self.peer_capacity_rows)
         if pg.ok:
             self._peer_gather = pg
         else:

@@ -43,6 +43,11 @@ def _worker(rank, world, port, frames, q_out, mode):
         kinds = ("frame", "global", "global", "global")  # the global layer three times: both window slots and a reuse
         outs = [chain.layer(gp, lp, x[chain.f_lo:chain.f_hi], q[r0:r1].contiguous(), kv[r0:r1].contiguous(), kind).cpu()
                 for kind in kinds]
+        # a second scene with other merge masks (other block heights) through the same chain object: the side stream, and
+        # with the peer transport the windows, are kept
+        gp, lp = chain.build_plans(1.0 - conf)
+        r0, r1 = chain.row_begin, chain.row_begin + lp.total
+        outs.append(chain.layer(gp, lp, x[chain.f_lo:chain.f_hi], q[r0:r1].contiguous(), kv[r0:r1].contiguous(), "global").cpu())
         from come_b200 import _lib
         status = _lib.device_status(clear=True)
         q_out.put((rank, chain.f_lo, chain.f_hi, outs, chain.exchange.transport, chain.exchange.peer_error, status))
@@ -77,12 +82,15 @@ def test_sharded_chain_matches_single_gpu(mode):
     gp, lp = single.build_plans(conf)
     P = lp.total
     want = [single.layer(gp, lp, x, q[:P].contiguous(), kv[:P].contiguous(), kind).cpu() for kind in ("frame", "global")]
-    want = [want[0], want[1], want[1], want[1]]
+    gp, lp = single.build_plans(1.0 - conf)
+    P = lp.total
+    second = single.layer(gp, lp, x, q[:P].contiguous(), kv[:P].contiguous(), "global").cpu()
+    want = [want[0], want[1], want[1], want[1], second]
     for rank, f_lo, f_hi, outs, transport, peer_error, status in results:
         assert status == 0, f"rank {rank}: device status word {status:#x}"
         if mode.startswith("overlap-peer"):
             assert transport == "peer", f"rank {rank} fell back to NCCL: {peer_error}"
-        for kind, got, ref in zip(("frame", "global", "global", "global"), outs, want):
+        for kind, got, ref in zip(("frame", "global", "global", "global", "global"), outs, want):
             tol = 2e-2 if (mode != "inline" and kind == "global") else 0.0
             torch.testing.assert_close(got, ref[f_lo:f_hi], atol=tol, rtol=0)
 
