@@ -54,6 +54,21 @@ def test_argument_errors_are_reported_without_a_gpu():
     assert rc == _lib.COME_ERR_ARG and "threshold" in _lib.last_error()
 
 
+def test_peer_entry_points_validate_before_touching_the_device():
+    """The peer-window entry points check their arguments first (no GPU needed to be told so)."""
+    from come_b200 import _lib
+    lib = _lib.lib()
+    assert lib.come_peer_alloc(0, None, None) == _lib.COME_ERR_ARG and "bytes" in _lib.last_error()
+    assert lib.come_peer_open(None, None) == _lib.COME_ERR_ARG
+    assert lib.come_peer_copy(None, None, -1, None) == _lib.COME_ERR_ARG
+    assert lib.come_peer_copy(None, None, 0, None) == _lib.COME_OK  # nothing to copy
+    assert lib.come_peer_signal(None, 2, 0, 1, None) == _lib.COME_ERR_ARG
+    flags = (ctypes.c_int32 * 4)()
+    assert lib.come_peer_wait(flags, 4, 7, 1, 10 ** 9, None) == _lib.COME_ERR_ARG and "rank" in _lib.last_error()
+    assert lib.come_peer_wait(flags, 4, 0, 1, 0, None) == _lib.COME_ERR_ARG and "limit_ns" in _lib.last_error()
+    assert lib.come_peer_close(None) == _lib.COME_OK and lib.come_peer_free(None) == _lib.COME_OK
+
+
 def test_python_validators_raise_value_error_on_cpu_tensors():
     import torch
     from come_b200 import token_merger as tm
