@@ -301,24 +301,19 @@ def run_frames(args):
     layers are local; a global layer all-gathers the merged K/V rows over NCCL on a side stream while the local query rows
     attend to the local keys, then attends them to the gathered rows and merges the two results (strong scaling: the
     scene is fixed, more GPUs shorten it).  At N = 1 there is no exchange and the global layer is one launch."""
-    from come_b200.dist import hiding_exchange_pays, pulls_first_pays
+    from come_b200.dist import hiding_exchange_pays
     frames = FRAMES_BY_WORKLOAD[args.workload]
     world_env = int(os.environ.get("WORLD_SIZE", "1"))
-    # auto: the form of the exchange that a model of a global layer says is shortest.  For the 100-frame scene: hidden behind
-    # the attention to the local keys on 2 to 4 GPUs; on 8 that attention is too short to cover an exchange that runs four
-    # times slower beside it: with peer windows the pulls then start first and the attention fills in behind them, with NCCL
-    # the exchange stays in line.
+    # auto: with peer windows the exchange is hidden behind the attention to the local keys at every N (measured best on 2, 4
+    # and 8 GPUs, even where that attention is shorter than the exchange); with NCCL it is hidden where the model of a global
+    # layer says it pays (2 to 4 GPUs for the 100-frame scene) and in line otherwise.
     rows_est = frames * (START + GRID * GRID - (GRID // WIN) ** 2 // 2 * (WIN * WIN - 1))  # half of the windows merged: 798 per frame
     shape = (rows_est, world_env, 2 * HEADS * HDIM * 2, HEADS, HDIM)
-    pulls_first = False
     if world_env <= 1 or args.overlap == "off":
         overlap = False
-    elif args.overlap == "on" or hiding_exchange_pays(*shape):
-        overlap = True
     else:
-        overlap = pulls_first = args.transport == "peer" and pulls_first_pays(*shape)
-    if args.pulls_first != "auto" and overlap and args.transport == "peer":
-        pulls_first = args.pulls_first == "on"
+        overlap = args.overlap == "on" or args.transport == "peer" or hiding_exchange_pays(*shape)
+    pulls_first = overlap and args.transport == "peer" and args.pulls_first == "on"
     torch, dist, world, rank, local, dev = init_ranks(cap_nccl_ctas=overlap and args.transport == "nccl")
     from come_b200 import _lib
     from come_b200.chain import ShardedOpChain
@@ -1161,7 +1156,7 @@ def main():
                          "100-frame scene through the whole alternating-attention stack (with its GEMMs), sharded by frame")
     ap.add_argument("--transport", default="peer", choices=["peer", "nccl"],
                     help="transport of the hidden K/V exchange at N > 1: copy engines over peer-mapped windows, or an NCCL all-gather")
-    ap.add_argument("--pulls-first", default="auto", choices=["auto", "on", "off"],
+    ap.add_argument("--pulls-first", default="off", choices=["on", "off"],
                     help="peer transport, hidden exchange: launch the attention to the local keys only once the pulls are runnable")
     ap.add_argument("--overlap", default="auto", choices=["auto", "on", "off"],
                     help="N > 1: hide the K/V all-gather of a global layer behind attention to the local keys (on), keep it in line "

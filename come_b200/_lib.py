@@ -19,7 +19,7 @@ EXPORTS = (
     "come_version", "come_last_error", "come_layout_info", "come_select_windows", "come_select_windows_ratios",
     "come_merge_plan_workspace_bytes", "come_merge_plan", "come_merge_plan_static", "come_merge", "come_merge_layernorm", "come_unmerge",
     "come_unmerge_strided", "come_unmerge_residual", "come_residual_layernorm", "come_suffix_add", "come_suffix_split",
-    "come_attn_varlen_fwd", "come_attn_varlen_fwd_rows", "come_attn_cross_fwd", "come_attn_combine", "come_attn_set_cta_limit", "come_qkv_prepare", "come_packed_positions",
+    "come_attn_varlen_fwd", "come_attn_varlen_fwd_rows", "come_attn_cross_fwd", "come_attn_cross_fwd_parts", "come_attn_combine", "come_attn_combine_parts", "come_attn_set_cta_limit", "come_qkv_prepare", "come_packed_positions",
     "come_device_status", "come_selftest_bounded_wait",
     "come_peer_alloc", "come_peer_open", "come_peer_close", "come_peer_free", "come_peer_copy", "come_peer_signal", "come_peer_wait",
 )
@@ -77,6 +77,8 @@ def lib() -> C.CDLL:
                                             vp, i64, vp, i32, vp]
     l.come_attn_cross_fwd.argtypes = [vp, vp, vp, i32, i64, i64, i32, i32, i64, i64, i64, vp, f32, vp, i64, vp, i32, vp]
     l.come_attn_combine.argtypes = [vp, vp, vp, vp, i32, i64, i32, i32, vp, vp, vp]
+    l.come_attn_cross_fwd_parts.argtypes = [vp, vp, vp, i32, i64, i64, i32, i32, i64, i64, i64, vp, f32, i32, vp, vp, i32, vp]
+    l.come_attn_combine_parts.argtypes = [vp, vp, i32, i32, i64, i32, i32, vp, vp, vp]
     l.come_attn_set_cta_limit.argtypes = [i32]
     l.come_qkv_prepare.argtypes = [vp, i32, i64, i32, i32, vp, vp, vp, vp, f32, vp, vp, vp, i64, vp, vp, vp]
     l.come_packed_positions.argtypes = [vp, vp, i64, C.POINTER(Layout), vp, vp]

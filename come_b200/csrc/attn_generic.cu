@@ -120,6 +120,42 @@ attn_combine_kernel(const T *__restrict__ oa, const float *__restrict__ la, cons
     }
 }
 
+// The same merge for `parts` results stored one behind the other (out_p = parts_out + p * part_o elements,
+// lse_p = parts_lse + p * H * rows floats): the shares of a launch that split the keys of its work items.
+template <typename T>
+__global__ void __launch_bounds__(256)
+attn_combine_parts_kernel(const T *__restrict__ parts_out, const float *__restrict__ parts_lse, int parts, int64_t part_o,
+                          int64_t rows, int H, int D, T *__restrict__ out, float *__restrict__ lse_out) {
+    const int per_head = D / 8;
+    const int64_t n = rows * H * per_head;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t rh = i / per_head;
+        const int64_t row = rh / H;
+        const int h = (int)(rh - row * H);
+        const int64_t l_at = (int64_t)h * rows + row;
+        float m = -INFINITY;
+        for (int p = 0; p < parts; ++p) m = fmaxf(m, parts_lse[(int64_t)p * H * rows + l_at]);
+        float acc[8] = {}, wsum = 0.0f;
+        if (m > -INFINITY) {
+            for (int p = 0; p < parts; ++p) {
+                const float w = expf(parts_lse[(int64_t)p * H * rows + l_at] - m);
+                const uint4 v = reinterpret_cast<const uint4 *>(parts_out + (int64_t)p * part_o)[i];
+                const T *x = reinterpret_cast<const T *>(&v);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) acc[e] += w * Elem<T>::to_f32(x[e]);
+                wsum += w;
+            }
+        }
+        const float inv = wsum > 0.0f ? 1.0f / wsum : 0.0f;
+        uint4 vo;
+        T *xo = reinterpret_cast<T *>(&vo);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) xo[e] = Elem<T>::from_f32(acc[e] * inv);
+        reinterpret_cast<uint4 *>(out)[i] = vo;
+        if (lse_out && (i - rh * per_head) == 0) lse_out[l_at] = (m > -INFINITY) ? m + logf(wsum) : -INFINITY;
+    }
+}
+
 }  // namespace come
 
 using namespace come;
@@ -128,7 +164,8 @@ static int attn_dispatch(const void *q_dev, const void *k_dev, const void *v_dev
                          int64_t q_begin, int64_t q_rows, int num_heads, int head_dim, int64_t q_row_stride,
                          int64_t k_row_stride, int64_t v_row_stride, const void *bias_dev, const int32_t *cu_seqlens_dev,
                          int num_segments, int max_seqlen, const int32_t *max_seqlen_dev, float softmax_scale, void *out_dev,
-                         int64_t out_row_stride, float *lse_dev, int backend, void *stream, bool q_free = false) {
+                         int64_t out_row_stride, float *lse_dev, int backend, void *stream, bool q_free = false, int k_parts = 1,
+                         int64_t part_o = 0) {
     COME_REQUIRE(dtype == COME_F16 || dtype == COME_BF16, "FlashAttention only support fp16 and bf16 data type");
     COME_REQUIRE(num_segments > 0, "batch size must be positive");
     COME_REQUIRE(total >= 0 && num_heads > 0, "total must be >= 0 and num_heads > 0");
@@ -153,6 +190,9 @@ static int attn_dispatch(const void *q_dev, const void *k_dev, const void *v_dev
     a.q_rs = q_row_stride; a.k_rs = k_row_stride; a.v_rs = v_row_stride; a.o_rs = out_row_stride;
     a.nseg = num_segments; a.max_seqlen = max_seqlen; a.max_seqlen_dev = max_seqlen_dev; a.scale = softmax_scale;
     a.q_free = q_free;
+    a.k_parts = k_parts;
+    a.part_o = part_o;
+    a.part_l = (int64_t)num_heads * q_rows;
 
     const bool tc_ok = attn_sm100_supported(a);
     if (backend == 2 && !tc_ok) {
@@ -160,6 +200,10 @@ static int attn_dispatch(const void *q_dev, const void *k_dev, const void *v_dev
         return COME_ERR_UNSUPPORTED;
     }
     if (tc_ok && backend != 1) return attn_sm100_launch(a, st);
+    if (k_parts > 1) {
+        set_error("attention with key shares runs on the tcgen05 kernel only (head_dim 64, TMA-compatible tensors, backend auto or tcgen05)");
+        return COME_ERR_UNSUPPORTED;
+    }
     if (dtype == COME_F16)
         return launch_generic<__half>(q_dev, k_dev, v_dev, q_row_stride, k_row_stride, v_row_stride, bias_dev, cu_seqlens_dev,
                                       num_segments, max_seqlen, num_heads, head_dim, softmax_scale, out_dev, out_row_stride,
@@ -200,6 +244,44 @@ extern "C" int come_attn_cross_fwd(const void *q_dev, const void *k_dev, const v
     return attn_dispatch(q_dev, k_dev, v_dev, dtype, kv_rows, 0, q_rows, num_heads, head_dim, q_row_stride, k_row_stride,
                          v_row_stride, bias_dev, nullptr, 1, max_len, nullptr, softmax_scale, out_dev, out_row_stride,
                          lse_dev, backend, stream, true);
+}
+
+extern "C" int come_attn_cross_fwd_parts(const void *q_dev, const void *k_dev, const void *v_dev, int dtype, int64_t q_rows,
+                                         int64_t kv_rows, int num_heads, int head_dim, int64_t q_row_stride,
+                                         int64_t k_row_stride, int64_t v_row_stride, const void *bias_dev, float softmax_scale,
+                                         int key_parts, void *out_parts_dev, float *lse_parts_dev, int backend, void *stream) {
+    COME_REQUIRE(kv_rows > 0 || q_rows == 0, "come_attn_cross_fwd_parts needs at least one key");
+    COME_REQUIRE(key_parts >= 1 && key_parts <= 64, "key_parts must be in [1, 64]");
+    COME_REQUIRE(lse_parts_dev != nullptr || q_rows == 0, "come_attn_cross_fwd_parts needs the log-sum-exp output");
+    const int max_len = (int)(kv_rows < (1ll << 31) ? kv_rows : 0);
+    const int64_t row_stride = (int64_t)num_heads * head_dim;  // every share is a contiguous [q_rows, num_heads, head_dim] block
+    return attn_dispatch(q_dev, k_dev, v_dev, dtype, kv_rows, 0, q_rows, num_heads, head_dim, q_row_stride, k_row_stride,
+                         v_row_stride, bias_dev, nullptr, 1, max_len, nullptr, softmax_scale, out_parts_dev, row_stride,
+                         lse_parts_dev, backend, stream, true, key_parts, q_rows * row_stride);
+}
+
+extern "C" int come_attn_combine_parts(const void *out_parts_dev, const float *lse_parts_dev, int key_parts, int dtype,
+                                       int64_t rows, int num_heads, int head_dim, void *out_dev, float *lse_out_dev,
+                                       void *stream) {
+    COME_REQUIRE(dtype == COME_F16 || dtype == COME_BF16, "come_attn_combine_parts: dtype must be COME_F16 or COME_BF16");
+    COME_REQUIRE(key_parts >= 1 && rows >= 0 && num_heads > 0 && head_dim > 0 && head_dim % 8 == 0, "come_attn_combine_parts: bad shape");
+    if (rows == 0) return COME_OK;
+    COME_REQUIRE(out_parts_dev && lse_parts_dev && out_dev, "come_attn_combine_parts: NULL pointer");
+    COME_REQUIRE(((uintptr_t)out_parts_dev & 15) == 0 && ((uintptr_t)out_dev & 15) == 0, "come_attn_combine_parts: outputs must be 16-byte aligned");
+    const int64_t n = rows * num_heads * (head_dim / 8);
+    int64_t blocks = (n + 255) / 256;
+    const int64_t cap = (int64_t)sm_count() * 8;
+    if (blocks > cap) blocks = cap;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int64_t part_o = rows * num_heads * head_dim;
+    if (dtype == COME_F16)
+        attn_combine_parts_kernel<__half><<<(unsigned)blocks, 256, 0, st>>>((const __half *)out_parts_dev, lse_parts_dev, key_parts, part_o,
+                                                                          rows, num_heads, head_dim, (__half *)out_dev, lse_out_dev);
+    else
+        attn_combine_parts_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, st>>>((const __nv_bfloat16 *)out_parts_dev, lse_parts_dev,
+                                                                                 key_parts, part_o, rows, num_heads, head_dim,
+                                                                                 (__nv_bfloat16 *)out_dev, lse_out_dev);
+    return check_launch("come_attn_combine_parts");
 }
 
 extern "C" int come_attn_combine(const void *out_a_dev, const float *lse_a_dev, const void *out_b_dev, const float *lse_b_dev,

@@ -336,6 +336,7 @@ struct WorkItem {
     int n_mt, n_kv;     // active query tiles (1 .. kTiles), key tiles
     bool ragged_tail;   // the last key tile is partial
     bool valid;
+    int kpart;          // which share of the keys this item covers (launches that split the keys of their items), else 0
 };
 
 // Query blocks of segment `seg` that hold rows of this launch.
@@ -351,9 +352,16 @@ __device__ __forceinline__ int segment_blocks(int seg, const int *__restrict__ c
 // inside the segment (attention of this GPU's rows to keys gathered from other GPUs); cu may then be NULL = [0, kv_total].
 template <bool kPrefix>
 __device__ __forceinline__ WorkItem decode_item(int item, int nblk_x, int nseg, const int *__restrict__ cu, int q_begin, int q_end,
-                                                const int *seg_prefix, int kv_total, bool q_free) {
+                                                const int *seg_prefix, int kv_total, bool q_free, int k_parts = 1) {
     WorkItem w;
     int bx, seg;
+    // Launches with k_parts > 1 (q_free only): consecutive items are the shares of the key tiles of one (head, block); every
+    // share writes its own output and log-sum-exp, merged afterwards.  The host picks k_parts so that no share is empty.
+    w.kpart = 0;
+    if (k_parts > 1) {
+        w.kpart = item % k_parts;
+        item /= k_parts;
+    }
     if constexpr (kPrefix) {
         const int per_head = seg_prefix[nseg];
         w.head = item / per_head;
@@ -384,6 +392,19 @@ __device__ __forceinline__ WorkItem decode_item(int item, int nblk_x, int nseg, 
     w.n_mt = min(kTiles, (w.q_hi - w.q_row0 + kBlockM - 1) / kBlockM);  // query tiles with at least one valid row
     w.n_kv = (seg_len + kBlockN - 1) / kBlockN;
     w.ragged_tail = (seg_len % kBlockN) != 0;
+    if (k_parts > 1) {
+        const int per_part = (w.n_kv + k_parts - 1) / k_parts;
+        const int t0 = w.kpart * per_part, t1 = min(w.n_kv, t0 + per_part);
+        if (t0 >= t1) {
+            w.valid = false;
+        } else {
+            const int s0 = w.s0;
+            w.s0 = s0 + t0 * kBlockN;
+            w.s1 = min(w.s1, s0 + t1 * kBlockN);
+            w.n_kv = t1 - t0;
+            w.ragged_tail = ((w.s1 - w.s0) % kBlockN) != 0;
+        }
+    }
     return w;
 }
 
@@ -398,7 +419,8 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                       const __grid_constant__ CUtensorMap map_v, const void *__restrict__ bias_ptr,
                       const int *__restrict__ cu, float scale_log2, float inv_scale, void *__restrict__ out_ptr, int64_t o_rs,
                       float *__restrict__ lse, int q_begin, int q_end, int nblk_x, int nseg, int num_heads,
-                      const int *__restrict__ max_len_dev, unsigned int *__restrict__ status, int kv_total, int q_free_flag) {
+                      const int *__restrict__ max_len_dev, unsigned int *__restrict__ status, int kv_total, int q_free_flag,
+                      int k_parts, long long part_o, long long part_l) {
     using T = typename std::conditional<kBF16, __nv_bfloat16, __half>::type;
     extern __shared__ uint8_t smem_raw[];
     SharedStorage &sh = *reinterpret_cast<SharedStorage *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -446,7 +468,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         __syncthreads();
     }
     const int *seg_prefix = use_prefix ? prefix_table : nullptr;
-    const int total_items = use_prefix ? prefix_table[nseg] * num_heads : nblk_x * nseg * num_heads;
+    const int total_items = (use_prefix ? prefix_table[nseg] * num_heads : nblk_x * nseg * num_heads) * k_parts;
     const bool has_bias = bias_ptr != nullptr;
     const bool q_free = q_free_flag != 0;
     // a key tile needs the bias step when there is a bias, or when it is the partial last tile (masking)
@@ -512,7 +534,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         int slab_it = 0;       // bias slab ring position, advanced once per key tile that uses the bias step
         int q_uses[kTiles] = {};  // items that loaded query tile t so far (buffer and phase of q_full / q_empty)
         for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
-            const WorkItem w = decode_item<kPrefix>(item, nblk_x, nseg, cu, q_begin, q_end, seg_prefix, kv_total, q_free);
+            const WorkItem w = decode_item<kPrefix>(item, nblk_x, nseg, cu, q_begin, q_end, seg_prefix, kv_total, q_free, k_parts);
             if (!w.valid) continue;
             if (lane == 0) {
                 for (int t = 0; t < w.n_mt && ok; ++t) {
@@ -592,7 +614,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         const long long tr_start = clock64();
 #endif
         for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
-            const WorkItem w = decode_item<kPrefix>(item, nblk_x, nseg, cu, q_begin, q_end, seg_prefix, kv_total, q_free);
+            const WorkItem w = decode_item<kPrefix>(item, nblk_x, nseg, cu, q_begin, q_end, seg_prefix, kv_total, q_free, k_parts);
             if (!w.valid) continue;
             if (t >= w.n_mt) {
                 // This query tile is empty in this item: release the K/V and slab slots without using them, so that the
@@ -728,7 +750,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         const long long tr_start = clock64();
 #endif
         for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
-            const WorkItem w = decode_item<kPrefix>(item, nblk_x, nseg, cu, q_begin, q_end, seg_prefix, kv_total, q_free);
+            const WorkItem w = decode_item<kPrefix>(item, nblk_x, nseg, cu, q_begin, q_end, seg_prefix, kv_total, q_free, k_parts);
             if (!w.valid || t >= w.n_mt) continue;
             const int n_kv = w.n_kv;
             const int row = w.q_row0 + t * kBlockM + r;
@@ -861,7 +883,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
 #pragma unroll
                         for (int i = 0; i < 32; i += 2)
                             pk[c * 16 + i / 2] = pack2<kBF16>(__uint_as_float(o[c][i]) * inv, __uint_as_float(o[c][i + 1]) * inv);
-                    T *dst_row = reinterpret_cast<T *>(out_ptr) + (int64_t)(row - q_begin) * o_rs + (int64_t)w.head * kHeadDim;
+                    T *dst_row = reinterpret_cast<T *>(out_ptr) + (int64_t)w.kpart * part_o + (int64_t)(row - q_begin) * o_rs + (int64_t)w.head * kHeadDim;
                     if ((reinterpret_cast<uintptr_t>(dst_row) & 31) == 0) {
 #pragma unroll
                         for (int i = 0; i < 32; i += 8)
@@ -874,7 +896,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
 #pragma unroll
                         for (int i = 0; i < 32; i += 4) dst[i / 4] = make_uint4(pk[i], pk[i + 1], pk[i + 2], pk[i + 3]);
                     }
-                    if (lse) lse[(int64_t)w.head * (q_end - q_begin) + (row - q_begin)] = (m_ref + log2f(l)) * kLn2;
+                    if (lse) lse[(int64_t)w.kpart * part_l + (int64_t)w.head * (q_end - q_begin) + (row - q_begin)] = (m_ref + log2f(l)) * kLn2;
                 }
             }
             TRACE_END(7);
@@ -1036,7 +1058,17 @@ int attn_sm100_launch(const AttnArgs &a, cudaStream_t stream) {
     const int64_t q_rows = a.q_end - a.q_begin;
     const int64_t span = a.q_free ? q_rows : (a.max_seqlen < q_rows ? a.max_seqlen : q_rows);  // most query rows any segment can own here
     const int nblk_x = (int)((span + kTiles * kBlockM - 1) / (kTiles * kBlockM));
-    const int64_t items = (int64_t)nblk_x * a.nseg * a.H;
+    const int k_parts = a.k_parts > 1 ? a.k_parts : 1;
+    if (k_parts > 1) {
+        // shares of the key tiles of every item: one segment whose keys all query rows attend to; no share may be empty
+        const int64_t tiles = (a.total + kBlockN - 1) / kBlockN, per_part = (tiles + k_parts - 1) / k_parts;
+        if (!a.q_free || a.lse == nullptr || (int64_t)(k_parts - 1) * per_part >= tiles) {
+            set_error("attention with %d key shares needs the one-segment cross form, a log-sum-exp output and at least one "
+                      "key tile per share (%lld tiles)", k_parts, (long long)tiles);
+            return COME_ERR_ARG;
+        }
+    }
+    const int64_t items = (int64_t)nblk_x * a.nseg * a.H * k_parts;
     if (items <= 0) return COME_OK;
     if (items >= (1ll << 31)) {
         set_error("come_attn_varlen_fwd: %lld work items do not fit 32 bits", (long long)items);
@@ -1053,7 +1085,8 @@ int attn_sm100_launch(const AttnArgs &a, cudaStream_t stream) {
         attn_fwd_sm100_kernel<BF16, PREFIX><<<grid, kThreads, smem, stream>>>(mq, mk, mv, a.bias, a.cu, scale_log2, inv_scale, a.out, \
                                                                               a.o_rs, a.lse, (int)a.q_begin, (int)a.q_end, nblk_x,   \
                                                                               a.nseg, a.H, a.max_seqlen_dev, status, (int)a.total,   \
-                                                                              a.q_free ? 1 : 0);                                     \
+                                                                              a.q_free ? 1 : 0, k_parts, (long long)a.part_o,        \
+                                                                              (long long)a.part_l);                                  \
     } while (0)
     if (a.dtype == COME_BF16) {
         if (with_table) COME_ATTN_LAUNCH(true, true, 0);

@@ -18,6 +18,10 @@ struct AttnArgs {
     const int *max_seqlen_dev;  // optional device-resident bound of the longest segment (tightens the work list)
     float scale;
     bool q_free;  // one segment; every query row attends to all of its keys wherever the row lies (cu may be NULL = [0, total])
+    // q_free launches may split the key tiles of every work item into k_parts shares (more, shorter items: for launches
+    // with few items per SM).  Share p writes out + p * part_o (elements) and lse + p * part_l (floats).
+    int k_parts = 1;
+    int64_t part_o = 0, part_l = 0;
 };
 
 // True when the tensor-core kernel can take the problem (head_dim 64, TMA-compatible addresses and strides).

@@ -160,7 +160,7 @@ class PeerGather:
     """
 
     def __init__(self, rows: Sequence[int], rank: int, row_bytes: int, device: torch.device,
-                 group: Optional[dist.ProcessGroup] = None, pull_streams: int = 2, wait_limit_s: float = 20.0,
+                 group: Optional[dist.ProcessGroup] = None, pull_streams: int = 7, wait_limit_s: float = 20.0,
                  capacity_rows: Optional[int] = None):
         """``capacity_rows``: rows a slot of every window can hold (default: the largest block of ``rows``).  A caller whose
         block heights change from scene to scene sizes the windows once for the largest block it can ever have and calls
@@ -454,7 +454,7 @@ class GlobalExchange:
     def attend(self, q: torch.Tensor, kv: torch.Tensor, scale: float, use_bias: bool = True) -> torch.Tensor:
         """Global attention of this rank's query rows ``q [rows, H, D]`` to the keys / values of ALL ranks, of which this
         rank holds ``kv [rows, 2, H, D]`` (key rows ``kv[:, 0]``, value rows ``kv[:, 1]``).  Returns ``[rows, H, D]``."""
-        from .flash_attn_fwd_cuda import combine, cross_fwd, cta_limit, varlen_fwd_rows
+        from .flash_attn_fwd_cuda import combine, cross_fwd_balanced, cta_limit, varlen_fwd_rows
         dtype = q.dtype
         kv = kv.contiguous()
         if not self.overlap:
@@ -496,13 +496,13 @@ class GlobalExchange:
         sms = torch.cuda.get_device_properties(q.device).multi_processor_count
         free = 2 if self._peer_gather is not None else self.comm_sms
         with cta_limit(sms - free if 0 < free < sms else 0):  # the exchange's kernels keep their SMs
-            out, lse = varlen_fwd_rows(q, kv[:, 0], kv[:, 1], self._cu_local, n_local, bias_local, scale, 0)
+            out, lse = cross_fwd_balanced(q, kv[:, 0], kv[:, 1], bias_local, scale)  # the local rows are the only keys here
         ev[2].record(main)
         main.wait_event(ev[1])
         if self._peer_gather is None and gathered.data_ptr() != self._buf.data_ptr():  # a stand-in gather allocated its own result on the side stream
             gathered.record_stream(main)
         remote = gathered[:n_remote]
-        out_r, lse_r = cross_fwd(q, remote[:, 0], remote[:, 1], bias_remote, scale)
+        out_r, lse_r = cross_fwd_balanced(q, remote[:, 0], remote[:, 1], bias_remote, scale)
         combine(out, lse, out_r, lse_r, out_=out, lse_out=lse)
         ev[3].record(main)
         if self.events is not None:

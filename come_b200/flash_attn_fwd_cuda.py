@@ -8,12 +8,15 @@ ignored.
 """
 from __future__ import annotations
 
+import threading
+
 import torch
 
 from . import _lib
 from ._torch_util import dtype_code, ptr, stream_ptr
 
-__all__ = ["varlen_fwd", "varlen_fwd_w_perkey_bias", "varlen_fwd_rows", "cross_fwd", "combine"]
+__all__ = ["varlen_fwd", "varlen_fwd_w_perkey_bias", "varlen_fwd_rows", "cross_fwd", "cross_fwd_balanced", "plan_tail_split",
+           "combine"]
 
 BACKEND_AUTO, BACKEND_CUDA_CORE, BACKEND_TCGEN05 = 0, 1, 2
 _backend = BACKEND_AUTO
@@ -30,15 +33,19 @@ class cta_limit:
     """``with cta_limit(n):`` the tensor-core attention launches of this thread inside the block use at most ``n`` CTAs
     (``come_attn_set_cta_limit``), leaving the other SMs to a kernel that runs beside them; ``n <= 0``: no limit."""
 
+    current = threading.local()  # the limit in force in this thread (0: none), for callers that size their launches by it
+
     def __init__(self, max_ctas: int):
         self.max_ctas = max(int(max_ctas), 0)
 
     def __enter__(self):
         _lib.check(_lib.lib().come_attn_set_cta_limit(self.max_ctas))
+        cta_limit.current.value = self.max_ctas
         return self
 
     def __exit__(self, *exc):
         _lib.check(_lib.lib().come_attn_set_cta_limit(0))
+        cta_limit.current.value = 0
         return False
 
 
@@ -256,6 +263,59 @@ def cross_fwd(q_rows, k, v, perkey_bias, softmax_scale, out_=None):
             k.stride(0), v.stride(0), ptr(perkey_bias), float(softmax_scale), ptr(out), out.stride(0), ptr(lse), _backend,
             stream_ptr(q_rows.device)))
     return [out, lse]
+
+
+_ROWS_PER_ITEM = 384  # query rows of a work item of the tensor-core kernel (three 128-row tiles)
+
+
+def plan_tail_split(rows: int, num_heads: int, kv_rows: int, ctas: int):
+    """``(main_rows, key_parts)`` for a one-segment attention launch of ``rows`` query rows on ``ctas`` persistent CTAs.
+    The kernel's work items (384 query rows of one head, all keys) are dealt round-robin; when the last round holds only a
+    few items, the query blocks behind the full rounds are better run with their keys split ``key_parts`` ways (one short
+    round that fills the machine).  ``key_parts == 1``: leave the launch alone (``main_rows == rows``)."""
+    blocks = -(-rows // _ROWS_PER_ITEM)
+    items = blocks * num_heads
+    full = items // max(ctas, 1)
+    if ctas <= 0 or full == 0 or items == full * ctas:
+        return rows, 1
+    main_blocks = (full * ctas) // num_heads
+    tail_items = (blocks - main_blocks) * num_heads
+    tiles = -(-kv_rows // 64)
+    parts = min(64, ctas // max(tail_items, 1), tiles)
+    if main_blocks == 0 or parts < 2:
+        return rows, 1
+    per = -(-tiles // parts)
+    parts = -(-tiles // per)  # no empty share
+    return (main_blocks * _ROWS_PER_ITEM, parts) if parts >= 2 else (rows, 1)
+
+
+def cross_fwd_balanced(q_rows, k, v, perkey_bias, softmax_scale, out_=None):
+    """:func:`cross_fwd` with the launch shaped by :func:`plan_tail_split`: the query blocks that would make up a nearly
+    empty last round are attended with their keys split into shares (``come_attn_cross_fwd_parts``) and merged from the
+    shares' log-sum-exps (``come_attn_combine_parts``).  Those rows differ from the one-launch result by the rounding of
+    the shares' outputs.  Returns ``[out [rows, H, D], softmax_lse [H, rows]]``."""
+    rows, num_heads, head_size = q_rows.shape
+    ctas = getattr(cta_limit.current, "value", 0) or torch.cuda.get_device_properties(q_rows.device).multi_processor_count
+    main_rows, parts = plan_tail_split(rows, num_heads, k.shape[0], ctas) if head_size == 64 else (rows, 1)
+    if parts == 1:
+        return cross_fwd(q_rows, k, v, perkey_bias, softmax_scale, out_=out_)
+    out = out_ if out_ is not None else torch.empty((rows, num_heads, head_size), dtype=q_rows.dtype, device=q_rows.device)
+    if not out.is_contiguous():
+        raise RuntimeError("out_ must be contiguous")
+    _, lse_main = cross_fwd(q_rows[:main_rows], k, v, perkey_bias, softmax_scale, out_=out[:main_rows])
+    tail = q_rows[main_rows:]
+    n_tail = rows - main_rows
+    out_parts = torch.empty((parts, n_tail, num_heads, head_size), dtype=q_rows.dtype, device=q_rows.device)
+    lse_parts = torch.empty((parts, num_heads, n_tail), dtype=torch.float32, device=q_rows.device)
+    lse_tail = torch.empty((num_heads, n_tail), dtype=torch.float32, device=q_rows.device)
+    with torch.cuda.device(q_rows.device):
+        lib, st = _lib.lib(), stream_ptr(q_rows.device)
+        _lib.check(lib.come_attn_cross_fwd_parts(
+            ptr(tail), ptr(k), ptr(v), dtype_code(q_rows.dtype), n_tail, k.shape[0], num_heads, head_size, tail.stride(0),
+            k.stride(0), v.stride(0), ptr(perkey_bias), float(softmax_scale), parts, ptr(out_parts), ptr(lse_parts), _backend, st))
+        _lib.check(lib.come_attn_combine_parts(ptr(out_parts), ptr(lse_parts), parts, dtype_code(q_rows.dtype), n_tail, num_heads,
+                                               head_size, ptr(out[main_rows:]), ptr(lse_tail), st))
+    return [out, torch.cat([lse_main, lse_tail], dim=1)]
 
 
 def combine(out_a, lse_a, out_b, lse_b, out_=None, lse_out=None):

@@ -304,6 +304,22 @@ int come_attn_combine(const void *out_a_dev, const float *lse_a_dev, const void 
                       int dtype, int64_t rows, int num_heads, int head_dim, void *out_dev, float *lse_out_dev, void *stream);
 
 /*
+ * come_attn_cross_fwd with the keys of every work item split into key_parts shares (1 .. 64, each at least one 64-key tile):
+ * for launches with few work items per SM, where the last round of the persistent kernel would run with most SMs idle
+ * (448 items on 148 SMs take four rounds; their last block of query rows split nine ways fills one short round instead).
+ * Share p attends the query rows to its share of the keys and writes out_parts[p] ([key_parts, q_rows, num_heads, head_dim]
+ * contiguous, dtype) and lse_parts[p] ([key_parts, num_heads, q_rows] float32, required); come_attn_combine_parts merges them
+ * like come_attn_combine (same rounding remark).  tcgen05 kernel only (head_dim 64), else COME_ERR_UNSUPPORTED.
+ * No counterpart in the reference.
+ */
+int come_attn_cross_fwd_parts(const void *q_dev, const void *k_dev, const void *v_dev, int dtype, int64_t q_rows,
+                              int64_t kv_rows, int num_heads, int head_dim, int64_t q_row_stride, int64_t k_row_stride,
+                              int64_t v_row_stride, const void *bias_dev, float softmax_scale, int key_parts,
+                              void *out_parts_dev, float *lse_parts_dev, int backend, void *stream);
+int come_attn_combine_parts(const void *out_parts_dev, const float *lse_parts_dev, int key_parts, int dtype, int64_t rows,
+                            int num_heads, int head_dim, void *out_dev, float *lse_out_dev, void *stream);
+
+/*
  * Pre-attention preparation of the packed qkv tensor [total, 3, num_heads, head_dim], in place, one pass:
  *   q, k <- LayerNorm over head_dim (affine gamma / beta; skipped when the four pointers are NULL)
  *   q, k <- 2-D rotary position embedding with integer positions pos[total, 2] = (y, x): the first head_dim/2

@@ -428,3 +428,74 @@ def _oracle_cross(q, k, v, bias, scale):
     l = p.sum(axis=-1, keepdims=True)
     out = np.einsum("hij,jhd->ihd", p / l, v.astype(np.float64))
     return out.astype(np.float32), (m + np.log(l))[:, :, 0].astype(np.float32)
+
+
+@pytest.mark.parametrize("rows,kv_rows,parts", [(300, 1000, 2), (500, 1037, 7), (129, 4096, 64), (40, 130, 3)])
+def test_cross_attention_with_key_shares(backend, rows, kv_rows, parts):
+    """``come_attn_cross_fwd_parts`` + ``come_attn_combine_parts``: the keys of every work item split into shares (ragged
+    last share, more shares than some launches have items), every share against the oracle on its own key range, the merged
+    result against the oracle over all keys (bar 2e-2) and against the one-launch kernel."""
+    from come_b200 import _lib, flash_attn_fwd_cuda as fa
+    from come_b200._torch_util import dtype_code, ptr, stream_ptr
+    backend(fa.BACKEND_TCGEN05)
+    H, D = 3, 64
+    rng = np.random.default_rng(rows + 13 * kv_rows + parts)
+    q = gi.round_kind(rng.standard_normal((rows, H, D), dtype=np.float32), "bf16")
+    kv = gi.round_kind(rng.standard_normal((kv_rows, 2, H, D), dtype=np.float32), "bf16")
+    bias = gi.round_kind(np.log(np.where(rng.random(kv_rows) < 0.2, 9.0, 1.0)).astype(np.float32), "bf16")
+    tq, tkv, tb = to_dev(q, "bf16"), to_dev(kv, "bf16"), to_dev(bias, "bf16")
+    scale = D ** -0.5
+    tiles = -(-kv_rows // 64)
+    per = -(-tiles // parts)
+    parts = -(-tiles // per)  # the caller's duty: no empty share
+    out_parts = torch.full((parts, rows, H, D), 7.0, dtype=torch.bfloat16, device="cuda")
+    lse_parts = torch.full((parts, H, rows), 7.0, dtype=torch.float32, device="cuda")
+    lib, st = _lib.lib(), stream_ptr(tq.device)
+    k, v = tkv[:, 0], tkv[:, 1]
+    _lib.check(lib.come_attn_cross_fwd_parts(ptr(tq), ptr(k), ptr(v), dtype_code(tq.dtype), rows, kv_rows, H, D, tq.stride(0),
+                                             k.stride(0), v.stride(0), ptr(tb), scale, parts, ptr(out_parts), ptr(lse_parts),
+                                             fa.BACKEND_TCGEN05, st))
+    for p in range(parts):
+        lo, hi = p * per * 64, min(kv_rows, (p + 1) * per * 64)
+        want = _oracle_cross(q, kv[lo:hi, 0], kv[lo:hi, 1], bias[lo:hi], scale)
+        assert np.abs(to_np(out_parts[p]) - want[0]).max() <= 2e-2, p
+        np.testing.assert_allclose(to_np(lse_parts[p]), want[1], atol=2e-3, rtol=1e-3)
+    out = torch.empty((rows, H, D), dtype=torch.bfloat16, device="cuda")
+    lse = torch.empty((H, rows), dtype=torch.float32, device="cuda")
+    _lib.check(lib.come_attn_combine_parts(ptr(out_parts), ptr(lse_parts), parts, dtype_code(tq.dtype), rows, H, D, ptr(out),
+                                           ptr(lse), st))
+    want = _oracle_cross(q, kv[:, 0], kv[:, 1], bias, scale)
+    assert np.abs(to_np(out) - want[0]).max() <= 2e-2
+    np.testing.assert_allclose(to_np(lse), want[1], atol=2e-3, rtol=1e-3)
+    one, one_lse = fa.cross_fwd(tq, k, v, tb, scale)
+    assert (out.float() - one.float()).abs().max().item() <= 2e-2
+    torch.testing.assert_close(lse, one_lse, atol=2e-3, rtol=1e-3)
+    # refusals: an empty share, no log-sum-exp output
+    rc = lib.come_attn_cross_fwd_parts(ptr(tq), ptr(k), ptr(v), dtype_code(tq.dtype), rows, 64, H, D, tq.stride(0), k.stride(0),
+                                       v.stride(0), ptr(tb), scale, 2, ptr(out_parts), ptr(lse_parts), fa.BACKEND_TCGEN05, st)
+    assert rc == _lib.COME_ERR_ARG and "share" in _lib.last_error()
+    _check_status()
+
+
+def test_balanced_cross_attention_splits_the_last_round():
+    """10,534 query rows x 16 heads are 448 work items: three rounds on 148 CTAs and four items.  ``cross_fwd_balanced``
+    runs the last query block with its keys in shares (nine for 70,138 keys); the result must agree with the one-launch kernel (rounding of
+    the shares' outputs only) and the plan must be the expected one."""
+    from come_b200 import flash_attn_fwd_cuda as fa
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    rows, kv_rows, H, D = 10534, 4096, 16, 64
+    main_rows, parts = fa.plan_tail_split(rows, H, kv_rows, sms)
+    if sms == 148:
+        assert (main_rows, parts) == (10368, 8)  # 64 key tiles in shares of 8 tiles (nine shares would leave one empty)
+        assert fa.plan_tail_split(rows, H, 70138, sms) == (10368, 9) and fa.plan_tail_split(9656, H, 70138, sms) == (9656, 1)
+    g = torch.Generator(device="cuda").manual_seed(3)
+    q = torch.randn((rows, H, D), device="cuda", generator=g).bfloat16()
+    kv = torch.randn((kv_rows, 2, H, D), device="cuda", generator=g).bfloat16()
+    bias = torch.where(torch.rand(kv_rows, device="cuda", generator=g) < 0.2, 9.0, 1.0).log().bfloat16()
+    one, one_lse = fa.cross_fwd(q, kv[:, 0], kv[:, 1], bias, D ** -0.5)
+    out, lse = fa.cross_fwd_balanced(q, kv[:, 0], kv[:, 1], bias, D ** -0.5)
+    assert tuple(out.shape) == (rows, H, D) and tuple(lse.shape) == (H, rows)
+    assert torch.equal(out[:main_rows], one[:main_rows]) and torch.equal(lse[:, :main_rows], one_lse[:, :main_rows])
+    assert (out.float() - one.float()).abs().max().item() <= 1e-2
+    torch.testing.assert_close(lse, one_lse, atol=2e-3, rtol=1e-3)
+    _check_status()
