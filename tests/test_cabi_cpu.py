@@ -106,3 +106,22 @@ def test_jagged_suffix_roundtrip_cpu():
     back, suf = ext.split_suffix(1)
     assert torch.equal(back.tokens, jag.tokens) and torch.equal(back.weight, jag.weight)
     assert torch.equal(back.offset, jag.offset) and torch.equal(suf, suffix)
+
+
+def test_tail_split_plan_is_a_pure_function_of_the_shape():
+    """``plan_tail_split``: 10,534 rows x 16 heads = 448 work items -> the 27 query blocks of three full rounds on 148 CTAs
+    in one launch, the last block with its keys in nine shares; launches whose last round is at least half full, launches
+    shorter than one round and exact multiples are left alone; no share is ever empty."""
+    from come_b200.flash_attn_fwd_cuda import plan_tail_split
+    assert plan_tail_split(10534, 16, 70138, 148) == (10368, 9)
+    assert plan_tail_split(10534, 16, 4096, 148) == (10368, 8)     # 64 key tiles: shares of 8 tiles
+    assert plan_tail_split(9656, 16, 71016, 148) == (9656, 1)      # 416 items: the third round is 81 % full
+    assert plan_tail_split(807, 16, 807, 148) == (807, 1)          # 48 items: less than one round
+    assert plan_tail_split(384 * 37, 4, 5000, 148) == (384 * 37, 1)  # 148 items: one exact round
+    assert plan_tail_split(80672, 16, 80672, 146) == (80256, 4)
+    for rows in range(1, 30000, 997):
+        for kv in (64, 65, 1000, 70138):
+            main_rows, parts = plan_tail_split(rows, 16, kv, 148)
+            tiles = -(-kv // 64)
+            assert 0 < main_rows <= rows and main_rows % 384 == 0 or main_rows == rows
+            assert parts == 1 or (2 <= parts <= 64 and (parts - 1) * -(-tiles // parts) < tiles)
