@@ -924,6 +924,19 @@ def run_only(args):
         ln = torch.nn.LayerNorm(CH, eps=1e-6).to(dev).to(dt)
         fn = lambda: residual_layernorm(x, br, gamma, ln)  # noqa: E731
         out.update(frames=args.frames, tokens=rows, dtype=args.dtype, bytes=4 * rows * CH * x.element_size() + 3 * CH * x.element_size())
+    elif args.only == "cross":
+        # Attention of `--rows` query rows to `--tokens` keys that do not contain them (what a rank of the sharded scene runs
+        # on the gathered rows of the other ranks): `--balanced 0` one launch, `--balanced 1` the launch cut by
+        # plan_tail_split (the last query blocks with their keys in shares).
+        from come_b200 import flash_attn_fwd_cuda as fa
+        q = torch.randn((args.rows, HEADS, HDIM), device=dev, generator=g).bfloat16()
+        kv = torch.randn((args.tokens, 2, HEADS, HDIM), device=dev, generator=g).bfloat16()
+        bias = torch.where(torch.rand(args.tokens, device=dev, generator=g) < 0.1, 9.0, 1.0).log().bfloat16()
+        call = fa.cross_fwd_balanced if args.balanced else fa.cross_fwd
+        fn = lambda: call(q, kv[:, 0], kv[:, 1], bias, HDIM ** -0.5)  # noqa: E731
+        sms = torch.cuda.get_device_properties(dev).multi_processor_count
+        out.update(rows=args.rows, keys=args.tokens, flops=4.0 * args.rows * args.tokens * HDIM * HEADS,
+                   work_items=-(-args.rows // 384) * HEADS, plan=list(fa.plan_tail_split(args.rows, HEADS, args.tokens, sms)) if args.balanced else None)
     elif args.only == "prepare":
         # q/k LayerNorm + 2-D rotary embedding + log(count) bias on the packed rows of `frames` half-merged frames
         from come_b200.qkv import RotaryPositionEmbedding2D, prepare_packed_self_attention_qkv
@@ -1132,7 +1145,7 @@ def run_aggregator(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--only", choices=["attn", "merge", "unmerge", "merge_ln", "unmerge_res", "prepare", "residual_ln", "direct", "aggregator", "model"],
+    ap.add_argument("--only", choices=["attn", "cross", "merge", "unmerge", "merge_ln", "unmerge_res", "prepare", "residual_ln", "direct", "aggregator", "model"],
                     help="run one kernel family on one size and exit; aggregator = the alternating-attention stack, merged against "
                          "unmerged; model = the same comparison from the images on (patch encoder with its merge after block 14 + aggregator)")
     ap.add_argument("--depth", type=int, default=24, help="--only aggregator: frame/global block pairs")
@@ -1143,6 +1156,8 @@ def main():
     ap.add_argument("--dtype", default="f32", choices=["f32", "bf16"], help="--only merge/unmerge: element type")
     ap.add_argument("--tokens", type=int, default=6384, help="--only attn with --segments 1: segment length")
     ap.add_argument("--segments", type=int, default=1, help="--only attn: 1 = one segment, else ragged 1374-8k sweep")
+    ap.add_argument("--rows", type=int, default=10534, help="--only cross: query rows (the keys are --tokens)")
+    ap.add_argument("--balanced", type=int, default=1, help="--only cross: 1 = launch cut by plan_tail_split, 0 = one launch")
     ap.add_argument("--iters", type=int, default=3, help="--only: timed launches")
     ap.add_argument("--graph", action="store_true", help="--only: time the launches inside one CUDA graph (no host cost)")
     ap.add_argument("--gpus", type=int, default=1)
