@@ -298,9 +298,10 @@ def sharded_check(torch, dist, world, rank, dev, transport="nccl", hidden=True, 
 
 def run_frames(args):
     """The default arm: ONE scene of 100 frames (137,400 tokens before merging) sharded by frame over the ranks.  Frame
-    layers are local; a global layer all-gathers the merged K/V rows over NCCL on a side stream while the local query rows
-    attend to the local keys, then attends them to the gathered rows and merges the two results (strong scaling: the
-    scene is fixed, more GPUs shorten it).  At N = 1 there is no exchange and the global layer is one launch."""
+    layers are local; a global layer gathers the merged K/V rows of the other ranks (pulls out of peer-mapped windows, or an
+    NCCL all-gather) on a side stream while the local query rows attend to the local keys, then attends them to the gathered
+    rows and merges the two results (strong scaling: the scene is fixed, more GPUs shorten it).  At N = 1 there is no
+    exchange and the global layer is one launch."""
     from come_b200.dist import hiding_exchange_pays
     frames = FRAMES_BY_WORKLOAD[args.workload]
     world_env = int(os.environ.get("WORLD_SIZE", "1"))
