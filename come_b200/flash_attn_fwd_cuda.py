@@ -296,7 +296,8 @@ def cross_fwd_balanced(q_rows, k, v, perkey_bias, softmax_scale, out_=None):
     the shares' outputs.  Returns ``[out [rows, H, D], softmax_lse [H, rows]]``."""
     rows, num_heads, head_size = q_rows.shape
     ctas = getattr(cta_limit.current, "value", 0) or torch.cuda.get_device_properties(q_rows.device).multi_processor_count
-    main_rows, parts = plan_tail_split(rows, num_heads, k.shape[0], ctas) if head_size == 64 else (rows, 1)
+    # key shares exist in the tensor-core kernel only (head_dim 64, not with the CUDA-core kernel forced)
+    main_rows, parts = plan_tail_split(rows, num_heads, k.shape[0], ctas) if (head_size == 64 and _backend != BACKEND_CUDA_CORE) else (rows, 1)
     if parts == 1:
         return cross_fwd(q_rows, k, v, perkey_bias, softmax_scale, out_=out_)
     out = out_ if out_ is not None else torch.empty((rows, num_heads, head_size), dtype=q_rows.dtype, device=q_rows.device)
@@ -310,9 +311,13 @@ def cross_fwd_balanced(q_rows, k, v, perkey_bias, softmax_scale, out_=None):
     lse_tail = torch.empty((num_heads, n_tail), dtype=torch.float32, device=q_rows.device)
     with torch.cuda.device(q_rows.device):
         lib, st = _lib.lib(), stream_ptr(q_rows.device)
-        _lib.check(lib.come_attn_cross_fwd_parts(
+        rc = lib.come_attn_cross_fwd_parts(
             ptr(tail), ptr(k), ptr(v), dtype_code(q_rows.dtype), n_tail, k.shape[0], num_heads, head_size, tail.stride(0),
-            k.stride(0), v.stride(0), ptr(perkey_bias), float(softmax_scale), parts, ptr(out_parts), ptr(lse_parts), _backend, st))
+            k.stride(0), v.stride(0), ptr(perkey_bias), float(softmax_scale), parts, ptr(out_parts), ptr(lse_parts), _backend, st)
+        if rc == _lib.COME_ERR_UNSUPPORTED:  # tensors the tensor-core kernel cannot take (alignment, strides): one more plain launch
+            _, lse_tail = cross_fwd(tail, k, v, perkey_bias, softmax_scale, out_=out[main_rows:])
+            return [out, torch.cat([lse_main, lse_tail], dim=1)]
+        _lib.check(rc)
         _lib.check(lib.come_attn_combine_parts(ptr(out_parts), ptr(lse_parts), parts, dtype_code(q_rows.dtype), n_tail, num_heads,
                                                head_size, ptr(out[main_rows:]), ptr(lse_tail), st))
     return [out, torch.cat([lse_main, lse_tail], dim=1)]
