@@ -28,6 +28,8 @@ __all__ = [
     "quantile_linear",
     "select_windows",
     "attention_bias",
+    "attention_combine",
+    "attention_combine_parts",
     "perkey_bias_from_weight",
     "max_seqlen",
     "rope_tables",
@@ -384,6 +386,22 @@ def attention_combine(out_a, lse_a, out_b, lse_b):
     wa, wb = np.exp(la - m, dtype=np.float32), np.exp(lb - m, dtype=np.float32)
     out = (wa * np.asarray(out_a, np.float32) + wb * np.asarray(out_b, np.float32)) / (wa + wb)
     return out.astype(np.float32), (m + np.log(wa + wb))[:, :, 0].T.astype(np.float32)
+
+
+def attention_combine_parts(outs, lses):
+    """The same merge for any number of results: ``outs [S, rows, H, D]``, ``lses [S, H, rows]`` -> ``(out [rows, H, D],
+    lse [H, rows])`` with ``m = max_s lse_s``, ``w_s = exp(lse_s - m)``, ``out = sum_s w_s out_s / sum_s w_s`` (shares summed
+    in index order), ``lse = m + log(sum_s w_s)``; float32."""
+    outs, lses = np.asarray(outs, np.float32), np.asarray(lses, np.float32)
+    l = np.transpose(lses, (0, 2, 1))[:, :, :, None]  # [S, rows, H, 1]
+    m = l.max(axis=0)
+    acc = np.zeros(outs.shape[1:], np.float32)
+    wsum = np.zeros(m.shape, np.float32)
+    for s in range(outs.shape[0]):
+        w = np.exp(l[s] - m, dtype=np.float32)
+        acc = acc + w * outs[s]
+        wsum = wsum + w
+    return (acc / wsum).astype(np.float32), (m + np.log(wsum))[:, :, 0].T.astype(np.float32)
 
 
 # --------------------------------------------------------------------------------------------------------

@@ -467,6 +467,10 @@ def test_cross_attention_with_key_shares(backend, rows, kv_rows, parts):
     want = _oracle_cross(q, kv[:, 0], kv[:, 1], bias, scale)
     assert np.abs(to_np(out) - want[0]).max() <= 2e-2
     np.testing.assert_allclose(to_np(lse), want[1], atol=2e-3, rtol=1e-3)
+    from oracle import come_oracle as orc
+    ref_out, ref_lse = orc.attention_combine_parts(to_np(out_parts), to_np(lse_parts))  # the merge kernel alone
+    np.testing.assert_allclose(to_np(out), ref_out, atol=2e-6, rtol=2 ** -7)  # one rounding to bfloat16
+    np.testing.assert_allclose(to_np(lse), ref_lse, atol=1e-5, rtol=1e-6)
     one, one_lse = fa.cross_fwd(tq, k, v, tb, scale)
     assert (out.float() - one.float()).abs().max().item() <= 2e-2
     torch.testing.assert_close(lse, one_lse, atol=2e-3, rtol=1e-3)

@@ -332,3 +332,32 @@ def test_torch_cpu_attention_matches_the_c_oracle():
     full, full_lse = clib.attention_bias(qkv, bias, cu, D ** -0.5)
     np.testing.assert_allclose(part[5 + 10:5 + 50], full[5 + 10:5 + 50], atol=2e-6, rtol=1e-5)
     np.testing.assert_allclose(part_lse[:, 5 + 10:5 + 50], full_lse[:, 5 + 10:5 + 50], atol=2e-6, rtol=1e-5)
+
+
+def test_n_way_attention_merge_agrees_with_the_pairwise_one():
+    """``attention_combine_parts`` with two shares is ``attention_combine``; with more shares it reproduces attention over the
+    union of the key sets (numpy float64 reference on a small case)."""
+    from oracle import come_oracle as orc
+    rng = np.random.default_rng(11)
+    rows, H, D, kv, S = 7, 2, 8, 40, 4
+    q = rng.standard_normal((rows, H, D)).astype(np.float32)
+    k = rng.standard_normal((kv, H, D)).astype(np.float32)
+    v = rng.standard_normal((kv, H, D)).astype(np.float32)
+
+    def attend(lo, hi):
+        s = np.einsum("ihd,jhd->hij", q.astype(np.float64), k[lo:hi].astype(np.float64))
+        m = s.max(-1, keepdims=True)
+        p = np.exp(s - m)
+        l = p.sum(-1, keepdims=True)
+        return np.einsum("hij,jhd->ihd", p / l, v[lo:hi].astype(np.float64)).astype(np.float32), (m + np.log(l))[:, :, 0].astype(np.float32)
+
+    parts = [attend(i * 10, (i + 1) * 10) for i in range(S)]
+    outs, lses = np.stack([p[0] for p in parts]), np.stack([p[1] for p in parts])
+    out, lse = orc.attention_combine_parts(outs, lses)
+    want, want_lse = attend(0, kv)
+    np.testing.assert_allclose(out, want, atol=2e-6, rtol=1e-5)
+    np.testing.assert_allclose(lse, want_lse, atol=2e-6, rtol=1e-6)
+    two, two_lse = orc.attention_combine_parts(outs[:2], lses[:2])
+    ref, ref_lse = orc.attention_combine(outs[0], lses[0], outs[1], lses[1])
+    np.testing.assert_allclose(two, ref, atol=1e-7, rtol=1e-6)
+    np.testing.assert_allclose(two_lse, ref_lse, atol=1e-6, rtol=1e-6)
